@@ -1,0 +1,222 @@
+"""oracle.py: Python face of the CPU oracle. TEST INFRASTRUCTURE ONLY: imported by tests/, the smoke check and the
+benchmark's CPU-baseline leg, never by the product package.
+
+Two independent restatements of the reference's block-float quantiser live here so that they can be checked against
+each other and against the golden vectors: the C one (oracle.c, through ctypes) and a vectorised numpy one (this
+file). The numpy quantiser follows moe/moe8.py:117-154 of XylolabsInc/tensix-kernels, generalised from 3 mantissa bits
+(bfloat4_b, pinned) to 7 (bfloat8_b, PARITY UNPINNED: the reference has no vector for it; its quantiser is inside the
+third-party wheel ttnn==0.81.1).
+"""
+
+import ctypes
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+MB = {"bfp8": 7, "bfp4": 3}
+_LIB = None
+
+
+def build():
+    """Compile oracle.c into liboracle.so beside it (gcc)."""
+    subprocess.run(["make", "-s", "-C", str(HERE), "liboracle.so"], check=True)
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        so = HERE / "liboracle.so"
+        if not so.exists() or so.stat().st_mtime < (HERE / "oracle.c").stat().st_mtime:
+            build()
+        L = ctypes.CDLL(str(so))
+        L.orc_bf16_ceil.restype = ctypes.c_float
+        L.orc_bf16_ceil.argtypes = [ctypes.c_float]
+        L.orc_bf16_rne.restype = ctypes.c_uint16
+        L.orc_bf16_rne.argtypes = [ctypes.c_float]
+        L.orc_key.restype = ctypes.c_uint32
+        L.orc_key.argtypes = [ctypes.c_uint16]
+        L.orc_key_value.restype = ctypes.c_float
+        L.orc_key_value.argtypes = [ctypes.c_uint32]
+        _LIB = L
+    return _LIB
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _i64(v):
+    return ctypes.c_int64(int(v))
+
+
+# --- quantiser --------------------------------------------------------------------------------------------------------
+
+
+def quantise_c(w, fmt):
+    """w float32 [K, N] -> (exps uint8 [K, N/16], codes uint8 [K, N]) by oracle.c."""
+    w = np.ascontiguousarray(w, np.float32)
+    k, n = w.shape
+    assert n % 16 == 0
+    exps = np.zeros((k, n // 16), np.uint8)
+    codes = np.zeros((k, n), np.uint8)
+    lib().orc_quantise(_p(w), _i64(k), _i64(n), MB[fmt], _p(exps), _p(codes))
+    return exps, codes
+
+
+def quantise_np(w, fmt):
+    """The same in numpy (moe8.py:134-150 with mantissa bits mb)."""
+    mb = MB[fmt]
+    w = np.ascontiguousarray(w, np.float32)
+    k, n = w.shape
+    bits = w.view(np.uint32).reshape(k, n // 16, 16)
+    exp = (bits >> 23) & 0xFF
+    sign = bits >> 31
+    man = ((bits & 0x7FFFFF) | (1 << 23)).astype(np.int64)
+    shared = exp.max(axis=-1, keepdims=True)
+    diff = (shared - exp).astype(np.int64)
+    m = np.where(diff > 31, 0, man >> np.minimum(diff, 31))
+    shift = 24 - mb
+    rnd = m & ((1 << shift) - 1)
+    m = m >> shift
+    guard = m & 1
+    tie = 1 << (shift - 1)
+    m = m + ((rnd > tie) | ((rnd == tie) & (guard == 1)))
+    m = np.minimum(m, (1 << mb) - 1)
+    m = np.where(exp == 0, 0, m)
+    s = np.where(m == 0, 0, sign)
+    codes = ((s << mb) | m).astype(np.uint8).reshape(k, n)
+    return shared.reshape(k, n // 16).astype(np.uint8), codes
+
+
+def dequantise(exps, codes, fmt):
+    """(exps, codes) -> float32 [K, N] (moe8.py:157-169: unit exponent 126 + mantissa bits)."""
+    mb = MB[fmt]
+    mag = (codes & ((1 << mb) - 1)).astype(np.float32)
+    sgn = np.where((codes >> mb) & 1, np.float32(-1), np.float32(1))
+    e = np.repeat(exps.astype(np.int32), 16, axis=1) - (126 + mb)
+    return (sgn * np.ldexp(mag, e)).astype(np.float32)
+
+
+def tiles(exps, codes, fmt):
+    """The reference's tile bytes [K/32, N/32, 576 | 1088] (moe8.py:125-154)."""
+    mb = MB[fmt]
+    k, n = codes.shape
+    tb = 64 + (512 if mb == 3 else 1024)
+    out = np.zeros((k // 32, n // 32, tb), np.uint8)
+    lib().orc_tiles(_p(np.ascontiguousarray(exps)), _p(np.ascontiguousarray(codes)), _i64(k), _i64(n), mb, _p(out))
+    return out
+
+
+def block_float(t, fmt):
+    """float [K, N] rounded to fmt's grid, float32: what a weight of that dtype holds (linear.py:159-163). bf16: RNE."""
+    if fmt == "bf16":
+        return torch.as_tensor(t).float().to(torch.bfloat16).float().numpy()
+    e, c = quantise_np(np.asarray(t, np.float32), fmt)
+    return dequantise(e, c, fmt)
+
+
+def native_values(t, fmt, col_scale=False):
+    """What linear.native_weight makes of a float [out, in] matrix (linear.py:144-156): (held values float32 [K, N],
+    scales float32 [N])."""
+    t = torch.as_tensor(t).float()
+    c = bf16_ceil(t.abs().amax(dim=1).clamp(min=1e-8)) if col_scale else torch.ones(t.shape[0])
+    wt = (t / c[:, None]).T.contiguous()
+    return block_float(wt.numpy(), fmt), c.numpy()
+
+
+def bf16_ceil(s):
+    """linear.py:110-114."""
+    b = s.to(torch.bfloat16).float()
+    up = (b.view(torch.int32) + 0x10000).view(torch.float32)
+    return torch.where(b >= s, b, up)
+
+
+def interleave_glu(gate, up):
+    """linear.py:122-130."""
+    o, i = gate.shape
+    return torch.stack([gate.reshape(o // 32, 32, i), up.reshape(o // 32, 32, i)], dim=1).reshape(2 * o, i)
+
+
+# --- matmul and output stages -----------------------------------------------------------------------------------------
+
+
+def reference(x, w, scale=None):
+    """linear.py:166-169, the reference's torch path: bf16(x) @ w (* scale) in float32."""
+    y = x.to(torch.bfloat16).float() @ torch.as_tensor(w).float()
+    return y * torch.as_tensor(scale).float()[None, :] if scale is not None else y
+
+
+def ref64(x, wk, scale=None):
+    """test_dense_reader.py:56-58: the same in float64, returned as float32."""
+    y = x.to(torch.bfloat16).double() @ torch.as_tensor(wk).double()
+    return (y * torch.as_tensor(scale).double()[None, :] if scale is not None else y).float()
+
+
+def matmul_f64(x, w):
+    """oracle.c's own loop: x torch [M, K] (rounded to bf16), w float32 [K, N] -> float64 numpy [M, N]."""
+    xb = x.to(torch.bfloat16).contiguous().view(torch.int16).numpy().view(np.uint16)
+    w = np.ascontiguousarray(w, np.float32)
+    m, k = xb.shape
+    y = np.zeros((m, w.shape[1]), np.float64)
+    lib().orc_matmul_f64(_p(np.ascontiguousarray(xb)), _i64(m), _i64(k), _p(w), _i64(w.shape[1]), _p(y))
+    return y
+
+
+def epilogue(acc, mode, acc2=None, act=0, scale=None, scale2=None, res=None, res32=None):
+    """oracle.c's output stages on float64 sums acc [M, N]; mode: 0 plain/scale, 1 GLU interleaved, 2 GLU two sums,
+    3 residual (res: torch bf16 [M, N]), 4 fp32 (+ res32). Returns float64."""
+    acc = np.ascontiguousarray(acc, np.float64)
+    m, n = acc.shape
+    out = np.zeros((m, n // 2 if mode == 1 else n), np.float64)
+    f = lambda a: None if a is None else np.ascontiguousarray(a, np.float32)  # noqa: E731
+    sc, sc2, r32 = f(scale), f(scale2), f(res32)
+    a2 = None if acc2 is None else np.ascontiguousarray(acc2, np.float64)
+    rb = None if res is None else np.ascontiguousarray(res.to(torch.bfloat16).contiguous().view(torch.int16).numpy().view(np.uint16))
+    q = lambda a: None if a is None else _p(a)  # noqa: E731
+    lib().orc_epilogue(_p(acc), q(a2), _i64(m), _i64(n), mode, act, q(sc), q(sc2), q(rb), q(r32), _p(out))
+    return out
+
+
+# --- top-k records ----------------------------------------------------------------------------------------------------
+
+
+def bf16_bits(t):
+    return t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def keys_of(bits):
+    """dense_writer.cpp:215 on uint16 bf16 bits."""
+    b = bits.astype(np.uint32)
+    return (b ^ (0x8000 | (0x7FFF & (0 - (b >> 15))))) & 0xFFFF
+
+
+def topk_canonical(y_row_bits, n, k, base):
+    """oracle.c's canonical top-k (key descending, index ascending) of one row: (keys uint32 [k], idx uint32 [k])."""
+    y = np.ascontiguousarray(y_row_bits, np.uint16)
+    keys, idx = np.zeros(k, np.uint32), np.zeros(k, np.uint32)
+    lib().orc_topk_canonical(_p(y), _i64(n), k, ctypes.c_uint32(base), _p(keys), _p(idx))
+    return keys, idx
+
+
+def topk_scan_ref(y_row_bits, c0, c1, n, k, base):
+    """The reference writer's running top-k over columns [c0, c1) (dense_writer.cpp:185-232)."""
+    y = np.ascontiguousarray(y_row_bits, np.uint16)
+    keys, idx = np.zeros(k, np.uint32), np.zeros(k, np.uint32)
+    lib().orc_topk_scan_ref(_p(y), _i64(c0), _i64(c1), _i64(n), k, ctypes.c_uint32(base), _p(keys), _p(idx))
+    return keys, idx
+
+
+def records_host(t, rows, k):
+    """Decode a records tensor as linear.py:753-768 does: (values float32 [rows, records * k], indices int64 [rows,
+    records * k]); an empty slot (key 0) gives -inf and -1. Written over numpy words here."""
+    words = t.contiguous().view(torch.int32).numpy().view(np.uint32).reshape(-1, 2, rows, k)
+    keys = np.transpose(words[:, 0], (1, 0, 2)).reshape(rows, -1)
+    idx = np.transpose(words[:, 1], (1, 0, 2)).reshape(rows, -1).astype(np.int64)
+    raw = np.where(keys >= 0x8000, keys & 0x7FFF, ~keys & 0xFFFF).astype(np.uint32) << 16
+    vals = raw.view(np.float32).copy()
+    vals[keys == 0] = -np.inf
+    idx[(keys == 0) | (idx == 0xFFFFFFFF)] = -1
+    return torch.from_numpy(vals), torch.from_numpy(idx)

@@ -1,0 +1,90 @@
+"""gen_golden.py: makes tests/golden/*.npz from the reference's own host functions.
+
+Run in a container that has the reference checkout (its path as argv[1], default /root/reference):
+
+    python tests/golden/gen_golden.py [/path/to/tensix-kernels]
+
+The reference's modules import ttnn at the top; a MagicMock stands in for it, which is enough for the pure-host
+functions used here: moe.moe8.bfp4_tiles / bfp4_values (the only in-tree statement of the block-float quantiser, pinned
+bit for bit to ttnn's BFP4_b conversion by moe/tests/test_moe.py:84-89), dense_reader.linear.records_host /
+interleave_glu / bf16_ceil / reference, common.device.split_arg. Nothing of the reference is copied: only the
+outputs of running it on seeded inputs are stored.
+"""
+
+import hashlib
+import sys
+from pathlib import Path
+from unittest.mock import MagicMock
+
+import numpy as np
+import torch
+
+ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+sys.modules["ttnn"] = MagicMock()
+sys.path.insert(0, str(ref))
+from common import device as cdev  # noqa: E402
+from dense_reader import linear as rlin  # noqa: E402
+from moe import moe8  # noqa: E402
+
+out = Path(__file__).resolve().parent
+sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()  # noqa: E731
+
+
+def retile(v):
+    """bfp4_values' [KT, NT, 32, 32] -> [K, N]."""
+    kt, nt = v.shape[:2]
+    return np.ascontiguousarray(v.transpose(0, 2, 1, 3).reshape(kt * 32, nt * 32))
+
+
+# 1. the quantiser: the input of moe/tests/test_moe.py:84-88, and test_formats' weight as [K, N]
+g = torch.Generator().manual_seed(0)
+w1 = torch.randn(256, 512, generator=g) * 0.02
+w1[3, 5], w1[7, 9] = 0.0, -1e-30
+t1 = moe8.bfp4_tiles(w1)
+v1 = retile(moe8.bfp4_values(t1))
+g = torch.Generator().manual_seed(2)
+w2 = (torch.randn(2048, 1024, generator=g) * 0.02).T.contiguous()
+t2 = moe8.bfp4_tiles(w2)
+# 2. rounding cases in one face row (ties to even, the clamp without an exponent bump, signs, flush of small values)
+w3 = torch.zeros(32, 32)
+w3[0, :16] = torch.tensor([1.0, 0.5, 0.25, 0.125, 0.0625, 0.1875, 0.3125, 0.4375, 0.5625, 0.6875, 0.9375, 0.96875,
+                           -0.96875, -0.0624, 1.9999, -1.0])
+v3 = retile(moe8.bfp4_values(moe8.bfp4_tiles(w3)))
+# 3. wide exponent spread inside face rows, denormals, zeros, huge values
+g = torch.Generator().manual_seed(5)
+w4 = torch.randn(64, 64, generator=g) * torch.exp2(torch.randint(-40, 40, (64, 64), generator=g).float())
+w4[0, :16] = 0.0
+w4[1, 0] = 1e-40
+w4[2, 3] = 3e38
+t4 = moe8.bfp4_tiles(w4)
+np.savez_compressed(
+    out / "quantiser_bfp4.npz",
+    w1_sha=sha(w1.numpy()), t1=t1, v1_sha=sha(v1), v1_row0=v1[0, :64],
+    t2_sha=sha(t2), t2_head=t2[:2, :2],
+    w3=w3.numpy(), v3=v3,
+    w4=w4.numpy(), t4=t4, v4=retile(moe8.bfp4_values(t4)),
+)
+
+# 4. host helpers of dense_reader/linear.py
+gate = torch.arange(128.0).reshape(64, 2)
+il = rlin.interleave_glu(gate, -gate)
+s = torch.tensor([0.0201, 1.0, 3.14159, 1e-8, 0.7, 123.456, 65504.0])
+bits = torch.tensor([0x3FC0, 0xC000, 0x0000, 0x8000, 0x7F80, 0xFF80, 0x0001, 0x8001, 0x4049], dtype=torch.int32)
+keys = torch.where(bits >= 0x8000, (~bits) & 0xFFFF, bits | 0x8000)
+rec = torch.zeros(3, 2 * 2 * 4, dtype=torch.int32)  # 3 records of rows 2, k 4
+rec[0, :8] = keys[:8]
+rec[0, 8:] = torch.arange(100, 108)
+rec[1, :4] = keys[5:9]
+rec[1, 8:12] = torch.tensor([7, 0xFFFFFFFF - (1 << 32), 9, 10], dtype=torch.int64).to(torch.int32)
+vals, idx = rlin.records_host(rec, 2, 4)
+x = torch.randn(3, 64, generator=torch.Generator().manual_seed(9))
+wk = torch.randn(64, 32, generator=torch.Generator().manual_seed(10)) * 0.02
+sc = torch.rand(32, generator=torch.Generator().manual_seed(11)) + 0.5
+np.savez_compressed(
+    out / "host_helpers.npz",
+    il=il.numpy(), ceil_in=s.numpy(), ceil_out=rlin.bf16_ceil(s).numpy(),
+    split=np.array([cdev.split_arg(True, v) for v in (0.5, 0.6, 2 / 3, 0.75)] + [cdev.split_arg(False)], np.int64),
+    bf16_bits=bits.numpy(), keys=keys.numpy(), rec=rec.numpy(), rec_vals=vals.numpy(), rec_idx=idx.numpy(),
+    x=x.numpy(), wk=wk.numpy(), sc=sc.numpy(), ref=rlin.reference(x, wk).numpy(), ref_sc=rlin.reference(x, wk, sc).numpy(),
+)
+print("t1", sha(t1), "v1", sha(v1), "t2", sha(t2))
