@@ -1,0 +1,127 @@
+/* tkd.h: C-ABI of libtkd, the B200 (sm_100a) implementation of the dense_reader path of XylolabsInc/tensix-kernels.
+ *
+ * Plain pointers and sizes only. Unless a comment says "host", every pointer is a device pointer of the current CUDA
+ * device, and `stream` is a cudaStream_t passed as void* (NULL: the default stream). Every function returns 0 or a
+ * TKD_ERR_* code (tkd_error_string); codes above 1000 are 1000 + a cudaError_t. Nothing here synchronises with the
+ * device unless it says so, and none of the functions taking a stream allocates device memory.
+ *
+ * Each entry point names the piece of the reference it stands in for (file:line within that project).
+ */
+#ifndef TKD_H
+#define TKD_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* weight formats: ttnn.bfloat8_b, ttnn.bfloat4_b, ttnn.bfloat16 (dense_reader/linear.py:49-50) */
+#define TKD_FMT_BFP8 0
+#define TKD_FMT_BFP4 1
+#define TKD_FMT_BF16 2
+
+#define TKD_OK 0
+#define TKD_ERR_BAD_ARG 1      /* a shape, pointer or option the path does not take */
+#define TKD_ERR_UNSUPPORTED 2  /* a legal request this build has no kernel for */
+#define TKD_ERR_TIMEOUT 3      /* written to the status word by a kernel whose bounded wait gave up */
+#define TKD_ERR_WORKSPACE 4    /* workspace missing or too small */
+#define TKD_ERR_WIDE 5         /* exponents inside one group of 16 columns spread further than the stream encodes */
+#define TKD_ERR_CUDA 1000
+
+/* output stages (dense_reader/kernels/dense_compute.cpp:200-356) */
+#define TKD_EPI_PLAIN 0     /* y = bf16(acc * scale) (scale optional)                    :302-356 */
+#define TKD_EPI_GLU_IL 1    /* act(gate) * up over an interleave_glu weight, N / 2 wide  :200-257 */
+#define TKD_EPI_GLU2 2      /* the same over two weights (w the gate's, w_up), N wide    :200-257, GLU2 */
+#define TKD_EPI_RESIDUAL 3  /* y = bf16(acc + bf16 residual)                             :100-120, 258-301 */
+#define TKD_EPI_OUT32 4     /* y = acc in float32 (+ a float32 residual, an extension)   :302-332 */
+
+#define TKD_DT_NONE 0
+#define TKD_DT_BF16 1
+#define TKD_DT_F32 2
+
+int tkd_version(void);
+const char* tkd_error_string(int code);
+
+/* --- weights: stands in for ttnn.from_torch(dtype=bfloat8_b|bfloat4_b|bfloat16) as native_weight and block_float call
+ * it (dense_reader/linear.py:155, :162) and for ttnn.to_torch on such a weight (tests' held(),
+ * dense_reader/tests/test_dense_reader.py:47-49). ------------------------------------------------------------------ */
+
+/* N rounded up to the 16 columns that share an exponent. */
+int64_t tkd_padded_cols(int64_t n);
+/* Bytes of the packed stream of a [K, N] weight: K * padded N * (1.0625 | 0.5625 | 2) for K a multiple of 32 (64 for
+ * bfloat4_b, whose last super-atom is zero-filled otherwise). */
+int64_t tkd_packed_bytes(int fmt, int64_t k, int64_t n);
+
+/* float32 -> the format's numbers, before any re-layout. src: orient 0 a row-major [N, K] matrix (torch [out, in]),
+ * orient 1 a row-major [K, N]. col_div (or NULL): [N] divisors applied first (native_weight's col_scale). exps
+ * [K, npad / 16] bytes (unused for bf16); codes [K, npad]: bytes sign << mantissa_bits | magnitude, or uint16 bf16 bits
+ * for TKD_FMT_BF16. */
+int tkd_quantise(int fmt, const float* src, int orient, int64_t k, int64_t n, const float* col_div, uint8_t* exps,
+                 void* codes, void* stream);
+/* canonical numbers -> the HBM stream. packed: tkd_packed_bytes; emax: npad / 16 bytes (unused for bf16); info: one
+ * int32, zeroed by the caller; bit 0 is set when the weight is "wide" (then tkd_matmul answers TKD_ERR_WIDE). */
+int tkd_pack(int fmt, int64_t k, int64_t n, const uint8_t* exps, const void* codes, void* packed, uint8_t* emax,
+             int32_t* info, void* stream);
+/* the stream back as float32 [K, npad]: the values the weight holds */
+int tkd_unpack(int fmt, int64_t k, int64_t n, const void* packed, const uint8_t* emax, float* out, void* stream);
+
+/* --- the op: stands in for ttnn.generic_op on the program dense_reader/linear.py:828-1070 (_launch) builds from
+ * plan() (:187-382): dense_reader.cpp + dense_compute.cpp + dense_writer.cpp. --------------------------------------- */
+
+typedef struct {
+    const void* w;          /* packed stream (the gate's with TKD_EPI_GLU2) */
+    const void* w_up;       /* the up weight's stream with TKD_EPI_GLU2, else NULL */
+    const uint8_t* emax;    /* tkd_pack's side array of w (NULL for bf16) */
+    const uint8_t* emax_up;
+    int64_t n;              /* real columns of w */
+    int64_t out_col0;       /* first output column of this block in out, in elements */
+} TkdBlock;
+
+typedef struct {
+    int32_t fmt;            /* TKD_FMT_* of every block */
+    int32_t m;              /* activation rows, 1..32 */
+    int64_t k;
+    const void* x;          /* bf16 [m, k], ldx elements a row, 16-byte aligned rows */
+    int64_t ldx;
+    int32_t nblocks;        /* 1, or 2..4 for a block list (linear.py:615-624) */
+    int32_t epilogue;       /* TKD_EPI_* */
+    TkdBlock block[4];
+    int32_t act;            /* GLU: 0 silu, 1 gelu_tanh (common/kernels/dense_ops.h:44-59) */
+    int32_t scale_dtype;    /* TKD_DT_NONE | BF16 (the reference's scale tensor) | F32 (extension) */
+    const void* scale;      /* [n] per output column of w */
+    const void* scale_up;   /* [n] of w_up (an extension: scales with a GLU) */
+    const void* residual;   /* [m, >= n]: bf16 with TKD_EPI_RESIDUAL, float32 with TKD_EPI_OUT32 (or NULL) */
+    int64_t ldr;
+    int32_t residual_dtype;
+    int32_t out_dtype;      /* TKD_DT_BF16, or TKD_DT_F32 with TKD_EPI_OUT32 */
+    void* out;              /* [m, ldo] */
+    int64_t ldo;
+    /* top-k records (dense_reader/kernels/dense_writer.cpp:185-258; record layout linear.py:771-785): one record per
+     * topk_unit columns, record slot0 + unit; a record is keys[rows][k] then indices[rows][k], uint32 each. Within a
+     * record: key descending, index ascending among equal keys. topk_k 0: none. */
+    void* records;
+    int32_t topk_k, topk_rows, topk_unit, topk_slot0, topk_write_y;
+    uint32_t topk_base;
+    int64_t topk_n;
+    void* workspace;        /* tkd_matmul_workspace bytes, zeroed once by the caller before its first use */
+    uint64_t workspace_bytes;
+    int32_t* status;        /* one int32 (or NULL): a kernel writes TKD_ERR_TIMEOUT here if a wait gives up */
+    int32_t ks;             /* k per slice, 0: default (a multiple of 256) */
+    int32_t max_ctas;       /* 0: one per SM */
+} TkdMatmul;
+
+/* What the launch of a TkdMatmul looks like: the counterpart of the dict plan() returns (linear.py:360-382). */
+typedef struct {
+    int32_t ks, nslices, panels, grid, stages, xslots, chunk_k, smem_bytes;
+    int64_t items, weight_bytes;
+} TkdPlan;
+
+int tkd_matmul_plan(const TkdMatmul* a, TkdPlan* plan);
+int tkd_matmul_workspace(const TkdMatmul* a, uint64_t* bytes);
+int tkd_matmul(const TkdMatmul* a, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

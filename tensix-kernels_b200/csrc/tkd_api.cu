@@ -1,0 +1,278 @@
+// tkd_api.cu: the extern "C" entry points of libtkd (include/tkd.h): argument checks, the launch plan, the launches.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "../../include/tkd.h"
+#include "tkd_internal.h"
+#include "tkd_layout.h"
+
+static_assert(TKD_FMT_BFP8 == TKD_BFP8 && TKD_FMT_BFP4 == TKD_BFP4 && TKD_FMT_BF16 == TKD_BF16, "format codes");
+
+namespace {
+
+constexpr int kMaxSmem = 227 * 1024;  // dynamic shared memory a CTA may take on sm_100
+
+inline int cuda_err(cudaError_t e) { return e == cudaSuccess ? TKD_OK : TKD_ERR_CUDA + (int)e; }
+inline int launch_err(int e) { return e == 0 ? TKD_OK : TKD_ERR_CUDA + e; }
+inline bool fmt_ok(int fmt) { return fmt == TKD_BFP8 || fmt == TKD_BFP4 || fmt == TKD_BF16; }
+inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+struct Layout {
+    TkdParams p;
+    int grid;
+    size_t smem;
+    int64_t weight_bytes;
+    // workspace map
+    int64_t off_counters, off_units, off_scratch, off_ytmp, ws_bytes;
+};
+
+// Everything a launch needs except the device pointers into the workspace. sms 0: ask the device.
+int make_layout(const TkdMatmul* a, Layout* L, int sms) {
+    if (!a || !fmt_ok(a->fmt)) return TKD_ERR_BAD_ARG;
+    if (a->m < 1 || a->m > 32 || a->k < 32 || a->k % 32 || a->k > (1 << 24)) return TKD_ERR_BAD_ARG;
+    if (a->nblocks < 1 || a->nblocks > 4) return TKD_ERR_BAD_ARG;
+    if (a->epilogue < TKD_EPI_PLAIN || a->epilogue > TKD_EPI_OUT32) return TKD_ERR_BAD_ARG;
+    const bool glu = a->epilogue == TKD_EPI_GLU_IL || a->epilogue == TKD_EPI_GLU2;
+    if (a->nblocks > 1 && !(a->epilogue == TKD_EPI_PLAIN || a->epilogue == TKD_EPI_GLU2)) return TKD_ERR_BAD_ARG;
+    if (a->nblocks > 1 && (a->scale_dtype != TKD_DT_NONE || a->topk_k)) return TKD_ERR_BAD_ARG;
+    if (a->topk_k && (glu || a->epilogue == TKD_EPI_OUT32 || a->epilogue == TKD_EPI_RESIDUAL)) return TKD_ERR_BAD_ARG;
+    if ((a->epilogue == TKD_EPI_OUT32) != (a->out_dtype == TKD_DT_F32)) return TKD_ERR_BAD_ARG;
+    if (a->out_dtype != TKD_DT_F32 && a->out_dtype != TKD_DT_BF16) return TKD_ERR_BAD_ARG;
+
+    TkdParams& p = L->p;
+    memset(&p, 0, sizeof(p));
+    p.fmt = a->fmt;
+    p.M = a->m;
+    p.K = (int)a->k;
+    p.nseg = a->nblocks;
+    p.epi = a->epilogue;
+    p.act = a->act;
+    const int mt = a->m <= 8 ? 1 : (a->m <= 16 ? 2 : 4);
+    const int ksa = tkd_ksa(a->fmt), sab = tkd_sab(a->fmt);
+    int chunk_k = a->fmt == TKD_BF16 ? 128 : 256;
+    if (mt == 4) chunk_k /= 2;
+    p.subsa = chunk_k / ksa;
+    p.ks = a->ks ? a->ks : (mt == 1 ? 256 : 512);
+    if (p.ks < chunk_k || p.ks % chunk_k || p.ks > 2048) return TKD_ERR_BAD_ARG;
+    p.nslices = (p.K + p.ks - 1) / p.ks;
+    p.run_bytes = tkd_run_bytes(a->fmt, a->k);
+    p.xslots = mt == 1 ? 4 : (mt == 2 ? 3 : 2);
+
+    int panels = 0;
+    L->weight_bytes = 0;
+    for (int s = 0; s < a->nblocks; ++s) {
+        const TkdBlock& b = a->block[s];
+        if (b.n < 1 || b.out_col0 < 0 || b.n > (1 << 28)) return TKD_ERR_BAD_ARG;
+        if (glu && a->epilogue == TKD_EPI_GLU_IL && b.n % 64) return TKD_ERR_BAD_ARG;
+        const int64_t npad = tkd_padded_cols(b.n);
+        TkdSegDev& d = p.seg[s];
+        d.w = static_cast<const uint8_t*>(b.w);
+        d.w2 = static_cast<const uint8_t*>(b.w_up);
+        d.emax = b.emax;
+        d.emax2 = b.emax_up;
+        d.groups = (int)(npad / 16);
+        d.n_valid = (int)b.n;
+        d.out_col0 = (int)b.out_col0;
+        d.panel0 = panels;
+        const bool two = a->epilogue == TKD_EPI_GLU2;
+        panels += two ? (d.groups + 3) / 4 : (d.groups + 7) / 8;
+        L->weight_bytes += (two ? 2 : 1) * tkd_stream_bytes(a->fmt, a->k, npad);
+    }
+    p.total_panels = panels;
+    p.total_items = (int64_t)panels * p.nslices;
+
+    // shared-memory map
+    const int mp = mt == 1 ? 8 : (mt == 2 ? 24 : 40);
+    p.rs = p.ks * 2 + 64;
+    p.off_x = TKD_SMEM_HEAD;
+    p.off_pbuf = (int)align_up(p.off_x + (int64_t)p.xslots * p.M * p.rs, 128);
+    p.off_tbuf = p.off_pbuf + 2 * TKD_PANEL_COLS * mp * 4;
+    p.off_ring = (int)align_up(p.off_tbuf + TKD_PANEL_COLS * mp * 4, 128);
+    p.sub_bytes = p.subsa * sab;
+    p.stage_bytes = 8 * p.sub_bytes;
+    p.nstages = (kMaxSmem - p.off_ring) / p.stage_bytes;
+    if (p.nstages > TKD_MAX_STAGES) p.nstages = TKD_MAX_STAGES;
+    if (p.nstages < 2) return TKD_ERR_UNSUPPORTED;
+    L->smem = (size_t)p.off_ring + (size_t)p.nstages * p.stage_bytes;
+
+    if (sms <= 0) sms = sm_count();
+    if (sms <= 0) sms = 148;
+    if (a->max_ctas > 0 && a->max_ctas < sms) sms = a->max_ctas;
+    L->grid = (int)(p.total_items < sms ? p.total_items : sms);
+
+    // top-k
+    p.topk_k = a->topk_k;
+    int units = 0;
+    if (a->topk_k) {
+        if (a->topk_rows < 1 || a->topk_rows > 16 || a->topk_k < 1 || a->topk_rows * a->topk_k > 64) return TKD_ERR_BAD_ARG;
+        if (a->topk_rows > a->m) return TKD_ERR_BAD_ARG;
+        if (a->topk_unit < TKD_PANEL_COLS || a->topk_unit % TKD_PANEL_COLS || a->topk_unit > 2048) return TKD_ERR_BAD_ARG;
+        p.topk_rows = a->topk_rows;
+        p.topk_unit = a->topk_unit;
+        p.topk_slot0 = a->topk_slot0;
+        p.write_y = a->topk_write_y;
+        p.topk_base = a->topk_base;
+        p.topk_n = a->topk_n;
+        units = (panels * TKD_PANEL_COLS + a->topk_unit - 1) / a->topk_unit;
+    }
+    // workspace map: panel counters, unit counters, slice sums, bf16 outputs of a call that writes no y
+    L->off_counters = 0;
+    L->off_units = (int64_t)panels * 4;
+    L->off_scratch = align_up(L->off_units + (int64_t)units * 4, 256);
+    const int64_t scratch = p.nslices > 1 ? (int64_t)panels * p.nslices * p.M * TKD_PANEL_COLS * 4 : 0;
+    L->off_ytmp = align_up(L->off_scratch + scratch, 256);
+    p.ld_ytmp = (int64_t)panels * TKD_PANEL_COLS;
+    const int64_t ytmp = a->topk_k && !a->topk_write_y ? (int64_t)a->topk_rows * p.ld_ytmp * 2 : 0;
+    L->ws_bytes = align_up(L->off_ytmp + ytmp, 256);
+    return TKD_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tkd_version(void) { return 1; }
+
+const char* tkd_error_string(int code) {
+    switch (code) {
+        case TKD_OK: return "ok";
+        case TKD_ERR_BAD_ARG: return "bad argument";
+        case TKD_ERR_UNSUPPORTED: return "unsupported";
+        case TKD_ERR_TIMEOUT: return "a kernel's bounded wait gave up";
+        case TKD_ERR_WORKSPACE: return "workspace missing or too small";
+        case TKD_ERR_WIDE: return "exponent spread inside a column group too wide for the stream";
+        default: return code > TKD_ERR_CUDA ? cudaGetErrorString((cudaError_t)(code - TKD_ERR_CUDA)) : "unknown";
+    }
+}
+
+int64_t tkd_padded_cols(int64_t n) { return (n + 15) / 16 * 16; }
+
+int64_t tkd_packed_bytes(int fmt, int64_t k, int64_t n) {
+    return fmt_ok(fmt) ? tkd_stream_bytes(fmt, k, tkd_padded_cols(n)) : -1;
+}
+
+int tkd_quantise(int fmt, const float* src, int orient, int64_t k, int64_t n, const float* col_div, uint8_t* exps,
+                 void* codes, void* stream) {
+    if (!fmt_ok(fmt) || !src || !codes || k < 1 || n < 1 || (fmt != TKD_BF16 && !exps) || (orient != 0 && orient != 1))
+        return TKD_ERR_BAD_ARG;
+    return launch_err(tkd_launch_quantise(fmt, src, orient, k, n, tkd_padded_cols(n), col_div, exps, codes,
+                                          static_cast<cudaStream_t>(stream)));
+}
+
+int tkd_pack(int fmt, int64_t k, int64_t n, const uint8_t* exps, const void* codes, void* packed, uint8_t* emax,
+             int32_t* info, void* stream) {
+    if (!fmt_ok(fmt) || !codes || !packed || k < 1 || n < 1) return TKD_ERR_BAD_ARG;
+    if (fmt != TKD_BF16 && (!exps || !emax || !info)) return TKD_ERR_BAD_ARG;
+    return launch_err(tkd_launch_permute(fmt, k, tkd_padded_cols(n), exps, codes, emax, info, packed,
+                                         static_cast<cudaStream_t>(stream)));
+}
+
+int tkd_unpack(int fmt, int64_t k, int64_t n, const void* packed, const uint8_t* emax, float* out, void* stream) {
+    if (!fmt_ok(fmt) || !packed || !out || k < 1 || n < 1 || (fmt != TKD_BF16 && !emax)) return TKD_ERR_BAD_ARG;
+    return launch_err(
+        tkd_launch_unpack(fmt, k, tkd_padded_cols(n), packed, emax, out, static_cast<cudaStream_t>(stream)));
+}
+
+int tkd_matmul_plan(const TkdMatmul* a, TkdPlan* plan) {
+    Layout L;
+    if (!plan) return TKD_ERR_BAD_ARG;
+    // (no device needed: without one the plan is made for 148 SMs)
+    int sms = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        sms = 148;
+    }
+    const int rc = make_layout(a, &L, sms);
+    if (rc) return rc;
+    plan->ks = L.p.ks;
+    plan->nslices = L.p.nslices;
+    plan->panels = L.p.total_panels;
+    plan->grid = L.grid;
+    plan->stages = L.p.nstages;
+    plan->xslots = L.p.xslots;
+    plan->chunk_k = L.p.subsa * tkd_ksa(L.p.fmt);
+    plan->smem_bytes = (int32_t)L.smem;
+    plan->items = L.p.total_items;
+    plan->weight_bytes = L.weight_bytes;
+    return TKD_OK;
+}
+
+int tkd_matmul_workspace(const TkdMatmul* a, uint64_t* bytes) {
+    Layout L;
+    if (!bytes) return TKD_ERR_BAD_ARG;
+    int sms = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        sms = 148;
+    }
+    const int rc = make_layout(a, &L, sms);
+    if (rc) return rc;
+    *bytes = (uint64_t)L.ws_bytes;
+    return TKD_OK;
+}
+
+int tkd_matmul(const TkdMatmul* a, void* stream) {
+    Layout L;
+    const int rc = make_layout(a, &L, 0);
+    if (rc) return rc;
+    TkdParams& p = L.p;
+    if (!a->x || !a->out || a->ldx < a->k || a->ldx % 8 || (reinterpret_cast<uintptr_t>(a->x) & 15)) return TKD_ERR_BAD_ARG;
+    for (int s = 0; s < a->nblocks; ++s) {
+        const TkdBlock& b = a->block[s];
+        if (!b.w || (reinterpret_cast<uintptr_t>(b.w) & 15)) return TKD_ERR_BAD_ARG;
+        if (a->fmt != TKD_BF16 && !b.emax) return TKD_ERR_BAD_ARG;
+        if (a->epilogue == TKD_EPI_GLU2) {
+            if (!b.w_up || (reinterpret_cast<uintptr_t>(b.w_up) & 15) || (a->fmt != TKD_BF16 && !b.emax_up))
+                return TKD_ERR_BAD_ARG;
+        }
+        const int64_t width = a->epilogue == TKD_EPI_GLU_IL ? b.n / 2 : b.n;
+        if (b.out_col0 + width > a->ldo) return TKD_ERR_BAD_ARG;
+    }
+    if (a->scale_dtype != TKD_DT_NONE) {
+        if (!a->scale || (a->epilogue == TKD_EPI_GLU2 && !a->scale_up)) return TKD_ERR_BAD_ARG;
+        if (a->scale_dtype != TKD_DT_BF16 && a->scale_dtype != TKD_DT_F32) return TKD_ERR_BAD_ARG;
+    }
+    if (a->epilogue == TKD_EPI_RESIDUAL && (!a->residual || a->residual_dtype != TKD_DT_BF16)) return TKD_ERR_BAD_ARG;
+    if (a->epilogue == TKD_EPI_OUT32 && a->residual && a->residual_dtype != TKD_DT_F32) return TKD_ERR_BAD_ARG;
+    if (a->epilogue != TKD_EPI_RESIDUAL && a->epilogue != TKD_EPI_OUT32 && a->residual) return TKD_ERR_BAD_ARG;
+    if (a->topk_k && !a->records) return TKD_ERR_BAD_ARG;
+    if (L.ws_bytes > 0 && (!a->workspace || a->workspace_bytes < (uint64_t)L.ws_bytes)) return TKD_ERR_WORKSPACE;
+    if (a->workspace && (reinterpret_cast<uintptr_t>(a->workspace) & 255)) return TKD_ERR_BAD_ARG;
+
+    p.x = static_cast<const uint16_t*>(a->x);
+    p.ldx = a->ldx;
+    p.scale = a->scale;
+    p.scale2 = a->scale_up;
+    p.scale_dt = a->scale_dtype;
+    p.res = a->residual;
+    p.res_dt = a->residual ? a->residual_dtype : TKD_DT_NONE;
+    p.ldr = a->ldr;
+    p.out = a->out;
+    p.out_dt = a->out_dtype;
+    p.ldo = a->ldo;
+    p.records = static_cast<uint32_t*>(a->records);
+    uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+    p.counters = reinterpret_cast<int*>(ws + L.off_counters);
+    p.unit_counters = reinterpret_cast<int*>(ws + L.off_units);
+    p.scratch = reinterpret_cast<float*>(ws + L.off_scratch);
+    p.ytmp = reinterpret_cast<uint16_t*>(ws + L.off_ytmp);
+    p.status = a->status;
+    return launch_err(tkd_launch_stream(p, L.grid, L.smem, static_cast<cudaStream_t>(stream)));
+}
+
+}  // extern "C"

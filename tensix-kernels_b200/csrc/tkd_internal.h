@@ -1,0 +1,77 @@
+// tkd_internal.h: what the translation units of libtkd share (not part of the C-ABI).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tkd.h"
+
+// --- packer (tkd_pack.cu) ---
+int tkd_launch_quantise(int fmt, const float* src, int orient, int64_t K, int64_t N, int64_t npad,
+                        const float* col_div, uint8_t* exps, void* codes, cudaStream_t st);
+int tkd_launch_permute(int fmt, int64_t K, int64_t npad, const uint8_t* exps, const void* codes, uint8_t* emax,
+                       int* info, void* stream, cudaStream_t st);
+int tkd_launch_unpack(int fmt, int64_t K, int64_t npad, const void* stream, const uint8_t* emax, float* out,
+                      cudaStream_t st);
+
+// --- streaming matmul (tkd_stream.cu) ---
+// (the TKD_EPI_* and TKD_DT_* codes are those of include/tkd.h)
+
+#define TKD_THREADS 416        // 1 producer warp + 8 streaming warps + 4 output warps
+#define TKD_PANEL_COLS 128     // columns one work item covers: 8 streaming warps x 16
+#define TKD_MAX_STAGES 16
+#define TKD_MAX_XSLOTS 8
+#define TKD_SMEM_HEAD 512      // barriers and flags
+
+struct TkdSegDev {
+    const uint8_t* w;     // packed stream (the gate's with a separate up weight)
+    const uint8_t* w2;    // the up weight's stream, or null
+    const uint8_t* emax;  // per group of 16 columns (null for bf16)
+    const uint8_t* emax2;
+    int groups;           // groups of 16 columns held by w
+    int n_valid;          // real columns of w
+    int out_col0;         // first output column of the segment in out (elements)
+    int panel0;           // first panel of the segment in the call's panel list
+};
+
+struct TkdParams {
+    TkdSegDev seg[4];
+    int nseg;
+    int fmt, M, K;
+    const uint16_t* x;  // bf16 bits, row-major, ldx elements a row
+    int64_t ldx;
+    int ks;             // k per slice (a multiple of the chunk depth)
+    int nslices;        // ceil(K / ks)
+    int subsa;          // super-atoms per chunk (one warp's share of a stage)
+    int nstages, xslots;
+    int64_t run_bytes;  // bytes of one group's run
+    int total_panels;
+    int64_t total_items;
+    int epi, act;
+    const void* scale;   // per output column of w (bf16 or f32), or null
+    const void* scale2;  // the up weight's, GLU two-weight form
+    int scale_dt;
+    const void* res;     // residual, bf16 (reference form) or f32 (with a float32 output)
+    int res_dt;
+    int64_t ldr;
+    void* out;
+    int out_dt;
+    int64_t ldo;
+    // top-k records (tkd_stream.cu, output warps)
+    uint32_t* records;
+    int topk_k, topk_rows, topk_unit, topk_slot0, write_y;
+    uint32_t topk_base;
+    int64_t topk_n;
+    uint16_t* ytmp;      // bf16 outputs of a call that does not write y: [rows][ld_ytmp]
+    int64_t ld_ytmp;
+    int* unit_counters;
+    // split-panel partial sums
+    float* scratch;
+    int* counters;
+    int* status;
+    // shared-memory map (bytes from the start of dynamic shared memory)
+    int rs;              // bytes per x row of a slot
+    int off_x, off_pbuf, off_tbuf, off_ring;
+    int sub_bytes, stage_bytes;
+};
+
+int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st);

@@ -1,0 +1,113 @@
+// tkd_layout.h: the packed HBM stream of a dense_reader weight, as index arithmetic usable on host and device.
+//
+// The reference keeps a [K, N] block-float weight as 32 x 32 tiles (64 exponent bytes, then the mantissas; one shared
+// exponent per 16 consecutive n at one k; dense_reader/linear.py:49-50, moe/moe8.py:125-154). Here the same numbers
+// (sign, magnitude, shared exponent) are laid out for a warp that multiplies 16 output columns by mma.sync
+// m16n8k16 with the weights as the A operand:
+//
+//   stream   = one run per group of 16 output columns, runs back to back
+//   run      = ceil(K / KSA) super-atoms, K ascending
+//   super-atom (bfloat8_b, 32 k, 544 B)  = 32 B exponent words, then 32 lanes x 16 B of codes
+//   super-atom (bfloat4_b, 64 k, 576 B)  = 64 B exponent words, then 32 lanes x 16 B of codes
+//   super-atom (bfloat16, 32 k, 1024 B)  = 2 x (32 lanes x 16 B) of A-fragment registers
+//
+// so bytes per weight stay 1.0625, 0.5625 and 2. Every super-atom size is a multiple of 16 B: any run of them is
+// a legal source of a 1-D bulk copy.
+//
+// Inside a k32 block, lane (g = lane / 4, t = lane % 4) of mma jj (0, 1) owns k = 8 t + 4 jj + r, r = 0..3: the 8
+// activations a lane needs for the two mmas are 16 consecutive bytes of a row of x. Fragment registers: a0 = column
+// g, r 0-1; a1 = column g + 8, r 0-1; a2 = column g, r 2-3; a3 = column g + 8, r 2-3 (r even in the low half).
+//
+// A code is kept as the bf16 bit pattern sign << 15 | magnitude (a bf16 subnormal: +-magnitude * 2^-133), and several
+// fragment registers share one 32-bit word by rotation, so that one rotate and one AND give a register:
+//   bfloat8_b word = a_even | rotl(a_odd, 8)                      (mask 0x807F807F)
+//   bfloat4_b word = a0 | rotl(a1, 4) | rotl(a2, 8) | rotl(a3, 12) (mask 0x80078007)
+// The exponents are kept biased against the group's largest, e' = e - emax[group] + 196 (1 for a row of the group
+// with no non-zero code), as bf16 exponent fields, four to a word: r 0 at bits 7-14, r 1 at 23-30, r 2 and r 3 the
+// same rotated left by 8. emax (one byte per group) is a side array; e is recovered exactly for every non-zero code.
+#pragma once
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define TKD_HD __host__ __device__ __forceinline__
+#else
+#define TKD_HD inline
+#endif
+
+enum { TKD_BFP8 = 0, TKD_BFP4 = 1, TKD_BF16 = 2 };
+
+// The exponent bias of the stream: e' = e - emax + TKD_EBIAS. A non-zero code whose e' would fall below TKD_EMIN_OK
+// marks the weight "wide" (the product of a subnormal code and the scaled activation would leave fp32's normal range).
+#define TKD_EBIAS 196
+#define TKD_EMIN_OK (TKD_EBIAS - 48)
+
+TKD_HD int tkd_mant_bits(int fmt) { return fmt == TKD_BFP8 ? 7 : 3; }
+TKD_HD int tkd_ksa(int fmt) { return fmt == TKD_BFP4 ? 64 : 32; }                          // k per super-atom
+TKD_HD int tkd_sab(int fmt) { return fmt == TKD_BFP8 ? 544 : (fmt == TKD_BFP4 ? 576 : 1024); }  // bytes per super-atom
+TKD_HD int tkd_exp_bytes(int fmt) { return fmt == TKD_BFP8 ? 32 : (fmt == TKD_BFP4 ? 64 : 0); }
+TKD_HD int tkd_unit_exp(int fmt) { return 126 + tkd_mant_bits(fmt); }  // value = m * 2^(e - unit)
+TKD_HD int64_t tkd_nsa(int fmt, int64_t K) { return (K + tkd_ksa(fmt) - 1) / tkd_ksa(fmt); }
+TKD_HD int64_t tkd_run_bytes(int fmt, int64_t K) { return tkd_nsa(fmt, K) * tkd_sab(fmt); }
+TKD_HD int64_t tkd_stream_bytes(int fmt, int64_t K, int64_t npad) { return (npad / 16) * tkd_run_bytes(fmt, K); }
+
+TKD_HD uint32_t tkd_rotl(uint32_t v, int s) { return s ? (v << s) | (v >> (32 - s)) : v; }
+TKD_HD uint32_t tkd_rotr(uint32_t v, int s) { return s ? (v >> s) | (v << (32 - s)) : v; }
+
+// Where element (k, n) of a weight lives.
+struct TkdLoc {
+    int64_t code_word;  // byte offset of the 32-bit word holding the code (bf16: of the 16-bit value itself)
+    int rot;            // the register is rotr(word, rot) & mask
+    int half;           // 0: low 16 bits of the register, 1: high
+    int64_t exp_word;   // byte offset of the exponent word
+    int exp_r;          // 0..3: the exponent's position in that word
+};
+
+TKD_HD TkdLoc tkd_locate(int fmt, int64_t K, int64_t k, int64_t n) {
+    TkdLoc L;
+    const int64_t group = n >> 4;
+    const int i = (int)(n & 15);
+    const int ksa = tkd_ksa(fmt);
+    const int64_t sa = k / ksa;
+    const int kk = (int)(k % ksa);
+    const int qq = kk >> 5;       // k32 block of the super-atom (bfloat4_b: 0, 1)
+    const int kr = kk & 31;
+    const int t = kr >> 3, jj = (kr >> 2) & 1, r = kr & 3;
+    const int lane = (i & 7) * 4 + t;
+    const int ai = (i >> 3) + 2 * (r >> 1);
+    const int64_t base = group * tkd_run_bytes(fmt, K) + sa * tkd_sab(fmt);
+    L.half = r & 1;
+    L.exp_r = r;
+    if (fmt == TKD_BF16) {
+        L.code_word = base + jj * 512 + lane * 16 + ai * 4 + L.half * 2;
+        L.rot = 0;
+        L.exp_word = -1;
+    } else if (fmt == TKD_BFP8) {
+        L.code_word = base + 32 + lane * 16 + (2 * jj + (ai >> 1)) * 4;
+        L.rot = 8 * (ai & 1);
+        L.exp_word = base + (t * 2 + jj) * 4;
+    } else {
+        const int j4 = 2 * qq + jj;
+        L.code_word = base + 64 + lane * 16 + j4 * 4;
+        L.rot = 4 * ai;
+        L.exp_word = base + (t * 4 + j4) * 4;
+    }
+    return L;
+}
+
+// A code (sign << mb | magnitude) as the bits it adds to its word.
+TKD_HD uint32_t tkd_code_bits(int fmt, uint32_t code, int rot, int half) {
+    const int mb = tkd_mant_bits(fmt);
+    const uint32_t v = ((code >> mb) << 15) | (code & ((1u << mb) - 1));
+    return tkd_rotl(v << (16 * half), rot);
+}
+// ... and back.
+TKD_HD uint32_t tkd_code_from_word(int fmt, uint32_t word, int rot, int half) {
+    const int mb = tkd_mant_bits(fmt);
+    const uint32_t v = (tkd_rotr(word, rot) >> (16 * half)) & 0xFFFFu;
+    return ((v >> 15) << mb) | (v & ((1u << mb) - 1));
+}
+// A biased exponent e' (1..254) as the bits it adds to its exponent word: a bf16 exponent field.
+TKD_HD uint32_t tkd_exp_bits(uint32_t e, int r) { return tkd_rotl((e << 7) << (16 * (r & 1)), 8 * (r >> 1)); }
+TKD_HD uint32_t tkd_exp_from_word(uint32_t word, int r) {
+    return ((tkd_rotr(word, 8 * (r >> 1)) >> (16 * (r & 1))) >> 7) & 0xFFu;
+}

@@ -1,0 +1,209 @@
+"""Parity of the CUDA path with the CPU oracle, through the package's API (which calls libtkd's C-ABI): bit-exact for
+the quantiser, the packed weights' held values and the top-k indices; 1e-2 relative (compared in bf16) for the sums."""
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from common import ttnn_like as ttnn  # noqa: E402
+from dense_reader import linear  # noqa: E402
+from oracle import oracle as orc  # noqa: E402
+
+DT = {"bfp8": ttnn.bfloat8_b, "bfp4": ttnn.bfloat4_b, "bf16": ttnn.bfloat16}
+
+
+def dev_x(device, x):
+    return ttnn.from_torch(x.reshape(1, 1, *x.shape).to(torch.bfloat16), dtype=ttnn.bfloat16, layout=ttnn.TILE_LAYOUT,
+                           device=device)
+
+
+def host(y):
+    return ttnn.to_torch(y).float().reshape(-1, y.shape[-1])
+
+
+def close_bf16(got, want, tol=1e-2):
+    """|got - want| within tol relative to the row's scale, both seen in bf16."""
+    g, w = got.to(torch.bfloat16).float(), torch.as_tensor(want).to(torch.bfloat16).float()
+    scale = w.abs().amax(dim=-1, keepdim=True).clamp(min=1e-30)
+    err = ((g - w).abs() / scale).max().item()
+    assert err < tol, err
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4", "bf16"])
+@pytest.mark.parametrize("k,n", [(64, 32), (96, 48), (1024, 2048), (4096, 1024 + 16)])
+def test_held_values_bit_exact(device, fmt, k, n):
+    g = torch.Generator().manual_seed(k * 7 + n)
+    w = torch.randn(n, k, generator=g) * 0.02 * torch.exp2(torch.randint(-6, 7, (n, 1), generator=g).float())
+    w[0] = 0
+    w[3, 5], w[7 % n, 9] = 0.0, -1e-30
+    n_ok = n if n % 32 == 0 else n  # (native_weight takes any N; the stream pads to 16)
+    tw, _ = linear.native_weight(device, w, DT[fmt])
+    got = ttnn.to_torch(tw)[0, 0, :, :n_ok].numpy()
+    want = orc.block_float(w.T.contiguous().numpy(), fmt)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # padded columns hold zeros
+    assert not ttnn.to_torch(tw)[0, 0, :, n_ok:].any()
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+def test_col_scale_and_block_float(device, fmt):
+    g = torch.Generator().manual_seed(11)
+    w = torch.randn(256, 128, generator=g) * 0.02
+    w[:100] *= 40
+    tw, ts = linear.native_weight(device, w, DT[fmt], col_scale=True)
+    want_w, want_c = orc.native_values(w, fmt, col_scale=True)
+    assert np.array_equal(ttnn.to_torch(tw)[0, 0, :, :256].numpy().view(np.uint32), want_w.view(np.uint32))
+    assert np.array_equal(ttnn.to_torch(ts).float().reshape(-1).numpy(), want_c)
+    t = torch.randn(2, 64, 96, generator=g)
+    got = linear.block_float(t, DT[fmt])
+    for i in range(2):
+        assert np.array_equal(got[i].numpy().view(np.uint32), orc.block_float(t[i].numpy(), fmt).view(np.uint32))
+
+
+def test_wide_weight_refused(device):
+    w = torch.full((32, 64), 1.0)
+    w[:, 3] = 1e-20
+    tw, _ = linear.native_weight(device, w, ttnn.bfloat8_b)
+    assert tw.wide
+    x = dev_x(device, torch.ones(1, 64))
+    with pytest.raises(RuntimeError):
+        linear.matmul(x, tw, None)
+
+
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4", "bf16"])
+@pytest.mark.parametrize("m", [1, 4, 8, 13, 32])
+def test_matmul_against_oracle(device, fmt, m):
+    k, n = 2048 + 32, 1024 + 32  # K not a multiple of the slice, N not of the panel
+    g = torch.Generator().manual_seed(100 + m)
+    w = torch.randn(n, k, generator=g) * 0.02
+    x = torch.randn(m, k, generator=g)
+    tw, _ = linear.native_weight(device, w, DT[fmt])
+    wk, _ = orc.native_values(w, fmt)
+    y = host(linear.matmul(dev_x(device, x), tw, None))
+    assert y.shape == (m, n)
+    want = orc.matmul_f64(x, wk)
+    close_bf16(y, want)
+    linear.check_status(device)
+
+
+def test_config_shapes_small_m(device):
+    """BASELINE's shapes, scaled down in N only where the oracle would take minutes: the README example (config 1)
+    at full size, the MLP gate/up with float32 column scales (config 2) and the down projection with a float32 residual
+    and output (config 3) at a quarter of N."""
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(4096, 2048, generator=g) * 0.02
+    x = torch.randn(1, 2048, generator=g)
+    tw, _ = linear.native_weight(device, w, ttnn.bfloat8_b)
+    close_bf16(host(linear.matmul(dev_x(device, x), tw, None)), orc.matmul_f64(x, orc.native_values(w, "bfp8")[0]))
+    # config 2: silu((x Wg) sg) * ((x Wu) su), bfloat4_b
+    k, n = 4096, 3584
+    wg, wu = torch.randn(n, k, generator=g) * 0.02, torch.randn(n, k, generator=g) * 0.02
+    sg, su = torch.rand(n, generator=g) + 0.5, torch.rand(n, generator=g) + 0.5
+    x = torch.randn(1, k, generator=g)
+    tg, _ = linear.native_weight(device, wg, ttnn.bfloat4_b)
+    tu, _ = linear.native_weight(device, wu, ttnn.bfloat4_b)
+    cs = (sg.to(device.torch), su.to(device.torch))
+    y = host(linear.matmul(dev_x(device, x), tg, None, w_up=tu, glu=True, col_scales=cs))
+    ag = orc.matmul_f64(x, orc.native_values(wg, "bfp4")[0])
+    au = orc.matmul_f64(x, orc.native_values(wu, "bfp4")[0])
+    close_bf16(y, orc.epilogue(ag, 2, acc2=au, scale=sg.numpy(), scale2=su.numpy()))
+    # the same through an interleaved weight
+    ti, _ = linear.native_weight(device, linear.interleave_glu(wg, wu), ttnn.bfloat4_b)
+    si = linear.interleave_glu(sg[:, None], su[:, None]).reshape(-1).to(device.torch)
+    y2 = host(linear.matmul(dev_x(device, x), ti, None, glu=True, col_scales=si))
+    assert torch.equal(y, y2)
+    # config 3: x W^T + residual in float32
+    k, n = 14336, 1024
+    w = torch.randn(n, k, generator=g) * 0.02
+    tw, _ = linear.native_weight(device, w, ttnn.bfloat8_b)
+    wk = orc.native_values(w, "bfp8")[0]
+    for m in (1, 8, 32):
+        x = torch.randn(m, k, generator=g)
+        res = torch.randn(m, n, generator=g)
+        tr = ttnn.from_torch(res.reshape(1, 1, m, n), dtype=ttnn.float32, layout=ttnn.TILE_LAYOUT, device=device)
+        y = linear.matmul(dev_x(device, x), tw, None, residual=tr, out32=True)
+        want = orc.epilogue(orc.matmul_f64(x, wk), 4, res32=res.numpy())
+        got = host(y)[:m]
+        assert got.dtype == torch.float32
+        rel = ((got.double() - torch.from_numpy(want)).norm() / torch.from_numpy(want).norm()).item()
+        assert rel < 1e-5, rel
+    linear.check_status(device)
+
+
+def test_block_list_config4(device):
+    """One launch over an attention layer's four projections (config 4) equals one call per weight, bit for bit, and
+    matches the oracle."""
+    k = 4096
+    g = torch.Generator().manual_seed(40)
+    shapes = [(4096, 0), (1024, 128), (1024, 160), (4096, 192)]
+    ws = [torch.randn(n, k, generator=g) * 0.02 for n, _ in shapes]
+    tws = [linear.native_weight(device, w, ttnn.bfloat8_b)[0] for w in ws]
+    for m in (1, 4):
+        x = torch.randn(m, k, generator=g)
+        tx = dev_x(device, x)
+        one = host(linear.matmul(tx, [(tw, c0) for tw, (_, c0) in zip(tws, shapes)], None))
+        assert one.shape == (m, 32 * 192 + 4096)
+        for tw, w, (n, c0) in zip(tws, ws, shapes):
+            own = host(linear.matmul(tx, tw, None))
+            assert torch.equal(one[:, 32 * c0 : 32 * c0 + n], own)
+            close_bf16(own, orc.matmul_f64(x, orc.native_values(w, "bfp8")[0]))
+    linear.check_status(device)
+
+
+def test_topk_indices_exact(device):
+    """Top-k candidate indices equal the oracle's canonical order (key descending, lower index first among ties) on
+    the op's own bf16 outputs, including heavy ties, a last partial unit and write_y False."""
+    k, n = 1024, 2048 * 2 + 384
+    g = torch.Generator().manual_seed(50)
+    w = (torch.randn(n, k, generator=g) * 4).round() / 64  # few distinct values: many exact ties in y
+    x = (torch.randn(2, k, generator=g) * 2).round()
+    tw, _ = linear.native_weight(device, w, ttnn.bfloat8_b)
+    tx = dev_x(device, x)
+    y = host(linear.matmul(tx, tw, None))
+    units, kk, rows = 3, 8, 2
+    for n_valid, base, write_y in ((n, 0, True), (n - 100, 5000, False)):
+        r = linear.topk_result(device, units + 1, rows, kk)
+        spec = {"r": r, "k": kk, "rows": rows, "slot0": 1, "base": base, "n": n_valid, "write_y": write_y}
+        out = ttnn.from_torch(torch.full((1, 1, 2, n), -7.0, dtype=torch.bfloat16), dtype=ttnn.bfloat16,
+                              layout=ttnn.TILE_LAYOUT, device=device)
+        linear.matmul(tx, tw, None, topk=spec, out=out)
+        if write_y:
+            assert torch.equal(host(out), y)
+        else:
+            assert bool((host(out) == -7.0).all())  # never written
+        rec = ttnn.to_torch(r).reshape(units + 1, 2, rows, kk).numpy().view(np.uint32)
+        assert not rec[0].any()  # slot 0 untouched
+        for u in range(units):
+            for t in range(rows):
+                c0, c1 = u * 2048, min((u + 1) * 2048, n_valid)
+                keys, idx = orc.topk_canonical(orc.bf16_bits(y[t, c0:c1]), c1 - c0, kk, base + c0)
+                assert np.array_equal(rec[1 + u, 0, t], keys), (u, t)
+                assert np.array_equal(rec[1 + u, 1, t], idx), (u, t)
+    linear.check_status(device)
+
+
+def test_full_size_properties(device):
+    """At BASELINE's full sizes (config 2's gate weight, 14336 x 4096 bfloat4_b; config 3's 4096 x 14336 bfloat8_b)
+    the oracle is too slow for every column; size-independent properties stand in: linearity in x (power-of-two
+    scaling is exact), a zero row of x gives zeros, columns of a sub-matrix equal the same columns computed alone,
+    and a sample of columns against the oracle."""
+    g = torch.Generator().manual_seed(60)
+    for fmt, n, k in (("bfp4", 14336, 4096), ("bfp8", 4096, 14336)):
+        w = torch.randn(n, k, generator=g) * 0.02
+        tw, _ = linear.native_weight(device, w, DT[fmt])
+        x = torch.randn(2, k, generator=g).to(torch.bfloat16).float()
+        x[1] = 0
+        y = host(linear.matmul(dev_x(device, x), tw, None))
+        assert not y[1].any()
+        y4 = host(linear.matmul(dev_x(device, x * 4), tw, None))
+        assert torch.equal(y4, y * 4)
+        cols = torch.randperm(n // 16, generator=g)[:24] * 16
+        sub = torch.cat([w[c : c + 16] for c in cols.tolist()])
+        ts, _ = linear.native_weight(device, sub, DT[fmt])
+        ysub = host(linear.matmul(dev_x(device, x), ts, None))
+        pick = torch.cat([y[:, c : c + 16] for c in cols.tolist()], dim=1)
+        assert torch.equal(ysub, pick)
+        close_bf16(ysub[:1], orc.matmul_f64(x[:1], orc.native_values(sub, fmt)[0]))
+    linear.check_status(device)
