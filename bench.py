@@ -1,0 +1,364 @@
+"""bench.py: weight-stream throughput of the dense_reader decode matmul on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c1|c5] [--rows M] [--impl reference]
+
+One step is one pass of the hot path over one batch of synthetic input: one call of linear.matmul. The default
+workload is BASELINE.json's configs[1] ("c2"): the Llama-3-8B MLP gate/up pair, x [1, 4096] bf16, two [14336, 4096]
+bfloat4_b weights with float32 per-column scales, output silu(x Wg) * (x Wu) in bf16. Inputs are seeded synthetic
+tensors of those shapes and distributions (there are no checkpoints here).
+
+Printed: ONE JSON line. `value` is weight-stream GB/s (packed weight bytes of the calls / device time, CUDA events,
+max over ranks, all ranks' bytes), inputs resident in HBM, the K steps replayed from one CUDA graph. The weights are
+smaller than the 126 MB L2, so the steps rotate over enough distinct packed copies to exceed twice the L2 (`config.l2`).
+`e2e` is the same metric through the public Python API with host buffers: every step copies x from pinned host
+memory, calls linear.matmul and reads y back to pinned host memory. `roofline` compares the kernel's algorithmic bytes
+per launch with the measured HBM copy bandwidth of MEASURED_PEAKS.json. `cpu_baseline` (rank 0, N = 1) times the
+reference's torch path (the oracle's port of dense_reader/linear.py:166-169 plus the SwiGLU stage) on the host cores on
+a bounded column sample of the same workload.
+
+N > 1 (torchrun, one rank per GPU, NCCL): weak scaling. Each rank streams its own column shard of the same size (a layer
+N times as wide, column-sharded as native_weight would pack it per rank) and the ranks' outputs are all-gathered over
+NCCL on a side stream while the next step's kernel runs.
+
+--impl reference: the reference's own CPU implementation of the path (the oracle port; the reference's device path needs
+ttnn and a Tensix simulator, neither of which exists here), all host threads, same metric.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tensix-kernels_b200"))
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (K, N per weight, format, description)
+    "c1": dict(k=2048, n=4096, fmt="bfp8", what="README example: x[1,2048] @ W[4096,2048] bfloat8_b, no epilogue"),
+    "c2": dict(k=4096, n=14336, fmt="bfp4", what="Llama-3-8B MLP gate/up: two [14336,4096] bfloat4_b, f32 column scales, SwiGLU"),
+    "c3": dict(k=14336, n=4096, fmt="bfp8", what="Llama-3-8B MLP down: [4096,14336] bfloat8_b + f32 residual, f32 out"),
+    "c5": dict(k=4096, n=151936, fmt="bfp8", what="LM head [151936,4096] bfloat8_b, top-8 records per 2048 columns"),
+}
+BYTES_PER_WEIGHT = {"bfp8": 1.0625, "bfp4": 0.5625, "bf16": 2.0}
+L2_BYTES = 126 * 1024 * 1024
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return json.loads(p.read_text())["hbm_gbs"], "measured (MEASURED_PEAKS.json: torch copy, read+write)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+class Clocks:
+    """nvidia-smi sampled every 200 ms while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        good = [r for r in self.rows if len(r) == 7 and r[0].isdigit()]
+        if not good:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in good)]
+        return {"sm_mhz": statistics.median(int(r[0]) for r in good), "sm_max_mhz": int(good[0][1]),
+                "samples": len(good), "reasons": reasons}
+
+
+def make_inputs(wl, m, seed):
+    """Seeded synthetic tensors of the workload's shapes: W ~ N(0,1) * 0.02, x ~ N(0,1), scales ~ U(0.5,1.5)."""
+    g = torch.Generator().manual_seed(seed)
+    k, n = wl["k"], wl["n"]
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    return g, x, k, n
+
+
+def build_gpu_case(name, m, device, copies, seed0):
+    """The device-side tensors of one workload: `copies` distinct packed weight sets, and a closure running step i."""
+    from common import ttnn_like as ttnn
+    from dense_reader import linear
+
+    wl = WORKLOADS[name]
+    dt = {"bfp8": ttnn.bfloat8_b, "bfp4": ttnn.bfloat4_b}[wl["fmt"]]
+    g, x, k, n = make_inputs(wl, m, seed0)
+    tx = ttnn.from_torch(x.reshape(1, 1, m, k), dtype=ttnn.bfloat16, layout=ttnn.TILE_LAYOUT, device=device)
+    sets = []
+    for c in range(copies):
+        gw = torch.Generator().manual_seed(seed0 + 1 + c)
+        if name == "c2":
+            wg = linear.native_weight(device, torch.randn(n, k, generator=gw) * 0.02, dt)[0]
+            wu = linear.native_weight(device, torch.randn(n, k, generator=gw) * 0.02, dt)[0]
+            sets.append((wg, wu))
+        else:
+            sets.append((linear.native_weight(device, torch.randn(n, k, generator=gw) * 0.02, dt)[0],))
+    extra = {}
+    if name == "c2":
+        sg = (torch.rand(n, generator=g) + 0.5).to(device.torch)
+        su = (torch.rand(n, generator=g) + 0.5).to(device.torch)
+        y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
+
+        def step(i, x_t=tx, y_t=y):
+            wg, wu = sets[i % copies]
+            return linear.matmul(x_t, wg, None, w_up=wu, glu=True, col_scales=(sg, su), out=y_t)
+        weights = 2
+    elif name == "c3":
+        res = ttnn.from_torch(torch.randn(1, 1, m, n, generator=g), dtype=ttnn.float32, layout=ttnn.TILE_LAYOUT, device=device)
+        y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.float32, ttnn.TILE_LAYOUT, device)
+
+        def step(i, x_t=tx, y_t=y):
+            # (a fresh output, not in place: the residual stays what it was for the next step)
+            return linear.matmul(x_t, sets[i % copies][0], None, residual=res, out32=True)
+        weights = 1
+        extra["res"] = res
+    elif name == "c5":
+        units = linear.topk_units(n)
+        r = linear.topk_result(device, units, 1, 8)
+        y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
+        spec = {"r": r, "k": 8, "rows": 1, "slot0": 0, "base": 0, "n": n, "write_y": False}
+
+        def step(i, x_t=tx, y_t=y):
+            linear.matmul(x_t, sets[i % copies][0], None, topk=spec, out=y_t)
+            return r
+        weights = 1
+    else:
+        y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
+
+        def step(i, x_t=tx, y_t=y):
+            return linear.matmul(x_t, sets[i % copies][0], None, out=y_t)
+        weights = 1
+    wbytes = int(weights * k * n * BYTES_PER_WEIGHT[wl["fmt"]])
+    # algorithmic bytes of one launch: the weight stream once, x, scales, residual, output
+    other = m * k * 2
+    other += {"c2": 2 * n * 4 + m * n * 2, "c3": 2 * m * n * 4, "c5": linear.topk_units(n) * 2 * 8 * 4 if name == "c5" else 0,
+              "c1": m * n * 2}[name]
+    return dict(step=step, x=tx, y=y, wbytes=wbytes, abytes=wbytes + other, x_host=x, sets=sets, **extra)
+
+
+def cpu_reference_arm(name, m, steps, warmup, budget_s=20.0):
+    """The reference's torch path on the host cores (oracle port): bf16(x).float() @ Wq.float() and the workload's
+    output stage, on a column sample sized to a few seconds. Returns (GB/s of packed-weight bytes, info)."""
+    from oracle import oracle as orc
+
+    wl = WORKLOADS[name]
+    torch.set_num_threads(os.cpu_count() or 1)
+    k = wl["k"]
+    n_s = min(wl["n"], 2048 if name != "c3" else 1024)  # the column sample
+    g, x, _, _ = make_inputs(wl, m, 1234)
+    gw = torch.Generator().manual_seed(1235)
+    nw = 2 if name == "c2" else 1
+    wq = [torch.from_numpy(orc.native_values(torch.randn(n_s, k, generator=gw) * 0.02, wl["fmt"])[0]) for _ in range(nw)]
+    sg = torch.rand(n_s, generator=g) + 0.5
+    su = torch.rand(n_s, generator=g) + 0.5
+    res = torch.randn(m, n_s, generator=g)
+
+    def one():
+        if name == "c2":
+            gt, up = orc.reference(x, wq[0], sg), orc.reference(x, wq[1], su)
+            return (torch.nn.functional.silu(gt) * up).to(torch.bfloat16)
+        if name == "c3":
+            return orc.reference(x, wq[0]) + res
+        y = orc.reference(x, wq[0]).to(torch.bfloat16)
+        if name == "c5":
+            return torch.topk(y.float().reshape(m, -1, min(2048, n_s)), 8, dim=-1)
+        return y
+
+    for _ in range(max(1, warmup)):
+        one()
+    t0 = time.perf_counter()
+    done = 0
+    while done < steps and (done < 3 or time.perf_counter() - t0 < budget_s):
+        one()
+        done += 1
+    dt = (time.perf_counter() - t0) / done
+    sample_bytes = nw * k * n_s * BYTES_PER_WEIGHT[wl["fmt"]]
+    info = {"cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n_s} of {wl['n']} columns per weight, {done} steps, fp32 dequantised weights resident in host memory",
+            "ms_per_step_sample": dt * 1e3}
+    return sample_bytes / dt / 1e9, info
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=600)
+    ap.add_argument("--warmup", type=int, default=30)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    wl = WORKLOADS[args.workload]
+    m = args.rows
+    steps, warmup = args.steps, max(3, args.warmup)
+    config = {"workload": f"{args.workload}: {wl['what']}", "rows": m, "K": wl["k"], "N": wl["n"], "format": wl["fmt"]}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        val, info = cpu_reference_arm(args.workload, m, steps, warmup, budget_s=60.0)
+        line = {
+            "impl": "reference", "metric": "weight_stream_gbps", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": warmup, "ms_per_step": info["ms_per_step_sample"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "cpu_baseline": {"value": val, "unit": "GB/s", **info},
+            "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference's torch CPU path (dense_reader/linear.py:166-169) as restated by the oracle; its device"
+                    " path (ttnn on a Tensix simulator) cannot run here",
+        }
+        print(json.dumps(line))
+        return 0
+
+    from common import ttnn_like as ttnn
+    from dense_reader import linear
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    device = ttnn.open_device(local)
+    copies = max(2, -(-2 * L2_BYTES // int((2 if args.workload == "c2" else 1) * wl["k"] * wl["n"] * BYTES_PER_WEIGHT[wl["fmt"]])) + 1)
+    copies = min(copies, 40)
+    case = build_gpu_case(args.workload, m, device, copies, seed0=100 + 1000 * rank)
+    step = case["step"]
+    launches_per_step = 1
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-resident: the K steps as one CUDA graph ----
+    for i in range(warmup):
+        step(i)
+    linear.check_status(device)
+    graph = torch.cuda.CUDAGraph()
+    cap = torch.cuda.Stream()
+    cap.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(cap):
+        step(0)
+        with torch.cuda.graph(graph, stream=cap):
+            for i in range(steps):
+                step(i)
+    torch.cuda.synchronize()
+    graph.replay()  # one untimed replay
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with Clocks(local) as clk:
+        time.sleep(0.25)
+        reps = max(1, int(0.6 / max(1e-6, steps * 12e-6)))  # keep the timed region long enough for a clock sample
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        time.sleep(0.15)
+    ms = e0.elapsed_time(e1) / reps
+    linear.check_status(device)
+    t = torch.tensor([ms], device=device.torch)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    value = case["wbytes"] * steps * world / (ms * 1e-3) / 1e9
+    us_call = ms * 1e3 / steps
+
+    # ---- end to end through the public API with host buffers ----
+    x_pin = case["x_host"].reshape(1, 1, m, wl["k"]).contiguous().pin_memory()
+    y_dev = case["y"]
+    out_dev = step(0)
+    out_t = out_dev.t if hasattr(out_dev, "t") else out_dev
+    y_pin = torch.empty(out_t.shape, dtype=out_t.dtype).pin_memory()
+    e_steps = min(steps, 300)
+
+    def e2e_step(i):
+        case["x"].t.copy_(x_pin, non_blocking=True)
+        o = step(i)
+        y_pin.copy_(o.t, non_blocking=True)
+
+    for i in range(warmup):
+        e2e_step(i)
+    barrier()
+    e0.record()
+    for i in range(e_steps):
+        e2e_step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device=device.torch)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    e2e_val = case["wbytes"] * e_steps * world / (e2e_ms * 1e-3) / 1e9
+    linear.check_status(device)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+    peak, peak_src = peaks()
+    achieved = case["abytes"] / (us_call * 1e-6) / 1e9
+    line = {
+        "metric": "weight_stream_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms / steps, "us_per_call": us_call, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 x block-float, fp32 accumulate", "data": "synthetic",
+        "config": {**config, "l2": f"rotation over {copies} distinct packed weight sets ({copies * case['wbytes'] / 1e6:.0f} MB > 2 x L2)",
+                   "timing": f"CUDA graph of {steps} launches, {reps} replays, CUDA events"},
+        "pct_of_8000": 100 * value / world / 8000.0,
+        "clocks": clk.summary(),
+        "e2e": {"value": e2e_val, "unit": "GB/s", "us_per_call": e2e_ms * 1e3 / e_steps, "steps": e_steps,
+                "h2d_bytes_per_step": x_pin.numel() * 2, "d2h_bytes_per_step": y_pin.numel() * y_pin.element_size()},
+        "gpu_launches": steps * reps * launches_per_step,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": TRAFFIC.get(args.workload), "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": case["abytes"]},
+    }
+    if world == 1 and not args.no_cpu:
+        val, info = cpu_reference_arm(args.workload, m, 10_000, 2, budget_s=15.0)
+        line["cpu_baseline"] = {"value": val, "unit": "GB/s", **info}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+# DRAM bytes per launch of tkd_stream_kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum), per
+# workload; None until a capture of that workload is summarised under profiles/.
+TRAFFIC = {}
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -12,6 +12,8 @@ static_assert(TKD_FMT_BFP8 == TKD_BFP8 && TKD_FMT_BFP4 == TKD_BFP4 && TKD_FMT_BF
 namespace {
 
 constexpr int kMaxSmem = 227 * 1024;  // dynamic shared memory a CTA may take on sm_100
+constexpr int kMaxPanels = 48 * 1024;  // panel counters at the start of the workspace (6 M columns a call)
+constexpr int kMaxUnits = 16 * 1024;   // then the top-k unit counters; 256 KB together
 
 inline int cuda_err(cudaError_t e) { return e == cudaSuccess ? TKD_OK : TKD_ERR_CUDA + (int)e; }
 inline int launch_err(int e) { return e == 0 ? TKD_OK : TKD_ERR_CUDA + e; }
@@ -128,10 +130,12 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
         p.topk_n = a->topk_n;
         units = (panels * TKD_PANEL_COLS + a->topk_unit - 1) / a->topk_unit;
     }
-    // workspace map: panel counters, unit counters, slice sums, bf16 outputs of a call that writes no y
+    // workspace map. The counters live in a fixed region at the start, the same for every call: they must stay zero
+    // between calls, so no call's slice sums or outputs may ever be laid over another call's counters.
+    if (panels > kMaxPanels || units > kMaxUnits) return TKD_ERR_UNSUPPORTED;
     L->off_counters = 0;
-    L->off_units = (int64_t)panels * 4;
-    L->off_scratch = align_up(L->off_units + (int64_t)units * 4, 256);
+    L->off_units = (int64_t)kMaxPanels * 4;
+    L->off_scratch = (int64_t)(kMaxPanels + kMaxUnits) * 4;
     const int64_t scratch = p.nslices > 1 ? (int64_t)panels * p.nslices * p.M * TKD_PANEL_COLS * 4 : 0;
     L->off_ytmp = align_up(L->off_scratch + scratch, 256);
     p.ld_ytmp = (int64_t)panels * TKD_PANEL_COLS;
