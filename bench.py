@@ -218,6 +218,8 @@ def main():
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--profile", action="store_true",
+                    help="for a profiler: warm-up, then `steps` plain launches (no graph, no e2e, no CPU leg, no JSON line)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -268,6 +270,11 @@ def main():
     for i in range(warmup):
         step(i)
     linear.check_status(device)
+    if args.profile:
+        for i in range(steps):
+            step(i)
+        linear.check_status(device)
+        return 0
     graph = torch.cuda.CUDAGraph()
     cap = torch.cuda.Stream()
     cap.wait_stream(torch.cuda.current_stream())

@@ -47,7 +47,7 @@ const char* tkd_error_string(int code);
  * it (dense_reader/linear.py:155, :162) and for ttnn.to_torch on such a weight (tests' held(),
  * dense_reader/tests/test_dense_reader.py:47-49). ------------------------------------------------------------------ */
 
-/* N rounded up to the 16 columns that share an exponent. */
+/* N rounded up to the 128 columns of a panel of the stream. */
 int64_t tkd_padded_cols(int64_t n);
 /* Bytes of the packed stream of a [K, N] weight: K * padded N * (1.0625 | 0.5625 | 2) for K a multiple of 32 (64 for
  * bfloat4_b, whose last super-atom is zero-filled otherwise). */
@@ -107,13 +107,13 @@ typedef struct {
     void* workspace;        /* tkd_matmul_workspace bytes, zeroed once by the caller before its first use */
     uint64_t workspace_bytes;
     int32_t* status;        /* one int32 (or NULL): a kernel writes TKD_ERR_TIMEOUT here if a wait gives up */
-    int32_t ks;             /* k per slice, 0: default (a multiple of 256) */
+    int32_t ks;             /* k per slice, 0: default; a multiple of 256 (128 for bf16) */
     int32_t max_ctas;       /* 0: one per SM */
 } TkdMatmul;
 
 /* What the launch of a TkdMatmul looks like: the counterpart of the dict plan() returns (linear.py:360-382). */
 typedef struct {
-    int32_t ks, nslices, panels, grid, stages, xslots, chunk_k, smem_bytes;
+    int32_t ks, nslices, panels, grid, stages, stream_warps, chunk_k, smem_bytes;
     int64_t items, weight_bytes;
 } TkdPlan;
 

@@ -63,15 +63,12 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     p.epi = a->epilogue;
     p.act = a->act;
     const int mt = a->m <= 8 ? 1 : (a->m <= 16 ? 2 : 4);
-    const int ksa = tkd_ksa(a->fmt), sab = tkd_sab(a->fmt);
-    int chunk_k = a->fmt == TKD_BF16 ? 128 : 256;
-    if (mt == 4) chunk_k /= 2;
-    p.subsa = chunk_k / ksa;
+    const int sab = tkd_sab(a->fmt);
+    const int chunk_k = tkd_chunk_k(a->fmt);
     p.ks = a->ks ? a->ks : (mt == 1 ? 256 : 512);
-    if (p.ks < chunk_k || p.ks % chunk_k || p.ks > 2048) return TKD_ERR_BAD_ARG;
+    if (p.ks < chunk_k || p.ks % chunk_k || p.ks > 4096) return TKD_ERR_BAD_ARG;
     p.nslices = (p.K + p.ks - 1) / p.ks;
-    p.run_bytes = tkd_run_bytes(a->fmt, a->k);
-    p.xslots = mt == 1 ? 4 : (mt == 2 ? 3 : 2);
+    p.panel_bytes = tkd_panel_bytes(a->fmt, a->k);
 
     int panels = 0;
     L->weight_bytes = 0;
@@ -85,26 +82,22 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
         d.w2 = static_cast<const uint8_t*>(b.w_up);
         d.emax = b.emax;
         d.emax2 = b.emax_up;
-        d.groups = (int)(npad / 16);
         d.n_valid = (int)b.n;
         d.out_col0 = (int)b.out_col0;
         d.panel0 = panels;
         const bool two = a->epilogue == TKD_EPI_GLU2;
-        panels += two ? (d.groups + 3) / 4 : (d.groups + 7) / 8;
+        panels += (int)(two ? npad / 64 : npad / TKD_PANEL_COLS);  // a (gate, up) panel: 64 columns of each weight
         L->weight_bytes += (two ? 2 : 1) * tkd_stream_bytes(a->fmt, a->k, npad);
     }
     p.total_panels = panels;
     p.total_items = (int64_t)panels * p.nslices;
 
-    // shared-memory map
+    // shared-memory map: barriers, the hand-over buffers of the streaming warps, the GLU exchange buffer, the ring
     const int mp = mt == 1 ? 8 : (mt == 2 ? 24 : 40);
-    p.rs = p.ks * 2 + 64;
-    p.off_x = TKD_SMEM_HEAD;
-    p.off_pbuf = (int)align_up(p.off_x + (int64_t)p.xslots * p.M * p.rs, 128);
-    p.off_tbuf = p.off_pbuf + 2 * TKD_PANEL_COLS * mp * 4;
+    p.off_pbuf = TKD_SMEM_HEAD;
+    p.off_tbuf = p.off_pbuf + 2 * 2 * TKD_PANEL_COLS * mp * 4;
     p.off_ring = (int)align_up(p.off_tbuf + TKD_PANEL_COLS * mp * 4, 128);
-    p.sub_bytes = p.subsa * sab;
-    p.stage_bytes = 8 * p.sub_bytes;
+    p.stage_bytes = 8 * tkd_subsa(a->fmt) * sab;
     p.nstages = (kMaxSmem - p.off_ring) / p.stage_bytes;
     if (p.nstages > TKD_MAX_STAGES) p.nstages = TKD_MAX_STAGES;
     if (p.nstages < 2) return TKD_ERR_UNSUPPORTED;
@@ -136,7 +129,7 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     L->off_counters = 0;
     L->off_units = (int64_t)kMaxPanels * 4;
     L->off_scratch = (int64_t)(kMaxPanels + kMaxUnits) * 4;
-    const int64_t scratch = p.nslices > 1 ? (int64_t)panels * p.nslices * p.M * TKD_PANEL_COLS * 4 : 0;
+    const int64_t scratch = p.nslices > 1 ? (int64_t)panels * p.nslices * 2 * p.M * TKD_PANEL_COLS * 4 : 0;
     L->off_ytmp = align_up(L->off_scratch + scratch, 256);
     p.ld_ytmp = (int64_t)panels * TKD_PANEL_COLS;
     const int64_t ytmp = a->topk_k && !a->topk_write_y ? (int64_t)a->topk_rows * p.ld_ytmp * 2 : 0;
@@ -162,7 +155,7 @@ const char* tkd_error_string(int code) {
     }
 }
 
-int64_t tkd_padded_cols(int64_t n) { return (n + 15) / 16 * 16; }
+int64_t tkd_padded_cols(int64_t n) { return (n + 127) / 128 * 128; }
 
 int64_t tkd_packed_bytes(int fmt, int64_t k, int64_t n) {
     return fmt_ok(fmt) ? tkd_stream_bytes(fmt, k, tkd_padded_cols(n)) : -1;
@@ -207,8 +200,8 @@ int tkd_matmul_plan(const TkdMatmul* a, TkdPlan* plan) {
     plan->panels = L.p.total_panels;
     plan->grid = L.grid;
     plan->stages = L.p.nstages;
-    plan->xslots = L.p.xslots;
-    plan->chunk_k = L.p.subsa * tkd_ksa(L.p.fmt);
+    plan->stream_warps = TKD_STREAM_WARPS;
+    plan->chunk_k = tkd_chunk_k(L.p.fmt);
     plan->smem_bytes = (int32_t)L.smem;
     plan->items = L.p.total_items;
     plan->weight_bytes = L.weight_bytes;

@@ -16,10 +16,10 @@ int tkd_launch_unpack(int fmt, int64_t K, int64_t npad, const void* stream, cons
 // --- streaming matmul (tkd_stream.cu) ---
 // (the TKD_EPI_* and TKD_DT_* codes are those of include/tkd.h)
 
-#define TKD_THREADS 416        // 1 producer warp + 8 streaming warps + 4 output warps
-#define TKD_PANEL_COLS 128     // columns one work item covers: 8 streaming warps x 16
+#define TKD_STREAM_WARPS 16    // streaming warps: 8 groups of 16 columns x 2 halves of each chunk's super-atoms
+#define TKD_THREADS ((1 + TKD_STREAM_WARPS + 4) * 32)  // + 1 producer warp + 4 output warps
+#define TKD_PANEL_COLS 128     // columns one work item covers
 #define TKD_MAX_STAGES 16
-#define TKD_MAX_XSLOTS 8
 #define TKD_SMEM_HEAD 512      // barriers and flags
 
 struct TkdSegDev {
@@ -27,10 +27,10 @@ struct TkdSegDev {
     const uint8_t* w2;    // the up weight's stream, or null
     const uint8_t* emax;  // per group of 16 columns (null for bf16)
     const uint8_t* emax2;
-    int groups;           // groups of 16 columns held by w
     int n_valid;          // real columns of w
     int out_col0;         // first output column of the segment in out (elements)
     int panel0;           // first panel of the segment in the call's panel list
+    int pad_;
 };
 
 struct TkdParams {
@@ -41,9 +41,8 @@ struct TkdParams {
     int64_t ldx;
     int ks;             // k per slice (a multiple of the chunk depth)
     int nslices;        // ceil(K / ks)
-    int subsa;          // super-atoms per chunk (one warp's share of a stage)
-    int nstages, xslots;
-    int64_t run_bytes;  // bytes of one group's run
+    int nstages;
+    int64_t panel_bytes;  // bytes of one 128-column panel of the stream
     int total_panels;
     int64_t total_items;
     int epi, act;
@@ -56,7 +55,7 @@ struct TkdParams {
     void* out;
     int out_dt;
     int64_t ldo;
-    // top-k records (tkd_stream.cu, output warps)
+    // top-k records (output warps)
     uint32_t* records;
     int topk_k, topk_rows, topk_unit, topk_slot0, write_y;
     uint32_t topk_base;
@@ -64,14 +63,13 @@ struct TkdParams {
     uint16_t* ytmp;      // bf16 outputs of a call that does not write y: [rows][ld_ytmp]
     int64_t ld_ytmp;
     int* unit_counters;
-    // split-panel partial sums
+    // slice sums of panels whose slices are spread over several CTAs: [panel][slice][half][row][128] floats
     float* scratch;
     int* counters;
     int* status;
     // shared-memory map (bytes from the start of dynamic shared memory)
-    int rs;              // bytes per x row of a slot
-    int off_x, off_pbuf, off_tbuf, off_ring;
-    int sub_bytes, stage_bytes;
+    int off_pbuf, off_tbuf, off_ring;
+    int stage_bytes;
 };
 
 int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st);

@@ -2,17 +2,19 @@
 //
 // The reference keeps a [K, N] block-float weight as 32 x 32 tiles (64 exponent bytes, then the mantissas; one shared
 // exponent per 16 consecutive n at one k; dense_reader/linear.py:49-50, moe/moe8.py:125-154). Here the same numbers
-// (sign, magnitude, shared exponent) are laid out for a warp that multiplies 16 output columns by mma.sync
-// m16n8k16 with the weights as the A operand:
+// (sign, magnitude, shared exponent) are laid out for a CTA that streams 128 output columns (a panel: 8 groups of 16)
+// through shared memory, one bulk copy per stage, and multiplies each group by mma.sync m16n8k16 with the weights as
+// the A operand:
 //
-//   stream   = one run per group of 16 output columns, runs back to back
-//   run      = ceil(K / KSA) super-atoms, K ascending
+//   stream   = panels of 128 columns back to back (N is padded to 128 with zero columns)
+//   panel    = chunks of CK k (256; 128 for bfloat16), K ascending; a chunk is what one stage of the ring holds
+//   chunk    = its 8 groups back to back, each the chunk's super-atoms, K ascending
 //   super-atom (bfloat8_b, 32 k, 544 B)  = 32 B exponent words, then 32 lanes x 16 B of codes
 //   super-atom (bfloat4_b, 64 k, 576 B)  = 64 B exponent words, then 32 lanes x 16 B of codes
 //   super-atom (bfloat16, 32 k, 1024 B)  = 2 x (32 lanes x 16 B) of A-fragment registers
 //
-// so bytes per weight stay 1.0625, 0.5625 and 2. Every super-atom size is a multiple of 16 B: any run of them is
-// a legal source of a 1-D bulk copy.
+// so bytes per weight stay 1.0625, 0.5625 and 2. Every super-atom size is a multiple of 16 B, and a chunk (or the
+// half of it that holds 4 groups) is one contiguous, 16-byte aligned source of a 1-D bulk copy.
 //
 // Inside a k32 block, lane (g = lane / 4, t = lane % 4) of mma jj (0, 1) owns k = 8 t + 4 jj + r, r = 0..3: the 8
 // activations a lane needs for the two mmas are 16 consecutive bytes of a row of x. Fragment registers: a0 = column
@@ -46,9 +48,35 @@ TKD_HD int tkd_ksa(int fmt) { return fmt == TKD_BFP4 ? 64 : 32; }               
 TKD_HD int tkd_sab(int fmt) { return fmt == TKD_BFP8 ? 544 : (fmt == TKD_BFP4 ? 576 : 1024); }  // bytes per super-atom
 TKD_HD int tkd_exp_bytes(int fmt) { return fmt == TKD_BFP8 ? 32 : (fmt == TKD_BFP4 ? 64 : 0); }
 TKD_HD int tkd_unit_exp(int fmt) { return 126 + tkd_mant_bits(fmt); }  // value = m * 2^(e - unit)
+TKD_HD int tkd_chunk_k(int fmt) { return fmt == TKD_BF16 ? 128 : 256; }                    // k per chunk (stage)
+TKD_HD int tkd_subsa(int fmt) { return tkd_chunk_k(fmt) / tkd_ksa(fmt); }                  // super-atoms per group and chunk
 TKD_HD int64_t tkd_nsa(int fmt, int64_t K) { return (K + tkd_ksa(fmt) - 1) / tkd_ksa(fmt); }
-TKD_HD int64_t tkd_run_bytes(int fmt, int64_t K) { return tkd_nsa(fmt, K) * tkd_sab(fmt); }
-TKD_HD int64_t tkd_stream_bytes(int fmt, int64_t K, int64_t npad) { return (npad / 16) * tkd_run_bytes(fmt, K); }
+TKD_HD int64_t tkd_run_bytes(int fmt, int64_t K) { return tkd_nsa(fmt, K) * tkd_sab(fmt); }  // one group, all of K
+TKD_HD int64_t tkd_panel_bytes(int fmt, int64_t K) { return 8 * tkd_run_bytes(fmt, K); }
+TKD_HD int64_t tkd_stream_bytes(int fmt, int64_t K, int64_t npad) { return (npad / 128) * tkd_panel_bytes(fmt, K); }
+// super-atoms of chunk c (the last chunk of a panel may be short)
+TKD_HD int tkd_chunk_nsa(int fmt, int64_t K, int64_t c) {
+    const int64_t left = tkd_nsa(fmt, K) - c * tkd_subsa(fmt);
+    return (int)(left < tkd_subsa(fmt) ? left : tkd_subsa(fmt));
+}
+// byte offset of super-atom `sa` (counted over all of K) of group `group` (counted over the whole weight)
+TKD_HD int64_t tkd_sa_offset(int fmt, int64_t K, int64_t group, int64_t sa) {
+    const int sub = tkd_subsa(fmt), sab = tkd_sab(fmt);
+    const int64_t c = sa / sub;
+    return (group >> 3) * tkd_panel_bytes(fmt, K) + c * sub * sab * 8 +
+           ((group & 7) * tkd_chunk_nsa(fmt, K, c) + sa % sub) * (int64_t)sab;
+}
+// ... and back: which (group, sa, byte inside the super-atom) owns byte `off` of the stream
+TKD_HD void tkd_sa_owner(int fmt, int64_t K, int64_t off, int64_t* group, int64_t* sa, int* inner) {
+    const int sub = tkd_subsa(fmt), sab = tkd_sab(fmt);
+    const int64_t pb = tkd_panel_bytes(fmt, K);
+    const int64_t panel = off / pb, r = off % pb;
+    const int64_t c = r / ((int64_t)sub * sab * 8), r2 = r % ((int64_t)sub * sab * 8);
+    const int n = tkd_chunk_nsa(fmt, K, c);
+    *group = panel * 8 + r2 / ((int64_t)n * sab);
+    *sa = c * sub + (r2 % ((int64_t)n * sab)) / sab;
+    *inner = (int)(r2 % sab);
+}
 
 TKD_HD uint32_t tkd_rotl(uint32_t v, int s) { return s ? (v << s) | (v >> (32 - s)) : v; }
 TKD_HD uint32_t tkd_rotr(uint32_t v, int s) { return s ? (v >> s) | (v << (32 - s)) : v; }
@@ -74,7 +102,7 @@ TKD_HD TkdLoc tkd_locate(int fmt, int64_t K, int64_t k, int64_t n) {
     const int t = kr >> 3, jj = (kr >> 2) & 1, r = kr & 3;
     const int lane = (i & 7) * 4 + t;
     const int ai = (i >> 3) + 2 * (r >> 1);
-    const int64_t base = group * tkd_run_bytes(fmt, K) + sa * tkd_sab(fmt);
+    const int64_t base = tkd_sa_offset(fmt, K, group, sa);
     L.half = r & 1;
     L.exp_r = r;
     if (fmt == TKD_BF16) {

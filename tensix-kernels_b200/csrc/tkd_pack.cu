@@ -110,12 +110,10 @@ __global__ void tkd_permute_kernel(int fmt, int64_t K, int64_t npad, const uint8
     const int64_t wi = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (wi >= words) return;
     const int64_t G = npad / 16;
-    const int sab = tkd_sab(fmt), ksa = tkd_ksa(fmt), eb = tkd_exp_bytes(fmt);
-    const int64_t run_words = tkd_run_bytes(fmt, K) / 4;
-    const int64_t g = wi / run_words;
-    const int64_t rw = wi % run_words;
-    const int64_t sa = rw / (sab / 4);
-    const int off = (int)(rw % (sab / 4)) * 4;  // byte offset of this word inside its super-atom
+    const int ksa = tkd_ksa(fmt), eb = tkd_exp_bytes(fmt);
+    int64_t g, sa;
+    int off;  // byte offset of this word inside its super-atom
+    tkd_sa_owner(fmt, K, wi * 4, &g, &sa, &off);
     uint32_t word = 0;
     if (fmt == TKD_BF16) {
         const uint16_t* codes = static_cast<const uint16_t*>(codes_v);

@@ -7,20 +7,25 @@
 // (dense_reader/linear.py:187-382).
 //
 // One persistent CTA per SM, three kinds of warps, coupled by mbarriers only:
-//   warp 0        producer: 1-D bulk copies (TMA, no multicast) of the weight stream and of the activation slice into
-//                 a ring of shared-memory stages;
-//   warps 1-8     streaming warps: warp w multiplies 16 output columns (one group of the stream) over the k slice of
-//                 the current item with mma.sync m16n8k16, the weights as A. Block-float codes go in as bf16
+//   warp 0        producer (one lane): one 1-D bulk copy (TMA, no multicast) per stage of the shared-memory ring; a
+//                 stage is one chunk of one panel (128 columns x 256 k), contiguous in the stream. (A bulk copy costs
+//                 the issuing SM about 140 cycles whatever its size, so stages are single copies of 17-35 KB.)
+//   warps 1-16    streaming warps: warp (group g, half h) multiplies the 16 columns of group g by every other
+//                 super-atom of the chunk with mma.sync m16n8k16, the weights as A. Block-float codes go in as bf16
 //                 subnormals (sign << 15 | magnitude) and the shared exponent is folded into the activations
-//                 (x * 2^e' is exact), so a register of two weights costs one rotate and one AND;
-//   warps 9-12    output warps (one thread per column of the 128-column panel): add the slice sums in ascending slice
-//                 order, run the output stage (exponent factor, scales, SwiGLU/GeGLU, residual, rounding), write y,
-//                 and keep the top-k records.
-// A work item is (panel of 128 columns, k slice of ks). Items are numbered panel-major and cut into equal contiguous
-// runs, one per CTA. Every slice sum starts from zero and the slices of a column are always added in ascending order
-// with plain fp32 adds, in registers when one CTA holds all of a panel's slices and through a scratch buffer
-// otherwise (the CTA that delivers a panel's last slices adds them up): a column's result depends on K, the format
-// and M's bucket only, never on N, on the number of CTAs or on the other weights of a block list.
+//                 (x * 2^e' is exact), so a register of two weights costs one rotate and one AND. The activations come
+//                 straight from global memory through L1 (16 bytes a lane per 32 k), loaded before the stage is waited
+//                 for.
+//   warps 17-20   output warps (one thread per column of the panel): finish the K sum, run the output stage (exponent
+//                 factor, scales, SwiGLU/GeGLU, residual, rounding), write y, and keep the top-k records.
+//
+// A work item is (panel, k slice of ks). Items are numbered panel-major and cut into equal contiguous runs, one per
+// CTA. The sum of a column is defined once and for all as T0 + T1, T_h = the sum over slices, in ascending order, of
+// streaming warp h's slice sum (itself acc_even + acc_odd, each started from zero per slice), all plain fp32 adds. A
+// streaming warp adds up its own slices in registers as long as its CTA holds the panel from slice 0 on; what a CTA
+// holds of a panel otherwise goes through a scratch buffer slice by slice, and the CTA that delivers last adds them
+// up in the same order. So a column's result depends on K, the format, ks and M's bucket only, never on N, on the
+// number of CTAs or on the other weights of a block list.
 //
 // Every wait is bounded: a wait that gives up records TKD_ERR_TIMEOUT in the status word, and every role then falls
 // through to the end of the kernel.
@@ -31,10 +36,24 @@
 #include "tkd_internal.h"
 #include "tkd_layout.h"
 
+#ifdef TKD_PROF
+__device__ long long tkd_prof[64];
+__device__ unsigned long long tkd_times[148 * 4];  // per CTA: entry, streaming warps done, output warps done (ns)
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define PROF_TIME(slot) do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 148) tkd_times[blockIdx.x * 4 + slot] = gtime(); } while (0)
+#define PROF_T0 long long _t0 = clock64()
+#define PROF_ADD(slot) do { long long _t1 = clock64(); if (blockIdx.x == 3 && (threadIdx.x & 31) == 0) tkd_prof[slot] += _t1 - _t0; _t0 = _t1; } while (0)
+#else
+#define PROF_T0
+#define PROF_ADD(slot)
+#define PROF_TIME(slot)
+#endif
+
 namespace {
 
-constexpr uint32_t kSpinLimit = 1u << 22;  // try_wait rounds before a wait gives up (each suspends for a while)
-constexpr int kStatusTimeout = 3;          // TKD_ERR_TIMEOUT of include/tkd.h
+constexpr uint32_t kWaitRounds = 1u << 12;   // try_wait rounds before a wait gives up ...
+constexpr uint32_t kWaitHintNs = 1000000u;   // ... each suspended for up to this long (woken at once on completion)
+constexpr int kStatusTimeout = 3;            // TKD_ERR_TIMEOUT of include/tkd.h
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -51,16 +70,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kWaitHintNs)
         : "memory");
     return ok != 0;
 }
 // Bounded wait: false (and the status word set) when the phase never completes.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i)
+    for (uint32_t i = 0; i < kWaitRounds; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     if (status) atomicExch(status, kStatusTimeout);
     return false;
@@ -71,7 +90,12 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
-__device__ __forceinline__ uint32_t rotr32(uint32_t v, int s) { return __funnelshift_r(v, v, s); }
+// rotr(w, s) & mask: a funnel shift and an AND. (The rotate as a 32 x 32 -> 64 multiply by 2^(32 - s), to move it
+// off the integer pipe this loop is bound by, measured 18 % slower on B200.)
+template <int S>
+__device__ __forceinline__ uint32_t rot_and(uint32_t w, uint32_t mask) {
+    return __funnelshift_r(w, w, S) & mask;
+}
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
@@ -95,111 +119,158 @@ __device__ __forceinline__ float act_gate(float g, int act) {
     return g / (1.f + __expf(-u));
 }
 
-struct ItemInfo {
-    int panel, slice, k0, kv, seg, pl;
+// Where a role stands in its CTA's run of items.
+struct Cursor {
+    int panel, slice, seg, pl;
 };
-__device__ __forceinline__ ItemInfo item_info(const TkdParams& p, int64_t it) {
-    ItemInfo I;
-    I.panel = (int)(it / p.nslices);
-    I.slice = (int)(it - (int64_t)I.panel * p.nslices);
-    I.k0 = I.slice * p.ks;
-    I.kv = min(p.ks, p.K - I.k0);
-    I.seg = 0;
+__device__ __forceinline__ void cursor_init(Cursor& c, const TkdParams& p, int64_t it) {
+    c.panel = (int)(it / p.nslices);
+    c.slice = (int)(it - (int64_t)c.panel * p.nslices);
+    c.seg = 0;
 #pragma unroll
     for (int s = 1; s < 4; ++s)
-        if (s < p.nseg && I.panel >= p.seg[s].panel0) I.seg = s;
-    I.pl = I.panel - p.seg[I.seg].panel0;
-    return I;
+        if (s < p.nseg && c.panel >= p.seg[s].panel0) c.seg = s;
+    c.pl = c.panel - p.seg[c.seg].panel0;
 }
-// The group of 16 columns streaming warp w of a panel works on: its run's base, or null when the panel has none.
-__device__ __forceinline__ const uint8_t* warp_run(const TkdParams& p, const ItemInfo& I, int w) {
-    const TkdSegDev& s = p.seg[I.seg];
-    if (p.epi == TKD_EPI_GLU2) {
-        const int g = I.pl * 4 + (w & 3);
-        if (g >= s.groups) return nullptr;
-        return (w < 4 ? s.w : s.w2) + (int64_t)g * p.run_bytes;
+__device__ __forceinline__ void cursor_next(Cursor& c, const TkdParams& p) {
+    if (++c.slice == p.nslices) {
+        c.slice = 0;
+        ++c.panel;
+        if (c.seg + 1 < p.nseg && c.panel >= p.seg[c.seg + 1].panel0) ++c.seg;
+        c.pl = c.panel - p.seg[c.seg].panel0;
     }
-    const int g = I.pl * 8 + w;
-    return g < s.groups ? s.w + (int64_t)g * p.run_bytes : nullptr;
+}
+// What a CTA does with an item's slice sums (the same answer in every role).
+struct Flow {
+    bool start;    // the running sum starts over with this slice
+    bool split;    // the panel's slices are spread over several CTAs: sums go to the scratch buffer
+    bool store;    // split: the running sum is written to the scratch slot of (panel, slice) after this slice
+    bool deliver;  // the streaming warps signal the output warps after this slice (whole: with their sums)
+    int count;     // split and deliver: slices of the panel this CTA has contributed
+};
+__device__ __forceinline__ Flow flow_of(const Cursor& c, const TkdParams& p, int64_t it, int64_t i0, int64_t i1) {
+    Flow f;
+    const int64_t pfirst = (int64_t)c.panel * p.nslices;
+    const bool nonprefix = pfirst < i0;  // the run begins inside this panel, past its slice 0
+    const bool last_here = c.slice == p.nslices - 1 || it == i1 - 1;
+    f.start = nonprefix || c.slice == 0;
+    f.split = nonprefix || pfirst + p.nslices > i1;
+    f.store = f.split && (nonprefix || last_here);
+    f.deliver = last_here;
+    f.count = nonprefix ? c.slice - (int)(i0 - pfirst) + 1 : c.slice + 1;
+    return f;
 }
 
 template <int FMT>
 struct Fmt;
 template <>
 struct Fmt<TKD_BFP8> {
-    static constexpr int KSA = 32, SAB = 544;
+    static constexpr int KSA = 32, SAB = 544, SUBSA = 8, XB = 1;
 };
 template <>
 struct Fmt<TKD_BFP4> {
-    static constexpr int KSA = 64, SAB = 576;
+    static constexpr int KSA = 64, SAB = 576, SUBSA = 4, XB = 2;
 };
 template <>
 struct Fmt<TKD_BF16> {
-    static constexpr int KSA = 32, SAB = 1024;
+    static constexpr int KSA = 32, SAB = 1024, SUBSA = 4, XB = 1;
 };
 
-// One chunk (nsa super-atoms of one group) times the activation slice rows in shared memory.
-// xrow[tile]: this lane's row of x (row 8 tile + lane / 4) at the slice's first k, or null beyond M.
-template <int FMT, int MT>
-__device__ __forceinline__ void chunk_mma(float (&acc)[MT][4], const uint8_t* sub, int nsa, int kk0, int kv,
-                                          const uint8_t* const (&xrow)[MT], int lane) {
+// The two mmas of one k32 block of one group of a block-float weight: cw / ew are this lane's code and exponent
+// words of the block (bfloat4_b: 2 and 2; bfloat8_b: 4 and 2).
+template <int FMT, int MT, int NA>
+__device__ __forceinline__ void block_mma(float (&acc)[NA][MT][4], const uint32_t (&cw)[4], const uint32_t (&ew)[2],
+                                          const uint4 (&xv)[MT]) {
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj) {
+        uint32_t a0, a1, a2, a3;
+        if constexpr (FMT == TKD_BFP4) {
+            const uint32_t w = cw[jj];
+            a0 = w & 0x80078007u, a1 = rot_and<4>(w, 0x80078007u);
+            a2 = rot_and<8>(w, 0x80078007u), a3 = rot_and<12>(w, 0x80078007u);
+        } else {
+            const uint32_t w0 = cw[2 * jj], w1 = cw[2 * jj + 1];
+            a0 = w0 & 0x807F807Fu, a1 = rot_and<8>(w0, 0x807F807Fu);
+            a2 = w1 & 0x807F807Fu, a3 = rot_and<8>(w1, 0x807F807Fu);
+        }
+        const uint32_t s0 = ew[jj] & 0x7F807F80u, s1 = rot_and<8>(ew[jj], 0x7F807F80u);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const uint32_t x0 = jj ? xv[m].z : xv[m].x, x1 = jj ? xv[m].w : xv[m].y;
+            mma_bf16(acc[jj % NA][m], a0, a1, a2, a3, mul_bf16x2(x0, s0), mul_bf16x2(x1, s1));
+        }
+    }
+}
+
+__device__ __forceinline__ uint4 ldg_x(const uint16_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+// One streaming warp's share of one chunk: super-atoms h, h + 2, ... of the group at `sub`. kc: the chunk's first k;
+// xp[m]: this lane's row of x at k = 8 t. FULL: the chunk has all its super-atoms and ends within K.
+template <int FMT, int MT, int NA, bool FULL>
+__device__ __forceinline__ void chunk_mma(float (&acc)[NA][MT][4], const uint8_t* sub, int h, int nsa, int kc, int K,
+                                          const uint16_t* const (&xp)[MT], int lane, uint32_t full_bar, uint32_t parity,
+                                          int* status, bool& ok) {
+    using F = Fmt<FMT>;
+    constexpr int NPW = F::SUBSA / 2;  // super-atoms a warp takes of a chunk
+    constexpr bool PREFETCH = MT <= 2;
+    constexpr int NXP = PREFETCH ? NPW * F::XB : 1;
     const int t = lane & 3;
-    for (int sa = 0; sa < nsa; ++sa) {
-        const uint8_t* b = sub + sa * Fmt<FMT>::SAB;
-        const int kk = kk0 + sa * Fmt<FMT>::KSA;
+    uint4 xpre[NXP][MT];
+    auto load_x = [&](int i, int q, uint4(&xv)[MT]) {
+        const int k = kc + (h + 2 * i) * F::KSA + 32 * q;
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+            xv[m] = FULL || k < K ? ldg_x(xp[m] + k) : make_uint4(0, 0, 0, 0);
+    };
+    PROF_T0;
+    if constexpr (PREFETCH) {
+#pragma unroll
+        for (int i = 0; i < NPW; ++i)
+#pragma unroll
+            for (int q = 0; q < F::XB; ++q) load_x(i, q, xpre[i * F::XB + q]);
+    }
+#ifdef TKD_PROF
+    if (threadIdx.x < 64) { asm volatile("" :: "r"(xpre[0][0].x)); PROF_ADD(20); }
+#endif
+    ok = mbar_wait(full_bar, parity, status);
+    if (!ok) return;
+#ifdef TKD_PROF
+    if (threadIdx.x < 64) PROF_ADD(21);
+#endif
+#pragma unroll
+    for (int i = 0; i < NPW; ++i) {
+        const int sa = h + 2 * i;
+        if (!FULL && sa >= nsa) break;
+        const uint8_t* b = sub + sa * F::SAB;
+        uint32_t cw[F::XB][4], ew[F::XB][2];
         if constexpr (FMT == TKD_BFP4) {
             const uint4 ev = *reinterpret_cast<const uint4*>(b + t * 16);
             const uint4 cv = *reinterpret_cast<const uint4*>(b + 64 + lane * 16);
-            const uint32_t ew[4] = {ev.x, ev.y, ev.z, ev.w}, cw[4] = {cv.x, cv.y, cv.z, cv.w};
-#pragma unroll
-            for (int qq = 0; qq < 2; ++qq) {
-                if (kk + 32 * qq >= kv) break;  // a K that ends in the middle of a super-atom
-                uint4 xv[MT];
-#pragma unroll
-                for (int m = 0; m < MT; ++m)
-                    xv[m] = xrow[m] ? *reinterpret_cast<const uint4*>(xrow[m] + (kk + 32 * qq + 8 * t) * 2)
-                                    : make_uint4(0, 0, 0, 0);
-#pragma unroll
-                for (int jj = 0; jj < 2; ++jj) {
-                    const uint32_t w = cw[2 * qq + jj], e = ew[2 * qq + jj];
-                    const uint32_t a0 = w & 0x80078007u, a1 = rotr32(w, 4) & 0x80078007u;
-                    const uint32_t a2 = rotr32(w, 8) & 0x80078007u, a3 = rotr32(w, 12) & 0x80078007u;
-                    const uint32_t s0 = e & 0x7F807F80u, s1 = rotr32(e, 8) & 0x7F807F80u;
-#pragma unroll
-                    for (int m = 0; m < MT; ++m)
-                        mma_bf16(acc[m], a0, a1, a2, a3, mul_bf16x2(jj ? xv[m].z : xv[m].x, s0),
-                                 mul_bf16x2(jj ? xv[m].w : xv[m].y, s1));
-                }
-            }
+            cw[0][0] = cv.x, cw[0][1] = cv.y, cw[1][0] = cv.z, cw[1][1] = cv.w;
+            cw[0][2] = cw[0][3] = cw[1][2] = cw[1][3] = 0;
+            ew[0][0] = ev.x, ew[0][1] = ev.y, ew[1][0] = ev.z, ew[1][1] = ev.w;
         } else if constexpr (FMT == TKD_BFP8) {
             const uint2 ev = *reinterpret_cast<const uint2*>(b + t * 8);
             const uint4 cv = *reinterpret_cast<const uint4*>(b + 32 + lane * 16);
-            uint4 xv[MT];
+            cw[0][0] = cv.x, cw[0][1] = cv.y, cw[0][2] = cv.z, cw[0][3] = cv.w;
+            ew[0][0] = ev.x, ew[0][1] = ev.y;
+        }
 #pragma unroll
-            for (int m = 0; m < MT; ++m)
-                xv[m] = xrow[m] ? *reinterpret_cast<const uint4*>(xrow[m] + (kk + 8 * t) * 2) : make_uint4(0, 0, 0, 0);
+        for (int q = 0; q < F::XB; ++q) {
+            if (!FULL && kc + sa * F::KSA + 32 * q >= K) break;  // a K that ends inside a super-atom
+            uint4 xnow[MT];
+            if constexpr (!PREFETCH) load_x(i, q, xnow);
+            const uint4(&xv)[MT] = PREFETCH ? xpre[PREFETCH ? i * F::XB + q : 0] : xnow;
+            if constexpr (FMT == TKD_BF16) {
 #pragma unroll
-            for (int jj = 0; jj < 2; ++jj) {
-                const uint32_t w0 = jj ? cv.z : cv.x, w1 = jj ? cv.w : cv.y, e = jj ? ev.y : ev.x;
-                const uint32_t a0 = w0 & 0x807F807Fu, a1 = rotr32(w0, 8) & 0x807F807Fu;
-                const uint32_t a2 = w1 & 0x807F807Fu, a3 = rotr32(w1, 8) & 0x807F807Fu;
-                const uint32_t s0 = e & 0x7F807F80u, s1 = rotr32(e, 8) & 0x7F807F80u;
+                for (int jj = 0; jj < 2; ++jj) {
+                    const uint4 a = *reinterpret_cast<const uint4*>(b + jj * 512 + lane * 16);
 #pragma unroll
-                for (int m = 0; m < MT; ++m)
-                    mma_bf16(acc[m], a0, a1, a2, a3, mul_bf16x2(jj ? xv[m].z : xv[m].x, s0),
-                             mul_bf16x2(jj ? xv[m].w : xv[m].y, s1));
-            }
-        } else {
-            uint4 xv[MT];
-#pragma unroll
-            for (int m = 0; m < MT; ++m)
-                xv[m] = xrow[m] ? *reinterpret_cast<const uint4*>(xrow[m] + (kk + 8 * t) * 2) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int jj = 0; jj < 2; ++jj) {
-                const uint4 a = *reinterpret_cast<const uint4*>(b + jj * 512 + lane * 16);
-#pragma unroll
-                for (int m = 0; m < MT; ++m)
-                    mma_bf16(acc[m], a.x, a.y, a.z, a.w, jj ? xv[m].z : xv[m].x, jj ? xv[m].w : xv[m].y);
+                    for (int m = 0; m < MT; ++m)
+                        mma_bf16(acc[jj % NA][m], a.x, a.y, a.z, a.w, jj ? xv[m].z : xv[m].x, jj ? xv[m].w : xv[m].y);
+                }
+            } else {
+                block_mma<FMT, MT, NA>(acc, cw[q], ew[q], xv);
             }
         }
     }
@@ -211,29 +282,29 @@ __device__ __forceinline__ uint32_t topk_key(uint16_t b) {
 }
 
 template <int FMT, int MT>
-__global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const TkdParams p) {
+__global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid_constant__ TkdParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int MP = MT == 1 ? 8 : (MT == 2 ? 24 : 40);  // floats per column in the partial buffers
+    using F = Fmt<FMT>;
+    constexpr int MP = MT == 1 ? 8 : (MT == 2 ? 24 : 40);  // floats per column in the hand-over buffers
     constexpr int MR = 8 * MT;                             // rows the accumulators cover
+    constexpr int NA = MT == 1 ? 2 : 1;                    // accumulator sets a streaming warp alternates between
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TKD_MAX_STAGES);
-    const uint32_t xempty0 = smem_u32(bars + 2 * TKD_MAX_STAGES);
-    const uint32_t pfull0 = smem_u32(bars + 2 * TKD_MAX_STAGES + TKD_MAX_XSLOTS), pempty0 = pfull0 + 16;
+    const uint32_t pfull0 = smem_u32(bars + 2 * TKD_MAX_STAGES), pempty0 = pfull0 + 16;
     volatile int* sflag = reinterpret_cast<volatile int*>(smem + TKD_SMEM_HEAD - 16);
-    uint8_t* xbuf = smem + p.off_x;
-    float* pbuf = reinterpret_cast<float*>(smem + p.off_pbuf);
-    float* tbuf = reinterpret_cast<float*>(smem + p.off_tbuf);
+    float* pbuf = reinterpret_cast<float*>(smem + p.off_pbuf);  // [2 buffers][2 halves][128 columns][MP]
+    float* tbuf = reinterpret_cast<float*>(smem + p.off_tbuf);  // [128 columns][MP]
     uint8_t* ring = smem + p.off_ring;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) PROF_TIME(0);
     if (tid == 0) {
         for (int s = 0; s < p.nstages; ++s) {
             mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 8);
+            mbar_init(empty0 + 8 * s, TKD_STREAM_WARPS);
         }
-        for (int s = 0; s < p.xslots; ++s) mbar_init(xempty0 + 8 * s, 8);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(pfull0 + 8 * s, 8);
+            mbar_init(pfull0 + 8 * s, TKD_STREAM_WARPS);
             mbar_init(pempty0 + 8 * s, 4);
         }
         sflag[0] = 0;
@@ -243,171 +314,262 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const TkdPar
 
     const int64_t T = p.total_items;
     const int64_t i0 = T * blockIdx.x / gridDim.x, i1 = T * (blockIdx.x + 1) / gridDim.x;
-    const int nst = p.nstages, xsl = p.xslots;
-    const int M = p.M;
+    const int nst = p.nstages;
+    const int M = p.M, K = p.K;
+    const bool glu2 = p.epi == TKD_EPI_GLU2;
+    constexpr int CK = F::SUBSA * F::KSA;
+    const int nsa_total = (K + F::KSA - 1) / F::KSA;
+    if (i0 >= i1) return;
+    // Order of a CTA's items: if its run ends inside a panel that it holds from slice 0 on, those slices come first.
+    // Their sum is one of several the panel is added up from by whichever CTA delivers last; done first, that exchange
+    // overlaps the rest of the run instead of sitting at the kernel's end.
+    const int64_t lastp0 = (i1 - 1) / p.nslices * p.nslices;
+    const int64_t tail0 = lastp0 > i0 && lastp0 + p.nslices > i1 ? lastp0 : i1;
+    const int64_t lead = i1 - tail0;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
-        uint32_t st = 0, xi = 0;
+        if (lane != 0) return;
+        Cursor c;
+        uint32_t st = 0;
         bool ok = true;
-        for (int64_t it = i0; it < i1 && ok; ++it, ++xi) {
-            const ItemInfo I = item_info(p, it);
-            const uint8_t* run = lane < 8 ? warp_run(p, I, lane) : nullptr;
-            const int nvalid = __popc(__ballot_sync(0xFFFFFFFFu, run != nullptr));
-            const uint32_t xs = xi % xsl;
-            if (lane == 0) ok = mbar_wait(xempty0 + 8 * xs, ((xi / xsl) & 1) ^ 1, p.status);
-            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-            if (!ok) break;
-            const int nsa_total = (I.kv + Fmt<FMT>::KSA - 1) / Fmt<FMT>::KSA;
-            const int sa0 = I.k0 / Fmt<FMT>::KSA;
-            const int nch = (nsa_total + p.subsa - 1) / p.subsa;
+        for (int64_t j = 0; j < i1 - i0 && ok; ++j) {
+            const int64_t it = j < lead ? tail0 + j : i0 + (j - lead);
+            if (j == 0 || j == lead)
+                cursor_init(c, p, it);
+            else
+                cursor_next(c, p);
+            const TkdSegDev& sg = p.seg[c.seg];
+            const int k0 = c.slice * p.ks, kv = min(p.ks, K - k0);
+            const int c0 = k0 / CK, nch = (kv + CK - 1) / CK;
+            // a panel of a (gate, up) pair is half a panel of each weight: 4 groups of the gate's, 4 of the up's
+            const uint8_t* src = sg.w + (int64_t)(glu2 ? c.pl >> 1 : c.pl) * p.panel_bytes;
+            const uint8_t* src2 = glu2 ? sg.w2 + (int64_t)(c.pl >> 1) * p.panel_bytes : nullptr;
             for (int ch = 0; ch < nch; ++ch, ++st) {
                 const uint32_t s = st % nst;
-                if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ((st / nst) & 1) ^ 1, p.status);
-                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                PROF_T0;
+                ok = mbar_wait(empty0 + 8 * s, ((st / nst) & 1) ^ 1, p.status);
                 if (!ok) break;
-                const int nsa = min(p.subsa, nsa_total - ch * p.subsa);
-                const uint32_t wbytes = (uint32_t)nsa * Fmt<FMT>::SAB;
-                const uint32_t xbytes = ch == 0 ? (uint32_t)I.kv * 2u : 0u;
-                if (lane == 0) mbar_expect_tx(full0 + 8 * s, nvalid * wbytes + M * xbytes);
-                __syncwarp();
-                if (run)
-                    bulk_g2s(smem_u32(ring + (size_t)s * p.stage_bytes + lane * p.sub_bytes),
-                             run + (int64_t)(sa0 + ch * p.subsa) * Fmt<FMT>::SAB, wbytes, full0 + 8 * s);
-                if (ch == 0 && lane >= 8)
-                    for (int m = lane - 8; m < M; m += 24)
-                        bulk_g2s(smem_u32(xbuf + ((size_t)xs * M + m) * p.rs), p.x + (int64_t)m * p.ldx + I.k0, xbytes,
-                                 full0 + 8 * s);
+                PROF_ADD(1);
+                const int nsa = min(F::SUBSA, nsa_total - (c0 + ch) * F::SUBSA);
+                const uint32_t gbytes = (uint32_t)nsa * F::SAB;  // one group's share of the chunk
+                const int64_t coff = (int64_t)(c0 + ch) * (F::SUBSA * F::SAB * 8);
+                const uint32_t dst = smem_u32(ring + (size_t)s * p.stage_bytes);
+                mbar_expect_tx(full0 + 8 * s, 8 * gbytes);
+                if (glu2) {
+                    const int64_t hoff = coff + (int64_t)(c.pl & 1) * 4 * gbytes;
+                    bulk_g2s(dst, src + hoff, 4 * gbytes, full0 + 8 * s);
+                    bulk_g2s(dst + 4 * gbytes, src2 + hoff, 4 * gbytes, full0 + 8 * s);
+                } else {
+                    bulk_g2s(dst, src + coff, 8 * gbytes, full0 + 8 * s);
+                }
+                PROF_ADD(2);
             }
         }
         // (every stage issued above is waited for by the streaming warps before they leave; after a timeout the copies
         // still in flight are given a bounded wait here so that none lands after the CTA has gone)
-        if (!ok && lane == 0) {
+        if (!ok) {
             for (uint32_t back = 1; back <= (uint32_t)nst && back <= st; ++back) {
                 const uint32_t q = st - back;
-                for (uint32_t i = 0; i < (1u << 16); ++i)
+                for (uint32_t i = 0; i < 64; ++i)
                     if (mbar_try_wait(full0 + 8 * (q % nst), (q / nst) & 1)) break;
             }
         }
-    } else if (warp <= 8) {
+    } else if (warp <= TKD_STREAM_WARPS) {
         // ---------------------------------------------------------------- streaming warps
         const int cw = warp - 1;
+        const int g8 = cw & 7, h = cw >> 3;
         const int g = lane >> 2, t = lane & 3;
-        uint32_t st = 0, xi = 0, pi = 0;
+        const uint16_t* xp[MT];
+#pragma unroll
+        // (a lane whose row lies beyond M reads row M - 1 instead: a B column only feeds its own output column, and
+        // the columns beyond M are never read, so those lanes need no predicate and no zero fill)
+        for (int m = 0; m < MT; ++m) xp[m] = p.x + (int64_t)min(8 * m + g, M - 1) * p.ldx + 8 * t;
+        Cursor c;
+        uint32_t slot = 0, phase = 0, pi = 0;  // ring position and its parity
         bool ok = true;
-        for (int64_t it = i0; it < i1 && ok; ++it, ++xi, ++pi) {
-            const ItemInfo I = item_info(p, it);
-            const bool valid = warp_run(p, I, cw) != nullptr;
-            const uint32_t xs = xi % xsl;
-            const uint8_t* xrow[MT];
+        float tot[MT][4];
+        for (int64_t j = 0; j < i1 - i0 && ok; ++j) {
+            const int64_t it = j < lead ? tail0 + j : i0 + (j - lead);
+            if (j == 0 || j == lead)
+                cursor_init(c, p, it);
+            else
+                cursor_next(c, p);
+            const Flow f = flow_of(c, p, it, i0, i1);
+            const int k0 = c.slice * p.ks, kv = min(p.ks, K - k0);
+            const int c0 = k0 / CK, nch = (kv + CK - 1) / CK;
+            float acc[NA][MT][4];
 #pragma unroll
-            for (int m = 0; m < MT; ++m)
-                xrow[m] = 8 * m + g < M ? xbuf + ((size_t)xs * M + 8 * m + g) * p.rs : nullptr;
-            float acc[MT][4];
+            for (int j = 0; j < NA; ++j)
 #pragma unroll
-            for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
-            const int nsa_total = (I.kv + Fmt<FMT>::KSA - 1) / Fmt<FMT>::KSA;
-            const int nch = (nsa_total + p.subsa - 1) / p.subsa;
-            for (int ch = 0; ch < nch; ++ch, ++st) {
-                const uint32_t s = st % nst;
-                ok = mbar_wait(full0 + 8 * s, (st / nst) & 1, p.status);
+                for (int m = 0; m < MT; ++m) acc[j][m][0] = acc[j][m][1] = acc[j][m][2] = acc[j][m][3] = 0.f;
+            PROF_T0;
+            for (int ch = 0; ch < nch; ++ch) {
+                const int kc = (c0 + ch) * CK;
+                const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
+                if (kc + CK <= K) {
+                    chunk_mma<FMT, MT, NA, true>(acc, stage + g8 * (F::SUBSA * F::SAB), h, F::SUBSA, kc, K, xp, lane,
+                                                 full0 + 8 * slot, phase, p.status, ok);
+                } else {
+                    const int nsa = nsa_total - (c0 + ch) * F::SUBSA;
+                    chunk_mma<FMT, MT, NA, false>(acc, stage + g8 * nsa * F::SAB, h, nsa, kc, K, xp, lane,
+                                                  full0 + 8 * slot, phase, p.status, ok);
+                }
                 if (!ok) break;
-                if (valid)
-                    chunk_mma<FMT, MT>(acc, ring + (size_t)s * p.stage_bytes + cw * p.sub_bytes,
-                                       min(p.subsa, nsa_total - ch * p.subsa), ch * p.subsa * Fmt<FMT>::KSA, I.kv, xrow,
-                                       lane);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(empty0 + 8 * s);
+                if (lane == 0) mbar_arrive(empty0 + 8 * slot);
+                if (++slot == (uint32_t)nst) slot = 0, phase ^= 1;
+                if (warp == 1) PROF_ADD(9);
             }
             if (!ok) break;
-            if (lane == 0) mbar_arrive(xempty0 + 8 * xs);
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float part = NA == 2 ? acc[0][m][e] + acc[NA - 1][m][e] : acc[0][m][e];
+                    tot[m][e] = f.start ? part : tot[m][e] + part;
+                }
+            if (f.store) {
+                // straight into the scratch slot of (panel, slice): [half][row][128 columns]
+                float* sc = p.scratch + (((size_t)c.panel * p.nslices + c.slice) * 2 + h) * M * TKD_PANEL_COLS + g8 * 16 + g;
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    const int r0 = 8 * m + 2 * t;
+                    if (r0 < M) {
+                        __stcg(sc + (size_t)r0 * TKD_PANEL_COLS, tot[m][0]);
+                        __stcg(sc + (size_t)r0 * TKD_PANEL_COLS + 8, tot[m][2]);
+                    }
+                    if (r0 + 1 < M) {
+                        __stcg(sc + (size_t)(r0 + 1) * TKD_PANEL_COLS, tot[m][1]);
+                        __stcg(sc + (size_t)(r0 + 1) * TKD_PANEL_COLS + 8, tot[m][3]);
+                    }
+                }
+            }
+            if (!f.deliver) continue;
             const uint32_t pb = pi & 1;
             ok = mbar_wait(pempty0 + 8 * pb, ((pi >> 1) & 1) ^ 1, p.status);
             if (!ok) break;
-            float* pc = pbuf + ((size_t)pb * TKD_PANEL_COLS + cw * 16 + g) * MP + 2 * t;
+            if (warp == 1) PROF_ADD(10);
+            if (!f.split) {
+                float* pc = pbuf + ((size_t)(pb * 2 + h) * TKD_PANEL_COLS + g8 * 16 + g) * MP + 2 * t;
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                *reinterpret_cast<float2*>(pc + 8 * m) = make_float2(acc[m][0], acc[m][1]);
-                *reinterpret_cast<float2*>(pc + 8 * MP + 8 * m) = make_float2(acc[m][2], acc[m][3]);
+                for (int m = 0; m < MT; ++m) {
+                    *reinterpret_cast<float2*>(pc + 8 * m) = make_float2(tot[m][0], tot[m][1]);
+                    *reinterpret_cast<float2*>(pc + 8 * MP + 8 * m) = make_float2(tot[m][2], tot[m][3]);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(pfull0 + 8 * pb);
+            ++pi;
+            if (warp == 1) PROF_ADD(11);
         }
+        if (warp == 1) PROF_TIME(1);
     } else {
         // ---------------------------------------------------------------- output warps
-        const int et = tid - 9 * 32;  // the panel column this thread owns
+        const int et = tid - (1 + TKD_STREAM_WARPS) * 32;  // the panel column this thread owns
+        const int ow = warp - (1 + TKD_STREAM_WARPS);
+        Cursor c;
         uint32_t pi = 0;
-        int given = 0;                // slices of the current split panel this CTA has put into scratch
         float tot[MR];
         bool ok = true;
-        for (int64_t it = i0; it < i1 && ok; ++it, ++pi) {
-            const ItemInfo I = item_info(p, it);
-            const TkdSegDev& sg = p.seg[I.seg];
+        for (int64_t j = 0; j < i1 - i0 && ok; ++j) {
+            const int64_t it = j < lead ? tail0 + j : i0 + (j - lead);
+            if (j == 0 || j == lead)
+                cursor_init(c, p, it);
+            else
+                cursor_next(c, p);
+            const Flow f = flow_of(c, p, it, i0, i1);
+            if (!f.deliver) continue;
+            const TkdSegDev& sg = p.seg[c.seg];
             const uint32_t pb = pi & 1;
+            PROF_T0;
             ok = mbar_wait(pfull0 + 8 * pb, (pi >> 1) & 1, p.status);
             if (!ok) break;
-            float part[MR];
-            const float* pc = pbuf + ((size_t)pb * TKD_PANEL_COLS + et) * MP;
+            if (ow == 0) PROF_ADD(16);
+            bool finish = !f.split;
+            if (!f.split) {
+                // the two halves' sums cover the whole panel
 #pragma unroll
-            for (int m = 0; m < MR; m += 4) {
-                const float4 v = *reinterpret_cast<const float4*>(pc + m);
-                part[m] = v.x, part[m + 1] = v.y, part[m + 2] = v.z, part[m + 3] = v.w;
+                for (int hh = 0; hh < 2; ++hh) {
+                    const float* pc = pbuf + ((size_t)(pb * 2 + hh) * TKD_PANEL_COLS + et) * MP;
+#pragma unroll
+                    for (int m = 0; m < MR; m += 4) {
+                        const float4 v = *reinterpret_cast<const float4*>(pc + m);
+                        const float part[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) tot[m + e] = hh == 0 ? part[e] : tot[m + e] + part[e];
+                    }
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(pempty0 + 8 * pb);
-
-            const int64_t pfirst = (int64_t)I.panel * p.nslices;
-            const bool whole = pfirst >= i0 && pfirst + p.nslices <= i1;
-            const bool last_here = I.slice == p.nslices - 1 || it == i1 - 1;
-            bool finish = false;
-            if (whole) {
-#pragma unroll
-                for (int m = 0; m < MR; ++m) tot[m] = I.slice == 0 ? part[m] : tot[m] + part[m];
-                finish = I.slice == p.nslices - 1;
-            } else {
-                float* sc = p.scratch + (((size_t)I.panel * p.nslices + I.slice) * M) * TKD_PANEL_COLS + et;
-#pragma unroll
-                for (int m = 0; m < MR; ++m)
-                    if (m < M) __stcg(sc + (size_t)m * TKD_PANEL_COLS, part[m]);
-                ++given;
-                if (last_here) {
+            ++pi;
+            if (f.split) {
+                // the streaming warps have put this CTA's slices of the panel into the scratch buffer (their arrival
+                // on the hand-over barrier orders those stores before this point): count them in, and if they were
+                // the last the panel waited for, add all of its slices up
+                if (et == 0) {
                     __threadfence();
-                    bar_output_warps();
-                    if (et == 0) {
-                        const int old = atomicAdd(p.counters + I.panel, given);
-                        const int last = old + given == p.nslices;
-                        if (last) p.counters[I.panel] = 0;  // ready for the next call
-                        sflag[0] = last;
-                    }
-                    bar_output_warps();
-                    finish = sflag[0] != 0;
-                    given = 0;
-                    if (finish) {
-                        __threadfence();
-                        const float* s0 = p.scratch + ((size_t)I.panel * p.nslices * M) * TKD_PANEL_COLS + et;
+                    const int old = atomicAdd(p.counters + c.panel, f.count);
+                    const int last = old + f.count == p.nslices;
+                    if (last) p.counters[c.panel] = 0;  // ready for the next call
+                    __threadfence();
+                    sflag[0] = last;
+                }
+                bar_output_warps();
+                finish = sflag[0] != 0;
+                if (finish) {
+                    // the panel's first slices came as one sum from the CTA that holds its slice 0: up to where?
+                    const int64_t pfirst = (int64_t)c.panel * p.nslices;
+                    const int64_t owner = ((pfirst + 1) * gridDim.x - 1) / T;
+                    const int64_t oend = T * (owner + 1) / gridDim.x;
+                    const int pe = (int)min((int64_t)p.nslices, oend - pfirst);
+                    const float* s0 = p.scratch + pfirst * 2 * M * TKD_PANEL_COLS + et;
+                    // term (s, hh, m) of the sums; the adds run in slice order, the loads many at a time
+                    auto term = [&](int s, int hh, int m) {
+                        return __ldcg(s0 + ((size_t)(s * 2 + hh) * M + m) * TKD_PANEL_COLS);
+                    };
+                    if (M == 1) {
+                        float t0 = term(pe - 1, 0, 0), t1 = term(pe - 1, 1, 0);
+                        for (int s = pe; s < p.nslices; s += 16) {
+                            float v0[16], v1[16];
 #pragma unroll
-                        for (int m = 0; m < MR; ++m) tot[m] = 0.f;
-                        for (int s = 0; s < p.nslices; ++s)
+                            for (int j = 0; j < 16; ++j)
+                                if (s + j < p.nslices) v0[j] = term(s + j, 0, 0), v1[j] = term(s + j, 1, 0);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (s + j < p.nslices) t0 += v0[j], t1 += v1[j];
+                        }
+                        tot[0] = t0 + t1;
+                    } else {
+                        float th[2][MR];
+#pragma unroll
+                        for (int m = 0; m < MR; ++m)
+                            if (m < M) th[0][m] = term(pe - 1, 0, m), th[1][m] = term(pe - 1, 1, m);
+                        for (int s = pe; s < p.nslices; ++s) {
+                            float v[2][MR];
 #pragma unroll
                             for (int m = 0; m < MR; ++m)
-                                if (m < M) {
-                                    const float v = __ldcg(s0 + ((size_t)s * M + m) * TKD_PANEL_COLS);
-                                    tot[m] = s == 0 ? v : tot[m] + v;
-                                }
+                                if (m < M) v[0][m] = term(s, 0, m), v[1][m] = term(s, 1, m);
+#pragma unroll
+                            for (int m = 0; m < MR; ++m)
+                                if (m < M) th[0][m] += v[0][m], th[1][m] += v[1][m];
+                        }
+#pragma unroll
+                        for (int m = 0; m < MR; ++m) tot[m] = th[0][m] + th[1][m];
                     }
-                    bar_output_warps();  // sflag may be written again only after everyone has read it
                 }
+                bar_output_warps();  // sflag may be written again only after everyone has read it
             }
+            if (ow == 0) PROF_ADD(17);
             if (!finish) continue;
 
             // ------------------------------------------------------------ the output stage of one panel
-            const bool glu2 = p.epi == TKD_EPI_GLU2;
             // this thread's column within its weight, and the block-float factor of its group
-            const int n = glu2 ? I.pl * 64 + (et & 63) : I.pl * TKD_PANEL_COLS + et;
-            const uint8_t* em = glu2 && et >= 64 ? sg.emax2 : sg.emax;
+            const int n = glu2 ? c.pl * 64 + (et & 63) : c.pl * TKD_PANEL_COLS + et;
             if constexpr (FMT != TKD_BF16) {
-                const int ngroup = n >> 4;
-                const int e = ngroup < sg.groups ? (int)em[ngroup] + 64 - (FMT == TKD_BFP8 ? 133 : 129) : 0;
+                const uint8_t* em = glu2 && et >= 64 ? sg.emax2 : sg.emax;
+                const int e = (int)em[n >> 4] + 64 - (FMT == TKD_BFP8 ? 133 : 129);
 #pragma unroll
                 for (int m = 0; m < MR; ++m) tot[m] = scalbnf(tot[m], e);
             }
@@ -430,8 +592,8 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const TkdPar
                 if (et < 64) {
                     // interleaved: 32 gate columns, then their 32 up columns; two weights: gate 0-63, up 64-127
                     const int gc = glu2 ? et : 64 * (et >> 5) + (et & 31), uc = glu2 ? et + 64 : gc + 32;
-                    const int nw = glu2 ? n : I.pl * TKD_PANEL_COLS + uc;  // the pair's last column in the weight
-                    if (nw < sg.n_valid) ocol = sg.out_col0 + I.pl * 64 + et;
+                    const int nw = glu2 ? n : c.pl * TKD_PANEL_COLS + uc;  // the pair's last column in the weight
+                    if (nw < sg.n_valid) ocol = sg.out_col0 + c.pl * 64 + et;
                     const float* gp = tbuf + (size_t)gc * MP;
                     const float* up = tbuf + (size_t)uc * MP;
 #pragma unroll
@@ -465,12 +627,13 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const TkdPar
                         }
                 }
             }
+            if (ow == 0) PROF_ADD(18);
             if (p.topk_k == 0) continue;
 
             // ------------------------------------------------------------ top-k records: one per unit of columns,
             // made by the CTA that completes the unit's last panel, from the bf16 outputs themselves
             const int upanels = p.topk_unit / TKD_PANEL_COLS;
-            const int unit = I.pl / upanels;
+            const int unit = c.pl / upanels;
             const int in_unit = min(upanels, p.total_panels - unit * upanels);
             __threadfence();
             bar_output_warps();
@@ -487,7 +650,7 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const TkdPar
             __threadfence();
             const uint16_t* ysrc = p.write_y ? y16 + sg.out_col0 : p.ytmp;
             const int64_t ldy = p.write_y ? p.ldo : p.ld_ytmp;
-            const int c0 = unit * p.topk_unit;  // the unit's first column (call-relative)
+            const int col0 = unit * p.topk_unit;  // the unit's first column (call-relative)
             uint32_t* red = reinterpret_cast<uint32_t*>(tbuf);
             uint32_t* rec = p.records + (size_t)(p.topk_slot0 + unit) * 2 * p.topk_rows * p.topk_k;
             for (int r = 0; r < p.topk_rows; ++r) {
@@ -496,11 +659,11 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const TkdPar
                 uint32_t cand[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const int c = et + j * TKD_PANEL_COLS, col = c0 + c;
+                    const int cc = et + j * TKD_PANEL_COLS, col = col0 + cc;
                     uint32_t key = 0;
-                    if (c < p.topk_unit && col < p.topk_n && col < sg.n_valid)
+                    if (cc < p.topk_unit && col < p.topk_n && col < sg.n_valid)
                         key = topk_key(__ldcg(ysrc + (size_t)r * ldy + col));
-                    cand[j] = key ? (key << 16) | (0xFFFFu - (uint32_t)c) : 0u;
+                    cand[j] = key ? (key << 16) | (0xFFFFu - (uint32_t)cc) : 0u;
                 }
                 uint32_t bound = 0xFFFFFFFFu;
                 for (int q = 0; q < p.topk_k; ++q) {
@@ -510,7 +673,7 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const TkdPar
                         if (cand[j] < bound && cand[j] > best) best = cand[j];
 #pragma unroll
                     for (int o = 16; o; o >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, o));
-                    if (lane == 0) red[warp - 9] = best;
+                    if (lane == 0) red[ow] = best;
                     bar_output_warps();
                     best = max(max(red[0], red[1]), max(red[2], red[3]));
                     bar_output_warps();
@@ -518,11 +681,12 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const TkdPar
                     if (et == 0) {
                         rec[r * p.topk_k + q] = best >> 16;
                         rec[(p.topk_rows + r) * p.topk_k + q] =
-                            best ? p.topk_base + (uint32_t)c0 + (0xFFFFu - (best & 0xFFFFu)) : 0xFFFFFFFFu;
+                            best ? p.topk_base + (uint32_t)col0 + (0xFFFFu - (best & 0xFFFFu)) : 0xFFFFFFFFu;
                     }
                 }
             }
         }
+        if (ow == 0) PROF_TIME(2);
     }
 }
 
@@ -551,3 +715,16 @@ int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st
         default: return launch_fmt<TKD_BF16>(p, grid, smem, st);
     }
 }
+
+#ifdef TKD_PROF
+// debug builds only: read and clear the cycle counters
+extern "C" int tkd_times_read(unsigned long long* host) {
+    return (int)cudaMemcpyFromSymbol(host, tkd_times, sizeof(tkd_times));
+}
+extern "C" int tkd_prof_read(long long* host) {
+    cudaError_t e = cudaMemcpyFromSymbol(host, tkd_prof, sizeof(tkd_prof));
+    long long zero[64] = {0};
+    cudaMemcpyToSymbol(tkd_prof, zero, sizeof(zero));
+    return (int)e;
+}
+#endif

@@ -5,10 +5,12 @@ non-zero code raises.
 """
 
 import ctypes
+import os
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parents[1]
-LIB_PATH = PKG / "csrc" / "libtkd.so"
+# (TKD_LIB names another build of the same library, e.g. one with instrumentation)
+LIB_PATH = Path(os.environ.get("TKD_LIB") or PKG / "csrc" / "libtkd.so")
 
 FMT_BFP8, FMT_BFP4, FMT_BF16 = 0, 1, 2
 EPI_PLAIN, EPI_GLU_IL, EPI_GLU2, EPI_RESIDUAL, EPI_OUT32 = range(5)
@@ -35,7 +37,7 @@ class TkdMatmul(ctypes.Structure):
 
 class TkdPlan(ctypes.Structure):
     _fields_ = [
-        ("ks", c_i32), ("nslices", c_i32), ("panels", c_i32), ("grid", c_i32), ("stages", c_i32), ("xslots", c_i32),
+        ("ks", c_i32), ("nslices", c_i32), ("panels", c_i32), ("grid", c_i32), ("stages", c_i32), ("stream_warps", c_i32),
         ("chunk_k", c_i32), ("smem_bytes", c_i32), ("items", c_i64), ("weight_bytes", c_i64),
     ]
 

@@ -66,12 +66,11 @@ void emul_pack(int fmt, int64_t K, int64_t npad, const uint8_t* exps, const void
 void emul_matmul(int fmt, int64_t K, int64_t npad, const uint8_t* stream, const uint8_t* emax, const uint16_t* x,
                  int M, double* y) {
     const int64_t G = npad / 16, nsa = tkd_nsa(fmt, K);
-    const int ksa = tkd_ksa(fmt), sab = tkd_sab(fmt);
+    const int ksa = tkd_ksa(fmt);
     for (int64_t g = 0; g < G; ++g) {
         std::vector<double> acc(16 * M, 0.0);
-        const uint8_t* run = stream + g * tkd_run_bytes(fmt, K);
         for (int64_t sa = 0; sa < nsa; ++sa) {
-            const uint8_t* b = run + sa * sab;
+            const uint8_t* b = stream + tkd_sa_offset(fmt, K, g, sa);
             for (int lane = 0; lane < 32; ++lane) {
                 const int gl = lane >> 2, t = lane & 3;
                 for (int j = 0; j < ksa / 16; ++j) {  // the mmas of the super-atom

@@ -41,8 +41,8 @@ def test_stream_sizes(tkd):
     assert L.tkd_packed_bytes(tkd.FMT_BFP4, 4096, 14336) * 2 == 66060288
     assert L.tkd_packed_bytes(tkd.FMT_BFP8, 14336, 4096) == 62390272
     assert L.tkd_packed_bytes(tkd.FMT_BFP8, 4096, 151936) == 661225472
-    assert L.tkd_packed_bytes(tkd.FMT_BF16, 1024, 48) == 1024 * 48 * 2
-    assert L.tkd_padded_cols(33) == 48
+    assert L.tkd_packed_bytes(tkd.FMT_BF16, 1024, 48) == 1024 * 128 * 2  # N padded to a panel of 128 columns
+    assert L.tkd_padded_cols(33) == 128
 
 
 def plan(tkd, **kw):

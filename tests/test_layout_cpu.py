@@ -46,7 +46,7 @@ def pack(emul, fmt, exps, codes):
 
 
 @pytest.mark.parametrize("fmt", ["bfp8", "bfp4", "bf16"])
-@pytest.mark.parametrize("k,n", [(64, 32), (96, 48), (256, 64)])
+@pytest.mark.parametrize("k,n", [(64, 128), (96, 128), (288, 256), (544, 128)])
 def test_stream_round_trip_and_decode(emul, fmt, k, n):
     g = torch.Generator().manual_seed(k + n)
     w = (torch.randn(k, n, generator=g) * 0.02 * torch.exp2(torch.randint(-3, 4, (k, 1), generator=g).float())).numpy()
@@ -69,7 +69,7 @@ def test_stream_round_trip_and_decode(emul, fmt, k, n):
 
 def test_every_stream_bit_is_owned_once(emul):
     """Packing all-ones codes and exponents fills the stream's code words completely: the layout is a bijection."""
-    k, n = 128, 32
+    k, n = 320, 128
     for fmt, code in (("bfp8", 0xFF), ("bfp4", 0x0F)):
         exps = np.full((k, n // 16), 100, np.uint8)
         codes = np.full((k, n), code, np.uint8)
@@ -82,7 +82,7 @@ def test_every_stream_bit_is_owned_once(emul):
 
 
 def test_wide_weight_is_flagged(emul):
-    w = np.full((64, 16), 1.0, np.float32)
+    w = np.full((64, 128), 1.0, np.float32)
     w[3] = 1e-20
     exps, codes = orc.quantise_c(w, "bfp8")
     assert pack(emul, "bfp8", exps, codes)[2] == 1
