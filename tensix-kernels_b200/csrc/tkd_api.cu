@@ -223,7 +223,7 @@ int tkd_matmul_workspace(const TkdMatmul* a, uint64_t* bytes) {
     return TKD_OK;
 }
 
-int tkd_matmul(const TkdMatmul* a, void* stream) {
+static int run_matmul(const TkdMatmul* a, void* workspace, uint64_t workspace_bytes, void* stream) {
     Layout L;
     const int rc = make_layout(a, &L, 0);
     if (rc) return rc;
@@ -248,8 +248,8 @@ int tkd_matmul(const TkdMatmul* a, void* stream) {
     if (a->epilogue == TKD_EPI_OUT32 && a->residual && a->residual_dtype != TKD_DT_F32) return TKD_ERR_BAD_ARG;
     if (a->epilogue != TKD_EPI_RESIDUAL && a->epilogue != TKD_EPI_OUT32 && a->residual) return TKD_ERR_BAD_ARG;
     if (a->topk_k && !a->records) return TKD_ERR_BAD_ARG;
-    if (L.ws_bytes > 0 && (!a->workspace || a->workspace_bytes < (uint64_t)L.ws_bytes)) return TKD_ERR_WORKSPACE;
-    if (a->workspace && (reinterpret_cast<uintptr_t>(a->workspace) & 255)) return TKD_ERR_BAD_ARG;
+    if (L.ws_bytes > 0 && (!workspace || workspace_bytes < (uint64_t)L.ws_bytes)) return TKD_ERR_WORKSPACE;
+    if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255)) return TKD_ERR_BAD_ARG;
 
     p.x = static_cast<const uint16_t*>(a->x);
     p.ldx = a->ldx;
@@ -263,13 +263,18 @@ int tkd_matmul(const TkdMatmul* a, void* stream) {
     p.out_dt = a->out_dtype;
     p.ldo = a->ldo;
     p.records = static_cast<uint32_t*>(a->records);
-    uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
     p.counters = reinterpret_cast<int*>(ws + L.off_counters);
     p.unit_counters = reinterpret_cast<int*>(ws + L.off_units);
     p.scratch = reinterpret_cast<float*>(ws + L.off_scratch);
     p.ytmp = reinterpret_cast<uint16_t*>(ws + L.off_ytmp);
     p.status = a->status;
     return launch_err(tkd_launch_stream(p, L.grid, L.smem, static_cast<cudaStream_t>(stream)));
+}
+
+int tkd_matmul(const TkdMatmul* a, void* stream) {
+    if (!a) return TKD_ERR_BAD_ARG;
+    return run_matmul(a, a->workspace, a->workspace_bytes, stream);
 }
 
 }  // extern "C"
