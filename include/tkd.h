@@ -27,6 +27,7 @@ extern "C" {
 #define TKD_ERR_TIMEOUT 3      /* written to the status word by a kernel whose bounded wait gave up */
 #define TKD_ERR_WORKSPACE 4    /* workspace missing or too small */
 #define TKD_ERR_WIDE 5         /* exponents inside one group of 16 columns spread further than the stream encodes */
+#define TKD_ERR_FIXED_SCRATCH 6 /* tkd_matmul_noalloc: the call needs more than TKD_NOALLOC_SCRATCH_BYTES of scratch */
 #define TKD_ERR_CUDA 1000
 
 /* output stages (dense_reader/kernels/dense_compute.cpp:200-356) */
@@ -120,6 +121,22 @@ typedef struct {
 int tkd_matmul_plan(const TkdMatmul* a, TkdPlan* plan);
 int tkd_matmul_workspace(const TkdMatmul* a, uint64_t* bytes);
 int tkd_matmul(const TkdMatmul* a, void* stream);
+
+/* tkd_matmul for callers that cannot allocate device memory (no counterpart in the reference: its device buffers
+ * all come from ttnn's allocator). Some hosts of this library never get to call cudaMalloc: a plugin running inside
+ * another framework's memory pool, a step replayed from a fixed arena, a process whose device memory was handed out
+ * entirely at start-up. For them the kernel's workspace comes from an array of TKD_NOALLOC_SCRATCH_BYTES built into
+ * the library's device image (every GPU that loads the library holds that much until exit); a->workspace and
+ * a->workspace_bytes are ignored, inputs and outputs are still the caller's. The call allocates nothing and frees
+ * nothing. A request whose workspace (tkd_matmul_workspace) exceeds the array is refused with TKD_ERR_FIXED_SCRATCH
+ * before anything is launched; as a guide, M = 1 fits up to about 7000 panel-slices (config 2's gate/up pair, config
+ * 3 and config 4 do; the 151936-column LM head does not).
+ * The first call on a device looks the array's device address up and clears its counters; make that first call
+ * outside any stream capture. All calls on a device share the one array, which keeps what the last call left in it
+ * (the kernel returns its counters to zero itself): two calls that overlap on the GPU, from different streams or
+ * processes' threads, race on it, so keep calls on one device in stream order. */
+#define TKD_NOALLOC_SCRATCH_BYTES (8u << 20)
+int tkd_matmul_noalloc(const TkdMatmul* a, void* stream);
 
 #ifdef __cplusplus
 }

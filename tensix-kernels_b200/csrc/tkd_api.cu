@@ -151,6 +151,7 @@ const char* tkd_error_string(int code) {
         case TKD_ERR_TIMEOUT: return "a kernel's bounded wait gave up";
         case TKD_ERR_WORKSPACE: return "workspace missing or too small";
         case TKD_ERR_WIDE: return "exponent spread inside a column group too wide for the stream";
+        case TKD_ERR_FIXED_SCRATCH: return "the call needs more scratch than tkd_matmul_noalloc's built-in array holds";
         default: return code > TKD_ERR_CUDA ? cudaGetErrorString((cudaError_t)(code - TKD_ERR_CUDA)) : "unknown";
     }
 }
@@ -275,6 +276,39 @@ static int run_matmul(const TkdMatmul* a, void* workspace, uint64_t workspace_by
 int tkd_matmul(const TkdMatmul* a, void* stream) {
     if (!a) return TKD_ERR_BAD_ARG;
     return run_matmul(a, a->workspace, a->workspace_bytes, stream);
+}
+
+// ---- tkd_matmul for callers that must not allocate ----------------------------------------------------------------
+// The same launch as tkd_matmul, with the kernel's workspace (its panel and unit counters, the slice sums of panels
+// spread over several CTAs, the bf16 outputs of a top-k call that writes no y) taken from an array that is part of
+// the library's device image instead of from the caller. Every GPU that loads libtkd holds these
+// TKD_NOALLOC_SCRATCH_BYTES until the process exits.
+//
+// tkd_noalloc_scratch below is the HOST-side handle of that array: passing it to a kernel would hand the GPU a host
+// address. The array's address on a device comes from cudaGetSymbolAddress, asked once per device with that device
+// current, and that address is what the kernel gets.
+static __device__ __align__(256) unsigned char tkd_noalloc_scratch[TKD_NOALLOC_SCRATCH_BYTES];
+
+int tkd_matmul_noalloc(const TkdMatmul* a, void* stream) {
+    static void* dev_ptr[64] = {nullptr};
+    Layout L;
+    const int rc = make_layout(a, &L, 0);
+    if (rc) return rc;
+    if ((uint64_t)L.ws_bytes > (uint64_t)TKD_NOALLOC_SCRATCH_BYTES) return TKD_ERR_FIXED_SCRATCH;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_err(e);
+    if (dev < 0 || dev >= 64) return TKD_ERR_UNSUPPORTED;
+    if (!dev_ptr[dev]) {
+        // first call on this device: resolve the array's device address and start its counters from zero
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, tkd_noalloc_scratch);
+        if (e != cudaSuccess) return cuda_err(e);
+        e = cudaMemsetAsync(ptr, 0, (size_t)(kMaxPanels + kMaxUnits) * 4, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return cuda_err(e);
+        dev_ptr[dev] = ptr;
+    }
+    return run_matmul(a, dev_ptr[dev], TKD_NOALLOC_SCRATCH_BYTES, stream);
 }
 
 }  // extern "C"

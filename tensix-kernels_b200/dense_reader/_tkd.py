@@ -15,7 +15,7 @@ LIB_PATH = Path(os.environ.get("TKD_LIB") or PKG / "csrc" / "libtkd.so")
 FMT_BFP8, FMT_BFP4, FMT_BF16 = 0, 1, 2
 EPI_PLAIN, EPI_GLU_IL, EPI_GLU2, EPI_RESIDUAL, EPI_OUT32 = range(5)
 DT_NONE, DT_BF16, DT_F32 = 0, 1, 2
-ERR_TIMEOUT, ERR_WIDE = 3, 5
+ERR_TIMEOUT, ERR_WIDE, ERR_FIXED_SCRATCH = 3, 5, 6
 
 c_i32, c_i64, c_u32, c_u64, c_vp = ctypes.c_int32, ctypes.c_int64, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
 
@@ -53,6 +53,7 @@ SYMBOLS = {
     "tkd_matmul_plan": (c_i32, [ctypes.POINTER(TkdMatmul), ctypes.POINTER(TkdPlan)]),
     "tkd_matmul_workspace": (c_i32, [ctypes.POINTER(TkdMatmul), ctypes.POINTER(c_u64)]),
     "tkd_matmul": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp]),
+    "tkd_matmul_noalloc": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp]),
 }
 
 _lib = None

@@ -1,0 +1,61 @@
+"""tkd_matmul_noalloc, the entry point for hosts that cannot allocate device memory (a plugin inside another
+framework's pool, a fixed-arena replay): called through the C-ABI, its output must equal tkd_matmul's bit for bit,
+call after call, because it is the same kernel with its workspace in the library's built-in array.
+
+Collected last on purpose (the file name): a run that stops at the first failure has then run every other test."""
+
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from common import ttnn_like as ttnn  # noqa: E402
+from dense_reader import _tkd, linear  # noqa: E402
+
+
+def describe(tw, x, out, m, k, n):
+    a = _tkd.TkdMatmul()
+    a.fmt, a.m, a.k = tw.fmt, m, k
+    a.x, a.ldx = x.data_ptr(), k
+    a.nblocks, a.epilogue = 1, _tkd.EPI_PLAIN
+    a.block[0].w, a.block[0].emax, a.block[0].n = tw.t.data_ptr(), tw.emax.data_ptr(), n
+    a.out, a.out_dtype, a.ldo = out.data_ptr(), _tkd.DT_BF16, n
+    return a
+
+
+@pytest.mark.parametrize("dtype,m", [(ttnn.bfloat8_b, 1), (ttnn.bfloat4_b, 3)])
+def test_noalloc_equals_matmul_twice(device, dtype, m):
+    L = _tkd.lib()
+    k, n = 4096, 4096 + 128  # 33 panels of 16 slices: most panels' slices are spread over several CTAs (scratch in use)
+    g = torch.Generator().manual_seed(71)
+    tw, _ = linear.native_weight(device, torch.randn(n, k, generator=g) * 0.02, dtype)
+    stream = torch.cuda.current_stream().cuda_stream
+    for call in range(2):
+        x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(device.torch)
+        want = torch.full((m, n), 7.0, dtype=torch.bfloat16, device=device.torch)
+        got = torch.full((m, n), -7.0, dtype=torch.bfloat16, device=device.torch)
+        a = describe(tw, x, want, m, k, n)
+        need = ctypes.c_uint64(0)
+        _tkd.check(L.tkd_matmul_workspace(ctypes.byref(a), ctypes.byref(need)), "workspace")
+        assert need.value <= 8 << 20
+        ws = torch.zeros(need.value, dtype=torch.uint8, device=device.torch)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        _tkd.check(L.tkd_matmul(ctypes.byref(a), stream), "tkd_matmul")
+        b = describe(tw, x, got, m, k, n)  # no workspace given
+        _tkd.check(L.tkd_matmul_noalloc(ctypes.byref(b), stream), "tkd_matmul_noalloc")
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"call {call}"
+        ref = x.float() @ ttnn.to_torch(tw)[0, 0, :, :n].to(device.torch)
+        assert ((got.float() - ref).norm() / ref.norm()).item() < 0.01
+
+
+def test_noalloc_refuses_what_does_not_fit(device):
+    """The LM head's 1187 panels of 16 slices need more scratch than the built-in array: refused, nothing launched."""
+    L = _tkd.lib()
+    a = _tkd.TkdMatmul()
+    a.fmt, a.m, a.k, a.nblocks, a.epilogue, a.out_dtype = _tkd.FMT_BFP8, 1, 4096, 1, _tkd.EPI_PLAIN, _tkd.DT_BF16
+    a.block[0].n = 151936
+    assert L.tkd_matmul_noalloc(ctypes.byref(a), None) == _tkd.ERR_FIXED_SCRATCH
+    assert b"built-in" in L.tkd_error_string(_tkd.ERR_FIXED_SCRATCH)
