@@ -20,7 +20,7 @@ int tkd_launch_unpack(int fmt, int64_t K, int64_t npad, const void* stream, cons
 #define TKD_THREADS ((1 + TKD_STREAM_WARPS + 4) * 32)  // + 1 producer warp + 4 output warps
 #define TKD_PANEL_COLS 128     // columns one work item covers
 #define TKD_MAX_STAGES 16
-#define TKD_SMEM_HEAD 512      // barriers and flags
+#define TKD_SMEM_HEAD 1024     // barriers, the stage headers, flags
 
 struct TkdSegDev {
     const uint8_t* w;     // packed stream (the gate's with a separate up weight)

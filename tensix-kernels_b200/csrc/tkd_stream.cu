@@ -38,11 +38,14 @@
 
 #ifdef TKD_PROF
 __device__ long long tkd_prof[64];
-__device__ unsigned long long tkd_times[148 * 4];  // per CTA: entry, streaming warps done, output warps done (ns)
+__device__ unsigned long long tkd_times[148 * 4];
+__device__ long long tkd_trace[4 * 256];
+__device__ long long tkd_trace2[8 * 256];  // CTA 3 warp 1, per item: more points  // CTA 3: per stage (first 256): streaming warp 1 wait-start, wait-end, done; producer issue time
+__device__ int tkd_trace_n[2];  // per CTA: entry, streaming warps done, output warps done (ns)
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 #define PROF_TIME(slot) do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 148) tkd_times[blockIdx.x * 4 + slot] = gtime(); } while (0)
 #define PROF_T0 long long _t0 = clock64()
-#define PROF_ADD(slot) do { long long _t1 = clock64(); if (blockIdx.x == 3 && (threadIdx.x & 31) == 0) tkd_prof[slot] += _t1 - _t0; _t0 = _t1; } while (0)
+#define PROF_ADD(slot) do { (void)_t0; } while (0)  // (a global read-modify-write here stalls the warp it measures)
 #else
 #define PROF_T0
 #define PROF_ADD(slot)
@@ -203,68 +206,70 @@ __device__ __forceinline__ void block_mma(float (&acc)[NA][MT][4], const uint32_
 }
 
 __device__ __forceinline__ uint4 ldg_x(const uint16_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
 
-// One streaming warp's share of one chunk: super-atoms h, h + 2, ... of the group at `sub`. kc: the chunk's first k;
-// xp[m]: this lane's row of x at k = 8 t. FULL: the chunk has all its super-atoms and ends within K.
-template <int FMT, int MT, int NA, bool FULL>
-__device__ __forceinline__ void chunk_mma(float (&acc)[NA][MT][4], const uint8_t* sub, int h, int nsa, int kc, int K,
-                                          const uint16_t* const (&xp)[MT], int lane, uint32_t full_bar, uint32_t parity,
-                                          int* status, bool& ok) {
+// What a stage of the ring holds for the streaming warps besides the weights: a 16-byte header the producer writes.
+// .x: flags; .y: the scratch slot (panel * slices + slice) of the stage's item; .z: first k of the next stage.
+enum : uint32_t {
+    ST_FIRST = 1,     // first chunk of its item: the slice sums start from zero
+    ST_LAST = 2,      // last chunk of its item: the flags below apply
+    ST_START = 4,     // the running sum starts over with this slice
+    ST_STORE = 8,     // the running sum goes to the scratch slot
+    ST_DELIVER = 16,  // the output warps are signalled
+    ST_SPLIT = 32,    // ... without the sums (they are in the scratch buffer)
+    ST_END = 64,      // last stage of this CTA's run
+};
+
+// One streaming warp's share of one chunk: super-atoms h, h + 2, ... of one group. code_a / exp_a: shared-memory
+// addresses of this lane's code and exponent words of super-atom h; xb[m]: this lane's row of x at k = 8 t + h * KSA;
+// kc: the chunk's first k. FULL: the chunk has all its super-atoms and ends within K (then xpre holds the activations,
+// loaded before the stage was waited for, when PRE).
+template <int FMT, int MT, int NA, bool FULL, bool PRE>
+__device__ __forceinline__ void chunk_mma(float (&acc)[NA][MT][4], uint32_t code_a, uint32_t exp_a,
+                                          const uint4 (&xpre)[Fmt<FMT>::SUBSA / 2 * Fmt<FMT>::XB][MT],
+                                          const uint16_t* const (&xb)[MT], int kc, int K, int h, int nsa) {
     using F = Fmt<FMT>;
     constexpr int NPW = F::SUBSA / 2;  // super-atoms a warp takes of a chunk
-    constexpr bool PREFETCH = MT <= 2;
-    constexpr int NXP = PREFETCH ? NPW * F::XB : 1;
-    const int t = lane & 3;
-    uint4 xpre[NXP][MT];
-    auto load_x = [&](int i, int q, uint4(&xv)[MT]) {
-        const int k = kc + (h + 2 * i) * F::KSA + 32 * q;
-#pragma unroll
-        for (int m = 0; m < MT; ++m)
-            xv[m] = FULL || k < K ? ldg_x(xp[m] + k) : make_uint4(0, 0, 0, 0);
-    };
-    PROF_T0;
-    if constexpr (PREFETCH) {
-#pragma unroll
-        for (int i = 0; i < NPW; ++i)
-#pragma unroll
-            for (int q = 0; q < F::XB; ++q) load_x(i, q, xpre[i * F::XB + q]);
-    }
-#ifdef TKD_PROF
-    if (threadIdx.x < 64) { asm volatile("" :: "r"(xpre[0][0].x)); PROF_ADD(20); }
-#endif
-    ok = mbar_wait(full_bar, parity, status);
-    if (!ok) return;
-#ifdef TKD_PROF
-    if (threadIdx.x < 64) PROF_ADD(21);
-#endif
 #pragma unroll
     for (int i = 0; i < NPW; ++i) {
-        const int sa = h + 2 * i;
-        if (!FULL && sa >= nsa) break;
-        const uint8_t* b = sub + sa * F::SAB;
+        if (!FULL && h + 2 * i >= nsa) break;
         uint32_t cw[F::XB][4], ew[F::XB][2];
         if constexpr (FMT == TKD_BFP4) {
-            const uint4 ev = *reinterpret_cast<const uint4*>(b + t * 16);
-            const uint4 cv = *reinterpret_cast<const uint4*>(b + 64 + lane * 16);
+            const uint4 ev = lds128(exp_a + 2 * i * F::SAB), cv = lds128(code_a + 2 * i * F::SAB);
             cw[0][0] = cv.x, cw[0][1] = cv.y, cw[1][0] = cv.z, cw[1][1] = cv.w;
             cw[0][2] = cw[0][3] = cw[1][2] = cw[1][3] = 0;
             ew[0][0] = ev.x, ew[0][1] = ev.y, ew[1][0] = ev.z, ew[1][1] = ev.w;
         } else if constexpr (FMT == TKD_BFP8) {
-            const uint2 ev = *reinterpret_cast<const uint2*>(b + t * 8);
-            const uint4 cv = *reinterpret_cast<const uint4*>(b + 32 + lane * 16);
+            const uint2 ev = lds64(exp_a + 2 * i * F::SAB);
+            const uint4 cv = lds128(code_a + 2 * i * F::SAB);
             cw[0][0] = cv.x, cw[0][1] = cv.y, cw[0][2] = cv.z, cw[0][3] = cv.w;
             ew[0][0] = ev.x, ew[0][1] = ev.y;
         }
 #pragma unroll
         for (int q = 0; q < F::XB; ++q) {
-            if (!FULL && kc + sa * F::KSA + 32 * q >= K) break;  // a K that ends inside a super-atom
-            uint4 xnow[MT];
-            if constexpr (!PREFETCH) load_x(i, q, xnow);
-            const uint4(&xv)[MT] = PREFETCH ? xpre[PREFETCH ? i * F::XB + q : 0] : xnow;
+            const int k = kc + 2 * i * F::KSA + 32 * q;  // (+ h * KSA, which xb carries)
+            if (!FULL && k + h * F::KSA >= K) break;     // a K that ends inside a super-atom
+            uint4 xv[MT];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                if constexpr (FULL && PRE)
+                    xv[m] = xpre[i * F::XB + q][m];
+                else
+                    xv[m] = ldg_x(xb[m] + k);
+            }
             if constexpr (FMT == TKD_BF16) {
 #pragma unroll
                 for (int jj = 0; jj < 2; ++jj) {
-                    const uint4 a = *reinterpret_cast<const uint4*>(b + jj * 512 + lane * 16);
+                    const uint4 a = lds128(code_a + 2 * i * F::SAB + jj * 512);
 #pragma unroll
                     for (int m = 0; m < MT; ++m)
                         mma_bf16(acc[jj % NA][m], a.x, a.y, a.z, a.w, jj ? xv[m].z : xv[m].x, jj ? xv[m].w : xv[m].y);
@@ -292,6 +297,7 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TKD_MAX_STAGES);
     const uint32_t pfull0 = smem_u32(bars + 2 * TKD_MAX_STAGES), pempty0 = pfull0 + 16;
     volatile int* sflag = reinterpret_cast<volatile int*>(smem + TKD_SMEM_HEAD - 16);
+    uint4* hdr = reinterpret_cast<uint4*>(smem + 512);  // one header per stage of the ring
     float* pbuf = reinterpret_cast<float*>(smem + p.off_pbuf);  // [2 buffers][2 halves][128 columns][MP]
     float* tbuf = reinterpret_cast<float*>(smem + p.off_tbuf);  // [128 columns][MP]
     uint8_t* ring = smem + p.off_ring;
@@ -330,15 +336,22 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
         if (lane != 0) return;
-        Cursor c;
+        Cursor c, cn;  // this item, and the one after it
         uint32_t st = 0;
         bool ok = true;
-        for (int64_t j = 0; j < i1 - i0 && ok; ++j) {
-            const int64_t it = j < lead ? tail0 + j : i0 + (j - lead);
-            if (j == 0 || j == lead)
-                cursor_init(c, p, it);
-            else
-                cursor_next(c, p);
+        const int64_t nitems = i1 - i0;
+        auto item_at = [&](int64_t j) { return j < lead ? tail0 + j : i0 + (j - lead); };
+        cursor_init(cn, p, item_at(0));
+        for (int64_t j = 0; j < nitems && ok; ++j) {
+            const int64_t it = item_at(j);
+            c = cn;
+            if (j + 1 < nitems) {
+                if (j + 1 == lead)
+                    cursor_init(cn, p, item_at(j + 1));
+                else
+                    cursor_next(cn, p);
+            }
+            const Flow f = flow_of(c, p, it, i0, i1);
             const TkdSegDev& sg = p.seg[c.seg];
             const int k0 = c.slice * p.ks, kv = min(p.ks, K - k0);
             const int c0 = k0 / CK, nch = (kv + CK - 1) / CK;
@@ -347,14 +360,20 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
             const uint8_t* src2 = glu2 ? sg.w2 + (int64_t)(c.pl >> 1) * p.panel_bytes : nullptr;
             for (int ch = 0; ch < nch; ++ch, ++st) {
                 const uint32_t s = st % nst;
-                PROF_T0;
                 ok = mbar_wait(empty0 + 8 * s, ((st / nst) & 1) ^ 1, p.status);
                 if (!ok) break;
-                PROF_ADD(1);
                 const int nsa = min(F::SUBSA, nsa_total - (c0 + ch) * F::SUBSA);
                 const uint32_t gbytes = (uint32_t)nsa * F::SAB;  // one group's share of the chunk
                 const int64_t coff = (int64_t)(c0 + ch) * (F::SUBSA * F::SAB * 8);
                 const uint32_t dst = smem_u32(ring + (size_t)s * p.stage_bytes);
+                // the stage's header, ordered before the streaming warps' reads by the arrival below
+                const bool last = ch == nch - 1;
+                uint32_t fl = (ch == 0 ? ST_FIRST : 0u) | (last && j == nitems - 1 ? ST_END : 0u);
+                if (last)
+                    fl |= ST_LAST | (f.start ? ST_START : 0u) | (f.store ? ST_STORE : 0u) |
+                          (f.deliver ? ST_DELIVER : 0u) | (f.split ? ST_SPLIT : 0u);
+                const int knext = last ? cn.slice * p.ks : (c0 + ch + 1) * CK;
+                hdr[s] = make_uint4(fl, (uint32_t)(c.panel * p.nslices + c.slice), (uint32_t)knext, 0u);
                 mbar_expect_tx(full0 + 8 * s, 8 * gbytes);
                 if (glu2) {
                     const int64_t hoff = coff + (int64_t)(c.pl & 1) * 4 * gbytes;
@@ -363,7 +382,6 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
                 } else {
                     bulk_g2s(dst, src + coff, 8 * gbytes, full0 + 8 * s);
                 }
-                PROF_ADD(2);
             }
         }
         // (every stage issued above is waited for by the streaming warps before they leave; after a timeout the copies
@@ -377,61 +395,69 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
         }
     } else if (warp <= TKD_STREAM_WARPS) {
         // ---------------------------------------------------------------- streaming warps
+        // One flat loop over the stages of the ring; everything about items comes with the stage's header.
         const int cw = warp - 1;
         const int g8 = cw & 7, h = cw >> 3;
         const int g = lane >> 2, t = lane & 3;
-        const uint16_t* xp[MT];
+        constexpr int NX = F::SUBSA / 2 * F::XB;
+        constexpr bool PRE = MT <= 2;
+        constexpr int EXPB = FMT == TKD_BFP4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
+        const uint16_t* xb[MT];
 #pragma unroll
         // (a lane whose row lies beyond M reads row M - 1 instead: a B column only feeds its own output column, and
         // the columns beyond M are never read, so those lanes need no predicate and no zero fill)
-        for (int m = 0; m < MT; ++m) xp[m] = p.x + (int64_t)min(8 * m + g, M - 1) * p.ldx + 8 * t;
-        Cursor c;
-        uint32_t slot = 0, phase = 0, pi = 0;  // ring position and its parity
-        bool ok = true;
-        float tot[MT][4];
-        for (int64_t j = 0; j < i1 - i0 && ok; ++j) {
-            const int64_t it = j < lead ? tail0 + j : i0 + (j - lead);
-            if (j == 0 || j == lead)
-                cursor_init(c, p, it);
-            else
-                cursor_next(c, p);
-            const Flow f = flow_of(c, p, it, i0, i1);
-            const int k0 = c.slice * p.ks, kv = min(p.ks, K - k0);
-            const int c0 = k0 / CK, nch = (kv + CK - 1) / CK;
-            float acc[NA][MT][4];
+        for (int m = 0; m < MT; ++m) xb[m] = p.x + (int64_t)min(8 * m + g, M - 1) * p.ldx + 8 * t + h * F::KSA;
+        const uint32_t ring_a = smem_u32(ring), hdr_a = smem_u32(hdr);
+        const uint32_t code_off = g8 * (F::SUBSA * F::SAB) + h * F::SAB + EXPB + lane * 16;
+        const uint32_t exp_off = g8 * (F::SUBSA * F::SAB) + h * F::SAB + t * (EXPB / 4);
+        uint32_t slot = 0, phase = 0, pi = 0;  // ring position and its parity; deliveries so far
+        int kc = (int)((lead > 0 ? tail0 : i0) % p.nslices) * p.ks;
+        float acc[NA][MT][4], tot[MT][4];
+        while (true) {
+            const bool full = kc + CK <= K;
+            uint4 xpre[NX][MT];
+            if (PRE && full) {
 #pragma unroll
-            for (int j = 0; j < NA; ++j)
+                for (int i = 0; i < F::SUBSA / 2; ++i)
 #pragma unroll
-                for (int m = 0; m < MT; ++m) acc[j][m][0] = acc[j][m][1] = acc[j][m][2] = acc[j][m][3] = 0.f;
-            PROF_T0;
-            for (int ch = 0; ch < nch; ++ch) {
-                const int kc = (c0 + ch) * CK;
-                const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
-                if (kc + CK <= K) {
-                    chunk_mma<FMT, MT, NA, true>(acc, stage + g8 * (F::SUBSA * F::SAB), h, F::SUBSA, kc, K, xp, lane,
-                                                 full0 + 8 * slot, phase, p.status, ok);
-                } else {
-                    const int nsa = nsa_total - (c0 + ch) * F::SUBSA;
-                    chunk_mma<FMT, MT, NA, false>(acc, stage + g8 * nsa * F::SAB, h, nsa, kc, K, xp, lane,
-                                                  full0 + 8 * slot, phase, p.status, ok);
-                }
-                if (!ok) break;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty0 + 8 * slot);
-                if (++slot == (uint32_t)nst) slot = 0, phase ^= 1;
-                if (warp == 1) PROF_ADD(9);
+                    for (int q = 0; q < F::XB; ++q)
+#pragma unroll
+                        for (int m = 0; m < MT; ++m) xpre[i * F::XB + q][m] = ldg_x(xb[m] + kc + 2 * i * F::KSA + 32 * q);
             }
-            if (!ok) break;
+            if (!mbar_wait(full0 + 8 * slot, phase, p.status)) break;
+            const uint4 hd = lds128(hdr_a + 16 * slot);
+            const uint32_t fl = hd.x;
+            if (fl & ST_FIRST) {
+#pragma unroll
+                for (int j = 0; j < NA; ++j)
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) acc[j][m][0] = acc[j][m][1] = acc[j][m][2] = acc[j][m][3] = 0.f;
+            }
+            const uint32_t sbase = ring_a + slot * p.stage_bytes;
+            if (full) {
+                chunk_mma<FMT, MT, NA, true, PRE>(acc, sbase + code_off, sbase + exp_off, xpre, xb, kc, K, h, F::SUBSA);
+            } else {
+                // the last chunk of K: fewer super-atoms, the groups closer together
+                const int nsa = nsa_total - kc / CK * F::SUBSA;
+                const uint32_t gb = sbase + g8 * nsa * F::SAB + h * F::SAB;
+                chunk_mma<FMT, MT, NA, false, PRE>(acc, gb + EXPB + lane * 16, gb + t * (EXPB / 4), xpre, xb, kc, K, h, nsa);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * slot);
+            if (++slot == (uint32_t)nst) slot = 0, phase ^= 1;
+            kc = (int)hd.z;
+            if (!(fl & ST_LAST)) continue;
+            // ---- the item's slice is done
 #pragma unroll
             for (int m = 0; m < MT; ++m)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float part = NA == 2 ? acc[0][m][e] + acc[NA - 1][m][e] : acc[0][m][e];
-                    tot[m][e] = f.start ? part : tot[m][e] + part;
+                    tot[m][e] = fl & ST_START ? part : tot[m][e] + part;
                 }
-            if (f.store) {
+            if (fl & ST_STORE) {
                 // straight into the scratch slot of (panel, slice): [half][row][128 columns]
-                float* sc = p.scratch + (((size_t)c.panel * p.nslices + c.slice) * 2 + h) * M * TKD_PANEL_COLS + g8 * 16 + g;
+                float* sc = p.scratch + ((size_t)hd.y * 2 + h) * M * TKD_PANEL_COLS + g8 * 16 + g;
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
                     const int r0 = 8 * m + 2 * t;
@@ -445,23 +471,22 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
                     }
                 }
             }
-            if (!f.deliver) continue;
-            const uint32_t pb = pi & 1;
-            ok = mbar_wait(pempty0 + 8 * pb, ((pi >> 1) & 1) ^ 1, p.status);
-            if (!ok) break;
-            if (warp == 1) PROF_ADD(10);
-            if (!f.split) {
-                float* pc = pbuf + ((size_t)(pb * 2 + h) * TKD_PANEL_COLS + g8 * 16 + g) * MP + 2 * t;
+            if (fl & ST_DELIVER) {
+                const uint32_t pb = pi & 1;
+                if (!mbar_wait(pempty0 + 8 * pb, ((pi >> 1) & 1) ^ 1, p.status)) break;
+                if (!(fl & ST_SPLIT)) {
+                    float* pc = pbuf + ((size_t)(pb * 2 + h) * TKD_PANEL_COLS + g8 * 16 + g) * MP + 2 * t;
 #pragma unroll
-                for (int m = 0; m < MT; ++m) {
-                    *reinterpret_cast<float2*>(pc + 8 * m) = make_float2(tot[m][0], tot[m][1]);
-                    *reinterpret_cast<float2*>(pc + 8 * MP + 8 * m) = make_float2(tot[m][2], tot[m][3]);
+                    for (int m = 0; m < MT; ++m) {
+                        *reinterpret_cast<float2*>(pc + 8 * m) = make_float2(tot[m][0], tot[m][1]);
+                        *reinterpret_cast<float2*>(pc + 8 * MP + 8 * m) = make_float2(tot[m][2], tot[m][3]);
+                    }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(pfull0 + 8 * pb);
+                ++pi;
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(pfull0 + 8 * pb);
-            ++pi;
-            if (warp == 1) PROF_ADD(11);
+            if (fl & ST_END) break;
         }
         if (warp == 1) PROF_TIME(1);
     } else {
@@ -531,32 +556,36 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
                     };
                     if (M == 1) {
                         float t0 = term(pe - 1, 0, 0), t1 = term(pe - 1, 1, 0);
-                        for (int s = pe; s < p.nslices; s += 16) {
-                            float v0[16], v1[16];
+                        for (int s = pe; s < p.nslices; s += 8) {
+                            float v0[8], v1[8];
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
+                            for (int j = 0; j < 8; ++j)
                                 if (s + j < p.nslices) v0[j] = term(s + j, 0, 0), v1[j] = term(s + j, 1, 0);
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
+                            for (int j = 0; j < 8; ++j)
                                 if (s + j < p.nslices) t0 += v0[j], t1 += v1[j];
                         }
                         tot[0] = t0 + t1;
                     } else {
-                        float th[2][MR];
-#pragma unroll
-                        for (int m = 0; m < MR; ++m)
-                            if (m < M) th[0][m] = term(pe - 1, 0, m), th[1][m] = term(pe - 1, 1, m);
-                        for (int s = pe; s < p.nslices; ++s) {
-                            float v[2][MR];
+#pragma unroll 1
+                        for (int hh = 0; hh < 2; ++hh) {
+                            float th[MR];
 #pragma unroll
                             for (int m = 0; m < MR; ++m)
-                                if (m < M) v[0][m] = term(s, 0, m), v[1][m] = term(s, 1, m);
+                                if (m < M) th[m] = term(pe - 1, hh, m);
+#pragma unroll 1
+                            for (int s = pe; s < p.nslices; ++s) {
+                                float v[MR];
 #pragma unroll
-                            for (int m = 0; m < MR; ++m)
-                                if (m < M) th[0][m] += v[0][m], th[1][m] += v[1][m];
+                                for (int m = 0; m < MR; ++m)
+                                    if (m < M) v[m] = term(s, hh, m);
+#pragma unroll
+                                for (int m = 0; m < MR; ++m)
+                                    if (m < M) th[m] += v[m];
+                            }
+#pragma unroll
+                            for (int m = 0; m < MR; ++m) tot[m] = hh == 0 ? th[m] : tot[m] + th[m];
                         }
-#pragma unroll
-                        for (int m = 0; m < MR; ++m) tot[m] = th[0][m] + th[1][m];
                     }
                 }
                 bar_output_warps();  // sflag may be written again only after everyone has read it
@@ -569,9 +598,12 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
             const int n = glu2 ? c.pl * 64 + (et & 63) : c.pl * TKD_PANEL_COLS + et;
             if constexpr (FMT != TKD_BF16) {
                 const uint8_t* em = glu2 && et >= 64 ? sg.emax2 : sg.emax;
+                // 2^e in two factors, each a normal float (e is within -69 .. 189)
                 const int e = (int)em[n >> 4] + 64 - (FMT == TKD_BFP8 ? 133 : 129);
+                const int e1 = e / 2, e2 = e - e1;
+                const float f1 = __uint_as_float((uint32_t)(e1 + 127) << 23), f2 = __uint_as_float((uint32_t)(e2 + 127) << 23);
 #pragma unroll
-                for (int m = 0; m < MR; ++m) tot[m] = scalbnf(tot[m], e);
+                for (int m = 0; m < MR; ++m) tot[m] = tot[m] * f1 * f2;
             }
             const bool in_w = n < sg.n_valid;
             if (p.scale_dt != TKD_DT_NONE && in_w) {
@@ -718,6 +750,13 @@ int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st
 
 #ifdef TKD_PROF
 // debug builds only: read and clear the cycle counters
+extern "C" int tkd_trace2_read(long long* host) { return (int)cudaMemcpyFromSymbol(host, tkd_trace2, sizeof(tkd_trace2)); }
+extern "C" int tkd_trace_read(long long* host) {
+    cudaError_t e = cudaMemcpyFromSymbol(host, tkd_trace, sizeof(tkd_trace));
+    int z[2] = {0, 0};
+    cudaMemcpyToSymbol(tkd_trace_n, z, sizeof(z));
+    return (int)e;
+}
 extern "C" int tkd_times_read(unsigned long long* host) {
     return (int)cudaMemcpyFromSymbol(host, tkd_times, sizeof(tkd_times));
 }
