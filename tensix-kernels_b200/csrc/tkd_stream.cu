@@ -52,6 +52,13 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #define PROF_TIME(slot)
 #endif
 
+#include <stdlib.h>
+// TKD_NO_PDL=1 in the environment turns programmatic dependent launch off (for comparisons).
+static bool tkd_pdl_enabled() {
+    static const bool on = [] { const char* v = getenv("TKD_NO_PDL"); return !(v && v[0] == '1'); }();
+    return on;
+}
+
 namespace {
 
 constexpr uint32_t kWaitRounds = 1u << 12;   // try_wait rounds before a wait gives up ...
@@ -303,6 +310,8 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
     uint8_t* ring = smem + p.off_ring;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // let the kernel after this one in the stream start its CTAs as SMs become free
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == 0) PROF_TIME(0);
     if (tid == 0) {
         for (int s = 0; s < p.nstages; ++s) {
@@ -396,6 +405,8 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
     } else if (warp <= TKD_STREAM_WARPS) {
         // ---------------------------------------------------------------- streaming warps
         // One flat loop over the stages of the ring; everything about items comes with the stage's header.
+        // (x, the scratch buffer and the outputs may belong to the kernel before this one: wait for it to complete)
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int cw = warp - 1;
         const int g8 = cw & 7, h = cw >> 3;
         const int g = lane >> 2, t = lane & 3;
@@ -491,6 +502,7 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
         if (warp == 1) PROF_TIME(1);
     } else {
         // ---------------------------------------------------------------- output warps
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int et = tid - (1 + TKD_STREAM_WARPS) * 32;  // the panel column this thread owns
         const int ow = warp - (1 + TKD_STREAM_WARPS);
         Cursor c;
@@ -725,10 +737,31 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
 template <int FMT, int MT>
 int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
     auto kern = tkd_stream_kernel<FMT, MT>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // (once per device and instantiation: allow the largest dynamic shared memory a CTA can have)
+    static bool allowed[64] = {false};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
-    kern<<<grid, TKD_THREADS, smem, st>>>(p);
-    return (int)cudaGetLastError();
+    if (dev < 0 || dev >= 64 || !allowed[dev]) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        if (dev >= 0 && dev < 64) allowed[dev] = true;
+    }
+    // Programmatic dependent launch: a CTA of this launch may start on an SM as soon as the kernel before it in the
+    // stream has left that SM (every CTA of the stream kernel lets its dependents go at once, see the kernel). Its
+    // producer then fills the ring with weights, which no earlier kernel writes, while the rest of the earlier kernel
+    // drains; everything else waits for the earlier kernel's completion (griddepcontrol.wait).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(TKD_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tkd_pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 template <int FMT>
