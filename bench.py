@@ -129,17 +129,18 @@ def build_gpu_case(name, m, device, copies, seed0):
         su = (torch.rand(n, generator=g) + 0.5).to(device.torch)
         y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
 
+        cs = (sg, su)
+
         def step(i, x_t=tx, y_t=y):
             wg, wu = sets[i % copies]
-            return linear.matmul(x_t, wg, None, w_up=wu, glu=True, col_scales=(sg, su), out=y_t)
+            return linear.matmul(x_t, wg, None, w_up=wu, glu=True, col_scales=cs, out=y_t)
         weights = 2
     elif name == "c3":
         res = ttnn.from_torch(torch.randn(1, 1, m, n, generator=g), dtype=ttnn.float32, layout=ttnn.TILE_LAYOUT, device=device)
         y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.float32, ttnn.TILE_LAYOUT, device)
 
         def step(i, x_t=tx, y_t=y):
-            # (a fresh output, not in place: the residual stays what it was for the next step)
-            return linear.matmul(x_t, sets[i % copies][0], None, residual=res, out32=True)
+            return linear.matmul(x_t, sets[i % copies][0], None, residual=res, out32=True, out=y_t)
         weights = 1
         extra["res"] = res
     elif name == "c5":
@@ -218,6 +219,7 @@ def main():
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--ks", type=int, default=0, help="k per slice of the kernel's work items (0: the library's default)")
     ap.add_argument("--profile", action="store_true",
                     help="for a profiler: warm-up, then `steps` plain launches (no graph, no e2e, no CPU leg, no JSON line)")
     args = ap.parse_args()
@@ -248,6 +250,8 @@ def main():
     from common import ttnn_like as ttnn
     from dense_reader import linear
 
+    if args.ks:
+        linear.KS = args.ks
     torch.cuda.set_device(local)
     if world > 1:
         import torch.distributed as dist

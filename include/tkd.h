@@ -129,8 +129,8 @@ int tkd_matmul(const TkdMatmul* a, void* stream);
  * the library's device image (every GPU that loads the library holds that much until exit); a->workspace and
  * a->workspace_bytes are ignored, inputs and outputs are still the caller's. The call allocates nothing and frees
  * nothing. A request whose workspace (tkd_matmul_workspace) exceeds the array is refused with TKD_ERR_FIXED_SCRATCH
- * before anything is launched; as a guide, M = 1 fits up to about 7000 panel-slices (config 2's gate/up pair, config
- * 3 and config 4 do; the 151936-column LM head does not).
+ * before anything is launched; as a guide, the array holds about 7900 / M panel-slices of sums (a panel is 128
+ * columns, a slice 1024 k by default): one row against the 151936-column LM head fits, eight rows do not.
  * The first call on a device looks the array's device address up and clears its counters; make that first call
  * outside any stream capture. All calls on a device share the one array, which keeps what the last call left in it
  * (the kernel returns its counters to zero itself): two calls that overlap on the GPU, from different streams or

@@ -77,6 +77,8 @@ _TENSIX_OPTS = {"cores_per_bank", "split", "rows", "xs", "kb", "kw", "sbw", "nos
 _OPTS = _TENSIX_OPTS | {"glu", "glu_act", "residual", "residual_mode", "out32", "blocks", "max_banks", "col_scales", "ks",
                         "max_ctas"}
 
+_CALLS = {}      # whole calls by the identity of their arguments (a hit goes straight to the library)
+_CALLS_MAX = 256
 _LAUNCHES = {}   # the launch cache: key -> (TkdMatmul, keep-alive)
 _CHOICE = {}     # the plan cache
 _WORKSPACE = {}  # device id -> zeroed uint8 tensor
@@ -361,10 +363,21 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     A block list in place of w, [(w | (gate, up), col0_tiles), ...]: one launch over two to four weights of one K and
     dtype, each written at its col0_tiles (in 32-column tiles); bit for bit one call per block. More than 32 rows run
     as slices of 32, each reading the weights once."""
+    call_key = None
+    if CACHE:
+        # The same call again (the same tensor objects and options): everything was checked and described the first
+        # time; only the addresses are looked at again. The entry keeps its arguments alive, so their ids stay theirs.
+        call_key = (id(x), id(w), id(scale), id(out), id(w_up), id(topk), col0, max_banks, KS, MAX_CTAS, TOPK_UNIT,
+                    tuple((k, tuple(map(id, v)) if type(v) is tuple else id(v)) for k, v in opts.items()))
+        hit = _CALLS.get(call_key)
+        if hit is not None and _replay(hit):
+            return hit["y"]
+    launched = []
     device = x.device()
     unknown = set(opts) - _OPTS
     if unknown:
         raise TypeError(f"dense_reader.matmul: unknown options {sorted(unknown)}")
+    opts_in = dict(opts)
     if not isinstance(w, (list, tuple)):
         check_banks(w, max_banks)
     elif is_block_list(w):
@@ -426,7 +439,8 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
         assert ext or residual.dtype == ttnn.bfloat16, residual.dtype
         assert residual.memory_config().memory_layout == ttnn.TensorMemoryLayout.INTERLEAVED
         assert tuple(residual.padded_shape) == (1, 1, -(-M // TILE) * TILE, -(-N // TILE) * TILE), (residual.shape, N)
-        assert col0 == 0 and (out is None or out is residual), "dense_reader: residual with a fresh output or in place"
+        # (the reference takes a fresh output or the residual itself; any other preallocated out is as safe here)
+        assert col0 == 0, "dense_reader: residual with a fresh output or in place"
     blocks_all = ((w, w_up, col0), *segs)
     ends = [(c0, -(-(g.shape[-1] // 2 if glu and u is None else g.shape[-1]) // TILE)) for g, u, c0 in blocks_all]
     if segs:
@@ -452,9 +466,39 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     if segs:
         _block_kw_check(device, x, blocks_all, full_sync, opts, slices)
     for m0, _ in slices:
-        _launch(x, blocks_all, scale, col_scales, y, m0, min(32, M - m0), topk, act, residual, glu, out32,
-                opts.get("ks") or KS or 0, opts.get("max_ctas") or MAX_CTAS or 0)
+        launched.append(_launch(x, blocks_all, scale, col_scales, y, m0, min(32, M - m0), topk, act, residual, glu,
+                                out32, opts.get("ks") or KS or 0, opts.get("max_ctas") or MAX_CTAS or 0))
+    if call_key is not None and out is not None:
+        # (only calls that write into a given output: a fresh output per call cannot be replayed)
+        if len(_CALLS) >= _CALLS_MAX:
+            _CALLS.clear()
+        ws = _WORKSPACE.get(device.id)
+        _CALLS[call_key] = {
+            "y": y, "launches": launched, "device": device, "ws": ws, "ws_ptr": ws.data_ptr(),
+            "keep": (x, w, scale, out, w_up, topk, opts_in),
+            "ptrs": (_raw(x).data_ptr(), _raw(y).data_ptr()),
+            "topk": None if topk is None else tuple(sorted((k, id(v)) for k, v in topk.items())),
+        }
     return y
+
+
+def _replay(hit):
+    """Launch a cached call again; False when something under it has moved (then the full path runs)."""
+    x, _, _, _, _, topk, _ = hit["keep"]
+    device = hit["device"]
+    if (_raw(x).data_ptr(), _raw(hit["y"]).data_ptr()) != hit["ptrs"] or _WORKSPACE.get(device.id) is not hit["ws"]:
+        return False
+    if torch.cuda.current_device() != device.id:
+        return False
+    if topk is not None and tuple(sorted((k, id(v)) for k, v in topk.items())) != hit["topk"]:
+        return False
+    fn = _tkd.lib().tkd_matmul
+    stream = torch.cuda.current_stream().cuda_stream
+    for a in hit["launches"]:
+        rc = fn(ctypes.byref(a), stream)
+        if rc:
+            _tkd.check(rc, "tkd_matmul")
+    return True
 
 
 def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, out32, ks=0, max_ctas=0):
@@ -511,6 +555,9 @@ def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, o
     a.residual = rt.data_ptr() + m0 * rt.shape[-1] * rt.element_size() if rt is not None else None
     with torch.cuda.device(device.torch):
         _tkd.check(_tkd.lib().tkd_matmul(ctypes.byref(a), torch.cuda.current_stream().cuda_stream), "tkd_matmul")
+    done = _tkd.TkdMatmul()
+    ctypes.pointer(done)[0] = a  # (a copy: the cached descriptor is rewritten by the next row slice or call)
+    return done
 
 
 # --- top-k records ----------------------------------------------------------------------------------------------------

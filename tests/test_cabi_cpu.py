@@ -61,7 +61,7 @@ def plan(tkd, **kw):
 
 def test_plans(tkd):
     rc, p = plan(tkd, fmt=tkd.FMT_BFP4, m=1, k=4096, ns=[14336], epilogue=tkd.EPI_GLU2)
-    assert rc == 0 and p.ks == 256 and p.nslices == 16 and p.panels == 224 and p.items == 3584
+    assert rc == 0 and p.ks == 1024 and p.nslices == 4 and p.panels == 224 and p.items == 896
     assert p.weight_bytes == 66060288 and p.smem_bytes <= 227 * 1024 and p.stages >= 8
     rc, p = plan(tkd, fmt=tkd.FMT_BFP8, m=32, k=14336, ns=[4096], epilogue=tkd.EPI_OUT32, out_dtype=tkd.DT_F32)
     assert rc == 0 and p.ks == 512 and p.nslices == 28 and p.panels == 32 and p.stages >= 3
@@ -72,6 +72,7 @@ def test_plans(tkd):
     assert plan(tkd, fmt=tkd.FMT_BFP8, m=1, k=4016, ns=[64])[0] == 1
     assert plan(tkd, fmt=7, m=1, k=4096, ns=[64])[0] == 1
     assert plan(tkd, fmt=tkd.FMT_BFP8, m=1, k=4096, ns=[64], ks=100)[0] == 1
+    assert plan(tkd, fmt=tkd.FMT_BFP8, m=1, k=2048, ns=[4096])[1].ks == 512 and plan(tkd, fmt=tkd.FMT_BFP8, m=1, k=1024, ns=[64])[1].ks == 256
     assert plan(tkd, fmt=tkd.FMT_BFP8, m=1, k=4096, ns=[96], epilogue=tkd.EPI_GLU_IL)[0] == 1
 
 

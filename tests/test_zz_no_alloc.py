@@ -52,10 +52,11 @@ def test_noalloc_equals_matmul_twice(device, dtype, m):
 
 
 def test_noalloc_refuses_what_does_not_fit(device):
-    """The LM head's 1187 panels of 16 slices need more scratch than the built-in array: refused, nothing launched."""
+    """Eight rows against the LM head (1187 panels of 4 slices, 8 KB of slice sums each) need more scratch than the
+    built-in array: refused, nothing launched."""
     L = _tkd.lib()
     a = _tkd.TkdMatmul()
-    a.fmt, a.m, a.k, a.nblocks, a.epilogue, a.out_dtype = _tkd.FMT_BFP8, 1, 4096, 1, _tkd.EPI_PLAIN, _tkd.DT_BF16
+    a.fmt, a.m, a.k, a.nblocks, a.epilogue, a.out_dtype = _tkd.FMT_BFP8, 8, 4096, 1, _tkd.EPI_PLAIN, _tkd.DT_BF16
     a.block[0].n = 151936
     assert L.tkd_matmul_noalloc(ctypes.byref(a), None) == _tkd.ERR_FIXED_SCRATCH
     assert b"built-in" in L.tkd_error_string(_tkd.ERR_FIXED_SCRATCH)
