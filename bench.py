@@ -252,6 +252,9 @@ def main():
 
     if args.ks:
         linear.KS = args.ks
+    if world > 1:
+        # NCCL's all-gather kernel needs SMs of its own to run beside the persistent stream kernel (one CTA per SM)
+        linear.MAX_CTAS = torch.cuda.get_device_properties(local).multi_processor_count - 4
     torch.cuda.set_device(local)
     if world > 1:
         import torch.distributed as dist
@@ -270,25 +273,78 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    # ---- N > 1: the ranks' outputs are joined by an NCCL all-gather on a side stream, overlapped with the next step ----
+    launches_per_step = 1
+    if world > 1 and args.workload != "c5":
+        ybuf = [case["y"], ttnn.allocate_tensor_on_device(case["y"].shape, case["y"].dtype, ttnn.TILE_LAYOUT, device)]
+        gbuf = [torch.empty(world * ybuf[0].t.numel(), dtype=ybuf[0].t.dtype, device=device.torch) for _ in range(2)]
+        side = torch.cuda.Stream()
+        plain_step = step
+
+        def step(i):
+            main = torch.cuda.current_stream()
+            if i >= 2:
+                main.wait_stream(side)  # the gather that read this output buffer two steps ago
+            plain_step(i, y_t=ybuf[i % 2])
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                dist.all_gather_into_tensor(gbuf[i % 2], ybuf[i % 2].t.reshape(-1))
+            return ybuf[i % 2]
+
+        def join_side():
+            torch.cuda.current_stream().wait_stream(side)
+    else:
+        def join_side():
+            pass
+    if world > 1 and args.workload == "c5":
+        from dense_reader import sharded  # noqa: F401
+        rbuf = torch.empty(world * case["step"](0).t.numel(), dtype=torch.int32, device=device.torch)
+        plain_step5 = step
+
+        def step(i):  # noqa: F811
+            r = plain_step5(i)
+            dist.all_gather_into_tensor(rbuf, r.t.reshape(-1))
+            return r
+
     # ---- device-resident: the K steps as one CUDA graph ----
     for i in range(warmup):
         step(i)
+    join_side()
     linear.check_status(device)
     if args.profile:
         for i in range(steps):
             step(i)
+        join_side()
         linear.check_status(device)
         return 0
     graph = torch.cuda.CUDAGraph()
     cap = torch.cuda.Stream()
     cap.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(cap):
-        step(0)
-        with torch.cuda.graph(graph, stream=cap):
+    graphed = True
+    try:
+        with torch.cuda.stream(cap):
+            step(0)
+            join_side()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=cap):
+                for i in range(steps):
+                    step(i)
+                join_side()
+        torch.cuda.synchronize()
+        graph.replay()  # one untimed replay
+    except Exception as e:  # (a collective that cannot be captured: time plain launches instead)
+        graphed = False
+        sys.stderr.write(f"bench: CUDA graph capture failed ({type(e).__name__}: {e}); timing plain launches\n")
+        torch.cuda.synchronize()
+
+    def run_once():
+        if graphed:
+            graph.replay()
+        else:
             for i in range(steps):
                 step(i)
-    torch.cuda.synchronize()
-    graph.replay()  # one untimed replay
+            join_side()
+
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with Clocks(local) as clk:
@@ -296,7 +352,7 @@ def main():
         reps = max(1, int(0.6 / max(1e-6, steps * 12e-6)))  # keep the timed region long enough for a clock sample
         e0.record()
         for _ in range(reps):
-            graph.replay()
+            run_once()
         e1.record()
         torch.cuda.synchronize()
         time.sleep(0.15)
@@ -324,10 +380,12 @@ def main():
 
     for i in range(warmup):
         e2e_step(i)
+    join_side()
     barrier()
     e0.record()
     for i in range(e_steps):
         e2e_step(i)
+    join_side()
     e1.record()
     torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1)], device=device.torch)
@@ -338,8 +396,7 @@ def main():
     linear.check_status(device)
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        finish(world)
         return 0
     peak, peak_src = peaks()
     achieved = case["abytes"] / (us_call * 1e-6) / 1e9
@@ -348,7 +405,10 @@ def main():
         "ms_per_step": ms / steps, "us_per_call": us_call, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 x block-float, fp32 accumulate", "data": "synthetic",
         "config": {**config, "l2": f"rotation over {copies} distinct packed weight sets ({copies * case['wbytes'] / 1e6:.0f} MB > 2 x L2)",
-                   "timing": f"CUDA graph of {steps} launches, {reps} replays, CUDA events"},
+                   "timing": (f"CUDA graph of {steps} launches, {reps} replays, CUDA events" if graphed
+                              else f"{steps} plain launches x {reps}, CUDA events"),
+                   "exchange": ("none (one GPU)" if world == 1 else
+                                "NCCL all-gather of every rank's output per step on a side stream, inside the timed region")},
         "pct_of_8000": 100 * value / world / 8000.0,
         "clocks": clk.summary(),
         "e2e": {"value": e2e_val, "unit": "GB/s", "us_per_call": e2e_ms * 1e3 / e_steps, "steps": e_steps,
@@ -361,10 +421,18 @@ def main():
     if world == 1 and not args.no_cpu:
         val, info = cpu_reference_arm(args.workload, m, 10_000, 2, budget_s=15.0)
         line["cpu_baseline"] = {"value": val, "unit": "GB/s", **info}
-    print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    print(json.dumps(line), flush=True)
+    finish(world)
     return 0
+
+
+def finish(world):
+    """Leave a multi-rank run without waiting on NCCL's teardown (captured collectives can keep it from returning)."""
+    if world > 1:
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 # DRAM bytes per launch of tkd_stream_kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum), per
