@@ -65,9 +65,9 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     const int mt = a->m <= 8 ? 1 : (a->m <= 16 ? 2 : 4);
     const int sab = tkd_sab(a->fmt);
     const int chunk_k = tkd_chunk_k(a->fmt);
-    // k per slice: a function of K and the row bucket only (a column's sum must not depend on anything else)
+    // k per slice: a function of K only (a column's sum must not depend on anything but K, the format and M's bucket)
     const int ks_k = a->k >= 4096 ? 1024 : (a->k >= 2048 ? 512 : 256);
-    p.ks = a->ks ? a->ks : (mt == 4 && ks_k > 512 ? 512 : ks_k);
+    p.ks = a->ks ? a->ks : (ks_k < chunk_k ? chunk_k : ks_k);
     if (p.ks < chunk_k || p.ks % chunk_k || p.ks > 4096) return TKD_ERR_BAD_ARG;
     p.nslices = (p.K + p.ks - 1) / p.ks;
     p.panel_bytes = tkd_panel_bytes(a->fmt, a->k);

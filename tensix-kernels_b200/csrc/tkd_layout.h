@@ -7,7 +7,8 @@
 // the A operand:
 //
 //   stream   = panels of 128 columns back to back (N is padded to 128 with zero columns)
-//   panel    = chunks of CK k (256; 128 for bfloat16), K ascending; a chunk is what one stage of the ring holds
+//   panel    = chunks of CK k (256 for bfloat8_b, 512 for bfloat4_b, 128 for bfloat16), K ascending; a chunk is what
+//              one stage of the ring holds
 //   chunk    = its 8 groups back to back, each the chunk's super-atoms, K ascending
 //   super-atom (bfloat8_b, 32 k, 544 B)  = 32 B exponent words, then 32 lanes x 16 B of codes
 //   super-atom (bfloat4_b, 64 k, 576 B)  = 64 B exponent words, then 32 lanes x 16 B of codes
@@ -48,7 +49,7 @@ TKD_HD int tkd_ksa(int fmt) { return fmt == TKD_BFP4 ? 64 : 32; }               
 TKD_HD int tkd_sab(int fmt) { return fmt == TKD_BFP8 ? 544 : (fmt == TKD_BFP4 ? 576 : 1024); }  // bytes per super-atom
 TKD_HD int tkd_exp_bytes(int fmt) { return fmt == TKD_BFP8 ? 32 : (fmt == TKD_BFP4 ? 64 : 0); }
 TKD_HD int tkd_unit_exp(int fmt) { return 126 + tkd_mant_bits(fmt); }  // value = m * 2^(e - unit)
-TKD_HD int tkd_chunk_k(int fmt) { return fmt == TKD_BF16 ? 128 : 256; }                    // k per chunk (stage)
+TKD_HD int tkd_chunk_k(int fmt) { return fmt == TKD_BF16 ? 128 : (fmt == TKD_BFP4 ? 512 : 256); }  // k per chunk (stage)
 TKD_HD int tkd_subsa(int fmt) { return tkd_chunk_k(fmt) / tkd_ksa(fmt); }                  // super-atoms per group and chunk
 TKD_HD int64_t tkd_nsa(int fmt, int64_t K) { return (K + tkd_ksa(fmt) - 1) / tkd_ksa(fmt); }
 TKD_HD int64_t tkd_run_bytes(int fmt, int64_t K) { return tkd_nsa(fmt, K) * tkd_sab(fmt); }  // one group, all of K

@@ -8,7 +8,7 @@
 //
 // One persistent CTA per SM, three kinds of warps, coupled by mbarriers only:
 //   warp 0        producer (one lane): one 1-D bulk copy (TMA, no multicast) per stage of the shared-memory ring; a
-//                 stage is one chunk of one panel (128 columns x 256 k), contiguous in the stream. (A bulk copy costs
+//                 stage is one chunk of one panel (128 columns x 256 or 512 k), contiguous in the stream. (A bulk copy costs
 //                 the issuing SM about 140 cycles whatever its size, so stages are single copies of 17-35 KB.)
 //   warps 1-16    streaming warps: warp (group g, half h) multiplies the 16 columns of group g by every other
 //                 super-atom of the chunk with mma.sync m16n8k16, the weights as A. Block-float codes go in as bf16
@@ -179,7 +179,7 @@ struct Fmt<TKD_BFP8> {
 };
 template <>
 struct Fmt<TKD_BFP4> {
-    static constexpr int KSA = 64, SAB = 576, SUBSA = 4, XB = 2;
+    static constexpr int KSA = 64, SAB = 576, SUBSA = 8, XB = 2;
 };
 template <>
 struct Fmt<TKD_BF16> {
@@ -581,22 +581,50 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
                     } else {
 #pragma unroll 1
                         for (int hh = 0; hh < 2; ++hh) {
-                            float th[MR];
+                            if constexpr (MT == 4) {
+                                // eight rows at a time, four slices' loads in flight together
 #pragma unroll
-                            for (int m = 0; m < MR; ++m)
-                                if (m < M) th[m] = term(pe - 1, hh, m);
+                                for (int rb = 0; rb < MR; rb += 8) {
+                                    if (rb >= M) break;
+                                    float th[8];
+#pragma unroll
+                                    for (int m = 0; m < 8; ++m)
+                                        if (rb + m < M) th[m] = term(pe - 1, hh, rb + m);
 #pragma unroll 1
-                            for (int s = pe; s < p.nslices; ++s) {
-                                float v[MR];
+                                    for (int s = pe; s < p.nslices; s += 4) {
+                                        float v[4][8];
+#pragma unroll
+                                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                            for (int m = 0; m < 8; ++m)
+                                                if (s + j < p.nslices && rb + m < M) v[j][m] = term(s + j, hh, rb + m);
+#pragma unroll
+                                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                            for (int m = 0; m < 8; ++m)
+                                                if (s + j < p.nslices && rb + m < M) th[m] += v[j][m];
+                                    }
+#pragma unroll
+                                    for (int m = 0; m < 8; ++m) tot[rb + m] = hh == 0 ? th[m] : tot[rb + m] + th[m];
+                                }
+                            } else {
+                                float th[MR];
 #pragma unroll
                                 for (int m = 0; m < MR; ++m)
-                                    if (m < M) v[m] = term(s, hh, m);
+                                    if (m < M) th[m] = term(pe - 1, hh, m);
+#pragma unroll 1
+                                for (int s = pe; s < p.nslices; ++s) {
+                                    float v[MR];
 #pragma unroll
-                                for (int m = 0; m < MR; ++m)
-                                    if (m < M) th[m] += v[m];
+                                    for (int m = 0; m < MR; ++m)
+                                        if (m < M) v[m] = term(s, hh, m);
+#pragma unroll
+                                    for (int m = 0; m < MR; ++m)
+                                        if (m < M) th[m] += v[m];
+                                }
+#pragma unroll
+                                for (int m = 0; m < MR; ++m) tot[m] = hh == 0 ? th[m] : tot[m] + th[m];
                             }
-#pragma unroll
-                            for (int m = 0; m < MR; ++m) tot[m] = hh == 0 ? th[m] : tot[m] + th[m];
                         }
                     }
                 }
