@@ -122,6 +122,12 @@ int tkd_matmul_plan(const TkdMatmul* a, TkdPlan* plan);
 int tkd_matmul_workspace(const TkdMatmul* a, uint64_t* bytes);
 int tkd_matmul(const TkdMatmul* a, void* stream);
 
+/* tkd_matmul with the activations and the result in HOST memory (pinned, for the copies to be asynchronous): copies
+ * x_host [m, k] bf16 into a->x, launches, copies a->out [m, ldo] to out_host, all on `stream`; a->x and a->out are the
+ * caller's device staging buffers (ldx == k). The counterpart of a caller doing ttnn.from_torch(x) ... ttnn.to_torch(y)
+ * around linear.matmul (e.g. examples/dense_reader_example.py:24-26 of the reference). Does not synchronise. */
+int tkd_matmul_host(const TkdMatmul* a, const void* x_host, void* out_host, void* stream);
+
 /* tkd_matmul for callers that cannot allocate device memory (no counterpart in the reference: its device buffers
  * all come from ttnn's allocator). Some hosts of this library never get to call cudaMalloc: a plugin running inside
  * another framework's memory pool, a step replayed from a fixed arena, a process whose device memory was handed out

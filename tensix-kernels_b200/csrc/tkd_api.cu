@@ -280,6 +280,19 @@ int tkd_matmul(const TkdMatmul* a, void* stream) {
     return run_matmul(a, a->workspace, a->workspace_bytes, stream);
 }
 
+int tkd_matmul_host(const TkdMatmul* a, const void* x_host, void* out_host, void* stream) {
+    if (!a || !x_host || !out_host || !a->x || !a->out) return TKD_ERR_BAD_ARG;
+    if (a->ldx != a->k) return TKD_ERR_BAD_ARG;  // the staging copy of x is one contiguous block
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(const_cast<void*>(a->x), x_host, (size_t)a->m * a->k * 2, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return cuda_err(e);
+    const int rc = run_matmul(a, a->workspace, a->workspace_bytes, stream);
+    if (rc) return rc;
+    const size_t esz = a->out_dtype == TKD_DT_F32 ? 4 : 2;
+    e = cudaMemcpyAsync(out_host, a->out, (size_t)a->m * a->ldo * esz, cudaMemcpyDeviceToHost, st);
+    return cuda_err(e);
+}
+
 // ---- tkd_matmul for callers that must not allocate ----------------------------------------------------------------
 // The same launch as tkd_matmul, with the kernel's workspace (its panel and unit counters, the slice sums of panels
 // spread over several CTAs, the bf16 outputs of a top-k call that writes no y) taken from an array that is part of

@@ -519,6 +519,18 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
             if (!f.deliver) continue;
             const TkdSegDev& sg = p.seg[c.seg];
             const uint32_t pb = pi & 1;
+            // this thread's column within its weight; its group's exponent byte and its scale are asked for now, so
+            // that their latency passes while the streaming warps are still at work
+            const int n = glu2 ? c.pl * 64 + (et & 63) : c.pl * TKD_PANEL_COLS + et;
+            const bool in_w = n < sg.n_valid;
+            int ebyte = 0;
+            float sc = 1.f;
+            if constexpr (FMT != TKD_BF16) ebyte = (glu2 && et >= 64 ? sg.emax2 : sg.emax)[n >> 4];
+            if (p.scale_dt != TKD_DT_NONE && in_w) {
+                const void* sp = glu2 && et >= 64 ? p.scale2 : p.scale;
+                sc = p.scale_dt == TKD_DT_BF16 ? bf16_bits_to_f32(static_cast<const uint16_t*>(sp)[n])
+                                               : static_cast<const float*>(sp)[n];
+            }
             PROF_T0;
             ok = mbar_wait(pfull0 + 8 * pb, (pi >> 1) & 1, p.status);
             if (!ok) break;
@@ -634,22 +646,16 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
             if (!finish) continue;
 
             // ------------------------------------------------------------ the output stage of one panel
-            // this thread's column within its weight, and the block-float factor of its group
-            const int n = glu2 ? c.pl * 64 + (et & 63) : c.pl * TKD_PANEL_COLS + et;
+            // the block-float factor of this thread's group
             if constexpr (FMT != TKD_BF16) {
-                const uint8_t* em = glu2 && et >= 64 ? sg.emax2 : sg.emax;
                 // 2^e in two factors, each a normal float (e is within -69 .. 189)
-                const int e = (int)em[n >> 4] + 64 - (FMT == TKD_BFP8 ? 133 : 129);
+                const int e = ebyte + 64 - (FMT == TKD_BFP8 ? 133 : 129);
                 const int e1 = e / 2, e2 = e - e1;
                 const float f1 = __uint_as_float((uint32_t)(e1 + 127) << 23), f2 = __uint_as_float((uint32_t)(e2 + 127) << 23);
 #pragma unroll
                 for (int m = 0; m < MR; ++m) tot[m] = tot[m] * f1 * f2;
             }
-            const bool in_w = n < sg.n_valid;
             if (p.scale_dt != TKD_DT_NONE && in_w) {
-                const void* sp = glu2 && et >= 64 ? p.scale2 : p.scale;
-                const float sc = p.scale_dt == TKD_DT_BF16 ? bf16_bits_to_f32(static_cast<const uint16_t*>(sp)[n])
-                                                           : static_cast<const float*>(sp)[n];
 #pragma unroll
                 for (int m = 0; m < MR; ++m) tot[m] *= sc;
             }

@@ -53,6 +53,7 @@ SYMBOLS = {
     "tkd_matmul_plan": (c_i32, [ctypes.POINTER(TkdMatmul), ctypes.POINTER(TkdPlan)]),
     "tkd_matmul_workspace": (c_i32, [ctypes.POINTER(TkdMatmul), ctypes.POINTER(c_u64)]),
     "tkd_matmul": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp]),
+    "tkd_matmul_host": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp, c_vp, c_vp]),
     "tkd_matmul_noalloc": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp]),
 }
 

@@ -171,11 +171,19 @@ def _raw(t):
     return t.t if isinstance(t, ttnn.Tensor) else t
 
 
+# Calls that may overlap on the GPU (different streams) must not share a workspace: the one in use is picked by slot.
+WORKSPACE_SLOT = 0
+
+
+def _ws_key(device):
+    return (device.id, WORKSPACE_SLOT)
+
+
 def _workspace(device, nbytes):
-    ws = _WORKSPACE.get(device.id)
+    ws = _WORKSPACE.get(_ws_key(device))
     if ws is None or ws.numel() < nbytes:
         # (zeroed once: the kernel leaves its counters at zero)
-        ws = _WORKSPACE[device.id] = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device.torch)
+        ws = _WORKSPACE[_ws_key(device)] = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device.torch)
     return ws
 
 
@@ -192,7 +200,8 @@ def check_status(device):
     code = int(status_word(device).item())
     if code:
         status_word(device).zero_()
-        _WORKSPACE.pop(device.id, None)  # its counters may be mid-count
+        for key in [k for k in _WORKSPACE if k[0] == device.id]:
+            _WORKSPACE.pop(key)  # their counters may be mid-count
         raise _tkd.TkdError(code, "a kernel reported")
 
 
@@ -367,9 +376,10 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     if CACHE:
         # The same call again (the same tensor objects and options): everything was checked and described the first
         # time; only the addresses are looked at again. The entry keeps its arguments alive, so their ids stay theirs.
-        call_key = (id(x), id(w), id(scale), id(out), id(w_up), id(topk), col0, max_banks, KS, MAX_CTAS, TOPK_UNIT,
-                    tuple((k, tuple(map(id, v)) if type(v) is tuple else id(v)) for k, v in opts.items()))
+        call_key = _call_key(x, w, scale, topk, out, col0, w_up, max_banks, opts)
         hit = _CALLS.get(call_key)
+        if hit is not None and hit["ws_key"][1] != WORKSPACE_SLOT:
+            hit = None
         if hit is not None and _replay(hit):
             return hit["y"]
     launched = []
@@ -472,9 +482,9 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
         # (only calls that write into a given output: a fresh output per call cannot be replayed)
         if len(_CALLS) >= _CALLS_MAX:
             _CALLS.clear()
-        ws = _WORKSPACE.get(device.id)
+        ws = _WORKSPACE.get(_ws_key(device))
         _CALLS[call_key] = {
-            "y": y, "launches": launched, "device": device, "ws": ws, "ws_ptr": ws.data_ptr(),
+            "y": y, "launches": launched, "device": device, "ws": ws, "ws_key": _ws_key(device),
             "keep": (x, w, scale, out, w_up, topk, opts_in),
             "ptrs": (_raw(x).data_ptr(), _raw(y).data_ptr()),
             "topk": None if topk is None else tuple(sorted((k, id(v)) for k, v in topk.items())),
@@ -482,11 +492,41 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     return y
 
 
+def _call_key(x, w, scale, topk, out, col0, w_up, max_banks, opts):
+    return (id(x), id(w), id(scale), id(out), id(w_up), id(topk), col0, max_banks, KS, MAX_CTAS, TOPK_UNIT, WORKSPACE_SLOT,
+            tuple((k, tuple(map(id, v)) if type(v) is tuple else id(v)) for k, v in opts.items()))
+
+
+def matmul_host(x_host, out_host, x, w, scale, *, topk=None, out=None, col0=0, w_up=None, max_banks=None, stream=None,
+                **opts):
+    """matmul for a caller whose activations and result live in host memory: x_host (pinned torch bf16 [M, K]) is
+    copied into the device tensor x, the op runs, and its output `out` (required) is copied to out_host (pinned), all
+    on the current stream (or `stream`, a torch.cuda.Stream) and without synchronising: one call into the library
+    (tkd_matmul_host) instead of three framework calls. The other arguments are matmul's; up to 32 rows. The first call with a given set of tensors goes
+    through matmul itself (which checks everything and also launches once)."""
+    assert out is not None and CACHE, "dense_reader.matmul_host: needs out= and the launch cache"
+    key = _call_key(x, w, scale, topk, out, col0, w_up, max_banks, opts)
+    hit = _CALLS.get(key)
+    if hit is None:
+        if stream is None:
+            matmul(x, w, scale, topk=topk, out=out, col0=col0, w_up=w_up, max_banks=max_banks, **opts)
+        else:
+            with torch.cuda.stream(stream):
+                matmul(x, w, scale, topk=topk, out=out, col0=col0, w_up=w_up, max_banks=max_banks, **opts)
+        hit = _CALLS[key]
+    assert len(hit["launches"]) == 1, "dense_reader.matmul_host: one launch (up to 32 rows)"
+    sp = torch.cuda.current_stream().cuda_stream if stream is None else stream.cuda_stream
+    rc = _tkd.lib().tkd_matmul_host(ctypes.byref(hit["launches"][0]), x_host.data_ptr(), out_host.data_ptr(), sp)
+    if rc:
+        _tkd.check(rc, "tkd_matmul_host")
+    return out
+
+
 def _replay(hit):
     """Launch a cached call again; False when something under it has moved (then the full path runs)."""
     x, _, _, _, _, topk, _ = hit["keep"]
     device = hit["device"]
-    if (_raw(x).data_ptr(), _raw(hit["y"]).data_ptr()) != hit["ptrs"] or _WORKSPACE.get(device.id) is not hit["ws"]:
+    if (_raw(x).data_ptr(), _raw(hit["y"]).data_ptr()) != hit["ptrs"] or _WORKSPACE.get(hit["ws_key"]) is not hit["ws"]:
         return False
     if torch.cuda.current_device() != device.id:
         return False

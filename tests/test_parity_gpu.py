@@ -207,3 +207,20 @@ def test_full_size_properties(device):
         assert torch.equal(ysub, pick)
         close_bf16(ysub[:1], orc.matmul_f64(x[:1], orc.native_values(sub, fmt)[0]))
     linear.check_status(device)
+
+
+def test_matmul_host_equals_matmul(device):
+    """The host-buffer call (pinned x in, pinned y out, one library call) gives what matmul gives."""
+    g = torch.Generator().manual_seed(70)
+    k, n, m = 2048, 1024, 3
+    tw, _ = linear.native_weight(device, torch.randn(n, k, generator=g) * 0.02, ttnn.bfloat8_b)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    tx = dev_x(device, torch.zeros(m, k))
+    out = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
+    x_pin, y_pin = x.contiguous().pin_memory(), torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):
+        linear.matmul_host(x_pin, y_pin, tx, tw, None, out=out)
+        torch.cuda.synchronize()
+        want = host(linear.matmul(dev_x(device, x.float()), tw, None))
+        assert torch.equal(y_pin.float(), want)
+    linear.check_status(device)
