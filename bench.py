@@ -17,8 +17,9 @@ reference's torch path (the oracle's port of dense_reader/linear.py:166-169 plus
 a bounded column sample of the same workload.
 
 N > 1 (torchrun, one rank per GPU, NCCL): weak scaling. Each rank streams its own column shard of the same size (a layer
-N times as wide, column-sharded as native_weight would pack it per rank) and the ranks' outputs are all-gathered over
-NCCL on a side stream while the next step's kernel runs.
+N times as wide, column-sharded as native_weight would pack it per rank) and every rank ends each step holding all
+ranks' outputs: by default the stream kernel stores them into the other ranks' buffers itself (peer stores over NVLink,
+sharded.Exchange); --exchange nccl all-gathers them with NCCL on a side stream instead.
 
 --impl reference: the reference's own CPU implementation of the path (the oracle port; the reference's device path needs
 ttnn and a Tensix simulator, neither of which exists here), all host threads, same metric.
@@ -97,22 +98,23 @@ class Clocks:
                 "samples": len(good), "reasons": reasons}
 
 
-def make_inputs(wl, m, seed):
+def make_inputs(wl, m, seed, n=None):
     """Seeded synthetic tensors of the workload's shapes: W ~ N(0,1) * 0.02, x ~ N(0,1), scales ~ U(0.5,1.5)."""
     g = torch.Generator().manual_seed(seed)
-    k, n = wl["k"], wl["n"]
+    k, n = wl["k"], n or wl["n"]
     x = torch.randn(m, k, generator=g).to(torch.bfloat16)
     return g, x, k, n
 
 
-def build_gpu_case(name, m, device, copies, seed0):
-    """The device-side tensors of one workload: `copies` distinct packed weight sets, and a closure running step i."""
+def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
+    """The device-side tensors of one workload (n_cols: this rank's columns of it, when it is split): `copies` distinct
+    packed weight sets, and a closure running step i."""
     from common import ttnn_like as ttnn
     from dense_reader import linear
 
     wl = WORKLOADS[name]
     dt = {"bfp8": ttnn.bfloat8_b, "bfp4": ttnn.bfloat4_b}[wl["fmt"]]
-    g, x, k, n = make_inputs(wl, m, seed0)
+    g, x, k, n = make_inputs(wl, m, seed0, n_cols)
     tx = ttnn.from_torch(x.reshape(1, 1, m, k), dtype=ttnn.bfloat16, layout=ttnn.TILE_LAYOUT, device=device)
     sets = []
     for c in range(copies):
@@ -131,9 +133,9 @@ def build_gpu_case(name, m, device, copies, seed0):
 
         cs = (sg, su)
 
-        def step(i, x_t=tx, y_t=y):
+        def step(i, x_t=tx, y_t=y, **kw):
             wg, wu = sets[i % copies]
-            return linear.matmul(x_t, wg, None, w_up=wu, glu=True, col_scales=cs, out=y_t)
+            return linear.matmul(x_t, wg, None, w_up=wu, glu=True, col_scales=cs, out=y_t, **kw)
 
         def host_step(i, x_pin, y_pin, x_t, y_t, stream):
             wg, wu = sets[i % copies]
@@ -144,8 +146,8 @@ def build_gpu_case(name, m, device, copies, seed0):
         res = ttnn.from_torch(torch.randn(1, 1, m, n, generator=g), dtype=ttnn.float32, layout=ttnn.TILE_LAYOUT, device=device)
         y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.float32, ttnn.TILE_LAYOUT, device)
 
-        def step(i, x_t=tx, y_t=y):
-            return linear.matmul(x_t, sets[i % copies][0], None, residual=res, out32=True, out=y_t)
+        def step(i, x_t=tx, y_t=y, res_t=res, **kw):
+            return linear.matmul(x_t, sets[i % copies][0], None, residual=res_t, out32=True, out=y_t, **kw)
 
         def host_step(i, x_pin, y_pin, x_t, y_t, stream):
             linear.matmul_host(x_pin, y_pin, x_t, sets[i % copies][0], None, residual=res, out32=True, out=y_t, stream=stream)
@@ -158,15 +160,15 @@ def build_gpu_case(name, m, device, copies, seed0):
         y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
         spec = {"r": r, "k": 8, "rows": 1, "slot0": 0, "base": 0, "n": n, "write_y": False}
 
-        def step(i, x_t=tx, y_t=y):
-            linear.matmul(x_t, sets[i % copies][0], None, topk=spec, out=y_t)
-            return r
+        def step(i, x_t=tx, y_t=y, spec_t=spec, **kw):
+            linear.matmul(x_t, sets[i % copies][0], None, topk=spec_t, out=y_t, **kw)
+            return spec_t["r"]
         weights = 1
     else:
         y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
 
-        def step(i, x_t=tx, y_t=y):
-            return linear.matmul(x_t, sets[i % copies][0], None, out=y_t)
+        def step(i, x_t=tx, y_t=y, **kw):
+            return linear.matmul(x_t, sets[i % copies][0], None, out=y_t, **kw)
 
         def host_step(i, x_pin, y_pin, x_t, y_t, stream):
             linear.matmul_host(x_pin, y_pin, x_t, sets[i % copies][0], None, out=y_t, stream=stream)
@@ -233,6 +235,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--ks", type=int, default=0, help="k per slice of the kernel's work items (0: the library's default)")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                    help="N > 1: weak: every rank streams a whole workload; strong: the one workload's columns are split")
+    ap.add_argument("--exchange", choices=["fused", "nccl", "none"], default="fused",
+                    help="N > 1: how every rank gets all ranks' outputs (fused: peer stores from the stream kernel)")
     ap.add_argument("--profile", action="store_true",
                     help="for a profiler: warm-up, then `steps` plain launches (no graph, no e2e, no CPU leg, no JSON line)")
     args = ap.parse_args()
@@ -265,18 +271,33 @@ def main():
 
     if args.ks:
         linear.KS = args.ks
-    if world > 1:
-        # NCCL's all-gather kernel needs SMs of its own to run beside the persistent stream kernel (one CTA per SM)
-        linear.MAX_CTAS = torch.cuda.get_device_properties(local).multi_processor_count - 4
+    fused = args.exchange == "fused"
+    if world > 1 and not fused:
+        # NCCL's all-gather kernel needs SMs of its own to run beside the persistent stream kernel (one CTA per SM; its
+        # CTAs fill an SM's shared memory, so NCCL's cannot share one with them), and few channels: it moves a few KB
+        linear.MAX_CTAS = torch.cuda.get_device_properties(local).multi_processor_count - 8
+        os.environ.setdefault("NCCL_MAX_NCHANNELS", "4")
+        os.environ.setdefault("NCCL_MIN_NCHANNELS", "1")
     torch.cuda.set_device(local)
     if world > 1:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     device = ttnn.open_device(local)
-    copies = max(2, -(-2 * L2_BYTES // int((2 if args.workload == "c2" else 1) * wl["k"] * wl["n"] * BYTES_PER_WEIGHT[wl["fmt"]])) + 1)
+    # the columns of this rank: weak scaling: a whole workload each (a layer N times as wide); strong: its share of the one
+    n_loc, col_start, n_total = wl["n"], rank * wl["n"], world * wl["n"]
+    if args.scaling == "strong" and world > 1:
+        from dense_reader import sharded
+
+        shards = sharded.column_shards(wl["n"], world, unit=2048 if args.workload == "c5" else 128)
+        (col_start, col_end), n_total = shards[rank], wl["n"]
+        n_loc = col_end - col_start
+    copies = max(2, -(-2 * L2_BYTES // int((2 if args.workload == "c2" else 1) * wl["k"] * n_loc * BYTES_PER_WEIGHT[wl["fmt"]])) + 1)
     copies = min(copies, 40)
-    case = build_gpu_case(args.workload, m, device, copies, seed0=100 + 1000 * rank)
+    if world > 1:
+        assert args.scaling == "weak" or fused, "bench: --scaling strong goes with the fused exchange"
+        config["columns_per_rank"] = n_loc
+    case = build_gpu_case(args.workload, m, device, copies, seed0=100 + 1000 * rank, n_cols=n_loc)
     step = case["step"]
     launches_per_step = 1
 
@@ -286,9 +307,46 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    # ---- N > 1: the ranks' outputs are joined by an NCCL all-gather on a side stream, overlapped with the next step ----
-    launches_per_step = 1
-    if world > 1 and args.workload != "c5":
+    def join_side():
+        pass
+
+    # ---- N > 1: every rank ends each step with all ranks' outputs (or top-k records). "fused": the stream kernel
+    # stores them into the other ranks' buffers itself and ends when every rank's have arrived (no collective launch);
+    # "nccl": an all-gather per step, on a side stream so that it overlaps the next step's kernel. ----
+    exchange_note = "none (one GPU)"
+    if world > 1 and fused:
+        from dense_reader import sharded
+
+        plain_step = step
+        ex = sharded.Exchange(device, 64 << 20)
+        nbuf = 2
+        exchange_note = ("in the stream kernel: peer stores of every output element / record into all ranks' buffers over"
+                         " NVLink, completion flags, the kernel ends when every rank's part has arrived")
+        def join_side():  # noqa: F811  (the last step's exchange)
+            ex.wait_all(linear.status_word(device))
+
+        if args.workload == "c5":
+            r0 = case["step"](0)
+            recs = [ex.tensor([1, 1, linear.topk_units(n_total), r0.shape[-1]], r0.dtype) for _ in range(nbuf)]
+            specs = [{"r": r, "k": 8, "rows": 1, "slot0": col_start // 2048, "base": col_start, "n": n_loc, "write_y": False}
+                     for r in recs]
+
+            def step(i):
+                return plain_step(i, spec_t=specs[i % nbuf], exchange=ex)
+        else:
+            outs = [ex.tensor([1, 1, m, n_total], case["y"].dtype) for _ in range(nbuf)]
+            kw = {}
+            if args.workload == "c3":  # the residual in the gathered output's coordinates
+                g = torch.Generator().manual_seed(77)
+                kw["res_t"] = ttnn.from_torch(torch.randn(1, 1, m, n_total, generator=g), dtype=ttnn.float32,
+                                              layout=ttnn.TILE_LAYOUT, device=device)
+
+            def step(i):
+                return plain_step(i, y_t=outs[i % nbuf], col0=col_start // 32, exchange=ex, **kw)
+    elif world > 1 and args.exchange == "none":
+        exchange_note = "none: every rank keeps its own columns (a diagnostic, not the path's result)"
+    elif world > 1 and args.workload != "c5":
+        exchange_note = "NCCL all-gather of every rank's output per step on a side stream, inside the timed region"
         ybuf = [case["y"], ttnn.allocate_tensor_on_device(case["y"].shape, case["y"].dtype, ttnn.TILE_LAYOUT, device)]
         gbuf = [torch.empty(world * ybuf[0].t.numel(), dtype=ybuf[0].t.dtype, device=device.torch) for _ in range(2)]
         side = torch.cuda.Stream()
@@ -304,13 +362,10 @@ def main():
                 dist.all_gather_into_tensor(gbuf[i % 2], ybuf[i % 2].t.reshape(-1))
             return ybuf[i % 2]
 
-        def join_side():
+        def join_side():  # noqa: F811
             torch.cuda.current_stream().wait_stream(side)
-    else:
-        def join_side():
-            pass
-    if world > 1 and args.workload == "c5":
-        from dense_reader import sharded  # noqa: F401
+    elif world > 1:
+        exchange_note = "NCCL all-gather of every rank's top-k records per step, inside the timed region"
         rbuf = torch.empty(world * case["step"](0).t.numel(), dtype=torch.int32, device=device.torch)
         plain_step5 = step
 
@@ -375,7 +430,11 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    value = case["wbytes"] * steps * world / (ms * 1e-3) / 1e9
+    wb = torch.tensor([case["wbytes"]], dtype=torch.float64, device=device.torch)
+    if world > 1:
+        dist.all_reduce(wb)  # all ranks' packed-weight bytes of one step
+    job_bytes = float(wb.item())
+    value = job_bytes * steps / (ms * 1e-3) / 1e9
     us_call = ms * 1e3 / steps
 
     # ---- end to end through the public API with host buffers ----
@@ -433,7 +492,7 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
-    e2e_val = case["wbytes"] * e_steps * world / (e2e_ms * 1e-3) / 1e9
+    e2e_val = job_bytes * e_steps / (e2e_ms * 1e-3) / 1e9
     linear.check_status(device)
 
     if rank != 0:
@@ -443,13 +502,12 @@ def main():
     achieved = case["abytes"] / (us_call * 1e-6) / 1e9
     line = {
         "metric": "weight_stream_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": ms / steps, "us_per_call": us_call, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms / steps, "us_per_call": us_call, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": "bf16 x block-float, fp32 accumulate", "data": "synthetic",
         "config": {**config, "l2": f"rotation over {copies} distinct packed weight sets ({copies * case['wbytes'] / 1e6:.0f} MB > 2 x L2)",
                    "timing": (f"CUDA graph of {steps} launches, {reps} replays, CUDA events" if graphed
                               else f"{steps} plain launches x {reps}, CUDA events"),
-                   "exchange": ("none (one GPU)" if world == 1 else
-                                "NCCL all-gather of every rank's output per step on a side stream, inside the timed region")},
+                   "exchange": exchange_note},
         "pct_of_8000": 100 * value / world / 8000.0,
         "clocks": clk.summary(),
         "e2e": {"value": e2e_val, "unit": "GB/s", "us_per_call": e2e_ms * 1e3 / e_steps, "steps": e_steps,

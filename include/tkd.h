@@ -42,6 +42,9 @@ extern "C" {
 #define TKD_DT_F32 2
 
 int tkd_version(void);
+/* sizeof of a structure of this header as the library was built (0 TkdMatmul, 1 TkdPlan, 2 TkdBlock): a binding
+ * compares it with its own mirror before the first call. */
+int tkd_struct_bytes(int which);
 const char* tkd_error_string(int code);
 
 /* --- weights: stands in for ttnn.from_torch(dtype=bfloat8_b|bfloat4_b|bfloat16) as native_weight and block_float call
@@ -110,7 +113,28 @@ typedef struct {
     int32_t* status;        /* one int32 (or NULL): a kernel writes TKD_ERR_TIMEOUT here if a wait gives up */
     int32_t ks;             /* k per slice, 0: default; a multiple of 256 (128 for bf16) */
     int32_t max_ctas;       /* 0: one per SM */
+    /* exchange between the GPUs of a column-sharded weight (nranks 0 or 1: none). The output stage writes every
+     * element of out, and every record, also to the same place of each other rank's buffer (peer stores over NVLink:
+     * the all-gather of the outputs happens inside the kernel, column by column as they finish). The warp that
+     * finishes last orders the call's stores system-wide, counts the call in flags[TKD_FLAG_SEQ] and writes that count
+     * to flags[rank] on every rank.
+     * peer_out / peer_records: the addresses, in this process, of the other ranks' buffers (NULL entries: that
+     * buffer is not exchanged), nranks - 1 of them in rank order with the own rank left out; peer_flags likewise. */
+    int32_t nranks, rank;
+    void* peer_out[7];
+    void* peer_records[7];
+    uint32_t* peer_flags[7];
+    uint32_t* flags;        /* this rank's TKD_FLAG_WORDS words, zeroed once, written by every rank */
+    int32_t exchange_wait;  /* 1: the kernel ends only when every rank's count for this call has arrived in flags
+                               (bounded, about a second: then TKD_ERR_TIMEOUT in the status word and tkd_exchange_wait
+                               can wait again); 2: the same wait, but for the exchanged call BEFORE this one (the exchange
+                               of one call overlaps the next call's run; tkd_exchange_wait flushes the last one); 0: no
+                               wait, the caller orders tkd_exchange_wait behind it */
+    int32_t pad_;
 } TkdMatmul;
+#define TKD_MAX_RANKS 8
+#define TKD_FLAG_SEQ 8      /* flags[0..7]: calls completed by rank r, as told by r; flags[8]: calls completed here */
+#define TKD_FLAG_WORDS 16
 
 /* What the launch of a TkdMatmul looks like: the counterpart of the dict plan() returns (linear.py:360-382). */
 typedef struct {
@@ -143,6 +167,21 @@ int tkd_matmul_host(const TkdMatmul* a, const void* x_host, void* out_host, void
  * processes' threads, race on it, so keep calls on one device in stream order. */
 #define TKD_NOALLOC_SCRATCH_BYTES (8u << 20)
 int tkd_matmul_noalloc(const TkdMatmul* a, void* stream);
+
+/* --- exchange between GPUs: stands in for the all-gather of the column shards' outputs (the reference runs on one
+ * device and has none; its multi-device callers would gather [M, N_local] outputs or top-k records). ---------------- */
+
+/* Wait on `stream` until every one of the nranks ranks has completed as many exchanged calls as this rank has
+ * (flags[r] >= flags[TKD_FLAG_SEQ] for all r, modulo 2^32); bounded (about a second), then TKD_ERR_TIMEOUT in *status. */
+int tkd_exchange_wait(uint32_t* flags, int nranks, int32_t* status, void* stream);
+/* Device memory other processes on this machine can map: allocates `bytes` (zeroed; synchronises) and writes its
+ * 64-byte inter-process handle to handle (host). The owner frees it with tkd_peer_free. */
+int tkd_peer_alloc(uint64_t bytes, void** ptr, void* handle);
+int tkd_peer_free(void* ptr);
+/* Map another process's tkd_peer_alloc memory from its handle (host, 64 bytes) into this process, with peer access
+ * between the two GPUs enabled; tkd_peer_close unmaps it. */
+int tkd_peer_open(const void* handle, void** ptr);
+int tkd_peer_close(void* ptr);
 
 #ifdef __cplusplus
 }

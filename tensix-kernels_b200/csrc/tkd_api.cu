@@ -14,6 +14,8 @@ namespace {
 constexpr int kMaxSmem = 227 * 1024;  // dynamic shared memory a CTA may take on sm_100
 constexpr int kMaxPanels = 48 * 1024;  // panel counters at the start of the workspace (6 M columns a call)
 constexpr int kMaxUnits = 16 * 1024;   // then the top-k unit counters; 256 KB together
+constexpr int kMaxMisc = 64;           // then the call's finished-CTA counter (exchange between GPUs)
+constexpr int64_t kCounterBytes = (int64_t)(kMaxPanels + kMaxUnits + kMaxMisc) * 4;
 
 inline int cuda_err(cudaError_t e) { return e == cudaSuccess ? TKD_OK : TKD_ERR_CUDA + (int)e; }
 inline int launch_err(int e) { return e == 0 ? TKD_OK : TKD_ERR_CUDA + e; }
@@ -38,7 +40,7 @@ struct Layout {
     size_t smem;
     int64_t weight_bytes;
     // workspace map
-    int64_t off_counters, off_units, off_scratch, off_ytmp, ws_bytes;
+    int64_t off_counters, off_units, off_misc, off_scratch, off_ytmp, ws_bytes;
 };
 
 // Everything a launch needs except the device pointers into the workspace. sms 0: ask the device.
@@ -53,6 +55,8 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     if (a->topk_k && (glu || a->epilogue == TKD_EPI_OUT32 || a->epilogue == TKD_EPI_RESIDUAL)) return TKD_ERR_BAD_ARG;
     if ((a->epilogue == TKD_EPI_OUT32) != (a->out_dtype == TKD_DT_F32)) return TKD_ERR_BAD_ARG;
     if (a->out_dtype != TKD_DT_F32 && a->out_dtype != TKD_DT_BF16) return TKD_ERR_BAD_ARG;
+    if (a->nranks < 0 || a->nranks > TKD_MAX_RANKS || (a->nranks > 1 && (a->rank < 0 || a->rank >= a->nranks)))
+        return TKD_ERR_BAD_ARG;
 
     TkdParams& p = L->p;
     memset(&p, 0, sizeof(p));
@@ -130,7 +134,8 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     if (panels > kMaxPanels || units > kMaxUnits) return TKD_ERR_UNSUPPORTED;
     L->off_counters = 0;
     L->off_units = (int64_t)kMaxPanels * 4;
-    L->off_scratch = (int64_t)(kMaxPanels + kMaxUnits) * 4;
+    L->off_misc = (int64_t)(kMaxPanels + kMaxUnits) * 4;
+    L->off_scratch = kCounterBytes;
     const int64_t scratch = p.nslices > 1 ? (int64_t)panels * p.nslices * 2 * p.M * TKD_PANEL_COLS * 4 : 0;
     L->off_ytmp = align_up(L->off_scratch + scratch, 256);
     p.ld_ytmp = (int64_t)panels * TKD_PANEL_COLS;
@@ -143,7 +148,11 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
 
 extern "C" {
 
-int tkd_version(void) { return 1; }
+int tkd_version(void) { return 2; }
+
+int tkd_struct_bytes(int which) {
+    return which == 0 ? (int)sizeof(TkdMatmul) : which == 1 ? (int)sizeof(TkdPlan) : which == 2 ? (int)sizeof(TkdBlock) : 0;
+}
 
 const char* tkd_error_string(int code) {
     switch (code) {
@@ -251,7 +260,7 @@ static int run_matmul(const TkdMatmul* a, void* workspace, uint64_t workspace_by
     if (a->epilogue == TKD_EPI_OUT32 && a->residual && a->residual_dtype != TKD_DT_F32) return TKD_ERR_BAD_ARG;
     if (a->epilogue != TKD_EPI_RESIDUAL && a->epilogue != TKD_EPI_OUT32 && a->residual) return TKD_ERR_BAD_ARG;
     if (a->topk_k && !a->records) return TKD_ERR_BAD_ARG;
-    if (L.ws_bytes > 0 && (!workspace || workspace_bytes < (uint64_t)L.ws_bytes)) return TKD_ERR_WORKSPACE;
+    if (!workspace || workspace_bytes < (uint64_t)L.ws_bytes) return TKD_ERR_WORKSPACE;
     if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255)) return TKD_ERR_BAD_ARG;
 
     p.x = static_cast<const uint16_t*>(a->x);
@@ -272,6 +281,20 @@ static int run_matmul(const TkdMatmul* a, void* workspace, uint64_t workspace_by
     p.scratch = reinterpret_cast<float*>(ws + L.off_scratch);
     p.ytmp = reinterpret_cast<uint16_t*>(ws + L.off_ytmp);
     p.status = a->status;
+    if (a->nranks > 1) {
+        if (!a->flags) return TKD_ERR_BAD_ARG;
+        p.npeers = a->nranks - 1;
+        p.rank = a->rank;
+        for (int q = 0; q < p.npeers; ++q) {
+            if (!a->peer_flags[q]) return TKD_ERR_BAD_ARG;
+            p.peer_out[q] = a->peer_out[q];
+            p.peer_records[q] = static_cast<uint32_t*>(a->peer_records[q]);
+            p.peer_flags[q] = a->peer_flags[q];
+        }
+        p.flags = a->flags;
+        p.grid_counter = reinterpret_cast<int*>(ws + L.off_misc);
+        p.exchange_wait = a->exchange_wait;
+    }
     return launch_err(tkd_launch_stream(p, L.grid, L.smem, static_cast<cudaStream_t>(stream)));
 }
 
@@ -319,11 +342,48 @@ int tkd_matmul_noalloc(const TkdMatmul* a, void* stream) {
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, tkd_noalloc_scratch);
         if (e != cudaSuccess) return cuda_err(e);
-        e = cudaMemsetAsync(ptr, 0, (size_t)(kMaxPanels + kMaxUnits) * 4, static_cast<cudaStream_t>(stream));
+        e = cudaMemsetAsync(ptr, 0, (size_t)kCounterBytes, static_cast<cudaStream_t>(stream));
         if (e != cudaSuccess) return cuda_err(e);
         dev_ptr[dev] = ptr;
     }
     return run_matmul(a, dev_ptr[dev], TKD_NOALLOC_SCRATCH_BYTES, stream);
 }
+
+// ---- exchange between GPUs -------------------------------------------------------------------------------------------
+
+int tkd_exchange_wait(uint32_t* flags, int nranks, int32_t* status, void* stream) {
+    if (!flags || nranks < 1 || nranks > TKD_MAX_RANKS) return TKD_ERR_BAD_ARG;
+    return launch_err(tkd_launch_exchange_wait(flags, nranks, status, static_cast<cudaStream_t>(stream)));
+}
+
+int tkd_peer_alloc(uint64_t bytes, void** ptr, void* handle) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is 64 bytes");
+    if (!bytes || !ptr || !handle) return TKD_ERR_BAD_ARG;
+    void* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, (size_t)bytes);
+    if (e != cudaSuccess) return cuda_err(e);
+    e = cudaMemset(d, 0, (size_t)bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, d);
+    if (e != cudaSuccess) {
+        (void)cudaFree(d);
+        return cuda_err(e);
+    }
+    memcpy(handle, &h, sizeof(h));
+    *ptr = d;
+    return TKD_OK;
+}
+
+int tkd_peer_free(void* ptr) { return ptr ? cuda_err(cudaFree(ptr)) : TKD_ERR_BAD_ARG; }
+
+int tkd_peer_open(const void* handle, void** ptr) {
+    if (!handle || !ptr) return TKD_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    return cuda_err(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+
+int tkd_peer_close(void* ptr) { return ptr ? cuda_err(cudaIpcCloseMemHandle(ptr)) : TKD_ERR_BAD_ARG; }
 
 }  // extern "C"

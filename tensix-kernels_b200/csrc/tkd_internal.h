@@ -67,9 +67,19 @@ struct TkdParams {
     float* scratch;
     int* counters;
     int* status;
+    // exchange with the other GPUs of a column-sharded weight: the output stage repeats its stores of y and of the
+    // records into the other ranks' buffers; npeers == 0: none
+    int npeers, rank;
+    void* peer_out[7];
+    uint32_t* peer_records[7];
+    uint32_t* peer_flags[7];
+    uint32_t* flags;     // this rank's flag words
+    int* grid_counter;   // CTAs of this call that have finished their output (returns to zero)
+    int exchange_wait;
     // shared-memory map (bytes from the start of dynamic shared memory)
     int off_pbuf, off_tbuf, off_ring;
     int stage_bytes;
 };
 
 int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
+int tkd_launch_exchange_wait(uint32_t* flags, int nranks, int* status, cudaStream_t st);

@@ -118,6 +118,26 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Spin (bounded: about a second) until flags[r] has reached `seq` (compared modulo 2^32) for every r < nranks; false
+// when it gave up.
+__device__ __noinline__ bool flags_wait(const uint32_t* flags, int nranks, uint32_t seq) {
+    for (int r = 0; r < nranks; ++r) {
+        int rounds = 0;
+        while ((int32_t)(ld_acquire_sys(flags + r) - seq) < 0) {
+            if (++rounds > (1 << 22)) return false;
+            __nanosleep(rounds < 64 ? 20 : 200);
+        }
+    }
+    return true;
+}
 __device__ __forceinline__ void bar_output_warps() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
@@ -691,6 +711,10 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
                             float v = tot[m];
                             if (p.res_dt == TKD_DT_F32) v += static_cast<const float*>(p.res)[(size_t)m * p.ldr + ocol];
                             y32[(size_t)m * p.ldo + ocol] = v;
+#pragma unroll
+                            for (int q = 0; q < 7; ++q)
+                                if (q < p.npeers && p.peer_out[q])
+                                    static_cast<float*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = v;
                         }
                 } else {
 #pragma unroll
@@ -700,7 +724,13 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
                             if (p.epi == TKD_EPI_RESIDUAL)
                                 v += bf16_bits_to_f32(static_cast<const uint16_t*>(p.res)[(size_t)m * p.ldr + ocol]);
                             const uint16_t b = f32_to_bf16_bits(v);
-                            if (store) y16[(size_t)m * p.ldo + ocol] = b;
+                            if (store) {
+                                y16[(size_t)m * p.ldo + ocol] = b;
+#pragma unroll
+                                for (int q = 0; q < 7; ++q)
+                                    if (q < p.npeers && p.peer_out[q])
+                                        static_cast<uint16_t*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = b;
+                            }
                             if (p.topk_k && !p.write_y && m < p.topk_rows) p.ytmp[(size_t)m * p.ld_ytmp + n] = b;
                         }
                 }
@@ -730,7 +760,8 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
             const int64_t ldy = p.write_y ? p.ldo : p.ld_ytmp;
             const int col0 = unit * p.topk_unit;  // the unit's first column (call-relative)
             uint32_t* red = reinterpret_cast<uint32_t*>(tbuf);
-            uint32_t* rec = p.records + (size_t)(p.topk_slot0 + unit) * 2 * p.topk_rows * p.topk_k;
+            const size_t rec_at = (size_t)(p.topk_slot0 + unit) * 2 * p.topk_rows * p.topk_k;
+            uint32_t* rec = p.records + rec_at;
             for (int r = 0; r < p.topk_rows; ++r) {
                 // candidates: (key << 16 | 0xFFFF - position in unit) orders by key descending, then column ascending;
                 // this thread's 16 (a unit holds at most 2048 columns) are loaded once
@@ -757,14 +788,56 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
                     bar_output_warps();
                     bound = best;  // (0: nothing left, the remaining slots stay empty)
                     if (et == 0) {
-                        rec[r * p.topk_k + q] = best >> 16;
-                        rec[(p.topk_rows + r) * p.topk_k + q] =
-                            best ? p.topk_base + (uint32_t)col0 + (0xFFFFu - (best & 0xFFFFu)) : 0xFFFFFFFFu;
+                        const uint32_t key = best >> 16;
+                        const uint32_t idx = best ? p.topk_base + (uint32_t)col0 + (0xFFFFu - (best & 0xFFFFu)) : 0xFFFFFFFFu;
+                        const int at_k = r * p.topk_k + q, at_i = (p.topk_rows + r) * p.topk_k + q;
+                        rec[at_k] = key;
+                        rec[at_i] = idx;
+#pragma unroll
+                        for (int pq = 0; pq < 7; ++pq)
+                            if (pq < p.npeers && p.peer_records[pq]) {
+                                p.peer_records[pq][rec_at + at_k] = key;
+                                p.peer_records[pq][rec_at + at_i] = idx;
+                            }
                     }
                 }
             }
         }
         if (ow == 0) PROF_TIME(2);
+        if (p.npeers) {
+            // Exchange: every output warp counts itself in once its stores are ordered GPU-wide (a cheap fence). The
+            // warp that counts last orders all of them system-wide with the call's ONE system fence (system fences
+            // serialise across the GPU: one per warp cost this kernel a third of its run), numbers the call and writes
+            // that number to this rank's word on every rank. (No CTA barrier: the warps may have left the loop at
+            // different points.)
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence();
+                const int old = atomicAdd(p.grid_counter, 1);
+                if (old + 1 == 4 * (int)gridDim.x) {
+                    *p.grid_counter = 0;
+                    const uint32_t seq = p.flags[TKD_FLAG_SEQ] + 1;
+                    p.flags[TKD_FLAG_SEQ] = seq;
+                    __threadfence_system();
+                    for (int q = 0; q < p.npeers; ++q) st_relaxed_sys(p.peer_flags[q] + p.rank, seq);
+                    st_relaxed_sys(p.flags + p.rank, seq);
+                    // (2: the call before this one, whose exchange has had this call's whole run to arrive)
+                    if (p.exchange_wait && !flags_wait(p.flags, p.npeers + 1, p.exchange_wait == 2 ? seq - 1 : seq)) {
+                        if (p.status) atomicExch(p.status, TKD_ERR_TIMEOUT);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Waits (one warp) until every rank's completed-call count in `flags` has reached this rank's own.
+__global__ void tkd_exchange_wait_kernel(uint32_t* flags, int nranks, int* status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x == 0) {
+        const uint32_t seq = ld_acquire_sys(flags + TKD_FLAG_SEQ);
+        if (!flags_wait(flags, nranks, seq) && status) atomicExch(status, TKD_ERR_TIMEOUT);
+        __threadfence_system();
     }
 }
 
@@ -806,6 +879,11 @@ int launch_fmt(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
 }
 
 }  // namespace
+
+int tkd_launch_exchange_wait(uint32_t* flags, int nranks, int* status, cudaStream_t st) {
+    tkd_exchange_wait_kernel<<<1, 32, 0, st>>>(flags, nranks, status);
+    return (int)cudaGetLastError();
+}
 
 int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
     switch (p.fmt) {

@@ -32,7 +32,12 @@ class TkdMatmul(ctypes.Structure):
         ("records", c_vp), ("topk_k", c_i32), ("topk_rows", c_i32), ("topk_unit", c_i32), ("topk_slot0", c_i32),
         ("topk_write_y", c_i32), ("topk_base", c_u32), ("topk_n", c_i64), ("workspace", c_vp), ("workspace_bytes", c_u64),
         ("status", c_vp), ("ks", c_i32), ("max_ctas", c_i32),
+        ("nranks", c_i32), ("rank", c_i32), ("peer_out", c_vp * 7), ("peer_records", c_vp * 7), ("peer_flags", c_vp * 7),
+        ("flags", c_vp), ("exchange_wait", c_i32), ("pad_", c_i32),
     ]
+
+
+MAX_RANKS, FLAG_SEQ, FLAG_WORDS = 8, 8, 16
 
 
 class TkdPlan(ctypes.Structure):
@@ -44,6 +49,7 @@ class TkdPlan(ctypes.Structure):
 
 SYMBOLS = {
     "tkd_version": (c_i32, []),
+    "tkd_struct_bytes": (c_i32, [c_i32]),
     "tkd_error_string": (ctypes.c_char_p, [c_i32]),
     "tkd_padded_cols": (c_i64, [c_i64]),
     "tkd_packed_bytes": (c_i64, [c_i32, c_i64, c_i64]),
@@ -55,6 +61,11 @@ SYMBOLS = {
     "tkd_matmul": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp]),
     "tkd_matmul_host": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp, c_vp, c_vp]),
     "tkd_matmul_noalloc": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp]),
+    "tkd_exchange_wait": (c_i32, [c_vp, c_i32, c_vp, c_vp]),
+    "tkd_peer_alloc": (c_i32, [c_u64, ctypes.POINTER(c_vp), c_vp]),
+    "tkd_peer_free": (c_i32, [c_vp]),
+    "tkd_peer_open": (c_i32, [c_vp, ctypes.POINTER(c_vp)]),
+    "tkd_peer_close": (c_i32, [c_vp]),
 }
 
 _lib = None
@@ -73,6 +84,10 @@ def lib():
         for name, (res, args) in SYMBOLS.items():
             fn = getattr(L, name)
             fn.restype, fn.argtypes = res, args
+        for which, mirror in enumerate((TkdMatmul, TkdPlan, TkdBlock)):
+            if L.tkd_struct_bytes(which) != ctypes.sizeof(mirror):
+                raise RuntimeError(f"dense_reader: {LIB_PATH} was built from another include/tkd.h ({mirror.__name__}"
+                                   f" is {L.tkd_struct_bytes(which)} bytes there, {ctypes.sizeof(mirror)} here): rebuild")
         _lib = L
     return _lib
 

@@ -75,7 +75,7 @@ MAX_CTAS = None
 
 _TENSIX_OPTS = {"cores_per_bank", "split", "rows", "xs", "kb", "kw", "sbw", "noscale", "glu2", "budget", "mt"}
 _OPTS = _TENSIX_OPTS | {"glu", "glu_act", "residual", "residual_mode", "out32", "blocks", "max_banks", "col_scales", "ks",
-                        "max_ctas"}
+                        "max_ctas", "exchange"}
 
 _CALLS = {}      # whole calls by the identity of their arguments (a hit goes straight to the library)
 _CALLS_MAX = 256
@@ -366,7 +366,9 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     GLU or top-k): y = bf16(x @ w + residual), out may be the residual itself; residual_mode "epilogue" | "preload" (one
     sum here: the residual is added to the finished K sum in fp32); out32: y in float32. The Tensix options
     (cores_per_bank, split, rows, xs, kb, kw, sbw, full_sync, fidelity, memory_config) are accepted and steer nothing.
-    Extensions: col_scales=(gate scales, up scales) float32 [N] each with w_up (or one float32 vector in the
+    Extensions: exchange= (a sharded.Exchange): the output and the records, where they lie inside the exchange's
+    buffer, are also written to every other rank's buffer, and the call completes when all ranks' have arrived.
+    col_scales=(gate scales, up scales) float32 [N] each with w_up (or one float32 vector in the
     interleaved weight's column order with glu); a float32 residual with out32 (y = x @ w + residual in float32).
 
     A block list in place of w, [(w | (gate, up), col0_tiles), ...]: one launch over two to four weights of one K and
@@ -414,6 +416,7 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     assert res_mode in ("epilogue", "preload"), res_mode
     residual = opts.pop("residual", None)
     col_scales = opts.pop("col_scales", None)
+    exchange = opts.pop("exchange", None)
     out32 = bool(opts.get("out32"))
     assert not (out32 and topk is not None), "dense_reader: out32 without top-k"
     assert not (out32 and out is not None and out.dtype != ttnn.float32), out.dtype
@@ -448,9 +451,11 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
         )
         assert ext or residual.dtype == ttnn.bfloat16, residual.dtype
         assert residual.memory_config().memory_layout == ttnn.TensorMemoryLayout.INTERLEAVED
-        assert tuple(residual.padded_shape) == (1, 1, -(-M // TILE) * TILE, -(-N // TILE) * TILE), (residual.shape, N)
-        # (the reference takes a fresh output or the residual itself; any other preallocated out is as safe here)
-        assert col0 == 0, "dense_reader: residual with a fresh output or in place"
+        wide = out is not None and tuple(residual.padded_shape) == tuple(out.padded_shape)
+        assert wide or tuple(residual.padded_shape) == (1, 1, -(-M // TILE) * TILE, -(-N // TILE) * TILE), (residual.shape, N)
+        # (the reference takes a fresh output or the residual itself; any other preallocated out is as safe here, and
+        # with col0 the residual is as wide as out: it is read at the output's own columns)
+        assert col0 == 0 or wide, "dense_reader: residual with a fresh output or in place"
     blocks_all = ((w, w_up, col0), *segs)
     ends = [(c0, -(-(g.shape[-1] // 2 if glu and u is None else g.shape[-1]) // TILE)) for g, u, c0 in blocks_all]
     if segs:
@@ -477,7 +482,7 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
         _block_kw_check(device, x, blocks_all, full_sync, opts, slices)
     for m0, _ in slices:
         launched.append(_launch(x, blocks_all, scale, col_scales, y, m0, min(32, M - m0), topk, act, residual, glu,
-                                out32, opts.get("ks") or KS or 0, opts.get("max_ctas") or MAX_CTAS or 0))
+                                out32, opts.get("ks") or KS or 0, opts.get("max_ctas") or MAX_CTAS or 0, exchange))
     if call_key is not None and out is not None:
         # (only calls that write into a given output: a fresh output per call cannot be replayed)
         if len(_CALLS) >= _CALLS_MAX:
@@ -541,7 +546,7 @@ def _replay(hit):
     return True
 
 
-def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, out32, ks=0, max_ctas=0):
+def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, out32, ks=0, max_ctas=0, exchange=None):
     """One launch of the stream kernel: rows m0 .. m0 + m of x into the same rows of y. The descriptor is cached by
     everything that shapes it; a hit only rewrites the activation, output and residual addresses.
     (linear.py:828-1070)"""
@@ -574,7 +579,7 @@ def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, o
         key = (
             tuple((g.t.data_ptr(), u.t.data_ptr() if u is not None else 0, g.k, g.n, g.dtype, c0) for g, u, c0 in entries),
             m, tuple(xt.shape), tuple(yt.shape), epi, act, sc.data_ptr() if sc is not None else 0,
-            sc_up.data_ptr() if sc_up is not None else 0, scale_dt, res_dt, tk, ks, max_ctas, device.id,
+            sc_up.data_ptr() if sc_up is not None else 0, scale_dt, res_dt, tk, ks, max_ctas, device.id, id(exchange),
         )
     hit = _LAUNCHES.get(key) if key is not None else None
     if hit is None:
@@ -582,7 +587,7 @@ def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, o
         a = _describe(xt, m, blocks, epi, act, sc, sc_up, scale_dt, rt, res_dt, yt, topk, ks, max_ctas)
         need = ctypes.c_uint64(0)
         _tkd.check(_tkd.lib().tkd_matmul_workspace(ctypes.byref(a), ctypes.byref(need)), "tkd_matmul_workspace")
-        hit = (a, need.value, (sc, sc_up))
+        hit = (a, need.value, (sc, sc_up, exchange))
         if key is not None:
             _LAUNCHES[key] = hit
     a, need, _ = hit
@@ -593,6 +598,8 @@ def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, o
     a.x = xt.data_ptr() + m0 * xt.shape[-1] * esz_x
     a.out = yt.data_ptr() + m0 * yt.shape[-1] * esz_y
     a.residual = rt.data_ptr() + m0 * rt.shape[-1] * rt.element_size() if rt is not None else None
+    if exchange is not None:
+        exchange.fill(a, a.out, a.records)
     with torch.cuda.device(device.torch):
         _tkd.check(_tkd.lib().tkd_matmul(ctypes.byref(a), torch.cuda.current_stream().cuda_stream), "tkd_matmul")
     done = _tkd.TkdMatmul()
