@@ -242,6 +242,16 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="for a profiler: warm-up, then `steps` plain launches (no graph, no e2e, no CPU leg, no JSON line)")
     args = ap.parse_args()
+    # stdout carries the one JSON line and nothing else: whatever libraries print there (NCCL's version banner) goes to
+    # stderr; emit() puts the line on the real stdout
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line):
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(line) + "\n").encode())
+
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -263,7 +273,7 @@ def main():
             "note": "the reference's torch CPU path (dense_reader/linear.py:166-169) as restated by the oracle; its device"
                     " path (ttnn on a Tensix simulator) cannot run here",
         }
-        print(json.dumps(line))
+        emit(line)
         return 0
 
     from common import ttnn_like as ttnn
@@ -520,7 +530,7 @@ def main():
     if world == 1 and not args.no_cpu:
         val, info = cpu_reference_arm(args.workload, m, 10_000, 2, budget_s=15.0)
         line["cpu_baseline"] = {"value": val, "unit": "GB/s", **info}
-    print(json.dumps(line), flush=True)
+    emit(line)
     finish(world)
     return 0
 

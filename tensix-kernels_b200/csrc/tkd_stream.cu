@@ -7,7 +7,7 @@
 // (dense_reader/linear.py:187-382).
 //
 // One persistent CTA per SM, three kinds of warps, coupled by mbarriers only:
-//   warp 0        producer (one lane): one 1-D bulk copy (TMA, no multicast) per stage of the shared-memory ring; a
+//   warp 0        producer (one lane): one 1-D bulk copy (TMA) per stage of the shared-memory ring; a
 //                 stage is one chunk of one panel (128 columns x 256 or 512 k), contiguous in the stream. (A bulk copy costs
 //                 the issuing SM about 140 cycles whatever its size, so stages are single copies of 17-35 KB.)
 //   warps 1-16    streaming warps: warp (group g, half h) multiplies the 16 columns of group g by every other
