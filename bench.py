@@ -160,10 +160,14 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
         y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
         spec = {"r": r, "k": 8, "rows": 1, "slot0": 0, "base": 0, "n": n, "write_y": False}
 
-        def step(i, x_t=tx, y_t=y, spec_t=spec, **kw):
+        top32 = linear.topk_result(device, 1, 1, 32)
+
+        def step(i, x_t=tx, y_t=y, spec_t=spec, merge=True, **kw):
+            # the records of every 2048-column unit, then the best 32 of them all (with an exchange: of all ranks')
             linear.matmul(x_t, sets[i % copies][0], None, topk=spec_t, out=y_t, **kw)
-            return spec_t["r"]
+            return linear.topk_merge(spec_t["r"], 1, 8, 32, out=top32) if merge else spec_t["r"]
         weights = 1
+        extra.update(launches=2, spec=spec, top32=top32)
     else:
         y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
 
@@ -309,7 +313,7 @@ def main():
         config["columns_per_rank"] = n_loc
     case = build_gpu_case(args.workload, m, device, copies, seed0=100 + 1000 * rank, n_cols=n_loc)
     step = case["step"]
-    launches_per_step = 1
+    launches_per_step = case.get("launches", 1)
 
     def barrier():
         torch.cuda.synchronize()
@@ -336,9 +340,12 @@ def main():
             ex.wait_all(linear.status_word(device))
 
         if args.workload == "c5":
-            r0 = case["step"](0)
-            recs = [ex.tensor([1, 1, linear.topk_units(n_total), r0.shape[-1]], r0.dtype) for _ in range(nbuf)]
-            specs = [{"r": r, "k": 8, "rows": 1, "slot0": col_start // 2048, "base": col_start, "n": n_loc, "write_y": False}
+            r0 = case["spec"]["r"]
+            strong = args.scaling == "strong"
+            units_all = linear.topk_units(n_total) if strong else world * linear.topk_units(n_loc)
+            slot0 = col_start // 2048 if strong else rank * linear.topk_units(n_loc)
+            recs = [ex.tensor([1, 1, units_all, r0.shape[-1]], r0.dtype) for _ in range(nbuf)]
+            specs = [{"r": r, "k": 8, "rows": 1, "slot0": slot0, "base": col_start, "n": n_loc, "write_y": False}
                      for r in recs]
 
             def step(i):
@@ -376,13 +383,15 @@ def main():
             torch.cuda.current_stream().wait_stream(side)
     elif world > 1:
         exchange_note = "NCCL all-gather of every rank's top-k records per step, inside the timed region"
-        rbuf = torch.empty(world * case["step"](0).t.numel(), dtype=torch.int32, device=device.torch)
+        r0 = case["spec"]["r"]
+        rbuf = ttnn.from_torch(torch.zeros(1, 1, world * r0.shape[-2], r0.shape[-1], dtype=torch.int32), dtype=ttnn.uint32,
+                               layout=ttnn.ROW_MAJOR_LAYOUT, device=device)
         plain_step5 = step
 
         def step(i):  # noqa: F811
-            r = plain_step5(i)
-            dist.all_gather_into_tensor(rbuf, r.t.reshape(-1))
-            return r
+            r = plain_step5(i, merge=False)
+            dist.all_gather_into_tensor(rbuf.t.reshape(-1), r.t.reshape(-1))
+            return linear.topk_merge(rbuf, 1, 8, 32, out=case["top32"])
 
     # ---- device-resident: the K steps as one CUDA graph ----
     for i in range(warmup):
@@ -524,7 +533,7 @@ def main():
                 "h2d_bytes_per_step": x_pin.numel() * 2, "d2h_bytes_per_step": y_pin.numel() * y_pin.element_size()},
         "gpu_launches": steps * reps * launches_per_step,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": TRAFFIC.get(args.workload), "peak_source": peak_src,
+                     "traffic": TRAFFIC.get(args.workload) if m == 1 else None, "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": case["abytes"]},
     }
     if world == 1 and not args.no_cpu:
@@ -545,8 +554,8 @@ def finish(world):
 
 
 # DRAM bytes per launch of tkd_stream_kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum), per
-# workload (profiles/tkd_stream_kernel_config2_bfp4_m1.md); None where no capture of the workload is summarised there.
-TRAFFIC = {"c2": 66_985_984}
+# workload at M = 1 (the summaries under profiles/); None where no capture of the workload is summarised there.
+TRAFFIC = {"c2": 68_071_168, "c3": 62_815_232, "c5": 667_897_344}
 
 if __name__ == "__main__":
     sys.exit(main())

@@ -168,6 +168,13 @@ int tkd_matmul_host(const TkdMatmul* a, const void* x_host, void* out_host, void
 #define TKD_NOALLOC_SCRATCH_BYTES (8u << 20)
 int tkd_matmul_noalloc(const TkdMatmul* a, void* stream);
 
+/* The best `top` candidates of every row among `nrecords` top-k records (the record layout above: keys[rows][k] then
+ * indices[rows][k]), key descending and index ascending among equal keys; out is one record of the same layout with
+ * `top` in place of k (slots beyond the candidates there are: key 0, index 0xFFFFFFFF). Stands in for the `vh.topk(top)`
+ * over the decoded records in the reference's LM head (lm_head_topk/lmhead.py:212-239, collect), whose records are one
+ * device's; here they may be every rank's, gathered. */
+int tkd_topk_merge(const uint32_t* records, int nrecords, int rows, int k, int top, uint32_t* out, void* stream);
+
 /* --- exchange between GPUs: stands in for the all-gather of the column shards' outputs (the reference runs on one
  * device and has none; its multi-device callers would gather [M, N_local] outputs or top-k records). ---------------- */
 

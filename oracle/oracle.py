@@ -209,6 +209,22 @@ def topk_scan_ref(y_row_bits, c0, c1, n, k, base):
     return keys, idx
 
 
+def topk_merge_ref(words, rows, k, top):
+    """The best `top` of every row among the records in `words` (uint32 [records, 2, rows, k]): key descending, index
+    ascending among equal keys, empty slots (key 0) never chosen; one record of rows x top, empty beyond the candidates
+    (key 0, index 0xFFFFFFFF). The definite-order form of the `vh.topk(top)` of lm_head_topk/lmhead.py:212-239."""
+    words = np.asarray(words, np.uint32).reshape(-1, 2, rows, k)
+    out = np.zeros((2, rows, top), np.uint32)
+    out[1] = 0xFFFFFFFF
+    for r in range(rows):
+        keys, idx = words[:, 0, r].reshape(-1).astype(np.int64), words[:, 1, r].reshape(-1).astype(np.int64)
+        live = keys != 0
+        keys, idx = keys[live], idx[live]
+        order = np.lexsort((idx, -keys))[:top]
+        out[0, r, : order.size], out[1, r, : order.size] = keys[order], idx[order]
+    return out
+
+
 def records_host(t, rows, k):
     """Decode a records tensor as linear.py:753-768 does: (values float32 [rows, records * k], indices int64 [rows,
     records * k]); an empty slot (key 0) gives -inf and -1. Written over numpy words here."""

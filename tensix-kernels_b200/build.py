@@ -11,7 +11,7 @@ import sys
 from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent / "csrc"
-SOURCES = ["tkd_api.cu", "tkd_pack.cu", "tkd_stream.cu"]
+SOURCES = ["tkd_api.cu", "tkd_pack.cu", "tkd_stream.cu", "tkd_topk.cu"]
 LIB = CSRC / "libtkd.so"
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-shared",

@@ -349,6 +349,13 @@ int tkd_matmul_noalloc(const TkdMatmul* a, void* stream) {
     return run_matmul(a, dev_ptr[dev], TKD_NOALLOC_SCRATCH_BYTES, stream);
 }
 
+int tkd_topk_merge(const uint32_t* records, int nrecords, int rows, int k, int top, uint32_t* out, void* stream) {
+    if (!records || !out || nrecords < 1 || rows < 1 || rows > 16 || k < 1 || rows * k > 64 || top < 1 || top > 1024)
+        return TKD_ERR_BAD_ARG;
+    if ((int64_t)nrecords * k > (1 << 24)) return TKD_ERR_BAD_ARG;
+    return launch_err(tkd_launch_topk_merge(records, nrecords, rows, k, top, out, static_cast<cudaStream_t>(stream)));
+}
+
 // ---- exchange between GPUs -------------------------------------------------------------------------------------------
 
 int tkd_exchange_wait(uint32_t* flags, int nranks, int32_t* status, void* stream) {

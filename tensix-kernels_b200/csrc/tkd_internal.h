@@ -82,4 +82,6 @@ struct TkdParams {
 };
 
 int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
+bool tkd_pdl_enabled();  // programmatic dependent launch (off with TKD_NO_PDL=1 in the environment)
+int tkd_launch_topk_merge(const uint32_t* records, int nrec, int rows, int k, int top, uint32_t* out, cudaStream_t st);
 int tkd_launch_exchange_wait(uint32_t* flags, int nranks, int* status, cudaStream_t st);

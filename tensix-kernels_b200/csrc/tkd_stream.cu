@@ -54,7 +54,7 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 
 #include <stdlib.h>
 // TKD_NO_PDL=1 in the environment turns programmatic dependent launch off (for comparisons).
-static bool tkd_pdl_enabled() {
+bool tkd_pdl_enabled() {
     static const bool on = [] { const char* v = getenv("TKD_NO_PDL"); return !(v && v[0] == '1'); }();
     return on;
 }

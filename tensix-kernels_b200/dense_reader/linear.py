@@ -643,6 +643,22 @@ def topk_result(device, records, rows, k):
                            layout=ttnn.ROW_MAJOR_LAYOUT, device=device, memory_config=ttnn.DRAM_MEMORY_CONFIG)
 
 
+def topk_merge(records, rows, k, top, out=None):
+    """The best `top` candidates of every row among all the records of a result tensor (topk_result's layout; any
+    number of records, e.g. every rank's after an exchange), on the device: value descending, lower index first among
+    equal values. Returns a result tensor of one record of rows x top (topk_records / records_host decode it); out: a
+    tensor to write into. The counterpart of `vh.topk(top)` in the reference's collect (lm_head_topk/lmhead.py:212-239),
+    with the tie order made definite."""
+    device = records.device()
+    nrec = _raw(records).numel() * _raw(records).element_size() // (8 * rows * k)
+    if out is None:
+        out = topk_result(device, 1, rows, top)
+    with torch.cuda.device(device.torch):
+        _tkd.check(_tkd.lib().tkd_topk_merge(_raw(records).data_ptr(), nrec, rows, k, top, _raw(out).data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream), "tkd_topk_merge")
+    return out
+
+
 def topk_units(n):
     """Records a call over n output columns writes: one per TOPK_UNIT columns."""
     return -(-(-(-n // 128) * 128) // TOPK_UNIT)

@@ -184,6 +184,23 @@ def test_topk_indices_exact(device):
     linear.check_status(device)
 
 
+@pytest.mark.parametrize("nrec,rows,k,top", [(75, 1, 8, 32), (7, 4, 8, 32), (300, 2, 16, 64), (3, 1, 4, 32)])
+def test_topk_merge_exact(device, nrec, rows, k, top):
+    """The device merge of records (any rank's, gathered) equals the oracle's: key descending, lower index first among
+    the many equal keys, empty slots skipped, fewer candidates than `top` leave empty slots."""
+    g = np.random.default_rng(nrec * 31 + rows)
+    words = np.zeros((nrec, 2, rows, k), np.uint32)
+    words[:, 0] = g.integers(0x8000, 0x8040, size=(nrec, rows, k))  # 64 distinct keys: heavy ties
+    words[:, 0][g.random((nrec, rows, k)) < 0.2] = 0                 # empty slots
+    words[:, 1] = g.permutation(nrec * rows * k).reshape(nrec, rows, k).astype(np.uint32) + 1000
+    words[:, 1][words[:, 0] == 0] = 0xFFFFFFFF
+    r = linear.topk_result(device, nrec, rows, k)
+    r.t.copy_(torch.from_numpy(words.view(np.int32)).reshape(r.t.shape))
+    got = ttnn.to_torch(linear.topk_merge(r, rows, k, top)).numpy().view(np.uint32).reshape(2, rows, top)
+    assert np.array_equal(got, orc.topk_merge_ref(words, rows, k, top))
+    linear.check_status(device)
+
+
 def test_full_size_properties(device):
     """At BASELINE's full sizes (config 2's gate weight, 14336 x 4096 bfloat4_b; config 3's 4096 x 14336 bfloat8_b)
     the oracle is too slow for every column; size-independent properties stand in: linearity in x (power-of-two
