@@ -175,6 +175,23 @@ int tkd_matmul_noalloc(const TkdMatmul* a, void* stream);
  * device's; here they may be every rank's, gathered. */
 int tkd_topk_merge(const uint32_t* records, int nrecords, int rows, int k, int top, uint32_t* out, void* stream);
 
+/* The LM head's exact rescore and pick on the device: stands in for head_pick.pick (lm_head_topk/head_pick.py:101-220;
+ * kernels/head_pick_reader.cpp, head_pick_compute.cpp, head_pick_writer.cpp). Per row r < rows: the best `top` (<= 32)
+ * slots of the records in order (record by record, slot by slot; an equal key keeps the earlier; key 0 or an index at
+ * or past `vocab`: empty), their logits recomputed from bf16 x [rows, ldx] and the bf16 head rows [>= vocab, ld_head]
+ * (float32 sums; rounded to bf16 with round_bf16), and the pick: the largest logit, a NaN counting as the largest, -0
+ * equal to +0, the lowest index among equals. out: 32 uint32 words a row: [token, the first candidate by the device's
+ * own logit, candidates held, 0 ...]; no candidate: [0, 0xFFFFFFFF, 0]. ids_out (or NULL): row 0's token, one word. */
+int tkd_head_pick(const uint32_t* records, int nrecords, int rows, int k, int top, uint32_t vocab, const void* x,
+                  int64_t ldx, int dim, const void* head_rows, int64_t ld_head, int round_bf16, uint32_t* out,
+                  uint32_t* ids_out, void* stream);
+/* The records-only pick: stands in for head_pick.pick_records (lm_head_topk/head_pick.py:243-335;
+ * kernels/head_pick_records.cpp). Per row the first slot, in the records' order, of the largest key (a NaN of either
+ * sign above every key, -0 equal to +0); its index (below `vocab`) is the token, or token_map[index] with a map
+ * (uint32 [>= vocab]). out as tkd_head_pick's, with the count of all valid slots. */
+int tkd_head_pick_records(const uint32_t* records, int nrecords, int rows, int k, uint32_t vocab, const uint32_t* token_map,
+                          uint32_t* out, uint32_t* ids_out, void* stream);
+
 /* --- exchange between GPUs: stands in for the all-gather of the column shards' outputs (the reference runs on one
  * device and has none; its multi-device callers would gather [M, N_local] outputs or top-k records). ---------------- */
 

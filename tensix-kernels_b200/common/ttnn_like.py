@@ -262,6 +262,12 @@ def reshape(t, shape):
     return Tensor(t.t.reshape(list(shape)), t.dtype, t.layout, t._device, t._mc)
 
 
+def to_memory_config(t, memory_config):
+    """A copy of t carrying another memory config (there is one kind of device memory here: the copy is what a caller
+    that deallocates the result expects)."""
+    return Tensor(t.t.clone(), t.dtype, t.layout, t._device, memory_config)
+
+
 def sharded_to_interleaved(t, memory_config=None):
     return Tensor(t.t, t.dtype, t.layout, t._device, memory_config or DRAM_MEMORY_CONFIG)
 

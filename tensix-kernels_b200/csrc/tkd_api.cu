@@ -356,6 +356,27 @@ int tkd_topk_merge(const uint32_t* records, int nrecords, int rows, int k, int t
     return launch_err(tkd_launch_topk_merge(records, nrecords, rows, k, top, out, static_cast<cudaStream_t>(stream)));
 }
 
+int tkd_head_pick(const uint32_t* records, int nrecords, int rows, int k, int top, uint32_t vocab, const void* x,
+                  int64_t ldx, int dim, const void* head_rows, int64_t ld_head, int round_bf16, uint32_t* out,
+                  uint32_t* ids_out, void* stream) {
+    if (!records || !out || !x || !head_rows || nrecords < 1 || rows < 1 || rows > 32 || k < 1 || top < 1 || top > 32)
+        return TKD_ERR_BAD_ARG;
+    if (dim < 8 || dim % 8 || ldx < dim || ldx % 8 || ld_head < dim || ld_head % 8 || vocab < 1) return TKD_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(head_rows)) & 15) return TKD_ERR_BAD_ARG;
+    if ((int64_t)nrecords * k > (1 << 24)) return TKD_ERR_BAD_ARG;
+    return launch_err(tkd_launch_head_pick(records, nrecords, rows, k, top, vocab, static_cast<const uint16_t*>(x), ldx, dim,
+                                           static_cast<const uint16_t*>(head_rows), ld_head, round_bf16, out, ids_out,
+                                           static_cast<cudaStream_t>(stream)));
+}
+
+int tkd_head_pick_records(const uint32_t* records, int nrecords, int rows, int k, uint32_t vocab, const uint32_t* token_map,
+                          uint32_t* out, uint32_t* ids_out, void* stream) {
+    if (!records || !out || nrecords < 1 || rows < 1 || rows > 32 || k < 1 || vocab < 1) return TKD_ERR_BAD_ARG;
+    if ((int64_t)nrecords * k > (1 << 24)) return TKD_ERR_BAD_ARG;
+    return launch_err(tkd_launch_head_pick_records(records, nrecords, rows, k, vocab, token_map, out, ids_out,
+                                                   static_cast<cudaStream_t>(stream)));
+}
+
 // ---- exchange between GPUs -------------------------------------------------------------------------------------------
 
 int tkd_exchange_wait(uint32_t* flags, int nranks, int32_t* status, void* stream) {

@@ -84,4 +84,9 @@ struct TkdParams {
 int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
 bool tkd_pdl_enabled();  // programmatic dependent launch (off with TKD_NO_PDL=1 in the environment)
 int tkd_launch_topk_merge(const uint32_t* records, int nrec, int rows, int k, int top, uint32_t* out, cudaStream_t st);
+int tkd_launch_head_pick(const uint32_t* records, int nrec, int rows, int k, int top, uint32_t vocab, const uint16_t* x,
+                         int64_t ldx, int dim, const uint16_t* head, int64_t ld_head, int round, uint32_t* out,
+                         uint32_t* ids_out, cudaStream_t st);
+int tkd_launch_head_pick_records(const uint32_t* records, int nrec, int rows, int k, uint32_t vocab, const uint32_t* tmap,
+                                 uint32_t* out, uint32_t* ids_out, cudaStream_t st);
 int tkd_launch_exchange_wait(uint32_t* flags, int nranks, int* status, cudaStream_t st);

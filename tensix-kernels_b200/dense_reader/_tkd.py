@@ -62,6 +62,8 @@ SYMBOLS = {
     "tkd_matmul_host": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp, c_vp, c_vp]),
     "tkd_matmul_noalloc": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp]),
     "tkd_topk_merge": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp]),
+    "tkd_head_pick": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_u32, c_vp, c_i64, c_i32, c_vp, c_i64, c_i32, c_vp, c_vp, c_vp]),
+    "tkd_head_pick_records": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_u32, c_vp, c_vp, c_vp, c_vp]),
     "tkd_exchange_wait": (c_i32, [c_vp, c_i32, c_vp, c_vp]),
     "tkd_peer_alloc": (c_i32, [c_u64, ctypes.POINTER(c_vp), c_vp]),
     "tkd_peer_free": (c_i32, [c_vp]),
