@@ -201,6 +201,27 @@ def test_topk_merge_exact(device, nrec, rows, k, top):
     linear.check_status(device)
 
 
+def test_packed_weight_cache_round_trip(device, tmp_path):
+    """A weight loaded from its cache directory is the packed weight bit for bit (stream, side array, scales), gives
+    the same outputs, and a cache of other weights is refused."""
+    from dense_reader import cache
+
+    g = torch.Generator().manual_seed(77)
+    w = torch.randn(384, 256, generator=g) * 0.02
+    for fmt, col_scale in ((ttnn.bfloat8_b, True), (ttnn.bfloat4_b, False), (ttnn.bfloat16, False)):
+        path = tmp_path / f"w_{fmt}"
+        tw, ts = cache.native_weight_cached(device, w, fmt, path, col_scale=col_scale)   # packs and writes
+        tw2, ts2 = cache.native_weight_cached(device, w, fmt, path, col_scale=col_scale)  # loads
+        assert torch.equal(tw.t, tw2.t) and (tw.emax is None or torch.equal(tw.emax, tw2.emax))
+        assert torch.equal(ts.t, ts2.t)
+        tx = dev_x(device, torch.randn(3, 256, generator=g))
+        assert torch.equal(host(linear.matmul(tx, tw, ts)), host(linear.matmul(tx, tw2, ts2)))
+        with pytest.raises(cache.PackCacheMismatch):
+            cache.native_weight_cached(device, w * 2, fmt, path, col_scale=col_scale)
+        tw3, _ = cache.native_weight_cached(device, w * 2, fmt, path, col_scale=col_scale, rebuild=True)
+        assert not torch.equal(tw3.t, tw.t)
+
+
 def test_full_size_properties(device):
     """At BASELINE's full sizes (config 2's gate weight, 14336 x 4096 bfloat4_b; config 3's 4096 x 14336 bfloat8_b)
     the oracle is too slow for every column; size-independent properties stand in: linearity in x (power-of-two
