@@ -64,6 +64,43 @@ __global__ void __launch_bounds__(kThreads) tkd_topk_merge_kernel(const uint32_t
     }
 }
 
+// The same for up to kWarpMax candidates a row (the LM head's 600): one warp, no block barriers. The candidates sit in
+// shared memory; every round each lane scans its share, then five shuffles.
+constexpr int kWarpMax = 1024;
+__global__ void __launch_bounds__(32) tkd_topk_merge_warp_kernel(const uint32_t* __restrict__ records, int nrec, int rows,
+                                                                 int k, int top, uint32_t* __restrict__ out) {
+    __shared__ unsigned long long cands[kWarpMax];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int r = blockIdx.x, lane = threadIdx.x;
+    const int n = nrec * k;
+    for (int c = lane; c < n; c += 32) {
+        const int rec = c / k, q = c - rec * k;
+        const uint32_t* page = records + (size_t)rec * 2 * rows * k;
+        const uint32_t key = __ldg(page + r * k + q), idx = __ldg(page + (rows + r) * k + q);
+        cands[c] = key ? ((unsigned long long)key << 32) | (uint32_t)~idx : 0ull;
+    }
+    __syncwarp();
+    unsigned long long bound = ~0ull;
+    for (int t = 0; t < top; ++t) {
+        unsigned long long best = 0;
+        for (int c = lane; c < n; c += 32) {
+            const unsigned long long v = cands[c];
+            if (v < bound && v > best) best = v;
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+            best = other > best ? other : best;
+        }
+        if (lane == 0) {
+            out[r * top + t] = (uint32_t)(best >> 32);
+            out[(rows + r) * top + t] = best ? ~(uint32_t)best : 0xFFFFFFFFu;
+        }
+        bound = best;
+    }
+}
+
 }  // namespace
 
 int tkd_launch_topk_merge(const uint32_t* records, int nrec, int rows, int k, int top, uint32_t* out, cudaStream_t st) {
@@ -76,6 +113,10 @@ int tkd_launch_topk_merge(const uint32_t* records, int nrec, int rows, int k, in
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = tkd_pdl_enabled() ? 1 : 0;
+    if (nrec * k <= kWarpMax) {
+        cfg.blockDim = dim3(32);
+        return (int)cudaLaunchKernelEx(&cfg, tkd_topk_merge_warp_kernel, records, nrec, rows, k, top, out);
+    }
     return (int)cudaLaunchKernelEx(&cfg, tkd_topk_merge_kernel, records, nrec, rows, k, top, out);
 }
 

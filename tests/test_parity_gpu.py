@@ -216,10 +216,13 @@ def test_packed_weight_cache_round_trip(device, tmp_path):
         assert torch.equal(ts.t, ts2.t)
         tx = dev_x(device, torch.randn(3, 256, generator=g))
         assert torch.equal(host(linear.matmul(tx, tw, ts)), host(linear.matmul(tx, tw2, ts2)))
+        other = torch.randn(384, 256, generator=g) * 0.02
         with pytest.raises(cache.PackCacheMismatch):
-            cache.native_weight_cached(device, w * 2, fmt, path, col_scale=col_scale)
-        tw3, _ = cache.native_weight_cached(device, w * 2, fmt, path, col_scale=col_scale, rebuild=True)
+            cache.native_weight_cached(device, other, fmt, path, col_scale=col_scale)
+        tw3, _ = cache.native_weight_cached(device, other, fmt, path, col_scale=col_scale, rebuild=True)
         assert not torch.equal(tw3.t, tw.t)
+        tw4, _ = cache.native_weight_cached(device, other, fmt, path, col_scale=col_scale)  # the rebuilt cache, loaded
+        assert torch.equal(tw4.t, tw3.t)
 
 
 def test_full_size_properties(device):
