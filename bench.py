@@ -308,7 +308,7 @@ def main():
         n_loc = col_end - col_start
     # (the same count on every rank, from the largest shard: every rank must make the same number of exchanged calls)
     n_max = n_loc if not (args.scaling == "strong" and world > 1) else max(b - a for a, b in shards)
-    copies = max(2, -(-2 * L2_BYTES // int((2 if args.workload == "c2" else 1) * wl["k"] * n_max * BYTES_PER_WEIGHT[wl["fmt"]])) + (1 if n_max == n_loc else 2))
+    copies = max(2, -(-2 * L2_BYTES // int((2 if args.workload == "c2" else 1) * wl["k"] * n_max * BYTES_PER_WEIGHT[wl["fmt"]])) + (2 if args.scaling == "strong" and world > 1 else 1))
     copies = min(copies, 40)
     if world > 1:
         assert args.scaling == "weak" or fused, "bench: --scaling strong goes with the fused exchange"
