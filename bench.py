@@ -239,6 +239,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--ks", type=int, default=0, help="k per slice of the kernel's work items (0: the library's default)")
+    ap.add_argument("--cols", type=int, default=0, help="output columns instead of the workload's own (for experiments)")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="N > 1: weak: every rank streams a whole workload; strong: the one workload's columns are split")
     ap.add_argument("--exchange", choices=["fused", "nccl", "none"], default="fused",
@@ -259,7 +260,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.cols:
+        wl["n"] = args.cols
     m = args.rows
     steps, warmup = args.steps, max(3, args.warmup)
     config = {"workload": f"{args.workload}: {wl['what']}", "rows": m, "K": wl["k"], "N": wl["n"], "format": wl["fmt"]}

@@ -69,8 +69,16 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     const int mt = a->m <= 8 ? 1 : (a->m <= 16 ? 2 : 4);
     const int sab = tkd_sab(a->fmt);
     const int chunk_k = tkd_chunk_k(a->fmt);
-    // k per slice: a function of K only (a column's sum must not depend on anything but K, the format and M's bucket)
-    const int ks_k = a->k >= 4096 ? 1024 : (a->k >= 2048 ? 512 : 256);
+    // k per slice: a function of K, the format and the row count only (a column's sum must not depend on anything
+    // else). One row: 1024 (less for a short K), so that the items divide well among the CTAs. More rows: a quarter of
+    // K if that is more (at most 4096): every slice a panel is cut into is another M x 128 sums through the scratch
+    // buffer for the CTA that adds the panel up, which costs more than the coarser split loses in balance.
+    int ks_k = a->k >= 4096 ? 1024 : (a->k >= 2048 ? 512 : 256);
+    if (a->m >= 2) {
+        int quarter = (int)((a->k / 4 + chunk_k - 1) / chunk_k) * chunk_k;
+        if (quarter > 4096) quarter = 4096;
+        if (quarter > ks_k) ks_k = quarter;
+    }
     p.ks = a->ks ? a->ks : (ks_k < chunk_k ? chunk_k : ks_k);
     if (p.ks < chunk_k || p.ks % chunk_k || p.ks > 4096) return TKD_ERR_BAD_ARG;
     p.nslices = (p.K + p.ks - 1) / p.ks;
@@ -212,7 +220,7 @@ int tkd_matmul_plan(const TkdMatmul* a, TkdPlan* plan) {
     plan->panels = L.p.total_panels;
     plan->grid = L.grid;
     plan->stages = L.p.nstages;
-    plan->stream_warps = TKD_STREAM_WARPS;
+    plan->stream_warps = a->m > 16 ? TKD_STREAM_WARPS_32ROWS : (a->m > 8 ? TKD_STREAM_WARPS_16ROWS : TKD_STREAM_WARPS);
     plan->chunk_k = tkd_chunk_k(L.p.fmt);
     plan->smem_bytes = (int32_t)L.smem;
     plan->items = L.p.total_items;

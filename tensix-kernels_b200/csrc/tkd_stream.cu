@@ -313,8 +313,10 @@ __device__ __forceinline__ uint32_t topk_key(uint16_t b) {
     return (uint32_t)(b ^ (0x8000u | (0x7FFFu & (0u - (uint32_t)(b >> 15))))) & 0xFFFFu;
 }
 
-template <int FMT, int MT>
-__global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid_constant__ TkdParams p) {
+// SW: streaming warps, 16 (a warp per column group and half of each chunk's super-atoms) or 8 (a warp takes both halves
+// of its group, one after the other: the 32-row kernel, whose accumulators need the registers that fewer warps leave).
+template <int FMT, int MT, int SW>
+__global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const __grid_constant__ TkdParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     using F = Fmt<FMT>;
     constexpr int MP = MT == 1 ? 8 : (MT == 2 ? 24 : 40);  // floats per column in the hand-over buffers
@@ -336,10 +338,10 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
     if (tid == 0) {
         for (int s = 0; s < p.nstages; ++s) {
             mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, TKD_STREAM_WARPS);
+            mbar_init(empty0 + 8 * s, SW);
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(pfull0 + 8 * s, TKD_STREAM_WARPS);
+            mbar_init(pfull0 + 8 * s, SW);
             mbar_init(pempty0 + 8 * s, 4);
         }
         sflag[0] = 0;
@@ -422,28 +424,32 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
                     if (mbar_try_wait(full0 + 8 * (q % nst), (q / nst) & 1)) break;
             }
         }
-    } else if (warp <= TKD_STREAM_WARPS) {
+    } else if (warp <= SW) {
         // ---------------------------------------------------------------- streaming warps
         // One flat loop over the stages of the ring; everything about items comes with the stage's header.
         // (x, the scratch buffer and the outputs may belong to the kernel before this one: wait for it to complete)
         asm volatile("griddepcontrol.wait;" ::: "memory");
         const int cw = warp - 1;
-        const int g8 = cw & 7, h = cw >> 3;
+        constexpr int NH = 16 / SW;  // halves of a chunk's super-atoms this warp takes
+        const int g8 = cw & 7, h0 = SW == 16 ? cw >> 3 : 0;
         const int g = lane >> 2, t = lane & 3;
         constexpr int NX = F::SUBSA / 2 * F::XB;
-        constexpr bool PRE = MT <= 2;
+        constexpr bool PRE = MT <= 2 && NH == 1;
         constexpr int EXPB = FMT == TKD_BFP4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
-        const uint16_t* xb[MT];
+        const uint16_t* xb[NH][MT];
 #pragma unroll
         // (a lane whose row lies beyond M reads row M - 1 instead: a B column only feeds its own output column, and
         // the columns beyond M are never read, so those lanes need no predicate and no zero fill)
-        for (int m = 0; m < MT; ++m) xb[m] = p.x + (int64_t)min(8 * m + g, M - 1) * p.ldx + 8 * t + h * F::KSA;
+        for (int hh = 0; hh < NH; ++hh)
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+                xb[hh][m] = p.x + (int64_t)min(8 * m + g, M - 1) * p.ldx + 8 * t + (h0 + hh) * F::KSA;
         const uint32_t ring_a = smem_u32(ring), hdr_a = smem_u32(hdr);
-        const uint32_t code_off = g8 * (F::SUBSA * F::SAB) + h * F::SAB + EXPB + lane * 16;
-        const uint32_t exp_off = g8 * (F::SUBSA * F::SAB) + h * F::SAB + t * (EXPB / 4);
+        const uint32_t code_off = g8 * (F::SUBSA * F::SAB) + h0 * F::SAB + EXPB + lane * 16;
+        const uint32_t exp_off = g8 * (F::SUBSA * F::SAB) + h0 * F::SAB + t * (EXPB / 4);
         uint32_t slot = 0, phase = 0, pi = 0;  // ring position and its parity; deliveries so far
         int kc = (int)((lead > 0 ? tail0 : i0) % p.nslices) * p.ks;
-        float acc[NA][MT][4], tot[MT][4];
+        float acc[NH][NA][MT][4], tot[NH][MT][4];
         while (true) {
             const bool full = kc + CK <= K;
             uint4 xpre[NX][MT];
@@ -453,25 +459,45 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
 #pragma unroll
                     for (int q = 0; q < F::XB; ++q)
 #pragma unroll
-                        for (int m = 0; m < MT; ++m) xpre[i * F::XB + q][m] = ldg_x(xb[m] + kc + 2 * i * F::KSA + 32 * q);
+                        for (int m = 0; m < MT; ++m) xpre[i * F::XB + q][m] = ldg_x(xb[0][m] + kc + 2 * i * F::KSA + 32 * q);
             }
             if (!mbar_wait(full0 + 8 * slot, phase, p.status)) break;
             const uint4 hd = lds128(hdr_a + 16 * slot);
             const uint32_t fl = hd.x;
+            if constexpr (!PRE) {
+                // the activations of the stage after this one, asked into L1 now (the warps share the lines out): by the
+                // time that stage is computed its loads hit L1 instead of waiting for L2 one block at a time
+                constexpr int LPR = CK * 2 / 128;  // 128-byte lines of a row's share of a chunk
+                const int kn = (int)hd.z;
+                for (int i = cw * 32 + lane; i < M * LPR; i += SW * 32) {
+                    const int row = i / LPR, seg = i - row * LPR;
+                    if (kn + seg * 64 < K)
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(p.x + (int64_t)row * p.ldx + kn + seg * 64));
+                }
+            }
             if (fl & ST_FIRST) {
 #pragma unroll
-                for (int j = 0; j < NA; ++j)
+                for (int hh = 0; hh < NH; ++hh)
 #pragma unroll
-                    for (int m = 0; m < MT; ++m) acc[j][m][0] = acc[j][m][1] = acc[j][m][2] = acc[j][m][3] = 0.f;
+                    for (int j = 0; j < NA; ++j)
+#pragma unroll
+                        for (int m = 0; m < MT; ++m)
+                            acc[hh][j][m][0] = acc[hh][j][m][1] = acc[hh][j][m][2] = acc[hh][j][m][3] = 0.f;
             }
             const uint32_t sbase = ring_a + slot * p.stage_bytes;
-            if (full) {
-                chunk_mma<FMT, MT, NA, true, PRE>(acc, sbase + code_off, sbase + exp_off, xpre, xb, kc, K, h, F::SUBSA);
-            } else {
-                // the last chunk of K: fewer super-atoms, the groups closer together
-                const int nsa = nsa_total - kc / CK * F::SUBSA;
-                const uint32_t gb = sbase + g8 * nsa * F::SAB + h * F::SAB;
-                chunk_mma<FMT, MT, NA, false, PRE>(acc, gb + EXPB + lane * 16, gb + t * (EXPB / 4), xpre, xb, kc, K, h, nsa);
+#pragma unroll
+            for (int hh = 0; hh < NH; ++hh) {
+                const int h = h0 + hh;
+                if (full) {
+                    chunk_mma<FMT, MT, NA, true, PRE>(acc[hh], sbase + code_off + hh * F::SAB, sbase + exp_off + hh * F::SAB,
+                                                      xpre, xb[hh], kc, K, h, F::SUBSA);
+                } else {
+                    // the last chunk of K: fewer super-atoms, the groups closer together
+                    const int nsa = nsa_total - kc / CK * F::SUBSA;
+                    const uint32_t gb = sbase + g8 * nsa * F::SAB + h * F::SAB;
+                    chunk_mma<FMT, MT, NA, false, PRE>(acc[hh], gb + EXPB + lane * 16, gb + t * (EXPB / 4), xpre, xb[hh], kc, K,
+                                                       h, nsa);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * slot);
@@ -480,25 +506,30 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
             if (!(fl & ST_LAST)) continue;
             // ---- the item's slice is done
 #pragma unroll
-            for (int m = 0; m < MT; ++m)
+            for (int hh = 0; hh < NH; ++hh)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float part = NA == 2 ? acc[0][m][e] + acc[NA - 1][m][e] : acc[0][m][e];
-                    tot[m][e] = fl & ST_START ? part : tot[m][e] + part;
-                }
+                for (int m = 0; m < MT; ++m)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float part = NA == 2 ? acc[hh][0][m][e] + acc[hh][NA - 1][m][e] : acc[hh][0][m][e];
+                        tot[hh][m][e] = fl & ST_START ? part : tot[hh][m][e] + part;
+                    }
             if (fl & ST_STORE) {
                 // straight into the scratch slot of (panel, slice): [half][row][128 columns]
-                float* sc = p.scratch + ((size_t)hd.y * 2 + h) * M * TKD_PANEL_COLS + g8 * 16 + g;
 #pragma unroll
-                for (int m = 0; m < MT; ++m) {
-                    const int r0 = 8 * m + 2 * t;
-                    if (r0 < M) {
-                        __stcg(sc + (size_t)r0 * TKD_PANEL_COLS, tot[m][0]);
-                        __stcg(sc + (size_t)r0 * TKD_PANEL_COLS + 8, tot[m][2]);
-                    }
-                    if (r0 + 1 < M) {
-                        __stcg(sc + (size_t)(r0 + 1) * TKD_PANEL_COLS, tot[m][1]);
-                        __stcg(sc + (size_t)(r0 + 1) * TKD_PANEL_COLS + 8, tot[m][3]);
+                for (int hh = 0; hh < NH; ++hh) {
+                    float* sc = p.scratch + ((size_t)hd.y * 2 + h0 + hh) * M * TKD_PANEL_COLS + g8 * 16 + g;
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const int r0 = 8 * m + 2 * t;
+                        if (r0 < M) {
+                            __stcg(sc + (size_t)r0 * TKD_PANEL_COLS, tot[hh][m][0]);
+                            __stcg(sc + (size_t)r0 * TKD_PANEL_COLS + 8, tot[hh][m][2]);
+                        }
+                        if (r0 + 1 < M) {
+                            __stcg(sc + (size_t)(r0 + 1) * TKD_PANEL_COLS, tot[hh][m][1]);
+                            __stcg(sc + (size_t)(r0 + 1) * TKD_PANEL_COLS + 8, tot[hh][m][3]);
+                        }
                     }
                 }
             }
@@ -506,11 +537,14 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
                 const uint32_t pb = pi & 1;
                 if (!mbar_wait(pempty0 + 8 * pb, ((pi >> 1) & 1) ^ 1, p.status)) break;
                 if (!(fl & ST_SPLIT)) {
-                    float* pc = pbuf + ((size_t)(pb * 2 + h) * TKD_PANEL_COLS + g8 * 16 + g) * MP + 2 * t;
 #pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        *reinterpret_cast<float2*>(pc + 8 * m) = make_float2(tot[m][0], tot[m][1]);
-                        *reinterpret_cast<float2*>(pc + 8 * MP + 8 * m) = make_float2(tot[m][2], tot[m][3]);
+                    for (int hh = 0; hh < NH; ++hh) {
+                        float* pc = pbuf + ((size_t)(pb * 2 + h0 + hh) * TKD_PANEL_COLS + g8 * 16 + g) * MP + 2 * t;
+#pragma unroll
+                        for (int m = 0; m < MT; ++m) {
+                            *reinterpret_cast<float2*>(pc + 8 * m) = make_float2(tot[hh][m][0], tot[hh][m][1]);
+                            *reinterpret_cast<float2*>(pc + 8 * MP + 8 * m) = make_float2(tot[hh][m][2], tot[hh][m][3]);
+                        }
                     }
                 }
                 __syncwarp();
@@ -523,8 +557,8 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
     } else {
         // ---------------------------------------------------------------- output warps
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        const int et = tid - (1 + TKD_STREAM_WARPS) * 32;  // the panel column this thread owns
-        const int ow = warp - (1 + TKD_STREAM_WARPS);
+        const int et = tid - (1 + SW) * 32;  // the panel column this thread owns
+        const int ow = warp - (1 + SW);
         Cursor c;
         uint32_t pi = 0;
         float tot[MR];
@@ -613,7 +647,7 @@ __global__ void __launch_bounds__(TKD_THREADS, 1) tkd_stream_kernel(const __grid
                     } else {
 #pragma unroll 1
                         for (int hh = 0; hh < 2; ++hh) {
-                            if constexpr (MT == 4) {
+                            if constexpr (MT >= 2) {
                                 // eight rows at a time, four slices' loads in flight together
 #pragma unroll
                                 for (int rb = 0; rb < MR; rb += 8) {
@@ -841,9 +875,9 @@ __global__ void tkd_exchange_wait_kernel(uint32_t* flags, int nranks, int* statu
     }
 }
 
-template <int FMT, int MT>
+template <int FMT, int MT, int SW>
 int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = tkd_stream_kernel<FMT, MT>;
+    auto kern = tkd_stream_kernel<FMT, MT, SW>;
     // (once per device and instantiation: allow the largest dynamic shared memory a CTA can have)
     static bool allowed[64] = {false};
     int dev = 0;
@@ -860,7 +894,7 @@ int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
     // drains; everything else waits for the earlier kernel's completion (griddepcontrol.wait).
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(TKD_THREADS);
+    cfg.blockDim = dim3((1 + SW + 4) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -873,9 +907,9 @@ int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
 
 template <int FMT>
 int launch_fmt(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    if (p.M <= 8) return launch_one<FMT, 1>(p, grid, smem, st);
-    if (p.M <= 16) return launch_one<FMT, 2>(p, grid, smem, st);
-    return launch_one<FMT, 4>(p, grid, smem, st);
+    if (p.M <= 8) return launch_one<FMT, 1, 16>(p, grid, smem, st);
+    if (p.M <= 16) return launch_one<FMT, 2, TKD_STREAM_WARPS_16ROWS>(p, grid, smem, st);
+    return launch_one<FMT, 4, TKD_STREAM_WARPS_32ROWS>(p, grid, smem, st);
 }
 
 }  // namespace
