@@ -109,8 +109,12 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     // shared-memory map: barriers, the hand-over buffers of the streaming warps, the GLU exchange buffer, the ring
     const int mp = mt == 1 ? 8 : (mt == 2 ? 24 : 40);
     p.off_pbuf = TKD_SMEM_HEAD;
-    p.off_tbuf = p.off_pbuf + 2 * 2 * TKD_PANEL_COLS * mp * 4;
-    p.off_ring = (int)align_up(p.off_tbuf + TKD_PANEL_COLS * mp * 4, 128);
+    // (32 rows: one hand-over buffer instead of two; 9 to 32 rows of bfloat8_b or bf16: two tiles of the activations, rows
+    // x one chunk of k; the same conditions as NPB and XS in the kernel)
+    p.off_tbuf = p.off_pbuf + (mt == 4 ? 1 : 2) * 2 * TKD_PANEL_COLS * mp * 4;
+    p.off_xt = (int)align_up(p.off_tbuf + TKD_PANEL_COLS * mp * 4, 128);
+    const int xt_bytes = mt >= 2 && a->fmt != TKD_BFP4 ? 2 * (8 * mt) * chunk_k * 2 : 0;
+    p.off_ring = (int)align_up(p.off_xt + xt_bytes, 128);
     p.stage_bytes = 8 * tkd_subsa(a->fmt) * sab;
     p.nstages = (kMaxSmem - p.off_ring) / p.stage_bytes;
     if (p.nstages > TKD_MAX_STAGES) p.nstages = TKD_MAX_STAGES;

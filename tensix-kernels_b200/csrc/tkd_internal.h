@@ -81,7 +81,7 @@ struct TkdParams {
     int* grid_counter;   // CTAs of this call that have finished their output (returns to zero)
     int exchange_wait;
     // shared-memory map (bytes from the start of dynamic shared memory)
-    int off_pbuf, off_tbuf, off_ring;
+    int off_pbuf, off_tbuf, off_xt, off_ring;
     int stage_bytes;
 };
 

@@ -33,6 +33,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "tkd_internal.h"
 #include "tkd_layout.h"
 
@@ -44,9 +46,13 @@ __device__ long long tkd_trace2[8 * 256];  // CTA 3 warp 1, per item: more point
 __device__ int tkd_trace_n[2];  // per CTA: entry, streaming warps done, output warps done (ns)
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 #define PROF_TIME(slot) do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 148) tkd_times[blockIdx.x * 4 + slot] = gtime(); } while (0)
+#define PROF_MARK(i) _pm[i] = gtime()
+#define PROF_MARKS_OUT do { if (finish && et == 0 && blockIdx.x < 148) tkd_times[blockIdx.x * 4 + 3] = ((_pm[1] - _pm[0]) >> 6) | (((_pm[2] - _pm[1]) >> 6) << 16) | (((_pm[3] - _pm[2]) >> 6) << 32); } while (0)
 #define PROF_T0 long long _t0 = clock64()
 #define PROF_ADD(slot) do { (void)_t0; } while (0)  // (a global read-modify-write here stalls the warp it measures)
 #else
+#define PROF_MARK(i)
+#define PROF_MARKS_OUT
 #define PROF_T0
 #define PROF_ADD(slot)
 #define PROF_TIME(slot)
@@ -137,6 +143,11 @@ __device__ __noinline__ bool flags_wait(const uint32_t* flags, int nranks, uint3
         }
     }
     return true;
+}
+__device__ __forceinline__ int atom_add_acq_rel(int* p, int v) {
+    int old;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
 }
 __device__ __forceinline__ void bar_output_warps() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -260,12 +271,16 @@ enum : uint32_t {
 // addresses of this lane's code and exponent words of super-atom h; xb[m]: this lane's row of x at k = 8 t + h * KSA;
 // kc: the chunk's first k. FULL: the chunk has all its super-atoms and ends within K (then xpre holds the activations,
 // loaded before the stage was waited for, when PRE).
-template <int FMT, int MT, int NA, bool FULL, bool PRE>
+// XS: the activations come from the stage's tile in shared memory instead (xt_a: this lane's row of it, xj: the 16-byte
+// piece of the row its first block starts at, xsw: the row's swizzle).
+template <int FMT, int MT, int NA, bool FULL, bool PRE, bool XS = false>
 __device__ __forceinline__ void chunk_mma(float (&acc)[NA][MT][4], uint32_t code_a, uint32_t exp_a,
                                           const uint4 (&xpre)[Fmt<FMT>::SUBSA / 2 * Fmt<FMT>::XB][MT],
-                                          const uint16_t* const (&xb)[MT], int kc, int K, int h, int nsa) {
+                                          const uint16_t* const (&xb)[MT], int kc, int K, int h, int nsa,
+                                          uint32_t xt_a = 0, int xj = 0, int xsw = 0) {
     using F = Fmt<FMT>;
     constexpr int NPW = F::SUBSA / 2;  // super-atoms a warp takes of a chunk
+    constexpr int XROW = F::SUBSA * F::KSA * 2;  // bytes of a tile row
 #pragma unroll
     for (int i = 0; i < NPW; ++i) {
         if (!FULL && h + 2 * i >= nsa) break;
@@ -288,7 +303,9 @@ __device__ __forceinline__ void chunk_mma(float (&acc)[NA][MT][4], uint32_t code
             uint4 xv[MT];
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-                if constexpr (FULL && PRE)
+                if constexpr (XS)
+                    xv[m] = lds128(xt_a + m * 8 * XROW + (((xj + (2 * i * F::KSA + 32 * q) / 8) ^ xsw) << 4));
+                else if constexpr (FULL && PRE)
                     xv[m] = xpre[i * F::XB + q][m];
                 else
                     xv[m] = ldg_x(xb[m] + k);
@@ -324,7 +341,13 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
     constexpr int NA = MT == 1 ? 2 : 1;                    // accumulator sets a streaming warp alternates between
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TKD_MAX_STAGES);
-    const uint32_t pfull0 = smem_u32(bars + 2 * TKD_MAX_STAGES), pempty0 = pfull0 + 16;
+    const uint32_t pfull0 = smem_u32(bars + 2 * TKD_MAX_STAGES), pempty0 = pfull0 + 16, xfull0 = pfull0 + 32;
+    // NH: halves of a chunk's super-atoms a streaming warp takes; XS: the activations are staged in shared memory (two
+    // tiles of MR rows x one chunk of k, filled by the streaming warps' own asynchronous copies one stage ahead);
+    // NPB: hand-over buffers between the streaming and the output warps
+    constexpr int NH = 16 / SW;
+    constexpr bool XS = NH == 2 && FMT != TKD_BFP4;
+    constexpr int NPB = MT == 4 ? 1 : 2;
     volatile int* sflag = reinterpret_cast<volatile int*>(smem + TKD_SMEM_HEAD - 16);
     uint4* hdr = reinterpret_cast<uint4*>(smem + 512);  // one header per stage of the ring
     float* pbuf = reinterpret_cast<float*>(smem + p.off_pbuf);  // [2 buffers][2 halves][128 columns][MP]
@@ -343,6 +366,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
         for (int s = 0; s < 2; ++s) {
             mbar_init(pfull0 + 8 * s, SW);
             mbar_init(pempty0 + 8 * s, 4);
+            mbar_init(xfull0 + 8 * s, SW * 32);
         }
         sflag[0] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -430,11 +454,29 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
         // (x, the scratch buffer and the outputs may belong to the kernel before this one: wait for it to complete)
         asm volatile("griddepcontrol.wait;" ::: "memory");
         const int cw = warp - 1;
-        constexpr int NH = 16 / SW;  // halves of a chunk's super-atoms this warp takes
         const int g8 = cw & 7, h0 = SW == 16 ? cw >> 3 : 0;
         const int g = lane >> 2, t = lane & 3;
         constexpr int NX = F::SUBSA / 2 * F::XB;
         constexpr bool PRE = MT <= 2 && NH == 1;
+        constexpr int XROW = CK * 2, XTILE = MR * XROW, XPR = CK / 8;  // a tile row's bytes, a tile's, 16-byte pieces a row
+        const uint32_t xt0 = smem_u32(smem + p.off_xt);
+        // a tile row r keeps its 16-byte piece j at position j ^ swz(r): the eight lanes a shared-memory load serves
+        // together (two rows, four pieces each) then fall into eight different bank groups
+        auto swz = [](int r) { return ((r & 1) << 2) ^ ((r >> 1) & 3); };
+        auto load_x = [&](int buf, int k0) {
+            for (int e = cw * 32 + lane; e < MR * XPR; e += SW * 32) {
+                const int r = e / XPR, j = e - r * XPR;
+                if (k0 + j * 8 < K) {
+                    const uint16_t* src = p.x + (int64_t)min(r, M - 1) * p.ldx + k0 + j * 8;
+                    const uint32_t dst = xt0 + buf * XTILE + r * XROW + ((j ^ swz(r)) << 4);
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+                }
+            }
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];" ::"r"(xfull0 + 8 * buf) : "memory");
+        };
+        const uint32_t xt_lane = xt0 + g * XROW;  // (rows 8 m + g of a tile: the swizzle depends on g alone)
+        const int xsw = swz(g);
+        uint32_t nstage = 0, prev_slot = 0, prev_phase = 0;
         constexpr int EXPB = FMT == TKD_BFP4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
         const uint16_t* xb[NH][MT];
 #pragma unroll
@@ -450,6 +492,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
         uint32_t slot = 0, phase = 0, pi = 0;  // ring position and its parity; deliveries so far
         int kc = (int)((lead > 0 ? tail0 : i0) % p.nslices) * p.ks;
         float acc[NH][NA][MT][4], tot[NH][MT][4];
+        if constexpr (XS) load_x(0, kc);
         while (true) {
             const bool full = kc + CK <= K;
             uint4 xpre[NX][MT];
@@ -464,7 +507,16 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             if (!mbar_wait(full0 + 8 * slot, phase, p.status)) break;
             const uint4 hd = lds128(hdr_a + 16 * slot);
             const uint32_t fl = hd.x;
-            if constexpr (!PRE) {
+            if constexpr (XS) {
+                // the next stage's activations into the other tile, once every warp has left the stage before this one
+                // (whose tile that was); then this stage's own tile must have landed
+                if (!(fl & ST_END)) {
+                    if (nstage && !mbar_wait(empty0 + 8 * prev_slot, prev_phase, p.status)) break;
+                    load_x((nstage + 1) & 1, (int)hd.z);
+                }
+                if (!mbar_wait(xfull0 + 8 * (nstage & 1), (nstage >> 1) & 1, p.status)) break;
+                prev_slot = slot, prev_phase = phase, ++nstage;
+            } else if constexpr (!PRE) {
                 // the activations of the stage after this one, asked into L1 now (the warps share the lines out): by the
                 // time that stage is computed its loads hit L1 instead of waiting for L2 one block at a time
                 constexpr int LPR = CK * 2 / 128;  // 128-byte lines of a row's share of a chunk
@@ -489,14 +541,15 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             for (int hh = 0; hh < NH; ++hh) {
                 const int h = h0 + hh;
                 if (full) {
-                    chunk_mma<FMT, MT, NA, true, PRE>(acc[hh], sbase + code_off + hh * F::SAB, sbase + exp_off + hh * F::SAB,
-                                                      xpre, xb[hh], kc, K, h, F::SUBSA);
+                    chunk_mma<FMT, MT, NA, true, PRE, XS>(acc[hh], sbase + code_off + hh * F::SAB, sbase + exp_off + hh * F::SAB,
+                                                          xpre, xb[hh], kc, K, h, F::SUBSA, xt_lane + ((nstage + 1) & 1) * XTILE,
+                                                          h * F::KSA / 8 + t, xsw);
                 } else {
                     // the last chunk of K: fewer super-atoms, the groups closer together
                     const int nsa = nsa_total - kc / CK * F::SUBSA;
                     const uint32_t gb = sbase + g8 * nsa * F::SAB + h * F::SAB;
-                    chunk_mma<FMT, MT, NA, false, PRE>(acc[hh], gb + EXPB + lane * 16, gb + t * (EXPB / 4), xpre, xb[hh], kc, K,
-                                                       h, nsa);
+                    chunk_mma<FMT, MT, NA, false, PRE, XS>(acc[hh], gb + EXPB + lane * 16, gb + t * (EXPB / 4), xpre, xb[hh], kc,
+                                                           K, h, nsa, xt_lane + ((nstage + 1) & 1) * XTILE, h * F::KSA / 8 + t, xsw);
                 }
             }
             __syncwarp();
@@ -534,8 +587,8 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                 }
             }
             if (fl & ST_DELIVER) {
-                const uint32_t pb = pi & 1;
-                if (!mbar_wait(pempty0 + 8 * pb, ((pi >> 1) & 1) ^ 1, p.status)) break;
+                const uint32_t pb = NPB == 2 ? pi & 1 : 0;
+                if (!mbar_wait(pempty0 + 8 * pb, ((NPB == 2 ? pi >> 1 : pi) & 1) ^ 1, p.status)) break;
                 if (!(fl & ST_SPLIT)) {
 #pragma unroll
                     for (int hh = 0; hh < NH; ++hh) {
@@ -553,6 +606,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             }
             if (fl & ST_END) break;
         }
+        if constexpr (XS) asm volatile("cp.async.wait_all;" ::: "memory");  // (none of this thread's copies may land later)
         if (warp == 1) PROF_TIME(1);
     } else {
         // ---------------------------------------------------------------- output warps
@@ -562,6 +616,9 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
         Cursor c;
         uint32_t pi = 0;
         float tot[MR];
+#ifdef TKD_PROF
+        unsigned long long _pm[4] = {0, 0, 0, 0};
+#endif
         bool ok = true;
         for (int64_t j = 0; j < i1 - i0 && ok; ++j) {
             const int64_t it = j < lead ? tail0 + j : i0 + (j - lead);
@@ -572,7 +629,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             const Flow f = flow_of(c, p, it, i0, i1);
             if (!f.deliver) continue;
             const TkdSegDev& sg = p.seg[c.seg];
-            const uint32_t pb = pi & 1;
+            const uint32_t pb = NPB == 2 ? pi & 1 : 0;
             // this thread's column within its weight; its group's exponent byte and its scale are asked for now, so
             // that their latency passes while the streaming warps are still at work
             const int n = glu2 ? c.pl * 64 + (et & 63) : c.pl * TKD_PANEL_COLS + et;
@@ -586,8 +643,9 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                                                : static_cast<const float*>(sp)[n];
             }
             PROF_T0;
-            ok = mbar_wait(pfull0 + 8 * pb, (pi >> 1) & 1, p.status);
+            ok = mbar_wait(pfull0 + 8 * pb, (NPB == 2 ? pi >> 1 : pi) & 1, p.status);
             if (!ok) break;
+            PROF_MARK(0);
             if (ow == 0) PROF_ADD(16);
             bool finish = !f.split;
             if (!f.split) {
@@ -612,15 +670,17 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                 // on the hand-over barrier orders those stores before this point): count them in, and if they were
                 // the last the panel waited for, add all of its slices up
                 if (et == 0) {
-                    __threadfence();
-                    const int old = atomicAdd(p.counters + c.panel, f.count);
+                    // (one release-acquire atomic: the slice sums stored before it, by the streaming warps whose
+                    // arrival this thread waited for, are visible to whichever CTA sees the count complete, and that CTA
+                    // sees all the others')
+                    const int old = atom_add_acq_rel(p.counters + c.panel, f.count);
                     const int last = old + f.count == p.nslices;
                     if (last) p.counters[c.panel] = 0;  // ready for the next call
-                    __threadfence();
                     sflag[0] = last;
                 }
                 bar_output_warps();
                 finish = sflag[0] != 0;
+                PROF_MARK(1);
                 if (finish) {
                     // the panel's first slices came as one sum from the CTA that holds its slice 0: up to where?
                     const int64_t pfirst = (int64_t)c.panel * p.nslices;
@@ -644,36 +704,43 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                                 if (s + j < p.nslices) t0 += v0[j], t1 += v1[j];
                         }
                         tot[0] = t0 + t1;
+                    } else if constexpr (MT >= 2) {
+                        // RB rows at a time; both halves' loads of four entries (the sum so far counts as one) in flight
+                        // together, unconditional (a row or entry that is not there re-reads the last that is) so that
+                        // they stay one block of code. (32 rows: four rows at a time, or the loads' registers do not fit
+                        // beside the 32 sums and the compiler takes them a few at a time.)
+                        constexpr int RB = MT == 4 ? 4 : 8;
+#pragma unroll
+                        for (int rb = 0; rb < MR; rb += RB) {
+                            if (rb >= M) break;
+                            float th[2][RB];
+#pragma unroll 1
+                            for (int s = pe - 1; s < p.nslices; s += 4) {
+                                float v[2][4][RB];
+#pragma unroll
+                                for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                        for (int m = 0; m < RB; ++m)
+                                            v[hh][j][m] = term(min(s + j, p.nslices - 1), hh, min(rb + m, M - 1));
+#pragma unroll
+                                for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                        for (int m = 0; m < RB; ++m) {
+                                            if (s + j >= p.nslices) continue;
+                                            th[hh][m] = s + j == pe - 1 ? v[hh][j][m] : th[hh][m] + v[hh][j][m];
+                                        }
+                            }
+#pragma unroll
+                            for (int m = 0; m < RB; ++m) tot[rb + m] = th[0][m] + th[1][m];
+                        }
                     } else {
 #pragma unroll 1
                         for (int hh = 0; hh < 2; ++hh) {
-                            if constexpr (MT >= 2) {
-                                // eight rows at a time, four slices' loads in flight together
-#pragma unroll
-                                for (int rb = 0; rb < MR; rb += 8) {
-                                    if (rb >= M) break;
-                                    float th[8];
-#pragma unroll
-                                    for (int m = 0; m < 8; ++m)
-                                        if (rb + m < M) th[m] = term(pe - 1, hh, rb + m);
-#pragma unroll 1
-                                    for (int s = pe; s < p.nslices; s += 4) {
-                                        float v[4][8];
-#pragma unroll
-                                        for (int j = 0; j < 4; ++j)
-#pragma unroll
-                                            for (int m = 0; m < 8; ++m)
-                                                if (s + j < p.nslices && rb + m < M) v[j][m] = term(s + j, hh, rb + m);
-#pragma unroll
-                                        for (int j = 0; j < 4; ++j)
-#pragma unroll
-                                            for (int m = 0; m < 8; ++m)
-                                                if (s + j < p.nslices && rb + m < M) th[m] += v[j][m];
-                                    }
-#pragma unroll
-                                    for (int m = 0; m < 8; ++m) tot[rb + m] = hh == 0 ? th[m] : tot[rb + m] + th[m];
-                                }
-                            } else {
+                            {
                                 float th[MR];
 #pragma unroll
                                 for (int m = 0; m < MR; ++m)
@@ -694,82 +761,103 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                         }
                     }
                 }
+                PROF_MARK(2);
                 bar_output_warps();  // sflag may be written again only after everyone has read it
             }
             if (ow == 0) PROF_ADD(17);
             if (!finish) continue;
 
             // ------------------------------------------------------------ the output stage of one panel
-            // the block-float factor of this thread's group
-            if constexpr (FMT != TKD_BF16) {
-                // 2^e in two factors, each a normal float (e is within -69 .. 189)
-                const int e = ebyte + 64 - (FMT == TKD_BFP8 ? 133 : 129);
-                const int e1 = e / 2, e2 = e - e1;
-                const float f1 = __uint_as_float((uint32_t)(e1 + 127) << 23), f2 = __uint_as_float((uint32_t)(e2 + 127) << 23);
-#pragma unroll
-                for (int m = 0; m < MR; ++m) tot[m] = tot[m] * f1 * f2;
-            }
-            if (p.scale_dt != TKD_DT_NONE && in_w) {
-#pragma unroll
-                for (int m = 0; m < MR; ++m) tot[m] *= sc;
-            }
+            // (a generic lambda over the rows it covers: a one-row call runs the one-row instance, a fraction of the code
+            // of the eight-, sixteen- or thirty-two-row one; this code runs once or twice a CTA, straight from the
+            // instruction cache's misses, so its length is its cost)
             uint16_t* y16 = static_cast<uint16_t*>(p.out);
-            int ocol = -1;  // the output column this thread writes, if any
-            if (p.epi == TKD_EPI_GLU_IL || glu2) {
-                float* tc = tbuf + (size_t)et * MP;
-#pragma unroll
-                for (int m = 0; m < MR; m += 4)
-                    *reinterpret_cast<float4*>(tc + m) = make_float4(tot[m], tot[m + 1], tot[m + 2], tot[m + 3]);
-                bar_output_warps();
-                if (et < 64) {
-                    // interleaved: 32 gate columns, then their 32 up columns; two weights: gate 0-63, up 64-127
-                    const int gc = glu2 ? et : 64 * (et >> 5) + (et & 31), uc = glu2 ? et + 64 : gc + 32;
-                    const int nw = glu2 ? n : c.pl * TKD_PANEL_COLS + uc;  // the pair's last column in the weight
-                    if (nw < sg.n_valid) ocol = sg.out_col0 + c.pl * 64 + et;
-                    const float* gp = tbuf + (size_t)gc * MP;
-                    const float* up = tbuf + (size_t)uc * MP;
-#pragma unroll
-                    for (int m = 0; m < MR; ++m) tot[m] = act_gate(gp[m], p.act) * up[m];
+            auto output_stage = [&](auto rows_const) {
+                constexpr int R = decltype(rows_const)::value;
+                // the block-float factor of this thread's group
+                if constexpr (FMT != TKD_BF16) {
+                    // 2^e in two factors, each a normal float (e is within -69 .. 189)
+                    const int e = ebyte + 64 - (FMT == TKD_BFP8 ? 133 : 129);
+                    const int e1 = e / 2, e2 = e - e1;
+                    const float f1 = __uint_as_float((uint32_t)(e1 + 127) << 23), f2 = __uint_as_float((uint32_t)(e2 + 127) << 23);
+    #pragma unroll
+                    for (int m = 0; m < R; ++m) tot[m] = tot[m] * f1 * f2;
                 }
-                bar_output_warps();  // tbuf is free again
-            } else if (in_w) {
-                ocol = sg.out_col0 + n;
-            }
-            const bool store = ocol >= 0 && (p.topk_k == 0 || p.write_y);
-            if (ocol >= 0) {
-                if (p.epi == TKD_EPI_OUT32) {
-                    float* y32 = static_cast<float*>(p.out);
-#pragma unroll
-                    for (int m = 0; m < MR; ++m)
-                        if (m < M) {
-                            float v = tot[m];
-                            if (p.res_dt == TKD_DT_F32) v += static_cast<const float*>(p.res)[(size_t)m * p.ldr + ocol];
-                            y32[(size_t)m * p.ldo + ocol] = v;
-#pragma unroll
-                            for (int q = 0; q < 7; ++q)
-                                if (q < p.npeers && p.peer_out[q])
-                                    static_cast<float*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = v;
+                if (p.scale_dt != TKD_DT_NONE && in_w) {
+    #pragma unroll
+                    for (int m = 0; m < R; ++m) tot[m] *= sc;
+                }
+                int ocol = -1;  // the output column this thread writes, if any
+                if (p.epi == TKD_EPI_GLU_IL || glu2) {
+                    float* tc = tbuf + (size_t)et * MP;
+    #pragma unroll
+                    for (int m = 0; m < R; ++m) tc[m] = tot[m];
+                    bar_output_warps();
+                    if (et < 64) {
+                        // interleaved: 32 gate columns, then their 32 up columns; two weights: gate 0-63, up 64-127
+                        const int gc = glu2 ? et : 64 * (et >> 5) + (et & 31), uc = glu2 ? et + 64 : gc + 32;
+                        const int nw = glu2 ? n : c.pl * TKD_PANEL_COLS + uc;  // the pair's last column in the weight
+                        if (nw < sg.n_valid) ocol = sg.out_col0 + c.pl * 64 + et;
+                        const float* gp = tbuf + (size_t)gc * MP;
+                        const float* up = tbuf + (size_t)uc * MP;
+    #pragma unroll
+                        for (int m = 0; m < R; ++m) tot[m] = act_gate(gp[m], p.act) * up[m];
+                    }
+                    bar_output_warps();  // tbuf is free again
+                } else if (in_w) {
+                    ocol = sg.out_col0 + n;
+                }
+                const bool store = ocol >= 0 && (p.topk_k == 0 || p.write_y);
+                if (ocol >= 0) {
+                    // (the residual is read for every row before anything is stored: the output may be the residual's own
+                    // memory, and loads placed after stores to what may be the same address would wait for each other row
+                    // by row)
+                    if (p.epi == TKD_EPI_OUT32) {
+                        if (p.res_dt == TKD_DT_F32) {
+    #pragma unroll
+                            for (int m = 0; m < R; ++m)
+                                if (m < M) tot[m] += static_cast<const float*>(p.res)[(size_t)m * p.ldr + ocol];
                         }
-                } else {
-#pragma unroll
-                    for (int m = 0; m < MR; ++m)
-                        if (m < M) {
-                            float v = tot[m];
-                            if (p.epi == TKD_EPI_RESIDUAL)
-                                v += bf16_bits_to_f32(static_cast<const uint16_t*>(p.res)[(size_t)m * p.ldr + ocol]);
-                            const uint16_t b = f32_to_bf16_bits(v);
-                            if (store) {
-                                y16[(size_t)m * p.ldo + ocol] = b;
-#pragma unroll
+                        float* y32 = static_cast<float*>(p.out);
+    #pragma unroll
+                        for (int m = 0; m < R; ++m)
+                            if (m < M) {
+                                y32[(size_t)m * p.ldo + ocol] = tot[m];
+    #pragma unroll
                                 for (int q = 0; q < 7; ++q)
                                     if (q < p.npeers && p.peer_out[q])
-                                        static_cast<uint16_t*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = b;
+                                        static_cast<float*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = tot[m];
                             }
-                            if (p.topk_k && !p.write_y && m < p.topk_rows) p.ytmp[(size_t)m * p.ld_ytmp + n] = b;
+                    } else {
+                        if (p.epi == TKD_EPI_RESIDUAL) {
+    #pragma unroll
+                            for (int m = 0; m < R; ++m)
+                                if (m < M)
+                                    tot[m] += bf16_bits_to_f32(static_cast<const uint16_t*>(p.res)[(size_t)m * p.ldr + ocol]);
                         }
+    #pragma unroll
+                        for (int m = 0; m < R; ++m)
+                            if (m < M) {
+                                const uint16_t b = f32_to_bf16_bits(tot[m]);
+                                if (store) {
+                                    y16[(size_t)m * p.ldo + ocol] = b;
+    #pragma unroll
+                                    for (int q = 0; q < 7; ++q)
+                                        if (q < p.npeers && p.peer_out[q])
+                                            static_cast<uint16_t*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = b;
+                                }
+                                if (p.topk_k && !p.write_y && m < p.topk_rows) p.ytmp[(size_t)m * p.ld_ytmp + n] = b;
+                            }
+                    }
                 }
-            }
+            };
+            if (M == 1)
+                output_stage(std::integral_constant<int, 1>{});
+            else
+                output_stage(std::integral_constant<int, MR>{});
             if (ow == 0) PROF_ADD(18);
+            PROF_MARK(3);
+            PROF_MARKS_OUT;
             if (p.topk_k == 0) continue;
 
             // ------------------------------------------------------------ top-k records: one per unit of columns,
