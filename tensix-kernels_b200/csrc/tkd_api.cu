@@ -125,6 +125,7 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     if (sms <= 0) sms = 148;
     if (a->max_ctas > 0 && a->max_ctas < sms) sms = a->max_ctas;
     L->grid = (int)(p.total_items < sms ? p.total_items : sms);
+    p.small = (p.total_items + 1) * (int64_t)(L->grid + 1) < (1ll << 32);
 
     // top-k
     p.topk_k = a->topk_k;

@@ -49,6 +49,7 @@ struct TkdParams {
     int64_t panel_bytes;  // bytes of one 128-column panel of the stream
     int total_panels;
     int64_t total_items;
+    int small;          // item counts times the grid fit 32 bits: the kernel divides in 32-bit arithmetic
     int epi, act;
     const void* scale;   // per output column of w (bf16 or f32), or null
     const void* scale2;  // the up weight's, GLU two-weight form

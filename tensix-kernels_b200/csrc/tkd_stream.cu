@@ -160,12 +160,18 @@ __device__ __forceinline__ float act_gate(float g, int act) {
     return g / (1.f + __expf(-u));
 }
 
+// Quotients of item counts: 32-bit arithmetic when the launch's numbers allow it (p.small): a 64-bit division is a long
+// subroutine on the GPU, and these sit on every CTA's way to its first copy and on the way to a panel's completion.
+__device__ __forceinline__ int64_t idiv(const TkdParams& p, int64_t num, int64_t den) {
+    return p.small ? (int64_t)((uint32_t)num / (uint32_t)den) : num / den;
+}
+
 // Where a role stands in its CTA's run of items.
 struct Cursor {
     int panel, slice, seg, pl;
 };
 __device__ __forceinline__ void cursor_init(Cursor& c, const TkdParams& p, int64_t it) {
-    c.panel = (int)(it / p.nslices);
+    c.panel = (int)idiv(p, it, p.nslices);
     c.slice = (int)(it - (int64_t)c.panel * p.nslices);
     c.seg = 0;
 #pragma unroll
@@ -374,7 +380,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
     __syncthreads();
 
     const int64_t T = p.total_items;
-    const int64_t i0 = T * blockIdx.x / gridDim.x, i1 = T * (blockIdx.x + 1) / gridDim.x;
+    const int64_t i0 = idiv(p, T * blockIdx.x, gridDim.x), i1 = idiv(p, T * (blockIdx.x + 1), gridDim.x);
     const int nst = p.nstages;
     const int M = p.M, K = p.K;
     const bool glu2 = p.epi == TKD_EPI_GLU2;
@@ -384,7 +390,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
     // Order of a CTA's items: if its run ends inside a panel that it holds from slice 0 on, those slices come first.
     // Their sum is one of several the panel is added up from by whichever CTA delivers last; done first, that exchange
     // overlaps the rest of the run instead of sitting at the kernel's end.
-    const int64_t lastp0 = (i1 - 1) / p.nslices * p.nslices;
+    const int64_t lastp0 = idiv(p, i1 - 1, p.nslices) * p.nslices;
     const int64_t tail0 = lastp0 > i0 && lastp0 + p.nslices > i1 ? lastp0 : i1;
     const int64_t lead = i1 - tail0;
 
@@ -490,7 +496,8 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
         const uint32_t code_off = g8 * (F::SUBSA * F::SAB) + h0 * F::SAB + EXPB + lane * 16;
         const uint32_t exp_off = g8 * (F::SUBSA * F::SAB) + h0 * F::SAB + t * (EXPB / 4);
         uint32_t slot = 0, phase = 0, pi = 0;  // ring position and its parity; deliveries so far
-        int kc = (int)((lead > 0 ? tail0 : i0) % p.nslices) * p.ks;
+        const int64_t first_it = lead > 0 ? tail0 : i0;
+        int kc = (int)(first_it - idiv(p, first_it, p.nslices) * p.nslices) * p.ks;
         float acc[NH][NA][MT][4], tot[NH][MT][4];
         if constexpr (XS) load_x(0, kc);
         while (true) {
@@ -684,8 +691,8 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                 if (finish) {
                     // the panel's first slices came as one sum from the CTA that holds its slice 0: up to where?
                     const int64_t pfirst = (int64_t)c.panel * p.nslices;
-                    const int64_t owner = ((pfirst + 1) * gridDim.x - 1) / T;
-                    const int64_t oend = T * (owner + 1) / gridDim.x;
+                    const int64_t owner = idiv(p, (pfirst + 1) * gridDim.x - 1, T);
+                    const int64_t oend = idiv(p, T * (owner + 1), gridDim.x);
                     const int pe = (int)min((int64_t)p.nslices, oend - pfirst);
                     const float* s0 = p.scratch + pfirst * 2 * M * TKD_PANEL_COLS + et;
                     // term (s, hh, m) of the sums; the adds run in slice order, the loads many at a time
