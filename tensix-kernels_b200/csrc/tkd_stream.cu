@@ -138,7 +138,7 @@ __device__ __noinline__ bool flags_wait(const uint32_t* flags, int nranks, uint3
     for (int r = 0; r < nranks; ++r) {
         int rounds = 0;
         while ((int32_t)(ld_acquire_sys(flags + r) - seq) < 0) {
-            if (++rounds > (1 << 22)) return false;
+            if (++rounds > (1 << 20)) return false;  // (about a microsecond a round)
             __nanosleep(rounds < 64 ? 20 : 200);
         }
     }

@@ -100,6 +100,29 @@ def test_records_reach_every_rank(device):
     linear.check_status(device)
 
 
+def test_wait_gives_up_and_reports(device):
+    """A wait for a rank that never reports runs out (about a second) and writes TKD_ERR_TIMEOUT to the status word;
+    the kernel returns, the context stays usable, and the same wait succeeds once the flag is there."""
+    import ctypes
+
+    from dense_reader import _tkd
+
+    flags = torch.zeros(_tkd.FLAG_WORDS, dtype=torch.int32, device=device.torch)
+    flags[_tkd.FLAG_SEQ] = 1  # this rank has completed one exchanged call ...
+    flags[0] = 1              # ... and said so; rank 1 never does
+    status = torch.zeros(1, dtype=torch.int32, device=device.torch)
+    sp = torch.cuda.current_stream().cuda_stream
+    _tkd.check(_tkd.lib().tkd_exchange_wait(flags.data_ptr(), 2, status.data_ptr(), sp), "tkd_exchange_wait")
+    torch.cuda.synchronize()
+    assert int(status.item()) == _tkd.ERR_TIMEOUT
+    status.zero_()
+    flags[1] = 1
+    _tkd.check(_tkd.lib().tkd_exchange_wait(flags.data_ptr(), 2, status.data_ptr(), sp), "tkd_exchange_wait")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert ctypes.c_int(_tkd.lib().tkd_exchange_wait(None, 2, None, sp)).value == 1  # bad argument, nothing launched
+
+
 def test_peer_memory_alloc_view_free(device):
     import ctypes
 
