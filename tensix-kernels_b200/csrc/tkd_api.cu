@@ -69,15 +69,15 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     const int mt = a->m <= 8 ? 1 : (a->m <= 16 ? 2 : 4);
     const int sab = tkd_sab(a->fmt);
     const int chunk_k = tkd_chunk_k(a->fmt);
-    // k per slice: a function of K, the format and the row count only (a column's sum must not depend on anything
-    // else). One row: 1024 (less for a short K), so that the items divide well among the CTAs. More rows: a quarter of
-    // K if that is more (at most 4096): every slice a panel is cut into is another M x 128 sums through the scratch
-    // buffer for the CTA that adds the panel up, which costs more than the coarser split loses in balance.
+    // k per slice: a function of K and the format only (a column's sum must not depend on anything else). 1024 (less
+    // for a short K) divides the items well among the CTAs; but every slice a panel is cut into is another M x 128 sums
+    // through the scratch buffer for the CTA that adds the panel up, and another hand-over: a long K is cut into four
+    // slices, at most 4096 each (config 3, K 14336, one row: 18.8 us with 1024, 16.4 with 1792, 15.6 with 3584).
     int ks_k = a->k >= 4096 ? 1024 : (a->k >= 2048 ? 512 : 256);
-    if (a->m >= 2) {
-        int quarter = (int)((a->k / 4 + chunk_k - 1) / chunk_k) * chunk_k;
-        if (quarter > 4096) quarter = 4096;
-        if (quarter > ks_k) ks_k = quarter;
+    {
+        int part = (int)((a->k / 4 + chunk_k - 1) / chunk_k) * chunk_k;
+        if (part > 4096) part = 4096;
+        if (part > ks_k) ks_k = part;
     }
     p.ks = a->ks ? a->ks : (ks_k < chunk_k ? chunk_k : ks_k);
     if (p.ks < chunk_k || p.ks % chunk_k || p.ks > 4096) return TKD_ERR_BAD_ARG;

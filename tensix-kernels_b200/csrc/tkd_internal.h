@@ -20,7 +20,10 @@ int tkd_launch_unpack(int fmt, int64_t K, int64_t npad, const void* stream, cons
 #ifndef TKD_STREAM_WARPS_16ROWS
 #define TKD_STREAM_WARPS_16ROWS 8  // ... of the kernel for 9 to 16 rows (as for 32: measured faster than 16)
 #endif
-#define TKD_STREAM_WARPS_32ROWS 8  // ... of the kernel for 17 to 32 rows: a warp per column group, both halves
+#ifndef TKD_STREAM_WARPS_32ROWS
+#define TKD_STREAM_WARPS_32ROWS 8
+#endif
+//  // ... of the kernel for 17 to 32 rows: a warp per column group, both halves
 #define TKD_THREADS ((1 + TKD_STREAM_WARPS + 4) * 32)  // + 1 producer warp + 4 output warps
 #define TKD_PANEL_COLS 128     // columns one work item covers
 #define TKD_MAX_STAGES 16

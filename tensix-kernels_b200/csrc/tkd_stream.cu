@@ -352,7 +352,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
     // tiles of MR rows x one chunk of k, filled by the streaming warps' own asynchronous copies one stage ahead);
     // NPB: hand-over buffers between the streaming and the output warps
     constexpr int NH = 16 / SW;
-    constexpr bool XS = NH == 2 && FMT != TKD_BFP4;
+    constexpr bool XS = MT >= 2 && FMT != TKD_BFP4;
     constexpr int NPB = MT == 4 ? 1 : 2;
     volatile int* sflag = reinterpret_cast<volatile int*>(smem + TKD_SMEM_HEAD - 16);
     uint4* hdr = reinterpret_cast<uint4*>(smem + 512);  // one header per stage of the ring
@@ -463,7 +463,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
         const int g8 = cw & 7, h0 = SW == 16 ? cw >> 3 : 0;
         const int g = lane >> 2, t = lane & 3;
         constexpr int NX = F::SUBSA / 2 * F::XB;
-        constexpr bool PRE = MT <= 2 && NH == 1;
+        constexpr bool PRE = MT <= 2 && NH == 1 && !XS;
         constexpr int XROW = CK * 2, XTILE = MR * XROW, XPR = CK / 8;  // a tile row's bytes, a tile's, 16-byte pieces a row
         const uint32_t xt0 = smem_u32(smem + p.off_xt);
         // a tile row r keeps its 16-byte piece j at position j ^ swz(r): the eight lanes a shared-memory load serves
