@@ -1,8 +1,8 @@
 """gen_golden.py: makes tests/golden/*.npz from the reference's own host functions.
 
-Run in a container that has the reference checkout (its path as argv[1], default /root/reference):
+Run where the reference checkout is, with its path as the argument:
 
-    python tests/golden/gen_golden.py [/path/to/tensix-kernels]
+    python tests/golden/gen_golden.py /path/to/tensix-kernels
 
 The reference's modules import ttnn at the top; a MagicMock stands in for it, which is enough for the pure-host
 functions used here: moe.moe8.bfp4_tiles / bfp4_values (the only in-tree statement of the block-float quantiser, pinned
@@ -19,7 +19,9 @@ from unittest.mock import MagicMock
 import numpy as np
 import torch
 
-ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/gen_golden.py /path/to/tensix-kernels")
+ref = Path(sys.argv[1])
 sys.modules["ttnn"] = MagicMock()
 sys.path.insert(0, str(ref))
 from common import device as cdev  # noqa: E402
