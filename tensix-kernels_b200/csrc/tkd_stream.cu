@@ -655,7 +655,19 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             PROF_MARK(0);
             if (ow == 0) PROF_ADD(16);
             bool finish = !f.split;
-            if (!f.split) {
+            // (9 rows and more: the column's sums live in the thread's row of tbuf, not in registers, and every loop over
+            // rows below is rolled: this code runs once or twice a CTA, at the speed of instruction cache misses, and
+            // unrolled over 32 rows it is thousands of instructions)
+            float* const trow = tbuf + (size_t)et * MP;
+            if (!f.split && MT >= 2) {
+                const float* p0 = pbuf + ((size_t)(pb * 2) * TKD_PANEL_COLS + et) * MP;
+                const float* p1 = p0 + (size_t)TKD_PANEL_COLS * MP;
+#pragma unroll 1
+                for (int m = 0; m < MR; m += 4) {
+                    const float4 a = *reinterpret_cast<const float4*>(p0 + m), b = *reinterpret_cast<const float4*>(p1 + m);
+                    *reinterpret_cast<float4*>(trow + m) = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+                }
+            } else if (!f.split) {
                 // the two halves' sums cover the whole panel
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
@@ -712,37 +724,36 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                         }
                         tot[0] = t0 + t1;
                     } else if constexpr (MT >= 2) {
-                        // RB rows at a time; both halves' loads of four entries (the sum so far counts as one) in flight
-                        // together, unconditional (a row or entry that is not there re-reads the last that is) so that
-                        // they stay one block of code. (32 rows: four rows at a time, or the loads' registers do not fit
-                        // beside the 32 sums and the compiler takes them a few at a time.)
-                        constexpr int RB = MT == 4 ? 4 : 8;
-#pragma unroll
-                        for (int rb = 0; rb < MR; rb += RB) {
-                            if (rb >= M) break;
-                            float th[2][RB];
+                        // eight rows at a time (a rolled loop, the sums into tbuf); both halves' loads of four entries
+                        // (the sum so far counts as one) in flight together, unconditional (a row or entry that is not
+                        // there re-reads the last that is) so that they stay one block of code
+#pragma unroll 1
+                        for (int rb = 0; rb < M; rb += 8) {
+                            float th[2][8];
 #pragma unroll 1
                             for (int s = pe - 1; s < p.nslices; s += 4) {
-                                float v[2][4][RB];
+                                float v[2][4][8];
 #pragma unroll
                                 for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
                                     for (int j = 0; j < 4; ++j)
 #pragma unroll
-                                        for (int m = 0; m < RB; ++m)
+                                        for (int m = 0; m < 8; ++m)
                                             v[hh][j][m] = term(min(s + j, p.nslices - 1), hh, min(rb + m, M - 1));
 #pragma unroll
                                 for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
                                     for (int j = 0; j < 4; ++j)
 #pragma unroll
-                                        for (int m = 0; m < RB; ++m) {
+                                        for (int m = 0; m < 8; ++m) {
                                             if (s + j >= p.nslices) continue;
                                             th[hh][m] = s + j == pe - 1 ? v[hh][j][m] : th[hh][m] + v[hh][j][m];
                                         }
                             }
-#pragma unroll
-                            for (int m = 0; m < RB; ++m) tot[rb + m] = th[0][m] + th[1][m];
+                            *reinterpret_cast<float4*>(trow + rb) =
+                                make_float4(th[0][0] + th[1][0], th[0][1] + th[1][1], th[0][2] + th[1][2], th[0][3] + th[1][3]);
+                            *reinterpret_cast<float4*>(trow + rb + 4) =
+                                make_float4(th[0][4] + th[1][4], th[0][5] + th[1][5], th[0][6] + th[1][6], th[0][7] + th[1][7]);
                         }
                     } else {
 #pragma unroll 1
@@ -858,10 +869,82 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                     }
                 }
             };
-            if (M == 1)
+            if constexpr (MT >= 2) {
+                // the same stage from the sums in tbuf, eight rows at a time in a rolled loop
+                float colf = 1.f, colg = 1.f;  // the column's block-float factor (in two normal floats) and its scale
+                if constexpr (FMT != TKD_BF16) {
+                    const int e = ebyte + 64 - (FMT == TKD_BFP8 ? 133 : 129);
+                    const int e1 = e / 2, e2 = e - e1;
+                    colf = __uint_as_float((uint32_t)(e1 + 127) << 23), colg = __uint_as_float((uint32_t)(e2 + 127) << 23);
+                }
+                const float cols = p.scale_dt != TKD_DT_NONE && in_w ? sc : 1.f;
+                const bool glu = p.epi == TKD_EPI_GLU_IL || glu2;
+                int ocol = -1;
+                const float *gp = trow, *up = trow;
+                if (glu) {
+                    // every column's sums scaled in place, then the (gate, up) pairs read across columns
+#pragma unroll 1
+                    for (int m = 0; m < MR; m += 4) {
+                        float4 v = *reinterpret_cast<float4*>(trow + m);
+                        v.x = v.x * colf * colg * cols, v.y = v.y * colf * colg * cols;
+                        v.z = v.z * colf * colg * cols, v.w = v.w * colf * colg * cols;
+                        *reinterpret_cast<float4*>(trow + m) = v;
+                    }
+                    bar_output_warps();
+                    if (et < 64) {
+                        const int gc = glu2 ? et : 64 * (et >> 5) + (et & 31), uc = glu2 ? et + 64 : gc + 32;
+                        const int nw = glu2 ? n : c.pl * TKD_PANEL_COLS + uc;
+                        if (nw < sg.n_valid) ocol = sg.out_col0 + c.pl * 64 + et;
+                        gp = tbuf + (size_t)gc * MP, up = tbuf + (size_t)uc * MP;
+                    }
+                } else if (in_w) {
+                    ocol = sg.out_col0 + n;
+                }
+                const bool store = ocol >= 0 && (p.topk_k == 0 || p.write_y);
+                if (ocol >= 0) {
+#pragma unroll 1
+                    for (int r0 = 0; r0 < M; r0 += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int m = 0; m < 8; ++m)
+                            v[m] = glu ? act_gate(gp[r0 + m], p.act) * up[r0 + m] : trow[r0 + m] * colf * colg * cols;
+                        // (the residual is read for all eight rows before anything is stored: see the one-row form)
+                        if (p.epi == TKD_EPI_OUT32 && p.res_dt == TKD_DT_F32) {
+#pragma unroll
+                            for (int m = 0; m < 8; ++m)
+                                if (r0 + m < M) v[m] += static_cast<const float*>(p.res)[(size_t)(r0 + m) * p.ldr + ocol];
+                        } else if (p.epi == TKD_EPI_RESIDUAL) {
+#pragma unroll
+                            for (int m = 0; m < 8; ++m)
+                                if (r0 + m < M)
+                                    v[m] += bf16_bits_to_f32(static_cast<const uint16_t*>(p.res)[(size_t)(r0 + m) * p.ldr + ocol]);
+                        }
+#pragma unroll
+                        for (int m = 0; m < 8; ++m) {
+                            if (r0 + m >= M) break;
+                            const size_t at = (size_t)(r0 + m) * p.ldo + ocol;
+                            if (p.epi == TKD_EPI_OUT32) {
+                                static_cast<float*>(p.out)[at] = v[m];
+                                for (int q = 0; q < p.npeers; ++q)
+                                    if (p.peer_out[q]) static_cast<float*>(p.peer_out[q])[at] = v[m];
+                            } else {
+                                const uint16_t b = f32_to_bf16_bits(v[m]);
+                                if (store) {
+                                    y16[at] = b;
+                                    for (int q = 0; q < p.npeers; ++q)
+                                        if (p.peer_out[q]) static_cast<uint16_t*>(p.peer_out[q])[at] = b;
+                                }
+                                if (p.topk_k && !p.write_y && r0 + m < p.topk_rows) p.ytmp[(size_t)(r0 + m) * p.ld_ytmp + n] = b;
+                            }
+                        }
+                    }
+                }
+                if (glu) bar_output_warps();  // tbuf is free again
+            } else if (M == 1) {
                 output_stage(std::integral_constant<int, 1>{});
-            else
+            } else {
                 output_stage(std::integral_constant<int, MR>{});
+            }
             if (ow == 0) PROF_ADD(18);
             PROF_MARK(3);
             PROF_MARKS_OUT;
