@@ -338,7 +338,10 @@ __device__ __forceinline__ uint32_t topk_key(uint16_t b) {
 
 // SW: streaming warps, 16 (a warp per column group and half of each chunk's super-atoms) or 8 (a warp takes both halves
 // of its group, one after the other: the 32-row kernel, whose accumulators need the registers that fewer warps leave).
-template <int FMT, int MT, int SW>
+// ONE: the call has one row (the decode case): the row count is a constant 1 and everything that serves more rows falls
+// away at compile time. (The length of this kernel's code matters beyond the parts that run: adding two more instances
+// of the output stage for 2 and 4 rows made the one-row call 1.5 us slower.)
+template <int FMT, int MT, int SW, bool ONE>
 __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const __grid_constant__ TkdParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     using F = Fmt<FMT>;
@@ -382,7 +385,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
     const int64_t T = p.total_items;
     const int64_t i0 = idiv(p, T * blockIdx.x, gridDim.x), i1 = idiv(p, T * (blockIdx.x + 1), gridDim.x);
     const int nst = p.nstages;
-    const int M = p.M, K = p.K;
+    const int M = ONE ? 1 : p.M, K = p.K;
     const bool glu2 = p.epi == TKD_EPI_GLU2;
     constexpr int CK = F::SUBSA * F::KSA;
     const int nsa_total = (K + F::KSA - 1) / F::KSA;
@@ -1053,9 +1056,9 @@ __global__ void tkd_exchange_wait_kernel(uint32_t* flags, int nranks, int* statu
     }
 }
 
-template <int FMT, int MT, int SW>
+template <int FMT, int MT, int SW, bool ONE = false>
 int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = tkd_stream_kernel<FMT, MT, SW>;
+    auto kern = tkd_stream_kernel<FMT, MT, SW, ONE>;
     // (once per device and instantiation: allow the largest dynamic shared memory a CTA can have)
     static bool allowed[64] = {false};
     int dev = 0;
@@ -1085,6 +1088,7 @@ int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
 
 template <int FMT>
 int launch_fmt(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
+    if (p.M == 1) return launch_one<FMT, 1, 16, true>(p, grid, smem, st);
     if (p.M <= 8) return launch_one<FMT, 1, 16>(p, grid, smem, st);
     if (p.M <= 16) return launch_one<FMT, 2, TKD_STREAM_WARPS_16ROWS>(p, grid, smem, st);
     return launch_one<FMT, 4, TKD_STREAM_WARPS_32ROWS>(p, grid, smem, st);
