@@ -341,7 +341,8 @@ __device__ __forceinline__ uint32_t topk_key(uint16_t b) {
 // ONE: the call has one row (the decode case): the row count is a constant 1 and everything that serves more rows falls
 // away at compile time. (The length of this kernel's code matters beyond the parts that run: adding two more instances
 // of the output stage for 2 and 4 rows made the one-row call 1.5 us slower.)
-template <int FMT, int MT, int SW, bool ONE>
+// PLAIN: no top-k records and no exchange with other GPUs (the plain matmuls of a decode step): that code falls away too.
+template <int FMT, int MT, int SW, bool ONE, bool PLAIN>
 __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const __grid_constant__ TkdParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     using F = Fmt<FMT>;
@@ -386,6 +387,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
     const int64_t i0 = idiv(p, T * blockIdx.x, gridDim.x), i1 = idiv(p, T * (blockIdx.x + 1), gridDim.x);
     const int nst = p.nstages;
     const int M = ONE ? 1 : p.M, K = p.K;
+    const int topk_k = PLAIN ? 0 : p.topk_k, npeers = PLAIN ? 0 : p.npeers;
     const bool glu2 = p.epi == TKD_EPI_GLU2;
     constexpr int CK = F::SUBSA * F::KSA;
     const int nsa_total = (K + F::KSA - 1) / F::KSA;
@@ -828,7 +830,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                 } else if (in_w) {
                     ocol = sg.out_col0 + n;
                 }
-                const bool store = ocol >= 0 && (p.topk_k == 0 || p.write_y);
+                const bool store = ocol >= 0 && (topk_k == 0 || p.write_y);
                 if (ocol >= 0) {
                     // (the residual is read for every row before anything is stored: the output may be the residual's own
                     // memory, and loads placed after stores to what may be the same address would wait for each other row
@@ -846,7 +848,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                                 y32[(size_t)m * p.ldo + ocol] = tot[m];
     #pragma unroll
                                 for (int q = 0; q < 7; ++q)
-                                    if (q < p.npeers && p.peer_out[q])
+                                    if (q < npeers && p.peer_out[q])
                                         static_cast<float*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = tot[m];
                             }
                     } else {
@@ -864,10 +866,10 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                                     y16[(size_t)m * p.ldo + ocol] = b;
     #pragma unroll
                                     for (int q = 0; q < 7; ++q)
-                                        if (q < p.npeers && p.peer_out[q])
+                                        if (q < npeers && p.peer_out[q])
                                             static_cast<uint16_t*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = b;
                                 }
-                                if (p.topk_k && !p.write_y && m < p.topk_rows) p.ytmp[(size_t)m * p.ld_ytmp + n] = b;
+                                if (topk_k && !p.write_y && m < p.topk_rows) p.ytmp[(size_t)m * p.ld_ytmp + n] = b;
                             }
                     }
                 }
@@ -903,7 +905,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                 } else if (in_w) {
                     ocol = sg.out_col0 + n;
                 }
-                const bool store = ocol >= 0 && (p.topk_k == 0 || p.write_y);
+                const bool store = ocol >= 0 && (topk_k == 0 || p.write_y);
                 if (ocol >= 0) {
 #pragma unroll 1
                     for (int r0 = 0; r0 < M; r0 += 8) {
@@ -928,16 +930,16 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                             const size_t at = (size_t)(r0 + m) * p.ldo + ocol;
                             if (p.epi == TKD_EPI_OUT32) {
                                 static_cast<float*>(p.out)[at] = v[m];
-                                for (int q = 0; q < p.npeers; ++q)
+                                for (int q = 0; q < npeers; ++q)
                                     if (p.peer_out[q]) static_cast<float*>(p.peer_out[q])[at] = v[m];
                             } else {
                                 const uint16_t b = f32_to_bf16_bits(v[m]);
                                 if (store) {
                                     y16[at] = b;
-                                    for (int q = 0; q < p.npeers; ++q)
+                                    for (int q = 0; q < npeers; ++q)
                                         if (p.peer_out[q]) static_cast<uint16_t*>(p.peer_out[q])[at] = b;
                                 }
-                                if (p.topk_k && !p.write_y && r0 + m < p.topk_rows) p.ytmp[(size_t)(r0 + m) * p.ld_ytmp + n] = b;
+                                if (topk_k && !p.write_y && r0 + m < p.topk_rows) p.ytmp[(size_t)(r0 + m) * p.ld_ytmp + n] = b;
                             }
                         }
                     }
@@ -951,7 +953,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             if (ow == 0) PROF_ADD(18);
             PROF_MARK(3);
             PROF_MARKS_OUT;
-            if (p.topk_k == 0) continue;
+            if (topk_k == 0) continue;
 
             // ------------------------------------------------------------ top-k records: one per unit of columns,
             // made by the CTA that completes the unit's last panel, from the bf16 outputs themselves
@@ -975,7 +977,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             const int64_t ldy = p.write_y ? p.ldo : p.ld_ytmp;
             const int col0 = unit * p.topk_unit;  // the unit's first column (call-relative)
             uint32_t* red = reinterpret_cast<uint32_t*>(tbuf);
-            const size_t rec_at = (size_t)(p.topk_slot0 + unit) * 2 * p.topk_rows * p.topk_k;
+            const size_t rec_at = (size_t)(p.topk_slot0 + unit) * 2 * p.topk_rows * topk_k;
             uint32_t* rec = p.records + rec_at;
             for (int r = 0; r < p.topk_rows; ++r) {
                 // candidates: (key << 16 | 0xFFFF - position in unit) orders by key descending, then column ascending;
@@ -990,7 +992,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                     cand[j] = key ? (key << 16) | (0xFFFFu - (uint32_t)cc) : 0u;
                 }
                 uint32_t bound = 0xFFFFFFFFu;
-                for (int q = 0; q < p.topk_k; ++q) {
+                for (int q = 0; q < topk_k; ++q) {
                     uint32_t best = 0;
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
@@ -1005,12 +1007,12 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                     if (et == 0) {
                         const uint32_t key = best >> 16;
                         const uint32_t idx = best ? p.topk_base + (uint32_t)col0 + (0xFFFFu - (best & 0xFFFFu)) : 0xFFFFFFFFu;
-                        const int at_k = r * p.topk_k + q, at_i = (p.topk_rows + r) * p.topk_k + q;
+                        const int at_k = r * topk_k + q, at_i = (p.topk_rows + r) * topk_k + q;
                         rec[at_k] = key;
                         rec[at_i] = idx;
 #pragma unroll
                         for (int pq = 0; pq < 7; ++pq)
-                            if (pq < p.npeers && p.peer_records[pq]) {
+                            if (pq < npeers && p.peer_records[pq]) {
                                 p.peer_records[pq][rec_at + at_k] = key;
                                 p.peer_records[pq][rec_at + at_i] = idx;
                             }
@@ -1019,7 +1021,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             }
         }
         if (ow == 0) PROF_TIME(2);
-        if (p.npeers) {
+        if (npeers) {
             // Exchange: every output warp counts itself in once its stores are ordered GPU-wide (a cheap fence). The
             // warp that counts last orders all of them system-wide with the call's ONE system fence (system fences
             // serialise across the GPU: one per warp cost this kernel a third of its run), numbers the call and writes
@@ -1034,10 +1036,10 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                     const uint32_t seq = p.flags[TKD_FLAG_SEQ] + 1;
                     p.flags[TKD_FLAG_SEQ] = seq;
                     __threadfence_system();
-                    for (int q = 0; q < p.npeers; ++q) st_relaxed_sys(p.peer_flags[q] + p.rank, seq);
+                    for (int q = 0; q < npeers; ++q) st_relaxed_sys(p.peer_flags[q] + p.rank, seq);
                     st_relaxed_sys(p.flags + p.rank, seq);
                     // (2: the call before this one, whose exchange has had this call's whole run to arrive)
-                    if (p.exchange_wait && !flags_wait(p.flags, p.npeers + 1, p.exchange_wait == 2 ? seq - 1 : seq)) {
+                    if (p.exchange_wait && !flags_wait(p.flags, npeers + 1, p.exchange_wait == 2 ? seq - 1 : seq)) {
                         if (p.status) atomicExch(p.status, TKD_ERR_TIMEOUT);
                     }
                 }
@@ -1056,9 +1058,9 @@ __global__ void tkd_exchange_wait_kernel(uint32_t* flags, int nranks, int* statu
     }
 }
 
-template <int FMT, int MT, int SW, bool ONE = false>
+template <int FMT, int MT, int SW, bool ONE = false, bool PLAIN = false>
 int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = tkd_stream_kernel<FMT, MT, SW, ONE>;
+    auto kern = tkd_stream_kernel<FMT, MT, SW, ONE, PLAIN>;
     // (once per device and instantiation: allow the largest dynamic shared memory a CTA can have)
     static bool allowed[64] = {false};
     int dev = 0;
@@ -1088,6 +1090,7 @@ int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
 
 template <int FMT>
 int launch_fmt(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
+    if (p.M == 1 && !p.topk_k && !p.npeers) return launch_one<FMT, 1, 16, true, true>(p, grid, smem, st);
     if (p.M == 1) return launch_one<FMT, 1, 16, true>(p, grid, smem, st);
     if (p.M <= 8) return launch_one<FMT, 1, 16>(p, grid, smem, st);
     if (p.M <= 16) return launch_one<FMT, 2, TKD_STREAM_WARPS_16ROWS>(p, grid, smem, st);
