@@ -342,7 +342,8 @@ __device__ __forceinline__ uint32_t topk_key(uint16_t b) {
 // away at compile time. (The length of this kernel's code matters beyond the parts that run: adding two more instances
 // of the output stage for 2 and 4 rows made the one-row call 1.5 us slower.)
 // PLAIN: no top-k records and no exchange with other GPUs (the plain matmuls of a decode step): that code falls away too.
-template <int FMT, int MT, int SW, bool ONE, bool PLAIN>
+// KWHOLE: K is a whole number of chunks, so the code for a last, shorter chunk falls away as well.
+template <int FMT, int MT, int SW, bool ONE, bool PLAIN, bool KWHOLE>
 __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const __grid_constant__ TkdParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     using F = Fmt<FMT>;
@@ -506,7 +507,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
         float acc[NH][NA][MT][4], tot[NH][MT][4];
         if constexpr (XS) load_x(0, kc);
         while (true) {
-            const bool full = kc + CK <= K;
+            const bool full = KWHOLE || kc + CK <= K;
             uint4 xpre[NX][MT];
             if (PRE && full) {
 #pragma unroll
@@ -1058,9 +1059,9 @@ __global__ void tkd_exchange_wait_kernel(uint32_t* flags, int nranks, int* statu
     }
 }
 
-template <int FMT, int MT, int SW, bool ONE = false, bool PLAIN = false>
+template <int FMT, int MT, int SW, bool ONE = false, bool PLAIN = false, bool KWHOLE = false>
 int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = tkd_stream_kernel<FMT, MT, SW, ONE, PLAIN>;
+    auto kern = tkd_stream_kernel<FMT, MT, SW, ONE, PLAIN, KWHOLE>;
     // (once per device and instantiation: allow the largest dynamic shared memory a CTA can have)
     static bool allowed[64] = {false};
     int dev = 0;
@@ -1088,13 +1089,20 @@ int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
     return (int)cudaLaunchKernelEx(&cfg, kern, p);
 }
 
+template <int FMT, bool KWHOLE>
+int launch_rows(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
+    if (p.M == 1 && !p.topk_k && !p.npeers) return launch_one<FMT, 1, 16, true, true, KWHOLE>(p, grid, smem, st);
+    if (p.M == 1) return launch_one<FMT, 1, 16, true, false, KWHOLE>(p, grid, smem, st);
+    if (p.M <= 8) return launch_one<FMT, 1, 16, false, false, KWHOLE>(p, grid, smem, st);
+    if (p.M <= 16) return launch_one<FMT, 2, TKD_STREAM_WARPS_16ROWS, false, false, KWHOLE>(p, grid, smem, st);
+    return launch_one<FMT, 4, TKD_STREAM_WARPS_32ROWS, false, false, KWHOLE>(p, grid, smem, st);
+}
+
 template <int FMT>
 int launch_fmt(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    if (p.M == 1 && !p.topk_k && !p.npeers) return launch_one<FMT, 1, 16, true, true>(p, grid, smem, st);
-    if (p.M == 1) return launch_one<FMT, 1, 16, true>(p, grid, smem, st);
-    if (p.M <= 8) return launch_one<FMT, 1, 16>(p, grid, smem, st);
-    if (p.M <= 16) return launch_one<FMT, 2, TKD_STREAM_WARPS_16ROWS>(p, grid, smem, st);
-    return launch_one<FMT, 4, TKD_STREAM_WARPS_32ROWS>(p, grid, smem, st);
+    // (a K of whole chunks, the usual case, runs the instantiation without the code for a last, shorter chunk)
+    return p.K % (Fmt<FMT>::SUBSA * Fmt<FMT>::KSA) == 0 ? launch_rows<FMT, true>(p, grid, smem, st)
+                                                       : launch_rows<FMT, false>(p, grid, smem, st);
 }
 
 }  // namespace
