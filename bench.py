@@ -265,7 +265,8 @@ def main():
         wl["n"] = args.cols
     m = args.rows
     steps, warmup = args.steps, max(3, args.warmup)
-    config = {"workload": f"{args.workload}: {wl['what']}", "rows": m, "K": wl["k"], "N": wl["n"], "format": wl["fmt"]}
+    config = {"workload": f"{args.workload}: {wl['what']}", "rows": m, "K": wl["k"], "N": wl["n"], "format": wl["fmt"],
+              "arithmetic": "bf16 activations x block-float weights (exact products), fp32 accumulation"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -527,7 +528,7 @@ def main():
     line = {
         "metric": "weight_stream_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms / steps, "us_per_call": us_call, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
-        "dtype": "bf16 x block-float, fp32 accumulate", "data": "synthetic",
+        "dtype": "bf16", "data": "synthetic",
         "config": {**config, "l2": f"rotation over {copies} distinct packed weight sets ({copies * case['wbytes'] / 1e6:.0f} MB > 2 x L2)",
                    "timing": (f"CUDA graph of {steps} launches, {reps} replays, CUDA events" if graphed
                               else f"{steps} plain launches x {reps}, CUDA events"),

@@ -8,7 +8,7 @@
 // HBM-bound kernel:
 //   1. tkd_quantise_kernel: float32 -> canonical exps [K, G] and codes [K, Npad] (the same numbers the reference's
 //      tiles hold, before any re-layout; what the parity tests compare bit for bit);
-//   2. tkd_emax_kernel: per group of 16 columns the largest exponent of a row with a non-zero code;
+//   2. tkd_emax_kernel: per group of 16 columns the largest exponent of a row with a non-zero code (a block a group);
 //   3. tkd_permute_kernel: canonical -> stream, one thread per 32-bit word of the stream.
 // tkd_unpack_kernel is the inverse (stream -> float32 [K, Npad]), used for the weight's read-back.
 #include <cuda_bf16.h>
@@ -84,22 +84,34 @@ __device__ __forceinline__ bool row_nonzero(const uint8_t* codes, int64_t npad, 
     return (c.x | c.y | c.z | c.w) != 0;
 }
 
-// One thread per group: emax[g] = the largest exponent among its rows that hold a non-zero code (0: none). info[0] is
-// OR-ed with 1 when a non-zero row's exponent lies more than TKD_EBIAS - TKD_EMIN_OK below it (a "wide" weight).
-__global__ void tkd_emax_kernel(const uint8_t* __restrict__ exps, const uint8_t* __restrict__ codes, int64_t K,
-                                int64_t npad, uint8_t* __restrict__ emax, int* __restrict__ info) {
-    const int64_t G = npad / 16;
-    const int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    if (g >= G) return;
+// One block per group: emax[g] = the largest exponent among its rows that hold a non-zero code (0: none). info[0] is
+// OR-ed with 1 when a non-zero row's exponent lies more than TKD_EBIAS - TKD_EMIN_OK below it (a "wide" weight). The
+// block's threads share the rows of K out and reduce (maxima and minima: the order does not matter).
+constexpr int kEmaxThreads = 256;
+__global__ void __launch_bounds__(kEmaxThreads) tkd_emax_kernel(const uint8_t* __restrict__ exps,
+                                                               const uint8_t* __restrict__ codes, int64_t K, int64_t npad,
+                                                               uint8_t* __restrict__ emax, int* __restrict__ info) {
+    __shared__ int shi[kEmaxThreads / 32], slo[kEmaxThreads / 32];
+    const int64_t G = npad / 16, g = blockIdx.x;
     int hi = 0, lo = 255;
-    for (int64_t k = 0; k < K; ++k) {
+    for (int64_t k = threadIdx.x; k < K; k += kEmaxThreads) {
         if (!row_nonzero(codes, npad, k, g)) continue;
         const int e = exps[k * G + g];
         hi = max(hi, e);
         lo = min(lo, e);
     }
-    emax[g] = (uint8_t)hi;
-    if (lo <= hi && lo - hi + TKD_EBIAS < TKD_EMIN_OK) atomicOr(info, 1);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        hi = max(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, o));
+        lo = min(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, o));
+    }
+    if ((threadIdx.x & 31) == 0) shi[threadIdx.x >> 5] = hi, slo[threadIdx.x >> 5] = lo;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kEmaxThreads / 32; ++w) hi = max(hi, shi[w]), lo = min(lo, slo[w]);
+        emax[g] = (uint8_t)hi;
+        if (lo <= hi && lo - hi + TKD_EBIAS < TKD_EMIN_OK) atomicOr(info, 1);
+    }
 }
 
 // One thread per 32-bit word of the stream.
@@ -202,8 +214,7 @@ int tkd_launch_permute(int fmt, int64_t K, int64_t npad, const uint8_t* exps, co
                        int* info, void* stream, cudaStream_t st) {
     const int64_t G = npad / 16;
     if (fmt != TKD_BF16) {
-        tkd_emax_kernel<<<(unsigned)((G + 127) / 128), 128, 0, st>>>(exps, static_cast<const uint8_t*>(codes), K, npad,
-                                                                    emax, info);
+        tkd_emax_kernel<<<(unsigned)G, kEmaxThreads, 0, st>>>(exps, static_cast<const uint8_t*>(codes), K, npad, emax, info);
     }
     const int64_t words = tkd_stream_bytes(fmt, K, npad) / 4;
     tkd_permute_kernel<<<(unsigned)((words + 255) / 256), 256, 0, st>>>(fmt, K, npad, exps, codes, emax,
