@@ -64,23 +64,29 @@ __global__ void __launch_bounds__(kThreads) tkd_topk_merge_kernel(const uint32_t
     }
 }
 
-// The same for up to kWarpMax candidates a row (the LM head's 600): one warp, no block barriers. The candidates sit in
-// shared memory; every round each lane scans its share, then five shuffles.
+// The same for up to kWarpMax candidates a row (the LM head's 600). All the block's threads fetch the candidates into
+// shared memory at once (one round trip to memory); then one warp runs the rounds without block barriers: every round
+// each lane scans its share, then five shuffles.
 constexpr int kWarpMax = 1024;
-__global__ void __launch_bounds__(32) tkd_topk_merge_warp_kernel(const uint32_t* __restrict__ records, int nrec, int rows,
-                                                                 int k, int top, uint32_t* __restrict__ out) {
+__global__ void __launch_bounds__(kThreads) tkd_topk_merge_warp_kernel(const uint32_t* __restrict__ records, int nrec,
+                                                                       int rows, int k, int top, uint32_t* __restrict__ out) {
     __shared__ unsigned long long cands[kWarpMax];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int r = blockIdx.x, lane = threadIdx.x;
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
     const int n = nrec * k;
-    for (int c = lane; c < n; c += 32) {
-        const int rec = c / k, q = c - rec * k;
-        const uint32_t* page = records + (size_t)rec * 2 * rows * k;
-        const uint32_t key = __ldg(page + r * k + q), idx = __ldg(page + (rows + r) * k + q);
-        cands[c] = key ? ((unsigned long long)key << 32) | (uint32_t)~idx : 0ull;
+#pragma unroll
+    for (int j = 0; j < kWarpMax / kThreads; ++j) {
+        const int c = tid + j * kThreads;
+        if (c < n) {
+            const int rec = c / k, q = c - rec * k;
+            const uint32_t* page = records + (size_t)rec * 2 * rows * k;
+            const uint32_t key = __ldg(page + r * k + q), idx = __ldg(page + (rows + r) * k + q);
+            cands[c] = key ? ((unsigned long long)key << 32) | (uint32_t)~idx : 0ull;
+        }
     }
-    __syncwarp();
+    __syncthreads();
+    if (tid >= 32) return;
     unsigned long long bound = ~0ull;
     for (int t = 0; t < top; ++t) {
         unsigned long long best = 0;
@@ -114,7 +120,6 @@ int tkd_launch_topk_merge(const uint32_t* records, int nrec, int rows, int k, in
     cfg.attrs = attr;
     cfg.numAttrs = tkd_pdl_enabled() ? 1 : 0;
     if (nrec * k <= kWarpMax) {
-        cfg.blockDim = dim3(32);
         return (int)cudaLaunchKernelEx(&cfg, tkd_topk_merge_warp_kernel, records, nrec, rows, k, top, out);
     }
     return (int)cudaLaunchKernelEx(&cfg, tkd_topk_merge_kernel, records, nrec, rows, k, top, out);
