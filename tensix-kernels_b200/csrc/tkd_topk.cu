@@ -64,46 +64,42 @@ __global__ void __launch_bounds__(kThreads) tkd_topk_merge_kernel(const uint32_t
     }
 }
 
-// The same for up to kWarpMax candidates a row (the LM head's 600). All the block's threads fetch the candidates into
-// shared memory at once (one round trip to memory); then one warp runs the rounds without block barriers: every round
-// each lane scans its share, then five shuffles.
+// The same for up to kWarpMax candidates a row (the LM head's 600): one warp, the candidates in registers (32 a lane,
+// fetched with all their loads in flight), and per round two warp-wide reductions in hardware (redux.sync) instead of
+// ten shuffles: the largest key, then among the lanes holding it the largest ~index.
 constexpr int kWarpMax = 1024;
-__global__ void __launch_bounds__(kThreads) tkd_topk_merge_warp_kernel(const uint32_t* __restrict__ records, int nrec,
-                                                                       int rows, int k, int top, uint32_t* __restrict__ out) {
-    __shared__ unsigned long long cands[kWarpMax];
+__global__ void __launch_bounds__(32) tkd_topk_merge_warp_kernel(const uint32_t* __restrict__ records, int nrec, int rows,
+                                                                 int k, int top, uint32_t* __restrict__ out) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+    const int r = blockIdx.x, lane = threadIdx.x;
     const int n = nrec * k;
+    unsigned long long own[kWarpMax / 32];
 #pragma unroll
-    for (int j = 0; j < kWarpMax / kThreads; ++j) {
-        const int c = tid + j * kThreads;
+    for (int j = 0; j < kWarpMax / 32; ++j) {
+        const int c = lane + 32 * j;
+        own[j] = 0ull;
         if (c < n) {
             const int rec = c / k, q = c - rec * k;
             const uint32_t* page = records + (size_t)rec * 2 * rows * k;
             const uint32_t key = __ldg(page + r * k + q), idx = __ldg(page + (rows + r) * k + q);
-            cands[c] = key ? ((unsigned long long)key << 32) | (uint32_t)~idx : 0ull;
+            own[j] = key ? ((unsigned long long)key << 32) | (uint32_t)~idx : 0ull;
         }
     }
-    __syncthreads();
-    if (tid >= 32) return;
     unsigned long long bound = ~0ull;
     for (int t = 0; t < top; ++t) {
-        unsigned long long best = 0;
-        for (int c = lane; c < n; c += 32) {
-            const unsigned long long v = cands[c];
-            if (v < bound && v > best) best = v;
-        }
+        unsigned long long mine = 0;
 #pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
-            best = other > best ? other : best;
-        }
+        for (int j = 0; j < kWarpMax / 32; ++j)
+            if (own[j] < bound && own[j] > mine) mine = own[j];
+        const uint32_t key = __reduce_max_sync(0xFFFFFFFFu, (uint32_t)(mine >> 32));
+        const uint32_t low = __reduce_max_sync(0xFFFFFFFFu, key && (uint32_t)(mine >> 32) == key ? (uint32_t)mine : 0u);
+        const unsigned long long best = key ? ((unsigned long long)key << 32) | low : 0ull;
         if (lane == 0) {
-            out[r * top + t] = (uint32_t)(best >> 32);
-            out[(rows + r) * top + t] = best ? ~(uint32_t)best : 0xFFFFFFFFu;
+            out[r * top + t] = key;
+            out[(rows + r) * top + t] = best ? ~low : 0xFFFFFFFFu;
         }
-        bound = best;
+        bound = best;  // (0: nothing left; the remaining slots come out empty)
     }
 }
 
@@ -120,6 +116,7 @@ int tkd_launch_topk_merge(const uint32_t* records, int nrec, int rows, int k, in
     cfg.attrs = attr;
     cfg.numAttrs = tkd_pdl_enabled() ? 1 : 0;
     if (nrec * k <= kWarpMax) {
+        cfg.blockDim = dim3(32);
         return (int)cudaLaunchKernelEx(&cfg, tkd_topk_merge_warp_kernel, records, nrec, rows, k, top, out);
     }
     return (int)cudaLaunchKernelEx(&cfg, tkd_topk_merge_kernel, records, nrec, rows, k, top, out);
