@@ -577,7 +577,11 @@ def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, o
         tk = None if topk is None else (_raw(topk["r"]).data_ptr(), topk["k"], topk["rows"], topk["slot0"], topk["base"],
                                         topk["n"], bool(topk.get("write_y", False)), TOPK_UNIT)
         key = (
-            tuple((g.t.data_ptr(), u.t.data_ptr() if u is not None else 0, g.k, g.n, g.dtype, c0) for g, u, c0 in entries),
+            # (every address the descriptor holds: a freed weight's memory may come back as another weight's stream with
+            # its side array elsewhere)
+            tuple((g.t.data_ptr(), g.emax.data_ptr() if g.emax is not None else 0, u.t.data_ptr() if u is not None else 0,
+                   u.emax.data_ptr() if u is not None and u.emax is not None else 0, g.k, g.n, g.dtype, c0)
+                  for g, u, c0 in entries),
             m, tuple(xt.shape), tuple(yt.shape), epi, act, sc.data_ptr() if sc is not None else 0,
             sc_up.data_ptr() if sc_up is not None else 0, scale_dt, res_dt, tk, ks, max_ctas, device.id, id(exchange),
         )
