@@ -847,10 +847,9 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                         for (int m = 0; m < R; ++m)
                             if (m < M) {
                                 y32[(size_t)m * p.ldo + ocol] = tot[m];
-    #pragma unroll
-                                for (int q = 0; q < 7; ++q)
-                                    if (q < npeers && p.peer_out[q])
-                                        static_cast<float*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = tot[m];
+    #pragma unroll 1
+                                for (int q = 0; q < npeers; ++q)
+                                    if (p.peer_out[q]) static_cast<float*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = tot[m];
                             }
                     } else {
                         if (p.epi == TKD_EPI_RESIDUAL) {
@@ -865,10 +864,9 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                                 const uint16_t b = f32_to_bf16_bits(tot[m]);
                                 if (store) {
                                     y16[(size_t)m * p.ldo + ocol] = b;
-    #pragma unroll
-                                    for (int q = 0; q < 7; ++q)
-                                        if (q < npeers && p.peer_out[q])
-                                            static_cast<uint16_t*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = b;
+    #pragma unroll 1
+                                    for (int q = 0; q < npeers; ++q)
+                                        if (p.peer_out[q]) static_cast<uint16_t*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = b;
                                 }
                                 if (topk_k && !p.write_y && m < p.topk_rows) p.ytmp[(size_t)m * p.ld_ytmp + n] = b;
                             }
@@ -1011,9 +1009,9 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                         const int at_k = r * topk_k + q, at_i = (p.topk_rows + r) * topk_k + q;
                         rec[at_k] = key;
                         rec[at_i] = idx;
-#pragma unroll
-                        for (int pq = 0; pq < 7; ++pq)
-                            if (pq < npeers && p.peer_records[pq]) {
+#pragma unroll 1
+                        for (int pq = 0; pq < npeers; ++pq)
+                            if (p.peer_records[pq]) {
                                 p.peer_records[pq][rec_at + at_k] = key;
                                 p.peer_records[pq][rec_at + at_i] = idx;
                             }
