@@ -100,6 +100,14 @@ def dequantise(exps, codes, fmt):
     return (sgn * np.ldexp(mag, e)).astype(np.float32)
 
 
+def dequantise_c(exps, codes, fmt):
+    """The same by oracle.c (orc_dequantise): for matrices too large for numpy temporaries."""
+    k, n = codes.shape
+    out = np.empty((k, n), np.float32)
+    lib().orc_dequantise(_p(np.ascontiguousarray(exps)), _p(np.ascontiguousarray(codes)), _i64(k), _i64(n), MB[fmt], _p(out))
+    return out
+
+
 def tiles(exps, codes, fmt):
     """The reference's tile bytes [K/32, N/32, 576 | 1088] (moe8.py:125-154)."""
     mb = MB[fmt]
@@ -120,10 +128,16 @@ def block_float(t, fmt):
 
 def native_values(t, fmt, col_scale=False):
     """What linear.native_weight makes of a float [out, in] matrix (linear.py:144-156): (held values float32 [K, N],
-    scales float32 [N])."""
+    scales float32 [N]). Matrices of more than 2^24 elements go through oracle.c's quantiser and dequantiser (the numpy
+    restatement would need several temporaries of the matrix's size); the two are checked against each other and the
+    golden vectors in tests/test_oracle.py."""
     t = torch.as_tensor(t).float()
     c = bf16_ceil(t.abs().amax(dim=1).clamp(min=1e-8)) if col_scale else torch.ones(t.shape[0])
-    wt = (t / c[:, None]).T.contiguous()
+    wt = ((t / c[:, None]) if col_scale else t).T.contiguous()
+    if fmt != "bf16" and wt.numel() > 1 << 24:
+        n = wt.shape[1]
+        assert n % 16 == 0, n
+        return dequantise_c(*quantise_c(wt.numpy(), fmt), fmt), c.numpy()
     return block_float(wt.numpy(), fmt), c.numpy()
 
 

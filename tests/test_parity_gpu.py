@@ -88,17 +88,18 @@ def test_matmul_against_oracle(device, fmt, m):
     linear.check_status(device)
 
 
-def test_config_shapes_small_m(device):
-    """BASELINE's shapes, scaled down in N only where the oracle would take minutes: the README example (config 1)
-    at full size, the MLP gate/up with float32 column scales (config 2) and the down projection with a float32 residual
-    and output (config 3) at a quarter of N."""
+def test_config_shapes_full_size(device):
+    """The benchmark configurations at their own sizes against the oracle over every column: the README example
+    (one token through a [4096, 2048] bfloat8_b weight), the MLP gate/up pair (two [14336, 4096] bfloat4_b weights,
+    float32 column scales, SwiGLU; as two weights and as one interleaved weight) and the down projection ([4096, 14336]
+    bfloat8_b, float32 residual and output) at 1, 8 and 32 rows."""
     g = torch.Generator().manual_seed(0)
     w = torch.randn(4096, 2048, generator=g) * 0.02
     x = torch.randn(1, 2048, generator=g)
     tw, _ = linear.native_weight(device, w, ttnn.bfloat8_b)
     close_bf16(host(linear.matmul(dev_x(device, x), tw, None)), orc.matmul_f64(x, orc.native_values(w, "bfp8")[0]))
-    # config 2: silu((x Wg) sg) * ((x Wu) su), bfloat4_b
-    k, n = 4096, 3584
+    # the gate/up pair: silu((x Wg) sg) * ((x Wu) su), bfloat4_b
+    k, n = 4096, 14336
     wg, wu = torch.randn(n, k, generator=g) * 0.02, torch.randn(n, k, generator=g) * 0.02
     sg, su = torch.rand(n, generator=g) + 0.5, torch.rand(n, generator=g) + 0.5
     x = torch.randn(1, k, generator=g)
@@ -106,6 +107,7 @@ def test_config_shapes_small_m(device):
     tu, _ = linear.native_weight(device, wu, ttnn.bfloat4_b)
     cs = (sg.to(device.torch), su.to(device.torch))
     y = host(linear.matmul(dev_x(device, x), tg, None, w_up=tu, glu=True, col_scales=cs))
+    assert y.shape == (1, n)
     ag = orc.matmul_f64(x, orc.native_values(wg, "bfp4")[0])
     au = orc.matmul_f64(x, orc.native_values(wu, "bfp4")[0])
     close_bf16(y, orc.epilogue(ag, 2, acc2=au, scale=sg.numpy(), scale2=su.numpy()))
@@ -114,8 +116,9 @@ def test_config_shapes_small_m(device):
     si = linear.interleave_glu(sg[:, None], su[:, None]).reshape(-1).to(device.torch)
     y2 = host(linear.matmul(dev_x(device, x), ti, None, glu=True, col_scales=si))
     assert torch.equal(y, y2)
-    # config 3: x W^T + residual in float32
-    k, n = 14336, 1024
+    del tg, tu, ti, wg, wu
+    # the down projection: x W^T + residual in float32
+    k, n = 14336, 4096
     w = torch.randn(n, k, generator=g) * 0.02
     tw, _ = linear.native_weight(device, w, ttnn.bfloat8_b)
     wk = orc.native_values(w, "bfp8")[0]
@@ -127,8 +130,87 @@ def test_config_shapes_small_m(device):
         want = orc.epilogue(orc.matmul_f64(x, wk), 4, res32=res.numpy())
         got = host(y)[:m]
         assert got.dtype == torch.float32
+        close_bf16(got, want)
         rel = ((got.double() - torch.from_numpy(want)).norm() / torch.from_numpy(want).norm()).item()
         assert rel < 1e-5, rel
+    linear.check_status(device)
+
+
+def test_lm_head_full_size(device):
+    """The LM head at its own size: x [1, 4096] through a [151936, 4096] bfloat8_b weight, one top-8 record per 2048
+    columns (74 full units and one of 384 columns), then the best 32 of them all. Every record equals the oracle's
+    canonical top-k of the call's own bf16 outputs bit for bit, the merged 32 equal the oracle's merge of those
+    records (and the canonical top-32 of the whole row), and the outputs match the oracle's sums over every column."""
+    k, n, kk, top = 4096, 151936, 8, 32
+    g = torch.Generator().manual_seed(5)
+    w = torch.randn(n, k, generator=g) * 0.02
+    x = torch.randn(1, k, generator=g)
+    tw, _ = linear.native_weight(device, w, ttnn.bfloat8_b)
+    units = linear.topk_units(n)
+    assert units == 75
+    r = linear.topk_result(device, units, 1, kk)
+    out = ttnn.allocate_tensor_on_device([1, 1, 1, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
+    spec = {"r": r, "k": kk, "rows": 1, "slot0": 0, "base": 0, "n": n, "write_y": True}
+    tx = dev_x(device, x)
+    linear.matmul(tx, tw, None, topk=spec, out=out)
+    merged = linear.topk_merge(r, 1, kk, top)
+    linear.check_status(device)
+    y = host(out)
+    rec = ttnn.to_torch(r).reshape(units, 2, 1, kk).numpy().view(np.uint32)
+    bits = orc.bf16_bits(y[0])
+    for u in range(units):
+        c0, c1 = u * 2048, min((u + 1) * 2048, n)
+        keys, idx = orc.topk_canonical(bits[c0:c1], c1 - c0, kk, c0)
+        assert np.array_equal(rec[u, 0, 0], keys), u
+        assert np.array_equal(rec[u, 1, 0], idx), u
+    got = ttnn.to_torch(merged).numpy().view(np.uint32).reshape(2, 1, top)
+    assert np.array_equal(got, orc.topk_merge_ref(rec, 1, kk, top))
+    keys, idx = orc.topk_canonical(bits, n, top, 0)
+    assert np.array_equal(got[0, 0], keys) and np.array_equal(got[1, 0], idx)
+    # the same records with write_y False (the outputs stay in the call's scratch buffer)
+    r2 = linear.topk_result(device, units, 1, kk)
+    linear.matmul(tx, tw, None, topk={**spec, "r": r2, "write_y": False}, out=out)
+    assert torch.equal(ttnn.to_torch(r2), ttnn.to_torch(r))
+    del tw
+    wk = orc.native_values(w, "bfp8")[0]
+    close_bf16(y, orc.matmul_f64(x, wk))
+    linear.check_status(device)
+
+
+def test_records_as_bfloat16(device):
+    """RECORDS_BF16 (the reference's linear.py:77-78, 775-778): the result tensor is bfloat16 with the same bytes as
+    the uint32 words. The op, the host decode, the device merge and the LM head's pick take it unchanged."""
+    from lm_head_topk import head_pick
+
+    k, n, kk, rows = 1024, 2048 * 2 + 384, 8, 2
+    g = torch.Generator().manual_seed(51)
+    w = torch.randn(n, k, generator=g) * 0.02
+    x = torch.randn(rows, k, generator=g)
+    tw, _ = linear.native_weight(device, w, ttnn.bfloat8_b)
+    tx = dev_x(device, x)
+    units = linear.topk_units(n)
+    spec = {"k": kk, "rows": rows, "slot0": 0, "base": 0, "n": n, "write_y": True}
+    r32 = linear.topk_result(device, units, rows, kk)
+    linear.matmul(tx, tw, None, topk={**spec, "r": r32})
+    linear.RECORDS_BF16 = True
+    try:
+        r16 = linear.topk_result(device, units, rows, kk)
+        assert r16.dtype == ttnn.bfloat16 and r16.shape[-1] == 4 * rows * kk
+        linear.matmul(tx, tw, None, topk={**spec, "r": r16})
+        a, b = ttnn.to_torch(r16), ttnn.to_torch(r32)
+        assert torch.equal(a.contiguous().view(torch.int32).reshape(-1), b.reshape(-1))
+        v16, i16 = linear.topk_records(r16, rows, kk)
+        v32, i32 = linear.topk_records(r32, rows, kk)
+        assert torch.equal(v16, v32) and torch.equal(i16, i32)
+        m16 = linear.topk_merge(r16, rows, kk, 32)
+        assert m16.dtype == ttnn.bfloat16
+    finally:
+        linear.RECORDS_BF16 = False
+    m32 = linear.topk_merge(r32, rows, kk, 32)
+    assert torch.equal(ttnn.to_torch(m16).contiguous().view(torch.int32).reshape(-1), ttnn.to_torch(m32).reshape(-1))
+    p16 = ttnn.to_torch(head_pick.pick_records(r16, rows, kk, n))
+    p32 = ttnn.to_torch(head_pick.pick_records(r32, rows, kk, n))
+    assert torch.equal(p16.reshape(32, 32)[:rows, :3], p32.reshape(32, 32)[:rows, :3])
     linear.check_status(device)
 
 
