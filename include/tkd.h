@@ -42,6 +42,9 @@ extern "C" {
 #define TKD_DT_F32 2
 
 int tkd_version(void);
+/* The version of the packed streams' bit layout (tkd_pack's output): it changes whenever the layout does, and a cache
+ * of packed weights records it (the counterpart of the pack cache's version key, moe/moe8.py:289-346). */
+int tkd_layout_version(void);
 /* sizeof of a structure of this header as the library was built (0 TkdMatmul, 1 TkdPlan, 2 TkdBlock): a binding
  * compares it with its own mirror before the first call. */
 int tkd_struct_bytes(int which);
@@ -64,9 +67,17 @@ int64_t tkd_packed_bytes(int fmt, int64_t k, int64_t n);
 int tkd_quantise(int fmt, const float* src, int orient, int64_t k, int64_t n, const float* col_div, uint8_t* exps,
                  void* codes, void* stream);
 /* canonical numbers -> the HBM stream. packed: tkd_packed_bytes; emax: npad / 16 bytes (unused for bf16); info: one
- * int32, zeroed by the caller; bit 0 is set when the weight is "wide" (then tkd_matmul answers TKD_ERR_WIDE). */
+ * int32, zeroed by the caller; bit 0 is set when the weight is "wide": inside some group of 16 columns a row with a
+ * non-zero code lies more than 48 binades below the group's largest row, further than the stream's exponents reach.
+ * tkd_matmul never sees the info word: a caller that finds the bit set must not launch on that stream (the far rows'
+ * exponents are clamped in it) and holds the weight as TKD_FMT_BF16 instead, which is exact: tkd_dequantise_bf16 on
+ * the same exps and codes, then tkd_pack with TKD_FMT_BF16 (what the Python layer does; TKD_ERR_WIDE is what a binding
+ * raises if it chooses to refuse instead). */
 int tkd_pack(int fmt, int64_t k, int64_t n, const uint8_t* exps, const void* codes, void* packed, uint8_t* emax,
              int32_t* info, void* stream);
+/* tkd_quantise's block-float numbers (TKD_FMT_BFP8 or BFP4) as bf16 bits [K, npad] (uint16), the canonical form
+ * tkd_pack takes for TKD_FMT_BF16: every such number is a bf16 value exactly, subnormals included. */
+int tkd_dequantise_bf16(int fmt, int64_t k, int64_t n, const uint8_t* exps, const void* codes, void* out_bf16, void* stream);
 /* the stream back as float32 [K, npad]: the values the weight holds */
 int tkd_unpack(int fmt, int64_t k, int64_t n, const void* packed, const uint8_t* emax, float* out, void* stream);
 
@@ -130,7 +141,11 @@ typedef struct {
                                can wait again); 2: the same wait, but for the exchanged call BEFORE this one (the exchange
                                of one call overlaps the next call's run; tkd_exchange_wait flushes the last one); 0: no
                                wait, the caller orders tkd_exchange_wait behind it */
-    int32_t pad_;
+    int32_t weights_fresh;  /* 0: every weight stream and emax array of the call was complete (by an event or a
+                               synchronisation) before this call was enqueued: the kernel is launched as a programmatic
+                               dependent of the work before it on the stream, and its first weight loads may run while
+                               that work drains. 1: something enqueued earlier on the stream still writes them (tkd_pack,
+                               a copy): the launch is ordered behind all of it, at the cost of that overlap. */
 } TkdMatmul;
 #define TKD_MAX_RANKS 8
 #define TKD_FLAG_SEQ 8      /* flags[0..7]: calls completed by rank r, as told by r; flags[8]: calls completed here */
@@ -144,6 +159,10 @@ typedef struct {
 
 int tkd_matmul_plan(const TkdMatmul* a, TkdPlan* plan);
 int tkd_matmul_workspace(const TkdMatmul* a, uint64_t* bytes);
+/* The launch. Ordering contract: the activations, scales, residual, outputs and workspace are read and written in
+ * stream order; the WEIGHT streams and emax arrays are read from the moment the kernel's first CTAs start, which with
+ * programmatic dependent launch is before the work enqueued ahead of it has finished. A caller that packs (or copies) a
+ * weight and multiplies by it on the same stream without a synchronisation in between sets a->weights_fresh. */
 int tkd_matmul(const TkdMatmul* a, void* stream);
 
 /* tkd_matmul with the activations and the result in HOST memory (pinned, for the copies to be asynchronous): copies
@@ -162,11 +181,22 @@ int tkd_matmul_host(const TkdMatmul* a, const void* x_host, void* out_host, void
  * before anything is launched; as a guide, the array holds about 7900 / M panel-slices of sums (a panel is 128
  * columns, a slice 1024 k by default): one row against the 151936-column LM head fits, eight rows do not.
  * The first call on a device looks the array's device address up and clears its counters; make that first call
- * outside any stream capture. All calls on a device share the one array, which keeps what the last call left in it
- * (the kernel returns its counters to zero itself): two calls that overlap on the GPU, from different streams or
- * processes' threads, race on it, so keep calls on one device in stream order. */
+ * outside any stream capture, and at start-up: under CUDA's lazy module loading it is also the moment the driver
+ * backs the array with memory, so a host whose pool has already taken all of the device's memory can see it fail
+ * (1000 + cudaError_t) there and nowhere later (CUDA_MODULE_LOADING=EAGER moves that to the library's load). All calls
+ * on a device share the one array, which keeps what the last call left in it (the kernel returns its counters to zero
+ * itself): two calls that overlap on the GPU, from different streams or processes' threads, race on it, so keep calls
+ * on one device in stream order. A kernel that gave up a bounded wait (TKD_ERR_TIMEOUT in the status word) may have
+ * left the counters mid-count: call tkd_matmul_noalloc_reset before the next tkd_matmul_noalloc on that device. */
 #define TKD_NOALLOC_SCRATCH_BYTES (8u << 20)
 int tkd_matmul_noalloc(const TkdMatmul* a, void* stream);
+/* Starts the built-in array's counters from zero again, on `stream` (a memset of its first 256 KB; allocates nothing).
+ * For use after TKD_ERR_TIMEOUT, ordered after the kernel that reported it and before the next call. No counterpart
+ * in the reference. */
+int tkd_matmul_noalloc_reset(void* stream);
+/* The built-in array's address on the current device (host out-pointer), for diagnostics and tests; resolves it like a
+ * first tkd_matmul_noalloc call does, without clearing anything. No counterpart in the reference. */
+int tkd_noalloc_scratch_address(void** ptr);
 
 /* The best `top` candidates of every row among `nrecords` top-k records (the record layout above: keys[rows][k] then
  * indices[rows][k]), key descending and index ascending among equal keys; out is one record of the same layout with

@@ -8,15 +8,15 @@ without it. nvcc cross-compiles: no GPU is needed to build.
 
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent / "csrc"
-SOURCES = ["tkd_api.cu", "tkd_pack.cu", "tkd_stream.cu", "tkd_topk.cu"]
+SOURCES = ["tkd_api.cu", "tkd_pack.cu", "tkd_stream.cu", "tkd_stream_bfp8.cu", "tkd_stream_bfp4.cu", "tkd_stream_bf16.cu",
+           "tkd_topk.cu"]
 LIB = CSRC / "libtkd.so"
-FLAGS = [
-    "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-shared",
-    "-Xcompiler", "-fPIC",
-]
+FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC"]
+OBJ = CSRC / "build"
 
 
 def stale():
@@ -27,16 +27,26 @@ def stale():
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(verbose=False, force=False):
-    if not force and not stale():
-        return LIB
-    cmd = ["nvcc", *FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(LIB), *[str(CSRC / s) for s in SOURCES]]
+def _run(cmd, verbose):
     r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or r.returncode:
         sys.stderr.write(r.stdout + r.stderr)
     if r.returncode:
-        raise RuntimeError("nvcc failed building libtkd.so")
-    return LIB
+        raise RuntimeError("nvcc failed building libtkd.so: " + " ".join(cmd))
+
+
+def build(verbose=False, force=False, defines=(), lib=LIB):
+    """Compile the sources (one nvcc per file, side by side) and link them. defines: extra -D flags (experiments)."""
+    if not force and not defines and not stale():
+        return lib
+    OBJ.mkdir(exist_ok=True)
+    extra = [*(["-Xptxas", "-v"] if verbose else []), *[f"-D{d}" for d in defines]]
+    objs = [OBJ / (Path(s).stem + "".join("_" + d.replace("=", "_") for d in defines) + ".o") for s in SOURCES]
+    with ThreadPoolExecutor(len(SOURCES)) as pool:
+        list(pool.map(lambda so: _run(["nvcc", *FLAGS, *extra, "-c", "-o", str(so[1]), str(CSRC / so[0])], verbose),
+                      zip(SOURCES, objs)))
+    _run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", str(lib), *map(str, objs)], verbose)
+    return lib
 
 
 if __name__ == "__main__":

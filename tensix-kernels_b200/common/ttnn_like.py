@@ -12,6 +12,7 @@ read (csrc/tkd_layout.h), made on the GPU by libtkd's packer.
 """
 
 import enum
+import itertools
 import math
 
 import torch
@@ -162,12 +163,18 @@ class Tensor:
 
 class Weight(Tensor):
     """A [1, 1, K, N] weight as the packed stream the kernels read. `t` is the stream (uint8), `emax` the per-group
-    side array (None for bfloat16), `banks` what its memory config reports (nothing is placed by bank on a GPU)."""
+    side array (None for a bfloat16 stream), `fmt` the stream's format: the dtype's own, or bfloat16 for a "wide"
+    block-float weight (one whose exponents inside a group of 16 columns spread further than the block-float stream
+    encodes: its values, all exact in bf16, are then streamed as bf16). `serial` numbers the weights of a process."""
 
-    def __init__(self, stream, emax, k, n, dtype, device, memory_config, wide=False):
+    _serials = itertools.count(1)
+
+    def __init__(self, stream, emax, k, n, dtype, device, memory_config, fmt=None):
         super().__init__(stream, dtype, TILE_LAYOUT, device, memory_config)
-        self.emax, self.k, self.n, self.wide = emax, k, n, wide
-        self.fmt = FMT[dtype]
+        self.emax, self.k, self.n = emax, k, n
+        self.fmt = FMT[dtype] if fmt is None else fmt
+        self.wide = self.fmt != FMT[dtype]
+        self.serial = next(Weight._serials)
         sp = memory_config.shard_spec
         self._npad = sp.shape[1] * sp.banks if sp else _pad(n)
 
@@ -210,8 +217,32 @@ def pack_weight(device, wt, dtype, orient, col_div=None, memory_config=None):
                        emax.data_ptr() if emax is not None else None, info.data_ptr(), _stream_ptr()),
             "tkd_pack",
         )
-        wide = bool(int(info.item()) & 1)
-    return Weight(stream, emax, k, n, dtype, device, memory_config or DRAM_MEMORY_CONFIG, wide=wide)
+        if int(info.item()) & 1:
+            # a wide weight: the same numbers as a bf16 stream (twice to four times the bytes, and exact)
+            vals = torch.empty(k * npad, dtype=torch.int16, device=device.torch)
+            _tkd.check(L.tkd_dequantise_bf16(fmt, k, n, exps.data_ptr(), codes.data_ptr(), vals.data_ptr(), _stream_ptr()),
+                       "tkd_dequantise_bf16")
+            fmt, emax = _tkd.FMT_BF16, None
+            stream = torch.empty(L.tkd_packed_bytes(fmt, k, n), dtype=torch.uint8, device=device.torch)
+            _tkd.check(L.tkd_pack(fmt, k, n, None, vals.data_ptr(), stream.data_ptr(), None, info.data_ptr(), _stream_ptr()),
+                       "tkd_pack")
+            torch.cuda.current_stream().synchronize()
+    return Weight(stream, emax, k, n, dtype, device, memory_config or DRAM_MEMORY_CONFIG, fmt=fmt)
+
+
+def as_bf16_stream(w):
+    """The weight `w` with its values streamed as bf16 (itself when it already is): what a block list does with its
+    other weights when one of them is wide, since one launch streams one format."""
+    if w.fmt == _tkd.FMT_BF16:
+        return w
+    twin = getattr(w, "_bf16_twin", None)
+    if twin is None:
+        vals = to_torch(w)[0, 0, :, : w.n]
+        twin = pack_weight(w._device, vals, bfloat16, 1, memory_config=w._mc)
+        twin.dtype = w.dtype
+        twin.wide = True
+        w._bf16_twin = twin
+    return twin
 
 
 def from_torch(t, dtype=None, layout=ROW_MAJOR_LAYOUT, device=None, memory_config=None):
@@ -252,10 +283,18 @@ def Shape(dims):
     return list(dims)
 
 
+# Counts deallocations: caches of launch descriptors (which hold raw addresses) key on it, so that nothing described
+# before a tensor was freed is launched after.
+EPOCH = 0
+
+
 def deallocate(t):
+    global EPOCH
+    EPOCH += 1
     t.t = None
     if isinstance(t, Weight):
         t.emax = None
+        t._bf16_twin = None
 
 
 def reshape(t, shape):

@@ -3,6 +3,8 @@
 #include <stdint.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "../../include/tkd.h"
 #include "tkd_internal.h"
 #include "tkd_layout.h"
@@ -66,6 +68,7 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     p.nseg = a->nblocks;
     p.epi = a->epilogue;
     p.act = a->act;
+    p.mul16 = 16, p.mul128 = 128;
     const int mt = a->m <= 8 ? 1 : (a->m <= 16 ? 2 : 4);
     const int sab = tkd_sab(a->fmt);
     const int chunk_k = tkd_chunk_k(a->fmt);
@@ -113,7 +116,13 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     // x one chunk of k; the same conditions as NPB and XS in the kernel)
     p.off_tbuf = p.off_pbuf + (mt == 4 ? 1 : 2) * 2 * TKD_PANEL_COLS * mp * 4;
     p.off_xt = (int)align_up(p.off_tbuf + TKD_PANEL_COLS * mp * 4, 128);
-    const int xt_bytes = mt >= 2 && a->fmt != TKD_BFP4 ? 2 * (8 * mt) * chunk_k * 2 : 0;
+    int xt_bytes = mt >= 2 && a->fmt != TKD_BFP4 ? 2 * (8 * mt) * chunk_k * 2 : 0;
+    // one row: all of x in shared memory (K rounded up to a chunk), if that leaves the ring at least four stages
+    const int64_t x_row = (a->k + chunk_k - 1) / chunk_k * chunk_k * 2;
+    if (a->m == 1 && p.off_xt + x_row + 4 * (int64_t)(8 * tkd_subsa(a->fmt) * sab) + 256 <= kMaxSmem) {
+        p.x_smem = 1;
+        xt_bytes = (int)x_row;
+    }
     p.off_ring = (int)align_up(p.off_xt + xt_bytes, 128);
     p.stage_bytes = 8 * tkd_subsa(a->fmt) * sab;
     p.nstages = (kMaxSmem - p.off_ring) / p.stage_bytes;
@@ -161,7 +170,9 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
 
 extern "C" {
 
-int tkd_version(void) { return 2; }
+int tkd_version(void) { return 3; }
+
+int tkd_layout_version(void) { return TKD_LAYOUT_VERSION; }
 
 int tkd_struct_bytes(int which) {
     return which == 0 ? (int)sizeof(TkdMatmul) : which == 1 ? (int)sizeof(TkdPlan) : which == 2 ? (int)sizeof(TkdBlock) : 0;
@@ -200,6 +211,12 @@ int tkd_pack(int fmt, int64_t k, int64_t n, const uint8_t* exps, const void* cod
     if (fmt != TKD_BF16 && (!exps || !emax || !info)) return TKD_ERR_BAD_ARG;
     return launch_err(tkd_launch_permute(fmt, k, tkd_padded_cols(n), exps, codes, emax, info, packed,
                                          static_cast<cudaStream_t>(stream)));
+}
+
+int tkd_dequantise_bf16(int fmt, int64_t k, int64_t n, const uint8_t* exps, const void* codes, void* out_bf16, void* stream) {
+    if ((fmt != TKD_BFP8 && fmt != TKD_BFP4) || !exps || !codes || !out_bf16 || k < 1 || n < 1) return TKD_ERR_BAD_ARG;
+    return launch_err(tkd_launch_dequantise_bf16(fmt, k, tkd_padded_cols(n), exps, codes, out_bf16,
+                                                 static_cast<cudaStream_t>(stream)));
 }
 
 int tkd_unpack(int fmt, int64_t k, int64_t n, const void* packed, const uint8_t* emax, float* out, void* stream) {
@@ -294,6 +311,7 @@ static int run_matmul(const TkdMatmul* a, void* workspace, uint64_t workspace_by
     p.scratch = reinterpret_cast<float*>(ws + L.off_scratch);
     p.ytmp = reinterpret_cast<uint16_t*>(ws + L.off_ytmp);
     p.status = a->status;
+    p.no_pdl = a->weights_fresh != 0;
     if (a->nranks > 1) {
         if (!a->flags) return TKD_ERR_BAD_ARG;
         p.npeers = a->nranks - 1;
@@ -340,26 +358,53 @@ int tkd_matmul_host(const TkdMatmul* a, const void* x_host, void* out_host, void
 // current, and that address is what the kernel gets.
 static __device__ __align__(256) unsigned char tkd_noalloc_scratch[TKD_NOALLOC_SCRATCH_BYTES];
 
-int tkd_matmul_noalloc(const TkdMatmul* a, void* stream) {
-    static void* dev_ptr[64] = {nullptr};
-    Layout L;
-    const int rc = make_layout(a, &L, 0);
-    if (rc) return rc;
-    if ((uint64_t)L.ws_bytes > (uint64_t)TKD_NOALLOC_SCRATCH_BYTES) return TKD_ERR_FIXED_SCRATCH;
+// The array's address on the current device, resolved on first use (a thread that loses the race to publish it has
+// resolved the same address). first: set when this call was the one that resolved it.
+static int noalloc_address(void** out, bool* first) {
+    static std::atomic<void*> dev_ptr[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_err(e);
     if (dev < 0 || dev >= 64) return TKD_ERR_UNSUPPORTED;
-    if (!dev_ptr[dev]) {
-        // first call on this device: resolve the array's device address and start its counters from zero
-        void* ptr = nullptr;
+    void* ptr = dev_ptr[dev].load(std::memory_order_acquire);
+    if (first) *first = false;
+    if (!ptr) {
         e = cudaGetSymbolAddress(&ptr, tkd_noalloc_scratch);
         if (e != cudaSuccess) return cuda_err(e);
-        e = cudaMemsetAsync(ptr, 0, (size_t)kCounterBytes, static_cast<cudaStream_t>(stream));
-        if (e != cudaSuccess) return cuda_err(e);
-        dev_ptr[dev] = ptr;
+        void* expected = nullptr;
+        if (dev_ptr[dev].compare_exchange_strong(expected, ptr, std::memory_order_acq_rel) && first) *first = true;
     }
-    return run_matmul(a, dev_ptr[dev], TKD_NOALLOC_SCRATCH_BYTES, stream);
+    *out = ptr;
+    return TKD_OK;
+}
+
+int tkd_matmul_noalloc(const TkdMatmul* a, void* stream) {
+    Layout L;
+    const int rc = make_layout(a, &L, 0);
+    if (rc) return rc;
+    if ((uint64_t)L.ws_bytes > (uint64_t)TKD_NOALLOC_SCRATCH_BYTES) return TKD_ERR_FIXED_SCRATCH;
+    void* ptr = nullptr;
+    bool first = false;
+    const int ra = noalloc_address(&ptr, &first);
+    if (ra) return ra;
+    if (first) {
+        // first call on this device: the array's counters start from zero
+        const cudaError_t e = cudaMemsetAsync(ptr, 0, (size_t)kCounterBytes, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return cuda_err(e);
+    }
+    return run_matmul(a, ptr, TKD_NOALLOC_SCRATCH_BYTES, stream);
+}
+
+int tkd_matmul_noalloc_reset(void* stream) {
+    void* ptr = nullptr;
+    const int ra = noalloc_address(&ptr, nullptr);
+    if (ra) return ra;
+    return cuda_err(cudaMemsetAsync(ptr, 0, (size_t)kCounterBytes, static_cast<cudaStream_t>(stream)));
+}
+
+int tkd_noalloc_scratch_address(void** ptr) {
+    if (!ptr) return TKD_ERR_BAD_ARG;
+    return noalloc_address(ptr, nullptr);
 }
 
 int tkd_topk_merge(const uint32_t* records, int nrecords, int rows, int k, int top, uint32_t* out, void* stream) {

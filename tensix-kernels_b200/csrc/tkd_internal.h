@@ -10,6 +10,8 @@ int tkd_launch_quantise(int fmt, const float* src, int orient, int64_t K, int64_
                         const float* col_div, uint8_t* exps, void* codes, cudaStream_t st);
 int tkd_launch_permute(int fmt, int64_t K, int64_t npad, const uint8_t* exps, const void* codes, uint8_t* emax,
                        int* info, void* stream, cudaStream_t st);
+int tkd_launch_dequantise_bf16(int fmt, int64_t K, int64_t npad, const uint8_t* exps, const void* codes, void* out,
+                               cudaStream_t st);
 int tkd_launch_unpack(int fmt, int64_t K, int64_t npad, const void* stream, const uint8_t* emax, float* out,
                       cudaStream_t st);
 
@@ -54,6 +56,7 @@ struct TkdParams {
     int64_t total_items;
     int small;          // item counts times the grid fit 32 bits: the kernel divides in 32-bit arithmetic
     int epi, act;
+    uint32_t mul16, mul128;  // 16 and 128: shifts done as multiplies (see shl_fma)
     const void* scale;   // per output column of w (bf16 or f32), or null
     const void* scale2;  // the up weight's, GLU two-weight form
     int scale_dt;
@@ -84,13 +87,14 @@ struct TkdParams {
     uint32_t* flags;     // this rank's flag words
     int* grid_counter;   // CTAs of this call that have finished their output (returns to zero)
     int exchange_wait;
+    int x_smem;          // one row, and all of it (K rounded up to a chunk) fits in shared memory at off_xt
+    int no_pdl;          // launch without programmatic dependent launch (the weights may still be being written)
     // shared-memory map (bytes from the start of dynamic shared memory)
     int off_pbuf, off_tbuf, off_xt, off_ring;
     int stage_bytes;
 };
 
 int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
-bool tkd_pdl_enabled();  // programmatic dependent launch (off with TKD_NO_PDL=1 in the environment)
 int tkd_launch_topk_merge(const uint32_t* records, int nrec, int rows, int k, int top, uint32_t* out, cudaStream_t st);
 int tkd_launch_head_pick(const uint32_t* records, int nrec, int rows, int k, int top, uint32_t vocab, const uint16_t* x,
                          int64_t ldx, int dim, const uint16_t* head, int64_t ld_head, int round, uint32_t* out,

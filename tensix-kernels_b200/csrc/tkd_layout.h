@@ -21,13 +21,22 @@
 // activations a lane needs for the two mmas are 16 consecutive bytes of a row of x. Fragment registers: a0 = column
 // g, r 0-1; a1 = column g + 8, r 0-1; a2 = column g, r 2-3; a3 = column g + 8, r 2-3 (r even in the low half).
 //
-// A code is kept as the bf16 bit pattern sign << 15 | magnitude (a bf16 subnormal: +-magnitude * 2^-133), and several
-// fragment registers share one 32-bit word by rotation, so that one rotate and one AND give a register:
-//   bfloat8_b word = a_even | rotl(a_odd, 8)                      (mask 0x807F807F)
-//   bfloat4_b word = a0 | rotl(a1, 4) | rotl(a2, 8) | rotl(a3, 12) (mask 0x80078007)
-// The exponents are kept biased against the group's largest, e' = e - emax[group] + 196 (1 for a row of the group
-// with no non-zero code), as bf16 exponent fields, four to a word: r 0 at bits 7-14, r 1 at 23-30, r 2 and r 3 the
-// same rotated left by 8. emax (one byte per group) is a side array; e is recovered exactly for every non-zero code.
+// A code is kept as a bf16 bit pattern with a zero exponent field: bits 0-7 of a bf16 are linear (the subnormals and
+// the first binade: value = bits * 2^-133), so sign << 15 | magnitude << p is +-magnitude * 2^(p - 133). Several
+// fragment registers share one 32-bit word, and the shifts that take a word apart are chosen so that as few as
+// possible run on the integer pipe, which bounds the bfloat4_b decode (a left shift is a multiply, which the
+// FMA pipe takes):
+//   bfloat8_b (p = 0, mask 0x807F807F): word = a_even | rotl(a_odd, 8)
+//             a_even = w & mask, a_odd = rotr(w, 8) & mask
+//   bfloat4_b (p = 4, mask 0x80708070): word = a0 | a1 >> 4 | rotl(a2, 8) | rotl(a3 >> 4, 8)
+//             a0 = w & mask, a1 = (w << 4) & mask, t = rotr(w, 8), a2 = t & mask, a3 = (t << 4) & mask
+// The exponents are kept biased against the group's largest (emax, one byte per group, a side array), four to a word:
+//   bfloat8_b: e' = e - emax + 196 (1 for a row of the group with no non-zero code) as bf16 exponent fields, r 0 at
+//             bits 7-14, r 1 at 23-30, r 2 and r 3 the same rotated left by 8; the activation is scaled by 2^(e' - 127)
+//   bfloat4_b: f = e - emax + 63 (0 for a row with no non-zero code) in 6 bits, r 0 at bits 7-12, r 1 at 23-28, r 2 at
+//             0-5, r 3 at 16-21: (w & 0x1F801F80) | 0x40004000 is the pair of bf16 scales 2^(f + 1) of r 0 and r 1, the
+//             same of w << 7 those of r 2 and r 3
+// e is recovered exactly for every non-zero code.
 #pragma once
 #include <stdint.h>
 
@@ -39,10 +48,21 @@
 
 enum { TKD_BFP8 = 0, TKD_BFP4 = 1, TKD_BF16 = 2 };
 
-// The exponent bias of the stream: e' = e - emax + TKD_EBIAS. A non-zero code whose e' would fall below TKD_EMIN_OK
-// marks the weight "wide" (the product of a subnormal code and the scaled activation would leave fp32's normal range).
-#define TKD_EBIAS 196
-#define TKD_EMIN_OK (TKD_EBIAS - 48)
+// Bumped with every change of the stream's bit layout (a packed-weight cache made by another layout is refused).
+#define TKD_LAYOUT_VERSION 3
+
+// The exponent bias of the stream: e' = e - emax + bias. A non-zero code whose exponent lies more than TKD_ESPREAD
+// below its group's largest marks the weight "wide" (the product of a code and the scaled activation would leave
+// fp32's normal range; bfloat4_b's 6-bit field would not hold it either).
+#define TKD_ESPREAD 48
+TKD_HD int tkd_ebias(int fmt) { return fmt == TKD_BFP4 ? 63 : 196; }
+TKD_HD int tkd_emin_ok(int fmt) { return tkd_ebias(fmt) - TKD_ESPREAD; }
+// what a row of a group with no non-zero code stores
+TKD_HD int tkd_ezero(int fmt) { return fmt == TKD_BFP4 ? 0 : 1; }
+// The column sums come out of the kernel in units of 2^tkd_out_exp(fmt, emax of the group):
+//   bfloat8_b: code m * 2^-133 times x * 2^(e' - 127) = m x 2^(e - emax - 64) for the true m x 2^(e - 133)
+//   bfloat4_b: code m * 2^-129 times x * 2^(f + 1)    = m x 2^(e - emax - 65) for the true m x 2^(e - 129)
+TKD_HD int tkd_out_exp(int fmt, int emax) { return fmt == TKD_BFP4 ? emax - 64 : emax + 64 - 133; }
 
 TKD_HD int tkd_mant_bits(int fmt) { return fmt == TKD_BFP8 ? 7 : 3; }
 TKD_HD int tkd_ksa(int fmt) { return fmt == TKD_BFP4 ? 64 : 32; }                          // k per super-atom
@@ -85,7 +105,7 @@ TKD_HD uint32_t tkd_rotr(uint32_t v, int s) { return s ? (v >> s) | (v << (32 - 
 // Where element (k, n) of a weight lives.
 struct TkdLoc {
     int64_t code_word;  // byte offset of the 32-bit word holding the code (bf16: of the 16-bit value itself)
-    int rot;            // the register is rotr(word, rot) & mask
+    int rot;            // bfloat8_b: the register is rotr(word, rot) & mask; bfloat4_b: which register a0..a3 (see above)
     int half;           // 0: low 16 bits of the register, 1: high
     int64_t exp_word;   // byte offset of the exponent word
     int exp_r;          // 0..3: the exponent's position in that word
@@ -117,26 +137,48 @@ TKD_HD TkdLoc tkd_locate(int fmt, int64_t K, int64_t k, int64_t n) {
     } else {
         const int j4 = 2 * qq + jj;
         L.code_word = base + 64 + lane * 16 + j4 * 4;
-        L.rot = 4 * ai;
+        L.rot = ai;
         L.exp_word = base + (t * 4 + j4) * 4;
     }
     return L;
 }
 
+#define TKD_MASK_BFP8 0x807F807Fu
+#define TKD_MASK_BFP4 0x80708070u
+// The fragment register of a word (rot: TkdLoc's), as the kernel takes it out.
+TKD_HD uint32_t tkd_reg_from_word(int fmt, uint32_t word, int rot) {
+    if (fmt == TKD_BFP8) return tkd_rotr(word, rot) & TKD_MASK_BFP8;
+    const uint32_t t = rot & 2 ? tkd_rotr(word, 8) : word;
+    return (rot & 1 ? t << 4 : t) & TKD_MASK_BFP4;
+}
 // A code (sign << mb | magnitude) as the bits it adds to its word.
 TKD_HD uint32_t tkd_code_bits(int fmt, uint32_t code, int rot, int half) {
     const int mb = tkd_mant_bits(fmt);
-    const uint32_t v = ((code >> mb) << 15) | (code & ((1u << mb) - 1));
-    return tkd_rotl(v << (16 * half), rot);
+    const uint32_t s = code >> mb, m = code & ((1u << mb) - 1);
+    if (fmt == TKD_BFP8) return tkd_rotl(((s << 15) | m) << (16 * half), rot);
+    uint32_t v = ((s << 15) | (m << 4)) << (16 * half);
+    if (rot & 1) v >>= 4;
+    return rot & 2 ? tkd_rotl(v, 8) : v;
 }
 // ... and back.
 TKD_HD uint32_t tkd_code_from_word(int fmt, uint32_t word, int rot, int half) {
     const int mb = tkd_mant_bits(fmt);
-    const uint32_t v = (tkd_rotr(word, rot) >> (16 * half)) & 0xFFFFu;
-    return ((v >> 15) << mb) | (v & ((1u << mb) - 1));
+    const uint32_t v = (tkd_reg_from_word(fmt, word, rot) >> (16 * half)) & 0xFFFFu;
+    return ((v >> 15) << mb) | ((fmt == TKD_BFP8 ? v : v >> 4) & ((1u << mb) - 1));
 }
-// A biased exponent e' (1..254) as the bits it adds to its exponent word: a bf16 exponent field.
-TKD_HD uint32_t tkd_exp_bits(uint32_t e, int r) { return tkd_rotl((e << 7) << (16 * (r & 1)), 8 * (r >> 1)); }
-TKD_HD uint32_t tkd_exp_from_word(uint32_t word, int r) {
-    return ((tkd_rotr(word, 8 * (r >> 1)) >> (16 * (r & 1))) >> 7) & 0xFFu;
+// A biased exponent as the bits it adds to its exponent word.
+#define TKD_EMASK_BFP4 0x1F801F80u
+#define TKD_EBASE_BFP4 0x40004000u
+TKD_HD uint32_t tkd_exp_bits(int fmt, uint32_t e, int r) {
+    if (fmt == TKD_BFP8) return tkd_rotl((e << 7) << (16 * (r & 1)), 8 * (r >> 1));
+    return (r & 2 ? e : e << 7) << (16 * (r & 1));
+}
+TKD_HD uint32_t tkd_exp_from_word(int fmt, uint32_t word, int r) {
+    if (fmt == TKD_BFP8) return ((tkd_rotr(word, 8 * (r >> 1)) >> (16 * (r & 1))) >> 7) & 0xFFu;
+    return (((r & 2 ? word << 7 : word) >> (16 * (r & 1))) >> 7) & 0x3Fu;
+}
+// The pair of bf16 scales (r 0 and r 1 for pair 0, r 2 and r 3 for pair 1) the kernel multiplies the activations by.
+TKD_HD uint32_t tkd_scales_from_word(int fmt, uint32_t word, int pair) {
+    if (fmt == TKD_BFP8) return (pair ? tkd_rotr(word, 8) : word) & 0x7F807F80u;
+    return ((pair ? word << 7 : word) & TKD_EMASK_BFP4) | TKD_EBASE_BFP4;
 }

@@ -85,7 +85,7 @@ __device__ __forceinline__ bool row_nonzero(const uint8_t* codes, int64_t npad, 
 }
 
 // One block per group: emax[g] = the largest exponent among its rows that hold a non-zero code (0: none). info[0] is
-// OR-ed with 1 when a non-zero row's exponent lies more than TKD_EBIAS - TKD_EMIN_OK below it (a "wide" weight). The
+// OR-ed with 1 when a non-zero row's exponent lies more than TKD_ESPREAD below it (a "wide" weight). The
 // block's threads share the rows of K out and reduce (maxima and minima: the order does not matter).
 constexpr int kEmaxThreads = 256;
 __global__ void __launch_bounds__(kEmaxThreads) tkd_emax_kernel(const uint8_t* __restrict__ exps,
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(kEmaxThreads) tkd_emax_kernel(const uint8_t* _
     if (threadIdx.x == 0) {
         for (int w = 1; w < kEmaxThreads / 32; ++w) hi = max(hi, shi[w]), lo = min(lo, slo[w]);
         emax[g] = (uint8_t)hi;
-        if (lo <= hi && lo - hi + TKD_EBIAS < TKD_EMIN_OK) atomicOr(info, 1);
+        if (lo <= hi && hi - lo > TKD_ESPREAD) atomicOr(info, 1);
     }
 }
 
@@ -143,9 +143,10 @@ __global__ void tkd_permute_kernel(int fmt, int64_t K, int64_t npad, const uint8
         const int qq = fmt == TKD_BFP4 ? j >> 1 : 0, jj = fmt == TKD_BFP4 ? j & 1 : j;
         for (int r = 0; r < 4; ++r) {
             const int64_t k = sa * ksa + qq * 32 + 8 * t + 4 * jj + r;
-            int e = 1;
-            if (k < K && row_nonzero(codes, npad, k, g)) e = max(1, (int)exps[k * G + g] - (int)emax[g] + TKD_EBIAS);
-            word |= tkd_exp_bits((uint32_t)e, r);
+            int e = tkd_ezero(fmt);
+            if (k < K && row_nonzero(codes, npad, k, g))
+                e = max(tkd_ezero(fmt), (int)exps[k * G + g] - (int)emax[g] + tkd_ebias(fmt));
+            word |= tkd_exp_bits(fmt, (uint32_t)e, r);
         }
     } else {
         const uint8_t* codes = static_cast<const uint8_t*>(codes_v);
@@ -166,11 +167,25 @@ __global__ void tkd_permute_kernel(int fmt, int64_t K, int64_t npad, const uint8
                 for (int half = 0; half < 2; ++half) {
                     const int64_t k = sa * ksa + qq * 32 + 8 * t + 4 * jj + 2 * (ai >> 1) + half;
                     const uint32_t c = k < K ? codes[k * npad + g * 16 + g8 + 8 * (ai & 1)] : 0u;
-                    word |= tkd_code_bits(fmt, c, 4 * ai, half);
+                    word |= tkd_code_bits(fmt, c, ai, half);
                 }
         }
     }
     stream[wi] = word;
+}
+
+// One thread per element: canonical block-float numbers -> bf16 bits [K, npad]. Every block-float value
+// +-m * 2^(e - unit) (m below 2^7, e from 1) is a bf16 value exactly, the subnormal ones included (multiples of 2^-132),
+// so the float's low 16 bits are zero and its high 16 are the bf16.
+__global__ void tkd_dequantise_bf16_kernel(int fmt, int64_t K, int64_t npad, const uint8_t* __restrict__ exps,
+                                           const uint8_t* __restrict__ codes, uint16_t* __restrict__ out) {
+    const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (idx >= K * npad) return;
+    const int64_t k = idx / npad, n = idx % npad;
+    const int mb = tkd_mant_bits(fmt);
+    const uint32_t c = codes[idx], m = c & ((1u << mb) - 1);
+    const float v = m ? ldexpf((float)m, (int)exps[k * (npad / 16) + (n >> 4)] - tkd_unit_exp(fmt)) : 0.f;
+    out[idx] = (uint16_t)((__float_as_uint(v) >> 16) | (((c >> mb) & 1u) << 15));
 }
 
 // One thread per element: stream -> float32 [K, npad].
@@ -190,7 +205,7 @@ __global__ void tkd_unpack_kernel(int fmt, int64_t K, int64_t npad, const uint8_
         const uint32_t c = tkd_code_from_word(fmt, w, L.rot, L.half);
         const uint32_t m = c & ((1u << mb) - 1);
         const uint32_t ew = *reinterpret_cast<const uint32_t*>(stream + L.exp_word);
-        const int e = (int)tkd_exp_from_word(ew, L.exp_r) + (int)emax[n >> 4] - TKD_EBIAS;
+        const int e = (int)tkd_exp_from_word(fmt, ew, L.exp_r) + (int)emax[n >> 4] - tkd_ebias(fmt);
         v = m ? ldexpf((float)m, e - tkd_unit_exp(fmt)) : 0.f;
         if ((c >> mb) & 1u) v = -v;
     }
@@ -219,6 +234,14 @@ int tkd_launch_permute(int fmt, int64_t K, int64_t npad, const uint8_t* exps, co
     const int64_t words = tkd_stream_bytes(fmt, K, npad) / 4;
     tkd_permute_kernel<<<(unsigned)((words + 255) / 256), 256, 0, st>>>(fmt, K, npad, exps, codes, emax,
                                                                        static_cast<uint32_t*>(stream));
+    return (int)cudaGetLastError();
+}
+
+int tkd_launch_dequantise_bf16(int fmt, int64_t K, int64_t npad, const uint8_t* exps, const void* codes, void* out,
+                               cudaStream_t st) {
+    const int64_t n = K * npad;
+    tkd_dequantise_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(fmt, K, npad, exps, static_cast<const uint8_t*>(codes),
+                                                                            static_cast<uint16_t*>(out));
     return (int)cudaGetLastError();
 }
 

@@ -1,1050 +1,20 @@
-// tkd_stream.cu: the weight-streaming decode matmul for sm_100a.
-//
-// y[m, n] = sum_k x[m, k] * w[k, n] with its fused output stage, M <= 32 activation rows, the weight a packed HBM
-// stream (tkd_layout.h). It takes the place of the reference's three Tensix kernels (dense_reader/kernels/
-// dense_reader.cpp: the DRAM loads; dense_compute.cpp: matmul_block accumulation and the output stages;
-// dense_writer.cpp: output writes and the running top-k) and of the work split linear.plan makes for them
-// (dense_reader/linear.py:187-382).
-//
-// One persistent CTA per SM, three kinds of warps, coupled by mbarriers only:
-//   warp 0        producer (one lane): one 1-D bulk copy (TMA) per stage of the shared-memory ring; a
-//                 stage is one chunk of one panel (128 columns x 256 or 512 k), contiguous in the stream. (A bulk copy costs
-//                 the issuing SM about 140 cycles whatever its size, so stages are single copies of 17-35 KB.)
-//   warps 1-16    streaming warps: warp (group g, half h) multiplies the 16 columns of group g by every other
-//                 super-atom of the chunk with mma.sync m16n8k16, the weights as A. Block-float codes go in as bf16
-//                 subnormals (sign << 15 | magnitude) and the shared exponent is folded into the activations
-//                 (x * 2^e' is exact), so a register of two weights costs one rotate and one AND. The activations come
-//                 straight from global memory through L1 (16 bytes a lane per 32 k), loaded before the stage is waited
-//                 for.
-//   warps 17-20   output warps (one thread per column of the panel): finish the K sum, run the output stage (exponent
-//                 factor, scales, SwiGLU/GeGLU, residual, rounding), write y, and keep the top-k records.
-//
-// A work item is (panel, k slice of ks). Items are numbered panel-major and cut into equal contiguous runs, one per
-// CTA. The sum of a column is defined once and for all as T0 + T1, T_h = the sum over slices, in ascending order, of
-// streaming warp h's slice sum (itself acc_even + acc_odd, each started from zero per slice), all plain fp32 adds. A
-// streaming warp adds up its own slices in registers as long as its CTA holds the panel from slice 0 on; what a CTA
-// holds of a panel otherwise goes through a scratch buffer slice by slice, and the CTA that delivers last adds them
-// up in the same order. So a column's result depends on K, the format, ks and M's bucket only, never on N, on the
-// number of CTAs or on the other weights of a block list.
-//
-// Every wait is bounded: a wait that gives up records TKD_ERR_TIMEOUT in the status word, and every role then falls
-// through to the end of the kernel.
-#include <cuda_bf16.h>
+// tkd_stream.cu: the launch of the stream kernel by weight format, and the small kernel that waits for an exchange.
 #include <cuda_runtime.h>
 #include <stdint.h>
-
-#include <type_traits>
 
 #include "tkd_internal.h"
 #include "tkd_layout.h"
 
-#ifdef TKD_PROF
-__device__ long long tkd_prof[64];
-__device__ unsigned long long tkd_times[148 * 4];
-__device__ long long tkd_trace[4 * 256];
-__device__ long long tkd_trace2[8 * 256];  // CTA 3 warp 1, per item: more points  // CTA 3: per stage (first 256): streaming warp 1 wait-start, wait-end, done; producer issue time
-__device__ int tkd_trace_n[2];  // per CTA: entry, streaming warps done, output warps done (ns)
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define PROF_TIME(slot) do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 148) tkd_times[blockIdx.x * 4 + slot] = gtime(); } while (0)
-#define PROF_MARK(i) _pm[i] = gtime()
-#define PROF_MARKS_OUT do { if (finish && et == 0 && blockIdx.x < 148) tkd_times[blockIdx.x * 4 + 3] = ((_pm[1] - _pm[0]) >> 6) | (((_pm[2] - _pm[1]) >> 6) << 16) | (((_pm[3] - _pm[2]) >> 6) << 32); } while (0)
-#define PROF_T0 long long _t0 = clock64()
-#define PROF_ADD(slot) do { (void)_t0; } while (0)  // (a global read-modify-write here stalls the warp it measures)
-#else
-#define PROF_MARK(i)
-#define PROF_MARKS_OUT
-#define PROF_T0
-#define PROF_ADD(slot)
-#define PROF_TIME(slot)
-#endif
-
-#include <stdlib.h>
-// TKD_NO_PDL=1 in the environment turns programmatic dependent launch off (for comparisons).
-bool tkd_pdl_enabled() {
-    static const bool on = [] { const char* v = getenv("TKD_NO_PDL"); return !(v && v[0] == '1'); }();
-    return on;
-}
+int tkd_launch_stream_bfp8(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
+int tkd_launch_stream_bfp4(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
+int tkd_launch_stream_bf16(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
 
 namespace {
 
-constexpr uint32_t kWaitRounds = 1u << 12;   // try_wait rounds before a wait gives up ...
-constexpr uint32_t kWaitHintNs = 1000000u;   // ... each suspended for up to this long (woken at once on completion)
-constexpr int kStatusTimeout = 3;            // TKD_ERR_TIMEOUT of include/tkd.h
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(kWaitHintNs)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: false (and the status word set) when the phase never completes.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
-    for (uint32_t i = 0; i < kWaitRounds; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    if (status) atomicExch(status, kStatusTimeout);
-    return false;
-}
-// global -> shared bulk copy (TMA, 1-D, this CTA only), completion counted in bytes on an mbarrier
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-// rotr(w, s) & mask: a funnel shift and an AND. (The rotate as a 32 x 32 -> 64 multiply by 2^(32 - s), to move it
-// off the integer pipe this loop is bound by, measured 18 % slower on B200.)
-template <int S>
-__device__ __forceinline__ uint32_t rot_and(uint32_t w, uint32_t mask) {
-    return __funnelshift_r(w, w, S) & mask;
-}
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
-}
-// Spin (bounded: about a second) until flags[r] has reached `seq` (compared modulo 2^32) for every r < nranks; false
-// when it gave up.
-__device__ __noinline__ bool flags_wait(const uint32_t* flags, int nranks, uint32_t seq) {
-    for (int r = 0; r < nranks; ++r) {
-        int rounds = 0;
-        while ((int32_t)(ld_acquire_sys(flags + r) - seq) < 0) {
-            if (++rounds > (1 << 20)) return false;  // (about a microsecond a round)
-            __nanosleep(rounds < 64 ? 20 : 200);
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ int atom_add_acq_rel(int* p, int v) {
-    int old;
-    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
-    return old;
-}
-__device__ __forceinline__ void bar_output_warps() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-__device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
-__device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
-
-// dense_ops.h:44-59 of the reference: silu, and gelu_tanh as x * sigmoid(2 u), u = sqrt(2 / pi) (x + 0.044715 x^3)
-__device__ __forceinline__ float act_gate(float g, int act) {
-    const float u = act ? g * (1.5957691216f + 0.0713548162f * (g * g)) : g;
-    return g / (1.f + __expf(-u));
-}
-
-// Quotients of item counts: 32-bit arithmetic when the launch's numbers allow it (p.small): a 64-bit division is a long
-// subroutine on the GPU, and these sit on every CTA's way to its first copy and on the way to a panel's completion.
-__device__ __forceinline__ int64_t idiv(const TkdParams& p, int64_t num, int64_t den) {
-    return p.small ? (int64_t)((uint32_t)num / (uint32_t)den) : num / den;
-}
-
-// Where a role stands in its CTA's run of items.
-struct Cursor {
-    int panel, slice, seg, pl;
-};
-__device__ __forceinline__ void cursor_init(Cursor& c, const TkdParams& p, int64_t it) {
-    c.panel = (int)idiv(p, it, p.nslices);
-    c.slice = (int)(it - (int64_t)c.panel * p.nslices);
-    c.seg = 0;
-#pragma unroll
-    for (int s = 1; s < 4; ++s)
-        if (s < p.nseg && c.panel >= p.seg[s].panel0) c.seg = s;
-    c.pl = c.panel - p.seg[c.seg].panel0;
-}
-__device__ __forceinline__ void cursor_next(Cursor& c, const TkdParams& p) {
-    if (++c.slice == p.nslices) {
-        c.slice = 0;
-        ++c.panel;
-        if (c.seg + 1 < p.nseg && c.panel >= p.seg[c.seg + 1].panel0) ++c.seg;
-        c.pl = c.panel - p.seg[c.seg].panel0;
-    }
-}
-// What a CTA does with an item's slice sums (the same answer in every role).
-struct Flow {
-    bool start;    // the running sum starts over with this slice
-    bool split;    // the panel's slices are spread over several CTAs: sums go to the scratch buffer
-    bool store;    // split: the running sum is written to the scratch slot of (panel, slice) after this slice
-    bool deliver;  // the streaming warps signal the output warps after this slice (whole: with their sums)
-    int count;     // split and deliver: slices of the panel this CTA has contributed
-};
-__device__ __forceinline__ Flow flow_of(const Cursor& c, const TkdParams& p, int64_t it, int64_t i0, int64_t i1) {
-    Flow f;
-    const int64_t pfirst = (int64_t)c.panel * p.nslices;
-    const bool nonprefix = pfirst < i0;  // the run begins inside this panel, past its slice 0
-    const bool last_here = c.slice == p.nslices - 1 || it == i1 - 1;
-    f.start = nonprefix || c.slice == 0;
-    f.split = nonprefix || pfirst + p.nslices > i1;
-    f.store = f.split && (nonprefix || last_here);
-    f.deliver = last_here;
-    f.count = nonprefix ? c.slice - (int)(i0 - pfirst) + 1 : c.slice + 1;
-    return f;
-}
-
-template <int FMT>
-struct Fmt;
-template <>
-struct Fmt<TKD_BFP8> {
-    static constexpr int KSA = 32, SAB = 544, SUBSA = 8, XB = 1;
-};
-template <>
-struct Fmt<TKD_BFP4> {
-    static constexpr int KSA = 64, SAB = 576, SUBSA = 8, XB = 2;
-};
-template <>
-struct Fmt<TKD_BF16> {
-    static constexpr int KSA = 32, SAB = 1024, SUBSA = 4, XB = 1;
-};
-
-// The two mmas of one k32 block of one group of a block-float weight: cw / ew are this lane's code and exponent
-// words of the block (bfloat4_b: 2 and 2; bfloat8_b: 4 and 2).
-template <int FMT, int MT, int NA>
-__device__ __forceinline__ void block_mma(float (&acc)[NA][MT][4], const uint32_t (&cw)[4], const uint32_t (&ew)[2],
-                                          const uint4 (&xv)[MT]) {
-#pragma unroll
-    for (int jj = 0; jj < 2; ++jj) {
-        uint32_t a0, a1, a2, a3;
-        if constexpr (FMT == TKD_BFP4) {
-            const uint32_t w = cw[jj];
-            a0 = w & 0x80078007u, a1 = rot_and<4>(w, 0x80078007u);
-            a2 = rot_and<8>(w, 0x80078007u), a3 = rot_and<12>(w, 0x80078007u);
-        } else {
-            const uint32_t w0 = cw[2 * jj], w1 = cw[2 * jj + 1];
-            a0 = w0 & 0x807F807Fu, a1 = rot_and<8>(w0, 0x807F807Fu);
-            a2 = w1 & 0x807F807Fu, a3 = rot_and<8>(w1, 0x807F807Fu);
-        }
-        const uint32_t s0 = ew[jj] & 0x7F807F80u, s1 = rot_and<8>(ew[jj], 0x7F807F80u);
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            const uint32_t x0 = jj ? xv[m].z : xv[m].x, x1 = jj ? xv[m].w : xv[m].y;
-            mma_bf16(acc[jj % NA][m], a0, a1, a2, a3, mul_bf16x2(x0, s0), mul_bf16x2(x1, s1));
-        }
-    }
-}
-
-__device__ __forceinline__ uint4 ldg_x(const uint16_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
-__device__ __forceinline__ uint4 lds128(uint32_t a) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-    return v;
-}
-
-// What a stage of the ring holds for the streaming warps besides the weights: a 16-byte header the producer writes.
-// .x: flags; .y: the scratch slot (panel * slices + slice) of the stage's item; .z: first k of the next stage.
-enum : uint32_t {
-    ST_FIRST = 1,     // first chunk of its item: the slice sums start from zero
-    ST_LAST = 2,      // last chunk of its item: the flags below apply
-    ST_START = 4,     // the running sum starts over with this slice
-    ST_STORE = 8,     // the running sum goes to the scratch slot
-    ST_DELIVER = 16,  // the output warps are signalled
-    ST_SPLIT = 32,    // ... without the sums (they are in the scratch buffer)
-    ST_END = 64,      // last stage of this CTA's run
-};
-
-// One streaming warp's share of one chunk: super-atoms h, h + 2, ... of one group. code_a / exp_a: shared-memory
-// addresses of this lane's code and exponent words of super-atom h; xb[m]: this lane's row of x at k = 8 t + h * KSA;
-// kc: the chunk's first k. FULL: the chunk has all its super-atoms and ends within K (then xpre holds the activations,
-// loaded before the stage was waited for, when PRE).
-// XS: the activations come from the stage's tile in shared memory instead (xt_a: this lane's row of it, xj: the 16-byte
-// piece of the row its first block starts at, xsw: the row's swizzle).
-template <int FMT, int MT, int NA, bool FULL, bool PRE, bool XS = false>
-__device__ __forceinline__ void chunk_mma(float (&acc)[NA][MT][4], uint32_t code_a, uint32_t exp_a,
-                                          const uint4 (&xpre)[Fmt<FMT>::SUBSA / 2 * Fmt<FMT>::XB][MT],
-                                          const uint16_t* const (&xb)[MT], int kc, int K, int h, int nsa,
-                                          uint32_t xt_a = 0, int xj = 0, int xsw = 0) {
-    using F = Fmt<FMT>;
-    constexpr int NPW = F::SUBSA / 2;  // super-atoms a warp takes of a chunk
-    constexpr int XROW = F::SUBSA * F::KSA * 2;  // bytes of a tile row
-#pragma unroll
-    for (int i = 0; i < NPW; ++i) {
-        if (!FULL && h + 2 * i >= nsa) break;
-        uint32_t cw[F::XB][4], ew[F::XB][2];
-        if constexpr (FMT == TKD_BFP4) {
-            const uint4 ev = lds128(exp_a + 2 * i * F::SAB), cv = lds128(code_a + 2 * i * F::SAB);
-            cw[0][0] = cv.x, cw[0][1] = cv.y, cw[1][0] = cv.z, cw[1][1] = cv.w;
-            cw[0][2] = cw[0][3] = cw[1][2] = cw[1][3] = 0;
-            ew[0][0] = ev.x, ew[0][1] = ev.y, ew[1][0] = ev.z, ew[1][1] = ev.w;
-        } else if constexpr (FMT == TKD_BFP8) {
-            const uint2 ev = lds64(exp_a + 2 * i * F::SAB);
-            const uint4 cv = lds128(code_a + 2 * i * F::SAB);
-            cw[0][0] = cv.x, cw[0][1] = cv.y, cw[0][2] = cv.z, cw[0][3] = cv.w;
-            ew[0][0] = ev.x, ew[0][1] = ev.y;
-        }
-#pragma unroll
-        for (int q = 0; q < F::XB; ++q) {
-            const int k = kc + 2 * i * F::KSA + 32 * q;  // (+ h * KSA, which xb carries)
-            if (!FULL && k + h * F::KSA >= K) break;     // a K that ends inside a super-atom
-            uint4 xv[MT];
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                if constexpr (XS)
-                    xv[m] = lds128(xt_a + m * 8 * XROW + (((xj + (2 * i * F::KSA + 32 * q) / 8) ^ xsw) << 4));
-                else if constexpr (FULL && PRE)
-                    xv[m] = xpre[i * F::XB + q][m];
-                else
-                    xv[m] = ldg_x(xb[m] + k);
-            }
-            if constexpr (FMT == TKD_BF16) {
-#pragma unroll
-                for (int jj = 0; jj < 2; ++jj) {
-                    const uint4 a = lds128(code_a + 2 * i * F::SAB + jj * 512);
-#pragma unroll
-                    for (int m = 0; m < MT; ++m)
-                        mma_bf16(acc[jj % NA][m], a.x, a.y, a.z, a.w, jj ? xv[m].z : xv[m].x, jj ? xv[m].w : xv[m].y);
-                }
-            } else {
-                block_mma<FMT, MT, NA>(acc, cw[q], ew[q], xv);
-            }
-        }
-    }
-}
-
-// bf16 output as the top-k records order it: a monotone 16-bit key, 0 below every value (dense_writer.cpp:215).
-__device__ __forceinline__ uint32_t topk_key(uint16_t b) {
-    return (uint32_t)(b ^ (0x8000u | (0x7FFFu & (0u - (uint32_t)(b >> 15))))) & 0xFFFFu;
-}
-
-// SW: streaming warps, 16 (a warp per column group and half of each chunk's super-atoms) or 8 (a warp takes both halves
-// of its group, one after the other: the 32-row kernel, whose accumulators need the registers that fewer warps leave).
-// ONE: the call has one row (the decode case): the row count is a constant 1 and everything that serves more rows falls
-// away at compile time. (The length of this kernel's code matters beyond the parts that run: adding two more instances
-// of the output stage for 2 and 4 rows made the one-row call 1.5 us slower.)
-// PLAIN: no top-k records and no exchange with other GPUs (the plain matmuls of a decode step): that code falls away too.
-// KWHOLE: K is a whole number of chunks, so the code for a last, shorter chunk falls away as well.
-template <int FMT, int MT, int SW, bool ONE, bool PLAIN, bool KWHOLE>
-__global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const __grid_constant__ TkdParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    using F = Fmt<FMT>;
-    constexpr int MP = MT == 1 ? 8 : (MT == 2 ? 24 : 40);  // floats per column in the hand-over buffers
-    constexpr int MR = 8 * MT;                             // rows the accumulators cover
-    constexpr int NA = MT == 1 ? 2 : 1;                    // accumulator sets a streaming warp alternates between
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TKD_MAX_STAGES);
-    const uint32_t pfull0 = smem_u32(bars + 2 * TKD_MAX_STAGES), pempty0 = pfull0 + 16, xfull0 = pfull0 + 32;
-    // NH: halves of a chunk's super-atoms a streaming warp takes; XS: the activations are staged in shared memory (two
-    // tiles of MR rows x one chunk of k, filled by the streaming warps' own asynchronous copies one stage ahead);
-    // NPB: hand-over buffers between the streaming and the output warps
-    constexpr int NH = 16 / SW;
-    constexpr bool XS = MT >= 2 && FMT != TKD_BFP4;
-    constexpr int NPB = MT == 4 ? 1 : 2;
-    volatile int* sflag = reinterpret_cast<volatile int*>(smem + TKD_SMEM_HEAD - 16);
-    uint4* hdr = reinterpret_cast<uint4*>(smem + 512);  // one header per stage of the ring
-    float* pbuf = reinterpret_cast<float*>(smem + p.off_pbuf);  // [2 buffers][2 halves][128 columns][MP]
-    float* tbuf = reinterpret_cast<float*>(smem + p.off_tbuf);  // [128 columns][MP]
-    uint8_t* ring = smem + p.off_ring;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // let the kernel after this one in the stream start its CTAs as SMs become free
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (tid == 0) PROF_TIME(0);
-    if (tid == 0) {
-        for (int s = 0; s < p.nstages; ++s) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, SW);
-        }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(pfull0 + 8 * s, SW);
-            mbar_init(pempty0 + 8 * s, 4);
-            mbar_init(xfull0 + 8 * s, SW * 32);
-        }
-        sflag[0] = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    const int64_t T = p.total_items;
-    const int64_t i0 = idiv(p, T * blockIdx.x, gridDim.x), i1 = idiv(p, T * (blockIdx.x + 1), gridDim.x);
-    const int nst = p.nstages;
-    const int M = ONE ? 1 : p.M, K = p.K;
-    const int topk_k = PLAIN ? 0 : p.topk_k, npeers = PLAIN ? 0 : p.npeers;
-    const bool glu2 = p.epi == TKD_EPI_GLU2;
-    constexpr int CK = F::SUBSA * F::KSA;
-    const int nsa_total = (K + F::KSA - 1) / F::KSA;
-    if (i0 >= i1) return;
-    // Order of a CTA's items: if its run ends inside a panel that it holds from slice 0 on, those slices come first.
-    // Their sum is one of several the panel is added up from by whichever CTA delivers last; done first, that exchange
-    // overlaps the rest of the run instead of sitting at the kernel's end.
-    const int64_t lastp0 = idiv(p, i1 - 1, p.nslices) * p.nslices;
-    const int64_t tail0 = lastp0 > i0 && lastp0 + p.nslices > i1 ? lastp0 : i1;
-    const int64_t lead = i1 - tail0;
-
-    if (warp == 0) {
-        // ---------------------------------------------------------------- producer
-        if (lane != 0) return;
-        Cursor c, cn;  // this item, and the one after it
-        uint32_t st = 0;
-        bool ok = true;
-        const int64_t nitems = i1 - i0;
-        auto item_at = [&](int64_t j) { return j < lead ? tail0 + j : i0 + (j - lead); };
-        cursor_init(cn, p, item_at(0));
-        for (int64_t j = 0; j < nitems && ok; ++j) {
-            const int64_t it = item_at(j);
-            c = cn;
-            if (j + 1 < nitems) {
-                if (j + 1 == lead)
-                    cursor_init(cn, p, item_at(j + 1));
-                else
-                    cursor_next(cn, p);
-            }
-            const Flow f = flow_of(c, p, it, i0, i1);
-            const TkdSegDev& sg = p.seg[c.seg];
-            const int k0 = c.slice * p.ks, kv = min(p.ks, K - k0);
-            const int c0 = k0 / CK, nch = (kv + CK - 1) / CK;
-            // a panel of a (gate, up) pair is half a panel of each weight: 4 groups of the gate's, 4 of the up's
-            const uint8_t* src = sg.w + (int64_t)(glu2 ? c.pl >> 1 : c.pl) * p.panel_bytes;
-            const uint8_t* src2 = glu2 ? sg.w2 + (int64_t)(c.pl >> 1) * p.panel_bytes : nullptr;
-            for (int ch = 0; ch < nch; ++ch, ++st) {
-                const uint32_t s = st % nst;
-                ok = mbar_wait(empty0 + 8 * s, ((st / nst) & 1) ^ 1, p.status);
-                if (!ok) break;
-                const int nsa = min(F::SUBSA, nsa_total - (c0 + ch) * F::SUBSA);
-                const uint32_t gbytes = (uint32_t)nsa * F::SAB;  // one group's share of the chunk
-                const int64_t coff = (int64_t)(c0 + ch) * (F::SUBSA * F::SAB * 8);
-                const uint32_t dst = smem_u32(ring + (size_t)s * p.stage_bytes);
-                // the stage's header, ordered before the streaming warps' reads by the arrival below
-                const bool last = ch == nch - 1;
-                uint32_t fl = (ch == 0 ? ST_FIRST : 0u) | (last && j == nitems - 1 ? ST_END : 0u);
-                if (last)
-                    fl |= ST_LAST | (f.start ? ST_START : 0u) | (f.store ? ST_STORE : 0u) |
-                          (f.deliver ? ST_DELIVER : 0u) | (f.split ? ST_SPLIT : 0u);
-                const int knext = last ? cn.slice * p.ks : (c0 + ch + 1) * CK;
-                hdr[s] = make_uint4(fl, (uint32_t)(c.panel * p.nslices + c.slice), (uint32_t)knext, 0u);
-                mbar_expect_tx(full0 + 8 * s, 8 * gbytes);
-                if (glu2) {
-                    const int64_t hoff = coff + (int64_t)(c.pl & 1) * 4 * gbytes;
-                    bulk_g2s(dst, src + hoff, 4 * gbytes, full0 + 8 * s);
-                    bulk_g2s(dst + 4 * gbytes, src2 + hoff, 4 * gbytes, full0 + 8 * s);
-                } else {
-                    bulk_g2s(dst, src + coff, 8 * gbytes, full0 + 8 * s);
-                }
-            }
-        }
-        // (every stage issued above is waited for by the streaming warps before they leave; after a timeout the copies
-        // still in flight are given a bounded wait here so that none lands after the CTA has gone)
-        if (!ok) {
-            for (uint32_t back = 1; back <= (uint32_t)nst && back <= st; ++back) {
-                const uint32_t q = st - back;
-                for (uint32_t i = 0; i < 64; ++i)
-                    if (mbar_try_wait(full0 + 8 * (q % nst), (q / nst) & 1)) break;
-            }
-        }
-    } else if (warp <= SW) {
-        // ---------------------------------------------------------------- streaming warps
-        // One flat loop over the stages of the ring; everything about items comes with the stage's header.
-        // (x, the scratch buffer and the outputs may belong to the kernel before this one: wait for it to complete)
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        const int cw = warp - 1;
-        const int g8 = cw & 7, h0 = SW == 16 ? cw >> 3 : 0;
-        const int g = lane >> 2, t = lane & 3;
-        constexpr int NX = F::SUBSA / 2 * F::XB;
-        constexpr bool PRE = MT <= 2 && NH == 1 && !XS;
-        constexpr int XROW = CK * 2, XTILE = MR * XROW, XPR = CK / 8;  // a tile row's bytes, a tile's, 16-byte pieces a row
-        const uint32_t xt0 = smem_u32(smem + p.off_xt);
-        // a tile row r keeps its 16-byte piece j at position j ^ swz(r): the eight lanes a shared-memory load serves
-        // together (two rows, four pieces each) then fall into eight different bank groups
-        auto swz = [](int r) { return ((r & 1) << 2) ^ ((r >> 1) & 3); };
-        auto load_x = [&](int buf, int k0) {
-            for (int e = cw * 32 + lane; e < MR * XPR; e += SW * 32) {
-                const int r = e / XPR, j = e - r * XPR;
-                if (k0 + j * 8 < K) {
-                    const uint16_t* src = p.x + (int64_t)min(r, M - 1) * p.ldx + k0 + j * 8;
-                    const uint32_t dst = xt0 + buf * XTILE + r * XROW + ((j ^ swz(r)) << 4);
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-                }
-            }
-            asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];" ::"r"(xfull0 + 8 * buf) : "memory");
-        };
-        const uint32_t xt_lane = xt0 + g * XROW;  // (rows 8 m + g of a tile: the swizzle depends on g alone)
-        const int xsw = swz(g);
-        uint32_t nstage = 0, prev_slot = 0, prev_phase = 0;
-        constexpr int EXPB = FMT == TKD_BFP4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
-        const uint16_t* xb[NH][MT];
-#pragma unroll
-        // (a lane whose row lies beyond M reads row M - 1 instead: a B column only feeds its own output column, and
-        // the columns beyond M are never read, so those lanes need no predicate and no zero fill)
-        for (int hh = 0; hh < NH; ++hh)
-#pragma unroll
-            for (int m = 0; m < MT; ++m)
-                xb[hh][m] = p.x + (int64_t)min(8 * m + g, M - 1) * p.ldx + 8 * t + (h0 + hh) * F::KSA;
-        const uint32_t ring_a = smem_u32(ring), hdr_a = smem_u32(hdr);
-        const uint32_t code_off = g8 * (F::SUBSA * F::SAB) + h0 * F::SAB + EXPB + lane * 16;
-        const uint32_t exp_off = g8 * (F::SUBSA * F::SAB) + h0 * F::SAB + t * (EXPB / 4);
-        uint32_t slot = 0, phase = 0, pi = 0;  // ring position and its parity; deliveries so far
-        const int64_t first_it = lead > 0 ? tail0 : i0;
-        int kc = (int)(first_it - idiv(p, first_it, p.nslices) * p.nslices) * p.ks;
-        float acc[NH][NA][MT][4], tot[NH][MT][4];
-        if constexpr (XS) load_x(0, kc);
-        while (true) {
-            const bool full = KWHOLE || kc + CK <= K;
-            uint4 xpre[NX][MT];
-            if (PRE && full) {
-#pragma unroll
-                for (int i = 0; i < F::SUBSA / 2; ++i)
-#pragma unroll
-                    for (int q = 0; q < F::XB; ++q)
-#pragma unroll
-                        for (int m = 0; m < MT; ++m) xpre[i * F::XB + q][m] = ldg_x(xb[0][m] + kc + 2 * i * F::KSA + 32 * q);
-            }
-            if (!mbar_wait(full0 + 8 * slot, phase, p.status)) break;
-            const uint4 hd = lds128(hdr_a + 16 * slot);
-            const uint32_t fl = hd.x;
-            if constexpr (XS) {
-                // the next stage's activations into the other tile, once every warp has left the stage before this one
-                // (whose tile that was); then this stage's own tile must have landed
-                if (!(fl & ST_END)) {
-                    if (nstage && !mbar_wait(empty0 + 8 * prev_slot, prev_phase, p.status)) break;
-                    load_x((nstage + 1) & 1, (int)hd.z);
-                }
-                if (!mbar_wait(xfull0 + 8 * (nstage & 1), (nstage >> 1) & 1, p.status)) break;
-                prev_slot = slot, prev_phase = phase, ++nstage;
-            } else if constexpr (!PRE) {
-                // the activations of the stage after this one, asked into L1 now (the warps share the lines out): by the
-                // time that stage is computed its loads hit L1 instead of waiting for L2 one block at a time
-                constexpr int LPR = CK * 2 / 128;  // 128-byte lines of a row's share of a chunk
-                const int kn = (int)hd.z;
-                for (int i = cw * 32 + lane; i < M * LPR; i += SW * 32) {
-                    const int row = i / LPR, seg = i - row * LPR;
-                    if (kn + seg * 64 < K)
-                        asm volatile("prefetch.global.L1 [%0];" ::"l"(p.x + (int64_t)row * p.ldx + kn + seg * 64));
-                }
-            }
-            if (fl & ST_FIRST) {
-#pragma unroll
-                for (int hh = 0; hh < NH; ++hh)
-#pragma unroll
-                    for (int j = 0; j < NA; ++j)
-#pragma unroll
-                        for (int m = 0; m < MT; ++m)
-                            acc[hh][j][m][0] = acc[hh][j][m][1] = acc[hh][j][m][2] = acc[hh][j][m][3] = 0.f;
-            }
-            const uint32_t sbase = ring_a + slot * p.stage_bytes;
-#pragma unroll
-            for (int hh = 0; hh < NH; ++hh) {
-                const int h = h0 + hh;
-                if (full) {
-                    chunk_mma<FMT, MT, NA, true, PRE, XS>(acc[hh], sbase + code_off + hh * F::SAB, sbase + exp_off + hh * F::SAB,
-                                                          xpre, xb[hh], kc, K, h, F::SUBSA, xt_lane + ((nstage + 1) & 1) * XTILE,
-                                                          h * F::KSA / 8 + t, xsw);
-                } else {
-                    // the last chunk of K: fewer super-atoms, the groups closer together
-                    const int nsa = nsa_total - kc / CK * F::SUBSA;
-                    const uint32_t gb = sbase + g8 * nsa * F::SAB + h * F::SAB;
-                    chunk_mma<FMT, MT, NA, false, PRE, XS>(acc[hh], gb + EXPB + lane * 16, gb + t * (EXPB / 4), xpre, xb[hh], kc,
-                                                           K, h, nsa, xt_lane + ((nstage + 1) & 1) * XTILE, h * F::KSA / 8 + t, xsw);
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + 8 * slot);
-            if (++slot == (uint32_t)nst) slot = 0, phase ^= 1;
-            kc = (int)hd.z;
-            if (!(fl & ST_LAST)) continue;
-            // ---- the item's slice is done
-#pragma unroll
-            for (int hh = 0; hh < NH; ++hh)
-#pragma unroll
-                for (int m = 0; m < MT; ++m)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float part = NA == 2 ? acc[hh][0][m][e] + acc[hh][NA - 1][m][e] : acc[hh][0][m][e];
-                        tot[hh][m][e] = fl & ST_START ? part : tot[hh][m][e] + part;
-                    }
-            if (fl & ST_STORE) {
-                // straight into the scratch slot of (panel, slice): [half][row][128 columns]
-#pragma unroll
-                for (int hh = 0; hh < NH; ++hh) {
-                    float* sc = p.scratch + ((size_t)hd.y * 2 + h0 + hh) * M * TKD_PANEL_COLS + g8 * 16 + g;
-#pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        const int r0 = 8 * m + 2 * t;
-                        if (r0 < M) {
-                            __stcg(sc + (size_t)r0 * TKD_PANEL_COLS, tot[hh][m][0]);
-                            __stcg(sc + (size_t)r0 * TKD_PANEL_COLS + 8, tot[hh][m][2]);
-                        }
-                        if (r0 + 1 < M) {
-                            __stcg(sc + (size_t)(r0 + 1) * TKD_PANEL_COLS, tot[hh][m][1]);
-                            __stcg(sc + (size_t)(r0 + 1) * TKD_PANEL_COLS + 8, tot[hh][m][3]);
-                        }
-                    }
-                }
-            }
-            if (fl & ST_DELIVER) {
-                const uint32_t pb = NPB == 2 ? pi & 1 : 0;
-                if (!mbar_wait(pempty0 + 8 * pb, ((NPB == 2 ? pi >> 1 : pi) & 1) ^ 1, p.status)) break;
-                if (!(fl & ST_SPLIT)) {
-#pragma unroll
-                    for (int hh = 0; hh < NH; ++hh) {
-                        float* pc = pbuf + ((size_t)(pb * 2 + h0 + hh) * TKD_PANEL_COLS + g8 * 16 + g) * MP + 2 * t;
-#pragma unroll
-                        for (int m = 0; m < MT; ++m) {
-                            *reinterpret_cast<float2*>(pc + 8 * m) = make_float2(tot[hh][m][0], tot[hh][m][1]);
-                            *reinterpret_cast<float2*>(pc + 8 * MP + 8 * m) = make_float2(tot[hh][m][2], tot[hh][m][3]);
-                        }
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(pfull0 + 8 * pb);
-                ++pi;
-            }
-            if (fl & ST_END) break;
-        }
-        if constexpr (XS) asm volatile("cp.async.wait_all;" ::: "memory");  // (none of this thread's copies may land later)
-        if (warp == 1) PROF_TIME(1);
-    } else {
-        // ---------------------------------------------------------------- output warps
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        const int et = tid - (1 + SW) * 32;  // the panel column this thread owns
-        const int ow = warp - (1 + SW);
-        Cursor c;
-        uint32_t pi = 0;
-        float tot[MR];
-#ifdef TKD_PROF
-        unsigned long long _pm[4] = {0, 0, 0, 0};
-#endif
-        bool ok = true;
-        for (int64_t j = 0; j < i1 - i0 && ok; ++j) {
-            const int64_t it = j < lead ? tail0 + j : i0 + (j - lead);
-            if (j == 0 || j == lead)
-                cursor_init(c, p, it);
-            else
-                cursor_next(c, p);
-            const Flow f = flow_of(c, p, it, i0, i1);
-            if (!f.deliver) continue;
-            const TkdSegDev& sg = p.seg[c.seg];
-            const uint32_t pb = NPB == 2 ? pi & 1 : 0;
-            // this thread's column within its weight; its group's exponent byte and its scale are asked for now, so
-            // that their latency passes while the streaming warps are still at work
-            const int n = glu2 ? c.pl * 64 + (et & 63) : c.pl * TKD_PANEL_COLS + et;
-            const bool in_w = n < sg.n_valid;
-            int ebyte = 0;
-            float sc = 1.f;
-            if constexpr (FMT != TKD_BF16) ebyte = (glu2 && et >= 64 ? sg.emax2 : sg.emax)[n >> 4];
-            if (p.scale_dt != TKD_DT_NONE && in_w) {
-                const void* sp = glu2 && et >= 64 ? p.scale2 : p.scale;
-                sc = p.scale_dt == TKD_DT_BF16 ? bf16_bits_to_f32(static_cast<const uint16_t*>(sp)[n])
-                                               : static_cast<const float*>(sp)[n];
-            }
-            PROF_T0;
-            ok = mbar_wait(pfull0 + 8 * pb, (NPB == 2 ? pi >> 1 : pi) & 1, p.status);
-            if (!ok) break;
-            PROF_MARK(0);
-            if (ow == 0) PROF_ADD(16);
-            bool finish = !f.split;
-            // (9 rows and more: the column's sums live in the thread's row of tbuf, not in registers, and every loop over
-            // rows below is rolled: this code runs once or twice a CTA, at the speed of instruction cache misses, and
-            // unrolled over 32 rows it is thousands of instructions)
-            float* const trow = tbuf + (size_t)et * MP;
-            if (!f.split && MT >= 2) {
-                const float* p0 = pbuf + ((size_t)(pb * 2) * TKD_PANEL_COLS + et) * MP;
-                const float* p1 = p0 + (size_t)TKD_PANEL_COLS * MP;
-#pragma unroll 1
-                for (int m = 0; m < MR; m += 4) {
-                    const float4 a = *reinterpret_cast<const float4*>(p0 + m), b = *reinterpret_cast<const float4*>(p1 + m);
-                    *reinterpret_cast<float4*>(trow + m) = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
-                }
-            } else if (!f.split) {
-                // the two halves' sums cover the whole panel
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const float* pc = pbuf + ((size_t)(pb * 2 + hh) * TKD_PANEL_COLS + et) * MP;
-#pragma unroll
-                    for (int m = 0; m < MR; m += 4) {
-                        const float4 v = *reinterpret_cast<const float4*>(pc + m);
-                        const float part[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) tot[m + e] = hh == 0 ? part[e] : tot[m + e] + part[e];
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(pempty0 + 8 * pb);
-            ++pi;
-            if (f.split) {
-                // the streaming warps have put this CTA's slices of the panel into the scratch buffer (their arrival
-                // on the hand-over barrier orders those stores before this point): count them in, and if they were
-                // the last the panel waited for, add all of its slices up
-                if (et == 0) {
-                    // (one release-acquire atomic: the slice sums stored before it, by the streaming warps whose
-                    // arrival this thread waited for, are visible to whichever CTA sees the count complete, and that CTA
-                    // sees all the others')
-                    const int old = atom_add_acq_rel(p.counters + c.panel, f.count);
-                    const int last = old + f.count == p.nslices;
-                    if (last) p.counters[c.panel] = 0;  // ready for the next call
-                    sflag[0] = last;
-                }
-                bar_output_warps();
-                finish = sflag[0] != 0;
-                PROF_MARK(1);
-                if (finish) {
-                    // the panel's first slices came as one sum from the CTA that holds its slice 0: up to where?
-                    const int64_t pfirst = (int64_t)c.panel * p.nslices;
-                    const int64_t owner = idiv(p, (pfirst + 1) * gridDim.x - 1, T);
-                    const int64_t oend = idiv(p, T * (owner + 1), gridDim.x);
-                    const int pe = (int)min((int64_t)p.nslices, oend - pfirst);
-                    const float* s0 = p.scratch + pfirst * 2 * M * TKD_PANEL_COLS + et;
-                    // term (s, hh, m) of the sums; the adds run in slice order, the loads many at a time
-                    auto term = [&](int s, int hh, int m) {
-                        return __ldcg(s0 + ((size_t)(s * 2 + hh) * M + m) * TKD_PANEL_COLS);
-                    };
-                    if (M == 1) {
-                        float t0 = term(pe - 1, 0, 0), t1 = term(pe - 1, 1, 0);
-                        for (int s = pe; s < p.nslices; s += 8) {
-                            float v0[8], v1[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                if (s + j < p.nslices) v0[j] = term(s + j, 0, 0), v1[j] = term(s + j, 1, 0);
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                if (s + j < p.nslices) t0 += v0[j], t1 += v1[j];
-                        }
-                        tot[0] = t0 + t1;
-                    } else if constexpr (MT >= 2) {
-                        // eight rows at a time (a rolled loop, the sums into tbuf); both halves' loads of four entries
-                        // (the sum so far counts as one) in flight together, unconditional (a row or entry that is not
-                        // there re-reads the last that is) so that they stay one block of code
-#pragma unroll 1
-                        for (int rb = 0; rb < M; rb += 8) {
-                            float th[2][8];
-#pragma unroll 1
-                            for (int s = pe - 1; s < p.nslices; s += 4) {
-                                float v[2][4][8];
-#pragma unroll
-                                for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j)
-#pragma unroll
-                                        for (int m = 0; m < 8; ++m)
-                                            v[hh][j][m] = term(min(s + j, p.nslices - 1), hh, min(rb + m, M - 1));
-#pragma unroll
-                                for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j)
-#pragma unroll
-                                        for (int m = 0; m < 8; ++m) {
-                                            if (s + j >= p.nslices) continue;
-                                            th[hh][m] = s + j == pe - 1 ? v[hh][j][m] : th[hh][m] + v[hh][j][m];
-                                        }
-                            }
-                            *reinterpret_cast<float4*>(trow + rb) =
-                                make_float4(th[0][0] + th[1][0], th[0][1] + th[1][1], th[0][2] + th[1][2], th[0][3] + th[1][3]);
-                            *reinterpret_cast<float4*>(trow + rb + 4) =
-                                make_float4(th[0][4] + th[1][4], th[0][5] + th[1][5], th[0][6] + th[1][6], th[0][7] + th[1][7]);
-                        }
-                    } else {
-#pragma unroll 1
-                        for (int hh = 0; hh < 2; ++hh) {
-                            {
-                                float th[MR];
-#pragma unroll
-                                for (int m = 0; m < MR; ++m)
-                                    if (m < M) th[m] = term(pe - 1, hh, m);
-#pragma unroll 1
-                                for (int s = pe; s < p.nslices; ++s) {
-                                    float v[MR];
-#pragma unroll
-                                    for (int m = 0; m < MR; ++m)
-                                        if (m < M) v[m] = term(s, hh, m);
-#pragma unroll
-                                    for (int m = 0; m < MR; ++m)
-                                        if (m < M) th[m] += v[m];
-                                }
-#pragma unroll
-                                for (int m = 0; m < MR; ++m) tot[m] = hh == 0 ? th[m] : tot[m] + th[m];
-                            }
-                        }
-                    }
-                }
-                PROF_MARK(2);
-                bar_output_warps();  // sflag may be written again only after everyone has read it
-            }
-            if (ow == 0) PROF_ADD(17);
-            if (!finish) continue;
-
-            // ------------------------------------------------------------ the output stage of one panel
-            // (a generic lambda over the rows it covers: a one-row call runs the one-row instance, a fraction of the code
-            // of the eight-, sixteen- or thirty-two-row one; this code runs once or twice a CTA, straight from the
-            // instruction cache's misses, so its length is its cost)
-            uint16_t* y16 = static_cast<uint16_t*>(p.out);
-            auto output_stage = [&](auto rows_const) {
-                constexpr int R = decltype(rows_const)::value;
-                // the block-float factor of this thread's group
-                if constexpr (FMT != TKD_BF16) {
-                    // 2^e in two factors, each a normal float (e is within -69 .. 189)
-                    const int e = ebyte + 64 - (FMT == TKD_BFP8 ? 133 : 129);
-                    const int e1 = e / 2, e2 = e - e1;
-                    const float f1 = __uint_as_float((uint32_t)(e1 + 127) << 23), f2 = __uint_as_float((uint32_t)(e2 + 127) << 23);
-    #pragma unroll
-                    for (int m = 0; m < R; ++m) tot[m] = tot[m] * f1 * f2;
-                }
-                if (p.scale_dt != TKD_DT_NONE && in_w) {
-    #pragma unroll
-                    for (int m = 0; m < R; ++m) tot[m] *= sc;
-                }
-                int ocol = -1;  // the output column this thread writes, if any
-                if (p.epi == TKD_EPI_GLU_IL || glu2) {
-                    float* tc = tbuf + (size_t)et * MP;
-    #pragma unroll
-                    for (int m = 0; m < R; ++m) tc[m] = tot[m];
-                    bar_output_warps();
-                    if (et < 64) {
-                        // interleaved: 32 gate columns, then their 32 up columns; two weights: gate 0-63, up 64-127
-                        const int gc = glu2 ? et : 64 * (et >> 5) + (et & 31), uc = glu2 ? et + 64 : gc + 32;
-                        const int nw = glu2 ? n : c.pl * TKD_PANEL_COLS + uc;  // the pair's last column in the weight
-                        if (nw < sg.n_valid) ocol = sg.out_col0 + c.pl * 64 + et;
-                        const float* gp = tbuf + (size_t)gc * MP;
-                        const float* up = tbuf + (size_t)uc * MP;
-    #pragma unroll
-                        for (int m = 0; m < R; ++m) tot[m] = act_gate(gp[m], p.act) * up[m];
-                    }
-                    bar_output_warps();  // tbuf is free again
-                } else if (in_w) {
-                    ocol = sg.out_col0 + n;
-                }
-                const bool store = ocol >= 0 && (topk_k == 0 || p.write_y);
-                if (ocol >= 0) {
-                    // (the residual is read for every row before anything is stored: the output may be the residual's own
-                    // memory, and loads placed after stores to what may be the same address would wait for each other row
-                    // by row)
-                    if (p.epi == TKD_EPI_OUT32) {
-                        if (p.res_dt == TKD_DT_F32) {
-    #pragma unroll
-                            for (int m = 0; m < R; ++m)
-                                if (m < M) tot[m] += static_cast<const float*>(p.res)[(size_t)m * p.ldr + ocol];
-                        }
-                        float* y32 = static_cast<float*>(p.out);
-    #pragma unroll
-                        for (int m = 0; m < R; ++m)
-                            if (m < M) {
-                                y32[(size_t)m * p.ldo + ocol] = tot[m];
-    #pragma unroll 1
-                                for (int q = 0; q < npeers; ++q)
-                                    if (p.peer_out[q]) static_cast<float*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = tot[m];
-                            }
-                    } else {
-                        if (p.epi == TKD_EPI_RESIDUAL) {
-    #pragma unroll
-                            for (int m = 0; m < R; ++m)
-                                if (m < M)
-                                    tot[m] += bf16_bits_to_f32(static_cast<const uint16_t*>(p.res)[(size_t)m * p.ldr + ocol]);
-                        }
-    #pragma unroll
-                        for (int m = 0; m < R; ++m)
-                            if (m < M) {
-                                const uint16_t b = f32_to_bf16_bits(tot[m]);
-                                if (store) {
-                                    y16[(size_t)m * p.ldo + ocol] = b;
-    #pragma unroll 1
-                                    for (int q = 0; q < npeers; ++q)
-                                        if (p.peer_out[q]) static_cast<uint16_t*>(p.peer_out[q])[(size_t)m * p.ldo + ocol] = b;
-                                }
-                                if (topk_k && !p.write_y && m < p.topk_rows) p.ytmp[(size_t)m * p.ld_ytmp + n] = b;
-                            }
-                    }
-                }
-            };
-            if constexpr (MT >= 2) {
-                // the same stage from the sums in tbuf, eight rows at a time in a rolled loop
-                float colf = 1.f, colg = 1.f;  // the column's block-float factor (in two normal floats) and its scale
-                if constexpr (FMT != TKD_BF16) {
-                    const int e = ebyte + 64 - (FMT == TKD_BFP8 ? 133 : 129);
-                    const int e1 = e / 2, e2 = e - e1;
-                    colf = __uint_as_float((uint32_t)(e1 + 127) << 23), colg = __uint_as_float((uint32_t)(e2 + 127) << 23);
-                }
-                const float cols = p.scale_dt != TKD_DT_NONE && in_w ? sc : 1.f;
-                const bool glu = p.epi == TKD_EPI_GLU_IL || glu2;
-                int ocol = -1;
-                const float *gp = trow, *up = trow;
-                if (glu) {
-                    // every column's sums scaled in place, then the (gate, up) pairs read across columns
-#pragma unroll 1
-                    for (int m = 0; m < MR; m += 4) {
-                        float4 v = *reinterpret_cast<float4*>(trow + m);
-                        v.x = v.x * colf * colg * cols, v.y = v.y * colf * colg * cols;
-                        v.z = v.z * colf * colg * cols, v.w = v.w * colf * colg * cols;
-                        *reinterpret_cast<float4*>(trow + m) = v;
-                    }
-                    bar_output_warps();
-                    if (et < 64) {
-                        const int gc = glu2 ? et : 64 * (et >> 5) + (et & 31), uc = glu2 ? et + 64 : gc + 32;
-                        const int nw = glu2 ? n : c.pl * TKD_PANEL_COLS + uc;
-                        if (nw < sg.n_valid) ocol = sg.out_col0 + c.pl * 64 + et;
-                        gp = tbuf + (size_t)gc * MP, up = tbuf + (size_t)uc * MP;
-                    }
-                } else if (in_w) {
-                    ocol = sg.out_col0 + n;
-                }
-                const bool store = ocol >= 0 && (topk_k == 0 || p.write_y);
-                if (ocol >= 0) {
-#pragma unroll 1
-                    for (int r0 = 0; r0 < M; r0 += 8) {
-                        float v[8];
-#pragma unroll
-                        for (int m = 0; m < 8; ++m)
-                            v[m] = glu ? act_gate(gp[r0 + m], p.act) * up[r0 + m] : trow[r0 + m] * colf * colg * cols;
-                        // (the residual is read for all eight rows before anything is stored: see the one-row form)
-                        if (p.epi == TKD_EPI_OUT32 && p.res_dt == TKD_DT_F32) {
-#pragma unroll
-                            for (int m = 0; m < 8; ++m)
-                                if (r0 + m < M) v[m] += static_cast<const float*>(p.res)[(size_t)(r0 + m) * p.ldr + ocol];
-                        } else if (p.epi == TKD_EPI_RESIDUAL) {
-#pragma unroll
-                            for (int m = 0; m < 8; ++m)
-                                if (r0 + m < M)
-                                    v[m] += bf16_bits_to_f32(static_cast<const uint16_t*>(p.res)[(size_t)(r0 + m) * p.ldr + ocol]);
-                        }
-#pragma unroll
-                        for (int m = 0; m < 8; ++m) {
-                            if (r0 + m >= M) break;
-                            const size_t at = (size_t)(r0 + m) * p.ldo + ocol;
-                            if (p.epi == TKD_EPI_OUT32) {
-                                static_cast<float*>(p.out)[at] = v[m];
-                                for (int q = 0; q < npeers; ++q)
-                                    if (p.peer_out[q]) static_cast<float*>(p.peer_out[q])[at] = v[m];
-                            } else {
-                                const uint16_t b = f32_to_bf16_bits(v[m]);
-                                if (store) {
-                                    y16[at] = b;
-                                    for (int q = 0; q < npeers; ++q)
-                                        if (p.peer_out[q]) static_cast<uint16_t*>(p.peer_out[q])[at] = b;
-                                }
-                                if (topk_k && !p.write_y && r0 + m < p.topk_rows) p.ytmp[(size_t)(r0 + m) * p.ld_ytmp + n] = b;
-                            }
-                        }
-                    }
-                }
-                if (glu) bar_output_warps();  // tbuf is free again
-            } else if (M == 1) {
-                output_stage(std::integral_constant<int, 1>{});
-            } else {
-                output_stage(std::integral_constant<int, MR>{});
-            }
-            if (ow == 0) PROF_ADD(18);
-            PROF_MARK(3);
-            PROF_MARKS_OUT;
-            if (topk_k == 0) continue;
-
-            // ------------------------------------------------------------ top-k records: one per unit of columns,
-            // made by the CTA that completes the unit's last panel, from the bf16 outputs themselves
-            const int upanels = p.topk_unit / TKD_PANEL_COLS;
-            const int unit = c.pl / upanels;
-            const int in_unit = min(upanels, p.total_panels - unit * upanels);
-            __threadfence();
-            bar_output_warps();
-            if (et == 0) {
-                const int old = atomicAdd(p.unit_counters + unit, 1);
-                const int last = old + 1 == in_unit;
-                if (last) p.unit_counters[unit] = 0;
-                sflag[0] = last;
-            }
-            bar_output_warps();
-            const bool scan = sflag[0] != 0;
-            bar_output_warps();
-            if (!scan) continue;
-            __threadfence();
-            const uint16_t* ysrc = p.write_y ? y16 + sg.out_col0 : p.ytmp;
-            const int64_t ldy = p.write_y ? p.ldo : p.ld_ytmp;
-            const int col0 = unit * p.topk_unit;  // the unit's first column (call-relative)
-            uint32_t* red = reinterpret_cast<uint32_t*>(tbuf);
-            const size_t rec_at = (size_t)(p.topk_slot0 + unit) * 2 * p.topk_rows * topk_k;
-            uint32_t* rec = p.records + rec_at;
-            for (int r = 0; r < p.topk_rows; ++r) {
-                // candidates: (key << 16 | 0xFFFF - position in unit) orders by key descending, then column ascending;
-                // this thread's 16 (a unit holds at most 2048 columns) are loaded once
-                uint32_t cand[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int cc = et + j * TKD_PANEL_COLS, col = col0 + cc;
-                    uint32_t key = 0;
-                    if (cc < p.topk_unit && col < p.topk_n && col < sg.n_valid)
-                        key = topk_key(__ldcg(ysrc + (size_t)r * ldy + col));
-                    cand[j] = key ? (key << 16) | (0xFFFFu - (uint32_t)cc) : 0u;
-                }
-                uint32_t bound = 0xFFFFFFFFu;
-                for (int q = 0; q < topk_k; ++q) {
-                    uint32_t best = 0;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (cand[j] < bound && cand[j] > best) best = cand[j];
-#pragma unroll
-                    for (int o = 16; o; o >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, o));
-                    if (lane == 0) red[ow] = best;
-                    bar_output_warps();
-                    best = max(max(red[0], red[1]), max(red[2], red[3]));
-                    bar_output_warps();
-                    bound = best;  // (0: nothing left, the remaining slots stay empty)
-                    if (et == 0) {
-                        const uint32_t key = best >> 16;
-                        const uint32_t idx = best ? p.topk_base + (uint32_t)col0 + (0xFFFFu - (best & 0xFFFFu)) : 0xFFFFFFFFu;
-                        const int at_k = r * topk_k + q, at_i = (p.topk_rows + r) * topk_k + q;
-                        rec[at_k] = key;
-                        rec[at_i] = idx;
-#pragma unroll 1
-                        for (int pq = 0; pq < npeers; ++pq)
-                            if (p.peer_records[pq]) {
-                                p.peer_records[pq][rec_at + at_k] = key;
-                                p.peer_records[pq][rec_at + at_i] = idx;
-                            }
-                    }
-                }
-            }
-        }
-        if (ow == 0) PROF_TIME(2);
-        if (npeers) {
-            // Exchange: every output warp counts itself in once its stores are ordered GPU-wide (a cheap fence). The
-            // warp that counts last orders all of them system-wide with the call's ONE system fence (system fences
-            // serialise across the GPU: one per warp cost this kernel a third of its run), numbers the call and writes
-            // that number to this rank's word on every rank. (No CTA barrier: the warps may have left the loop at
-            // different points.)
-            __syncwarp();
-            if (lane == 0) {
-                __threadfence();
-                const int old = atomicAdd(p.grid_counter, 1);
-                if (old + 1 == 4 * (int)gridDim.x) {
-                    *p.grid_counter = 0;
-                    const uint32_t seq = p.flags[TKD_FLAG_SEQ] + 1;
-                    p.flags[TKD_FLAG_SEQ] = seq;
-                    __threadfence_system();
-                    for (int q = 0; q < npeers; ++q) st_relaxed_sys(p.peer_flags[q] + p.rank, seq);
-                    st_relaxed_sys(p.flags + p.rank, seq);
-                    // (2: the call before this one, whose exchange has had this call's whole run to arrive)
-                    if (p.exchange_wait && !flags_wait(p.flags, npeers + 1, p.exchange_wait == 2 ? seq - 1 : seq)) {
-                        if (p.status) atomicExch(p.status, TKD_ERR_TIMEOUT);
-                    }
-                }
-            }
-        }
-    }
 }
 
 // Waits (one warp) until every rank's completed-call count in `flags` has reached this rank's own.
@@ -1052,55 +22,20 @@ __global__ void tkd_exchange_wait_kernel(uint32_t* flags, int nranks, int* statu
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         const uint32_t seq = ld_acquire_sys(flags + TKD_FLAG_SEQ);
-        if (!flags_wait(flags, nranks, seq) && status) atomicExch(status, TKD_ERR_TIMEOUT);
+        bool ok = true;
+        for (int r = 0; r < nranks && ok; ++r) {
+            int rounds = 0;  // (bounded: about a second)
+            while ((int32_t)(ld_acquire_sys(flags + r) - seq) < 0) {
+                if (++rounds > (1 << 20)) {
+                    ok = false;
+                    break;
+                }
+                __nanosleep(rounds < 64 ? 20 : 200);
+            }
+        }
+        if (!ok && status) atomicExch(status, TKD_ERR_TIMEOUT);
         __threadfence_system();
     }
-}
-
-template <int FMT, int MT, int SW, bool ONE = false, bool PLAIN = false, bool KWHOLE = false>
-int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = tkd_stream_kernel<FMT, MT, SW, ONE, PLAIN, KWHOLE>;
-    // (once per device and instantiation: allow the largest dynamic shared memory a CTA can have)
-    static bool allowed[64] = {false};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= 64 || !allowed[dev]) {
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e != cudaSuccess) return (int)e;
-        if (dev >= 0 && dev < 64) allowed[dev] = true;
-    }
-    // Programmatic dependent launch: a CTA of this launch may start on an SM as soon as the kernel before it in the
-    // stream has left that SM (every CTA of the stream kernel lets its dependents go at once, see the kernel). Its
-    // producer then fills the ring with weights, which no earlier kernel writes, while the rest of the earlier kernel
-    // drains; everything else waits for the earlier kernel's completion (griddepcontrol.wait).
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3((1 + SW + 4) * 32);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = tkd_pdl_enabled() ? 1 : 0;
-    return (int)cudaLaunchKernelEx(&cfg, kern, p);
-}
-
-template <int FMT, bool KWHOLE>
-int launch_rows(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    if (p.M == 1 && !p.topk_k && !p.npeers) return launch_one<FMT, 1, 16, true, true, KWHOLE>(p, grid, smem, st);
-    if (p.M == 1) return launch_one<FMT, 1, 16, true, false, KWHOLE>(p, grid, smem, st);
-    if (p.M <= 8) return launch_one<FMT, 1, 16, false, false, KWHOLE>(p, grid, smem, st);
-    if (p.M <= 16) return launch_one<FMT, 2, TKD_STREAM_WARPS_16ROWS, false, false, KWHOLE>(p, grid, smem, st);
-    return launch_one<FMT, 4, TKD_STREAM_WARPS_32ROWS, false, false, KWHOLE>(p, grid, smem, st);
-}
-
-template <int FMT>
-int launch_fmt(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    // (a K of whole chunks, the usual case, runs the instantiation without the code for a last, shorter chunk)
-    return p.K % (Fmt<FMT>::SUBSA * Fmt<FMT>::KSA) == 0 ? launch_rows<FMT, true>(p, grid, smem, st)
-                                                       : launch_rows<FMT, false>(p, grid, smem, st);
 }
 
 }  // namespace
@@ -1112,28 +47,8 @@ int tkd_launch_exchange_wait(uint32_t* flags, int nranks, int* status, cudaStrea
 
 int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
     switch (p.fmt) {
-        case TKD_BFP8: return launch_fmt<TKD_BFP8>(p, grid, smem, st);
-        case TKD_BFP4: return launch_fmt<TKD_BFP4>(p, grid, smem, st);
-        default: return launch_fmt<TKD_BF16>(p, grid, smem, st);
+        case TKD_BFP8: return tkd_launch_stream_bfp8(p, grid, smem, st);
+        case TKD_BFP4: return tkd_launch_stream_bfp4(p, grid, smem, st);
+        default: return tkd_launch_stream_bf16(p, grid, smem, st);
     }
 }
-
-#ifdef TKD_PROF
-// debug builds only: read and clear the cycle counters
-extern "C" int tkd_trace2_read(long long* host) { return (int)cudaMemcpyFromSymbol(host, tkd_trace2, sizeof(tkd_trace2)); }
-extern "C" int tkd_trace_read(long long* host) {
-    cudaError_t e = cudaMemcpyFromSymbol(host, tkd_trace, sizeof(tkd_trace));
-    int z[2] = {0, 0};
-    cudaMemcpyToSymbol(tkd_trace_n, z, sizeof(z));
-    return (int)e;
-}
-extern "C" int tkd_times_read(unsigned long long* host) {
-    return (int)cudaMemcpyFromSymbol(host, tkd_times, sizeof(tkd_times));
-}
-extern "C" int tkd_prof_read(long long* host) {
-    cudaError_t e = cudaMemcpyFromSymbol(host, tkd_prof, sizeof(tkd_prof));
-    long long zero[64] = {0};
-    cudaMemcpyToSymbol(tkd_prof, zero, sizeof(zero));
-    return (int)e;
-}
-#endif

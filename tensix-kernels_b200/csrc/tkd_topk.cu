@@ -114,7 +114,7 @@ int tkd_launch_topk_merge(const uint32_t* records, int nrec, int rows, int k, in
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = tkd_pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = 1;
     if (nrec * k <= kWarpMax) {
         cfg.blockDim = dim3(32);
         return (int)cudaLaunchKernelEx(&cfg, tkd_topk_merge_warp_kernel, records, nrec, rows, k, top, out);
@@ -269,7 +269,7 @@ int launch_pick(const uint32_t* records, int nrec, int rows, int k, int top, uin
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = tkd_pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = 1;
     return (int)cudaLaunchKernelEx(&cfg, tkd_head_pick_kernel<RECORDS>, records, nrec, rows, k, top, vocab, x, ldx, dim, head,
                                    ld_head, round, tmap, out, ids_out);
 }

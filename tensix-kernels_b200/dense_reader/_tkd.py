@@ -5,12 +5,10 @@ non-zero code raises.
 """
 
 import ctypes
-import os
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parents[1]
-# (TKD_LIB names another build of the same library, e.g. one with instrumentation)
-LIB_PATH = Path(os.environ.get("TKD_LIB") or PKG / "csrc" / "libtkd.so")
+LIB_PATH = PKG / "csrc" / "libtkd.so"
 
 FMT_BFP8, FMT_BFP4, FMT_BF16 = 0, 1, 2
 EPI_PLAIN, EPI_GLU_IL, EPI_GLU2, EPI_RESIDUAL, EPI_OUT32 = range(5)
@@ -33,7 +31,7 @@ class TkdMatmul(ctypes.Structure):
         ("topk_write_y", c_i32), ("topk_base", c_u32), ("topk_n", c_i64), ("workspace", c_vp), ("workspace_bytes", c_u64),
         ("status", c_vp), ("ks", c_i32), ("max_ctas", c_i32),
         ("nranks", c_i32), ("rank", c_i32), ("peer_out", c_vp * 7), ("peer_records", c_vp * 7), ("peer_flags", c_vp * 7),
-        ("flags", c_vp), ("exchange_wait", c_i32), ("pad_", c_i32),
+        ("flags", c_vp), ("exchange_wait", c_i32), ("weights_fresh", c_i32),
     ]
 
 
@@ -55,12 +53,16 @@ SYMBOLS = {
     "tkd_packed_bytes": (c_i64, [c_i32, c_i64, c_i64]),
     "tkd_quantise": (c_i32, [c_i32, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
     "tkd_pack": (c_i32, [c_i32, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "tkd_layout_version": (c_i32, []),
+    "tkd_dequantise_bf16": (c_i32, [c_i32, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
     "tkd_unpack": (c_i32, [c_i32, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
     "tkd_matmul_plan": (c_i32, [ctypes.POINTER(TkdMatmul), ctypes.POINTER(TkdPlan)]),
     "tkd_matmul_workspace": (c_i32, [ctypes.POINTER(TkdMatmul), ctypes.POINTER(c_u64)]),
     "tkd_matmul": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp]),
     "tkd_matmul_host": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp, c_vp, c_vp]),
     "tkd_matmul_noalloc": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp]),
+    "tkd_matmul_noalloc_reset": (c_i32, [c_vp]),
+    "tkd_noalloc_scratch_address": (c_i32, [ctypes.POINTER(c_vp)]),
     "tkd_topk_merge": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp]),
     "tkd_head_pick": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_u32, c_vp, c_i64, c_i32, c_vp, c_i64, c_i32, c_vp, c_vp, c_vp]),
     "tkd_head_pick_records": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_u32, c_vp, c_vp, c_vp, c_vp]),

@@ -286,7 +286,7 @@ _PLAN_ARGS = set(plan.__code__.co_varnames[: plan.__code__.co_argcount])
 def choose(device, x, w, full_sync=False, **forced):
     """[(first row, plan)] for x's rows, cached by shapes and settings. (linear.py:455-495)"""
     blocks = forced.get("blocks")
-    shapes = tuple((b.k, b.n, b.dtype) for b in (blocks or (w,)))
+    shapes = tuple((b.k, b.n, b.dtype, b.fmt) for b in (blocks or (w,)))
     key = (shapes, tuple(x.shape), tuple(sorted((k, v) for k, v in forced.items() if k != "blocks")), KS, MAX_CTAS)
     got = _CHOICE.get(key)
     if got is None:
@@ -330,9 +330,19 @@ def block_entries(w):
     return out
 
 
+def _one_stream_format(entries):
+    """The entries of one launch with all their weights in one stream format. They are (one dtype), unless some are
+    "wide" (held as a bf16 stream, see ttnn_like.Weight): then the others' values are streamed as bf16 too (a twin kept
+    with the weight). Such a list's sums are those of bf16 weights, not bit for bit the block-float kernels'."""
+    ws = [t for g, u, _ in entries for t in (g, u) if t is not None]
+    if len({t.fmt for t in ws}) == 1:
+        return entries
+    return [(ttnn.as_bf16_stream(g), None if u is None else ttnn.as_bf16_stream(u), c0) for g, u, c0 in entries]
+
+
 def choose_blocks(device, x, w, full_sync=False, **forced):
     """choose for a block list: the plan of its one call. (linear.py:559-562)"""
-    entries = block_entries(w)
+    entries = _one_stream_format(block_entries(w))
     return choose(device, x, entries[0][0], full_sync, blocks=tuple(g for g, _, _ in entries), noscale=True,
                   glu=entries[0][1] is not None, glu2=entries[0][1] is not None, **forced)
 
@@ -401,7 +411,7 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     segs = ()
     if isinstance(w, (list, tuple)):
         assert is_block_list(w), "dense_reader: w is one weight or a block list [(w | (gate, up), col0_tiles), ...]"
-        entries = block_entries(w)
+        entries = _one_stream_format(block_entries(w))
         assert scale is None and topk is None and col0 == 0 and w_up is None, (
             "dense_reader: a block list takes no scale, topk, col0 or w_up (each block carries its own col0_tiles)"
         )
@@ -475,8 +485,8 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     if topk is not None:
         assert M <= 32, "dense_reader: top-k needs one row slice"
         assert 1 <= topk["rows"] <= 16 and topk["rows"] * topk["k"] <= 64 and topk["rows"] <= M, topk
-    if w.wide or (w_up is not None and w_up.wide) or any(g.wide or (u is not None and u.wide) for g, u, _ in segs):
-        raise _tkd.TkdError(_tkd.ERR_WIDE, "matmul")
+    if w_up is not None and w_up.fmt != w.fmt:
+        ((w, w_up, _),) = _one_stream_format([(w, w_up, 0)])
     slices = choose(device, x, w, full_sync, **opts)
     if segs:
         _block_kw_check(device, x, blocks_all, full_sync, opts, slices)
@@ -498,7 +508,9 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
 
 
 def _call_key(x, w, scale, topk, out, col0, w_up, max_banks, opts):
-    return (id(x), id(w), id(scale), id(out), id(w_up), id(topk), col0, max_banks, KS, MAX_CTAS, TOPK_UNIT, WORKSPACE_SLOT,
+    # (the entry keeps its arguments alive, so their ids stay theirs; ttnn.deallocate starts a new epoch, which retires
+    # every entry made before it)
+    return (ttnn.EPOCH, id(x), id(w), id(scale), id(out), id(w_up), id(topk), col0, max_banks, KS, MAX_CTAS, TOPK_UNIT, WORKSPACE_SLOT,
             tuple((k, tuple(map(id, v)) if type(v) is tuple else id(v)) for k, v in opts.items()))
 
 
@@ -577,11 +589,9 @@ def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, o
         tk = None if topk is None else (_raw(topk["r"]).data_ptr(), topk["k"], topk["rows"], topk["slot0"], topk["base"],
                                         topk["n"], bool(topk.get("write_y", False)), TOPK_UNIT)
         key = (
-            # (every address the descriptor holds: a freed weight's memory may come back as another weight's stream with
-            # its side array elsewhere)
-            tuple((g.t.data_ptr(), g.emax.data_ptr() if g.emax is not None else 0, u.t.data_ptr() if u is not None else 0,
-                   u.emax.data_ptr() if u is not None and u.emax is not None else 0, g.k, g.n, g.dtype, c0)
-                  for g, u, c0 in entries),
+            # (weights by their serial numbers, never by address: a freed weight's memory may come back as another
+            # weight's stream, a serial does not come back)
+            ttnn.EPOCH, tuple((g.serial, u.serial if u is not None else 0, c0) for g, u, c0 in entries),
             m, tuple(xt.shape), tuple(yt.shape), epi, act, sc.data_ptr() if sc is not None else 0,
             sc_up.data_ptr() if sc_up is not None else 0, scale_dt, res_dt, tk, ks, max_ctas, device.id, id(exchange),
         )

@@ -39,17 +39,20 @@ void emul_pack(int fmt, int64_t K, int64_t npad, const uint8_t* exps, const void
             if (any) { hi = exps[k * G + g] > hi ? exps[k * G + g] : hi; lo = exps[k * G + g] < lo ? exps[k * G + g] : lo; }
         }
         emax[g] = (uint8_t)hi;
-        if (lo <= hi && lo - hi + TKD_EBIAS < TKD_EMIN_OK) *wide = 1;
+        if (lo <= hi && hi - lo > TKD_ESPREAD) *wide = 1;
     }
-    // every exponent slot of the stream, padded k included, holds at least 1
+    // every exponent slot of the stream, padded k included, holds at least the format's "no code" value
     const int64_t kpad = tkd_nsa(fmt, K) * tkd_ksa(fmt);
     for (int64_t k = 0; k < kpad; ++k)
         for (int64_t g = 0; g < G; ++g) {
             TkdLoc L = tkd_locate(fmt, K, k, g * 16);
-            int e = 1;
-            if (k < K && nz[k * G + g]) { e = (int)exps[k * G + g] - (int)emax[g] + TKD_EBIAS; if (e < 1) e = 1; }
+            int e = tkd_ezero(fmt);
+            if (k < K && nz[k * G + g]) {
+                e = (int)exps[k * G + g] - (int)emax[g] + tkd_ebias(fmt);
+                if (e < tkd_ezero(fmt)) e = tkd_ezero(fmt);
+            }
             uint32_t w; memcpy(&w, stream + L.exp_word, 4);
-            w |= tkd_exp_bits((uint32_t)e, L.exp_r);
+            w |= tkd_exp_bits(fmt, (uint32_t)e, L.exp_r);
             memcpy(stream + L.exp_word, &w, 4);
         }
     for (int64_t k = 0; k < K; ++k)
@@ -80,8 +83,10 @@ void emul_matmul(int fmt, int64_t K, int64_t npad, const uint8_t* stream, const 
                         uint32_t w, e;
                         memcpy(&w, b + 64 + lane * 16 + j * 4, 4);
                         memcpy(&e, b + t * 16 + j * 4, 4);
-                        for (int i = 0; i < 4; ++i) a[i] = tkd_rotr(w, 4 * i) & 0x80078007u;
-                        s0 = e & 0x7F807F80u, s1 = tkd_rotr(e, 8) & 0x7F807F80u;
+                        const uint32_t t8 = tkd_rotr(w, 8);  // (the kernel's own five operations)
+                        a[0] = w & TKD_MASK_BFP4, a[1] = (w << 4) & TKD_MASK_BFP4;
+                        a[2] = t8 & TKD_MASK_BFP4, a[3] = (t8 << 4) & TKD_MASK_BFP4;
+                        s0 = (e & TKD_EMASK_BFP4) | TKD_EBASE_BFP4, s1 = ((e << 7) & TKD_EMASK_BFP4) | TKD_EBASE_BFP4;
                     } else if (fmt == TKD_BFP8) {
                         uint32_t w0, w1, e;
                         memcpy(&w0, b + 32 + lane * 16 + (2 * jj) * 4, 4);
@@ -109,7 +114,7 @@ void emul_matmul(int fmt, int64_t K, int64_t npad, const uint8_t* stream, const 
                 }
             }
         }
-        const int e = fmt == TKD_BF16 ? 0 : (int)emax[g] + 64 - tkd_unit_exp(fmt);
+        const int e = fmt == TKD_BF16 ? 0 : tkd_out_exp(fmt, (int)emax[g]);
         for (int i = 0; i < 16; ++i)
             for (int m = 0; m < M; ++m) y[(int64_t)m * npad + g * 16 + i] = ldexp(acc[i * M + m], e);
     }
@@ -130,7 +135,7 @@ void emul_unpack(int fmt, int64_t K, int64_t npad, const uint8_t* stream, const 
                 memcpy(&w, stream + L.code_word, 4);
                 memcpy(&ew, stream + L.exp_word, 4);
                 const uint32_t c = tkd_code_from_word(fmt, w, L.rot, L.half), m = c & ((1u << mb) - 1);
-                const int e = (int)tkd_exp_from_word(ew, L.exp_r) + (int)emax[n >> 4] - TKD_EBIAS;
+                const int e = (int)tkd_exp_from_word(fmt, ew, L.exp_r) + (int)emax[n >> 4] - tkd_ebias(fmt);
                 v = m ? ldexpf((float)m, e - tkd_unit_exp(fmt)) : 0.f;
                 if ((c >> mb) & 1u) v = -v;
             }

@@ -30,7 +30,7 @@ def test_exports_match_header(tkd):
     lib = ctypes.CDLL(str(tkd.LIB_PATH))
     for name in declared:
         assert hasattr(lib, name), name
-    assert tkd.lib().tkd_version() == 2
+    assert tkd.lib().tkd_version() == 3 and tkd.lib().tkd_layout_version() >= 3
     assert tkd.lib().tkd_error_string(3).decode().startswith("a kernel")
 
 

@@ -78,7 +78,8 @@ def test_every_stream_bit_is_owned_once(emul):
         eb = SAB[fmt] - 512
         assert np.all(sa[:, eb:] == 0xFF)
         words = sa[:, :eb].copy().view(np.uint32)
-        assert np.all(words == np.uint32(0x62626262))  # four exponent fields of 196 = 0xC4 << 7, rotated: all bits owned
+        # bfloat8_b: four exponent fields of 196 = 0xC4 << 7, rotated: all bits owned; bfloat4_b: four 6-bit fields of 63
+        assert np.all(words == np.uint32(0x62626262 if fmt == "bfp8" else 0x1FBF1FBF))
 
 
 def test_wide_weight_is_flagged(emul):

@@ -1,6 +1,8 @@
 """Parity of the CUDA path with the CPU oracle, through the package's API (which calls libtkd's C-ABI): bit-exact for
 the quantiser, the packed weights' held values and the top-k indices; 1e-2 relative (compared in bf16) for the sums."""
 
+from pathlib import Path
+
 import numpy as np
 import pytest
 import torch
@@ -12,6 +14,7 @@ from dense_reader import linear  # noqa: E402
 from oracle import oracle as orc  # noqa: E402
 
 DT = {"bfp8": ttnn.bfloat8_b, "bfp4": ttnn.bfloat4_b, "bf16": ttnn.bfloat16}
+GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
 def dev_x(device, x):
@@ -62,14 +65,42 @@ def test_col_scale_and_block_float(device, fmt):
         assert np.array_equal(got[i].numpy().view(np.uint32), orc.block_float(t[i].numpy(), fmt).view(np.uint32))
 
 
-def test_wide_weight_refused(device):
-    w = torch.full((32, 64), 1.0)
-    w[:, 3] = 1e-20
-    tw, _ = linear.native_weight(device, w, ttnn.bfloat8_b)
-    assert tw.wide
-    x = dev_x(device, torch.ones(1, 64))
-    with pytest.raises(RuntimeError):
-        linear.matmul(x, tw, None)
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4"])
+def test_wide_weight_runs(device, fmt):
+    """A weight whose exponents inside a group of 16 columns spread further than the block-float stream encodes (the
+    reference takes any float matrix, linear.py:144-156): here a dead input channel of 1e-17-size noise beside
+    0.02-size rows, and the quantiser golden file's wide-spread matrix (zeros, denormals, huge values). The weight holds
+    the oracle's values bit for bit and the matmul matches the oracle, also when only the tiny rows see activations."""
+    g = torch.Generator().manual_seed(66)
+    n, k = 256, 512
+    w = torch.randn(n, k, generator=g) * 0.02
+    w[:, 7] = torch.randn(n, generator=g) * 1e-17
+    tw, _ = linear.native_weight(device, w, DT[fmt])
+    assert tw.wide and tw.dtype == DT[fmt]
+    wk = orc.native_values(w, fmt)[0]
+    assert np.array_equal(ttnn.to_torch(tw)[0, 0, :, :n].numpy().view(np.uint32), wk.view(np.uint32))
+    x = torch.randn(3, k, generator=g)
+    x[1] = 0
+    x[1, 7] = 3.0   # only the dead channel: the sums are of 1e-17 size
+    x[2, 7] = 2.0 ** 60
+    y = host(linear.matmul(dev_x(device, x), tw, None))
+    want = orc.matmul_f64(x, wk)
+    close_bf16(y, want)
+    assert y[1].abs().max() > 0
+    # a block list with a weight that is not wide: one launch, one stream format
+    w2 = torch.randn(128, k, generator=g) * 0.02
+    t2, _ = linear.native_weight(device, w2, DT[fmt])
+    assert not t2.wide
+    both = host(linear.matmul(dev_x(device, x), [(tw, 0), (t2, n // 32)], None))
+    assert torch.equal(both[:, :n], y)
+    close_bf16(both[:, n:], orc.matmul_f64(x, orc.native_values(w2, fmt)[0]))
+    if fmt == "bfp4":
+        gold = np.load(GOLDEN / "quantiser_bfp4.npz")
+        w4 = torch.from_numpy(gold["w4"].astype(np.float32))  # [K, N]
+        t4 = ttnn.from_torch(w4, dtype=ttnn.bfloat4_b, device=device)
+        held = ttnn.to_torch(t4)[0, 0, :, : w4.shape[1]].numpy()
+        assert np.array_equal(held.view(np.uint32), orc.block_float(w4.numpy(), "bfp4").view(np.uint32))
+    linear.check_status(device)
 
 
 @pytest.mark.parametrize("fmt", ["bfp8", "bfp4", "bf16"])
@@ -346,4 +377,29 @@ def test_matmul_host_equals_matmul(device):
         torch.cuda.synchronize()
         want = host(linear.matmul(dev_x(device, x.float()), tw, None))
         assert torch.equal(y_pin.float(), want)
+    linear.check_status(device)
+
+
+def test_launch_cache_survives_freed_weights(device):
+    """The launch caches hold raw addresses. A weight is freed, another of the same shape is packed (its stream
+    usually lands on the freed one's address) and the same call objects are used again: the result is the new
+    weight's, with and without ttnn.deallocate having been told."""
+    g = torch.Generator().manual_seed(81)
+    k, n = 1024, 512
+    x = dev_x(device, torch.randn(2, k, generator=g))
+    out = ttnn.allocate_tensor_on_device([1, 1, 2, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
+    for told in (False, True):
+        w1, w2 = torch.randn(n, k, generator=g) * 0.02, torch.randn(n, k, generator=g) * 0.02
+        t1, _ = linear.native_weight(device, w1, ttnn.bfloat8_b)
+        y1 = host(linear.matmul(x, t1, None, out=out)).clone()
+        y1b = host(linear.matmul(x, t1, None, out=out))  # the replayed call
+        assert torch.equal(y1, y1b)
+        addr = t1.t.data_ptr()
+        if told:
+            ttnn.deallocate(t1)
+        del t1
+        t2, _ = linear.native_weight(device, w2, ttnn.bfloat8_b)
+        y2 = host(linear.matmul(x, t2, None, out=out)).clone()
+        close_bf16(y2, orc.matmul_f64(ttnn.to_torch(x).reshape(2, k).float(), orc.native_values(w2, "bfp8")[0]))
+        assert not torch.equal(y1, y2), addr
     linear.check_status(device)
