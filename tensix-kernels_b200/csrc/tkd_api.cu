@@ -111,20 +111,28 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
 
     // shared-memory map: barriers, the hand-over buffers of the streaming warps, the GLU exchange buffer, the ring
     const int mp = mt == 1 ? 8 : (mt == 2 ? 24 : 40);
-    p.off_pbuf = TKD_SMEM_HEAD;
-    // (32 rows: one hand-over buffer instead of two; 9 to 32 rows of bfloat8_b or bf16: two tiles of the activations, rows
-    // x one chunk of k; the same conditions as NPB and XS in the kernel)
-    p.off_tbuf = p.off_pbuf + (mt == 4 ? 1 : 2) * 2 * TKD_PANEL_COLS * mp * 4;
-    p.off_xt = (int)align_up(p.off_tbuf + TKD_PANEL_COLS * mp * 4, 128);
-    int xt_bytes = mt >= 2 && a->fmt != TKD_BFP4 ? 2 * (8 * mt) * chunk_k * 2 : 0;
-    // one row: all of x in shared memory (K rounded up to a chunk), if that leaves the ring at least four stages
-    const int64_t x_row = (a->k + chunk_k - 1) / chunk_k * chunk_k * 2;
-    if (a->m == 1 && p.off_xt + x_row + 4 * (int64_t)(8 * tkd_subsa(a->fmt) * sab) + 256 <= kMaxSmem) {
-        p.x_smem = 1;
-        xt_bytes = (int)x_row;
-    }
-    p.off_ring = (int)align_up(p.off_xt + xt_bytes, 128);
     p.stage_bytes = 8 * tkd_subsa(a->fmt) * sab;
+    p.off_pbuf = TKD_SMEM_HEAD;
+    if (a->m > 8) {
+        // 9 to 32 rows, the tensor-memory kernel: the running sums [128][40] floats, then (from the next 1024-byte
+        // boundary of the window, hence the slack) 2 operand slots of two A tiles (16 KB) and two x tiles (4 KB), then the ring
+        p.tc = 1;
+        p.off_tbuf = TKD_SMEM_HEAD;
+        p.off_xt = p.off_tbuf + TKD_PANEL_COLS * 40 * 4;
+        p.off_ring = (int)align_up(p.off_xt + 1024 + 2 * 2 * (16384 + 4096), 128);
+    } else {
+        // (one to eight rows: two hand-over buffers; one row: all of x in shared memory, K rounded up to a chunk, if
+        // that leaves the ring at least four stages)
+        p.off_tbuf = p.off_pbuf + 2 * 2 * TKD_PANEL_COLS * mp * 4;
+        p.off_xt = (int)align_up(p.off_tbuf + TKD_PANEL_COLS * mp * 4, 128);
+        int xt_bytes = 0;
+        const int64_t x_row = (a->k + chunk_k - 1) / chunk_k * chunk_k * 2;
+        if (a->m == 1 && p.off_xt + x_row + 4 * (int64_t)p.stage_bytes + 256 <= kMaxSmem) {
+            p.x_smem = 1;
+            xt_bytes = (int)x_row;
+        }
+        p.off_ring = (int)align_up(p.off_xt + xt_bytes, 128);
+    }
     p.nstages = (kMaxSmem - p.off_ring) / p.stage_bytes;
     if (p.nstages > TKD_MAX_STAGES) p.nstages = TKD_MAX_STAGES;
     if (p.nstages < 2) return TKD_ERR_UNSUPPORTED;
@@ -242,7 +250,7 @@ int tkd_matmul_plan(const TkdMatmul* a, TkdPlan* plan) {
     plan->panels = L.p.total_panels;
     plan->grid = L.grid;
     plan->stages = L.p.nstages;
-    plan->stream_warps = a->m > 16 ? TKD_STREAM_WARPS_32ROWS : (a->m > 8 ? TKD_STREAM_WARPS_16ROWS : TKD_STREAM_WARPS);
+    plan->stream_warps = TKD_STREAM_WARPS;
     plan->chunk_k = tkd_chunk_k(L.p.fmt);
     plan->smem_bytes = (int32_t)L.smem;
     plan->items = L.p.total_items;

@@ -87,6 +87,7 @@ struct TkdParams {
     uint32_t* flags;     // this rank's flag words
     int* grid_counter;   // CTAs of this call that have finished their output (returns to zero)
     int exchange_wait;
+    int tc;              // 9 to 32 rows: the tensor-memory kernel (tkd_stream_tc.cuh); off_xt is where its operand tiles go
     int x_smem;          // one row, and all of it (K rounded up to a chunk) fits in shared memory at off_xt
     int no_pdl;          // launch without programmatic dependent launch (the weights may still be being written)
     // shared-memory map (bytes from the start of dynamic shared memory)

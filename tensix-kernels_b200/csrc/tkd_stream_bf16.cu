@@ -1,7 +1,7 @@
 // tkd_stream_bf16.cu: the stream kernel's instantiations for one weight format (a translation unit per format, so that
 // they compile side by side).
-#include "tkd_stream_kernel.cuh"
+#include "tkd_stream_tc.cuh"
 
 int tkd_launch_stream_bf16(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    return launch_fmt<TKD_BF16>(p, grid, smem, st);
+    return launch_fmt_all<TKD_BF16>(p, grid, smem, st);
 }

@@ -47,6 +47,9 @@ namespace {
 constexpr uint32_t kWaitRounds = 1u << 12;   // try_wait rounds before a wait gives up ...
 constexpr uint32_t kWaitHintNs = 1000000u;   // ... each suspended for up to this long (woken at once on completion)
 constexpr int kStatusTimeout = 3;            // TKD_ERR_TIMEOUT of include/tkd.h
+#ifndef TKD_PARK_NS
+#define TKD_PARK_NS 100
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -76,6 +79,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
         if (mbar_try_wait(bar, parity)) return true;
     if (status) atomicExch(status, kStatusTimeout);
     return false;
+}
+// The same for the roles that spend most of the kernel waiting (the producer lane, the output warps): between tries the
+// warp sleeps, so that its polling does not take issue slots and integer-pipe cycles from the streaming warps.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, int* status) {
+#ifdef TKD_NO_PARKED_SLEEP
+    return mbar_wait(bar, parity, status);
+#else
+    for (uint32_t i = 0; i < (kWaitRounds << 6); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(TKD_PARK_NS);
+    }
+    if (status) atomicExch(status, kStatusTimeout);
+    return false;
+#endif
 }
 // global -> shared bulk copy (TMA, 1-D, this CTA only), completion counted in bytes on an mbarrier
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -332,6 +349,102 @@ __device__ __forceinline__ uint32_t topk_key(uint16_t b) {
     return (uint32_t)(b ^ (0x8000u | (0x7FFFu & (0u - (uint32_t)(b >> 15))))) & 0xFFFFu;
 }
 
+// The top-k records of the unit of columns that panel c.pl belongs to, made by the CTA whose output warps complete the
+// unit's last panel, from the bf16 outputs themselves (all four output warps call this after a panel's output stage).
+__device__ __forceinline__ void topk_records(const TkdParams& p, const Cursor& c, const TkdSegDev& sg, int et, int ow, int lane,
+                                             float* tbuf, volatile int* sflag, uint16_t* y16, int topk_k, int npeers) {
+                // ------------------------------------------------------------ top-k records: one per unit of columns,
+                // made by the CTA that completes the unit's last panel, from the bf16 outputs themselves
+                const int upanels = p.topk_unit / TKD_PANEL_COLS;
+                const int unit = c.pl / upanels;
+                const int in_unit = min(upanels, p.total_panels - unit * upanels);
+                __threadfence();
+                bar_output_warps();
+                if (et == 0) {
+                    const int old = atomicAdd(p.unit_counters + unit, 1);
+                    const int last = old + 1 == in_unit;
+                    if (last) p.unit_counters[unit] = 0;
+                    sflag[0] = last;
+                }
+                bar_output_warps();
+                const bool scan = sflag[0] != 0;
+                bar_output_warps();
+                if (!scan) return;
+                __threadfence();
+                const uint16_t* ysrc = p.write_y ? y16 + sg.out_col0 : p.ytmp;
+                const int64_t ldy = p.write_y ? p.ldo : p.ld_ytmp;
+                const int col0 = unit * p.topk_unit;  // the unit's first column (call-relative)
+                uint32_t* red = reinterpret_cast<uint32_t*>(tbuf);
+                const size_t rec_at = (size_t)(p.topk_slot0 + unit) * 2 * p.topk_rows * topk_k;
+                uint32_t* rec = p.records + rec_at;
+                for (int r = 0; r < p.topk_rows; ++r) {
+                    // candidates: (key << 16 | 0xFFFF - position in unit) orders by key descending, then column ascending;
+                    // this thread's 16 (a unit holds at most 2048 columns) are loaded once
+                    uint32_t cand[16];
+    #pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int cc = et + j * TKD_PANEL_COLS, col = col0 + cc;
+                        uint32_t key = 0;
+                        if (cc < p.topk_unit && col < p.topk_n && col < sg.n_valid)
+                            key = topk_key(__ldcg(ysrc + (size_t)r * ldy + col));
+                        cand[j] = key ? (key << 16) | (0xFFFFu - (uint32_t)cc) : 0u;
+                    }
+                    uint32_t bound = 0xFFFFFFFFu;
+                    for (int q = 0; q < topk_k; ++q) {
+                        uint32_t best = 0;
+    #pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (cand[j] < bound && cand[j] > best) best = cand[j];
+    #pragma unroll
+                        for (int o = 16; o; o >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, o));
+                        if (lane == 0) red[ow] = best;
+                        bar_output_warps();
+                        best = max(max(red[0], red[1]), max(red[2], red[3]));
+                        bar_output_warps();
+                        bound = best;  // (0: nothing left, the remaining slots stay empty)
+                        if (et == 0) {
+                            const uint32_t key = best >> 16;
+                            const uint32_t idx = best ? p.topk_base + (uint32_t)col0 + (0xFFFFu - (best & 0xFFFFu)) : 0xFFFFFFFFu;
+                            const int at_k = r * topk_k + q, at_i = (p.topk_rows + r) * topk_k + q;
+                            rec[at_k] = key;
+                            rec[at_i] = idx;
+    #pragma unroll 1
+                            for (int pq = 0; pq < npeers; ++pq)
+                                if (p.peer_records[pq]) {
+                                    p.peer_records[pq][rec_at + at_k] = key;
+                                    p.peer_records[pq][rec_at + at_i] = idx;
+                                }
+                        }
+                    }
+                }
+}
+
+// The end of an exchanged call, run by every output warp after its last panel.
+__device__ __forceinline__ void exchange_done(const TkdParams& p, int lane, int npeers) {
+    // Exchange: every output warp counts itself in once its stores are ordered GPU-wide (a cheap fence). The
+    // warp that counts last orders all of them system-wide with the call's ONE system fence (system fences
+    // serialise across the GPU: one per warp cost this kernel a third of its run), numbers the call and writes
+    // that number to this rank's word on every rank. (No CTA barrier: the warps may have left the loop at
+    // different points.)
+    __syncwarp();
+    if (lane == 0) {
+        __threadfence();
+        const int old = atomicAdd(p.grid_counter, 1);
+        if (old + 1 == 4 * (int)gridDim.x) {
+            *p.grid_counter = 0;
+            const uint32_t seq = p.flags[TKD_FLAG_SEQ] + 1;
+            p.flags[TKD_FLAG_SEQ] = seq;
+            __threadfence_system();
+            for (int q = 0; q < npeers; ++q) st_relaxed_sys(p.peer_flags[q] + p.rank, seq);
+            st_relaxed_sys(p.flags + p.rank, seq);
+            // (2: the call before this one, whose exchange has had this call's whole run to arrive)
+            if (p.exchange_wait && !flags_wait(p.flags, npeers + 1, p.exchange_wait == 2 ? seq - 1 : seq)) {
+                if (p.status) atomicExch(p.status, TKD_ERR_TIMEOUT);
+            }
+        }
+    }
+}
+
 // SW: streaming warps, 16 (a warp per column group and half of each chunk's super-atoms) or 8 (a warp takes both halves
 // of its group, one after the other: the 32-row kernel, whose accumulators need the registers that fewer warps leave).
 // ONE: the call has one row (the decode case): the row count is a constant 1 and everything that serves more rows falls
@@ -341,7 +454,7 @@ __device__ __forceinline__ uint32_t topk_key(uint16_t b) {
 // KWHOLE: K is a whole number of chunks, so the code for a last, shorter chunk falls away as well.
 template <int FMT, int MT, int SW, bool ONE, bool PLAIN, bool KWHOLE>
 __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const __grid_constant__ TkdParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ __align__(1024) uint8_t smem[];
     using F = Fmt<FMT>;
     constexpr int MP = MT == 1 ? 8 : (MT == 2 ? 24 : 40);  // floats per column in the hand-over buffers
     constexpr int MR = 8 * MT;                             // rows the accumulators cover
@@ -422,7 +535,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             const uint8_t* src2 = glu2 ? sg.w2 + (int64_t)(c.pl >> 1) * p.panel_bytes : nullptr;
             for (int ch = 0; ch < nch; ++ch, ++st) {
                 const uint32_t s = st % nst;
-                ok = mbar_wait(empty0 + 8 * s, ((st / nst) & 1) ^ 1, p.status);
+                ok = mbar_wait_parked(empty0 + 8 * s, ((st / nst) & 1) ^ 1, p.status);
                 if (!ok) break;
                 const int nsa = min(F::SUBSA, nsa_total - (c0 + ch) * F::SUBSA);
                 const uint32_t gbytes = (uint32_t)nsa * F::SAB;  // one group's share of the chunk
@@ -665,7 +778,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                 sc = p.scale_dt == TKD_DT_BF16 ? bf16_bits_to_f32(static_cast<const uint16_t*>(sp)[n])
                                                : static_cast<const float*>(sp)[n];
             }
-            ok = mbar_wait(pfull0 + 8 * pb, (NPB == 2 ? pi >> 1 : pi) & 1, p.status);
+            ok = mbar_wait_parked(pfull0 + 8 * pb, (NPB == 2 ? pi >> 1 : pi) & 1, p.status);
             if (!ok) break;
             bool finish = !f.split;
             // (9 rows and more: the column's sums live in the thread's row of tbuf, not in registers, and every loop over
@@ -955,95 +1068,10 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             }
             if (topk_k == 0) continue;
 
-            // ------------------------------------------------------------ top-k records: one per unit of columns,
-            // made by the CTA that completes the unit's last panel, from the bf16 outputs themselves
-            const int upanels = p.topk_unit / TKD_PANEL_COLS;
-            const int unit = c.pl / upanels;
-            const int in_unit = min(upanels, p.total_panels - unit * upanels);
-            __threadfence();
-            bar_output_warps();
-            if (et == 0) {
-                const int old = atomicAdd(p.unit_counters + unit, 1);
-                const int last = old + 1 == in_unit;
-                if (last) p.unit_counters[unit] = 0;
-                sflag[0] = last;
-            }
-            bar_output_warps();
-            const bool scan = sflag[0] != 0;
-            bar_output_warps();
-            if (!scan) continue;
-            __threadfence();
-            const uint16_t* ysrc = p.write_y ? y16 + sg.out_col0 : p.ytmp;
-            const int64_t ldy = p.write_y ? p.ldo : p.ld_ytmp;
-            const int col0 = unit * p.topk_unit;  // the unit's first column (call-relative)
-            uint32_t* red = reinterpret_cast<uint32_t*>(tbuf);
-            const size_t rec_at = (size_t)(p.topk_slot0 + unit) * 2 * p.topk_rows * topk_k;
-            uint32_t* rec = p.records + rec_at;
-            for (int r = 0; r < p.topk_rows; ++r) {
-                // candidates: (key << 16 | 0xFFFF - position in unit) orders by key descending, then column ascending;
-                // this thread's 16 (a unit holds at most 2048 columns) are loaded once
-                uint32_t cand[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int cc = et + j * TKD_PANEL_COLS, col = col0 + cc;
-                    uint32_t key = 0;
-                    if (cc < p.topk_unit && col < p.topk_n && col < sg.n_valid)
-                        key = topk_key(__ldcg(ysrc + (size_t)r * ldy + col));
-                    cand[j] = key ? (key << 16) | (0xFFFFu - (uint32_t)cc) : 0u;
-                }
-                uint32_t bound = 0xFFFFFFFFu;
-                for (int q = 0; q < topk_k; ++q) {
-                    uint32_t best = 0;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (cand[j] < bound && cand[j] > best) best = cand[j];
-#pragma unroll
-                    for (int o = 16; o; o >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, o));
-                    if (lane == 0) red[ow] = best;
-                    bar_output_warps();
-                    best = max(max(red[0], red[1]), max(red[2], red[3]));
-                    bar_output_warps();
-                    bound = best;  // (0: nothing left, the remaining slots stay empty)
-                    if (et == 0) {
-                        const uint32_t key = best >> 16;
-                        const uint32_t idx = best ? p.topk_base + (uint32_t)col0 + (0xFFFFu - (best & 0xFFFFu)) : 0xFFFFFFFFu;
-                        const int at_k = r * topk_k + q, at_i = (p.topk_rows + r) * topk_k + q;
-                        rec[at_k] = key;
-                        rec[at_i] = idx;
-#pragma unroll 1
-                        for (int pq = 0; pq < npeers; ++pq)
-                            if (p.peer_records[pq]) {
-                                p.peer_records[pq][rec_at + at_k] = key;
-                                p.peer_records[pq][rec_at + at_i] = idx;
-                            }
-                    }
-                }
-            }
+            topk_records(p, c, sg, et, ow, lane, tbuf, sflag, y16, topk_k, npeers);
+        
         }
-        if (npeers) {
-            // Exchange: every output warp counts itself in once its stores are ordered GPU-wide (a cheap fence). The
-            // warp that counts last orders all of them system-wide with the call's ONE system fence (system fences
-            // serialise across the GPU: one per warp cost this kernel a third of its run), numbers the call and writes
-            // that number to this rank's word on every rank. (No CTA barrier: the warps may have left the loop at
-            // different points.)
-            __syncwarp();
-            if (lane == 0) {
-                __threadfence();
-                const int old = atomicAdd(p.grid_counter, 1);
-                if (old + 1 == 4 * (int)gridDim.x) {
-                    *p.grid_counter = 0;
-                    const uint32_t seq = p.flags[TKD_FLAG_SEQ] + 1;
-                    p.flags[TKD_FLAG_SEQ] = seq;
-                    __threadfence_system();
-                    for (int q = 0; q < npeers; ++q) st_relaxed_sys(p.peer_flags[q] + p.rank, seq);
-                    st_relaxed_sys(p.flags + p.rank, seq);
-                    // (2: the call before this one, whose exchange has had this call's whole run to arrive)
-                    if (p.exchange_wait && !flags_wait(p.flags, npeers + 1, p.exchange_wait == 2 ? seq - 1 : seq)) {
-                        if (p.status) atomicExch(p.status, TKD_ERR_TIMEOUT);
-                    }
-                }
-            }
-        }
+        if (npeers) exchange_done(p, lane, npeers);
     }
 }
 

@@ -1,0 +1,652 @@
+// tkd_stream_tc.cuh: the stream kernel for 9 to 32 activation rows, on the fifth-generation tensor cores (tcgen05).
+//
+// The reference multiplies a tile of up to 32 activation rows by each weight tile it has read (dense_reader/kernels/
+// dense_compute.cpp:95-143, matmul_block): more rows cost it no more weight traffic and hardly more time. With
+// mma.sync the same holds for the traffic but not for the time: 32 rows of accumulators leave room for two streaming
+// warps per scheduler, which wait on their own shared-memory loads and mma chains. Here the weights of a panel are
+// decoded into bf16 tiles in shared memory once, whatever the row count, and one thread issues tcgen05.mma on them with
+// the accumulators in tensor memory:
+//
+//   warp 0         producer (one lane): the same ring of packed-weight chunks as tkd_stream_kernel, one bulk copy a stage
+//   warps 1-16     decode warps: warp (group g, half h) turns its 16 columns' share of a chunk into bf16 (code times
+//                  2^e', one multiply per two weights: every block-float value is a bf16 value) and stores it into an
+//   warps 17-20    output warps (thread = panel column = tensor-memory lane): read a slice's sums with tcgen05.ld, keep
+//                  the running sums in shared memory, and from there on do what tkd_stream_kernel's output warps do
+//                  A tile: 128 columns x 64 k, K-major, 128-byte swizzle, 16 KB. Beside it in the same slot goes the
+//                  tile of activations it is multiplied by (32 rows x 64 k, rows past M zero, 4 KB): the warps that
+//                  write an A tile share its 256 16-byte pieces out, each lane loading its pieces of the NEXT chunk's
+//                  tiles into registers while it decodes this chunk (they come from L2, a microsecond away) and
+//                  storing them with the A tile. (A loader warp with cp.async was tried first: the proxy fence it
+//                  needs before the tensor core may read waits for ALL its copies in flight, which serialised them.)
+//   warp 21        one lane issues the MMAs: D[128 columns, 32 rows] += A tile x (x tile)^T, 4 x (K = 16) a tile,
+//                  tcgen05.commit onto the slot's "empty" barrier and, at a slice's end, onto the accumulator's "full"
+//
+// A slice's sum is accumulated from zero in tensor memory, in FOUR accumulators of 32 columns: the j-th block of 16 k
+// of every tile goes to accumulator j, because an MMA that adds to the accumulator of the MMA before it waits for it
+// (about 100 ns each, measured; the four of a tile are independent this way), and the slice's sum is ((d0 + d1) + d2)
+// + d3. Two such sets, so that the MMAs of the next slice run while the output warps drain this one. A column's sum is
+// the ascending sum of its slices' sums in plain fp32 adds, as in tkd_stream_kernel, so it depends on K, the format and
+// ks only. No cluster, no multicast, no
+// second CTA: cta_group::1 throughout. Every wait is bounded; the kernel always reaches its end, where the warp that
+// allocated the tensor memory frees it.
+#pragma once
+#include "tkd_stream_kernel.cuh"
+
+namespace {
+
+constexpr int kTcSlots = 2;          // operand slots, each a unit of two tiles: [A 0][A 1][x 0][x 1]
+constexpr int kTcATile = 128 * 128;  // bytes: 128 columns x 64 k of bf16
+constexpr int kTcXTile = 32 * 128;   // bytes: 32 rows x 64 k of bf16
+constexpr int kTcSlot = 2 * (kTcATile + kTcXTile);
+constexpr int kTcWarps = 1 + 16 + 4 + 1;
+constexpr int kTcMP = 40;            // floats per column in tbuf (32 rows, padded)
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major operand tile in the 128-byte swizzle: rows of 128 bytes (64 bf16),
+// groups of 8 rows 1024 bytes apart (the stride offset); the leading offset is not used by this layout. Bits 46-47:
+// descriptor version 1 (sm_100); bits 61-63: layout 2 (128-byte swizzle). The tile starts on a 1024-byte boundary;
+// the k-th block of 16 k inside it is the same descriptor with the start moved on by 32 k bytes.
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9, 10-12 = 1), both K-major (bits 15,
+// 16 = 0), N = 32 (bits 17-22 = N / 8), M = 128 (bits 24-28 = M / 16).
+constexpr uint32_t kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
+
+// (the descriptors as their 32-bit halves: the issuing thread's own instructions are its cost, a tile's four MMAs
+// leave it ~150 cycles, and moving a descriptor on is then one 32-bit add instead of a 64-bit one)
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t alo, uint32_t blo, uint32_t hi, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(alo), "r"(blo), "r"(hi), "r"(kTcIdesc), "r"(accumulate)
+        : "memory");
+}
+// the barrier gets one arrival once every MMA issued so far by this thread has completed
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <int FMT, bool KWHOLE>
+__global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const __grid_constant__ TkdParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    using F = Fmt<FMT>;
+    constexpr int SW = 16, MP = kTcMP, MR = 32;
+    constexpr int CK = F::SUBSA * F::KSA;
+    // Every decode warp writes to (and arrives on) every unit of two tiles: bfloat4_b's super-atom is a whole tile, so a
+    // warp of half h takes the unit's tile h; the other formats' super-atoms are half tiles: half h of both tiles.
+    constexpr int NWT = 16;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TKD_MAX_STAGES);
+    const uint32_t afull0 = smem_u32(bars + 2 * TKD_MAX_STAGES), aempty0 = afull0 + 8 * kTcSlots;
+    const uint32_t accfull0 = aempty0 + 8 * kTcSlots, accempty0 = accfull0 + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TKD_SMEM_HEAD - 32);
+    volatile int* sflag = reinterpret_cast<volatile int*>(smem + TKD_SMEM_HEAD - 16);
+    uint4* hdr = reinterpret_cast<uint4*>(smem + 512);
+    float* tbuf = reinterpret_cast<float*>(smem + p.off_tbuf);  // [128 columns][MP]: the running sums
+    uint8_t* ring = smem + p.off_ring;
+    // the operand tiles start on a 1024-byte boundary of the shared-memory window (the swizzle is a function of the address)
+    const uint32_t ops0 = (smem_u32(smem + p.off_xt) + 1023u) & ~1023u;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tid == 0) {
+        for (int s = 0; s < p.nstages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, SW);
+        }
+        for (int s = 0; s < kTcSlots; ++s) {
+            mbar_init(afull0 + 8 * s, NWT);
+            mbar_init(aempty0 + 8 * s, 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(accfull0 + 8 * s, 1);
+            mbar_init(accempty0 + 8 * s, 4);
+        }
+        sflag[0] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int64_t T = p.total_items;
+    const int64_t i0 = idiv(p, T * blockIdx.x, gridDim.x), i1 = idiv(p, T * (blockIdx.x + 1), gridDim.x);
+    const int nst = p.nstages;
+    const int M = p.M, K = p.K;
+    const int topk_k = p.topk_k, npeers = p.npeers;
+    const bool glu2 = p.epi == TKD_EPI_GLU2;
+    const int nsa_total = (K + F::KSA - 1) / F::KSA;
+    if (i0 >= i1) return;  // (before any tensor memory is held; the grid is never larger than the item count)
+    const int64_t lastp0 = idiv(p, i1 - 1, p.nslices) * p.nslices;
+    const int64_t tail0 = lastp0 > i0 && lastp0 + p.nslices > i1 ? lastp0 : i1;
+    const int64_t lead = i1 - tail0;
+    const int64_t nitems = i1 - i0;
+    auto item_at = [&](int64_t j) { return j < lead ? tail0 + j : i0 + (j - lead); };
+
+    // tensor memory: 256 columns (two sets of four accumulators of 32), allocated and freed by warp 21
+    if (warp == 21) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem0 = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer (as in tkd_stream_kernel; the whole
+        // warp walks the loop and one lane issues: a warp whose other lanes wait at the kernel's final barrier while one
+        // lane works runs that lane at a fraction of its speed)
+        {
+            Cursor c, cn;
+            uint32_t st = 0;
+            bool ok = true;
+            cursor_init(cn, p, item_at(0));
+            for (int64_t j = 0; j < nitems && ok; ++j) {
+                c = cn;
+                if (j + 1 < nitems) {
+                    if (j + 1 == lead)
+                        cursor_init(cn, p, item_at(j + 1));
+                    else
+                        cursor_next(cn, p);
+                }
+                const TkdSegDev& sg = p.seg[c.seg];
+                const int k0 = c.slice * p.ks, kv = min(p.ks, K - k0);
+                const int c0 = k0 / CK, nch = (kv + CK - 1) / CK;
+                const uint8_t* src = sg.w + (int64_t)(glu2 ? c.pl >> 1 : c.pl) * p.panel_bytes;
+                const uint8_t* src2 = glu2 ? sg.w2 + (int64_t)(c.pl >> 1) * p.panel_bytes : nullptr;
+                for (int ch = 0; ch < nch; ++ch, ++st) {
+                    const uint32_t s = st % nst;
+                    ok = mbar_wait_parked(empty0 + 8 * s, ((st / nst) & 1) ^ 1, p.status);
+                    if (!ok) break;
+                    const int nsa = min(F::SUBSA, nsa_total - (c0 + ch) * F::SUBSA);
+                    const uint32_t gbytes = (uint32_t)nsa * F::SAB;
+                    const int64_t coff = (int64_t)(c0 + ch) * (F::SUBSA * F::SAB * 8);
+                    const uint32_t dst = smem_u32(ring + (size_t)s * p.stage_bytes);
+                    const bool last = ch == nch - 1, end = last && j == nitems - 1;
+                    const int knext = end ? K : (last ? cn.slice * p.ks : (c0 + ch + 1) * CK);  // the next stage's first k
+                    if (lane == 0) {
+                        hdr[s] = make_uint4(end ? ST_END : 0u, 0u, (uint32_t)knext, (uint32_t)((c0 + ch) * CK));
+                        mbar_expect_tx(full0 + 8 * s, 8 * gbytes);
+                        if (glu2) {
+                            const int64_t hoff = coff + (int64_t)(c.pl & 1) * 4 * gbytes;
+                            bulk_g2s(dst, src + hoff, 4 * gbytes, full0 + 8 * s);
+                            bulk_g2s(dst + 4 * gbytes, src2 + hoff, 4 * gbytes, full0 + 8 * s);
+                        } else {
+                            bulk_g2s(dst, src + coff, 8 * gbytes, full0 + 8 * s);
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            if (!ok) {
+                for (uint32_t back = 1; back <= (uint32_t)nst && back <= st; ++back) {
+                    const uint32_t q = st - back;
+                    for (uint32_t i = 0; i < 64; ++i)
+                        if (mbar_try_wait(full0 + 8 * (q % nst), (q / nst) & 1)) break;
+                }
+            }
+        }
+    } else if (warp <= SW) {
+        // ---------------------------------------------------------------- decode warps
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // (x may be the output of the kernel before this one)
+        const int cw = warp - 1;
+        const int g8 = cw & 7, h = cw >> 3;
+        const int g = lane >> 2, t = lane & 3;
+        constexpr int EXPB = FMT == TKD_BFP4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
+        const uint2 sh = make_uint2(p.mul16, p.mul128);
+        const uint32_t ring_a = smem_u32(ring), hdr_a = smem_u32(hdr);
+        // This lane's two rows of an A tile, for panel columns 16 g8 + g and + 8: row groups 2 g8 and 2 g8 + 1, and inside
+        // the group row pg = g's bits rotated (g >> 1 | (g & 1) << 2), not g: the eight lanes a 16-byte store is served
+        // for together are two g (2q, 2q + 1) x four t, and the swizzle puts piece c of row r at c ^ r; with rows 2q and
+        // 2q + 1 the two g's pieces fall on the same four bank groups, with rows q and q + 4 on all eight. The output
+        // warps undo the permutation (tensor-memory lane -> column).
+        const int pg = (g >> 1) | ((g & 1) << 2);
+        const uint32_t arow = (uint32_t)(2 * g8) * 1024u + (uint32_t)pg * 128u;
+        uint32_t slot = 0, phase = 0, useq = 0;
+        // This lane's pieces of the x tiles: tile i of this warp's tiles of a chunk (bfloat4_b: the tiles of its half,
+        // 32 pieces a warp; else every tile, 16 pieces a warp on its first 16 lanes), piece = (row, 16 bytes of the row).
+        constexpr int XT = FMT == TKD_BF16 ? 2 : 4;  // tiles of a chunk a warp writes to
+        const int xe = FMT == TKD_BFP4 ? g8 * 32 + lane : cw * 16 + (lane & 15);
+        const bool xmine = FMT == TKD_BFP4 || lane < 16;
+        const int xr_ = xe >> 3, xc_ = xe & 7;
+        const uint16_t* const xrow = p.x + (int64_t)min(xr_, M - 1) * p.ldx + 8 * xc_;
+        const uint32_t xdst = 2 * kTcATile + xr_ * 128 + ((xc_ ^ (xr_ & 7)) << 4);
+        auto load_x = [&](uint4 (&v)[XT], int k0) {
+#pragma unroll
+            for (int i = 0; i < XT; ++i) {
+                const int k = k0 + 64 * (FMT == TKD_BFP4 ? 2 * i + h : i);  // the tile's first k
+                v[i] = xmine && xr_ < M && k + 8 * xc_ < K ? ldg_x(xrow + k) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        };
+        uint4 xcur[XT], xnext[XT];
+        {
+            const int64_t first_it = lead > 0 ? tail0 : i0;
+            load_x(xcur, (int)(first_it - idiv(p, first_it, p.nslices) * p.nslices) * p.ks);
+        }
+        while (true) {
+            if (!mbar_wait(full0 + 8 * slot, phase, p.status)) break;
+            const uint4 hd = lds128(hdr_a + 16 * slot);
+            const int kc = (int)hd.w;
+            load_x(xnext, (int)hd.z);  // (used a whole chunk from now)
+            const int nsa = KWHOLE ? F::SUBSA : min(F::SUBSA, nsa_total - kc / CK * F::SUBSA);
+            const int ntiles = (nsa * F::KSA + 63) / 64;
+            const uint32_t gb = ring_a + slot * p.stage_bytes + g8 * nsa * F::SAB;
+            bool ok = true;
+            // This warp's share of the chunk, a unit of two tiles at a time (unrolled: the x pieces are indexed at compile
+            // time): the slot is waited for, the tiles decoded and stored, then one proxy fence and one arrival. (The
+            // hand-over costs both sides a fixed time per barrier, the MMA warp most of all: a unit of two tiles halves it.)
+            auto tile_of = [&](int i) { return FMT == TKD_BFP4 ? 2 * i + h : i; };
+            // tile i of this warp's tiles of the chunk into place `sub` (0, 1) of the unit at shared-memory address sb
+            auto do_tile = [&](int i, uint32_t sb, int sub) {
+                const int ti = tile_of(i);
+                const int sa = FMT == TKD_BFP4 ? ti : 2 * ti + h;  // this warp's super-atom of the tile
+                if (sa < nsa) {
+                    const uint32_t ab = sb + sub * kTcATile + arow;
+                    const uint32_t sab = gb + sa * F::SAB;
+                    if constexpr (FMT == TKD_BF16) {
+                        const uint4 a = lds128(sab + lane * 16), b = lds128(sab + 512 + lane * 16);
+                        const uint32_t cc = (uint32_t)(((4 * h + t) ^ pg) << 4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ab + cc), "r"(a.x), "r"(a.z), "r"(b.x), "r"(b.z)
+                                     : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ab + 1024 + cc), "r"(a.y), "r"(a.w), "r"(b.y),
+                                     "r"(b.w)
+                                     : "memory");
+                    } else {
+                        uint32_t cwd[4], ewd[4];
+                        if constexpr (FMT == TKD_BFP8) {
+                            const uint2 ev = lds64(sab + t * 8);
+                            const uint4 cv = lds128(sab + EXPB + lane * 16);
+                            cwd[0] = cv.x, cwd[1] = cv.y, cwd[2] = cv.z, cwd[3] = cv.w;
+                            ewd[0] = ev.x, ewd[1] = ev.y, ewd[2] = ewd[3] = 0;
+                        } else {
+                            const uint4 ev = lds128(sab + t * 16), cv = lds128(sab + EXPB + lane * 16);
+                            cwd[0] = cv.x, cwd[1] = cv.y, cwd[2] = cv.z, cwd[3] = cv.w;
+                            ewd[0] = ev.x, ewd[1] = ev.y, ewd[2] = ev.z, ewd[3] = ev.w;
+                        }
+                        // one k32 block (bfloat8_b: the super-atom; bfloat4_b: each of its two) -> 8 k of two columns
+#pragma unroll
+                        for (int q = 0; q < F::XB; ++q) {
+                            uint32_t lo[4], hi[4];  // columns g and g + 8: k pairs (0,1) (2,3) (4,5) (6,7) of this lane's 8
+#pragma unroll
+                            for (int jj = 0; jj < 2; ++jj) {
+                                uint32_t a0, a1, a2, a3, s0, s1;
+                                if constexpr (FMT == TKD_BFP4) {
+                                    const uint32_t w = cwd[2 * q + jj], tt = __funnelshift_r(w, w, 8), ew = ewd[2 * q + jj];
+                                    a0 = w & TKD_MASK_BFP4, a1 = shl_fma<4>(w, sh.x) & TKD_MASK_BFP4;
+                                    a2 = tt & TKD_MASK_BFP4, a3 = shl_fma<4>(tt, sh.x) & TKD_MASK_BFP4;
+                                    s0 = (ew & TKD_EMASK_BFP4) | TKD_EBASE_BFP4;
+                                    s1 = (shl_fma<7>(ew, sh.y) & TKD_EMASK_BFP4) | TKD_EBASE_BFP4;
+                                } else {
+                                    const uint32_t w0 = cwd[2 * jj], w1 = cwd[2 * jj + 1], ew = ewd[jj];
+                                    a0 = w0 & TKD_MASK_BFP8, a1 = rot_and<8>(w0, TKD_MASK_BFP8);
+                                    a2 = w1 & TKD_MASK_BFP8, a3 = rot_and<8>(w1, TKD_MASK_BFP8);
+                                    s0 = ew & 0x7F807F80u, s1 = rot_and<8>(ew, 0x7F807F80u);
+                                }
+                                lo[2 * jj] = mul_bf16x2(a0, s0), lo[2 * jj + 1] = mul_bf16x2(a2, s1);
+                                hi[2 * jj] = mul_bf16x2(a1, s0), hi[2 * jj + 1] = mul_bf16x2(a3, s1);
+                            }
+                            const int c16 = FMT == TKD_BFP4 ? 4 * q + t : 4 * h + t;  // the 16-byte piece of the tile's rows
+                            const uint32_t cc = (uint32_t)((c16 ^ pg) << 4);
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ab + cc), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]),
+                                         "r"(lo[3])
+                                         : "memory");
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ab + 1024 + cc), "r"(hi[0]), "r"(hi[1]),
+                                         "r"(hi[2]), "r"(hi[3])
+                                         : "memory");
+                        }
+                    }
+                }
+                if (xmine) {
+                    const uint4 v = xcur[i];
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sb + sub * kTcXTile + xdst), "r"(v.x), "r"(v.y),
+                                 "r"(v.z), "r"(v.w)
+                                 : "memory");
+                }
+            };
+            constexpr int UPC = FMT == TKD_BFP4 ? 4 : XT / 2;  // units of a whole chunk
+            const int nunits = (ntiles + 1) >> 1;
+#pragma unroll
+            for (int u = 0; u < UPC; ++u) {
+                if (u >= nunits || !ok) break;
+                const uint32_t us = useq + u, ps = us % kTcSlots;
+                ok = mbar_wait(aempty0 + 8 * ps, ((us / kTcSlots) & 1) ^ 1, p.status);
+                if (!ok) break;
+                const uint32_t sb = ops0 + ps * kTcSlot;
+                if constexpr (FMT == TKD_BFP4) {
+                    if (2 * u + h < ntiles) do_tile(u, sb, h);
+                } else {
+                    do_tile(2 * u, sb, 0);
+                    if (2 * u + 1 < ntiles) do_tile(2 * u + 1, sb, 1);
+                }
+                fence_proxy_async();  // this lane's stores, for the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(afull0 + 8 * ps);
+            }
+            if (!ok) break;
+#pragma unroll
+            for (int i = 0; i < XT; ++i) xcur[i] = xnext[i];
+            useq += nunits;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * slot);
+            if (++slot == (uint32_t)nst) slot = 0, phase ^= 1;
+            if (hd.x & ST_END) break;
+        }
+    } else if (warp == 21) {
+        // ---------------------------------------------------------------- the MMA issuer (the warp walks the loop, one
+        // lane issues)
+        {
+            Cursor c;
+            uint32_t us = 0;
+            bool ok = true;
+            // the descriptors of slot 0's tiles as 32-bit halves (the high halves are equal; a slot further on is
+            // kTcSlot / 16 more in the low half, a block of 16 k is 2 more)
+            const uint64_t ad0 = tc_desc(ops0), bd0 = tc_desc(ops0 + 2 * kTcATile);
+            const uint32_t dhi = (uint32_t)(ad0 >> 32), alo0 = (uint32_t)ad0, blo0 = (uint32_t)bd0;
+            for (int64_t j = 0; j < nitems && ok; ++j) {
+                if (j == 0 || j == lead)
+                    cursor_init(c, p, item_at(j));
+                else
+                    cursor_next(c, p);
+                const int kv = min(p.ks, K - c.slice * p.ks);
+                const int nch = (kv + CK - 1) / CK;
+                const uint32_t buf = (uint32_t)j & 1;
+                // the accumulators must have been read out (the slice two before this one)
+                ok = mbar_wait_parked(accempty0 + 8 * buf, (((uint32_t)j >> 1) & 1) ^ 1, p.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem0 + buf * 128;
+                uint32_t acc = 0;
+                for (int ch = 0; ch < nch && ok; ++ch) {
+                    int kleft = min(CK, kv - ch * CK);  // k of this chunk not yet multiplied
+                    for (; kleft > 0 && ok; ++us) {
+                        const uint32_t ps = us % kTcSlots;
+                        ok = mbar_wait(afull0 + 8 * ps, (us / kTcSlots) & 1, p.status);
+                        if (!ok) break;
+                        if (lane == 0) {
+                            uint32_t al = alo0 + ps * (kTcSlot >> 4), bl = blo0 + ps * (kTcSlot >> 4);
+                            if (kleft >= 128) {
+                                // (a whole unit: two tiles of four blocks of 16 k; block j of a tile to accumulator j)
+                                tc_mma(d, al, bl, dhi, acc);
+                                tc_mma(d + 32, al + 2, bl + 2, dhi, acc);
+                                tc_mma(d + 64, al + 4, bl + 4, dhi, acc);
+                                tc_mma(d + 96, al + 6, bl + 6, dhi, acc);
+                                al += kTcATile >> 4, bl += kTcXTile >> 4;
+                                tc_mma(d, al, bl, dhi, 1);
+                                tc_mma(d + 32, al + 2, bl + 2, dhi, 1);
+                                tc_mma(d + 64, al + 4, bl + 4, dhi, 1);
+                                tc_mma(d + 96, al + 6, bl + 6, dhi, 1);
+                            } else {
+                                const int nb = (kleft + 15) >> 4;  // a short last unit of K
+                                for (int b = 0; b < nb; ++b) {
+                                    if (b == 4) al += (kTcATile >> 4) - 8, bl += (kTcXTile >> 4) - 8;
+                                    tc_mma(d + 32 * (b & 3), al + 2 * b, bl + 2 * b, dhi, b >= 4 ? 1u : acc);
+                                }
+                            }
+                            tc_commit(aempty0 + 8 * ps);
+                        }
+                        acc = 1;
+                        kleft -= 128;
+                        __syncwarp();
+                    }
+                }
+                if (ok && lane == 0) tc_commit(accfull0 + 8 * buf);
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- output warps (warps 17-20)
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        const int ow = warp & 3;          // the quarter of the tensor memory's lanes this warp may read
+        // the panel column this thread owns: its tensor-memory lane is A-tile row ow * 32 + lane, whose row group holds
+        // eight columns in the decode warps' permuted order
+        const int et = (ow * 32 + (lane & 24)) + (((lane & 3) << 1) | ((lane >> 2) & 1));
+        Cursor c;
+        bool ok = true;
+        float* const trow = tbuf + (size_t)et * MP;
+        uint16_t* y16 = static_cast<uint16_t*>(p.out);
+        for (int64_t j = 0; j < nitems && ok; ++j) {
+            const int64_t it = item_at(j);
+            if (j == 0 || j == lead)
+                cursor_init(c, p, it);
+            else
+                cursor_next(c, p);
+            const Flow f = flow_of(c, p, it, i0, i1);
+            const TkdSegDev& sg = p.seg[c.seg];
+            const int n = glu2 ? c.pl * 64 + (et & 63) : c.pl * TKD_PANEL_COLS + et;
+            const bool in_w = n < sg.n_valid;
+            int ebyte = 0;
+            float sc = 1.f;
+            if (f.deliver) {
+                if constexpr (FMT != TKD_BF16) ebyte = (glu2 && et >= 64 ? sg.emax2 : sg.emax)[n >> 4];
+                if (p.scale_dt != TKD_DT_NONE && in_w) {
+                    const void* sp = glu2 && et >= 64 ? p.scale2 : p.scale;
+                    sc = p.scale_dt == TKD_DT_BF16 ? bf16_bits_to_f32(static_cast<const uint16_t*>(sp)[n])
+                                                   : static_cast<const float*>(sp)[n];
+                }
+            }
+            const uint32_t buf = (uint32_t)j & 1;
+            ok = mbar_wait_parked(accfull0 + 8 * buf, ((uint32_t)j >> 1) & 1, p.status);
+            if (!ok) break;
+            tc_fence_after();
+            {
+                // the slice's sum: ((d0 + d1) + d2) + d3 over the accumulators the slice touched (all four unless it is
+                // shorter than 64 k), sixteen rows at a time
+                const int kv = min(p.ks, K - c.slice * p.ks);
+                const int nacc = min(4, (kv + 15) / 16);
+                const uint32_t ta = tmem0 + ((uint32_t)(ow * 32) << 16) + buf * 128;
+                auto ld16 = [&](uint32_t addr, float (&o)[16], bool add) {
+                    uint32_t r[16];
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                        : "r"(addr)
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int m = 0; m < 16; ++m) o[m] = add ? o[m] + __uint_as_float(r[m]) : __uint_as_float(r[m]);
+                };
+#pragma unroll 1
+                for (int hf = 0; hf < 2; ++hf) {
+                    float v[16];
+                    ld16(ta + 16 * hf, v, false);
+#pragma unroll 1
+                    for (int a = 1; a < nacc; ++a) ld16(ta + 32 * a + 16 * hf, v, true);
+                    // the running sums of this thread's column: they start over with the slice, or the slice is added
+#pragma unroll
+                    for (int m = 0; m < 16; m += 4) {
+                        float4 q = make_float4(v[m], v[m + 1], v[m + 2], v[m + 3]);
+                        if (!f.start) {
+                            const float4 o = *reinterpret_cast<const float4*>(trow + 16 * hf + m);
+                            q = make_float4(o.x + q.x, o.y + q.y, o.z + q.z, o.w + q.w);
+                        }
+                        *reinterpret_cast<float4*>(trow + 16 * hf + m) = q;
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(accempty0 + 8 * buf);
+            }
+            if (f.store) {
+                // the running sums into the scratch slot of (panel, slice): [row][128 columns] (the first half of a slot
+                // as tkd_stream_kernel lays it out; there is no second half here)
+                float* scr = p.scratch + (size_t)(c.panel * p.nslices + c.slice) * 2 * M * TKD_PANEL_COLS + et;
+#pragma unroll 1
+                for (int m = 0; m < M; ++m) __stcg(scr + (size_t)m * TKD_PANEL_COLS, trow[m]);
+            }
+            if (!f.deliver) continue;
+            bool finish = !f.split;
+            if (f.split) {
+                // count this CTA's slices of the panel in; if they were the last the panel waited for, add all of its
+                // slices up (bar.sync orders the 128 threads' scratch stores before thread 0's release)
+                bar_output_warps();
+                if (et == 0) {
+                    const int old = atom_add_acq_rel(p.counters + c.panel, f.count);
+                    const int last = old + f.count == p.nslices;
+                    if (last) p.counters[c.panel] = 0;
+                    sflag[0] = last;
+                }
+                bar_output_warps();
+                finish = sflag[0] != 0;
+                if (finish) {
+                    const int64_t pfirst = (int64_t)c.panel * p.nslices;
+                    const int64_t owner = idiv(p, (pfirst + 1) * gridDim.x - 1, T);
+                    const int64_t oend = idiv(p, T * (owner + 1), gridDim.x);
+                    const int pe = (int)min((int64_t)p.nslices, oend - pfirst);
+                    const float* s0 = p.scratch + pfirst * 2 * M * TKD_PANEL_COLS + et;
+                    auto term = [&](int s, int m) { return __ldcg(s0 + ((size_t)(s * 2) * M + m) * TKD_PANEL_COLS); };
+#pragma unroll 1
+                    for (int rb = 0; rb < M; rb += 8) {
+                        float th[8];
+#pragma unroll 1
+                        for (int s = pe - 1; s < p.nslices; s += 4) {
+                            float v[4][8];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                                for (int m = 0; m < 8; ++m) v[q][m] = term(min(s + q, p.nslices - 1), min(rb + m, M - 1));
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                                for (int m = 0; m < 8; ++m) {
+                                    if (s + q >= p.nslices) continue;
+                                    th[m] = s + q == pe - 1 ? v[q][m] : th[m] + v[q][m];
+                                }
+                        }
+                        *reinterpret_cast<float4*>(trow + rb) = make_float4(th[0], th[1], th[2], th[3]);
+                        *reinterpret_cast<float4*>(trow + rb + 4) = make_float4(th[4], th[5], th[6], th[7]);
+                    }
+                }
+                bar_output_warps();  // sflag may be written again only after everyone has read it
+            }
+            if (!finish) continue;
+
+            // ------------------------------------------------------------ the output stage of one panel, from the sums
+            // in tbuf, eight rows at a time in a rolled loop (the same stage as tkd_stream_kernel's for 9 rows and more)
+            {
+                float colf = 1.f, colg = 1.f;
+                if constexpr (FMT != TKD_BF16) {
+                    const int e = tkd_out_exp(FMT, ebyte);
+                    const int e1 = e / 2, e2 = e - e1;
+                    colf = __uint_as_float((uint32_t)(e1 + 127) << 23), colg = __uint_as_float((uint32_t)(e2 + 127) << 23);
+                }
+                const float cols = p.scale_dt != TKD_DT_NONE && in_w ? sc : 1.f;
+                const bool glu = p.epi == TKD_EPI_GLU_IL || glu2;
+                int ocol = -1;
+                const float *gp = trow, *up = trow;
+                if (glu) {
+#pragma unroll 1
+                    for (int m = 0; m < MR; m += 4) {
+                        float4 v = *reinterpret_cast<float4*>(trow + m);
+                        v.x = v.x * colf * colg * cols, v.y = v.y * colf * colg * cols;
+                        v.z = v.z * colf * colg * cols, v.w = v.w * colf * colg * cols;
+                        *reinterpret_cast<float4*>(trow + m) = v;
+                    }
+                    bar_output_warps();
+                    if (et < 64) {
+                        const int gc = glu2 ? et : 64 * (et >> 5) + (et & 31), uc = glu2 ? et + 64 : gc + 32;
+                        const int nw = glu2 ? n : c.pl * TKD_PANEL_COLS + uc;
+                        if (nw < sg.n_valid) ocol = sg.out_col0 + c.pl * 64 + et;
+                        gp = tbuf + (size_t)gc * MP, up = tbuf + (size_t)uc * MP;
+                    }
+                } else if (in_w) {
+                    ocol = sg.out_col0 + n;
+                }
+                const bool store = ocol >= 0 && (topk_k == 0 || p.write_y);
+                if (ocol >= 0) {
+#pragma unroll 1
+                    for (int r0 = 0; r0 < M; r0 += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int m = 0; m < 8; ++m)
+                            v[m] = glu ? act_gate(gp[r0 + m], p.act) * up[r0 + m] : trow[r0 + m] * colf * colg * cols;
+                        if (p.epi == TKD_EPI_OUT32 && p.res_dt == TKD_DT_F32) {
+#pragma unroll
+                            for (int m = 0; m < 8; ++m)
+                                if (r0 + m < M) v[m] += static_cast<const float*>(p.res)[(size_t)(r0 + m) * p.ldr + ocol];
+                        } else if (p.epi == TKD_EPI_RESIDUAL) {
+#pragma unroll
+                            for (int m = 0; m < 8; ++m)
+                                if (r0 + m < M)
+                                    v[m] += bf16_bits_to_f32(static_cast<const uint16_t*>(p.res)[(size_t)(r0 + m) * p.ldr + ocol]);
+                        }
+#pragma unroll
+                        for (int m = 0; m < 8; ++m) {
+                            if (r0 + m >= M) break;
+                            const size_t at = (size_t)(r0 + m) * p.ldo + ocol;
+                            if (p.epi == TKD_EPI_OUT32) {
+                                static_cast<float*>(p.out)[at] = v[m];
+                                for (int q = 0; q < npeers; ++q)
+                                    if (p.peer_out[q]) static_cast<float*>(p.peer_out[q])[at] = v[m];
+                            } else {
+                                const uint16_t b = f32_to_bf16_bits(v[m]);
+                                if (store) {
+                                    y16[at] = b;
+                                    for (int q = 0; q < npeers; ++q)
+                                        if (p.peer_out[q]) static_cast<uint16_t*>(p.peer_out[q])[at] = b;
+                                }
+                                if (topk_k && !p.write_y && r0 + m < p.topk_rows) p.ytmp[(size_t)(r0 + m) * p.ld_ytmp + n] = b;
+                            }
+                        }
+                    }
+                }
+                if (glu) bar_output_warps();  // tbuf is free again
+            }
+            if (topk_k == 0) continue;
+            topk_records(p, c, sg, et, ow, lane, tbuf, sflag, y16, topk_k, npeers);
+        }
+        if (npeers) exchange_done(p, lane, npeers);
+    }
+    // ---- the end: everyone is here (a role whose wait gave up falls through to this point too), and the tensor memory
+    // goes back
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 21) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem0), "r"(256u) : "memory");
+    }
+}
+
+template <int FMT, bool KWHOLE>
+int launch_tc(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
+    auto kern = tkd_stream_tc_kernel<FMT, KWHOLE>;
+    static bool allowed[64] = {false};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64 || !allowed[dev]) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        if (dev >= 0 && dev < 64) allowed[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kTcWarps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.no_pdl ? 0 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+template <int FMT>
+int launch_fmt_all(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
+    if (p.tc) {
+        return p.K % (Fmt<FMT>::SUBSA * Fmt<FMT>::KSA) == 0 ? launch_tc<FMT, true>(p, grid, smem, st)
+                                                           : launch_tc<FMT, false>(p, grid, smem, st);
+    }
+    return launch_fmt<FMT>(p, grid, smem, st);
+}
+
+}  // namespace
