@@ -3,23 +3,29 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c1|c5] [--rows M] [--impl reference]
 
 One step is one pass of the hot path over one batch of synthetic input: one call of linear.matmul. The default
-workload is BASELINE.json's configs[1] ("c2"): the Llama-3-8B MLP gate/up pair, x [1, 4096] bf16, two [14336, 4096]
-bfloat4_b weights with float32 per-column scales, output silu(x Wg) * (x Wu) in bf16. Inputs are seeded synthetic
-tensors of those shapes and distributions (there are no checkpoints here).
+workload ("c2") is the Llama-3-8B MLP gate/up pair, x [1, 4096] bf16, two [14336, 4096] bfloat4_b weights with float32
+per-column scales, output silu(x Wg) * (x Wu) in bf16. Inputs are seeded synthetic tensors of those shapes and
+distributions (there are no checkpoints here).
 
 Printed: ONE JSON line. `value` is weight-stream GB/s (packed weight bytes of the calls / device time, CUDA events,
 max over ranks, all ranks' bytes), inputs resident in HBM, the K steps replayed from one CUDA graph. The weights are
 smaller than the 126 MB L2, so the steps rotate over enough distinct packed copies to exceed twice the L2 (`config.l2`).
 `e2e` is the same metric through the public Python API with host buffers: every step copies x from pinned host
-memory, calls linear.matmul and reads y back to pinned host memory. `roofline` compares the kernel's algorithmic bytes
-per launch with the measured HBM copy bandwidth of MEASURED_PEAKS.json. `cpu_baseline` (rank 0, N = 1) times the
-reference's torch path (the oracle's port of dense_reader/linear.py:166-169 plus the SwiGLU stage) on the host cores on
-a bounded column sample of the same workload.
+memory, runs the op and reads y back to pinned host memory (one library call a step, two steps in flight; the
+one-step-at-a-time latency is given beside it). `roofline` compares the kernel's algorithmic bytes per launch with the
+measured HBM copy bandwidth (the driver's peak file at the repository root, when present). `cpu_baseline` (rank 0,
+N = 1) times the reference's torch path (the oracle's port of dense_reader/linear.py:166-169 plus the SwiGLU stage) on
+the host cores on a bounded column sample of the same workload, for a fixed wall time.
+
+Beside the headline the line carries, timed in the same run: `sub` (the down projection, bfloat8_b [4096, 14336] with a
+float32 residual, one row), `rows32` (the same at 32 rows: the metric is quoted at one row and at 32) and, with N > 1,
+`c5_strong` (the LM head's 151936 columns split over the N ranks, top-k records exchanged, global top-32 on every rank).
 
 N > 1 (torchrun, one rank per GPU, NCCL): weak scaling. Each rank streams its own column shard of the same size (a layer
 N times as wide, column-sharded as native_weight would pack it per rank) and every rank ends each step holding all
 ranks' outputs: by default the stream kernel stores them into the other ranks' buffers itself (peer stores over NVLink,
-sharded.Exchange); --exchange nccl all-gathers them with NCCL on a side stream instead.
+sharded.Exchange); --exchange nccl all-gathers them with NCCL on a side stream instead. Before anything is timed every
+rank checks the exchanged buffer bit for bit against an NCCL all-gather of the ranks' own outputs (`exchange_check`).
 
 --impl reference: the reference's own CPU implementation of the path (the oracle port; the reference's device path needs
 ttnn and a Tensix simulator, neither of which exists here), all host threads, same metric.
@@ -137,9 +143,9 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
             wg, wu = sets[i % copies]
             return linear.matmul(x_t, wg, None, w_up=wu, glu=True, col_scales=cs, out=y_t, **kw)
 
-        def host_step(i, x_pin, y_pin, x_t, y_t, stream):
+        def host_step(i, x_pin, y_pin, x_t, y_t, stream, **kw):
             wg, wu = sets[i % copies]
-            linear.matmul_host(x_pin, y_pin, x_t, wg, None, w_up=wu, glu=True, col_scales=cs, out=y_t, stream=stream)
+            linear.matmul_host(x_pin, y_pin, x_t, wg, None, w_up=wu, glu=True, col_scales=cs, out=y_t, stream=stream, **kw)
         extra["host_step"] = host_step
         weights = 2
     elif name == "c3":
@@ -149,8 +155,9 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
         def step(i, x_t=tx, y_t=y, res_t=res, **kw):
             return linear.matmul(x_t, sets[i % copies][0], None, residual=res_t, out32=True, out=y_t, **kw)
 
-        def host_step(i, x_pin, y_pin, x_t, y_t, stream):
-            linear.matmul_host(x_pin, y_pin, x_t, sets[i % copies][0], None, residual=res, out32=True, out=y_t, stream=stream)
+        def host_step(i, x_pin, y_pin, x_t, y_t, stream, **kw):
+            linear.matmul_host(x_pin, y_pin, x_t, sets[i % copies][0], None, residual=res, out32=True, out=y_t, stream=stream,
+                               **kw)
         extra["host_step"] = host_step
         weights = 1
         extra["res"] = res
@@ -174,8 +181,8 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
         def step(i, x_t=tx, y_t=y, **kw):
             return linear.matmul(x_t, sets[i % copies][0], None, out=y_t, **kw)
 
-        def host_step(i, x_pin, y_pin, x_t, y_t, stream):
-            linear.matmul_host(x_pin, y_pin, x_t, sets[i % copies][0], None, out=y_t, stream=stream)
+        def host_step(i, x_pin, y_pin, x_t, y_t, stream, **kw):
+            linear.matmul_host(x_pin, y_pin, x_t, sets[i % copies][0], None, out=y_t, stream=stream, **kw)
         extra["host_step"] = host_step
         weights = 1
     wbytes = int(weights * k * n * BYTES_PER_WEIGHT[wl["fmt"]])
@@ -186,9 +193,11 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
     return dict(step=step, x=tx, y=y, wbytes=wbytes, abytes=wbytes + other, x_host=x, sets=sets, **extra)
 
 
-def cpu_reference_arm(name, m, steps, warmup, budget_s=20.0):
+def cpu_reference_arm(name, m, steps, warmup, budget_s=20.0, min_s=3.0):
     """The reference's torch path on the host cores (oracle port): bf16(x).float() @ Wq.float() and the workload's
-    output stage, on a column sample sized to a few seconds. Returns (GB/s of packed-weight bytes, info)."""
+    output stage, on a column sample, repeated for at least min_s seconds of wall time (and `steps` repetitions, but
+    never past budget_s): a few milliseconds of work timed over twenty repetitions moved by 60 % from run to run.
+    Returns (GB/s of packed-weight bytes, info)."""
     from oracle import oracle as orc
 
     wl = WORKLOADS[name]
@@ -214,13 +223,16 @@ def cpu_reference_arm(name, m, steps, warmup, budget_s=20.0):
             return torch.topk(y.float().reshape(m, -1, min(2048, n_s)), 8, dim=-1)
         return y
 
-    for _ in range(max(1, warmup)):
+    for _ in range(max(3, warmup)):
         one()
     t0 = time.perf_counter()
     done = 0
-    while done < steps and (done < 3 or time.perf_counter() - t0 < budget_s):
+    while True:
         one()
         done += 1
+        el = time.perf_counter() - t0
+        if el >= budget_s or (el >= min_s and done >= steps):
+            break
     dt = (time.perf_counter() - t0) / done
     sample_bytes = nw * k * n_s * BYTES_PER_WEIGHT[wl["fmt"]]
     info = {"cores": torch.get_num_threads(), "kind": "port",
@@ -271,7 +283,7 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
-        val, info = cpu_reference_arm(args.workload, m, steps, warmup, budget_s=60.0)
+        val, info = cpu_reference_arm(args.workload, m, steps, warmup, budget_s=60.0, min_s=5.0)
         line = {
             "impl": "reference", "metric": "weight_stream_gbps", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
             "steps": steps, "warmup": warmup, "ms_per_step": info["ms_per_step_sample"], "higher_is_better": True,
@@ -351,6 +363,7 @@ def main():
             units_all = linear.topk_units(n_total) if strong else world * linear.topk_units(n_loc)
             slot0 = col_start // 2048 if strong else rank * linear.topk_units(n_loc)
             recs = [ex.tensor([1, 1, units_all, r0.shape[-1]], r0.dtype) for _ in range(nbuf)]
+            case["exchanged_records"] = recs
             specs = [{"r": r, "k": 8, "rows": 1, "slot0": slot0, "base": col_start, "n": n_loc, "write_y": False}
                      for r in recs]
 
@@ -399,62 +412,25 @@ def main():
             dist.all_gather_into_tensor(rbuf.t.reshape(-1), r.t.reshape(-1))
             return linear.topk_merge(rbuf, 1, 8, 32, out=case["top32"])
 
+    # ---- N > 1: the exchanged buffer against an NCCL all-gather of the ranks' own results, bit for bit ----
+    exchange_check = None
+    if world > 1 and fused:
+        exchange_check = check_exchange(args.workload, case, step, join_side, device, world, rank, m, n_loc, col_start,
+                                        n_total, args.scaling == "strong", shards if args.scaling == "strong" else None)
+        if not exchange_check["ok"]:
+            sys.stderr.write(f"bench: rank {rank}: the exchanged buffer differs from the gathered results: {exchange_check}\n")
+            os._exit(3)
+
     # ---- device-resident: the K steps as one CUDA graph ----
-    for i in range(warmup):
-        step(i)
-    join_side()
-    linear.check_status(device)
     if args.profile:
-        for i in range(steps):
+        for i in range(warmup + steps):
             step(i)
         join_side()
         linear.check_status(device)
         return 0
-    graph = torch.cuda.CUDAGraph()
-    cap = torch.cuda.Stream()
-    cap.wait_stream(torch.cuda.current_stream())
-    graphed = True
-    try:
-        with torch.cuda.stream(cap):
-            step(0)
-            join_side()
-            torch.cuda.synchronize()
-            with torch.cuda.graph(graph, stream=cap):
-                for i in range(steps):
-                    step(i)
-                join_side()
-        torch.cuda.synchronize()
-        graph.replay()  # one untimed replay
-    except Exception as e:  # (a collective that cannot be captured: time plain launches instead)
-        graphed = False
-        sys.stderr.write(f"bench: CUDA graph capture failed ({type(e).__name__}: {e}); timing plain launches\n")
-        torch.cuda.synchronize()
-
-    def run_once():
-        if graphed:
-            graph.replay()
-        else:
-            for i in range(steps):
-                step(i)
-            join_side()
-
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with Clocks(local) as clk:
-        time.sleep(0.25)
-        reps = max(1, int(0.6 / max(1e-6, steps * 12e-6)))  # keep the timed region long enough for a clock sample
-        e0.record()
-        for _ in range(reps):
-            run_once()
-        e1.record()
-        torch.cuda.synchronize()
-        time.sleep(0.15)
-    ms = e0.elapsed_time(e1) / reps
+        ms, reps, graphed = timed_graph(step, join_side, steps, warmup, world, device, min_s=0.6)
     linear.check_status(device)
-    t = torch.tensor([ms], device=device.torch)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
     wb = torch.tensor([case["wbytes"]], dtype=torch.float64, device=device.torch)
     if world > 1:
         dist.all_reduce(wb)  # all ranks' packed-weight bytes of one step
@@ -463,61 +439,19 @@ def main():
     us_call = ms * 1e3 / steps
 
     # ---- end to end through the public API with host buffers ----
-    x_pin = case["x_host"].reshape(1, 1, m, wl["k"]).contiguous().pin_memory()
-    y_dev = case["y"]
-    out_dev = step(0)
-    out_t = out_dev.t if hasattr(out_dev, "t") else out_dev
-    y_pin = torch.empty(out_t.shape, dtype=out_t.dtype).pin_memory()
-    e_steps = min(steps, 300)
+    e2e = None
+    if case.get("host_step") is not None and not (world > 1 and (args.workload == "c3" or not fused)):
+        e2e = end_to_end(args.workload, case, wl, m, device, world, rank, n_total, col_start, copies, min(steps, 300),
+                         warmup, job_bytes, fused)
+    linear.check_status(device)
 
-    host_call = case.get("host_step") if world == 1 else None
-    # two lanes (stream, device staging tensors, pinned buffers, workspace slot) take the steps in turn, so that one
-    # step's copies overlap the other's kernel; each lane's steps stay in order on its stream
-    lanes = []
-    if host_call is not None:
-        for ln in range(2):
-            lanes.append(dict(
-                stream=torch.cuda.Stream(), slot=1 + ln,
-                x=ttnn.from_torch(torch.zeros(1, 1, m, wl["k"], dtype=torch.bfloat16), dtype=ttnn.bfloat16,
-                                  layout=ttnn.TILE_LAYOUT, device=device),
-                y=ttnn.allocate_tensor_on_device(case["y"].shape, case["y"].dtype, ttnn.TILE_LAYOUT, device),
-                xp=x_pin.clone().pin_memory(), yp=torch.empty(out_t.shape, dtype=out_t.dtype).pin_memory()))
-
-    def e2e_step(i):
-        if host_call is not None:  # one library call: H2D copy of x, the launch, D2H copy of y
-            ln = lanes[i % 2]
-            linear.WORKSPACE_SLOT = ln["slot"]
-            host_call(i, ln["xp"], ln["yp"], ln["x"], ln["y"], ln["stream"])
-            linear.WORKSPACE_SLOT = 0
-            return
-        case["x"].t.copy_(x_pin, non_blocking=True)
-        o = step(i)
-        y_pin.copy_(o.t, non_blocking=True)
-
-    def e2e_join():
-        for ln in lanes:
-            torch.cuda.current_stream().wait_stream(ln["stream"])
-        join_side()
-
-    for ln in lanes:
-        ln["stream"].wait_stream(torch.cuda.current_stream())
-    for i in range(max(warmup, 2 * copies)):
-        e2e_step(i)
-    e2e_join()
-    barrier()
-    for ln in lanes:
-        ln["stream"].wait_stream(torch.cuda.current_stream())
-    e0.record()
-    for i in range(e_steps):
-        e2e_step(i)
-    e2e_join()
-    e1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1)], device=device.torch)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
-    e2e_val = job_bytes * e_steps / (e2e_ms * 1e-3) / 1e9
+    # ---- what else the metric names, timed in the same run ----
+    subs = {}
+    if world == 1 and args.workload == "c2" and m == 1 and not args.cols:
+        for key, rows in (("sub", 1), ("rows32", 32)):
+            subs[key] = sub_case("c3", rows, device, max(50, steps // 3))
+    if args.workload == "c2" and m == 1 and not args.cols and (world == 1 or fused):
+        subs["c5_strong"] = lm_head_strong(device, world, rank, max(30, steps // 10))
     linear.check_status(device)
 
     if rank != 0:
@@ -535,19 +469,263 @@ def main():
                    "exchange": exchange_note},
         "pct_of_8000": 100 * value / world / 8000.0,
         "clocks": clk.summary(),
-        "e2e": {"value": e2e_val, "unit": "GB/s", "us_per_call": e2e_ms * 1e3 / e_steps, "steps": e_steps,
-                "h2d_bytes_per_step": x_pin.numel() * 2, "d2h_bytes_per_step": y_pin.numel() * y_pin.element_size()},
         "gpu_launches": steps * reps * launches_per_step,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": TRAFFIC.get(args.workload) if m == 1 else None, "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": case["abytes"]},
     }
+    if e2e is not None:
+        line["e2e"] = e2e
+    if exchange_check is not None:
+        line["exchange_check"] = exchange_check
+    line.update(subs)
     if world == 1 and not args.no_cpu:
-        val, info = cpu_reference_arm(args.workload, m, 10_000, 2, budget_s=15.0)
+        val, info = cpu_reference_arm(args.workload, m, 50, 3, budget_s=15.0, min_s=4.0)
         line["cpu_baseline"] = {"value": val, "unit": "GB/s", **info}
     emit(line)
     finish(world)
     return 0
+
+
+def _barrier(world):
+    torch.cuda.synchronize()
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        torch.cuda.synchronize()
+
+
+def _max_over_ranks(v, world, device):
+    t = torch.tensor([v], device=device.torch)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def timed_graph(step, join, steps, warmup, world, device, min_s=0.3):
+    """`warmup` calls, then `steps` calls captured in one CUDA graph and replayed for at least min_s seconds between
+    two CUDA events (after a barrier; the maximum over ranks). Returns (ms per replay, replays, whether a graph was used)."""
+    from dense_reader import linear
+
+    for i in range(warmup):
+        step(i)
+    join()
+    linear.check_status(device)
+    graph = torch.cuda.CUDAGraph()
+    cap = torch.cuda.Stream()
+    cap.wait_stream(torch.cuda.current_stream())
+    graphed = True
+    try:
+        with torch.cuda.stream(cap):
+            step(0)
+            join()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=cap):
+                for i in range(steps):
+                    step(i)
+                join()
+        torch.cuda.synchronize()
+        graph.replay()  # one untimed replay
+    except Exception as e:  # (a collective that cannot be captured: time plain launches instead)
+        graphed = False
+        sys.stderr.write(f"bench: CUDA graph capture failed ({type(e).__name__}: {e}); timing plain launches\n")
+        torch.cuda.synchronize()
+
+    def run_once():
+        if graphed:
+            graph.replay()
+        else:
+            for i in range(steps):
+                step(i)
+            join()
+
+    _barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    time.sleep(0.25)
+    reps = max(1, int(min_s / max(1e-6, steps * 12e-6)))  # keep the timed region long enough for a clock sample
+    e0.record()
+    for _ in range(reps):
+        run_once()
+    e1.record()
+    torch.cuda.synchronize()
+    time.sleep(0.15)
+    return _max_over_ranks(e0.elapsed_time(e1) / reps, world, device), reps, graphed
+
+
+def check_exchange(name, case, step, join, device, world, rank, m, n_loc, col_start, n_total, strong, shards):
+    """Every rank runs one step with the in-kernel exchange and one without, the plain results are all-gathered with
+    NCCL, and the exchange buffer must hold exactly that: evidence that the peer stores over NVLink land where they
+    should, in every rank's buffer."""
+    import torch.distributed as dist
+
+    from dense_reader import linear, sharded
+
+    out = step(0)  # exchanged: this rank's part into every rank's buffer
+    join()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    if name == "c5":
+        # the records of this rank's columns, made without an exchange, with the exchanged call's numbering
+        units_loc = linear.topk_units(n_loc)
+        umax = torch.tensor([units_loc], device=device.torch)
+        dist.all_reduce(umax, op=dist.ReduceOp.MAX)
+        umax = int(umax.item())
+        r = linear.topk_result(device, umax, 1, 8)
+        spec = {"r": r, "k": 8, "rows": 1, "slot0": 0, "base": col_start, "n": n_loc, "write_y": False}
+        case["step"](0, spec_t=spec, merge=False)
+        torch.cuda.synchronize()
+        gathered = sharded.gather_records(r.t.reshape(umax, -1))
+        counts = [torch.zeros(1, dtype=torch.int64, device=device.torch) for _ in range(world)]
+        dist.all_gather(counts, torch.tensor([units_loc], dtype=torch.int64, device=device.torch))
+        want = torch.cat([gathered[q * umax : q * umax + int(c.item())] for q, c in enumerate(counts)])
+        got = case["exchanged_records"][0].t.reshape(-1, want.shape[-1])[: want.shape[0]]
+    else:
+        case["step"](0)  # plain: this rank's columns only, into its own output
+        torch.cuda.synchronize()
+        widths = [b - a for a, b in shards] if strong else [n_loc] * world
+        starts = [a for a, _ in shards] if strong else [q * n_loc for q in range(world)]
+        want = sharded.gather_outputs(case["y"].t.reshape(m, -1), [(s0, s0 + w) for s0, w in zip(starts, widths)])
+        got = out.t.reshape(m, -1)
+    ok = bool(torch.equal(got.reshape(-1).view(torch.uint8), want.contiguous().reshape(-1).view(torch.uint8)))
+    t = torch.tensor([int(ok)], device=device.torch)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return {"ok": bool(t.item()), "ranks": world, "compared_bytes": int(want.numel() * want.element_size()),
+            "against": "NCCL all-gather of every rank's own result, bit for bit, on every rank"}
+
+
+def end_to_end(name, case, wl, m, device, world, rank, n_total, col_start, copies, e_steps, warmup, job_bytes, fused):
+    """The same metric with the activations and the result in pinned host memory: every step is one library call
+    (tkd_matmul_host: the copy of x to the device, the launch, the copy of the result back), two lanes (stream, staging
+    tensors, pinned buffers, workspace; with N > 1 an exchange of its own) taking the steps in turn so that one step's
+    copies overlap the other's kernel. Beside it the latency of one call at a time (the call, then a synchronise)."""
+    from common import ttnn_like as ttnn
+    from dense_reader import linear, sharded
+
+    host_call = case["host_step"]
+    out_shape = [1, 1, m, n_total if world > 1 else case["y"].shape[-1]]
+    x_pin = case["x_host"].reshape(1, 1, m, wl["k"]).contiguous().pin_memory()
+    lanes = []
+    for ln in range(2):
+        ex = sharded.Exchange(device, 4 << 20) if world > 1 and fused else None
+        y = (ex.tensor(out_shape, case["y"].dtype) if ex is not None
+             else ttnn.allocate_tensor_on_device(out_shape, case["y"].dtype, ttnn.TILE_LAYOUT, device))
+        lanes.append(dict(
+            stream=torch.cuda.Stream(), slot=1 + ln, ex=ex, y=y,
+            x=ttnn.from_torch(torch.zeros(1, 1, m, wl["k"], dtype=torch.bfloat16), dtype=ttnn.bfloat16,
+                              layout=ttnn.TILE_LAYOUT, device=device),
+            xp=x_pin.clone().pin_memory(), yp=torch.empty(out_shape, dtype=y.t.dtype).pin_memory()))
+
+    def call(i, ln):
+        linear.WORKSPACE_SLOT = ln["slot"]
+        kw = {} if ln["ex"] is None else {"exchange": ln["ex"], "col0": col_start // 32}
+        host_call(i, ln["xp"], ln["yp"], ln["x"], ln["y"], ln["stream"], **kw)
+        linear.WORKSPACE_SLOT = 0
+
+    def join():
+        for ln in lanes:
+            if ln["ex"] is not None:
+                ln["ex"].wait_all(linear.status_word(device), stream=ln["stream"])
+            torch.cuda.current_stream().wait_stream(ln["stream"])
+
+    def fork():
+        for ln in lanes:
+            ln["stream"].wait_stream(torch.cuda.current_stream())
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fork()
+    for i in range(max(warmup, 2 * copies)):
+        call(i, lanes[i % 2])
+    join()
+    _barrier(world)
+    fork()
+    e0.record()
+    for i in range(e_steps):
+        call(i, lanes[i % 2])
+    join()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = _max_over_ranks(e0.elapsed_time(e1), world, device)
+    linear.check_status(device)
+    # one call at a time: host wall clock around call + synchronise (a decode step that needs its result before the next)
+    lat_steps = min(e_steps, 100)
+    _barrier(world)
+    t0 = time.perf_counter()
+    for i in range(lat_steps):
+        call(i, lanes[0])
+        lanes[0]["stream"].synchronize()
+    lat_us = _max_over_ranks((time.perf_counter() - t0) / lat_steps * 1e6, world, device)
+    linear.check_status(device)
+    return {"value": job_bytes * e_steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "us_per_call": e2e_ms * 1e3 / e_steps,
+            "steps": e_steps, "mode": "pipelined x2 (two calls in flight on two streams)",
+            "h2d_bytes_per_step": x_pin.numel() * 2, "d2h_bytes_per_step": lanes[0]["yp"].numel() * lanes[0]["yp"].element_size(),
+            "one_call_at_a_time_us": lat_us}
+
+
+def sub_case(name, rows, device, steps):
+    """Another workload at N = 1, device-resident, graph-replayed: microseconds per call and its roofline."""
+    wl = WORKLOADS[name]
+    copies = min(40, max(2, -(-2 * L2_BYTES // int(wl["k"] * wl["n"] * BYTES_PER_WEIGHT[wl["fmt"]])) + 1))
+    case = build_gpu_case(name, rows, device, copies, seed0=500 + rows)
+    ms, reps, _ = timed_graph(case["step"], lambda: None, steps, 5, 1, device, min_s=0.2)
+    us = ms * 1e3 / steps
+    peak, _ = peaks()
+    achieved = case["abytes"] / (us * 1e-6) / 1e9
+    out = {"workload": f"{name}: {wl['what']}", "rows": rows, "us_per_call": us, "value": case["wbytes"] / (us * 1e-6) / 1e9,
+           "unit": "GB/s", "steps": steps,
+           "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                        "algorithmic_bytes_per_launch": case["abytes"]}}
+    del case
+    torch.cuda.empty_cache()
+    return out
+
+
+def lm_head_strong(device, world, rank, steps):
+    """The LM head's 151936 columns split over the ranks by 2048-column units (strong scaling): every rank streams its
+    shard, its top-k records go into every rank's buffer from inside the kernel, and every rank merges the global
+    top-32. Microseconds per step (max over ranks), with the exchanged records checked against an NCCL gather."""
+    from dense_reader import linear, sharded
+
+    wl = WORKLOADS["c5"]
+    if world > 1:
+        import torch.distributed as dist
+
+        shards = sharded.column_shards(wl["n"], world, unit=2048)
+    else:
+        shards = [(0, wl["n"])]
+    a, b = shards[rank]
+    n_loc = b - a
+    case = build_gpu_case("c5", 1, device, 2 if world > 1 else 1, seed0=900 + rank, n_cols=n_loc)
+    step, join, check = case["step"], (lambda: None), None
+    if world > 1:
+        ex = sharded.Exchange(device, 1 << 20)
+        r0 = case["spec"]["r"]
+        units_all = linear.topk_units(wl["n"])
+        recs = [ex.tensor([1, 1, units_all, r0.shape[-1]], r0.dtype) for _ in range(2)]
+        specs = [{"r": r, "k": 8, "rows": 1, "slot0": a // 2048, "base": a, "n": n_loc, "write_y": False} for r in recs]
+        plain = case["step"]
+        case["exchanged_records"] = recs
+
+        def step(i):  # noqa: F811
+            return plain(i, spec_t=specs[i % 2], exchange=ex)
+
+        def join():  # noqa: F811
+            ex.wait_all(linear.status_word(device))
+
+        check = check_exchange("c5", case, step, join, device, world, rank, 1, n_loc, a, wl["n"], True, shards)
+    ms, reps, _ = timed_graph(step, join, steps, 5, world, device, min_s=0.2)
+    linear.check_status(device)
+    out = {"workload": f"c5: {wl['what']}", "us_per_call": ms * 1e3 / steps, "columns_per_rank": n_loc, "steps": steps,
+           "value": wl["k"] * wl["n"] * BYTES_PER_WEIGHT[wl["fmt"]] / (ms * 1e-3 / steps) / 1e9, "unit": "GB/s",
+           "launches_per_step": 2}
+    if check is not None:
+        out["exchange_check"] = check
+    del case
+    torch.cuda.empty_cache()
+    return out
 
 
 def finish(world):

@@ -1110,9 +1110,8 @@ int launch_rows(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
     // (p.x_smem: the one row of x fits beside the ring in shared memory, which the one-row instantiations rely on)
     if (p.M == 1 && p.x_smem && !p.topk_k && !p.npeers) return launch_one<FMT, 1, 16, true, true, KWHOLE>(p, grid, smem, st);
     if (p.M == 1 && p.x_smem) return launch_one<FMT, 1, 16, true, false, KWHOLE>(p, grid, smem, st);
-    if (p.M <= 8) return launch_one<FMT, 1, 16, false, false, KWHOLE>(p, grid, smem, st);
-    if (p.M <= 16) return launch_one<FMT, 2, TKD_STREAM_WARPS_16ROWS, false, false, KWHOLE>(p, grid, smem, st);
-    return launch_one<FMT, 4, TKD_STREAM_WARPS_32ROWS, false, false, KWHOLE>(p, grid, smem, st);
+    // (9 to 32 rows run tkd_stream_tc_kernel: the caller never gets here with them)
+    return launch_one<FMT, 1, 16, false, false, KWHOLE>(p, grid, smem, st);
 }
 
 template <int FMT>
