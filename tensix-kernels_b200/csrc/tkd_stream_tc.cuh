@@ -7,19 +7,24 @@
 // decoded into bf16 tiles in shared memory once, whatever the row count, and one thread issues tcgen05.mma on them with
 // the accumulators in tensor memory:
 //
-//   warp 0         producer (one lane): the same ring of packed-weight chunks as tkd_stream_kernel, one bulk copy a stage
-//   warps 1-16     decode warps: warp (group g, half h) turns its 16 columns' share of a chunk into bf16 (code times
-//                  2^e', one multiply per two weights: every block-float value is a bf16 value) and stores it into an
-//   warps 17-20    output warps (thread = panel column = tensor-memory lane): read a slice's sums with tcgen05.ld, keep
+//   warps 4-19     decode warps: warp (group g, half h) turns its 16 columns' share of a chunk into bf16 (code times
+//                  2^e', one multiply per two weights: every block-float value is a bf16 value) and writes it straight
+//                  into TENSOR MEMORY with tcgen05.st.16x256b, whose thread layout is the mma A fragment's the stream is
+//                  packed for (thread (g, t): rows g and g + 8, two 32-bit columns): the A operand of the MMAs is read
+//                  from tensor memory, never from shared memory. (A first version stored the A tiles in shared memory:
+//                  32 KB written and 32 KB read by the tensor core per 17 KB of stream made the shared-memory
+//                  bandwidth the bound, at 3 TB/s.) A warp owns the tensor-memory lanes of its 16 columns (its
+//                  number mod 4 is their quarter). A block of 16 k as the MMA sees it is this layout's: position
+//                  4 t + r holds k = 8 t + 4 jj + r of a block of 32 k; the activations are laid out to match.
+//                  The same warps write the tile of activations a unit is multiplied by (32 rows x 64 k, rows past M
+//                  zero, K-major with the 128-byte swizzle, in that order of k) into shared memory: each lane loads
+//                  its 16 bytes of the NEXT chunk's tiles into registers while it decodes this chunk (they come from
+//                  L2, a microsecond away).
+//   warps 20-23    output warps (thread = panel column = tensor-memory lane): read a slice's sums with tcgen05.ld, keep
 //                  the running sums in shared memory, and from there on do what tkd_stream_kernel's output warps do
-//                  A tile: 128 columns x 64 k, K-major, 128-byte swizzle, 16 KB. Beside it in the same slot goes the
-//                  tile of activations it is multiplied by (32 rows x 64 k, rows past M zero, 4 KB): the warps that
-//                  write an A tile share its 256 16-byte pieces out, each lane loading its pieces of the NEXT chunk's
-//                  tiles into registers while it decodes this chunk (they come from L2, a microsecond away) and
-//                  storing them with the A tile. (A loader warp with cp.async was tried first: the proxy fence it
-//                  needs before the tensor core may read waits for ALL its copies in flight, which serialised them.)
-//   warp 21        one lane issues the MMAs: D[128 columns, 32 rows] += A tile x (x tile)^T, 4 x (K = 16) a tile,
-//                  tcgen05.commit onto the slot's "empty" barrier and, at a slice's end, onto the accumulator's "full"
+//   warp 1         producer (one lane issues): the same ring of packed-weight chunks as tkd_stream_kernel
+//   warp 0         one lane issues the MMAs: D[128 columns, 32 rows] += A (tensor memory) x (x tile)^T, 4 x (K = 16) a
+//                  tile, tcgen05.commit onto the unit's "empty" barrier and, at a slice's end, the accumulators' "full"
 //
 // A slice's sum is accumulated from zero in tensor memory, in FOUR accumulators of 32 columns: the j-th block of 16 k
 // of every tile goes to accumulator j, because an MMA that adds to the accumulator of the MMA before it waits for it
@@ -34,11 +39,15 @@
 
 namespace {
 
-constexpr int kTcSlots = 2;          // operand slots, each a unit of two tiles: [A 0][A 1][x 0][x 1]
-constexpr int kTcATile = 128 * 128;  // bytes: 128 columns x 64 k of bf16
-constexpr int kTcXTile = 32 * 128;   // bytes: 32 rows x 64 k of bf16
-constexpr int kTcSlot = 2 * (kTcATile + kTcXTile);
-constexpr int kTcWarps = 1 + 16 + 4 + 1;
+constexpr int kTcSlots = 3;          // operand slots, each a unit of two tiles of 64 k
+constexpr int kTcXTile = 32 * 128;   // bytes of an x tile in shared memory: 32 rows x 64 k of bf16
+constexpr int kTcSlot = 2 * kTcXTile;  // ... of a slot's two x tiles
+constexpr int kTcACols = 32;         // tensor-memory columns of an A tile: 128 lanes x 64 k of bf16, two to a column
+constexpr int kTcAcc0 = 0, kTcA0 = 256;  // tensor-memory columns: two sets of four accumulators of 32, then the A slots
+// Warps: 0 the MMA issuer, 1 the producer, 2-3 idle, 4-19 decode, 20-23 output. The MMA issuer is the warp with the
+// lowest number on purpose: the schedulers favour older warps, and as the last warp of the CTA it got an issue slot
+// every twenty cycles beside four decode warps that are always ready (its unit of eight MMAs took 770 ns).
+constexpr int kTcWarps = 24, kTcMmaWarp = 0, kTcProducerWarp = 1, kTcDecodeWarp0 = 4, kTcOutputWarp0 = 20;
 constexpr int kTcMP = 40;            // floats per column in tbuf (32 rows, padded)
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -57,16 +66,16 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
 // 16 = 0), N = 32 (bits 17-22 = N / 8), M = 128 (bits 24-28 = M / 16).
 constexpr uint32_t kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
 
-// (the descriptors as their 32-bit halves: the issuing thread's own instructions are its cost, a tile's four MMAs
-// leave it ~150 cycles, and moving a descriptor on is then one 32-bit add instead of a 64-bit one)
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t alo, uint32_t blo, uint32_t hi, uint32_t accumulate) {
+// D (tensor memory) (+)= A (tensor memory) x B (shared memory, by descriptor). The descriptor comes as its 32-bit
+// halves: the issuing thread's own instructions are its cost (a unit's eight MMAs leave it ~40 cycles each), and
+// moving a descriptor on is then one 32-bit add instead of a 64-bit one.
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_tmem, uint32_t blo, uint32_t bhi, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
         "setp.ne.b32 p, %5, 0;\n\t"
-        "mov.b64 da, {%1, %3};\n\t"
         "mov.b64 db, {%2, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
-        ::"r"(d_tmem), "r"(alo), "r"(blo), "r"(hi), "r"(kTcIdesc), "r"(accumulate)
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(blo), "r"(bhi), "r"(kTcIdesc), "r"(accumulate)
         : "memory");
 }
 // the barrier gets one arrival once every MMA issued so far by this thread has completed
@@ -129,9 +138,10 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
     const int64_t nitems = i1 - i0;
     auto item_at = [&](int64_t j) { return j < lead ? tail0 + j : i0 + (j - lead); };
 
-    // tensor memory: 256 columns (two sets of four accumulators of 32), allocated and freed by warp 21
-    if (warp == 21) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u)
+    // tensor memory: all 512 columns (two sets of four accumulators of 32, three A slots of 64), allocated and freed by
+    // the MMA warp
+    if (warp == kTcMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -140,7 +150,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
     tc_fence_after();
     const uint32_t tmem0 = *tmem_slot;
 
-    if (warp == 0) {
+    if (warp == kTcProducerWarp) {
         // ---------------------------------------------------------------- producer (as in tkd_stream_kernel; the whole
         // warp walks the loop and one lane issues: a warp whose other lanes wait at the kernel's final barrier while one
         // lane works runs that lane at a fraction of its speed)
@@ -194,22 +204,18 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                 }
             }
         }
-    } else if (warp <= SW) {
+    } else if (warp >= kTcDecodeWarp0 && warp < kTcDecodeWarp0 + SW) {
         // ---------------------------------------------------------------- decode warps
         asm volatile("griddepcontrol.wait;" ::: "memory");  // (x may be the output of the kernel before this one)
-        const int cw = warp - 1;
-        const int g8 = cw & 7, h = cw >> 3;
+        // (a warp may touch the tensor-memory lanes 32 (warp % 4) .. + 31 only: its group's 16 columns are among them)
+        const int cw = warp - kTcDecodeWarp0;
+        const int g8 = 2 * (cw & 3) + ((cw >> 2) & 1), h = cw >> 3;
         const int g = lane >> 2, t = lane & 3;
         constexpr int EXPB = FMT == TKD_BFP4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
         const uint2 sh = make_uint2(p.mul16, p.mul128);
         const uint32_t ring_a = smem_u32(ring), hdr_a = smem_u32(hdr);
-        // This lane's two rows of an A tile, for panel columns 16 g8 + g and + 8: row groups 2 g8 and 2 g8 + 1, and inside
-        // the group row pg = g's bits rotated (g >> 1 | (g & 1) << 2), not g: the eight lanes a 16-byte store is served
-        // for together are two g (2q, 2q + 1) x four t, and the swizzle puts piece c of row r at c ^ r; with rows 2q and
-        // 2q + 1 the two g's pieces fall on the same four bank groups, with rows q and q + 4 on all eight. The output
-        // warps undo the permutation (tensor-memory lane -> column).
-        const int pg = (g >> 1) | ((g & 1) << 2);
-        const uint32_t arow = (uint32_t)(2 * g8) * 1024u + (uint32_t)pg * 128u;
+        // the tensor-memory address of this warp's 16 lanes (panel columns 16 g8 .. + 15) at the first A column
+        const uint32_t alane = tmem0 + ((uint32_t)(16 * g8) << 16) + kTcA0;
         uint32_t slot = 0, phase = 0, useq = 0;
         // This lane's pieces of the x tiles: tile i of this warp's tiles of a chunk (bfloat4_b: the tiles of its half,
         // 32 pieces a warp; else every tile, 16 pieces a warp on its first 16 lanes), piece = (row, 16 bytes of the row).
@@ -218,7 +224,12 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
         const bool xmine = FMT == TKD_BFP4 || lane < 16;
         const int xr_ = xe >> 3, xc_ = xe & 7;
         const uint16_t* const xrow = p.x + (int64_t)min(xr_, M - 1) * p.ldx + 8 * xc_;
-        const uint32_t xdst = 2 * kTcATile + xr_ * 128 + ((xc_ ^ (xr_ & 7)) << 4);
+        // This lane's 16 bytes (8 k of one row) go to two places of the row's 128 bytes, 8 bytes each: k 0-3 to the block of
+        // 16 k with jj = 0 of its block of 32 k, k 4-7 to the one with jj = 1, both at position 4 t (t = the piece's number
+        // within the block of 32 k); then the swizzle (16-byte piece ^ row).
+        const uint32_t xo0 = 64 * (xc_ >> 2) + 8 * (xc_ & 3), xo1 = xo0 + 32;
+        const uint32_t xdst0 = xr_ * 128 + ((((xo0 >> 4) ^ (xr_ & 7)) << 4) | (xo0 & 15));
+        const uint32_t xdst1 = xr_ * 128 + ((((xo1 >> 4) ^ (xr_ & 7)) << 4) | (xo1 & 15));
         auto load_x = [&](uint4 (&v)[XT], int k0) {
 #pragma unroll
             for (int i = 0; i < XT; ++i) {
@@ -244,21 +255,25 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
             // time): the slot is waited for, the tiles decoded and stored, then one proxy fence and one arrival. (The
             // hand-over costs both sides a fixed time per barrier, the MMA warp most of all: a unit of two tiles halves it.)
             auto tile_of = [&](int i) { return FMT == TKD_BFP4 ? 2 * i + h : i; };
-            // tile i of this warp's tiles of the chunk into place `sub` (0, 1) of the unit at shared-memory address sb
-            auto do_tile = [&](int i, uint32_t sb, int sub) {
+            // tile i of this warp's tiles of the chunk into place `sub` (0, 1) of a unit: the A part into tensor memory
+            // at column ta (the unit's first), the x part into shared memory at sb
+            auto st_a = [&](uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+                // rows g (r0, r1) and g + 8 (r2, r3) of this warp's 16 lanes, 32-bit columns 2 t and 2 t + 1 of the block
+                asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r0), "r"(r1),
+                             "r"(r2), "r"(r3)
+                             : "memory");
+            };
+            auto do_tile = [&](int i, uint32_t sb, uint32_t ta, int sub) {
                 const int ti = tile_of(i);
                 const int sa = FMT == TKD_BFP4 ? ti : 2 * ti + h;  // this warp's super-atom of the tile
                 if (sa < nsa) {
-                    const uint32_t ab = sb + sub * kTcATile + arow;
                     const uint32_t sab = gb + sa * F::SAB;
+                    // (a tile is four blocks of 16 k, 8 columns each: block 2 (block of 32 k) + jj)
+                    const uint32_t tb = ta + sub * kTcACols + (FMT == TKD_BFP4 ? 0 : 16 * h);
                     if constexpr (FMT == TKD_BF16) {
                         const uint4 a = lds128(sab + lane * 16), b = lds128(sab + 512 + lane * 16);
-                        const uint32_t cc = (uint32_t)(((4 * h + t) ^ pg) << 4);
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ab + cc), "r"(a.x), "r"(a.z), "r"(b.x), "r"(b.z)
-                                     : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ab + 1024 + cc), "r"(a.y), "r"(a.w), "r"(b.y),
-                                     "r"(b.w)
-                                     : "memory");
+                        st_a(tb, a.x, a.z, a.y, a.w);
+                        st_a(tb + 8, b.x, b.z, b.y, b.w);
                     } else {
                         uint32_t cwd[4], ewd[4];
                         if constexpr (FMT == TKD_BFP8) {
@@ -271,10 +286,8 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                             cwd[0] = cv.x, cwd[1] = cv.y, cwd[2] = cv.z, cwd[3] = cv.w;
                             ewd[0] = ev.x, ewd[1] = ev.y, ewd[2] = ev.z, ewd[3] = ev.w;
                         }
-                        // one k32 block (bfloat8_b: the super-atom; bfloat4_b: each of its two) -> 8 k of two columns
 #pragma unroll
                         for (int q = 0; q < F::XB; ++q) {
-                            uint32_t lo[4], hi[4];  // columns g and g + 8: k pairs (0,1) (2,3) (4,5) (6,7) of this lane's 8
 #pragma unroll
                             for (int jj = 0; jj < 2; ++jj) {
                                 uint32_t a0, a1, a2, a3, s0, s1;
@@ -290,25 +303,18 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                                     a2 = w1 & TKD_MASK_BFP8, a3 = rot_and<8>(w1, TKD_MASK_BFP8);
                                     s0 = ew & 0x7F807F80u, s1 = rot_and<8>(ew, 0x7F807F80u);
                                 }
-                                lo[2 * jj] = mul_bf16x2(a0, s0), lo[2 * jj + 1] = mul_bf16x2(a2, s1);
-                                hi[2 * jj] = mul_bf16x2(a1, s0), hi[2 * jj + 1] = mul_bf16x2(a3, s1);
+                                // (the code times 2^e': the weight itself, in units the output stage knows)
+                                st_a(tb + 16 * q + 8 * jj, mul_bf16x2(a0, s0), mul_bf16x2(a2, s1), mul_bf16x2(a1, s0),
+                                     mul_bf16x2(a3, s1));
                             }
-                            const int c16 = FMT == TKD_BFP4 ? 4 * q + t : 4 * h + t;  // the 16-byte piece of the tile's rows
-                            const uint32_t cc = (uint32_t)((c16 ^ pg) << 4);
-                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ab + cc), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]),
-                                         "r"(lo[3])
-                                         : "memory");
-                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ab + 1024 + cc), "r"(hi[0]), "r"(hi[1]),
-                                         "r"(hi[2]), "r"(hi[3])
-                                         : "memory");
                         }
                     }
                 }
                 if (xmine) {
                     const uint4 v = xcur[i];
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sb + sub * kTcXTile + xdst), "r"(v.x), "r"(v.y),
-                                 "r"(v.z), "r"(v.w)
-                                 : "memory");
+                    const uint32_t xb = sb + sub * kTcXTile;
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(xb + xdst0), "r"(v.x), "r"(v.y) : "memory");
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(xb + xdst1), "r"(v.z), "r"(v.w) : "memory");
                 }
             };
             constexpr int UPC = FMT == TKD_BFP4 ? 4 : XT / 2;  // units of a whole chunk
@@ -319,14 +325,16 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                 const uint32_t us = useq + u, ps = us % kTcSlots;
                 ok = mbar_wait(aempty0 + 8 * ps, ((us / kTcSlots) & 1) ^ 1, p.status);
                 if (!ok) break;
-                const uint32_t sb = ops0 + ps * kTcSlot;
+                const uint32_t sb = ops0 + ps * kTcSlot, ta = alane + ps * 2 * kTcACols;
                 if constexpr (FMT == TKD_BFP4) {
-                    if (2 * u + h < ntiles) do_tile(u, sb, h);
+                    if (2 * u + h < ntiles) do_tile(u, sb, ta, h);
                 } else {
-                    do_tile(2 * u, sb, 0);
-                    if (2 * u + 1 < ntiles) do_tile(2 * u + 1, sb, 1);
+                    do_tile(2 * u, sb, ta, 0);
+                    if (2 * u + 1 < ntiles) do_tile(2 * u + 1, sb, ta, 1);
                 }
-                fence_proxy_async();  // this lane's stores, for the tensor core's reads
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");  // this warp's tensor-memory stores are done
+                tc_fence_before();
+                fence_proxy_async();  // this lane's shared-memory stores, for the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(afull0 + 8 * ps);
             }
@@ -339,17 +347,17 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
             if (++slot == (uint32_t)nst) slot = 0, phase ^= 1;
             if (hd.x & ST_END) break;
         }
-    } else if (warp == 21) {
+    } else if (warp == kTcMmaWarp) {
         // ---------------------------------------------------------------- the MMA issuer (the warp walks the loop, one
         // lane issues)
         {
             Cursor c;
             uint32_t us = 0;
             bool ok = true;
-            // the descriptors of slot 0's tiles as 32-bit halves (the high halves are equal; a slot further on is
-            // kTcSlot / 16 more in the low half, a block of 16 k is 2 more)
-            const uint64_t ad0 = tc_desc(ops0), bd0 = tc_desc(ops0 + 2 * kTcATile);
-            const uint32_t dhi = (uint32_t)(ad0 >> 32), alo0 = (uint32_t)ad0, blo0 = (uint32_t)bd0;
+            // the descriptor of slot 0's first x tile as 32-bit halves (a slot further on is kTcSlot / 16 more in the low
+            // half, a tile kTcXTile / 16, a block of 16 k 2 more); the A operand: tensor-memory columns, 8 a block
+            const uint64_t bd0 = tc_desc(ops0);
+            const uint32_t dhi = (uint32_t)(bd0 >> 32), blo0 = (uint32_t)bd0, alo0 = tmem0 + kTcA0;
             for (int64_t j = 0; j < nitems && ok; ++j) {
                 if (j == 0 || j == lead)
                     cursor_init(c, p, item_at(j));
@@ -362,7 +370,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                 ok = mbar_wait_parked(accempty0 + 8 * buf, (((uint32_t)j >> 1) & 1) ^ 1, p.status);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d = tmem0 + buf * 128;
+                const uint32_t d = tmem0 + kTcAcc0 + buf * 128;
                 uint32_t acc = 0;
                 for (int ch = 0; ch < nch && ok; ++ch) {
                     int kleft = min(CK, kv - ch * CK);  // k of this chunk not yet multiplied
@@ -370,24 +378,25 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                         const uint32_t ps = us % kTcSlots;
                         ok = mbar_wait(afull0 + 8 * ps, (us / kTcSlots) & 1, p.status);
                         if (!ok) break;
+                        tc_fence_after();  // (the decode warps' tensor-memory stores, completed before they arrived)
                         if (lane == 0) {
-                            uint32_t al = alo0 + ps * (kTcSlot >> 4), bl = blo0 + ps * (kTcSlot >> 4);
+                            uint32_t al = alo0 + ps * 2 * kTcACols, bl = blo0 + ps * (kTcSlot >> 4);
                             if (kleft >= 128) {
                                 // (a whole unit: two tiles of four blocks of 16 k; block j of a tile to accumulator j)
                                 tc_mma(d, al, bl, dhi, acc);
-                                tc_mma(d + 32, al + 2, bl + 2, dhi, acc);
-                                tc_mma(d + 64, al + 4, bl + 4, dhi, acc);
-                                tc_mma(d + 96, al + 6, bl + 6, dhi, acc);
-                                al += kTcATile >> 4, bl += kTcXTile >> 4;
+                                tc_mma(d + 32, al + 8, bl + 2, dhi, acc);
+                                tc_mma(d + 64, al + 16, bl + 4, dhi, acc);
+                                tc_mma(d + 96, al + 24, bl + 6, dhi, acc);
+                                al += kTcACols, bl += kTcXTile >> 4;
                                 tc_mma(d, al, bl, dhi, 1);
-                                tc_mma(d + 32, al + 2, bl + 2, dhi, 1);
-                                tc_mma(d + 64, al + 4, bl + 4, dhi, 1);
-                                tc_mma(d + 96, al + 6, bl + 6, dhi, 1);
+                                tc_mma(d + 32, al + 8, bl + 2, dhi, 1);
+                                tc_mma(d + 64, al + 16, bl + 4, dhi, 1);
+                                tc_mma(d + 96, al + 24, bl + 6, dhi, 1);
                             } else {
                                 const int nb = (kleft + 15) >> 4;  // a short last unit of K
                                 for (int b = 0; b < nb; ++b) {
-                                    if (b == 4) al += (kTcATile >> 4) - 8, bl += (kTcXTile >> 4) - 8;
-                                    tc_mma(d + 32 * (b & 3), al + 2 * b, bl + 2 * b, dhi, b >= 4 ? 1u : acc);
+                                    if (b == 4) al += kTcACols - 32, bl += (kTcXTile >> 4) - 8;
+                                    tc_mma(d + 32 * (b & 3), al + 8 * b, bl + 2 * b, dhi, b >= 4 ? 1u : acc);
                                 }
                             }
                             tc_commit(aempty0 + 8 * ps);
@@ -401,13 +410,11 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                 __syncwarp();
             }
         }
-    } else {
-        // ---------------------------------------------------------------- output warps (warps 17-20)
+    } else if (warp >= kTcOutputWarp0) {
+        // ---------------------------------------------------------------- output warps
         asm volatile("griddepcontrol.wait;" ::: "memory");
         const int ow = warp & 3;          // the quarter of the tensor memory's lanes this warp may read
-        // the panel column this thread owns: its tensor-memory lane is A-tile row ow * 32 + lane, whose row group holds
-        // eight columns in the decode warps' permuted order
-        const int et = (ow * 32 + (lane & 24)) + (((lane & 3) << 1) | ((lane >> 2) & 1));
+        const int et = ow * 32 + lane;    // the panel column (= A row = tensor-memory lane) this thread owns
         Cursor c;
         bool ok = true;
         float* const trow = tbuf + (size_t)et * MP;
@@ -441,7 +448,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                 // shorter than 64 k), sixteen rows at a time
                 const int kv = min(p.ks, K - c.slice * p.ks);
                 const int nacc = min(4, (kv + 15) / 16);
-                const uint32_t ta = tmem0 + ((uint32_t)(ow * 32) << 16) + buf * 128;
+                const uint32_t ta = tmem0 + ((uint32_t)(ow * 32) << 16) + kTcAcc0 + buf * 128;
                 auto ld16 = [&](uint32_t addr, float (&o)[16], bool add) {
                     uint32_t r[16];
                     asm volatile(
@@ -609,9 +616,9 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
     // goes back
     tc_fence_before();
     __syncthreads();
-    if (warp == 21) {
+    if (warp == kTcMmaWarp) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem0), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem0), "r"(512u) : "memory");
     }
 }
 
