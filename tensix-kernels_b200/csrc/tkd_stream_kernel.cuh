@@ -420,17 +420,20 @@ __device__ __forceinline__ void topk_records(const TkdParams& p, const Cursor& c
 }
 
 // The end of an exchanged call, run by every output warp after its last panel.
-__device__ __forceinline__ void exchange_done(const TkdParams& p, int lane, int npeers) {
-    // Exchange: every output warp counts itself in once its stores are ordered GPU-wide (a cheap fence). The
-    // warp that counts last orders all of them system-wide with the call's ONE system fence (system fences
-    // serialise across the GPU: one per warp cost this kernel a third of its run), numbers the call and writes
-    // that number to this rank's word on every rank. (No CTA barrier: the warps may have left the loop at
-    // different points.)
+__device__ __forceinline__ void exchange_done(const TkdParams& p, int lane, int npeers, volatile int* sflag) {
+    // Exchange: every output warp orders its stores GPU-wide (a cheap fence) and counts itself in, first within its
+    // CTA (a shared-memory counter, sflag[1]); the CTA's last warp counts the CTA in on the call's one global counter
+    // (148 atomics on one address instead of 592: they arrive together at the kernel's end and serialise). The CTA
+    // that counts last orders everything system-wide with the call's ONE system fence (system fences serialise
+    // across the GPU: one per warp cost this kernel a third of its run), numbers the call and writes that number to
+    // this rank's word on every rank. (No CTA barrier: the warps may have left the loop at different points.)
     __syncwarp();
     if (lane == 0) {
         __threadfence();
+        if (atomicAdd_block(const_cast<int*>(sflag) + 1, 1) != 3) return;
+        __threadfence();
         const int old = atomicAdd(p.grid_counter, 1);
-        if (old + 1 == 4 * (int)gridDim.x) {
+        if (old + 1 == (int)gridDim.x) {
             *p.grid_counter = 0;
             const uint32_t seq = p.flags[TKD_FLAG_SEQ] + 1;
             p.flags[TKD_FLAG_SEQ] = seq;
@@ -487,7 +490,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             mbar_init(pempty0 + 8 * s, 4);
             mbar_init(xfull0 + 8 * s, SW * 32);
         }
-        sflag[0] = 0;
+        sflag[0] = sflag[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -1071,7 +1074,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             topk_records(p, c, sg, et, ow, lane, tbuf, sflag, y16, topk_k, npeers);
         
         }
-        if (npeers) exchange_done(p, lane, npeers);
+        if (npeers) exchange_done(p, lane, npeers, sflag);
     }
 }
 

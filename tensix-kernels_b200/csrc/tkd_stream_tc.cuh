@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
             mbar_init(accfull0 + 8 * s, 1);
             mbar_init(accempty0 + 8 * s, 4);
         }
-        sflag[0] = 0;
+        sflag[0] = sflag[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -610,7 +610,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
             if (topk_k == 0) continue;
             topk_records(p, c, sg, et, ow, lane, tbuf, sflag, y16, topk_k, npeers);
         }
-        if (npeers) exchange_done(p, lane, npeers);
+        if (npeers) exchange_done(p, lane, npeers, sflag);
     }
     // ---- the end: everyone is here (a role whose wait gave up falls through to this point too), and the tensor memory
     // goes back

@@ -91,13 +91,16 @@ def read(path, meta, rebuild=False):
 
 
 def weight_meta(dtype, k, n, col_scale, extra=None):
+    """What a cache directory must say to be taken: the weight asked for and the library's stream layout version
+    (tkd_layout_version: it changes with every change of the packed stream's bit layout, which the C-ABI version and
+    the checksums would not notice)."""
     return {"format": _NAMES[dtype], "k": int(k), "n": int(n), "col_scale": bool(col_scale),
-            "layout_version": int(_tkd.lib().tkd_version()), **(extra or {})}
+            "layout_version": int(_tkd.lib().tkd_layout_version()), **(extra or {})}
 
 
 def save_weight(path, tw, ts=None, col_scale=False, extra=None):
     """A packed weight (native_weight's tw and, optionally, its scales ts) into the directory `path`."""
-    assert not tw.wide, "dense_reader: a wide weight (refused by matmul) is not cached"
+    assert not tw.wide, "dense_reader: a wide weight (held as a bf16 stream) is not cached"
     arrays = {"stream": tw.t.cpu().numpy(), "emax": tw.emax.cpu().numpy() if tw.emax is not None else None,
               "scale": ts.t.reshape(-1).view(torch.int16).cpu().numpy() if ts is not None else None}
     write(path, weight_meta(tw.dtype, tw.k, tw.n, col_scale, extra), arrays)

@@ -312,22 +312,30 @@ def is_block_list(w):
 def block_entries(w):
     """A block list as [(gate, up or None, col0_tiles)], checked: two to four entries, all plain weights or all
     pairs, of one K, dtype and bank count. (linear.py:533-556)"""
-    out = []
-    for item in w:
-        assert isinstance(item, (tuple, list)) and len(item) == 2, f"dense_reader: a block is (weight, col0_tiles): {item!r}"
-        wt, c0 = item
-        gate, up = (wt[0], wt[1]) if isinstance(wt, (tuple, list)) else (wt, None)
-        assert isinstance(c0, int) and c0 >= 0, f"dense_reader: col0_tiles {c0!r}"
-        if up is not None:
-            assert up.dtype == gate.dtype and tuple(up.padded_shape) == tuple(gate.padded_shape), "gate and up differ"
-            assert str(up.memory_config()) == str(gate.memory_config()), "dense_reader: gate and up differ"
-        out.append((gate, up, c0))
-    assert 2 <= len(out) <= 4, f"dense_reader: {len(out)} blocks (2 to 4; one weight goes in on its own)"
-    assert len({up is None for _, up, _ in out}) == 1, "dense_reader: blocks all plain or all (gate, up) pairs"
-    assert all(is_dram_sharded(g) for g, _, _ in out), "dense_reader: blocks are DRAM-sharded"
-    kinds = {(g.shape[-2], g.dtype, g.memory_config().shard_spec.num_cores()) for g, _, _ in out}
-    assert len(kinds) == 1, "dense_reader: blocks of one K, dtype, bank count, shard grid and orientation"
-    return out
+    def split(entry):
+        ok = isinstance(entry, (list, tuple)) and len(entry) == 2
+        assert ok, f"dense_reader: a block is (weight, col0_tiles): {entry!r}"
+        weight, col0_tiles = entry
+        assert type(col0_tiles) is int and col0_tiles >= 0, f"dense_reader: col0_tiles {col0_tiles!r}"
+        if not isinstance(weight, (list, tuple)):
+            return weight, None, col0_tiles
+        gate, up = weight
+        alike = (up.dtype, tuple(up.padded_shape), str(up.memory_config())) == (
+            gate.dtype, tuple(gate.padded_shape), str(gate.memory_config()))
+        assert alike, "dense_reader: gate and up differ"
+        return gate, up, col0_tiles
+
+    entries = [split(e) for e in w]
+    assert len(entries) in (2, 3, 4), f"dense_reader: {len(entries)} blocks (2 to 4; one weight goes in on its own)"
+    pairs = [up is not None for _, up, _ in entries]
+    assert all(pairs) or not any(pairs), "dense_reader: blocks all plain or all (gate, up) pairs"
+    for gate, _, _ in entries:
+        assert is_dram_sharded(gate), "dense_reader: blocks are DRAM-sharded"
+    first = entries[0][0]
+    same = all((g.shape[-2], g.dtype, g.memory_config().shard_spec.num_cores())
+               == (first.shape[-2], first.dtype, first.memory_config().shard_spec.num_cores()) for g, _, _ in entries)
+    assert same, "dense_reader: blocks of one K, dtype, bank count, shard grid and orientation"
+    return entries
 
 
 def _one_stream_format(entries):
@@ -412,16 +420,13 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     if isinstance(w, (list, tuple)):
         assert is_block_list(w), "dense_reader: w is one weight or a block list [(w | (gate, up), col0_tiles), ...]"
         entries = _one_stream_format(block_entries(w))
-        assert scale is None and topk is None and col0 == 0 and w_up is None, (
-            "dense_reader: a block list takes no scale, topk, col0 or w_up (each block carries its own col0_tiles)"
-        )
-        assert "residual" not in opts and not opts.get("out32"), "dense_reader: a block list: no residual or out32"
+        for what, given in (("scale", scale is not None), ("topk", topk is not None), ("col0", col0 != 0),
+                            ("w_up", w_up is not None), ("residual", "residual" in opts), ("out32", bool(opts.get("out32")))):
+            assert not given, (f"dense_reader: a block list takes no {what} (no scale, topk, col0, w_up, residual or out32:"
+                               " each block carries its own col0_tiles)")
         assert x.shape[-2] <= 32, "dense_reader: a block list is a decode call: up to 32 rows"
-        w, w_up, col0 = entries[0]
-        segs = tuple(entries[1:])
-        if w_up is not None:
-            opts = {**opts, "glu": True}
-        opts = {**opts, "blocks": tuple(g for g, _, _ in entries)}
+        (w, w_up, col0), segs = entries[0], tuple(entries[1:])
+        opts = {**opts, "blocks": tuple(g for g, _, _ in entries), **({"glu": True} if w_up is not None else {})}
     res_mode = opts.pop("residual_mode", "epilogue")
     assert res_mode in ("epilogue", "preload"), res_mode
     residual = opts.pop("residual", None)
@@ -436,23 +441,22 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     glu = bool(opts.get("glu", False))
     act = opts.pop("glu_act", 0)
     assert act in (0, 1) and (act == 0 or glu), "dense_reader: glu_act (0 silu, 1 gelu_tanh) needs glu"
-    if glu:
-        assert scale is None, "dense_reader: glu takes weights without scales"
+    assert not (glu and scale is not None), "dense_reader: glu takes weights without scales"
     assert col_scales is None or (glu and not segs), "dense_reader: col_scales go with a GLU over one weight or pair"
-    if scale is None:
-        opts = {**opts, "noscale": True}
-    else:
+    if scale is not None:
         assert scale.dtype == ttnn.bfloat16 and scale.memory_config().memory_layout == ttnn.TensorMemoryLayout.INTERLEAVED
+    extra = {"noscale": True} if scale is None else {}
     if max_banks is not None:
-        opts = {**opts, "max_banks": max_banks}
-    if w_up is not None:
-        assert glu, "dense_reader: w_up is the GLU's up weight (glu=True)"
-        assert w_up.dtype == w.dtype and tuple(w_up.padded_shape) == tuple(w.padded_shape)
-        assert str(w_up.memory_config()) == str(w.memory_config()), "dense_reader: gate and up differ"
-        opts = {**opts, "glu2": True}
-        N = w.shape[-1]
+        extra["max_banks"] = max_banks
+    N = w.shape[-1]
+    if w_up is None:
+        N = N // 2 if glu else N
     else:
-        N = w.shape[-1] // 2 if glu else w.shape[-1]
+        assert glu, "dense_reader: w_up is the GLU's up weight (glu=True)"
+        assert (w_up.dtype, tuple(w_up.padded_shape)) == (w.dtype, tuple(w.padded_shape)), "dense_reader: gate and up differ"
+        assert str(w_up.memory_config()) == str(w.memory_config()), "dense_reader: gate and up differ"
+        extra["glu2"] = True
+    opts = {**opts, **extra}
     M = x.shape[-2]
     if residual is not None:
         ext = out32 and residual.dtype == ttnn.float32  # (extension: a float32 residual into the float32 output)
@@ -687,31 +691,29 @@ def linear(x, w, scale, memory_config=None, activation=None, out_dtype=None, **o
     wide; or w is (gate, up), the output N wide). out_dtype ttnn.float32: out32. A block list for w: plain weights with
     activation None, (gate, up) pairs with "swiglu" or "geglu". opts go to matmul. (linear.py:1073-1124)"""
     shape = list(x.shape)
-    if out_dtype is not None and out_dtype != ttnn.bfloat16:
+    glu_kinds = {"swiglu": 0, "geglu": 1}
+    if out_dtype not in (None, ttnn.bfloat16):
         assert out_dtype == ttnn.float32, f"dense_reader.linear: out_dtype {out_dtype}"
         opts = {**opts, "out32": True}
     blocks = is_block_list(w)
     if blocks:
         pairs = isinstance(w[0][0], (tuple, list))
         assert activation != "silu", "dense_reader.linear: no silu after a block list"
-        takes = ("swiglu", "geglu") if pairs else (None,)
-        assert activation in takes, (
+        allowed = tuple(glu_kinds) if pairs else (None,)
+        assert activation in allowed, (
             f"dense_reader.linear: a block list of {'(gate, up) pairs' if pairs else 'plain weights'} takes activation"
-            f" {' or '.join(map(repr, takes))}, not {activation!r}"
+            f" {' or '.join(map(repr, allowed))}, not {activation!r}"
         )
-        if activation == "geglu":
+        if glu_kinds.get(activation):
             opts = {**opts, "glu_act": 1}
         n = max(TILE * c0 + (wt[0] if pairs else wt).shape[-1] for wt, c0 in w)
-    elif isinstance(w, (tuple, list)):
-        assert activation in ("swiglu", "geglu"), "dense_reader.linear: two weights are the GLU's gate and up"
-        w, w_up = w
-        opts = {**opts, "w_up": w_up}
-    if not blocks:
+    else:
+        if isinstance(w, (tuple, list)):
+            assert activation in glu_kinds, "dense_reader.linear: two weights are the GLU's gate and up"
+            w, opts = w[0], {**opts, "w_up": w[1]}
         n = w.shape[-1]
-        if activation in ("swiglu", "geglu"):
-            opts = {**opts, "glu": True}
-            if activation == "geglu":
-                opts["glu_act"] = 1
+        if activation in glu_kinds:
+            opts = {**opts, "glu": True, **({"glu_act": 1} if glu_kinds[activation] else {})}
             if opts.get("w_up") is None:
                 n //= 2
     x4 = x if len(shape) == 4 else ttnn.reshape(x, [1, 1, shape[-2], shape[-1]])

@@ -30,25 +30,28 @@ def _stream():
 
 def head_rows(device, weight):
     """The bf16 head [vocab, dim] (torch) as a row-major device tensor [1, 1, vocab, dim]. (head_pick.py:44-54)"""
-    vocab, dim = weight.shape
-    return ttnn.from_torch(weight.to(torch.bfloat16).reshape(1, 1, vocab, dim), dtype=ttnn.bfloat16,
-                           layout=ttnn.ROW_MAJOR_LAYOUT, device=device, memory_config=ttnn.DRAM_MEMORY_CONFIG)
+    table = weight.to(torch.bfloat16)[None, None]
+    return ttnn.from_torch(table, dtype=ttnn.bfloat16, layout=ttnn.ROW_MAJOR_LAYOUT, device=device,
+                           memory_config=ttnn.DRAM_MEMORY_CONFIG)
 
 
 def check_rows(rows_t, dim, vocab=None):
     """A bf16 head table pick can gather from: row-major bf16 [rows, dim] or [1, 1, rows, dim] in device memory, with at
     least `vocab` rows when that is given. (head_pick.py:57-73)"""
-    shape = tuple(rows_t.shape)
+    *lead, nrows, width = tuple(rows_t.shape)
     mc = rows_t.memory_config()
-    assert (
-        rows_t.dtype == ttnn.bfloat16
-        and rows_t.layout == ttnn.ROW_MAJOR_LAYOUT
-        and mc.memory_layout == ttnn.TensorMemoryLayout.INTERLEAVED
-        and mc.buffer_type == ttnn.BufferType.DRAM
-        and all(s == 1 for s in shape[:-2])
-        and shape[-1] == dim
-        and (vocab is None or shape[-2] >= vocab)
-    ), (shape, rows_t.dtype, rows_t.layout, str(mc), dim, vocab)
+    problems = [
+        what for what, bad in (
+            ("dtype bfloat16", rows_t.dtype != ttnn.bfloat16),
+            ("row-major layout", rows_t.layout != ttnn.ROW_MAJOR_LAYOUT),
+            ("interleaved device memory", mc.memory_layout != ttnn.TensorMemoryLayout.INTERLEAVED
+             or mc.buffer_type != ttnn.BufferType.DRAM),
+            ("leading dimensions of 1", any(d != 1 for d in lead)),
+            (f"rows of {dim}", width != dim),
+            (f"at least {vocab} rows", vocab is not None and nrows < vocab),
+        ) if bad
+    ]
+    assert not problems, f"head_pick: the head table needs {', '.join(problems)}: {tuple(rows_t.shape)} {rows_t.dtype} {mc}"
 
 
 def check_ids_out(t):

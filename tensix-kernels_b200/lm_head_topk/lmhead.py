@@ -50,91 +50,107 @@ class DeviceHead:
         device_pick=True is the records-only pick and token_map (a list, a tensor of ids, or head_pick.token_map's device
         tensor) maps the head's rows to token ids. l1x: accepted (the reference copies x into L1 once a call; the GPU
         reads x through its caches). opts go to linear.matmul."""
-        vocab, dim = weight.shape
-        chunks = len(blocks) if blocks is not None else chunks
-        step = vocab // chunks
-        assert step * chunks == vocab and step % 32 == 0, (vocab, chunks)
-        assert fmt in FORMATS, fmt
-        assert logits in ("bf16", "float32"), logits
-        self.round = logits == "bf16"
-        self.logits = logits
+        if fmt not in FORMATS:
+            raise AssertionError(f"lmhead: fmt {fmt!r} (one of {sorted(FORMATS)})")
+        if logits not in ("bf16", "float32"):
+            raise AssertionError(f"lmhead: logits {logits!r}")
+        self.device, self.fmt, self.k, self.top, self.opts = device, fmt, k, top, opts
+        self.vocab, self.dim = weight.shape
+        nblocks = chunks if blocks is None else len(blocks)
+        self.step, left = divmod(self.vocab, nblocks)
+        assert left == 0 and self.step % 32 == 0, (self.vocab, nblocks)
+        self.slots = linear.topk_units(self.step)  # records a block writes: one per unit of output columns
+        self.logits, self.round, self.l1x, self.valid = logits, logits == "bf16", l1x, valid
         self.device_pick = bool(device_pick)
-        self.l1x = l1x
-        self.rows_t, self.own_rows = None, False  # the bf16 head on the device, and whether it was made here
-        self.valid = valid
-        self.picks = {}    # rows -> the pick's output page
-        self.records_pick = not rescore and self.device_pick
-        self.tmap, self.own_tmap = None, False
-        assert token_map is None or self.records_pick, "lmhead: token_map is for rescore=False, device_pick=True"
-        self.slots = linear.topk_units(step)  # records per block: one per unit of output columns
-        self.device, self.fmt, self.step, self.k, self.opts = device, fmt, step, k, opts
-        self.vocab, self.dim, self.top = vocab, dim, top
-        self.results = {}  # rows -> the top-k result tensor
-        self.y = None      # the matmuls' placeholder output (never written)
-        self.host = None
-        if self.records_pick and token_map is not None:
-            if isinstance(token_map, ttnn.Tensor):
-                self.tmap = token_map
+        self.records_pick = self.device_pick and not rescore
+        # what calls keep from one to the next: result tensors and pick pages by row count, the placeholder output
+        self.results, self.picks, self.y = {}, {}, None
+        self.miss = 0  # rows whose best candidate by the device's logit lost the rescore
+        # the three ways to turn candidates into tokens
+        self.host = None                          # host rescore: the head in bf16 on the host
+        self.rows_t, self.own_rows = None, False  # device rescore: the bf16 head on the device (ours to free?)
+        self.tmap, self.own_tmap = None, False    # records-only pick: the optional token map (ours to free?)
+        if token_map is not None:
+            assert self.records_pick, "lmhead: token_map is for rescore=False, device_pick=True"
+            self._take_token_map(token_map)
+        if rescore:
+            if self.device_pick:
+                self._take_head_rows(weight, rows)
             else:
-                assert len(token_map) == vocab, (len(token_map), vocab)
-                self.tmap, self.own_tmap = head_pick.token_map(device, token_map), True
-        if rescore and self.device_pick:
-            assert 1 <= top <= 32, f"lmhead: the device pick rescores at most 32 candidates, top {top}"
-            if rows is not None:
-                head_pick.check_rows(rows, dim, vocab if valid is None else valid)
-                self.rows_t = rows
-            else:
-                self.rows_t, self.own_rows = head_pick.head_rows(device, weight), True
-        elif rescore:
-            self.host = weight.to(torch.bfloat16)
-        self.miss = 0  # rows whose device-best candidate was not the rescored best
-        if blocks is not None:
-            self.blocks = list(blocks)
+                self.host = weight.to(torch.bfloat16)
+        self.blocks = list(blocks) if blocks is not None else self._pack(weight)
+
+    def _take_token_map(self, token_map):
+        if isinstance(token_map, ttnn.Tensor):
+            self.tmap = token_map
             return
-        self.blocks = []
-        for a in range(0, vocab, step):
-            tw, ts = linear.native_weight(device, weight[a : a + step], FORMATS[fmt])
+        assert len(token_map) == self.vocab, (len(token_map), self.vocab)
+        self.tmap, self.own_tmap = head_pick.token_map(self.device, token_map), True
+
+    def _take_head_rows(self, weight, rows):
+        assert 1 <= self.top <= 32, f"lmhead: the device pick rescores at most 32 candidates, top {self.top}"
+        if rows is None:
+            self.rows_t, self.own_rows = head_pick.head_rows(self.device, weight), True
+        else:
+            head_pick.check_rows(rows, self.dim, self.valid if self.valid is not None else self.vocab)
+            self.rows_t = rows
+
+    def _pack(self, weight):
+        """The head's blocks as device weights with unit scales, in vocabulary order."""
+        made = []
+        for first in range(0, self.vocab, self.step):
+            tw, ts = linear.native_weight(self.device, weight[first : first + self.step], FORMATS[self.fmt])
             ttnn.deallocate(ts)
-            self.blocks.append((tw, None))  # unit scales
+            made.append((tw, None))
+        return made
+
+    def _result(self, rows):
+        if rows not in self.results:
+            self.results[rows] = linear.topk_result(self.device, len(self.blocks) * self.slots, rows, self.k)
+        return self.results[rows]
+
+    def _placeholder(self, x):
+        """The matmuls' output tensor: never written (write_y False), as tall as x."""
+        if self.y is not None and self.y.shape[-2] == x.shape[-2]:
+            return self.y
+        if self.y is not None:
+            ttnn.deallocate(self.y)
+        self.y = ttnn.allocate_tensor_on_device(ttnn.Shape([1, 1, x.shape[-2], self.step]), ttnn.bfloat16, ttnn.TILE_LAYOUT,
+                                                self.device, ttnn.DRAM_MEMORY_CONFIG)
+        return self.y
 
     def logits_topk(self, x, rows=1, ids_out=None):
         """The device part: per block the matmul that keeps each unit's best k of the first `rows` rows (no logits are
         written), then with device_pick the rescore and the pick. Returns the result tensor (block b's records at
         b * slots ..). Nothing is read back and the tensors are kept from call to call, so a CUDA graph can hold it.
         (lmhead.py:135-197)"""
-        assert 1 <= rows <= 16 and rows <= x.shape[-2], f"lmhead: 1 to 16 rows, at most x's ({rows})"
-        r = self.results.get(rows)
-        if r is None:
-            r = self.results[rows] = linear.topk_result(self.device, len(self.blocks) * self.slots, rows, self.k)
-        if self.y is None or self.y.shape[-2] != x.shape[-2]:
-            if self.y is not None:
-                ttnn.deallocate(self.y)
-            self.y = ttnn.allocate_tensor_on_device(ttnn.Shape([1, 1, x.shape[-2], self.step]), ttnn.bfloat16,
-                                                    ttnn.TILE_LAYOUT, self.device, ttnn.DRAM_MEMORY_CONFIG)
+        assert 1 <= rows <= min(16, x.shape[-2]), f"lmhead: 1 to 16 rows, at most x's ({rows})"
+        assert ids_out is None or self.rows_t is not None or self.records_pick, "lmhead: ids_out needs the device pick"
+        r, y = self._result(rows), self._placeholder(x)
         for b, (tw, ts) in enumerate(self.blocks):
-            spec = {"r": r, "k": self.k, "rows": rows, "slot0": b * self.slots, "base": b * self.step, "n": self.step,
-                    "write_y": False}
-            linear.matmul(x, tw, ts, topk=spec, out=self.y, **self.opts)
+            linear.matmul(x, tw, ts, out=y, **self.opts,
+                          topk={"r": r, "k": self.k, "rows": rows, "slot0": b * self.slots, "base": b * self.step,
+                                "n": self.step, "write_y": False})
+        page = self.picks.get(rows)
         if self.rows_t is not None:
-            self.picks[rows] = head_pick.pick(r, x, self.rows_t, rows, self.k, top=self.top, logits=self.logits,
-                                              out=self.picks.get(rows), valid=self.valid, ids_out=ids_out)
+            self.picks[rows] = head_pick.pick(r, x, self.rows_t, rows, self.k, top=self.top, logits=self.logits, out=page,
+                                              valid=self.valid, ids_out=ids_out)
         elif self.records_pick:
-            self.picks[rows] = head_pick.pick_records(r, rows, self.k, self.vocab if self.valid is None else self.valid,
-                                                      tmap=self.tmap, out=self.picks.get(rows), ids_out=ids_out)
-        assert ids_out is None or rows in self.picks, "lmhead: ids_out needs the device pick"
+            self.picks[rows] = head_pick.pick_records(r, rows, self.k, self.valid if self.valid is not None else self.vocab,
+                                                      tmap=self.tmap, out=page, ids_out=ids_out)
         return r
 
     def candidates(self, x, rows):
         """(values [rows, c] float, global ids [rows, c] long) of the device's candidates. (lmhead.py:199-202)"""
-        r = self.logits_topk(x, rows)
-        return linear.topk_records(r, rows, self.k)
+        return linear.topk_records(self.logits_topk(x, rows), rows, self.k)
 
     def rescore(self, xh, ids):
         """Exact logits of the candidates: x (bf16) times the bf16 weight rows, float32 sums, rounded to bf16 unless
         logits="float32". (lmhead.py:204-209)"""
-        w = self.host[ids.reshape(-1)].float().reshape(*ids.shape, self.dim)
-        z = torch.einsum("rd,rcd->rc", xh.float(), w)
-        return z.to(torch.bfloat16).float() if self.round else z
+        nrows, ncand = ids.shape
+        picked = self.host.index_select(0, ids.reshape(-1)).float().reshape(nrows, ncand, self.dim)
+        exact = torch.bmm(picked, xh.float().reshape(nrows, self.dim, 1)).reshape(nrows, ncand)
+        return exact.to(torch.bfloat16).float() if self.round else exact
 
     def __call__(self, x, rows=1):
         """Token ids [rows] (long) for the first `rows` rows of x [1, 1, >= rows, dim] bf16."""

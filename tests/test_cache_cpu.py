@@ -40,3 +40,18 @@ def test_write_read_and_refusals(tmp_path):
     (path / "meta.json").write_text("{")
     with pytest.raises(cache.PackCacheMismatch):
         cache.read(path, meta)
+
+
+def test_layout_version_is_part_of_the_key(tmp_path):
+    """A cache written by a library with another stream layout is refused: weight_meta carries tkd_layout_version
+    (not the C-ABI version), so a change of the packed stream's bit layout invalidates every cache."""
+    from common import ttnn_like as ttnn
+    from dense_reader import _tkd
+
+    meta = cache.weight_meta(ttnn.bfloat4_b, 64, 32, False)
+    assert meta["layout_version"] == _tkd.lib().tkd_layout_version() >= 3
+    path = tmp_path / "w"
+    cache.write(path, dict(meta, layout_version=meta["layout_version"] - 1),
+                {"stream": np.zeros(16, np.uint8), "emax": np.zeros(2, np.uint8), "scale": None})
+    with pytest.raises(cache.PackCacheMismatch, match="layout_version"):
+        cache.read(path, meta)

@@ -1,3 +1,7 @@
+# SPDX-License-Identifier: Apache-2.0
+# Copyright 2026 Xylolabs
+# Ported from XylolabsInc/tensix-kernels, dense_reader/tests/test_dense_reader.py (Apache-2.0): the test cases, shapes, seeds and bars are that
+# file's; the imports and the device API under them are this package's.
 """The reference's own dense_reader checks (its dense_reader/tests/test_dense_reader.py), same shapes, seeds and bars,
 against this package's API on a B200: y against x rounded to bf16 times the weight's own values read back, in float64
 (relative Frobenius error below 1 %, PCC above 0.9999; 0.1 % for the fp32 output), and bit for bit wherever two

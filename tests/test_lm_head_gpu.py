@@ -1,3 +1,7 @@
+# SPDX-License-Identifier: Apache-2.0
+# Copyright 2026 Xylolabs
+# Ported from XylolabsInc/tensix-kernels, lm_head_topk/tests/test_lm_head.py (Apache-2.0): the test cases, shapes, seeds and bars are that
+# file's; the imports and the device API under them are this package's.
 """The top-k LM head (lm_head_topk/lmhead.py, head_pick.py) against torch, case for case the reference's
 lm_head_topk/tests/test_lm_head.py: a random bf16 head [8192, 1024] as four bfloat4_b blocks and random x rows;
 - the records hold the block matmul's own bf16 logits at their ids, and each row's best k over the records are its best

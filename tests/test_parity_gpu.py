@@ -403,3 +403,59 @@ def test_launch_cache_survives_freed_weights(device):
         close_bf16(y2, orc.matmul_f64(ttnn.to_torch(x).reshape(2, k).float(), orc.native_values(w2, "bfp8")[0]))
         assert not torch.equal(y1, y2), addr
     linear.check_status(device)
+
+
+def test_pack_then_matmul_in_stream_order(device):
+    """Through the C-ABI: a weight packed and multiplied by on one stream with no synchronisation in between. The
+    matmul's first weight loads may start before the work ahead of it has finished (programmatic dependent launch)
+    unless the call says the weights are fresh (TkdMatmul.weights_fresh): with it, the result equals the synchronised
+    one bit for bit."""
+    import ctypes
+
+    from dense_reader import _tkd
+
+    L = _tkd.lib()
+    k, n, m = 4096, 2048, 2
+    g = torch.Generator().manual_seed(91)
+    npad = L.tkd_padded_cols(n)
+    src = [(torch.randn(k, n, generator=g) * 0.02).to(device.torch) for _ in range(2)]
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(device.torch)
+    exps = torch.empty(k * npad // 16, dtype=torch.uint8, device=device.torch)
+    codes = torch.empty(k * npad, dtype=torch.uint8, device=device.torch)
+    packed = torch.zeros(L.tkd_packed_bytes(_tkd.FMT_BFP8, k, n), dtype=torch.uint8, device=device.torch)
+    emax = torch.zeros(npad // 16, dtype=torch.uint8, device=device.torch)
+    info = torch.zeros(1, dtype=torch.int32, device=device.torch)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def pack(w):
+        _tkd.check(L.tkd_quantise(_tkd.FMT_BFP8, w.data_ptr(), 1, k, n, None, exps.data_ptr(), codes.data_ptr(), st), "quantise")
+        _tkd.check(L.tkd_pack(_tkd.FMT_BFP8, k, n, exps.data_ptr(), codes.data_ptr(), packed.data_ptr(), emax.data_ptr(),
+                              info.data_ptr(), st), "pack")
+
+    def describe(out, fresh):
+        a = _tkd.TkdMatmul()
+        a.fmt, a.m, a.k, a.x, a.ldx = _tkd.FMT_BFP8, m, k, x.data_ptr(), k
+        a.nblocks, a.epilogue, a.out_dtype, a.out, a.ldo = 1, _tkd.EPI_PLAIN, _tkd.DT_BF16, out.data_ptr(), n
+        a.block[0].w, a.block[0].emax, a.block[0].n = packed.data_ptr(), emax.data_ptr(), n
+        a.weights_fresh = fresh
+        need = ctypes.c_uint64(0)
+        _tkd.check(L.tkd_matmul_workspace(ctypes.byref(a), ctypes.byref(need)), "workspace")
+        ws = torch.zeros(need.value, dtype=torch.uint8, device=device.torch)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        return a, ws
+
+    outs = [torch.empty(m, n, dtype=torch.bfloat16, device=device.torch) for _ in range(3)]
+    pack(src[0])
+    torch.cuda.synchronize()
+    a, ws = describe(outs[0], 0)
+    _tkd.check(L.tkd_matmul(ctypes.byref(a), st), "tkd_matmul")  # the first weight, packed and synchronised
+    torch.cuda.synchronize()
+    # the second weight over the same stream, no synchronisation before its matmul
+    pack(src[1])
+    b, ws2 = describe(outs[1], 1)
+    _tkd.check(L.tkd_matmul(ctypes.byref(b), st), "tkd_matmul")
+    torch.cuda.synchronize()
+    c, ws3 = describe(outs[2], 0)
+    _tkd.check(L.tkd_matmul(ctypes.byref(c), st), "tkd_matmul")  # ... and after a synchronisation
+    torch.cuda.synchronize()
+    assert torch.equal(outs[1], outs[2]) and not torch.equal(outs[0], outs[1])
