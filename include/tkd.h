@@ -140,7 +140,10 @@ typedef struct {
                                (bounded, about a second: then TKD_ERR_TIMEOUT in the status word and tkd_exchange_wait
                                can wait again); 2: the same wait, but for the exchanged call BEFORE this one (the exchange
                                of one call overlaps the next call's run; tkd_exchange_wait flushes the last one); 0: no
-                               wait, the caller orders tkd_exchange_wait behind it */
+                               wait, the caller orders tkd_exchange_wait behind it; 3: the kernel only stores (no
+                               counting, no fence, no flags): the caller announces the call with tkd_exchange_publish
+                               once the kernel has completed, e.g. from a second stream behind an event, so that the
+                               announcement's system-wide fence and the flags' flight overlap the next call */
     int32_t weights_fresh;  /* 0: every weight stream and emax array of the call was complete (by an event or a
                                synchronisation) before this call was enqueued: the kernel is launched as a programmatic
                                dependent of the work before it on the stream, and its first weight loads may run while
@@ -228,6 +231,12 @@ int tkd_head_pick_records(const uint32_t* records, int nrecords, int rows, int k
 /* Wait on `stream` until every one of the nranks ranks has completed as many exchanged calls as this rank has
  * (flags[r] >= flags[TKD_FLAG_SEQ] for all r, modulo 2^32); bounded (about a second), then TKD_ERR_TIMEOUT in *status. */
 int tkd_exchange_wait(uint32_t* flags, int nranks, int32_t* status, void* stream);
+/* Announce an exchanged call made with exchange_wait 3, on a stream on which the call's kernel has completed: counts
+ * the call in flags[TKD_FLAG_SEQ] and writes that count to flags[rank] on every rank (peer_flags: host array of the
+ * nranks - 1 other ranks' flag words, as in TkdMatmul). lag_wait: then wait (bounded) until every rank has announced
+ * the call before this one. No counterpart in the reference (one device). */
+int tkd_exchange_publish(uint32_t* flags, uint32_t* const* peer_flags, int nranks, int rank, int lag_wait, int32_t* status,
+                         void* stream);
 /* Device memory other processes on this machine can map: allocates `bytes` (zeroed; synchronises) and writes its
  * 64-byte inter-process handle to handle (host). The owner frees it with tkd_peer_free. */
 int tkd_peer_alloc(uint64_t bytes, void** ptr, void* handle);

@@ -450,6 +450,17 @@ int tkd_exchange_wait(uint32_t* flags, int nranks, int32_t* status, void* stream
     return launch_err(tkd_launch_exchange_wait(flags, nranks, status, static_cast<cudaStream_t>(stream)));
 }
 
+int tkd_exchange_publish(uint32_t* flags, uint32_t* const* peer_flags, int nranks, int rank, int lag_wait, int32_t* status,
+                         void* stream) {
+    if (!flags || !peer_flags || nranks < 2 || nranks > TKD_MAX_RANKS || rank < 0 || rank >= nranks) return TKD_ERR_BAD_ARG;
+    TkdPeerFlags pf = {};
+    for (int q = 0; q < nranks - 1; ++q) {
+        if (!peer_flags[q]) return TKD_ERR_BAD_ARG;
+        pf.p[q] = peer_flags[q];
+    }
+    return launch_err(tkd_launch_exchange_publish(flags, pf, nranks, rank, lag_wait, status, static_cast<cudaStream_t>(stream)));
+}
+
 int tkd_peer_alloc(uint64_t bytes, void** ptr, void* handle) {
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is 64 bytes");
     if (!bytes || !ptr || !handle) return TKD_ERR_BAD_ARG;

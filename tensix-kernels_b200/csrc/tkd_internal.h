@@ -103,3 +103,8 @@ int tkd_launch_head_pick(const uint32_t* records, int nrec, int rows, int k, int
 int tkd_launch_head_pick_records(const uint32_t* records, int nrec, int rows, int k, uint32_t vocab, const uint32_t* tmap,
                                  uint32_t* out, uint32_t* ids_out, cudaStream_t st);
 int tkd_launch_exchange_wait(uint32_t* flags, int nranks, int* status, cudaStream_t st);
+struct TkdPeerFlags {
+    uint32_t* p[7];
+};
+int tkd_launch_exchange_publish(uint32_t* flags, const TkdPeerFlags& peers, int nranks, int rank, int lag_wait, int* status,
+                                cudaStream_t st);

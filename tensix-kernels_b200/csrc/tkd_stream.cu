@@ -38,7 +38,38 @@ __global__ void tkd_exchange_wait_kernel(uint32_t* flags, int nranks, int* statu
     }
 }
 
+// Numbers this rank's exchanged call and tells every rank (one thread). It runs, by stream order, after the stream
+// kernel whose peer stores it announces has completed; with lag_wait it then checks (bounded) that every rank's call
+// BEFORE this one has been announced here.
+__global__ void tkd_exchange_publish_kernel(uint32_t* flags, TkdPeerFlags peers, int nranks, int rank, int lag_wait, int* status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x != 0) return;
+    const uint32_t seq = flags[TKD_FLAG_SEQ] + 1;
+    flags[TKD_FLAG_SEQ] = seq;
+    __threadfence_system();
+    for (int q = 0; q < nranks - 1; ++q)
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(peers.p[q] + rank), "r"(seq) : "memory");
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(flags + rank), "r"(seq) : "memory");
+    if (!lag_wait) return;
+    for (int r = 0; r < nranks; ++r) {
+        int rounds = 0;  // (bounded: about a second)
+        while ((int32_t)(ld_acquire_sys(flags + r) - (seq - 1)) < 0) {
+            if (++rounds > (1 << 20)) {
+                if (status) atomicExch(status, TKD_ERR_TIMEOUT);
+                return;
+            }
+            __nanosleep(rounds < 64 ? 20 : 200);
+        }
+    }
+}
+
 }  // namespace
+
+int tkd_launch_exchange_publish(uint32_t* flags, const TkdPeerFlags& peers, int nranks, int rank, int lag_wait, int* status,
+                                cudaStream_t st) {
+    tkd_exchange_publish_kernel<<<1, 32, 0, st>>>(flags, peers, nranks, rank, lag_wait, status);
+    return (int)cudaGetLastError();
+}
 
 int tkd_launch_exchange_wait(uint32_t* flags, int nranks, int* status, cudaStream_t st) {
     tkd_exchange_wait_kernel<<<1, 32, 0, st>>>(flags, nranks, status);

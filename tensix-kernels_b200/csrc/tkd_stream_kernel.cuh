@@ -427,6 +427,8 @@ __device__ __forceinline__ void exchange_done(const TkdParams& p, int lane, int 
     // that counts last orders everything system-wide with the call's ONE system fence (system fences serialise
     // across the GPU: one per warp cost this kernel a third of its run), numbers the call and writes that number to
     // this rank's word on every rank. (No CTA barrier: the warps may have left the loop at different points.)
+    // exchange_wait 3: none of this; the caller announces the call once the kernel has completed.
+    if (p.exchange_wait == 3) return;
     __syncwarp();
     if (lane == 0) {
         __threadfence();

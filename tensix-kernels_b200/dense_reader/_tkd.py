@@ -67,6 +67,7 @@ SYMBOLS = {
     "tkd_head_pick": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_u32, c_vp, c_i64, c_i32, c_vp, c_i64, c_i32, c_vp, c_vp, c_vp]),
     "tkd_head_pick_records": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_u32, c_vp, c_vp, c_vp, c_vp]),
     "tkd_exchange_wait": (c_i32, [c_vp, c_i32, c_vp, c_vp]),
+    "tkd_exchange_publish": (c_i32, [c_vp, ctypes.POINTER(c_vp), c_i32, c_i32, c_i32, c_vp, c_vp]),
     "tkd_peer_alloc": (c_i32, [c_u64, ctypes.POINTER(c_vp), c_vp]),
     "tkd_peer_free": (c_i32, [c_vp]),
     "tkd_peer_open": (c_i32, [c_vp, ctypes.POINTER(c_vp)]),

@@ -503,7 +503,7 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
             _CALLS.clear()
         ws = _WORKSPACE.get(_ws_key(device))
         _CALLS[call_key] = {
-            "y": y, "launches": launched, "device": device, "ws": ws, "ws_key": _ws_key(device),
+            "y": y, "launches": launched, "device": device, "ws": ws, "ws_key": _ws_key(device), "exchange": exchange,
             "keep": (x, w, scale, out, w_up, topk, opts_in),
             "ptrs": (_raw(x).data_ptr(), _raw(y).data_ptr()),
             "topk": None if topk is None else tuple(sorted((k, id(v)) for k, v in topk.items())),
@@ -536,6 +536,8 @@ def matmul_host(x_host, out_host, x, w, scale, *, topk=None, out=None, col0=0, w
                 matmul(x, w, scale, topk=topk, out=out, col0=col0, w_up=w_up, max_banks=max_banks, **opts)
         hit = _CALLS[key]
     assert len(hit["launches"]) == 1, "dense_reader.matmul_host: one launch (up to 32 rows)"
+    assert hit["exchange"] is None or hit["exchange"].side is None, (
+        "dense_reader.matmul_host: the result is copied out by the same call, so an exchange must complete inside the kernel")
     sp = torch.cuda.current_stream().cuda_stream if stream is None else stream.cuda_stream
     rc = _tkd.lib().tkd_matmul_host(ctypes.byref(hit["launches"][0]), x_host.data_ptr(), out_host.data_ptr(), sp)
     if rc:
@@ -559,6 +561,8 @@ def _replay(hit):
         rc = fn(ctypes.byref(a), stream)
         if rc:
             _tkd.check(rc, "tkd_matmul")
+        if hit["exchange"] is not None:
+            hit["exchange"].after_launch(status_word(device))
     return True
 
 
@@ -620,6 +624,8 @@ def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, o
         exchange.fill(a, a.out, a.records)
     with torch.cuda.device(device.torch):
         _tkd.check(_tkd.lib().tkd_matmul(ctypes.byref(a), torch.cuda.current_stream().cuda_stream), "tkd_matmul")
+        if exchange is not None:
+            exchange.after_launch(status_word(device))
     done = _tkd.TkdMatmul()
     ctypes.pointer(done)[0] = a  # (a copy: the cached descriptor is rewritten by the next row slice or call)
     return done

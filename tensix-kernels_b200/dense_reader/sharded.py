@@ -1,6 +1,6 @@
 """sharded.py: the dense_reader path over the GPUs of one box, one process per GPU (torch.distributed).
 
-The reference runs on one device; BASELINE's north star adds this: large weights (the LM head, the MLP's gate/up) are
+The reference runs on one device; on a box of GPUs large weights (the LM head, the MLP's gate/up) are
 split by output columns, each rank packs and streams only its own columns (linear.native_weight on its rows of the
 [out, in] matrix, linear.matmul on the replicated activations), and the small results are joined by one all-gather:
 the [M, N_local] outputs, or the top-k records followed by a merge every rank does for itself. There is no sharding of
@@ -51,10 +51,14 @@ class Exchange:
     arrived; a call must not write a tensor again before every rank has read what the last call but one left there
     (alternate between two tensors). wait="lagged": each kernel ends when all ranks' parts of the exchanged call BEFORE
     it have arrived, so that an exchange's latency passes during the next call's run (wait_all() flushes the last one;
-    a tensor may be written again four calls later). wait=False: nothing waits but wait_all()."""
+    a tensor may be written again four calls later). wait=False: nothing waits but wait_all(). wait="deferred": the
+    kernel only stores; a one-thread kernel on a second stream, ordered behind the call by an event, announces it (its
+    system-wide fence, the flags' flight and a bounded check that every rank announced the call before overlap the
+    next call instead of ending this one); wait_all() joins that stream and waits for the last call."""
 
     def __init__(self, device, nbytes, group=None, wait=True):
         self.device, self.group, self.wait = device, group, wait
+        self.side = torch.cuda.Stream(device=device.torch) if wait == "deferred" else None
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         assert self.world <= _tkd.MAX_RANKS, "dense_reader: an exchange spans the GPUs of one box (8)"
         self.nbytes = (int(nbytes) + 255) // 256 * 256
@@ -97,16 +101,31 @@ class Exchange:
     def fill(self, a, out_ptr, rec_ptr):
         """Put this exchange into a launch descriptor: the peers' addresses of the output and of the records (where
         those lie inside the buffer) and the flag words."""
-        a.nranks, a.rank, a.flags, a.exchange_wait = self.world, self.rank, self.base, 2 if self.wait == "lagged" else int(bool(self.wait))
+        mode = {"lagged": 2, "deferred": 3}.get(self.wait, int(bool(self.wait)))
+        a.nranks, a.rank, a.flags, a.exchange_wait = self.world, self.rank, self.base, mode
         outs, recs = self._peers_of(out_ptr), self._peers_of(rec_ptr)
         for q, b in enumerate(self.peer_base):
             a.peer_flags[q] = b
             a.peer_out[q] = outs[q] if outs else None
             a.peer_records[q] = recs[q] if recs else None
 
+    def after_launch(self, status=None):
+        """wait="deferred": announce the call just launched on the current stream, from the side stream."""
+        if self.side is None:
+            return
+        done = torch.cuda.Event()
+        done.record(torch.cuda.current_stream())
+        self.side.wait_event(done)
+        peers = (ctypes.c_void_p * 7)(*self.peer_base)
+        _tkd.check(_tkd.lib().tkd_exchange_publish(self.base, peers, self.world, self.rank, 1,
+                                                   status.data_ptr() if status is not None else None, self.side.cuda_stream),
+                   "tkd_exchange_publish")
+
     def wait_all(self, status=None, stream=None):
-        """Order a wait for every rank's last exchanged call behind the current stream's work (for wait=False, or
-        after a kernel's own wait gave up)."""
+        """Order a wait for every rank's last exchanged call behind the current stream's work (for wait=False or
+        "deferred", or after a kernel's own wait gave up)."""
+        if self.side is not None:
+            (torch.cuda.current_stream() if stream is None else stream).wait_stream(self.side)
         sp = torch.cuda.current_stream().cuda_stream if stream is None else stream.cuda_stream
         _tkd.check(_tkd.lib().tkd_exchange_wait(self.base, self.world, status.data_ptr() if status is not None else None, sp),
                    "tkd_exchange_wait")

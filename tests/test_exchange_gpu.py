@@ -20,10 +20,11 @@ from dense_reader import linear, sharded  # noqa: E402
 ROOT = Path(__file__).resolve().parents[1]
 
 
-def fake_rank(device, rank, world, bufs, nbytes):
+def fake_rank(device, rank, world, bufs, nbytes, wait=False):
     """An Exchange over plain buffers of one GPU: rank `rank`'s view of `bufs` (no IPC, no process group)."""
     ex = object.__new__(sharded.Exchange)
-    ex.device, ex.group, ex.wait = device, None, False
+    ex.device, ex.group, ex.wait = device, None, wait
+    ex.side = torch.cuda.Stream(device=device.torch) if wait == "deferred" else None
     ex.rank, ex.world, ex.nbytes, ex._used = rank, world, nbytes, 256
     ex.base = bufs[rank].data_ptr()
     ex.peer_base = [b.data_ptr() for r, b in enumerate(bufs) if r != rank]
@@ -35,8 +36,11 @@ def dev_x(device, x):
                            device=device)
 
 
-@pytest.mark.parametrize("fmt,out32", [(ttnn.bfloat8_b, False), (ttnn.bfloat4_b, True)])
-def test_outputs_reach_every_rank(device, fmt, out32):
+@pytest.mark.parametrize("fmt,out32,wait", [(ttnn.bfloat8_b, False, False), (ttnn.bfloat4_b, True, False),
+                                            (ttnn.bfloat8_b, False, "deferred")])
+def test_outputs_reach_every_rank(device, fmt, out32, wait):
+    """(wait "deferred": the kernels only store, each call is announced by tkd_exchange_publish from the rank's second
+    stream; an announcement waits for the other ranks' announcements of the step before, all launched by then.)"""
     world, m, k = 3, 3, 2048
     shards = sharded.column_shards(1024 * 3 - 96, world)  # the last rank's shard is ragged
     n = shards[-1][1]
@@ -46,7 +50,7 @@ def test_outputs_reach_every_rank(device, fmt, out32):
     full = ttnn.to_torch(linear.matmul(tx, linear.native_weight(device, w, fmt)[0], None, out32=out32))
     nbytes = 1 << 20
     bufs = [torch.zeros(nbytes + 256, dtype=torch.uint8, device=device.torch) for _ in range(world)]
-    ranks = [fake_rank(device, r, world, bufs, nbytes) for r in range(world)]
+    ranks = [fake_rank(device, r, world, bufs, nbytes, wait) for r in range(world)]
     outs = [[ex.tensor([1, 1, m, n], ttnn.float32 if out32 else ttnn.bfloat16) for _ in range(2)] for ex in ranks]
     tws = [linear.native_weight(device, sharded.shard_rows(w, shards, r), fmt)[0] for r in range(world)]
     status = torch.zeros(1, dtype=torch.int32, device=device.torch)

@@ -339,7 +339,7 @@ def test_packed_weight_cache_round_trip(device, tmp_path):
 
 
 def test_full_size_properties(device):
-    """At BASELINE's full sizes (config 2's gate weight, 14336 x 4096 bfloat4_b; config 3's 4096 x 14336 bfloat8_b)
+    """At the benchmark configurations' full sizes (the gate weight, 14336 x 4096 bfloat4_b; the down projection's 4096 x 14336 bfloat8_b)
     the oracle is too slow for every column; size-independent properties stand in: linearity in x (power-of-two
     scaling is exact), a zero row of x gives zeros, columns of a sub-matrix equal the same columns computed alone,
     and a sample of columns against the oracle."""
