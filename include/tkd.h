@@ -97,7 +97,7 @@ typedef struct {
     int32_t fmt;            /* TKD_FMT_* of every block */
     int32_t m;              /* activation rows, 1..32 */
     int64_t k;
-    const void* x;          /* bf16 [m, k], ldx elements a row, 16-byte aligned rows */
+    const void* x;          /* bf16 [m, k], ldx elements a row (at most 2^26 for m > 8), 16-byte aligned rows */
     int64_t ldx;
     int32_t nblocks;        /* 1, or 2..4 for a block list (linear.py:615-624) */
     int32_t epilogue;       /* TKD_EPI_* */

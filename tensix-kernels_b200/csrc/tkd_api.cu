@@ -115,11 +115,13 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     p.off_pbuf = TKD_SMEM_HEAD;
     if (a->m > 8) {
         // 9 to 32 rows, the tensor-memory kernel: the running sums [128][40] floats, then (from the next 1024-byte
-        // boundary of the window, hence the slack) 3 slots of two x tiles (4 KB each), then the ring
+        // boundary of the window, hence the slack) TKD_TC_SLOTS slots of two x tiles (4 KB each), then the ring. (The kernel
+        // addresses x by 32-bit element offsets.)
+        if (a->ldx > (1 << 26)) return TKD_ERR_BAD_ARG;
         p.tc = 1;
         p.off_tbuf = TKD_SMEM_HEAD;
         p.off_xt = p.off_tbuf + TKD_PANEL_COLS * 40 * 4;
-        p.off_ring = (int)align_up(p.off_xt + 1024 + 3 * 2 * 4096, 128);
+        p.off_ring = (int)align_up(p.off_xt + 1024 + TKD_TC_SLOTS * 2 * 4096, 128);
     } else {
         // (one to eight rows: two hand-over buffers; one row: all of x in shared memory, K rounded up to a chunk, if
         // that leaves the ring at least four stages)

@@ -30,6 +30,7 @@ int tkd_launch_unpack(int fmt, int64_t K, int64_t npad, const void* stream, cons
 #define TKD_PANEL_COLS 128     // columns one work item covers
 #define TKD_MAX_STAGES 16
 #define TKD_SMEM_HEAD 1024     // barriers, the stage headers, flags
+#define TKD_TC_SLOTS 6         // tensor-memory kernel: operand slots (a unit of two 64-k tiles: 64 columns of A, 8 KB of x)
 
 struct TkdSegDev {
     const uint8_t* w;     // packed stream (the gate's with a separate up weight)

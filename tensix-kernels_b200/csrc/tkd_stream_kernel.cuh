@@ -86,7 +86,7 @@ __device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, 
 #ifdef TKD_NO_PARKED_SLEEP
     return mbar_wait(bar, parity, status);
 #else
-    for (uint32_t i = 0; i < (kWaitRounds << 6); ++i) {
+    for (uint32_t i = 0; i < (kWaitRounds << 2); ++i) {  // (a failing try_wait has itself waited microseconds)
         if (mbar_try_wait(bar, parity)) return true;
         __nanosleep(TKD_PARK_NS);
     }

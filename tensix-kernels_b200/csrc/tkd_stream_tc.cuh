@@ -7,31 +7,31 @@
 // decoded into bf16 tiles in shared memory once, whatever the row count, and one thread issues tcgen05.mma on them with
 // the accumulators in tensor memory:
 //
-//   warps 4-19     decode warps: warp (group g, half h) turns its 16 columns' share of a chunk into bf16 (code times
-//                  2^e', one multiply per two weights: every block-float value is a bf16 value) and writes it straight
-//                  into TENSOR MEMORY with tcgen05.st.16x256b, whose thread layout is the mma A fragment's the stream is
-//                  packed for (thread (g, t): rows g and g + 8, two 32-bit columns): the A operand of the MMAs is read
-//                  from tensor memory, never from shared memory. (A first version stored the A tiles in shared memory:
-//                  32 KB written and 32 KB read by the tensor core per 17 KB of stream made the shared-memory
-//                  bandwidth the bound, at 3 TB/s.) A warp owns the tensor-memory lanes of its 16 columns (its
-//                  number mod 4 is their quarter). A block of 16 k as the MMA sees it is this layout's: position
-//                  4 t + r holds k = 8 t + 4 jj + r of a block of 32 k; the activations are laid out to match.
+//   warps 3-18     decode warps, in two groups of eight; a unit of two tiles of 64 k is one group's work (units in turn:
+//                  while one group waits for its stores to land, the other decodes). A warp turns its 16 columns' share
+//                  of the unit into bf16 (code times 2^e', one multiply per two weights: every block-float value is a
+//                  bf16 value) and writes it straight into TENSOR MEMORY with tcgen05.st.16x256b, whose thread layout
+//                  is the mma A fragment's the stream is packed for (thread (g, t): rows g and g + 8, two 32-bit
+//                  columns): the A operand of the MMAs is read from tensor memory, never from shared memory. (A first
+//                  version stored the A tiles in shared memory: 32 KB written and 32 KB read by the tensor core per
+//                  17 KB of stream made the shared-memory bandwidth the bound, at 3 TB/s.) A warp owns the
+//                  tensor-memory lanes of its 16 columns (its number mod 4 is their quarter). A block of 16 k as the
+//                  MMA sees it is this layout's: position 4 t + r holds k = 8 t + 4 jj + r of a block of 32 k; the
+//                  activations are laid out to match.
 //                  The same warps write the tile of activations a unit is multiplied by (32 rows x 64 k, rows past M
 //                  zero, K-major with the 128-byte swizzle, in that order of k) into shared memory: each lane loads
 //                  its 16 bytes of the NEXT chunk's tiles into registers while it decodes this chunk (they come from
 //                  L2, a microsecond away).
-//   warps 20-23    output warps (thread = panel column = tensor-memory lane): read a slice's sums with tcgen05.ld, keep
+//   warps 19-22    output warps (thread = panel column = tensor-memory lane): read a slice's sums with tcgen05.ld, keep
 //                  the running sums in shared memory, and from there on do what tkd_stream_kernel's output warps do
 //   warp 1         producer (one lane issues): the same ring of packed-weight chunks as tkd_stream_kernel
-//   warp 0         one lane issues the MMAs: D[128 columns, 32 rows] += A (tensor memory) x (x tile)^T, 4 x (K = 16) a
-//                  tile, tcgen05.commit onto the unit's "empty" barrier and, at a slice's end, the accumulators' "full"
+//   warps 0, 2     one lane of each issues MMAs: D[128 columns, 32 rows] += A (tensor memory) x (x tile)^T, 4 x (K = 16)
+//                  a tile, tcgen05.commit onto the unit's "empty" barrier and, at a slice's end, the accumulators' "full"
 //
-// A slice's sum is accumulated from zero in tensor memory, in FOUR accumulators of 32 columns: the j-th block of 16 k
-// of every tile goes to accumulator j, because an MMA that adds to the accumulator of the MMA before it waits for it
-// (about 100 ns each, measured; the four of a tile are independent this way), and the slice's sum is ((d0 + d1) + d2)
-// + d3. Two such sets, so that the MMAs of the next slice run while the output warps drain this one. A column's sum is
-// the ascending sum of its slices' sums in plain fp32 adds, as in tkd_stream_kernel, so it depends on K, the format and
-// ks only. No cluster, no multicast, no
+// A slice's sum is accumulated from zero in tensor memory, in two accumulators of 32 columns: two MMA warps take
+// the slice's units in turn, each into its own accumulator; the slice's sum is d0 + d1. Two such sets, so that the MMAs of the next slice run while
+// the output warps drain this one. A column's sum is the ascending sum of its slices' sums in plain fp32 adds, as in
+// tkd_stream_kernel, so it depends on K, the format and ks only. No cluster, no multicast, no
 // second CTA: cta_group::1 throughout. Every wait is bounded; the kernel always reaches its end, where the warp that
 // allocated the tensor memory frees it.
 #pragma once
@@ -39,15 +39,20 @@
 
 namespace {
 
-constexpr int kTcSlots = 3;          // operand slots, each a unit of two tiles of 64 k
+constexpr int kTcGroups = 2;           // groups of decode warps; a unit is one group's
+constexpr int kTcSlots = TKD_TC_SLOTS;  // operand slots, each a unit of two tiles of 64 k
 constexpr int kTcXTile = 32 * 128;   // bytes of an x tile in shared memory: 32 rows x 64 k of bf16
 constexpr int kTcSlot = 2 * kTcXTile;  // ... of a slot's two x tiles
 constexpr int kTcACols = 32;         // tensor-memory columns of an A tile: 128 lanes x 64 k of bf16, two to a column
-constexpr int kTcAcc0 = 0, kTcA0 = 256;  // tensor-memory columns: two sets of four accumulators of 32, then the A slots
-// Warps: 0 the MMA issuer, 1 the producer, 2-3 idle, 4-19 decode, 20-23 output. The MMA issuer is the warp with the
+constexpr int kTcAcc0 = 0, kTcA0 = 128;  // tensor-memory columns: two sets of two accumulators of 32, then the A slots
+static_assert(kTcA0 + kTcSlots * 2 * kTcACols <= 512, "the A slots must fit the tensor memory");
+// Warps: 0 and 2 the MMA issuers, 1 the producer, 3-18 decode, 19-22 output (23 warps: 736 threads may use 88
+// registers each, 768 only 80, two fewer than the kernel needs without spilling). The MMA issuer is the warp with the
 // lowest number on purpose: the schedulers favour older warps, and as the last warp of the CTA it got an issue slot
 // every twenty cycles beside four decode warps that are always ready (its unit of eight MMAs took 770 ns).
-constexpr int kTcWarps = 24, kTcMmaWarp = 0, kTcProducerWarp = 1, kTcDecodeWarp0 = 4, kTcOutputWarp0 = 20;
+constexpr int kTcWarps = 23, kTcMmaWarp = 0, kTcProducerWarp = 1, kTcDecodeWarp0 = 3, kTcOutputWarp0 = 19, kTcMmaWarps = 2;
+// the MMA warp number (0, 1) of a warp, or -1: warps 0 and 2
+__device__ __forceinline__ int tc_mma_warp(int warp) { return warp == 0 ? 0 : warp == 2 ? 1 : -1; }
 constexpr int kTcMP = 40;            // floats per column in tbuf (32 rows, padded)
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -87,11 +92,10 @@ template <int FMT, bool KWHOLE>
 __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const __grid_constant__ TkdParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     using F = Fmt<FMT>;
-    constexpr int SW = 16, MP = kTcMP, MR = 32;
+    constexpr int SW = 16, MP = kTcMP;
     constexpr int CK = F::SUBSA * F::KSA;
-    // Every decode warp writes to (and arrives on) every unit of two tiles: bfloat4_b's super-atom is a whole tile, so a
-    // warp of half h takes the unit's tile h; the other formats' super-atoms are half tiles: half h of both tiles.
-    constexpr int NWT = 16;
+    // A unit of two tiles is written (and its "full" barrier arrived on) by the warps of one group of decode warps.
+    constexpr int NWT = 16 / kTcGroups;  // the warps of a group
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TKD_MAX_STAGES);
     const uint32_t afull0 = smem_u32(bars + 2 * TKD_MAX_STAGES), aempty0 = afull0 + 8 * kTcSlots;
@@ -113,10 +117,10 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
         }
         for (int s = 0; s < kTcSlots; ++s) {
             mbar_init(afull0 + 8 * s, NWT);
-            mbar_init(aempty0 + 8 * s, 1);
+            mbar_init(aempty0 + 8 * s, kTcMmaWarps);
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(accfull0 + 8 * s, 1);
+            mbar_init(accfull0 + 8 * s, kTcMmaWarps);
             mbar_init(accempty0 + 8 * s, 4);
         }
         sflag[0] = sflag[1] = 0;
@@ -138,7 +142,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
     const int64_t nitems = i1 - i0;
     auto item_at = [&](int64_t j) { return j < lead ? tail0 + j : i0 + (j - lead); };
 
-    // tensor memory: all 512 columns (two sets of four accumulators of 32, three A slots of 64), allocated and freed by
+    // tensor memory: all 512 columns (two sets of two accumulators of 32, then the A slots of 64), allocated and freed by
     // the MMA warp
     if (warp == kTcMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
@@ -207,130 +211,170 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
     } else if (warp >= kTcDecodeWarp0 && warp < kTcDecodeWarp0 + SW) {
         // ---------------------------------------------------------------- decode warps
         asm volatile("griddepcontrol.wait;" ::: "memory");  // (x may be the output of the kernel before this one)
-        // (a warp may touch the tensor-memory lanes 32 (warp % 4) .. + 31 only: its group's 16 columns are among them)
+        // The warps form G groups, and a unit (by its number in this CTA's sequence, mod G) is one group's work from its
+        // slot's "empty" to its "full": while a group waits for its stores to land (tcgen05.wait::st, the proxy fence),
+        // the others decode. A slot is always the same group's (kTcSlots is a multiple of G), so the group's warps see
+        // every phase of its barriers. A warp may touch the tensor-memory lanes 32 (warp % 4) .. + 31 only: its RG row
+        // groups of 16 panel columns are among them.
+        constexpr int G = kTcGroups, RG = G / 2, PP = G / 2;
+        static_assert(kTcSlots % G == 0 && (G == 2 || G == 4), "a slot belongs to one group");
         const int cw = warp - kTcDecodeWarp0;
-        const int g8 = 2 * (cw & 3) + ((cw >> 2) & 1), h = cw >> 3;
-        const int g = lane >> 2, t = lane & 3;
+        const int qtr = warp & 3, sub4 = cw >> 2;  // (any four warps in a row cover the four quarters)
+        const int grp = G == 2 ? sub4 >> 1 : sub4;                  // this warp's group
+        const int rg0 = G == 2 ? 2 * qtr + (sub4 & 1) : 2 * qtr;    // its first row group
+        const int gl = (G == 2 ? 2 * qtr + (sub4 & 1) : qtr) * 32 + lane;  // this lane's number within the group
+        const int t = lane & 3;
         constexpr int EXPB = FMT == TKD_BFP4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
+        constexpr int UPC = CK / 128;              // units of a whole chunk
+        constexpr int MU = (UPC + G - 1) / G;      // ... of them one group's, at most
+        constexpr int XT = MU * 2 * PP;            // x pieces a lane holds for a chunk
         const uint2 sh = make_uint2(p.mul16, p.mul128);
         const uint32_t ring_a = smem_u32(ring), hdr_a = smem_u32(hdr);
-        // the tensor-memory address of this warp's 16 lanes (panel columns 16 g8 .. + 15) at the first A column
-        const uint32_t alane = tmem0 + ((uint32_t)(16 * g8) << 16) + kTcA0;
+        // the tensor-memory address of this warp's first 16 lanes (panel columns 16 rg0 .. + 15) at the first A column
+        const uint32_t alane = tmem0 + ((uint32_t)(16 * rg0) << 16) + kTcA0;
         uint32_t slot = 0, phase = 0, useq = 0;
-        // This lane's pieces of the x tiles: tile i of this warp's tiles of a chunk (bfloat4_b: the tiles of its half,
-        // 32 pieces a warp; else every tile, 16 pieces a warp on its first 16 lanes), piece = (row, 16 bytes of the row).
-        constexpr int XT = FMT == TKD_BF16 ? 2 : 4;  // tiles of a chunk a warp writes to
-        const int xe = FMT == TKD_BFP4 ? g8 * 32 + lane : cw * 16 + (lane & 15);
-        const bool xmine = FMT == TKD_BFP4 || lane < 16;
-        const int xr_ = xe >> 3, xc_ = xe & 7;
-        const uint16_t* const xrow = p.x + (int64_t)min(xr_, M - 1) * p.ldx + 8 * xc_;
-        // This lane's 16 bytes (8 k of one row) go to two places of the row's 128 bytes, 8 bytes each: k 0-3 to the block of
-        // 16 k with jj = 0 of its block of 32 k, k 4-7 to the one with jj = 1, both at position 4 t (t = the piece's number
-        // within the block of 32 k); then the swizzle (16-byte piece ^ row).
-        const uint32_t xo0 = 64 * (xc_ >> 2) + 8 * (xc_ & 3), xo1 = xo0 + 32;
-        const uint32_t xdst0 = xr_ * 128 + ((((xo0 >> 4) ^ (xr_ & 7)) << 4) | (xo0 & 15));
-        const uint32_t xdst1 = xr_ * 128 + ((((xo1 >> 4) ^ (xr_ & 7)) << 4) | (xo1 & 15));
-        auto load_x = [&](uint4 (&v)[XT], int k0) {
+        // This lane's pieces of an x tile (PP of the 256: piece = (row, 16 bytes of the row)). A piece's 16 bytes (8 k of
+        // one row) go to two places of the row's 128 bytes, 8 bytes each: k 0-3 to the block of 16 k with jj = 0 of its
+        // block of 32 k, k 4-7 to the one with jj = 1, both at position 4 t (t = the piece's number within the block of
+        // 32 k); then the swizzle (16-byte piece ^ row).
+        uint32_t xrow[PP];  // (an element offset into x: x is at most 32 rows)
+        uint32_t xdst0[PP], xdst1[PP];
+        int xk[PP];         // the piece's first k within its tile (past K for a row past M: such a piece stays zero)
 #pragma unroll
-            for (int i = 0; i < XT; ++i) {
-                const int k = k0 + 64 * (FMT == TKD_BFP4 ? 2 * i + h : i);  // the tile's first k
-                v[i] = xmine && xr_ < M && k + 8 * xc_ < K ? ldg_x(xrow + k) : make_uint4(0u, 0u, 0u, 0u);
-            }
+        for (int pp = 0; pp < PP; ++pp) {
+            const int xe = gl + pp * (512 / G), xr_ = xe >> 3, xc_ = xe & 7;
+            xrow[pp] = (uint32_t)(min(xr_, M - 1) * p.ldx + 8 * xc_);
+            xk[pp] = xr_ < M ? 8 * xc_ : (1 << 30);
+            const uint32_t xo0 = 64 * (xc_ >> 2) + 8 * (xc_ & 3), xo1 = xo0 + 32;
+            xdst0[pp] = xr_ * 128 + ((((xo0 >> 4) ^ (xr_ & 7)) << 4) | (xo0 & 15));
+            xdst1[pp] = xr_ * 128 + ((((xo1 >> 4) ^ (xr_ & 7)) << 4) | (xo1 & 15));
+        }
+        // the pieces of the group's units u0, u0 + G, .. of the chunk that starts at k0
+        auto load_x = [&](uint4 (&v)[XT], int k0, int u0) {
+#pragma unroll
+            for (int i = 0; i < MU; ++i)
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub)
+#pragma unroll
+                    for (int pp = 0; pp < PP; ++pp) {
+                        const int u = u0 + G * i, k = k0 + 64 * (2 * u + sub);  // the tile's first k
+                        v[(2 * i + sub) * PP + pp] =
+                            u < UPC && k + xk[pp] < K ? ldg_x(p.x + xrow[pp] + k) : make_uint4(0u, 0u, 0u, 0u);
+                    }
         };
         uint4 xcur[XT], xnext[XT];
         {
             const int64_t first_it = lead > 0 ? tail0 : i0;
-            load_x(xcur, (int)(first_it - idiv(p, first_it, p.nslices) * p.nslices) * p.ks);
+            load_x(xcur, (int)(first_it - idiv(p, first_it, p.nslices) * p.nslices) * p.ks, grp);
         }
+        // One store a tile's share: rows g (registers 4 b, 4 b + 1) and g + 8 (4 b + 2, 4 b + 3) of the warp's 16 lanes,
+        // 32-bit columns 2 t and 2 t + 1 of block b of 8 columns (16 k); two or four blocks an instruction.
+        auto st_a2 = [&](uint32_t taddr, const uint32_t (&r)[8]) {
+            asm volatile("tcgen05.st.sync.aligned.16x256b.x2.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+                         "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                         : "memory");
+        };
+        auto st_a4 = [&](uint32_t taddr, const uint32_t (&r)[16]) {
+            asm volatile(
+                "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
+                "%15, %16};" ::"r"(taddr),
+                "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+                "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                : "memory");
+        };
+        // super-atom `sab` (a shared-memory address) of one row group, decoded and stored at tensor-memory column tb:
+        // 16 columns of A (32 k; bfloat4_b: 32 columns, 64 k)
+        auto decode_sa = [&](uint32_t sab, uint32_t tb) {
+            if constexpr (FMT == TKD_BF16) {
+                const uint4 a = lds128(sab + lane * 16), b = lds128(sab + 512 + lane * 16);
+                const uint32_t r[8] = {a.x, a.z, a.y, a.w, b.x, b.z, b.y, b.w};
+                st_a2(tb, r);
+            } else {
+                uint32_t cwd[4], ewd[4];
+                if constexpr (FMT == TKD_BFP8) {
+                    const uint2 ev = lds64(sab + t * 8);
+                    const uint4 cv = lds128(sab + EXPB + lane * 16);
+                    cwd[0] = cv.x, cwd[1] = cv.y, cwd[2] = cv.z, cwd[3] = cv.w;
+                    ewd[0] = ev.x, ewd[1] = ev.y, ewd[2] = ewd[3] = 0;
+                } else {
+                    const uint4 ev = lds128(sab + t * 16), cv = lds128(sab + EXPB + lane * 16);
+                    cwd[0] = cv.x, cwd[1] = cv.y, cwd[2] = cv.z, cwd[3] = cv.w;
+                    ewd[0] = ev.x, ewd[1] = ev.y, ewd[2] = ev.z, ewd[3] = ev.w;
+                }
+                uint32_t r[8 * F::XB];
+#pragma unroll
+                for (int q = 0; q < F::XB; ++q) {
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) {
+                        uint32_t a0, a1, a2, a3, s0, s1;
+                        if constexpr (FMT == TKD_BFP4) {
+                            const uint32_t w = cwd[2 * q + jj], tt = __funnelshift_r(w, w, 8), ew = ewd[2 * q + jj];
+                            a0 = w & TKD_MASK_BFP4, a1 = shl_fma<4>(w, sh.x) & TKD_MASK_BFP4;
+                            a2 = tt & TKD_MASK_BFP4, a3 = shl_fma<4>(tt, sh.x) & TKD_MASK_BFP4;
+                            s0 = (ew & TKD_EMASK_BFP4) | TKD_EBASE_BFP4;
+                            s1 = (shl_fma<7>(ew, sh.y) & TKD_EMASK_BFP4) | TKD_EBASE_BFP4;
+                        } else {
+                            const uint32_t w0 = cwd[2 * jj], w1 = cwd[2 * jj + 1], ew = ewd[jj];
+                            a0 = w0 & TKD_MASK_BFP8, a1 = rot_and<8>(w0, TKD_MASK_BFP8);
+                            a2 = w1 & TKD_MASK_BFP8, a3 = rot_and<8>(w1, TKD_MASK_BFP8);
+                            s0 = ew & 0x7F807F80u, s1 = rot_and<8>(ew, 0x7F807F80u);
+                        }
+                        // (the code times 2^e': the weight itself, in units the output stage knows)
+                        const int b = 4 * (2 * q + jj);  // block 2 q + jj of the super-atom: columns 16 q + 8 jj
+                        r[b] = mul_bf16x2(a0, s0), r[b + 1] = mul_bf16x2(a2, s1);
+                        r[b + 2] = mul_bf16x2(a1, s0), r[b + 3] = mul_bf16x2(a3, s1);
+                    }
+                }
+                if constexpr (FMT == TKD_BFP4)
+                    st_a4(tb, r);
+                else
+                    st_a2(tb, r);
+            }
+        };
         while (true) {
             if (!mbar_wait(full0 + 8 * slot, phase, p.status)) break;
             const uint4 hd = lds128(hdr_a + 16 * slot);
             const int kc = (int)hd.w;
-            load_x(xnext, (int)hd.z);  // (used a whole chunk from now)
+            const bool at_end = (hd.x & ST_END) != 0;
             const int nsa = KWHOLE ? F::SUBSA : min(F::SUBSA, nsa_total - kc / CK * F::SUBSA);
             const int ntiles = (nsa * F::KSA + 63) / 64;
-            const uint32_t gb = ring_a + slot * p.stage_bytes + g8 * nsa * F::SAB;
-            bool ok = true;
-            // This warp's share of the chunk, a unit of two tiles at a time (unrolled: the x pieces are indexed at compile
-            // time): the slot is waited for, the tiles decoded and stored, then one proxy fence and one arrival. (The
-            // hand-over costs both sides a fixed time per barrier, the MMA warp most of all: a unit of two tiles halves it.)
-            auto tile_of = [&](int i) { return FMT == TKD_BFP4 ? 2 * i + h : i; };
-            // tile i of this warp's tiles of the chunk into place `sub` (0, 1) of a unit: the A part into tensor memory
-            // at column ta (the unit's first), the x part into shared memory at sb
-            auto st_a = [&](uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
-                // rows g (r0, r1) and g + 8 (r2, r3) of this warp's 16 lanes, 32-bit columns 2 t and 2 t + 1 of the block
-                asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r0), "r"(r1),
-                             "r"(r2), "r"(r3)
-                             : "memory");
-            };
-            auto do_tile = [&](int i, uint32_t sb, uint32_t ta, int sub) {
-                const int ti = tile_of(i);
-                const int sa = FMT == TKD_BFP4 ? ti : 2 * ti + h;  // this warp's super-atom of the tile
-                if (sa < nsa) {
-                    const uint32_t sab = gb + sa * F::SAB;
-                    // (a tile is four blocks of 16 k, 8 columns each: block 2 (block of 32 k) + jj)
-                    const uint32_t tb = ta + sub * kTcACols + (FMT == TKD_BFP4 ? 0 : 16 * h);
-                    if constexpr (FMT == TKD_BF16) {
-                        const uint4 a = lds128(sab + lane * 16), b = lds128(sab + 512 + lane * 16);
-                        st_a(tb, a.x, a.z, a.y, a.w);
-                        st_a(tb + 8, b.x, b.z, b.y, b.w);
-                    } else {
-                        uint32_t cwd[4], ewd[4];
-                        if constexpr (FMT == TKD_BFP8) {
-                            const uint2 ev = lds64(sab + t * 8);
-                            const uint4 cv = lds128(sab + EXPB + lane * 16);
-                            cwd[0] = cv.x, cwd[1] = cv.y, cwd[2] = cv.z, cwd[3] = cv.w;
-                            ewd[0] = ev.x, ewd[1] = ev.y, ewd[2] = ewd[3] = 0;
-                        } else {
-                            const uint4 ev = lds128(sab + t * 16), cv = lds128(sab + EXPB + lane * 16);
-                            cwd[0] = cv.x, cwd[1] = cv.y, cwd[2] = cv.z, cwd[3] = cv.w;
-                            ewd[0] = ev.x, ewd[1] = ev.y, ewd[2] = ev.z, ewd[3] = ev.w;
-                        }
-#pragma unroll
-                        for (int q = 0; q < F::XB; ++q) {
-#pragma unroll
-                            for (int jj = 0; jj < 2; ++jj) {
-                                uint32_t a0, a1, a2, a3, s0, s1;
-                                if constexpr (FMT == TKD_BFP4) {
-                                    const uint32_t w = cwd[2 * q + jj], tt = __funnelshift_r(w, w, 8), ew = ewd[2 * q + jj];
-                                    a0 = w & TKD_MASK_BFP4, a1 = shl_fma<4>(w, sh.x) & TKD_MASK_BFP4;
-                                    a2 = tt & TKD_MASK_BFP4, a3 = shl_fma<4>(tt, sh.x) & TKD_MASK_BFP4;
-                                    s0 = (ew & TKD_EMASK_BFP4) | TKD_EBASE_BFP4;
-                                    s1 = (shl_fma<7>(ew, sh.y) & TKD_EMASK_BFP4) | TKD_EBASE_BFP4;
-                                } else {
-                                    const uint32_t w0 = cwd[2 * jj], w1 = cwd[2 * jj + 1], ew = ewd[jj];
-                                    a0 = w0 & TKD_MASK_BFP8, a1 = rot_and<8>(w0, TKD_MASK_BFP8);
-                                    a2 = w1 & TKD_MASK_BFP8, a3 = rot_and<8>(w1, TKD_MASK_BFP8);
-                                    s0 = ew & 0x7F807F80u, s1 = rot_and<8>(ew, 0x7F807F80u);
-                                }
-                                // (the code times 2^e': the weight itself, in units the output stage knows)
-                                st_a(tb + 16 * q + 8 * jj, mul_bf16x2(a0, s0), mul_bf16x2(a2, s1), mul_bf16x2(a1, s0),
-                                     mul_bf16x2(a3, s1));
-                            }
-                        }
-                    }
-                }
-                if (xmine) {
-                    const uint4 v = xcur[i];
-                    const uint32_t xb = sb + sub * kTcXTile;
-                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(xb + xdst0), "r"(v.x), "r"(v.y) : "memory");
-                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(xb + xdst1), "r"(v.z), "r"(v.w) : "memory");
-                }
-            };
-            constexpr int UPC = FMT == TKD_BFP4 ? 4 : XT / 2;  // units of a whole chunk
             const int nunits = (ntiles + 1) >> 1;
+            const int u0 = (int)((uint32_t)grp - useq) & (G - 1);  // the group's first unit of this chunk
+            load_x(xnext, (int)hd.z, (int)((uint32_t)grp - (useq + nunits)) & (G - 1));  // (used a whole chunk from now)
+            const uint32_t gb = ring_a + slot * p.stage_bytes + rg0 * nsa * F::SAB;
+            bool ok = true;
+            // The group's units of the chunk (unrolled: the x pieces are indexed at compile time): the slot is waited
+            // for, both tiles decoded and stored, then one proxy fence and one arrival.
 #pragma unroll
-            for (int u = 0; u < UPC; ++u) {
-                if (u >= nunits || !ok) break;
+            for (int i = 0; i < MU; ++i) {
+                const int u = u0 + G * i;
+                if (u >= nunits) break;
                 const uint32_t us = useq + u, ps = us % kTcSlots;
                 ok = mbar_wait(aempty0 + 8 * ps, ((us / kTcSlots) & 1) ^ 1, p.status);
                 if (!ok) break;
                 const uint32_t sb = ops0 + ps * kTcSlot, ta = alane + ps * 2 * kTcACols;
-                if constexpr (FMT == TKD_BFP4) {
-                    if (2 * u + h < ntiles) do_tile(u, sb, ta, h);
-                } else {
-                    do_tile(2 * u, sb, ta, 0);
-                    if (2 * u + 1 < ntiles) do_tile(2 * u + 1, sb, ta, 1);
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub) {
+                    const int ti = 2 * u + sub;  // the tile of the chunk
+                    if (ti >= ntiles) break;
+#pragma unroll
+                    for (int r = 0; r < RG; ++r) {
+                        const uint32_t tr = ta + ((uint32_t)(16 * r) << 16) + sub * kTcACols;
+                        const uint32_t gr = gb + r * nsa * F::SAB;
+                        if constexpr (FMT == TKD_BFP4) {
+                            decode_sa(gr + ti * F::SAB, tr);  // (a super-atom is a whole tile)
+                        } else {
+                            decode_sa(gr + 2 * ti * F::SAB, tr);
+                            if (2 * ti + 1 < nsa) decode_sa(gr + (2 * ti + 1) * F::SAB, tr + 16);
+                        }
+                    }
+#pragma unroll
+                    for (int pp = 0; pp < PP; ++pp) {
+                        const uint4 v = xcur[(2 * i + sub) * PP + pp];
+                        const uint32_t xb = sb + sub * kTcXTile;
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(xb + xdst0[pp]), "r"(v.x), "r"(v.y) : "memory");
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(xb + xdst1[pp]), "r"(v.z), "r"(v.w) : "memory");
+                    }
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");  // this warp's tensor-memory stores are done
                 tc_fence_before();
@@ -345,12 +389,15 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * slot);
             if (++slot == (uint32_t)nst) slot = 0, phase ^= 1;
-            if (hd.x & ST_END) break;
+            if (at_end) break;
         }
-    } else if (warp == kTcMmaWarp) {
-        // ---------------------------------------------------------------- the MMA issuer (the warp walks the loop, one
-        // lane issues)
+    } else if (tc_mma_warp(warp) >= 0) {
+        // ---------------------------------------------------------------- the MMA issuers (a warp walks the loop, one
+        // lane issues). Two warps take the units of a slice in turn (unit i of the slice: warp i & 1), each with an
+        // accumulator of its own per set: issuing a unit's eight MMAs costs a warp ~450 ns beside the decode warps (45
+        // cycles an MMA on an idle SM, about 115 here), more than the decode of a unit takes.
         {
+            const int mw = tc_mma_warp(warp);
             Cursor c;
             uint32_t us = 0;
             bool ok = true;
@@ -370,42 +417,40 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                 ok = mbar_wait_parked(accempty0 + 8 * buf, (((uint32_t)j >> 1) & 1) ^ 1, p.status);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d = tmem0 + kTcAcc0 + buf * 128;
+                const uint32_t d = tmem0 + kTcAcc0 + buf * 64 + mw * 32;
                 uint32_t acc = 0;
+                int ui = 0;  // the unit's number within the slice
                 for (int ch = 0; ch < nch && ok; ++ch) {
                     int kleft = min(CK, kv - ch * CK);  // k of this chunk not yet multiplied
-                    for (; kleft > 0 && ok; ++us) {
+                    for (; kleft > 0 && ok; ++us, ++ui, kleft -= 128) {
                         const uint32_t ps = us % kTcSlots;
                         ok = mbar_wait(afull0 + 8 * ps, (us / kTcSlots) & 1, p.status);
                         if (!ok) break;
+                        if (ui % kTcMmaWarps != mw) {
+                            // another warp's unit. This warp has seen the slot's barrier pass all the same and says so:
+                            // a parity wait tells phases n and n + 2 apart only for a warp that has watched every one,
+                            // and the decode warps refill a slot only when every MMA warp is past its last use.
+                            if (lane == 0) mbar_arrive(aempty0 + 8 * ps);
+                            continue;
+                        }
                         tc_fence_after();  // (the decode warps' tensor-memory stores, completed before they arrived)
                         if (lane == 0) {
                             uint32_t al = alo0 + ps * 2 * kTcACols, bl = blo0 + ps * (kTcSlot >> 4);
-                            if (kleft >= 128) {
-                                // (a whole unit: two tiles of four blocks of 16 k; block j of a tile to accumulator j)
-                                tc_mma(d, al, bl, dhi, acc);
-                                tc_mma(d + 32, al + 8, bl + 2, dhi, acc);
-                                tc_mma(d + 64, al + 16, bl + 4, dhi, acc);
-                                tc_mma(d + 96, al + 24, bl + 6, dhi, acc);
-                                al += kTcACols, bl += kTcXTile >> 4;
-                                tc_mma(d, al, bl, dhi, 1);
-                                tc_mma(d + 32, al + 8, bl + 2, dhi, 1);
-                                tc_mma(d + 64, al + 16, bl + 4, dhi, 1);
-                                tc_mma(d + 96, al + 24, bl + 6, dhi, 1);
-                            } else {
-                                const int nb = (kleft + 15) >> 4;  // a short last unit of K
-                                for (int b = 0; b < nb; ++b) {
-                                    if (b == 4) al += kTcACols - 32, bl += (kTcXTile >> 4) - 8;
-                                    tc_mma(d + 32 * (b & 3), al + 8 * b, bl + 2 * b, dhi, b >= 4 ? 1u : acc);
-                                }
+                            // (the unit's blocks of 16 k, eight if it is whole: two tiles of four)
+                            const int nb = kleft >= 128 ? 8 : (kleft + 15) >> 4;
+#pragma unroll
+                            for (int b = 0; b < 8; ++b) {
+                                if (b >= nb) break;
+                                if (b == 4) al += kTcACols - 32, bl += (kTcXTile >> 4) - 8;
+                                tc_mma(d, al + 8 * b, bl + 2 * b, dhi, b ? 1u : acc);
                             }
                             tc_commit(aempty0 + 8 * ps);
                         }
                         acc = 1;
-                        kleft -= 128;
                         __syncwarp();
                     }
                 }
+                // (a warp without a unit in this slice commits all the same: the barrier counts both)
                 if (ok && lane == 0) tc_commit(accfull0 + 8 * buf);
                 __syncwarp();
             }
@@ -440,37 +485,42 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                 }
             }
             const uint32_t buf = (uint32_t)j & 1;
-            ok = mbar_wait_parked(accfull0 + 8 * buf, ((uint32_t)j >> 1) & 1, p.status);
+            ok = mbar_wait(accfull0 + 8 * buf, ((uint32_t)j >> 1) & 1, p.status);
             if (!ok) break;
             tc_fence_after();
             {
-                // the slice's sum: ((d0 + d1) + d2) + d3 over the accumulators the slice touched (all four unless it is
-                // shorter than 64 k), sixteen rows at a time
+                // the slice's sum d0 + d1 (d1 only if the slice has a second unit), sixteen rows at a time: both
+                // accumulators' loads are in flight together, and rows past M are not read at all
                 const int kv = min(p.ks, K - c.slice * p.ks);
-                const int nacc = min(4, (kv + 15) / 16);
-                const uint32_t ta = tmem0 + ((uint32_t)(ow * 32) << 16) + kTcAcc0 + buf * 128;
-                auto ld16 = [&](uint32_t addr, float (&o)[16], bool add) {
-                    uint32_t r[16];
+                const bool two = kv > 128;
+                const uint32_t ta = tmem0 + ((uint32_t)(ow * 32) << 16) + kTcAcc0 + buf * 64;
+                auto ld16 = [&](uint32_t addr, uint32_t (&r)[16]) {
                     asm volatile(
                         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                         : "r"(addr)
                         : "memory");
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                    for (int m = 0; m < 16; ++m) o[m] = add ? o[m] + __uint_as_float(r[m]) : __uint_as_float(r[m]);
                 };
 #pragma unroll 1
-                for (int hf = 0; hf < 2; ++hf) {
-                    float v[16];
-                    ld16(ta + 16 * hf, v, false);
-#pragma unroll 1
-                    for (int a = 1; a < nacc; ++a) ld16(ta + 32 * a + 16 * hf, v, true);
+                for (int hf = 0; hf < (M > 16 ? 2 : 1); ++hf) {
+                    uint32_t r0[16], r1[16];
+                    ld16(ta + 16 * hf, r0);
+                    if (two)
+                        ld16(ta + 32 + 16 * hf, r1);
+                    else {
+#pragma unroll
+                        for (int m = 0; m < 16; ++m) r1[m] = 0u;
+                    }
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     // the running sums of this thread's column: they start over with the slice, or the slice is added
 #pragma unroll
                     for (int m = 0; m < 16; m += 4) {
-                        float4 q = make_float4(v[m], v[m + 1], v[m + 2], v[m + 3]);
+                        float4 q;
+                        q.x = two ? __uint_as_float(r0[m]) + __uint_as_float(r1[m]) : __uint_as_float(r0[m]);
+                        q.y = two ? __uint_as_float(r0[m + 1]) + __uint_as_float(r1[m + 1]) : __uint_as_float(r0[m + 1]);
+                        q.z = two ? __uint_as_float(r0[m + 2]) + __uint_as_float(r1[m + 2]) : __uint_as_float(r0[m + 2]);
+                        q.w = two ? __uint_as_float(r0[m + 3]) + __uint_as_float(r1[m + 3]) : __uint_as_float(r0[m + 3]);
                         if (!f.start) {
                             const float4 o = *reinterpret_cast<const float4*>(trow + 16 * hf + m);
                             q = make_float4(o.x + q.x, o.y + q.y, o.z + q.z, o.w + q.w);
@@ -551,7 +601,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                 const float *gp = trow, *up = trow;
                 if (glu) {
 #pragma unroll 1
-                    for (int m = 0; m < MR; m += 4) {
+                    for (int m = 0; m < (M > 16 ? 32 : 16); m += 4) {
                         float4 v = *reinterpret_cast<float4*>(trow + m);
                         v.x = v.x * colf * colg * cols, v.y = v.y * colf * colg * cols;
                         v.z = v.z * colf * colg * cols, v.w = v.w * colf * colg * cols;
