@@ -28,8 +28,8 @@
 //   warps 0, 2     one lane of each issues MMAs: D[128 columns, 32 rows] += A (tensor memory) x (x tile)^T, 4 x (K = 16)
 //                  a tile, tcgen05.commit onto the unit's "empty" barrier and, at a slice's end, the accumulators' "full"
 //
-// A slice's sum is accumulated from zero in tensor memory, in two accumulators of 32 columns: two MMA warps take
-// the slice's units in turn, each into its own accumulator; the slice's sum is d0 + d1. Two such sets, so that the MMAs of the next slice run while
+// A slice's sum is accumulated from zero in tensor memory, in two accumulators of 32 columns (the slice's even units
+// in d0, its odd units in d1; the slice's sum is d0 + d1). Two such sets, so that the MMAs of the next slice run while
 // the output warps drain this one. A column's sum is the ascending sum of its slices' sums in plain fp32 adds, as in
 // tkd_stream_kernel, so it depends on K, the format and ks only. No cluster, no multicast, no
 // second CTA: cta_group::1 throughout. Every wait is bounded; the kernel always reaches its end, where the warp that
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
         }
         for (int s = 0; s < kTcSlots; ++s) {
             mbar_init(afull0 + 8 * s, NWT);
-            mbar_init(aempty0 + 8 * s, kTcMmaWarps);
+            mbar_init(aempty0 + 8 * s, 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(accfull0 + 8 * s, kTcMmaWarps);
@@ -218,6 +218,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
         // groups of 16 panel columns are among them.
         constexpr int G = kTcGroups, RG = G / 2, PP = G / 2;
         static_assert(kTcSlots % G == 0 && (G == 2 || G == 4), "a slot belongs to one group");
+        static_assert(kTcSlots % kTcMmaWarps == 0 && kTcMmaWarps == 2, "and to one MMA warp");
         const int cw = warp - kTcDecodeWarp0;
         const int qtr = warp & 3, sub4 = cw >> 2;  // (any four warps in a row cover the four quarters)
         const int grp = G == 2 ? sub4 >> 1 : sub4;                  // this warp's group
@@ -393,13 +394,17 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
         }
     } else if (tc_mma_warp(warp) >= 0) {
         // ---------------------------------------------------------------- the MMA issuers (a warp walks the loop, one
-        // lane issues). Two warps take the units of a slice in turn (unit i of the slice: warp i & 1), each with an
-        // accumulator of its own per set: issuing a unit's eight MMAs costs a warp ~450 ns beside the decode warps (45
-        // cycles an MMA on an idle SM, about 115 here), more than the decode of a unit takes.
+        // lane issues). Issuing a unit's eight MMAs costs a warp ~450 ns beside the decode warps (60 cycles an MMA on an
+        // idle SM, about 115 here) and its loop as much again, more than the decode of a unit takes: two warps share the
+        // units by their number in the CTA's sequence (even: the first warp; odd: the second), so that a slot's
+        // barriers are always the same warp's and it sees every phase of them (a parity wait tells phase n from n + 2
+        // only then). The accumulator is chosen by the unit's number within its SLICE (even: d0, odd: d1), so that a
+        // slice's sums do not depend on where in the sequence it starts; the two warps are on opposite parities at
+        // any time, hence on different accumulators.
         {
             const int mw = tc_mma_warp(warp);
             Cursor c;
-            uint32_t us = 0;
+            uint32_t us = 0;  // units before this slice
             bool ok = true;
             // the descriptor of slot 0's first x tile as 32-bit halves (a slot further on is kTcSlot / 16 more in the low
             // half, a tile kTcXTile / 16, a block of 16 k 2 more); the A operand: tensor-memory columns, 8 a block
@@ -411,45 +416,35 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                 else
                     cursor_next(c, p);
                 const int kv = min(p.ks, K - c.slice * p.ks);
-                const int nch = (kv + CK - 1) / CK;
+                const int nu = (kv + 127) >> 7;  // units of the slice (a chunk is a whole number of units but for K's end)
                 const uint32_t buf = (uint32_t)j & 1;
                 // the accumulators must have been read out (the slice two before this one)
                 ok = mbar_wait_parked(accempty0 + 8 * buf, (((uint32_t)j >> 1) & 1) ^ 1, p.status);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d = tmem0 + kTcAcc0 + buf * 64 + mw * 32;
-                uint32_t acc = 0;
-                int ui = 0;  // the unit's number within the slice
-                for (int ch = 0; ch < nch && ok; ++ch) {
-                    int kleft = min(CK, kv - ch * CK);  // k of this chunk not yet multiplied
-                    for (; kleft > 0 && ok; ++us, ++ui, kleft -= 128) {
-                        const uint32_t ps = us % kTcSlots;
-                        ok = mbar_wait(afull0 + 8 * ps, (us / kTcSlots) & 1, p.status);
-                        if (!ok) break;
-                        if (ui % kTcMmaWarps != mw) {
-                            // another warp's unit. This warp has seen the slot's barrier pass all the same and says so:
-                            // a parity wait tells phases n and n + 2 apart only for a warp that has watched every one,
-                            // and the decode warps refill a slot only when every MMA warp is past its last use.
-                            if (lane == 0) mbar_arrive(aempty0 + 8 * ps);
-                            continue;
-                        }
-                        tc_fence_after();  // (the decode warps' tensor-memory stores, completed before they arrived)
-                        if (lane == 0) {
-                            uint32_t al = alo0 + ps * 2 * kTcACols, bl = blo0 + ps * (kTcSlot >> 4);
-                            // (the unit's blocks of 16 k, eight if it is whole: two tiles of four)
-                            const int nb = kleft >= 128 ? 8 : (kleft + 15) >> 4;
+                const uint32_t dbase = tmem0 + kTcAcc0 + buf * 64;
+                for (int ui = (int)(((uint32_t)mw - us) & 1u); ui < nu; ui += 2) {
+                    const uint32_t g = us + ui, ps = g % kTcSlots;
+                    ok = mbar_wait(afull0 + 8 * ps, (g / kTcSlots) & 1, p.status);
+                    if (!ok) break;
+                    tc_fence_after();  // (the decode warps' tensor-memory stores, completed before they arrived)
+                    if (lane == 0) {
+                        const uint32_t d = dbase + (ui & 1) * 32, acc = ui >= 2;
+                        uint32_t al = alo0 + ps * 2 * kTcACols, bl = blo0 + ps * (kTcSlot >> 4);
+                        // (the unit's blocks of 16 k, eight if it is whole: two tiles of four)
+                        const int kleft = kv - 128 * ui;
+                        const int nb = kleft >= 128 ? 8 : (kleft + 15) >> 4;
 #pragma unroll
-                            for (int b = 0; b < 8; ++b) {
-                                if (b >= nb) break;
-                                if (b == 4) al += kTcACols - 32, bl += (kTcXTile >> 4) - 8;
-                                tc_mma(d, al + 8 * b, bl + 2 * b, dhi, b ? 1u : acc);
-                            }
-                            tc_commit(aempty0 + 8 * ps);
+                        for (int b = 0; b < 8; ++b) {
+                            if (b >= nb) break;
+                            if (b == 4) al += kTcACols - 32, bl += (kTcXTile >> 4) - 8;
+                            tc_mma(d, al + 8 * b, bl + 2 * b, dhi, b ? 1u : acc);
                         }
-                        acc = 1;
-                        __syncwarp();
+                        tc_commit(aempty0 + 8 * ps);
                     }
+                    __syncwarp();
                 }
+                us += nu;
                 // (a warp without a unit in this slice commits all the same: the barrier counts both)
                 if (ok && lane == 0) tc_commit(accfull0 + 8 * buf);
                 __syncwarp();
@@ -597,6 +592,108 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                 }
                 const float cols = p.scale_dt != TKD_DT_NONE && in_w ? sc : 1.f;
                 const bool glu = p.epi == TKD_EPI_GLU_IL || glu2;
+                if (topk_k == 0) {
+                    // No records: the panel leaves through a transposition in shared memory. Every thread scales its own
+                    // column in place; then a lane is a ROW and a warp takes every fourth group of 8 output columns:
+                    // 8 sums of the row (consecutive lanes, consecutive words: no bank conflict), the epilogue, one
+                    // 16-byte store (two for fp32 output). A fifth of the instructions of a store per element, and the
+                    // peers get 16-byte stores too.
+                    const int mr = M > 16 ? 32 : 16;
+#pragma unroll 1
+                    for (int m = 0; m < mr; m += 4) {
+                        float4 v = *reinterpret_cast<float4*>(trow + m);
+                        v.x = v.x * colf * colg * cols, v.y = v.y * colf * colg * cols;
+                        v.z = v.z * colf * colg * cols, v.w = v.w * colf * colg * cols;
+                        *reinterpret_cast<float4*>(trow + m) = v;
+                    }
+                    bar_output_warps();
+                    const int nout = glu ? 64 : TKD_PANEL_COLS;        // output columns of the panel
+                    const int oc0 = sg.out_col0 + c.pl * nout;         // the first of them
+                    // how many of them exist (GLU, interleaved: output o needs column 64 (o >> 5) + (o & 31) + 32)
+                    int nv;
+                    if (!glu || glu2)
+                        nv = min(nout, sg.n_valid - c.pl * nout);
+                    else {
+                        const int left = sg.n_valid - c.pl * TKD_PANEL_COLS;  // columns of this panel that exist (a multiple of 64)
+                        nv = left >= 128 ? 64 : (left >= 64 ? 32 : 0);
+                    }
+                    const bool f32out = p.epi == TKD_EPI_OUT32;
+                    const int esz = f32out ? 4 : 2;
+                    const bool vec = ((reinterpret_cast<uintptr_t>(p.out) | (uintptr_t)(p.ldo * esz) | (uintptr_t)(oc0 * esz)) & 15) == 0;
+                    const int r = lane;
+                    if (r < M) {
+#pragma unroll 1
+                        for (int cc = ow; 8 * cc < nv; cc += 4) {
+                            float v[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int o = 8 * cc + i;
+                                if (glu) {
+                                    const int gc = glu2 ? o : 64 * (o >> 5) + (o & 31), uc = glu2 ? o + 64 : gc + 32;
+                                    v[i] = act_gate(tbuf[(size_t)gc * MP + r], p.act) * tbuf[(size_t)uc * MP + r];
+                                } else {
+                                    v[i] = tbuf[(size_t)o * MP + r];
+                                }
+                            }
+                            const int here = min(8, nv - 8 * cc);  // columns of this group that exist
+                            const size_t at = (size_t)r * p.ldo + oc0 + 8 * cc;
+                            if (f32out && p.res_dt == TKD_DT_F32) {
+                                const float* rp = static_cast<const float*>(p.res) + (size_t)r * p.ldr + oc0 + 8 * cc;
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    if (i < here) v[i] += rp[i];
+                            } else if (p.epi == TKD_EPI_RESIDUAL) {
+                                const uint16_t* rp = static_cast<const uint16_t*>(p.res) + (size_t)r * p.ldr + oc0 + 8 * cc;
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    if (i < here) v[i] += bf16_bits_to_f32(rp[i]);
+                            }
+                            if (f32out) {
+                                if (vec && here == 8) {
+                                    const float4 lo = make_float4(v[0], v[1], v[2], v[3]), hi = make_float4(v[4], v[5], v[6], v[7]);
+                                    float4* op = reinterpret_cast<float4*>(static_cast<float*>(p.out) + at);
+                                    op[0] = lo, op[1] = hi;
+                                    for (int q = 0; q < npeers; ++q)
+                                        if (p.peer_out[q]) {
+                                            float4* pp = reinterpret_cast<float4*>(static_cast<float*>(p.peer_out[q]) + at);
+                                            pp[0] = lo, pp[1] = hi;
+                                        }
+                                } else {
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) {
+                                        if (i >= here) break;
+                                        static_cast<float*>(p.out)[at + i] = v[i];
+                                        for (int q = 0; q < npeers; ++q)
+                                            if (p.peer_out[q]) static_cast<float*>(p.peer_out[q])[at + i] = v[i];
+                                    }
+                                }
+                            } else {
+                                uint16_t b[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) b[i] = f32_to_bf16_bits(v[i]);
+                                if (vec && here == 8) {
+                                    const uint4 w = make_uint4(b[0] | ((uint32_t)b[1] << 16), b[2] | ((uint32_t)b[3] << 16),
+                                                               b[4] | ((uint32_t)b[5] << 16), b[6] | ((uint32_t)b[7] << 16));
+                                    *reinterpret_cast<uint4*>(y16 + at) = w;
+                                    for (int q = 0; q < npeers; ++q)
+                                        if (p.peer_out[q]) *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.peer_out[q]) + at) = w;
+                                } else {
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) {
+                                        if (i >= here) break;
+                                        y16[at + i] = b[i];
+                                        for (int q = 0; q < npeers; ++q)
+                                            if (p.peer_out[q]) static_cast<uint16_t*>(p.peer_out[q])[at + i] = b[i];
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    bar_output_warps();  // tbuf is free again
+                    continue;
+                }
+                // With records: a store per element, eight rows at a time in a rolled loop (the same stage as
+                // tkd_stream_kernel's for 9 rows and more).
                 int ocol = -1;
                 const float *gp = trow, *up = trow;
                 if (glu) {
