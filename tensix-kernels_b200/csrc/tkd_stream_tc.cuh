@@ -83,6 +83,13 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_tmem, uint32_
         ::"r"(d_tmem), "r"(a_tmem), "r"(blo), "r"(bhi), "r"(kTcIdesc), "r"(accumulate)
         : "memory");
 }
+// One lane of a converged warp (the hardware's choice). Code under elect.sync instead of `lane == 0` came out faster
+// here: the descriptors and addresses of the MMAs it guards stay warp-uniform.
+__device__ __forceinline__ bool tc_elect() {
+    uint32_t e;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(e));
+    return e != 0;
+}
 // the barrier gets one arrival once every MMA issued so far by this thread has completed
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -428,7 +435,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                     ok = mbar_wait(afull0 + 8 * ps, (g / kTcSlots) & 1, p.status);
                     if (!ok) break;
                     tc_fence_after();  // (the decode warps' tensor-memory stores, completed before they arrived)
-                    if (lane == 0) {
+                    if (tc_elect()) {
                         const uint32_t d = dbase + (ui & 1) * 32, acc = ui >= 2;
                         uint32_t al = alo0 + ps * 2 * kTcACols, bl = blo0 + ps * (kTcSlot >> 4);
                         // (the unit's blocks of 16 k, eight if it is whole: two tiles of four)
