@@ -382,6 +382,7 @@ def main():
                 g = torch.Generator().manual_seed(77)
                 kw["res_t"] = ttnn.from_torch(torch.randn(1, 1, m, n_total, generator=g), dtype=ttnn.float32,
                                               layout=ttnn.TILE_LAYOUT, device=device)
+                case["res_gathered"] = kw["res_t"]
 
             def step(i):
                 return plain_step(i, y_t=outs[i % nbuf], col0=col_start // 32, exchange=ex, **kw)
@@ -590,7 +591,13 @@ def check_exchange(name, case, step, join, device, world, rank, m, n_loc, col_st
         want = torch.cat([gathered[q * umax : q * umax + int(c.item())] for q, c in enumerate(counts)])
         got = case["exchanged_records"][0].t.reshape(-1, want.shape[-1])[: want.shape[0]]
     else:
-        case["step"](0)  # plain: this rank's columns only, into its own output
+        kw = {}
+        if "res_gathered" in case:  # the plain call adds this rank's columns of the same residual
+            from common import ttnn_like as ttnn
+
+            part = case["res_gathered"].t[..., col_start : col_start + n_loc].contiguous()
+            kw["res_t"] = ttnn.Tensor(part, case["res_gathered"].dtype, ttnn.TILE_LAYOUT, device, None)
+        case["step"](0, **kw)  # plain: this rank's columns only, into its own output
         torch.cuda.synchronize()
         widths = [b - a for a, b in shards] if strong else [n_loc] * world
         starts = [a for a, _ in shards] if strong else [q * n_loc for q in range(world)]
