@@ -119,6 +119,39 @@ def test_matmul_against_oracle(device, fmt, m):
     linear.check_status(device)
 
 
+@pytest.mark.parametrize("fmt", ["bfp8", "bfp4", "bf16"])
+@pytest.mark.parametrize("m,n", [(9, 1024 + 16), (17, 1024 + 128), (32, 2048 + 80)])
+def test_many_rows_epilogues_against_oracle(device, fmt, m, n):
+    """The kernel for 9 to 32 rows: every epilogue, N with a ragged last panel, K with a short last slice."""
+    k = 1024 + 96
+    g = torch.Generator().manual_seed(7 * m + n)
+    w, w2 = torch.randn(n, k, generator=g) * 0.02, torch.randn(n, k, generator=g) * 0.02
+    x = torch.randn(m, k, generator=g)
+    tx = dev_x(device, x)
+    tw, _ = linear.native_weight(device, w, DT[fmt])
+    tw2, _ = linear.native_weight(device, w2, DT[fmt])
+    wk, _ = orc.native_values(w, fmt)
+    wk2, _ = orc.native_values(w2, fmt)
+    plain = orc.matmul_f64(x, wk)
+    close_bf16(host(linear.matmul(tx, tw, None)), plain)
+    # fp32 output with an fp32 residual
+    res = torch.randn(m, n, generator=g)
+    tr = ttnn.from_torch(res.reshape(1, 1, m, n), dtype=ttnn.float32, layout=ttnn.TILE_LAYOUT, device=device)
+    y32 = host(linear.matmul(tx, tw, None, residual=tr, out32=True)).double().numpy()
+    np.testing.assert_allclose(y32, plain + res.double().numpy(), rtol=2e-3, atol=2e-3)
+    # bf16 residual
+    resb = res.to(torch.bfloat16)
+    trb = ttnn.from_torch(resb.reshape(1, 1, m, n), dtype=ttnn.bfloat16, layout=ttnn.TILE_LAYOUT, device=device)
+    close_bf16(host(linear.matmul(tx, tw, None, residual=trb)), plain + resb.double().numpy())
+    # column scales
+    sc = (torch.rand(n, generator=g) + 0.5).to(torch.bfloat16)
+    close_bf16(host(linear.matmul(tx, tw, linear.scale_tensor(device, sc.float()))), plain * sc.double().numpy()[None, :])
+    # SwiGLU from two weights
+    gate, up = torch.from_numpy(plain), torch.from_numpy(orc.matmul_f64(x, wk2))
+    close_bf16(host(linear.matmul(tx, tw, None, w_up=tw2, glu=True)), (torch.nn.functional.silu(gate) * up).numpy())
+    linear.check_status(device)
+
+
 def test_config_shapes_full_size(device):
     """The benchmark configurations at their own sizes against the oracle over every column: the README example
     (one token through a [4096, 2048] bfloat8_b weight), the MLP gate/up pair (two [14336, 4096] bfloat4_b weights,
