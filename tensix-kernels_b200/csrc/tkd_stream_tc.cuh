@@ -410,7 +410,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
         // any time, hence on different accumulators.
         {
             const int mw = tc_mma_warp(warp);
-            Cursor c;
+            int slice = 0;    // the item's slice of its panel: all this role needs to know of it
             uint32_t us = 0;  // units before this slice
             bool ok = true;
             // the descriptor of slot 0's first x tile as 32-bit halves (a slot further on is kTcSlot / 16 more in the low
@@ -418,15 +418,17 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
             const uint64_t bd0 = tc_desc(ops0);
             const uint32_t dhi = (uint32_t)(bd0 >> 32), blo0 = (uint32_t)bd0, alo0 = tmem0 + kTcA0;
             for (int64_t j = 0; j < nitems && ok; ++j) {
-                if (j == 0 || j == lead)
-                    cursor_init(c, p, item_at(j));
-                else
-                    cursor_next(c, p);
-                const int kv = min(p.ks, K - c.slice * p.ks);
+                if (j == 0 || j == lead) {
+                    const int64_t it = item_at(j);
+                    slice = (int)(it - idiv(p, it, p.nslices) * p.nslices);
+                } else if (++slice == p.nslices) {
+                    slice = 0;
+                }
+                const int kv = min(p.ks, K - slice * p.ks);
                 const int nu = (kv + 127) >> 7;  // units of the slice (a chunk is a whole number of units but for K's end)
                 const uint32_t buf = (uint32_t)j & 1;
                 // the accumulators must have been read out (the slice two before this one)
-                ok = mbar_wait_parked(accempty0 + 8 * buf, (((uint32_t)j >> 1) & 1) ^ 1, p.status);
+                ok = mbar_wait(accempty0 + 8 * buf, (((uint32_t)j >> 1) & 1) ^ 1, p.status);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t dbase = tmem0 + kTcAcc0 + buf * 64;
