@@ -488,6 +488,18 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                                                    : static_cast<const float*>(sp)[n];
                 }
             }
+            if (f.deliver && p.res && topk_k == 0) {
+                // the panel's residual on its way to L2 while the slice is still being multiplied: row et & 31, line et >> 5
+                // of the row's 128 (GLU: 64) columns
+                const int rr = et & 31, ln = et >> 5, rsz_ = p.res_dt == TKD_DT_F32 ? 4 : 2;
+                const int ncol = (p.epi == TKD_EPI_GLU_IL || glu2) ? 64 : TKD_PANEL_COLS;
+                const int nout_valid = p.epi == TKD_EPI_GLU_IL ? sg.n_valid / 2 : sg.n_valid;  // (only elements that exist)
+                if (rr < M && ln * 128 < ncol * rsz_ && c.pl * ncol + ln * (128 / rsz_) < nout_valid) {
+                    const char* rp = static_cast<const char*>(p.res) +
+                                     ((size_t)rr * p.ldr + sg.out_col0 + (size_t)c.pl * ncol) * rsz_ + ln * 128;
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(rp));
+                }
+            }
             const uint32_t buf = (uint32_t)j & 1;
             ok = mbar_wait(accfull0 + 8 * buf, ((uint32_t)j >> 1) & 1, p.status);
             if (!ok) break;
@@ -630,9 +642,34 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                     const int esz = f32out ? 4 : 2;
                     const bool vec = ((reinterpret_cast<uintptr_t>(p.out) | (uintptr_t)(p.ldo * esz) | (uintptr_t)(oc0 * esz)) & 15) == 0;
                     const int r = lane;
-                    if (r < M) {
+                    // the residual of this lane's groups, asked for with 16-byte loads two groups ahead (four round trips to
+                    // L2 one after the other were most of this stage)
+                    const bool res32 = f32out && p.res_dt == TKD_DT_F32, res16 = p.epi == TKD_EPI_RESIDUAL;
+                    const int rsz = res32 ? 4 : 2;
+                    const bool rvec = vec && (res32 || res16) &&
+                                      ((reinterpret_cast<uintptr_t>(p.res) | (uintptr_t)(p.ldr * rsz) | (uintptr_t)(oc0 * rsz)) & 15) == 0;
 #pragma unroll 1
-                        for (int cc = ow; 8 * cc < nv; cc += 4) {
+                    for (int half = 0; half < 2 && r < M; ++half) {  // (two of a warp's four groups at a time)
+                        uint4 rq[2][2];
+                        if (rvec) {
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                const int cc = ow + 4 * (2 * half + i);
+                                if (8 * cc + 8 <= nv) {
+                                    const size_t ra = (size_t)r * p.ldr + oc0 + 8 * cc;
+                                    if (res32) {
+                                        const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const float*>(p.res) + ra);
+                                        rq[i][0] = rp[0], rq[i][1] = rp[1];
+                                    } else {
+                                        rq[i][0] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.res) + ra);
+                                    }
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int gi = 0; gi < 2; ++gi) {
+                            const int cc = ow + 4 * (2 * half + gi);
+                            if (8 * cc >= nv) break;
                             float v[8];
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
@@ -646,12 +683,25 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                             }
                             const int here = min(8, nv - 8 * cc);  // columns of this group that exist
                             const size_t at = (size_t)r * p.ldo + oc0 + 8 * cc;
-                            if (f32out && p.res_dt == TKD_DT_F32) {
+                            if (rvec && here == 8) {
+                                const uint4 q0 = rq[gi][0], q1 = rq[gi][1];
+                                if (res32) {
+                                    v[0] += __uint_as_float(q0.x), v[1] += __uint_as_float(q0.y);
+                                    v[2] += __uint_as_float(q0.z), v[3] += __uint_as_float(q0.w);
+                                    v[4] += __uint_as_float(q1.x), v[5] += __uint_as_float(q1.y);
+                                    v[6] += __uint_as_float(q1.z), v[7] += __uint_as_float(q1.w);
+                                } else {
+                                    v[0] += __uint_as_float(q0.x << 16), v[1] += __uint_as_float(q0.x & 0xFFFF0000u);
+                                    v[2] += __uint_as_float(q0.y << 16), v[3] += __uint_as_float(q0.y & 0xFFFF0000u);
+                                    v[4] += __uint_as_float(q0.z << 16), v[5] += __uint_as_float(q0.z & 0xFFFF0000u);
+                                    v[6] += __uint_as_float(q0.w << 16), v[7] += __uint_as_float(q0.w & 0xFFFF0000u);
+                                }
+                            } else if (res32) {
                                 const float* rp = static_cast<const float*>(p.res) + (size_t)r * p.ldr + oc0 + 8 * cc;
 #pragma unroll
                                 for (int i = 0; i < 8; ++i)
                                     if (i < here) v[i] += rp[i];
-                            } else if (p.epi == TKD_EPI_RESIDUAL) {
+                            } else if (res16) {
                                 const uint16_t* rp = static_cast<const uint16_t*>(p.res) + (size_t)r * p.ldr + oc0 + 8 * cc;
 #pragma unroll
                                 for (int i = 0; i < 8; ++i)
