@@ -1,8 +1,8 @@
 // tkd_stream_kernel.cuh: the weight-streaming decode matmul for sm_100a (the kernel template; tkd_stream_bfp8.cu,
 // tkd_stream_bfp4.cu and tkd_stream_bf16.cu each compile one format's instantiations of it).
 //
-// y[m, n] = sum_k x[m, k] * w[k, n] with its fused output stage, M <= 32 activation rows, the weight a packed HBM
-// stream (tkd_layout.h). It takes the place of the reference's three Tensix kernels (dense_reader/kernels/
+// y[m, n] = sum_k x[m, k] * w[k, n] with its fused output stage, M <= 8 activation rows (9 to 32 rows:
+// tkd_stream_tc.cuh, which shares this file's helpers), the weight a packed HBM stream (tkd_layout.h). It takes the place of the reference's three Tensix kernels (dense_reader/kernels/
 // dense_reader.cpp: the DRAM loads; dense_compute.cpp: matmul_block accumulation and the output stages;
 // dense_writer.cpp: output writes and the running top-k) and of the work split linear.plan makes for them
 // (dense_reader/linear.py:187-382).
@@ -14,9 +14,9 @@
 //   warps 1-16    streaming warps: warp (group g, half h) multiplies the 16 columns of group g by every other
 //                 super-atom of the chunk with mma.sync m16n8k16, the weights as A. Block-float codes go in as bf16
 //                 subnormals (sign << 15 | magnitude) and the shared exponent is folded into the activations
-//                 (x * 2^e' is exact), so a register of two weights costs one rotate and one AND. The activations come
-//                 straight from global memory through L1 (16 bytes a lane per 32 k), loaded before the stage is waited
-//                 for.
+//                 (x * 2^e' is exact), so a register of two weights costs one rotate and one AND. The one row of a
+//                 decode call lies in shared memory whole; two to eight rows come straight from global memory through
+//                 L1 (16 bytes a lane per 32 k), loaded before the stage is waited for.
 //   warps 17-20   output warps (one thread per column of the panel): finish the K sum, run the output stage (exponent
 //                 factor, scales, SwiGLU/GeGLU, residual, rounding), write y, and keep the top-k records.
 //
@@ -287,17 +287,15 @@ enum : uint32_t {
 // addresses of this lane's code and exponent words of super-atom h; xb[m]: this lane's row of x at k = 8 t + h * KSA;
 // kc: the chunk's first k. FULL: the chunk has all its super-atoms and ends within K (then xpre holds the activations,
 // loaded before the stage was waited for, when PRE).
-// XS: the activations come from the stage's tile in shared memory instead (xt_a: this lane's row of it, xj: the 16-byte
-// piece of the row its first block starts at, xsw: the row's swizzle). XSM: a one-row call keeps all of x in shared
-// memory (zero-filled up to a whole chunk): xt_a is the address of this lane's 16 bytes of the chunk's first block.
-template <int FMT, int MT, int NA, bool FULL, bool PRE, bool XS = false, bool XSM = false>
+// XSM: a one-row call keeps all of x in shared memory (zero-filled up to a whole chunk): xt_a is the address of this
+// lane's 16 bytes of the chunk's first block.
+template <int FMT, int MT, int NA, bool FULL, bool PRE, bool XSM = false>
 __device__ __forceinline__ void chunk_mma(float (&acc)[NA][MT][4], uint32_t code_a, uint32_t exp_a,
                                           const uint4 (&xpre)[Fmt<FMT>::SUBSA / 2 * Fmt<FMT>::XB][MT],
                                           const uint16_t* const (&xb)[MT], int kc, int K, int h, int nsa, const uint2 sh,
-                                          uint32_t xt_a = 0, int xj = 0, int xsw = 0) {
+                                          uint32_t xt_a = 0) {
     using F = Fmt<FMT>;
     constexpr int NPW = F::SUBSA / 2;  // super-atoms a warp takes of a chunk
-    constexpr int XROW = F::SUBSA * F::KSA * 2;  // bytes of a tile row
 #pragma unroll
     for (int i = 0; i < NPW; ++i) {
         if (!FULL && h + 2 * i >= nsa) break;
@@ -322,8 +320,6 @@ __device__ __forceinline__ void chunk_mma(float (&acc)[NA][MT][4], uint32_t code
             for (int m = 0; m < MT; ++m) {
                 if constexpr (XSM)  // (the one row of x, whole, in shared memory: xt_a is this lane's address at k = kc)
                     xv[m] = lds128(xt_a + (2 * i * F::KSA + 32 * q) * 2);
-                else if constexpr (XS)
-                    xv[m] = lds128(xt_a + m * 8 * XROW + (((xj + (2 * i * F::KSA + 32 * q) / 8) ^ xsw) << 4));
                 else if constexpr (FULL && PRE)
                     xv[m] = xpre[i * F::XB + q][m];
                 else
@@ -450,29 +446,30 @@ __device__ __forceinline__ void exchange_done(const TkdParams& p, int lane, int 
     }
 }
 
-// SW: streaming warps, 16 (a warp per column group and half of each chunk's super-atoms) or 8 (a warp takes both halves
-// of its group, one after the other: the 32-row kernel, whose accumulators need the registers that fewer warps leave).
+// The kernel for 1 to 8 rows (9 to 32 run tkd_stream_tc_kernel). Sixteen streaming warps: a warp per column group and half
+// of each chunk's super-atoms.
 // ONE: the call has one row (the decode case): the row count is a constant 1 and everything that serves more rows falls
 // away at compile time. (The length of this kernel's code matters beyond the parts that run: adding two more instances
 // of the output stage for 2 and 4 rows made the one-row call 1.5 us slower.)
 // PLAIN: no top-k records and no exchange with other GPUs (the plain matmuls of a decode step): that code falls away too.
 // KWHOLE: K is a whole number of chunks, so the code for a last, shorter chunk falls away as well.
-template <int FMT, int MT, int SW, bool ONE, bool PLAIN, bool KWHOLE>
-__global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const __grid_constant__ TkdParams p) {
+constexpr int kStreamWarps = 16;
+template <int FMT, bool ONE, bool PLAIN, bool KWHOLE>
+__global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_kernel(const __grid_constant__ TkdParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     using F = Fmt<FMT>;
-    constexpr int MP = MT == 1 ? 8 : (MT == 2 ? 24 : 40);  // floats per column in the hand-over buffers
-    constexpr int MR = 8 * MT;                             // rows the accumulators cover
-    constexpr int NA = MT == 1 ? 2 : 1;                    // accumulator sets a streaming warp alternates between
+    constexpr int SW = kStreamWarps;
+    constexpr int MT = 1;   // m16n8 tiles of rows (8 rows each)
+    constexpr int MP = 8;   // floats per column in the hand-over buffers
+    constexpr int MR = 8;   // rows the accumulators cover
+    constexpr int NA = 2;   // accumulator sets a streaming warp alternates between
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TKD_MAX_STAGES);
-    const uint32_t pfull0 = smem_u32(bars + 2 * TKD_MAX_STAGES), pempty0 = pfull0 + 16, xfull0 = pfull0 + 32;
-    // NH: halves of a chunk's super-atoms a streaming warp takes; XS: the activations are staged in shared memory (two
-    // tiles of MR rows x one chunk of k, filled by the streaming warps' own asynchronous copies one stage ahead);
-    // NPB: hand-over buffers between the streaming and the output warps
-    constexpr int NH = 16 / SW;
-    constexpr bool XS = MT >= 2 && FMT != TKD_BFP4;
-    constexpr int NPB = MT == 4 ? 1 : 2;
+    const uint32_t pfull0 = smem_u32(bars + 2 * TKD_MAX_STAGES), pempty0 = pfull0 + 16;
+    // NH: halves of a chunk's super-atoms a streaming warp takes; NPB: hand-over buffers between the streaming and the
+    // output warps
+    constexpr int NH = 1;
+    constexpr int NPB = 2;
     volatile int* sflag = reinterpret_cast<volatile int*>(smem + TKD_SMEM_HEAD - 16);
     uint4* hdr = reinterpret_cast<uint4*>(smem + 512);  // one header per stage of the ring
     float* pbuf = reinterpret_cast<float*>(smem + p.off_pbuf);  // [2 buffers][2 halves][128 columns][MP]
@@ -490,7 +487,6 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
         for (int s = 0; s < 2; ++s) {
             mbar_init(pfull0 + 8 * s, SW);
             mbar_init(pempty0 + 8 * s, 4);
-            mbar_init(xfull0 + 8 * s, SW * 32);
         }
         sflag[0] = sflag[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -579,7 +575,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
         // (x, the scratch buffer and the outputs may belong to the kernel before this one: wait for it to complete)
         asm volatile("griddepcontrol.wait;" ::: "memory");
         const int cw = warp - 1;
-        const int g8 = cw & 7, h0 = SW == 16 ? cw >> 3 : 0;
+        const int g8 = cw & 7, h0 = cw >> 3;
         const int g = lane >> 2, t = lane & 3;
         constexpr int NX = F::SUBSA / 2 * F::XB;
         // XSM: a one-row call copies its row of x into shared memory once (K rounded up to a chunk, the rest zeros) and
@@ -587,26 +583,9 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
         // SM's memory given to the ring, each miss a trip to L2 behind the weight stream's traffic, and the stage waits
         // for its slowest warp.)
         constexpr bool XSM = ONE;
-        constexpr bool PRE = MT <= 2 && NH == 1 && !XS && !XSM;
-        constexpr int XROW = CK * 2, XTILE = MR * XROW, XPR = CK / 8;  // a tile row's bytes, a tile's, 16-byte pieces a row
+        // PRE: two to eight rows: the chunk's activations are loaded (through L1) before the stage is waited for
+        constexpr bool PRE = !XSM;
         const uint32_t xt0 = smem_u32(smem + p.off_xt);
-        // a tile row r keeps its 16-byte piece j at position j ^ swz(r): the eight lanes a shared-memory load serves
-        // together (two rows, four pieces each) then fall into eight different bank groups
-        auto swz = [](int r) { return ((r & 1) << 2) ^ ((r >> 1) & 3); };
-        auto load_x = [&](int buf, int k0) {
-            for (int e = cw * 32 + lane; e < MR * XPR; e += SW * 32) {
-                const int r = e / XPR, j = e - r * XPR;
-                if (k0 + j * 8 < K) {
-                    const uint16_t* src = p.x + (int64_t)min(r, M - 1) * p.ldx + k0 + j * 8;
-                    const uint32_t dst = xt0 + buf * XTILE + r * XROW + ((j ^ swz(r)) << 4);
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-                }
-            }
-            asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];" ::"r"(xfull0 + 8 * buf) : "memory");
-        };
-        const uint32_t xt_lane = xt0 + g * XROW;  // (rows 8 m + g of a tile: the swizzle depends on g alone)
-        const int xsw = swz(g);
-        uint32_t nstage = 0, prev_slot = 0, prev_phase = 0;
         constexpr int EXPB = FMT == TKD_BFP4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
         const uint16_t* xb[NH][MT];
 #pragma unroll
@@ -624,7 +603,6 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
         int kc = (int)(first_it - idiv(p, first_it, p.nslices) * p.nslices) * p.ks;
         float acc[NH][NA][MT][4], tot[NH][MT][4];
         const uint2 sh = make_uint2(p.mul16, p.mul128);
-        if constexpr (XS) load_x(0, kc);
         const uint32_t xs_lane = xt0 + (8 * t + h0 * F::KSA) * 2;
         if constexpr (XSM) {
             const int pieces = (K + CK - 1) / CK * (CK / 8);
@@ -649,26 +627,6 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             if (!mbar_wait(full0 + 8 * slot, phase, p.status)) break;
             const uint4 hd = lds128(hdr_a + 16 * slot);
             const uint32_t fl = hd.x;
-            if constexpr (XS) {
-                // the next stage's activations into the other tile, once every warp has left the stage before this one
-                // (whose tile that was); then this stage's own tile must have landed
-                if (!(fl & ST_END)) {
-                    if (nstage && !mbar_wait(empty0 + 8 * prev_slot, prev_phase, p.status)) break;
-                    load_x((nstage + 1) & 1, (int)hd.z);
-                }
-                if (!mbar_wait(xfull0 + 8 * (nstage & 1), (nstage >> 1) & 1, p.status)) break;
-                prev_slot = slot, prev_phase = phase, ++nstage;
-            } else if constexpr (!PRE && !XSM) {
-                // the activations of the stage after this one, asked into L1 now (the warps share the lines out): by the
-                // time that stage is computed its loads hit L1 instead of waiting for L2 one block at a time
-                constexpr int LPR = CK * 2 / 128;  // 128-byte lines of a row's share of a chunk
-                const int kn = (int)hd.z;
-                for (int i = cw * 32 + lane; i < M * LPR; i += SW * 32) {
-                    const int row = i / LPR, seg = i - row * LPR;
-                    if (kn + seg * 64 < K)
-                        asm volatile("prefetch.global.L1 [%0];" ::"l"(p.x + (int64_t)row * p.ldx + kn + seg * 64));
-                }
-            }
             if (fl & ST_FIRST) {
 #pragma unroll
                 for (int hh = 0; hh < NH; ++hh)
@@ -683,18 +641,14 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             for (int hh = 0; hh < NH; ++hh) {
                 const int h = h0 + hh;
                 if (full) {
-                    chunk_mma<FMT, MT, NA, true, PRE, XS, XSM>(acc[hh], sbase + code_off + hh * F::SAB,
-                                                               sbase + exp_off + hh * F::SAB, xpre, xb[hh], kc, K, h, F::SUBSA, sh,
-                                                               XSM ? xs_lane + kc * 2 : xt_lane + ((nstage + 1) & 1) * XTILE,
-                                                               h * F::KSA / 8 + t, xsw);
+                    chunk_mma<FMT, MT, NA, true, PRE, XSM>(acc[hh], sbase + code_off + hh * F::SAB, sbase + exp_off + hh * F::SAB,
+                                                           xpre, xb[hh], kc, K, h, F::SUBSA, sh, xs_lane + kc * 2);
                 } else {
                     // the last chunk of K: fewer super-atoms, the groups closer together
                     const int nsa = nsa_total - kc / CK * F::SUBSA;
                     const uint32_t gb = sbase + g8 * nsa * F::SAB + h * F::SAB;
-                    chunk_mma<FMT, MT, NA, false, PRE, XS, XSM>(acc[hh], gb + EXPB + lane * 16, gb + t * (EXPB / 4), xpre, xb[hh],
-                                                                kc, K, h, nsa, sh,
-                                                                XSM ? xs_lane + kc * 2 : xt_lane + ((nstage + 1) & 1) * XTILE,
-                                                                h * F::KSA / 8 + t, xsw);
+                    chunk_mma<FMT, MT, NA, false, PRE, XSM>(acc[hh], gb + EXPB + lane * 16, gb + t * (EXPB / 4), xpre, xb[hh], kc,
+                                                            K, h, nsa, sh, xs_lane + kc * 2);
                 }
             }
             __syncwarp();
@@ -751,7 +705,6 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             }
             if (fl & ST_END) break;
         }
-        if constexpr (XS) asm volatile("cp.async.wait_all;" ::: "memory");  // (none of this thread's copies may land later)
     } else {
         // ---------------------------------------------------------------- output warps
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -786,19 +739,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             ok = mbar_wait_parked(pfull0 + 8 * pb, (NPB == 2 ? pi >> 1 : pi) & 1, p.status);
             if (!ok) break;
             bool finish = !f.split;
-            // (9 rows and more: the column's sums live in the thread's row of tbuf, not in registers, and every loop over
-            // rows below is rolled: this code runs once or twice a CTA, at the speed of instruction cache misses, and
-            // unrolled over 32 rows it is thousands of instructions)
-            float* const trow = tbuf + (size_t)et * MP;
-            if (!f.split && MT >= 2) {
-                const float* p0 = pbuf + ((size_t)(pb * 2) * TKD_PANEL_COLS + et) * MP;
-                const float* p1 = p0 + (size_t)TKD_PANEL_COLS * MP;
-#pragma unroll 1
-                for (int m = 0; m < MR; m += 4) {
-                    const float4 a = *reinterpret_cast<const float4*>(p0 + m), b = *reinterpret_cast<const float4*>(p1 + m);
-                    *reinterpret_cast<float4*>(trow + m) = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
-                }
-            } else if (!f.split) {
+            if (!f.split) {
                 // the two halves' sums cover the whole panel
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
@@ -853,38 +794,6 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                                 if (s + j < p.nslices) t0 += v0[j], t1 += v1[j];
                         }
                         tot[0] = t0 + t1;
-                    } else if constexpr (MT >= 2) {
-                        // eight rows at a time (a rolled loop, the sums into tbuf); both halves' loads of four entries
-                        // (the sum so far counts as one) in flight together, unconditional (a row or entry that is not
-                        // there re-reads the last that is) so that they stay one block of code
-#pragma unroll 1
-                        for (int rb = 0; rb < M; rb += 8) {
-                            float th[2][8];
-#pragma unroll 1
-                            for (int s = pe - 1; s < p.nslices; s += 4) {
-                                float v[2][4][8];
-#pragma unroll
-                                for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j)
-#pragma unroll
-                                        for (int m = 0; m < 8; ++m)
-                                            v[hh][j][m] = term(min(s + j, p.nslices - 1), hh, min(rb + m, M - 1));
-#pragma unroll
-                                for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j)
-#pragma unroll
-                                        for (int m = 0; m < 8; ++m) {
-                                            if (s + j >= p.nslices) continue;
-                                            th[hh][m] = s + j == pe - 1 ? v[hh][j][m] : th[hh][m] + v[hh][j][m];
-                                        }
-                            }
-                            *reinterpret_cast<float4*>(trow + rb) =
-                                make_float4(th[0][0] + th[1][0], th[0][1] + th[1][1], th[0][2] + th[1][2], th[0][3] + th[1][3]);
-                            *reinterpret_cast<float4*>(trow + rb + 4) =
-                                make_float4(th[0][4] + th[1][4], th[0][5] + th[1][5], th[0][6] + th[1][6], th[0][7] + th[1][7]);
-                        }
                     } else {
 #pragma unroll 1
                         for (int hh = 0; hh < 2; ++hh) {
@@ -914,9 +823,9 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
             if (!finish) continue;
 
             // ------------------------------------------------------------ the output stage of one panel
-            // (a generic lambda over the rows it covers: a one-row call runs the one-row instance, a fraction of the code
-            // of the eight-, sixteen- or thirty-two-row one; this code runs once or twice a CTA, straight from the
-            // instruction cache's misses, so its length is its cost)
+            // (a generic lambda over the rows it covers: a one-row call runs the one-row instance, an eighth of the code of
+            // the eight-row one; this code runs once or twice a CTA, straight from the instruction cache's misses, so
+            // its length is its cost)
             uint16_t* y16 = static_cast<uint16_t*>(p.out);
             auto output_stage = [&](auto rows_const) {
                 constexpr int R = decltype(rows_const)::value;
@@ -995,78 +904,7 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
                     }
                 }
             };
-            if constexpr (MT >= 2) {
-                // the same stage from the sums in tbuf, eight rows at a time in a rolled loop
-                float colf = 1.f, colg = 1.f;  // the column's block-float factor (in two normal floats) and its scale
-                if constexpr (FMT != TKD_BF16) {
-                    const int e = tkd_out_exp(FMT, ebyte);
-                    const int e1 = e / 2, e2 = e - e1;
-                    colf = __uint_as_float((uint32_t)(e1 + 127) << 23), colg = __uint_as_float((uint32_t)(e2 + 127) << 23);
-                }
-                const float cols = p.scale_dt != TKD_DT_NONE && in_w ? sc : 1.f;
-                const bool glu = p.epi == TKD_EPI_GLU_IL || glu2;
-                int ocol = -1;
-                const float *gp = trow, *up = trow;
-                if (glu) {
-                    // every column's sums scaled in place, then the (gate, up) pairs read across columns
-#pragma unroll 1
-                    for (int m = 0; m < MR; m += 4) {
-                        float4 v = *reinterpret_cast<float4*>(trow + m);
-                        v.x = v.x * colf * colg * cols, v.y = v.y * colf * colg * cols;
-                        v.z = v.z * colf * colg * cols, v.w = v.w * colf * colg * cols;
-                        *reinterpret_cast<float4*>(trow + m) = v;
-                    }
-                    bar_output_warps();
-                    if (et < 64) {
-                        const int gc = glu2 ? et : 64 * (et >> 5) + (et & 31), uc = glu2 ? et + 64 : gc + 32;
-                        const int nw = glu2 ? n : c.pl * TKD_PANEL_COLS + uc;
-                        if (nw < sg.n_valid) ocol = sg.out_col0 + c.pl * 64 + et;
-                        gp = tbuf + (size_t)gc * MP, up = tbuf + (size_t)uc * MP;
-                    }
-                } else if (in_w) {
-                    ocol = sg.out_col0 + n;
-                }
-                const bool store = ocol >= 0 && (topk_k == 0 || p.write_y);
-                if (ocol >= 0) {
-#pragma unroll 1
-                    for (int r0 = 0; r0 < M; r0 += 8) {
-                        float v[8];
-#pragma unroll
-                        for (int m = 0; m < 8; ++m)
-                            v[m] = glu ? act_gate(gp[r0 + m], p.act) * up[r0 + m] : trow[r0 + m] * colf * colg * cols;
-                        // (the residual is read for all eight rows before anything is stored: see the one-row form)
-                        if (p.epi == TKD_EPI_OUT32 && p.res_dt == TKD_DT_F32) {
-#pragma unroll
-                            for (int m = 0; m < 8; ++m)
-                                if (r0 + m < M) v[m] += static_cast<const float*>(p.res)[(size_t)(r0 + m) * p.ldr + ocol];
-                        } else if (p.epi == TKD_EPI_RESIDUAL) {
-#pragma unroll
-                            for (int m = 0; m < 8; ++m)
-                                if (r0 + m < M)
-                                    v[m] += bf16_bits_to_f32(static_cast<const uint16_t*>(p.res)[(size_t)(r0 + m) * p.ldr + ocol]);
-                        }
-#pragma unroll
-                        for (int m = 0; m < 8; ++m) {
-                            if (r0 + m >= M) break;
-                            const size_t at = (size_t)(r0 + m) * p.ldo + ocol;
-                            if (p.epi == TKD_EPI_OUT32) {
-                                static_cast<float*>(p.out)[at] = v[m];
-                                for (int q = 0; q < npeers; ++q)
-                                    if (p.peer_out[q]) static_cast<float*>(p.peer_out[q])[at] = v[m];
-                            } else {
-                                const uint16_t b = f32_to_bf16_bits(v[m]);
-                                if (store) {
-                                    y16[at] = b;
-                                    for (int q = 0; q < npeers; ++q)
-                                        if (p.peer_out[q]) static_cast<uint16_t*>(p.peer_out[q])[at] = b;
-                                }
-                                if (topk_k && !p.write_y && r0 + m < p.topk_rows) p.ytmp[(size_t)(r0 + m) * p.ld_ytmp + n] = b;
-                            }
-                        }
-                    }
-                }
-                if (glu) bar_output_warps();  // tbuf is free again
-            } else if (M == 1) {
+            if (M == 1) {
                 output_stage(std::integral_constant<int, 1>{});
             } else {
                 output_stage(std::integral_constant<int, MR>{});
@@ -1080,9 +918,9 @@ __global__ void __launch_bounds__((1 + SW + 4) * 32, 1) tkd_stream_kernel(const 
     }
 }
 
-template <int FMT, int MT, int SW, bool ONE = false, bool PLAIN = false, bool KWHOLE = false>
+template <int FMT, bool ONE = false, bool PLAIN = false, bool KWHOLE = false>
 int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = tkd_stream_kernel<FMT, MT, SW, ONE, PLAIN, KWHOLE>;
+    auto kern = tkd_stream_kernel<FMT, ONE, PLAIN, KWHOLE>;
     // (once per device and instantiation: allow the largest dynamic shared memory a CTA can have)
     static bool allowed[64] = {false};
     int dev = 0;
@@ -1099,7 +937,7 @@ int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
     // drains; everything else waits for the earlier kernel's completion (griddepcontrol.wait).
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3((1 + SW + 4) * 32);
+    cfg.blockDim = dim3((1 + kStreamWarps + 4) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -1113,10 +951,10 @@ int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
 template <int FMT, bool KWHOLE>
 int launch_rows(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
     // (p.x_smem: the one row of x fits beside the ring in shared memory, which the one-row instantiations rely on)
-    if (p.M == 1 && p.x_smem && !p.topk_k && !p.npeers) return launch_one<FMT, 1, 16, true, true, KWHOLE>(p, grid, smem, st);
-    if (p.M == 1 && p.x_smem) return launch_one<FMT, 1, 16, true, false, KWHOLE>(p, grid, smem, st);
+    if (p.M == 1 && p.x_smem && !p.topk_k && !p.npeers) return launch_one<FMT, true, true, KWHOLE>(p, grid, smem, st);
+    if (p.M == 1 && p.x_smem) return launch_one<FMT, true, false, KWHOLE>(p, grid, smem, st);
     // (9 to 32 rows run tkd_stream_tc_kernel: the caller never gets here with them)
-    return launch_one<FMT, 1, 16, false, false, KWHOLE>(p, grid, smem, st);
+    return launch_one<FMT, false, false, KWHOLE>(p, grid, smem, st);
 }
 
 template <int FMT>
