@@ -123,15 +123,17 @@ int make_layout(const TkdMatmul* a, Layout* L, int sms) {
         p.off_xt = p.off_tbuf + TKD_PANEL_COLS * 40 * 4;
         p.off_ring = (int)align_up(p.off_xt + 1024 + TKD_TC_SLOTS * 2 * 4096, 128);
     } else {
-        // (one to eight rows: two hand-over buffers; one row: all of x in shared memory, K rounded up to a chunk, if
-        // that leaves the ring at least four stages)
+        // (one to eight rows: two hand-over buffers; all of x in shared memory, K rounded up to a chunk, if that leaves
+        // the ring at least four stages; rows 64 bytes further apart than their length, so that the eight rows a warp
+        // reads together fall on different banks)
         p.off_tbuf = p.off_pbuf + 2 * 2 * TKD_PANEL_COLS * mp * 4;
         p.off_xt = (int)align_up(p.off_tbuf + TKD_PANEL_COLS * mp * 4, 128);
-        int xt_bytes = 0;
-        const int64_t x_row = (a->k + chunk_k - 1) / chunk_k * chunk_k * 2;
-        if (a->m == 1 && p.off_xt + x_row + 4 * (int64_t)p.stage_bytes + 256 <= kMaxSmem) {
+        int64_t xt_bytes = 0;
+        const int64_t x_row = (a->k + chunk_k - 1) / chunk_k * chunk_k * 2 + (a->m > 1 ? 64 : 0);
+        if (p.off_xt + a->m * x_row + 4 * (int64_t)p.stage_bytes + 256 <= kMaxSmem) {
             p.x_smem = 1;
-            xt_bytes = (int)x_row;
+            p.x_stride = (int)x_row;
+            xt_bytes = a->m * x_row;
         }
         p.off_ring = (int)align_up(p.off_xt + xt_bytes, 128);
     }

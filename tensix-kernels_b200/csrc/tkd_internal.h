@@ -89,7 +89,8 @@ struct TkdParams {
     int* grid_counter;   // CTAs of this call that have finished their output (returns to zero)
     int exchange_wait;
     int tc;              // 9 to 32 rows: the tensor-memory kernel (tkd_stream_tc.cuh); off_xt is where its operand tiles go
-    int x_smem;          // one row, and all of it (K rounded up to a chunk) fits in shared memory at off_xt
+    int x_smem;          // 1 to 8 rows, and all of x (K rounded up to a chunk) fits in shared memory at off_xt
+    int x_stride;        // ... bytes from one row of it to the next
     int no_pdl;          // launch without programmatic dependent launch (the weights may still be being written)
     // shared-memory map (bytes from the start of dynamic shared memory)
     int off_pbuf, off_tbuf, off_xt, off_ring;

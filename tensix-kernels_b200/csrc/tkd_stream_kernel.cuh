@@ -453,8 +453,9 @@ __device__ __forceinline__ void exchange_done(const TkdParams& p, int lane, int 
 // of the output stage for 2 and 4 rows made the one-row call 1.5 us slower.)
 // PLAIN: no top-k records and no exchange with other GPUs (the plain matmuls of a decode step): that code falls away too.
 // KWHOLE: K is a whole number of chunks, so the code for a last, shorter chunk falls away as well.
+// XSM: all of x lies in shared memory (always so for ONE; two to eight rows: if it fits beside four stages of the ring).
 constexpr int kStreamWarps = 16;
-template <int FMT, bool ONE, bool PLAIN, bool KWHOLE>
+template <int FMT, bool ONE, bool PLAIN, bool KWHOLE, bool XSM>
 __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_kernel(const __grid_constant__ TkdParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     using F = Fmt<FMT>;
@@ -578,12 +579,12 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
         const int g8 = cw & 7, h0 = cw >> 3;
         const int g = lane >> 2, t = lane & 3;
         constexpr int NX = F::SUBSA / 2 * F::XB;
-        // XSM: a one-row call copies its row of x into shared memory once (K rounded up to a chunk, the rest zeros) and
+        // XSM: the call's rows of x are copied into shared memory once (K rounded up to a chunk, the rest zeros) and
         // every block's 16 bytes a lane come from there. (Through L1 they missed one time in seven with most of the
         // SM's memory given to the ring, each miss a trip to L2 behind the weight stream's traffic, and the stage waits
         // for its slowest warp.)
-        constexpr bool XSM = ONE;
-        // PRE: two to eight rows: the chunk's activations are loaded (through L1) before the stage is waited for
+        static_assert(XSM || !ONE, "the one-row instantiations keep x in shared memory");
+        // PRE: x too large for that: the chunk's activations are loaded (through L1) before the stage is waited for
         constexpr bool PRE = !XSM;
         const uint32_t xt0 = smem_u32(smem + p.off_xt);
         constexpr int EXPB = FMT == TKD_BFP4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
@@ -603,13 +604,19 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
         int kc = (int)(first_it - idiv(p, first_it, p.nslices) * p.nslices) * p.ks;
         float acc[NH][NA][MT][4], tot[NH][MT][4];
         const uint2 sh = make_uint2(p.mul16, p.mul128);
-        const uint32_t xs_lane = xt0 + (8 * t + h0 * F::KSA) * 2;
+        // (a lane's row of x: row g, or the last row for the lanes beyond M, as in xb)
+        const uint32_t xs_lane = xt0 + (ONE ? 0 : min(g, M - 1) * p.x_stride) + (8 * t + h0 * F::KSA) * 2;
         if constexpr (XSM) {
-            const int pieces = (K + CK - 1) / CK * (CK / 8);
-            for (int e = cw * 32 + lane; e < pieces; e += SW * 32) {
-                const uint4 v = e * 8 < K ? ldg_x(p.x + e * 8) : make_uint4(0u, 0u, 0u, 0u);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xt0 + e * 16), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                             : "memory");
+            const int pieces = (K + CK - 1) / CK * (CK / 8);  // 16-byte pieces of a row
+            for (int r = 0; r < M; ++r) {
+                const uint16_t* xr = p.x + (int64_t)r * p.ldx;
+                const uint32_t dst = xt0 + (ONE ? 0 : r * p.x_stride);
+                for (int e = cw * 32 + lane; e < pieces; e += SW * 32) {
+                    const uint4 v = e * 8 < K ? ldg_x(xr + e * 8) : make_uint4(0u, 0u, 0u, 0u);
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + e * 16), "r"(v.x), "r"(v.y), "r"(v.z),
+                                 "r"(v.w)
+                                 : "memory");
+                }
             }
             asm volatile("bar.sync 2, %0;" ::"n"(SW * 32) : "memory");
         }
@@ -918,9 +925,9 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
     }
 }
 
-template <int FMT, bool ONE = false, bool PLAIN = false, bool KWHOLE = false>
+template <int FMT, bool ONE, bool PLAIN, bool KWHOLE, bool XSM>
 int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = tkd_stream_kernel<FMT, ONE, PLAIN, KWHOLE>;
+    auto kern = tkd_stream_kernel<FMT, ONE, PLAIN, KWHOLE, XSM>;
     // (once per device and instantiation: allow the largest dynamic shared memory a CTA can have)
     static bool allowed[64] = {false};
     int dev = 0;
@@ -950,11 +957,12 @@ int launch_one(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
 
 template <int FMT, bool KWHOLE>
 int launch_rows(const TkdParams& p, int grid, size_t smem, cudaStream_t st) {
-    // (p.x_smem: the one row of x fits beside the ring in shared memory, which the one-row instantiations rely on)
-    if (p.M == 1 && p.x_smem && !p.topk_k && !p.npeers) return launch_one<FMT, true, true, KWHOLE>(p, grid, smem, st);
-    if (p.M == 1 && p.x_smem) return launch_one<FMT, true, false, KWHOLE>(p, grid, smem, st);
+    // (p.x_smem: x fits beside the ring in shared memory, which the one-row instantiations rely on)
+    if (p.M == 1 && p.x_smem && !p.topk_k && !p.npeers) return launch_one<FMT, true, true, KWHOLE, true>(p, grid, smem, st);
+    if (p.M == 1 && p.x_smem) return launch_one<FMT, true, false, KWHOLE, true>(p, grid, smem, st);
     // (9 to 32 rows run tkd_stream_tc_kernel: the caller never gets here with them)
-    return launch_one<FMT, false, false, KWHOLE>(p, grid, smem, st);
+    if (p.x_smem) return launch_one<FMT, false, false, KWHOLE, true>(p, grid, smem, st);
+    return launch_one<FMT, false, false, KWHOLE, false>(p, grid, smem, st);
 }
 
 template <int FMT>
