@@ -466,7 +466,7 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
     constexpr int NA = 2;   // accumulator sets a streaming warp alternates between
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TKD_MAX_STAGES);
-    const uint32_t pfull0 = smem_u32(bars + 2 * TKD_MAX_STAGES), pempty0 = pfull0 + 16;
+    const uint32_t pfull0 = smem_u32(bars + 2 * TKD_MAX_STAGES), pempty0 = pfull0 + 16, xbar = pfull0 + 32;
     // NH: halves of a chunk's super-atoms a streaming warp takes; NPB: hand-over buffers between the streaming and the
     // output warps
     constexpr int NH = 1;
@@ -489,6 +489,7 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
             mbar_init(pfull0 + 8 * s, SW);
             mbar_init(pempty0 + 8 * s, 4);
         }
+        mbar_init(xbar, 1);
         sflag[0] = sflag[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -573,9 +574,19 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
     } else if (warp <= SW) {
         // ---------------------------------------------------------------- streaming warps
         // One flat loop over the stages of the ring; everything about items comes with the stage's header.
+        const int cw = warp - 1;
+        if constexpr (XSM && !KWHOLE) {
+            // the rows of x in shared memory end in zeros up to a whole chunk: written here, before the wait below, by
+            // whichever lanes, and seen by all after the barrier
+            const int pieces = (K + CK - 1) / CK * (CK / 8);  // 16-byte pieces of a row
+            const uint32_t xz = smem_u32(smem + p.off_xt);
+            for (int r = 0; r < (ONE ? 1 : p.M); ++r)
+                for (int e = K / 8 + cw * 32 + lane; e < pieces; e += SW * 32)
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(xz + r * p.x_stride + e * 16), "r"(0u) : "memory");
+            asm volatile("bar.sync 2, %0;" ::"n"(SW * 32) : "memory");
+        }
         // (x, the scratch buffer and the outputs may belong to the kernel before this one: wait for it to complete)
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        const int cw = warp - 1;
         const int g8 = cw & 7, h0 = cw >> 3;
         const int g = lane >> 2, t = lane & 3;
         constexpr int NX = F::SUBSA / 2 * F::XB;
@@ -606,21 +617,20 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
         const uint2 sh = make_uint2(p.mul16, p.mul128);
         // (a lane's row of x: row g, or the last row for the lanes beyond M, as in xb)
         const uint32_t xs_lane = xt0 + (ONE ? 0 : min(g, M - 1) * p.x_stride) + (8 * t + h0 * F::KSA) * 2;
+        bool x_here = true;
         if constexpr (XSM) {
-            const int pieces = (K + CK - 1) / CK * (CK / 8);  // 16-byte pieces of a row
-            for (int r = 0; r < M; ++r) {
-                const uint16_t* xr = p.x + (int64_t)r * p.ldx;
-                const uint32_t dst = xt0 + (ONE ? 0 : r * p.x_stride);
-                for (int e = cw * 32 + lane; e < pieces; e += SW * 32) {
-                    const uint4 v = e * 8 < K ? ldg_x(xr + e * 8) : make_uint4(0u, 0u, 0u, 0u);
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + e * 16), "r"(v.x), "r"(v.y), "r"(v.z),
-                                 "r"(v.w)
-                                 : "memory");
-                }
+            // The call's rows of x into shared memory, one bulk copy a row (K is a multiple of 32 and the rows are 16-byte
+            // aligned: include/tkd.h), issued by one lane as soon as x may be read; every streaming warp waits for their
+            // bytes on one barrier. (512 lanes loading and storing their pieces and a barrier among them took 2.0 us of a
+            // 13 us launch, all of it before the first chunk.)
+            if (cw == 0 && lane == 0) {
+                mbar_expect_tx(xbar, (uint32_t)(M * K * 2));
+                for (int r = 0; r < M; ++r)
+                    bulk_g2s(xt0 + (ONE ? 0 : r * p.x_stride), p.x + (int64_t)r * p.ldx, (uint32_t)(K * 2), xbar);
             }
-            asm volatile("bar.sync 2, %0;" ::"n"(SW * 32) : "memory");
+            x_here = mbar_wait(xbar, 0, p.status);
         }
-        while (true) {
+        while (x_here) {
             const bool full = KWHOLE || kc + CK <= K;
             uint4 xpre[NX][MT];
             if (PRE && full) {
