@@ -648,28 +648,8 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                     const int rsz = res32 ? 4 : 2;
                     const bool rvec = vec && (res32 || res16) &&
                                       ((reinterpret_cast<uintptr_t>(p.res) | (uintptr_t)(p.ldr * rsz) | (uintptr_t)(oc0 * rsz)) & 15) == 0;
-#pragma unroll 1
-                    for (int half = 0; half < 2 && r < M; ++half) {  // (two of a warp's four groups at a time)
-                        uint4 rq[2][2];
-                        if (rvec) {
-#pragma unroll
-                            for (int i = 0; i < 2; ++i) {
-                                const int cc = ow + 4 * (2 * half + i);
-                                if (8 * cc + 8 <= nv) {
-                                    const size_t ra = (size_t)r * p.ldr + oc0 + 8 * cc;
-                                    if (res32) {
-                                        const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const float*>(p.res) + ra);
-                                        rq[i][0] = rp[0], rq[i][1] = rp[1];
-                                    } else {
-                                        rq[i][0] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.res) + ra);
-                                    }
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int gi = 0; gi < 2; ++gi) {
-                            const int cc = ow + 4 * (2 * half + gi);
-                            if (8 * cc >= nv) break;
+                    // one group of 8 output columns of this lane's row (have: its residual came in q0, q1)
+                    auto group = [&](int cc, bool have, uint4 q0, uint4 q1) {
                             float v[8];
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
@@ -683,8 +663,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                             }
                             const int here = min(8, nv - 8 * cc);  // columns of this group that exist
                             const size_t at = (size_t)r * p.ldo + oc0 + 8 * cc;
-                            if (rvec && here == 8) {
-                                const uint4 q0 = rq[gi][0], q1 = rq[gi][1];
+                            if (have && here == 8) {
                                 if (res32) {
                                     v[0] += __uint_as_float(q0.x), v[1] += __uint_as_float(q0.y);
                                     v[2] += __uint_as_float(q0.z), v[3] += __uint_as_float(q0.w);
@@ -745,6 +724,33 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                                             if (p.peer_out[q]) static_cast<uint16_t*>(p.peer_out[q])[at + i] = b[i];
                                     }
                                 }
+                            }
+                    };
+                    if (r < M && !(res32 || res16)) {
+#pragma unroll 1
+                        for (int cc = ow; 8 * cc < nv; cc += 4) group(cc, false, make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u));
+                    } else if (r < M) {
+#pragma unroll 1
+                        for (int half = 0; half < 2; ++half) {  // (two of a warp's four groups at a time)
+                            uint4 rq[2][2];
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                const int cc = ow + 4 * (2 * half + i);
+                                rq[i][0] = rq[i][1] = make_uint4(0u, 0u, 0u, 0u);
+                                if (rvec && 8 * cc + 8 <= nv) {
+                                    const size_t ra = (size_t)r * p.ldr + oc0 + 8 * cc;
+                                    if (res32) {
+                                        const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const float*>(p.res) + ra);
+                                        rq[i][0] = rp[0], rq[i][1] = rp[1];
+                                    } else {
+                                        rq[i][0] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.res) + ra);
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int gi = 0; gi < 2; ++gi) {
+                                const int cc = ow + 4 * (2 * half + gi);
+                                if (8 * cc < nv) group(cc, rvec, rq[gi][0], rq[gi][1]);
                             }
                         }
                     }
