@@ -576,6 +576,40 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) tkd_stream_tc_kernel(const _
                     const int pe = (int)min((int64_t)p.nslices, oend - pfirst);
                     const float* s0 = p.scratch + pfirst * 2 * M * TKD_PANEL_COLS + et;
                     auto term = [&](int s, int m) { return __ldcg(s0 + ((size_t)(s * 2) * M + m) * TKD_PANEL_COLS); };
+                    const int ns = p.nslices - pe + 1;  // sums to add: the owner's, then one per later slice
+                    if (j == nitems - 1 && (size_t)ns * M * 512 <= (size_t)nst * p.stage_bytes) {
+                        // The CTA's last item: the ring is idle, and the sums (M x 512 bytes a slice, contiguous) are copied
+                        // into it 16 bytes at a time, all copies in flight together (one trip to L2 instead of one per 32
+                        // loads a thread), then added up in slice order from shared memory.
+                        const uint32_t ring_a = smem_u32(ring);
+                        const int per = M * 32;  // 16-byte pieces of a slice's sums
+                        for (int si = 0; si < ns; ++si) {
+                            const float* src = p.scratch + ((pfirst + pe - 1 + si) * 2 * M) * TKD_PANEL_COLS;
+                            const uint32_t dst = ring_a + si * per * 16;
+                            for (int q = et; q < per; q += 128)
+                                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + q * 16), "l"(src + q * 4)
+                                             : "memory");
+                        }
+                        asm volatile("cp.async.wait_all;" ::: "memory");
+                        bar_output_warps();
+                        const float* rs = reinterpret_cast<const float*>(ring) + et;
+#pragma unroll 1
+                        for (int rb = 0; rb < M; rb += 8) {  // (eight rows' loads at a time; a row past M re-reads the last)
+                            float th[8];
+#pragma unroll
+                            for (int m = 0; m < 8; ++m) th[m] = rs[(size_t)min(rb + m, M - 1) * TKD_PANEL_COLS];
+#pragma unroll 1
+                            for (int si = 1; si < ns; ++si) {
+                                float v[8];
+#pragma unroll
+                                for (int m = 0; m < 8; ++m) v[m] = rs[((size_t)si * M + min(rb + m, M - 1)) * TKD_PANEL_COLS];
+#pragma unroll
+                                for (int m = 0; m < 8; ++m) th[m] += v[m];
+                            }
+                            *reinterpret_cast<float4*>(trow + rb) = make_float4(th[0], th[1], th[2], th[3]);
+                            *reinterpret_cast<float4*>(trow + rb + 4) = make_float4(th[4], th[5], th[6], th[7]);
+                        }
+                    } else
 #pragma unroll 1
                     for (int rb = 0; rb < M; rb += 8) {
                         float th[8];
