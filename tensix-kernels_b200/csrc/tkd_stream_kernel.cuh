@@ -585,8 +585,17 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
                     asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(xz + r * p.x_stride + e * 16), "r"(0u) : "memory");
             asm volatile("bar.sync 2, %0;" ::"n"(SW * 32) : "memory");
         }
+        const uint32_t xt0 = smem_u32(smem + p.off_xt);
         // (x, the scratch buffer and the outputs may belong to the kernel before this one: wait for it to complete)
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        if constexpr (XSM) {
+            // the first thing after that wait: the weights are in the ring already, everything waits for x
+            if (cw == 0 && lane == 0) {
+                mbar_expect_tx(xbar, (uint32_t)(M * K * 2));
+                for (int r = 0; r < M; ++r)
+                    bulk_g2s(xt0 + (ONE ? 0 : r * p.x_stride), p.x + (int64_t)r * p.ldx, (uint32_t)(K * 2), xbar);
+            }
+        }
         const int g8 = cw & 7, h0 = cw >> 3;
         const int g = lane >> 2, t = lane & 3;
         constexpr int NX = F::SUBSA / 2 * F::XB;
@@ -597,7 +606,6 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
         static_assert(XSM || !ONE, "the one-row instantiations keep x in shared memory");
         // PRE: x too large for that: the chunk's activations are loaded (through L1) before the stage is waited for
         constexpr bool PRE = !XSM;
-        const uint32_t xt0 = smem_u32(smem + p.off_xt);
         constexpr int EXPB = FMT == TKD_BFP4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
         const uint16_t* xb[NH][MT];
 #pragma unroll
@@ -623,12 +631,7 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
             // aligned: include/tkd.h), issued by one lane as soon as x may be read; every streaming warp waits for their
             // bytes on one barrier. (512 lanes loading and storing their pieces and a barrier among them took 2.0 us of a
             // 13 us launch, all of it before the first chunk.)
-            if (cw == 0 && lane == 0) {
-                mbar_expect_tx(xbar, (uint32_t)(M * K * 2));
-                for (int r = 0; r < M; ++r)
-                    bulk_g2s(xt0 + (ONE ? 0 : r * p.x_stride), p.x + (int64_t)r * p.ldx, (uint32_t)(K * 2), xbar);
-            }
-            x_here = mbar_wait(xbar, 0, p.status);
+            x_here = mbar_wait(xbar, 0, p.status);  // (the copies were issued right after the wait for the kernel before)
         }
         while (x_here) {
             const bool full = KWHOLE || kc + CK <= K;
