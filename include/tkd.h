@@ -20,6 +20,8 @@ extern "C" {
 #define TKD_FMT_BFP8 0
 #define TKD_FMT_BFP4 1
 #define TKD_FMT_BF16 2
+#define TKD_FMT_INT4 3   /* int4 codes -7..7 with one bf16 scale per column and 32 k (int4/w4a16.py of the reference):
+                           m <= 8 only; tkd_pack takes the scales in place of exps, see there */
 
 #define TKD_OK 0
 #define TKD_ERR_BAD_ARG 1      /* a shape, pointer or option the path does not take */
@@ -72,7 +74,10 @@ int tkd_quantise(int fmt, const float* src, int orient, int64_t k, int64_t n, co
  * tkd_matmul never sees the info word: a caller that finds the bit set must not launch on that stream (the far rows'
  * exponents are clamped in it) and holds the weight as TKD_FMT_BF16 instead, which is exact: tkd_dequantise_bf16 on
  * the same exps and codes, then tkd_pack with TKD_FMT_BF16 (what the Python layer does; TKD_ERR_WIDE is what a binding
- * raises if it chooses to refuse instead). */
+ * raises if it chooses to refuse instead).
+ * TKD_FMT_INT4 (the reference's int4_weight + group_scales, int4/w4a16.py:70-105): codes [K, npad] bytes
+ * sign << 3 | magnitude (magnitude 0..7), exps = the group scales as bf16 bits [ceil(K / 32), npad] (uint16; K a
+ * multiple of 32), emax and info unused (NULL). The weight is code * scale exactly; tkd_unpack returns that. */
 int tkd_pack(int fmt, int64_t k, int64_t n, const uint8_t* exps, const void* codes, void* packed, uint8_t* emax,
              int32_t* info, void* stream);
 /* tkd_quantise's block-float numbers (TKD_FMT_BFP8 or BFP4) as bf16 bits [K, npad] (uint16), the canonical form

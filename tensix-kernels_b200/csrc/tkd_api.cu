@@ -9,7 +9,8 @@
 #include "tkd_internal.h"
 #include "tkd_layout.h"
 
-static_assert(TKD_FMT_BFP8 == TKD_BFP8 && TKD_FMT_BFP4 == TKD_BFP4 && TKD_FMT_BF16 == TKD_BF16, "format codes");
+static_assert(TKD_FMT_BFP8 == TKD_BFP8 && TKD_FMT_BFP4 == TKD_BFP4 && TKD_FMT_BF16 == TKD_BF16 && TKD_FMT_INT4 == TKD_INT4,
+              "format codes");
 
 namespace {
 
@@ -21,7 +22,9 @@ constexpr int64_t kCounterBytes = (int64_t)(kMaxPanels + kMaxUnits + kMaxMisc) *
 
 inline int cuda_err(cudaError_t e) { return e == cudaSuccess ? TKD_OK : TKD_ERR_CUDA + (int)e; }
 inline int launch_err(int e) { return e == 0 ? TKD_OK : TKD_ERR_CUDA + e; }
-inline bool fmt_ok(int fmt) { return fmt == TKD_BFP8 || fmt == TKD_BFP4 || fmt == TKD_BF16; }
+inline bool fmt_ok(int fmt) { return fmt == TKD_BFP8 || fmt == TKD_BFP4 || fmt == TKD_BF16 || fmt == TKD_INT4; }
+// (formats whose stream carries biased exponents against a side array of per-group maxima)
+inline bool has_emax(int fmt) { return fmt == TKD_BFP8 || fmt == TKD_BFP4; }
 inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
 int sm_count() {
@@ -49,6 +52,9 @@ struct Layout {
 int make_layout(const TkdMatmul* a, Layout* L, int sms) {
     if (!a || !fmt_ok(a->fmt)) return TKD_ERR_BAD_ARG;
     if (a->m < 1 || a->m > 32 || a->k < 32 || a->k % 32 || a->k > (1 << 24)) return TKD_ERR_BAD_ARG;
+    // (the int4 weight with group scales is the reference's one-token op; more rows go through its dequantised
+    // bfloat8_b form, as there: int4/w4a16.py dequantize)
+    if (a->fmt == TKD_INT4 && a->m > 8) return TKD_ERR_UNSUPPORTED;
     if (a->nblocks < 1 || a->nblocks > 4) return TKD_ERR_BAD_ARG;
     if (a->epilogue < TKD_EPI_PLAIN || a->epilogue > TKD_EPI_OUT32) return TKD_ERR_BAD_ARG;
     const bool glu = a->epilogue == TKD_EPI_GLU_IL || a->epilogue == TKD_EPI_GLU2;
@@ -211,7 +217,8 @@ int64_t tkd_packed_bytes(int fmt, int64_t k, int64_t n) {
 
 int tkd_quantise(int fmt, const float* src, int orient, int64_t k, int64_t n, const float* col_div, uint8_t* exps,
                  void* codes, void* stream) {
-    if (!fmt_ok(fmt) || !src || !codes || k < 1 || n < 1 || (fmt != TKD_BF16 && !exps) || (orient != 0 && orient != 1))
+    if (!fmt_ok(fmt) || fmt == TKD_INT4 || !src || !codes || k < 1 || n < 1 || (fmt != TKD_BF16 && !exps) ||
+        (orient != 0 && orient != 1))
         return TKD_ERR_BAD_ARG;
     return launch_err(tkd_launch_quantise(fmt, src, orient, k, n, tkd_padded_cols(n), col_div, exps, codes,
                                           static_cast<cudaStream_t>(stream)));
@@ -220,7 +227,8 @@ int tkd_quantise(int fmt, const float* src, int orient, int64_t k, int64_t n, co
 int tkd_pack(int fmt, int64_t k, int64_t n, const uint8_t* exps, const void* codes, void* packed, uint8_t* emax,
              int32_t* info, void* stream) {
     if (!fmt_ok(fmt) || !codes || !packed || k < 1 || n < 1) return TKD_ERR_BAD_ARG;
-    if (fmt != TKD_BF16 && (!exps || !emax || !info)) return TKD_ERR_BAD_ARG;
+    if (has_emax(fmt) && (!exps || !emax || !info)) return TKD_ERR_BAD_ARG;
+    if (fmt == TKD_INT4 && !exps) return TKD_ERR_BAD_ARG;  // (the group scales)
     return launch_err(tkd_launch_permute(fmt, k, tkd_padded_cols(n), exps, codes, emax, info, packed,
                                          static_cast<cudaStream_t>(stream)));
 }
@@ -232,7 +240,7 @@ int tkd_dequantise_bf16(int fmt, int64_t k, int64_t n, const uint8_t* exps, cons
 }
 
 int tkd_unpack(int fmt, int64_t k, int64_t n, const void* packed, const uint8_t* emax, float* out, void* stream) {
-    if (!fmt_ok(fmt) || !packed || !out || k < 1 || n < 1 || (fmt != TKD_BF16 && !emax)) return TKD_ERR_BAD_ARG;
+    if (!fmt_ok(fmt) || !packed || !out || k < 1 || n < 1 || (has_emax(fmt) && !emax)) return TKD_ERR_BAD_ARG;
     return launch_err(
         tkd_launch_unpack(fmt, k, tkd_padded_cols(n), packed, emax, out, static_cast<cudaStream_t>(stream)));
 }
@@ -286,9 +294,9 @@ static int run_matmul(const TkdMatmul* a, void* workspace, uint64_t workspace_by
     for (int s = 0; s < a->nblocks; ++s) {
         const TkdBlock& b = a->block[s];
         if (!b.w || (reinterpret_cast<uintptr_t>(b.w) & 15)) return TKD_ERR_BAD_ARG;
-        if (a->fmt != TKD_BF16 && !b.emax) return TKD_ERR_BAD_ARG;
+        if (has_emax(a->fmt) && !b.emax) return TKD_ERR_BAD_ARG;
         if (a->epilogue == TKD_EPI_GLU2) {
-            if (!b.w_up || (reinterpret_cast<uintptr_t>(b.w_up) & 15) || (a->fmt != TKD_BF16 && !b.emax_up))
+            if (!b.w_up || (reinterpret_cast<uintptr_t>(b.w_up) & 15) || (has_emax(a->fmt) && !b.emax_up))
                 return TKD_ERR_BAD_ARG;
         }
         const int64_t width = a->epilogue == TKD_EPI_GLU_IL ? b.n / 2 : b.n;

@@ -37,6 +37,14 @@
 //             0-5, r 3 at 16-21: (w & 0x1F801F80) | 0x40004000 is the pair of bf16 scales 2^(f + 1) of r 0 and r 1, the
 //             same of w << 7 those of r 2 and r 3
 // e is recovered exactly for every non-zero code.
+//
+// TKD_INT4 (the reference's int4 weight with group scales, int4/w4a16.py: symmetric codes q in -7..7, sign-magnitude,
+// one bf16 scale per output column and 32 consecutive k, the weight being q * s) shares bfloat4_b's geometry and code
+// words: a 3-bit magnitude and a sign are exactly a bfloat4_b code. Where bfloat4_b keeps 64 bytes of exponents, a
+// super-atom (64 k x 16 columns) keeps its 32 scales: word 2 g + q (g = 0..7, q = the k32 block) holds the scales of
+// columns g (low half) and g + 8 (high half), each as the bf16 of s * 2^65. The kernel multiplies a k32 block of codes
+// (bf16 subnormals q * 2^-129) by the activations times 2^64 into a fresh accumulator and adds that, times the stored
+// scale, to the running sum: acc += (2^-65 * sum x q) * (s * 2^65).
 #pragma once
 #include <stdint.h>
 
@@ -46,7 +54,7 @@
 #define TKD_HD inline
 #endif
 
-enum { TKD_BFP8 = 0, TKD_BFP4 = 1, TKD_BF16 = 2 };
+enum { TKD_BFP8 = 0, TKD_BFP4 = 1, TKD_BF16 = 2, TKD_INT4 = 3 };
 
 // Bumped with every change of the stream's bit layout (a packed-weight cache made by another layout is refused).
 #define TKD_LAYOUT_VERSION 3
@@ -64,12 +72,15 @@ TKD_HD int tkd_ezero(int fmt) { return fmt == TKD_BFP4 ? 0 : 1; }
 //   bfloat4_b: code m * 2^-129 times x * 2^(f + 1)    = m x 2^(e - emax - 65) for the true m x 2^(e - 129)
 TKD_HD int tkd_out_exp(int fmt, int emax) { return fmt == TKD_BFP4 ? emax - 64 : emax + 64 - 133; }
 
+#define TKD_INT4_SCALE_EXP 65
+// (the block-float geometry of a format: TKD_INT4 is laid out as bfloat4_b)
+TKD_HD int tkd_geo(int fmt) { return fmt == TKD_INT4 ? TKD_BFP4 : fmt; }
 TKD_HD int tkd_mant_bits(int fmt) { return fmt == TKD_BFP8 ? 7 : 3; }
-TKD_HD int tkd_ksa(int fmt) { return fmt == TKD_BFP4 ? 64 : 32; }                          // k per super-atom
-TKD_HD int tkd_sab(int fmt) { return fmt == TKD_BFP8 ? 544 : (fmt == TKD_BFP4 ? 576 : 1024); }  // bytes per super-atom
-TKD_HD int tkd_exp_bytes(int fmt) { return fmt == TKD_BFP8 ? 32 : (fmt == TKD_BFP4 ? 64 : 0); }
+TKD_HD int tkd_ksa(int fmt) { return tkd_geo(fmt) == TKD_BFP4 ? 64 : 32; }                          // k per super-atom
+TKD_HD int tkd_sab(int fmt) { return fmt == TKD_BFP8 ? 544 : (tkd_geo(fmt) == TKD_BFP4 ? 576 : 1024); }  // bytes per super-atom
+TKD_HD int tkd_exp_bytes(int fmt) { return fmt == TKD_BFP8 ? 32 : (tkd_geo(fmt) == TKD_BFP4 ? 64 : 0); }
 TKD_HD int tkd_unit_exp(int fmt) { return 126 + tkd_mant_bits(fmt); }  // value = m * 2^(e - unit)
-TKD_HD int tkd_chunk_k(int fmt) { return fmt == TKD_BF16 ? 128 : (fmt == TKD_BFP4 ? 512 : 256); }  // k per chunk (stage)
+TKD_HD int tkd_chunk_k(int fmt) { return fmt == TKD_BF16 ? 128 : (tkd_geo(fmt) == TKD_BFP4 ? 512 : 256); }  // k per chunk (stage)
 TKD_HD int tkd_subsa(int fmt) { return tkd_chunk_k(fmt) / tkd_ksa(fmt); }                  // super-atoms per group and chunk
 TKD_HD int64_t tkd_nsa(int fmt, int64_t K) { return (K + tkd_ksa(fmt) - 1) / tkd_ksa(fmt); }
 TKD_HD int64_t tkd_run_bytes(int fmt, int64_t K) { return tkd_nsa(fmt, K) * tkd_sab(fmt); }  // one group, all of K
@@ -139,6 +150,11 @@ TKD_HD TkdLoc tkd_locate(int fmt, int64_t K, int64_t k, int64_t n) {
         L.code_word = base + 64 + lane * 16 + j4 * 4;
         L.rot = ai;
         L.exp_word = base + (t * 4 + j4) * 4;
+        if (fmt == TKD_INT4) {
+            // the scale of (column i, k32 block qq): half (i >> 3) of word 2 (i & 7) + qq
+            L.exp_word = base + (2 * (i & 7) + qq) * 4;
+            L.exp_r = i >> 3;
+        }
     }
     return L;
 }

@@ -136,6 +136,20 @@ __global__ void tkd_permute_kernel(int fmt, int64_t K, int64_t npad, const uint8
             const uint32_t v = k < K ? codes[k * npad + g * 16 + i] : 0u;
             word |= v << (16 * half);
         }
+    } else if (fmt == TKD_INT4 && off < eb) {
+        // the scales of the super-atom's k32 block qq for columns g8 and g8 + 8 (exps: bf16 bits [ceil(K / 32), npad]),
+        // each times 2^TKD_INT4_SCALE_EXP (exact: a bf16 keeps its significand; the product is a normal number)
+        const uint16_t* sc = reinterpret_cast<const uint16_t*>(exps);
+        const int g8 = (off / 4) >> 1, qq = (off / 4) & 1;
+        const int64_t kg = sa * 2 + qq;
+        for (int half = 0; half < 2; ++half) {
+            uint32_t b = 0;
+            if (kg * 32 < K) {
+                const float v = __uint_as_float((uint32_t)sc[kg * npad + g * 16 + g8 + 8 * half] << 16);
+                b = __float_as_uint(v * 0x1p65f) >> 16;
+            }
+            word |= b << (16 * half);
+        }
     } else if (off < eb) {
         const uint8_t* codes = static_cast<const uint8_t*>(codes_v);
         const int per_t = fmt == TKD_BFP4 ? 4 : 2;
@@ -205,8 +219,14 @@ __global__ void tkd_unpack_kernel(int fmt, int64_t K, int64_t npad, const uint8_
         const uint32_t c = tkd_code_from_word(fmt, w, L.rot, L.half);
         const uint32_t m = c & ((1u << mb) - 1);
         const uint32_t ew = *reinterpret_cast<const uint32_t*>(stream + L.exp_word);
-        const int e = (int)tkd_exp_from_word(fmt, ew, L.exp_r) + (int)emax[n >> 4] - tkd_ebias(fmt);
-        v = m ? ldexpf((float)m, e - tkd_unit_exp(fmt)) : 0.f;
+        if (fmt == TKD_INT4) {
+            // q * s: the stored scale is s * 2^65
+            const float s65 = __uint_as_float(((ew >> (16 * L.exp_r)) & 0xFFFFu) << 16);
+            v = (float)m * (s65 * 0x1p-65f);
+        } else {
+            const int e = (int)tkd_exp_from_word(fmt, ew, L.exp_r) + (int)emax[n >> 4] - tkd_ebias(fmt);
+            v = m ? ldexpf((float)m, e - tkd_unit_exp(fmt)) : 0.f;
+        }
         if ((c >> mb) & 1u) v = -v;
     }
     out[idx] = v;
@@ -228,7 +248,7 @@ int tkd_launch_quantise(int fmt, const float* src, int orient, int64_t K, int64_
 int tkd_launch_permute(int fmt, int64_t K, int64_t npad, const uint8_t* exps, const void* codes, uint8_t* emax,
                        int* info, void* stream, cudaStream_t st) {
     const int64_t G = npad / 16;
-    if (fmt != TKD_BF16) {
+    if (fmt != TKD_BF16 && fmt != TKD_INT4) {
         tkd_emax_kernel<<<(unsigned)G, kEmaxThreads, 0, st>>>(exps, static_cast<const uint8_t*>(codes), K, npad, emax, info);
     }
     const int64_t words = tkd_stream_bytes(fmt, K, npad) / 4;

@@ -8,6 +8,7 @@
 int tkd_launch_stream_bfp8(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
 int tkd_launch_stream_bfp4(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
 int tkd_launch_stream_bf16(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
+int tkd_launch_stream_int4(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
 
 namespace {
 
@@ -80,6 +81,7 @@ int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st
     switch (p.fmt) {
         case TKD_BFP8: return tkd_launch_stream_bfp8(p, grid, smem, st);
         case TKD_BFP4: return tkd_launch_stream_bfp4(p, grid, smem, st);
+        case TKD_INT4: return tkd_launch_stream_int4(p, grid, smem, st);
         default: return tkd_launch_stream_bf16(p, grid, smem, st);
     }
 }

@@ -225,6 +225,10 @@ struct Fmt<TKD_BFP4> {
     static constexpr int KSA = 64, SAB = 576, SUBSA = 8, XB = 2;
 };
 template <>
+struct Fmt<TKD_INT4> {  // (bfloat4_b's geometry: tkd_layout.h)
+    static constexpr int KSA = 64, SAB = 576, SUBSA = 8, XB = 2;
+};
+template <>
 struct Fmt<TKD_BF16> {
     static constexpr int KSA = 32, SAB = 1024, SUBSA = 4, XB = 1;
 };
@@ -305,6 +309,13 @@ __device__ __forceinline__ void chunk_mma(float (&acc)[NA][MT][4], uint32_t code
             cw[0][0] = cv.x, cw[0][1] = cv.y, cw[1][0] = cv.z, cw[1][1] = cv.w;
             cw[0][2] = cw[0][3] = cw[1][2] = cw[1][3] = 0;
             ew[0][0] = ev.x, ew[0][1] = ev.y, ew[1][0] = ev.z, ew[1][1] = ev.w;
+        } else if constexpr (FMT == TKD_INT4) {
+            // (exp_a: this lane's two scale words of the super-atom, one per k32 block: columns g and g + 8)
+            const uint2 sv = lds64(exp_a + 2 * i * F::SAB);
+            const uint4 cv = lds128(code_a + 2 * i * F::SAB);
+            cw[0][0] = cv.x, cw[0][1] = cv.y, cw[1][0] = cv.z, cw[1][1] = cv.w;
+            cw[0][2] = cw[0][3] = cw[1][2] = cw[1][3] = 0;
+            ew[0][0] = sv.x, ew[1][0] = sv.y, ew[0][1] = ew[1][1] = 0;
         } else if constexpr (FMT == TKD_BFP8) {
             const uint2 ev = lds64(exp_a + 2 * i * F::SAB);
             const uint4 cv = lds128(code_a + 2 * i * F::SAB);
@@ -332,6 +343,26 @@ __device__ __forceinline__ void chunk_mma(float (&acc)[NA][MT][4], uint32_t code
 #pragma unroll
                     for (int m = 0; m < MT; ++m)
                         mma_bf16(acc[jj % NA][m], a.x, a.y, a.z, a.w, jj ? xv[m].z : xv[m].x, jj ? xv[m].w : xv[m].y);
+                }
+            } else if constexpr (FMT == TKD_INT4) {
+                // The k32 block's codes (bf16 subnormals q * 2^-129) times the activations times 2^64, summed from zero;
+                // then the block's scale (s * 2^65, a pair of bf16 in ew[q][0]: column g low, g + 8 high) takes the sum
+                // into the running one. The running sums alternate between the two accumulator sets by q.
+                const float s_lo = __uint_as_float(ew[q][0] << 16), s_hi = __uint_as_float(ew[q][0] & 0xFFFF0000u);
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    float tmp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) {
+                        const uint32_t w = cw[q][jj], t8 = __funnelshift_r(w, w, 8);
+                        const uint32_t a0 = w & TKD_MASK_BFP4, a1 = shl_fma<4>(w, sh.x) & TKD_MASK_BFP4;
+                        const uint32_t a2 = t8 & TKD_MASK_BFP4, a3 = shl_fma<4>(t8, sh.x) & TKD_MASK_BFP4;
+                        const uint32_t x0 = jj ? xv[m].z : xv[m].x, x1 = jj ? xv[m].w : xv[m].y;
+                        mma_bf16(tmp, a0, a1, a2, a3, mul_bf16x2(x0, 0x5F805F80u), mul_bf16x2(x1, 0x5F805F80u));
+                    }
+                    float(&a)[4] = acc[q % NA][m];
+                    a[0] = fmaf(tmp[0], s_lo, a[0]), a[1] = fmaf(tmp[1], s_lo, a[1]);
+                    a[2] = fmaf(tmp[2], s_hi, a[2]), a[3] = fmaf(tmp[3], s_hi, a[3]);
                 }
             } else {
                 block_mma<FMT, MT, NA>(acc, cw[q], ew[q], xv, sh);
@@ -606,7 +637,7 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
         static_assert(XSM || !ONE, "the one-row instantiations keep x in shared memory");
         // PRE: x too large for that: the chunk's activations are loaded (through L1) before the stage is waited for
         constexpr bool PRE = !XSM;
-        constexpr int EXPB = FMT == TKD_BFP4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
+        constexpr int EXPB = FMT == TKD_BFP4 || FMT == TKD_INT4 ? 64 : (FMT == TKD_BFP8 ? 32 : 0);
         const uint16_t* xb[NH][MT];
 #pragma unroll
         // (a lane whose row lies beyond M reads row M - 1 instead: a B column only feeds its own output column, and
@@ -617,7 +648,9 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
                 xb[hh][m] = p.x + (int64_t)min(8 * m + g, M - 1) * p.ldx + 8 * t + (h0 + hh) * F::KSA;
         const uint32_t ring_a = smem_u32(ring), hdr_a = smem_u32(hdr);
         const uint32_t code_off = g8 * (F::SUBSA * F::SAB) + h0 * F::SAB + EXPB + lane * 16;
-        const uint32_t exp_off = g8 * (F::SUBSA * F::SAB) + h0 * F::SAB + t * (EXPB / 4);
+        // (this lane's exponent words of a super-atom; TKD_INT4: its pair of scale words, by its row of the fragment)
+        const uint32_t exp_lane = FMT == TKD_INT4 ? g * 8 : t * (EXPB / 4);
+        const uint32_t exp_off = g8 * (F::SUBSA * F::SAB) + h0 * F::SAB + exp_lane;
         uint32_t slot = 0, phase = 0, pi = 0;  // ring position and its parity; deliveries so far
         const int64_t first_it = lead > 0 ? tail0 : i0;
         int kc = (int)(first_it - idiv(p, first_it, p.nslices) * p.nslices) * p.ks;
@@ -667,7 +700,7 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
                     // the last chunk of K: fewer super-atoms, the groups closer together
                     const int nsa = nsa_total - kc / CK * F::SUBSA;
                     const uint32_t gb = sbase + g8 * nsa * F::SAB + h * F::SAB;
-                    chunk_mma<FMT, MT, NA, false, PRE, XSM>(acc[hh], gb + EXPB + lane * 16, gb + t * (EXPB / 4), xpre, xb[hh], kc,
+                    chunk_mma<FMT, MT, NA, false, PRE, XSM>(acc[hh], gb + EXPB + lane * 16, gb + exp_lane, xpre, xb[hh], kc,
                                                             K, h, nsa, sh, xs_lane + kc * 2);
                 }
             }
@@ -750,7 +783,7 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
             const bool in_w = n < sg.n_valid;
             int ebyte = 0;
             float sc = 1.f;
-            if constexpr (FMT != TKD_BF16) ebyte = (glu2 && et >= 64 ? sg.emax2 : sg.emax)[n >> 4];
+            if constexpr (FMT == TKD_BFP8 || FMT == TKD_BFP4) ebyte = (glu2 && et >= 64 ? sg.emax2 : sg.emax)[n >> 4];
             if (p.scale_dt != TKD_DT_NONE && in_w) {
                 const void* sp = glu2 && et >= 64 ? p.scale2 : p.scale;
                 sc = p.scale_dt == TKD_DT_BF16 ? bf16_bits_to_f32(static_cast<const uint16_t*>(sp)[n])
@@ -850,7 +883,7 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
             auto output_stage = [&](auto rows_const) {
                 constexpr int R = decltype(rows_const)::value;
                 // the block-float factor of this thread's group
-                if constexpr (FMT != TKD_BF16) {
+                if constexpr (FMT == TKD_BFP8 || FMT == TKD_BFP4) {
                     // 2^e in two factors, each a normal float (e is within -69 .. 191)
                     const int e = tkd_out_exp(FMT, ebyte);
                     const int e1 = e / 2, e2 = e - e1;

@@ -10,7 +10,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parents[1]
 LIB_PATH = PKG / "csrc" / "libtkd.so"
 
-FMT_BFP8, FMT_BFP4, FMT_BF16 = 0, 1, 2
+FMT_BFP8, FMT_BFP4, FMT_BF16, FMT_INT4 = 0, 1, 2, 3
 EPI_PLAIN, EPI_GLU_IL, EPI_GLU2, EPI_RESIDUAL, EPI_OUT32 = range(5)
 DT_NONE, DT_BF16, DT_F32 = 0, 1, 2
 ERR_TIMEOUT, ERR_WIDE, ERR_FIXED_SCRATCH = 3, 5, 6
