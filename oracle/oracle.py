@@ -250,3 +250,37 @@ def records_host(t, rows, k):
     vals[keys == 0] = -np.inf
     idx[(keys == 0) | (idx == 0xFFFFFFFF)] = -1
     return torch.from_numpy(vals), torch.from_numpy(idx)
+
+
+# ---- the int4 weight with group scales (int4/w4a16.py of the reference): codes q in -7..7, one bf16 scale per output
+# column and 32 consecutive inputs, the weight being q * s exactly. PARITY PINNED for the host forms (nibbles,
+# dequantized, reference: golden vectors made by running the reference's own functions, tests/golden/int4.npz).
+
+def int4_nibbles(codes):
+    """int codes [K, N] numpy (-7..7) -> uint8 [K / 32, N / 32, 512] (w4a16.py:59-66): per 32 x 32 tile its four 16 x 16
+    faces in the order (rows 0-15, cols 0-15), (0-15, 16-31), (16-31, 0-15), (16-31, 16-31), each row-major, a value as
+    sign << 3 | magnitude, element 2 i in the low nibble of byte i."""
+    q = np.asarray(codes, dtype=np.int16)
+    k, n = q.shape
+    out = np.zeros((k // 32, n // 32, 512), np.uint8)
+    for kt in range(k // 32):
+        for nt in range(n // 32):
+            tile = q[32 * kt : 32 * kt + 32, 32 * nt : 32 * nt + 32]
+            faces = [tile[:16, :16], tile[:16, 16:], tile[16:, :16], tile[16:, 16:]]
+            flat = np.concatenate([f.reshape(-1) for f in faces])
+            v = (np.abs(flat) | ((flat < 0).astype(np.int16) << 3)).astype(np.uint8)
+            out[kt, nt] = v[0::2] | (v[1::2] << 4)
+    return out
+
+
+def int4_dequantized(codes, scales):
+    """float32 [N_out, K]: q * s with s rounded to bf16 (w4a16.py:100-102). codes [N_out, K] int, scales [N_out, K / 32]."""
+    s = torch.as_tensor(scales).to(torch.bfloat16).float().numpy()
+    return np.asarray(codes, dtype=np.float32) * np.repeat(s, 32, axis=1)
+
+
+def int4_reference(x, codes, scales):
+    """x (rounded to bf16) @ (q * s).T, accumulated in float64 (w4a16.py:105-107 states it in float32; the tests' bars
+    are relative, test_int4.py:8-12). x torch [M, K]."""
+    xb = torch.as_tensor(x).to(torch.bfloat16).double().numpy()
+    return xb @ int4_dequantized(codes, scales).astype(np.float64).T

@@ -27,6 +27,7 @@ sys.path.insert(0, str(ref))
 from common import device as cdev  # noqa: E402
 from dense_reader import linear as rlin  # noqa: E402
 from moe import moe8  # noqa: E402
+from int4 import w4a16  # noqa: E402
 
 out = Path(__file__).resolve().parent
 sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()  # noqa: E731
@@ -90,3 +91,30 @@ np.savez_compressed(
     x=x.numpy(), wk=wk.numpy(), sc=sc.numpy(), ref=rlin.reference(x, wk).numpy(), ref_sc=rlin.reference(x, wk, sc).numpy(),
 )
 print("t1", sha(t1), "v1", sha(v1), "t2", sha(t2))
+
+
+# 6. the int4 weight with group scales (int4/w4a16.py): nibbles, dequantized and reference on the test file's own
+# case generator (int4/tests/test_int4.py:27-31, seeds of test_matmul's first case and a small one)
+def int4_case(n, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    codes = torch.randint(-7, 8, (n, k), generator=g).to(torch.int8)
+    scales = (torch.rand(n, k // 32, generator=g) * 0.01 + 0.001).to(torch.bfloat16)
+    return codes, scales
+
+
+c1, s1 = int4_case(64, 96, 5)
+g = torch.Generator().manual_seed(6)
+x1 = torch.randn(1, 96, generator=g)
+c2, s2 = int4_case(1152, 1024, 1024 + 1152)
+g = torch.Generator().manual_seed(1152)
+x2 = torch.randn(1, 1024, generator=g)
+x2[:, torch.randperm(1024, generator=g)[:8]] *= 20
+np.savez_compressed(
+    out / "int4.npz",
+    codes1=c1.numpy(), scales1_bits=s1.view(torch.int16).numpy(), x1=x1.numpy(),
+    nib1=w4a16.nibbles(c1.T.contiguous()).numpy(), deq1=w4a16.dequantized(c1, s1).numpy(),
+    ref1=w4a16.reference(x1, c1, s1).numpy(),
+    codes2_sha=sha(c2.numpy()), nib2_sha=sha(w4a16.nibbles(c2.T.contiguous()).numpy()),
+    deq2_sha=sha(w4a16.dequantized(c2, s2).numpy()), ref2=w4a16.reference(x2, c2, s2).numpy(),
+)
+print("wrote", out / "int4.npz")
