@@ -53,8 +53,10 @@ WORKLOADS = {
     "c2": dict(k=4096, n=14336, fmt="bfp4", what="Llama-3-8B MLP gate/up: two [14336,4096] bfloat4_b, f32 column scales, SwiGLU"),
     "c3": dict(k=14336, n=4096, fmt="bfp8", what="Llama-3-8B MLP down: [4096,14336] bfloat8_b + f32 residual, f32 out"),
     "c5": dict(k=4096, n=151936, fmt="bfp8", what="LM head [151936,4096] bfloat8_b, top-8 records per 2048 columns"),
+    # the sibling streamer (int4/w4a16.py of the reference): the gate and up weights of config 2 as one int4 weight
+    "w4": dict(k=4096, n=28672, fmt="int4", what="int4 codes with bf16 group scales (G = 32): [28672,4096], one token"),
 }
-BYTES_PER_WEIGHT = {"bfp8": 1.0625, "bfp4": 0.5625, "bf16": 2.0}
+BYTES_PER_WEIGHT = {"bfp8": 1.0625, "bfp4": 0.5625, "bf16": 2.0, "int4": 0.5625}
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -119,13 +121,19 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
     from dense_reader import linear
 
     wl = WORKLOADS[name]
-    dt = {"bfp8": ttnn.bfloat8_b, "bfp4": ttnn.bfloat4_b}[wl["fmt"]]
+    dt = {"bfp8": ttnn.bfloat8_b, "bfp4": ttnn.bfloat4_b, "int4": None}[wl["fmt"]]
     g, x, k, n = make_inputs(wl, m, seed0, n_cols)
     tx = ttnn.from_torch(x.reshape(1, 1, m, k), dtype=ttnn.bfloat16, layout=ttnn.TILE_LAYOUT, device=device)
     sets = []
     for c in range(copies):
         gw = torch.Generator().manual_seed(seed0 + 1 + c)
-        if name == "c2":
+        if name == "w4":
+            from int4 import w4a16
+
+            codes = torch.randint(-7, 8, (n, k), generator=gw).to(torch.int8)
+            scales = (torch.rand(n, k // 32, generator=gw) * 0.01 + 0.001).to(torch.bfloat16)
+            sets.append((w4a16.packed(w4a16.int4_weight(device, codes), w4a16.group_scales(device, scales)),))
+        elif name == "c2":
             wg = linear.native_weight(device, torch.randn(n, k, generator=gw) * 0.02, dt)[0]
             wu = linear.native_weight(device, torch.randn(n, k, generator=gw) * 0.02, dt)[0]
             sets.append((wg, wu))
@@ -189,7 +197,7 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
     # algorithmic bytes of one launch: the weight stream once, x, scales, residual, output
     other = m * k * 2
     other += {"c2": 2 * n * 4 + m * n * 2, "c3": 2 * m * n * 4, "c5": linear.topk_units(n) * 2 * 8 * 4 if name == "c5" else 0,
-              "c1": m * n * 2}[name]
+              "c1": m * n * 2, "w4": m * n * 2}[name]
     return dict(step=step, x=tx, y=y, wbytes=wbytes, abytes=wbytes + other, x_host=x, sets=sets, **extra)
 
 
@@ -207,7 +215,12 @@ def cpu_reference_arm(name, m, steps, warmup, budget_s=20.0, min_s=3.0):
     g, x, _, _ = make_inputs(wl, m, 1234)
     gw = torch.Generator().manual_seed(1235)
     nw = 2 if name == "c2" else 1
-    wq = [torch.from_numpy(orc.native_values(torch.randn(n_s, k, generator=gw) * 0.02, wl["fmt"])[0]) for _ in range(nw)]
+    if name == "w4":  # (the reference's own host statement: x as bf16 times q * s in float32, int4/w4a16.py:105-107)
+        codes = torch.randint(-7, 8, (n_s, k), generator=gw).to(torch.int8)
+        scales = (torch.rand(n_s, k // 32, generator=gw) * 0.01 + 0.001).to(torch.bfloat16)
+        wq = [torch.from_numpy(orc.int4_dequantized(codes.numpy(), scales)).T.contiguous()]
+    else:
+        wq = [torch.from_numpy(orc.native_values(torch.randn(n_s, k, generator=gw) * 0.02, wl["fmt"])[0]) for _ in range(nw)]
     sg = torch.rand(n_s, generator=g) + 0.5
     su = torch.rand(n_s, generator=g) + 0.5
     res = torch.randn(m, n_s, generator=g)
@@ -279,6 +292,8 @@ def main():
     steps, warmup = args.steps, max(3, args.warmup)
     config = {"workload": f"{args.workload}: {wl['what']}", "rows": m, "K": wl["k"], "N": wl["n"], "format": wl["fmt"],
               "arithmetic": "bf16 activations x block-float weights (exact products), fp32 accumulation"}
+    if wl["fmt"] == "int4":
+        config["arithmetic"] = "bf16 activations x int4 codes (exact products), fp32 sums per 32 k, times the bf16 group scale in fp32"
 
     if args.impl == "reference":
         if rank != 0:
@@ -457,6 +472,7 @@ def main():
     if world == 1 and args.workload == "c2" and m == 1 and not args.cols:
         for key, rows in (("sub", 1), ("rows32", 32)):
             subs[key] = sub_case("c3", rows, device, max(50, steps // 3))
+        subs["int4"] = sub_case("w4", 1, device, max(50, steps // 3))
     if args.workload == "c2" and m == 1 and not args.cols and (world == 1 or fused):
         subs["c5_strong"] = lm_head_strong(device, world, rank, max(30, steps // 10))
     linear.check_status(device)
@@ -752,7 +768,7 @@ def finish(world):
 
 # DRAM bytes per launch of tkd_stream_kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum), per
 # workload at M = 1 (the summaries under profiles/); None where no capture of the workload is summarised there.
-TRAFFIC = {"c2": 66_769_408, "c3": 62_681_600, "c5": 667_036_928}
+TRAFFIC = {"c2": 66_769_408, "c3": 62_681_600, "c5": 667_036_928, "w4": 66_386_432}
 
 if __name__ == "__main__":
     sys.exit(main())
