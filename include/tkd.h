@@ -206,6 +206,14 @@ int tkd_matmul_noalloc_reset(void* stream);
  * first tkd_matmul_noalloc call does, without clearing anything. No counterpart in the reference. */
 int tkd_noalloc_scratch_address(void** ptr);
 
+/* The block Hadamard rotation in front of the reference's ternary projections (ternary_matmul/t2.py:262-340 hadamard,
+ * kernels/had_reader.cpp, had_compute.cpp, had_writer.cpp; rotate_rows :220-259 for many rows): per row and block of 1024
+ * inputs out = H_1024 (s * x), H the +-1 Sylvester matrix, unnormalised (32 times the orthonormal transform), computed in
+ * float32 and rounded to bf16 once. x, out: bf16 [rows, k] with ldx, ldo elements a row (multiples of 4, 8-byte aligned
+ * bases; out may be x); k a multiple of 1024; signs: k / 2 words, word q with bit 15 set when input 2 q is negated and
+ * bit 31 for input 2 q + 1 (the reference's mask, t2.py:185-202). */
+int tkd_hadamard(const void* x, int64_t ldx, const uint32_t* signs, int rows, int k, void* out, int64_t ldo, void* stream);
+
 /* The best `top` candidates of every row among `nrecords` top-k records (the record layout above: keys[rows][k] then
  * indices[rows][k]), key descending and index ascending among equal keys; out is one record of the same layout with
  * `top` in place of k (slots beyond the candidates there are: key 0, index 0xFFFFFFFF). Stands in for the `vh.topk(top)`

@@ -284,3 +284,56 @@ def int4_reference(x, codes, scales):
     are relative, test_int4.py:8-12). x torch [M, K]."""
     xb = torch.as_tensor(x).to(torch.bfloat16).double().numpy()
     return xb @ int4_dequantized(codes, scales).astype(np.float64).T
+
+
+# ---- the ternary weight with group scales and its block Hadamard (ternary_matmul/t2.py of the reference). PARITY PINNED
+# for the host forms (tiles, rotate, dequantize, reference: tests/golden/ternary.npz, made by running the reference).
+
+T2_FORMATS = {"bfp2": (320, 127, 2), "bfp2c": (320, 127, 2), "bfp4": (576, 129, 4)}
+
+
+def t2_tiles(q, fmt="bfp2"):
+    """trits [K, N] numpy -> uint8 [K / 32, N / 32, tile bytes] (t2.py:81-99): 64 exponent bytes (127 for the 2-bit
+    codes, 129 for the 4-bit ones), then the 1024 codes face by face; 2-bit code = sign << 1 | magnitude, four to a
+    byte from the low bits up; 4-bit code = sign << 3 | magnitude, two to a byte."""
+    tb, exp, bits = T2_FORMATS[fmt]
+    q = np.asarray(q, dtype=np.int16)
+    k, n = q.shape
+    out = np.zeros((k // 32, n // 32, tb), np.uint8)
+    out[..., :64] = exp
+    for kt in range(k // 32):
+        for nt in range(n // 32):
+            tile = q[32 * kt : 32 * kt + 32, 32 * nt : 32 * nt + 32]
+            flat = np.concatenate([f.reshape(-1) for f in (tile[:16, :16], tile[:16, 16:], tile[16:, :16], tile[16:, 16:])])
+            neg, mag = (flat < 0).astype(np.uint8), (flat != 0).astype(np.uint8)
+            if bits == 2:
+                c = (neg << 1) | mag
+                out[kt, nt, 64:] = c[0::4] | (c[1::4] << 2) | (c[2::4] << 4) | (c[3::4] << 6)
+            else:
+                c = (neg << 3) | mag
+                out[kt, nt, 64:] = c[0::2] | (c[1::2] << 4)
+    return out
+
+
+def t2_rotate(x, signs, block=1024):
+    """x' = H_block (signs * x) / sqrt(block) per block of the last dimension, float64 (t2.py:213-217), by butterflies
+    (the Sylvester matrix's own recursion) instead of the matrix product."""
+    v = (np.asarray(x, dtype=np.float64) * np.asarray(signs, dtype=np.float64)).reshape(-1, block).copy()
+    h = 1
+    while h < block:
+        w = v.reshape(-1, block // (2 * h), 2, h)
+        a, b = w[:, :, 0, :].copy(), w[:, :, 1, :].copy()
+        w[:, :, 0, :], w[:, :, 1, :] = a + b, a - b
+        h *= 2
+    return (v / np.sqrt(block)).reshape(np.asarray(x).shape)
+
+
+def t2_dequantize(trits, scales, g):
+    """float32 [N_out, K]: q * s, s as given (t2.py:343-345)."""
+    return np.asarray(trits, dtype=np.float32) * np.repeat(torch.as_tensor(scales).float().numpy(), g, axis=1)
+
+
+def t2_reference(x, trits, scales, g):
+    """x (as bf16) @ (q * bf16(s)).T, accumulated in float64 (t2.py:348-350 states it in float32)."""
+    xb = torch.as_tensor(x).to(torch.bfloat16).double().numpy()
+    return xb @ t2_dequantize(trits, torch.as_tensor(scales).to(torch.bfloat16), g).astype(np.float64).T

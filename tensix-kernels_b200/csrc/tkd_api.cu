@@ -427,6 +427,14 @@ int tkd_noalloc_scratch_address(void** ptr) {
     return noalloc_address(ptr, nullptr);
 }
 
+int tkd_hadamard(const void* x, int64_t ldx, const uint32_t* signs, int rows, int k, void* out, int64_t ldo, void* stream) {
+    if (!x || !signs || !out || rows < 1 || rows > 65535 || k < 1024 || k % 1024 || ldx < k || ldo < k || (ldx | ldo) % 4)
+        return TKD_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(signs)) & 7)
+        return TKD_ERR_BAD_ARG;
+    return launch_err(tkd_launch_hadamard(x, ldx, signs, rows, k, out, ldo, static_cast<cudaStream_t>(stream)));
+}
+
 int tkd_topk_merge(const uint32_t* records, int nrecords, int rows, int k, int top, uint32_t* out, void* stream) {
     if (!records || !out || nrecords < 1 || rows < 1 || rows > 16 || k < 1 || rows * k > 64 || top < 1 || top > 1024)
         return TKD_ERR_BAD_ARG;

@@ -98,6 +98,8 @@ struct TkdParams {
 };
 
 int tkd_launch_stream(const TkdParams& p, int grid, size_t smem, cudaStream_t st);
+int tkd_launch_hadamard(const void* x, int64_t ldx, const uint32_t* signs, int rows, int K, void* out, int64_t ldo,
+                        cudaStream_t st);
 int tkd_launch_topk_merge(const uint32_t* records, int nrec, int rows, int k, int top, uint32_t* out, cudaStream_t st);
 int tkd_launch_head_pick(const uint32_t* records, int nrec, int rows, int k, int top, uint32_t vocab, const uint16_t* x,
                          int64_t ldx, int dim, const uint16_t* head, int64_t ld_head, int round, uint32_t* out,

@@ -63,6 +63,7 @@ SYMBOLS = {
     "tkd_matmul_noalloc": (c_i32, [ctypes.POINTER(TkdMatmul), c_vp]),
     "tkd_matmul_noalloc_reset": (c_i32, [c_vp]),
     "tkd_noalloc_scratch_address": (c_i32, [ctypes.POINTER(c_vp)]),
+    "tkd_hadamard": (c_i32, [c_vp, c_i64, c_vp, c_i32, c_i32, c_vp, c_i64, c_vp]),
     "tkd_topk_merge": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp]),
     "tkd_head_pick": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_u32, c_vp, c_i64, c_i32, c_vp, c_i64, c_i32, c_vp, c_vp, c_vp]),
     "tkd_head_pick_records": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_u32, c_vp, c_vp, c_vp, c_vp]),

@@ -28,6 +28,7 @@ from common import device as cdev  # noqa: E402
 from dense_reader import linear as rlin  # noqa: E402
 from moe import moe8  # noqa: E402
 from int4 import w4a16  # noqa: E402
+from ternary_matmul import t2 as tern  # noqa: E402
 
 out = Path(__file__).resolve().parent
 sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()  # noqa: E731
@@ -118,3 +119,29 @@ np.savez_compressed(
     deq2_sha=sha(w4a16.dequantized(c2, s2).numpy()), ref2=w4a16.reference(x2, c2, s2).numpy(),
 )
 print("wrote", out / "int4.npz")
+
+
+# 7. the ternary weight (ternary_matmul/t2.py): tiles in its three forms, rotate, dequantize, reference on the test file's
+# own generators (ternary_matmul/tests/test_ternary.py:35-62)
+def t2_weight(n, k, g_, seed, zeros=0.3):
+    gen = torch.Generator().manual_seed(seed)
+    u = torch.randint(0, 2000, (n, k), generator=gen, dtype=torch.int16)
+    trits = torch.where(u < 2000 * zeros, 0, torch.where(u % 2 == 0, 1, -1)).to(torch.int8)
+    scales = (0.01 + 0.02 * torch.rand(n, k // g_, generator=gen)).to(torch.float16)
+    return trits, scales
+
+
+tr, sc = t2_weight(64, 2048, 128, 5)
+gen = torch.Generator().manual_seed(6)
+sg = torch.where(torch.rand(2048, generator=gen) < 0.5, -1.0, 1.0)
+gen = torch.Generator().manual_seed(7)
+xt = torch.randn(2, 2048, generator=gen).to(torch.bfloat16)
+np.savez_compressed(
+    out / "ternary.npz",
+    trits=tr.numpy(), scales_bits=sc.view(torch.int16).numpy(), signs=sg.numpy(), x_bits=xt.view(torch.int16).numpy(),
+    tiles_bfp2=tern.tiles(tr.T.contiguous(), "bfp2").numpy(), tiles_bfp2c=tern.tiles(tr.T.contiguous(), "bfp2c").numpy(),
+    tiles_bfp4=tern.tiles(tr.T.contiguous(), "bfp4").numpy(),
+    rotated=tern.rotate(xt.double(), sg).numpy(), deq=tern.dequantize(tr, sc.to(torch.bfloat16), 128).numpy(),
+    ref=tern.reference(xt, tr, sc, 128).numpy(), sylvester8=tern.sylvester(8).numpy(),
+)
+print("wrote", out / "ternary.npz")
