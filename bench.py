@@ -55,6 +55,8 @@ WORKLOADS = {
     "c5": dict(k=4096, n=151936, fmt="bfp8", what="LM head [151936,4096] bfloat8_b, top-8 records per 2048 columns"),
     # the sibling streamer (int4/w4a16.py of the reference): the gate and up weights of config 2 as one int4 weight
     "w4": dict(k=4096, n=28672, fmt="int4", what="int4 codes with bf16 group scales (G = 32): [28672,4096], one token"),
+    # ... and ternary_matmul/t2.py: the same shape in trits with G = 128, the block Hadamard in front (two launches)
+    "t2": dict(k=4096, n=28672, fmt="int4", what="ternary weight (G = 128) behind the block Hadamard: [28672,4096], one token"),
 }
 BYTES_PER_WEIGHT = {"bfp8": 1.0625, "bfp4": 0.5625, "bf16": 2.0, "int4": 0.5625}
 L2_BYTES = 126 * 1024 * 1024
@@ -118,7 +120,7 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
     """The device-side tensors of one workload (n_cols: this rank's columns of it, when it is split): `copies` distinct
     packed weight sets, and a closure running step i."""
     from common import ttnn_like as ttnn
-    from dense_reader import linear
+    from dense_reader import _tkd, linear
 
     wl = WORKLOADS[name]
     dt = {"bfp8": ttnn.bfloat8_b, "bfp4": ttnn.bfloat4_b, "int4": None}[wl["fmt"]]
@@ -127,7 +129,15 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
     sets = []
     for c in range(copies):
         gw = torch.Generator().manual_seed(seed0 + 1 + c)
-        if name == "w4":
+        if name == "t2":
+            from ternary_matmul import t2
+
+            u = torch.randint(0, 2000, (n, k), generator=gw, dtype=torch.int16)
+            trits = torch.where(u < 600, 0, torch.where(u % 2 == 0, 1, -1)).to(torch.int8)
+            scales = (0.01 + 0.02 * torch.rand(n, k // 128, generator=gw)).to(torch.float16)
+            sets.append((t2.packed(t2.ternary_weight(device, trits, fmt="bfp4"),
+                                   t2.group_scales(device, scales, t2.HADAMARD_SCALE), 128),))
+        elif name == "w4":
             from int4 import w4a16
 
             codes = torch.randint(-7, 8, (n, k), generator=gw).to(torch.int8)
@@ -183,6 +193,20 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
             return linear.topk_merge(spec_t["r"], 1, 8, 32, out=top32) if merge else spec_t["r"]
         weights = 1
         extra.update(launches=2, spec=spec, top32=top32)
+    elif name == "t2":
+        from ternary_matmul import t2
+
+        mask = t2.hadamard_signs(device, torch.where(torch.rand(k, generator=g) < 0.5, -1.0, 1.0))
+        y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
+        xr = ttnn.allocate_tensor_on_device([1, 1, m, k], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
+
+        def step(i, x_t=tx, y_t=y, **kw):
+            # the rotation (tkd_hadamard into a fixed buffer), then the stream kernel
+            _tkd.check(_tkd.lib().tkd_hadamard(x_t.t.data_ptr(), k, mask.t.data_ptr(), m, k, xr.t.data_ptr(), k,
+                                               torch.cuda.current_stream().cuda_stream), "tkd_hadamard")
+            return linear.matmul(xr, sets[i % copies][0], None, out=y_t, **kw)
+        weights = 1
+        extra.update(launches=2)
     else:
         y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
 
@@ -197,7 +221,7 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
     # algorithmic bytes of one launch: the weight stream once, x, scales, residual, output
     other = m * k * 2
     other += {"c2": 2 * n * 4 + m * n * 2, "c3": 2 * m * n * 4, "c5": linear.topk_units(n) * 2 * 8 * 4 if name == "c5" else 0,
-              "c1": m * n * 2, "w4": m * n * 2}[name]
+              "c1": m * n * 2, "w4": m * n * 2, "t2": m * n * 2 + 2 * m * k * 2 + k // 2 * 4}[name]
     return dict(step=step, x=tx, y=y, wbytes=wbytes, abytes=wbytes + other, x_host=x, sets=sets, **extra)
 
 
@@ -215,7 +239,16 @@ def cpu_reference_arm(name, m, steps, warmup, budget_s=20.0, min_s=3.0):
     g, x, _, _ = make_inputs(wl, m, 1234)
     gw = torch.Generator().manual_seed(1235)
     nw = 2 if name == "c2" else 1
-    if name == "w4":  # (the reference's own host statement: x as bf16 times q * s in float32, int4/w4a16.py:105-107)
+    if name == "t2":  # (ternary_matmul/t2.py:213-217, :348-350: x rotated, then times q * s in float32)
+        u = torch.randint(0, 2000, (n_s, k), generator=gw, dtype=torch.int16)
+        trits = torch.where(u < 600, 0, torch.where(u % 2 == 0, 1, -1)).to(torch.int8)
+        scales = (0.01 + 0.02 * torch.rand(n_s, k // 128, generator=gw)).to(torch.float16)
+        wq = [torch.from_numpy(orc.t2_dequantize(trits.numpy(), scales.to(torch.bfloat16), 128)).T.contiguous()]
+        signs = torch.where(torch.rand(k, generator=g) < 0.5, -1.0, 1.0)
+        h32 = torch.tensor([[1.0]])
+        while h32.shape[0] < 1024:
+            h32 = torch.cat([torch.cat([h32, h32], 1), torch.cat([h32, -h32], 1)], 0)
+    elif name == "w4":  # (the reference's own host statement: x as bf16 times q * s in float32, int4/w4a16.py:105-107)
         codes = torch.randint(-7, 8, (n_s, k), generator=gw).to(torch.int8)
         scales = (torch.rand(n_s, k // 32, generator=gw) * 0.01 + 0.001).to(torch.bfloat16)
         wq = [torch.from_numpy(orc.int4_dequantized(codes.numpy(), scales)).T.contiguous()]
@@ -231,6 +264,9 @@ def cpu_reference_arm(name, m, steps, warmup, budget_s=20.0, min_s=3.0):
             return (torch.nn.functional.silu(gt) * up).to(torch.bfloat16)
         if name == "c3":
             return orc.reference(x, wq[0]) + res
+        if name == "t2":
+            xr = ((x.float() * signs).reshape(m, -1, 1024) @ h32.T).reshape(m, k).to(torch.bfloat16)
+            return orc.reference(xr, wq[0]).to(torch.bfloat16)
         y = orc.reference(x, wq[0]).to(torch.bfloat16)
         if name == "c5":
             return torch.topk(y.float().reshape(m, -1, min(2048, n_s)), 8, dim=-1)
@@ -473,6 +509,7 @@ def main():
         for key, rows in (("sub", 1), ("rows32", 32)):
             subs[key] = sub_case("c3", rows, device, max(50, steps // 3))
         subs["int4"] = sub_case("w4", 1, device, max(50, steps // 3))
+        subs["ternary"] = sub_case("t2", 1, device, max(50, steps // 3))
     if args.workload == "c2" and m == 1 and not args.cols and (world == 1 or fused):
         subs["c5_strong"] = lm_head_strong(device, world, rank, max(30, steps // 10))
     linear.check_status(device)
