@@ -55,7 +55,7 @@ WORKLOADS = {
     "c5": dict(k=4096, n=151936, fmt="bfp8", what="LM head [151936,4096] bfloat8_b, top-8 records per 2048 columns"),
     # the sibling streamer (int4/w4a16.py of the reference): the gate and up weights of config 2 as one int4 weight
     "w4": dict(k=4096, n=28672, fmt="int4", what="int4 codes with bf16 group scales (G = 32): [28672,4096], one token"),
-    # ... and ternary_matmul/t2.py: the same shape in trits with G = 128, the block Hadamard in front (two launches)
+    # ... and ternary_matmul/t2.py: the same shape in trits with G = 128, the block Hadamard in front (inside the kernel)
     "t2": dict(k=4096, n=28672, fmt="int4", what="ternary weight (G = 128) behind the block Hadamard: [28672,4096], one token"),
 }
 BYTES_PER_WEIGHT = {"bfp8": 1.0625, "bfp4": 0.5625, "bf16": 2.0, "int4": 0.5625}
@@ -120,7 +120,7 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
     """The device-side tensors of one workload (n_cols: this rank's columns of it, when it is split): `copies` distinct
     packed weight sets, and a closure running step i."""
     from common import ttnn_like as ttnn
-    from dense_reader import _tkd, linear
+    from dense_reader import linear
 
     wl = WORKLOADS[name]
     dt = {"bfp8": ttnn.bfloat8_b, "bfp4": ttnn.bfloat4_b, "int4": None}[wl["fmt"]]
@@ -198,15 +198,15 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
 
         mask = t2.hadamard_signs(device, torch.where(torch.rand(k, generator=g) < 0.5, -1.0, 1.0))
         y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
-        xr = ttnn.allocate_tensor_on_device([1, 1, m, k], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
 
         def step(i, x_t=tx, y_t=y, **kw):
-            # the rotation (tkd_hadamard into a fixed buffer), then the stream kernel
-            _tkd.check(_tkd.lib().tkd_hadamard(x_t.t.data_ptr(), k, mask.t.data_ptr(), m, k, xr.t.data_ptr(), k,
-                                               torch.cuda.current_stream().cuda_stream), "tkd_hadamard")
-            return linear.matmul(xr, sets[i % copies][0], None, out=y_t, **kw)
+            # one launch: the stream kernel rotates its own copy of x first
+            return linear.matmul(x_t, sets[i % copies][0], None, out=y_t, hadamard=mask, **kw)
+
+        def host_step(i, x_pin, y_pin, x_t, y_t, stream, **kw):
+            linear.matmul_host(x_pin, y_pin, x_t, sets[i % copies][0], None, out=y_t, stream=stream, hadamard=mask, **kw)
+        extra["host_step"] = host_step
         weights = 1
-        extra.update(launches=2)
     else:
         y = ttnn.allocate_tensor_on_device([1, 1, m, n], ttnn.bfloat16, ttnn.TILE_LAYOUT, device)
 
@@ -221,7 +221,7 @@ def build_gpu_case(name, m, device, copies, seed0, n_cols=None):
     # algorithmic bytes of one launch: the weight stream once, x, scales, residual, output
     other = m * k * 2
     other += {"c2": 2 * n * 4 + m * n * 2, "c3": 2 * m * n * 4, "c5": linear.topk_units(n) * 2 * 8 * 4 if name == "c5" else 0,
-              "c1": m * n * 2, "w4": m * n * 2, "t2": m * n * 2 + 2 * m * k * 2 + k // 2 * 4}[name]
+              "c1": m * n * 2, "w4": m * n * 2, "t2": m * n * 2 + k // 2 * 4}[name]
     return dict(step=step, x=tx, y=y, wbytes=wbytes, abytes=wbytes + other, x_host=x, sets=sets, **extra)
 
 

@@ -154,6 +154,11 @@ typedef struct {
                                dependent of the work before it on the stream, and its first weight loads may run while
                                that work drains. 1: something enqueued earlier on the stream still writes them (tkd_pack,
                                a copy): the launch is ordered behind all of it, at the cost of that overlap. */
+    const uint32_t* hadamard; /* or NULL. TKD_FMT_INT4 only (the ternary projections of a rotated checkpoint,
+                               ternary_matmul/t2.py:409-495 hadamard=): the activations are rotated first, x' = H_1024
+                               (s * x) per block of 1024 inputs, unnormalised, exactly as tkd_hadamard does it (its sign
+                               words), inside the kernel's own copy of x: k a multiple of 1024, and x must fit in shared
+                               memory beside the ring (TKD_ERR_UNSUPPORTED otherwise: call tkd_hadamard first) */
 } TkdMatmul;
 #define TKD_MAX_RANKS 8
 #define TKD_FLAG_SEQ 8      /* flags[0..7]: calls completed by rank r, as told by r; flags[8]: calls completed here */

@@ -332,6 +332,11 @@ static int run_matmul(const TkdMatmul* a, void* workspace, uint64_t workspace_by
     p.ytmp = reinterpret_cast<uint16_t*>(ws + L.off_ytmp);
     p.status = a->status;
     p.no_pdl = a->weights_fresh != 0;
+    if (a->hadamard) {
+        if (a->fmt != TKD_INT4 || a->k % 1024 || !p.x_smem) return TKD_ERR_UNSUPPORTED;
+        if (reinterpret_cast<uintptr_t>(a->hadamard) & 15) return TKD_ERR_BAD_ARG;
+        p.had = a->hadamard;
+    }
     if (a->nranks > 1) {
         if (!a->flags) return TKD_ERR_BAD_ARG;
         p.npeers = a->nranks - 1;

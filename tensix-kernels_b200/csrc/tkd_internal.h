@@ -92,6 +92,7 @@ struct TkdParams {
     int x_smem;          // 1 to 8 rows, and all of x (K rounded up to a chunk) fits in shared memory at off_xt
     int x_stride;        // ... bytes from one row of it to the next
     int no_pdl;          // launch without programmatic dependent launch (the weights may still be being written)
+    const uint32_t* had;  // TKD_INT4: sign words of the block Hadamard applied to x in shared memory first (or null)
     // shared-memory map (bytes from the start of dynamic shared memory)
     int off_pbuf, off_tbuf, off_xt, off_ring;
     int stage_bytes;

@@ -665,6 +665,62 @@ __global__ void __launch_bounds__((1 + kStreamWarps + 4) * 32, 1) tkd_stream_ker
             // bytes on one barrier. (512 lanes loading and storing their pieces and a barrier among them took 2.0 us of a
             // 13 us launch, all of it before the first chunk.)
             x_here = mbar_wait(xbar, 0, p.status);  // (the copies were issued right after the wait for the kernel before)
+            if constexpr (FMT == TKD_INT4) {
+                // The ternary projections' block Hadamard (ternary_matmul/t2.py:409-495, hadamard=), on this CTA's copy of
+                // x: x' = H_1024 (s * x), unnormalised. A warp takes a (row, block of 1024) at a time, a lane 32
+                // consecutive inputs in registers: five butterfly stages inside the lane, five across lanes by shuffles,
+                // in the order and with the operands of tkd_hadamard_kernel (stage h pairs i and i + h: a + c, a - c),
+                // so both give the same bits; then bf16 again, in place.
+                if (p.had && x_here) {
+                    const int nblk = K >> 10;
+                    for (int task = cw; task < M * nblk; task += SW) {
+                        const int r = task / nblk, b = task - r * nblk;
+                        const uint32_t xa = xt0 + (ONE ? 0 : r * p.x_stride) + b * 2048 + lane * 64;
+                        const uint4* sg = reinterpret_cast<const uint4*>(p.had + ((b << 10) + lane * 32) / 2);
+                        float v[32];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 raw = lds128(xa + 16 * q), sw = __ldg(sg + q);
+                            const uint32_t w[4] = {raw.x ^ (sw.x & 0x80008000u), raw.y ^ (sw.y & 0x80008000u),
+                                                   raw.z ^ (sw.z & 0x80008000u), raw.w ^ (sw.w & 0x80008000u)};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                v[8 * q + 2 * j] = __uint_as_float(w[j] << 16);
+                                v[8 * q + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+                            }
+                        }
+#pragma unroll
+                        for (int h = 1; h < 32; h <<= 1)
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (!(i & h)) {
+                                    const float a = v[i], c = v[i + h];
+                                    v[i] = a + c, v[i + h] = a - c;
+                                }
+#pragma unroll
+                        for (int s = 0; s < 5; ++s) {
+                            const bool upper = (lane >> s) & 1;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const float o = __shfl_xor_sync(0xFFFFFFFFu, v[i], 1 << s);
+                                v[i] = upper ? o - v[i] : v[i] + o;  // (lower: a + c; upper: a - c with a the partner's)
+                            }
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t o[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                o[j] = (uint32_t)f32_to_bf16_bits(v[8 * q + 2 * j]) |
+                                       ((uint32_t)f32_to_bf16_bits(v[8 * q + 2 * j + 1]) << 16);
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xa + 16 * q), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                                         "r"(o[3])
+                                         : "memory");
+                        }
+                    }
+                    asm volatile("bar.sync 2, %0;" ::"n"(SW * 32) : "memory");
+                }
+            }
         }
         while (x_here) {
             const bool full = KWHOLE || kc + CK <= K;

@@ -13,7 +13,7 @@ LIB_PATH = PKG / "csrc" / "libtkd.so"
 FMT_BFP8, FMT_BFP4, FMT_BF16, FMT_INT4 = 0, 1, 2, 3
 EPI_PLAIN, EPI_GLU_IL, EPI_GLU2, EPI_RESIDUAL, EPI_OUT32 = range(5)
 DT_NONE, DT_BF16, DT_F32 = 0, 1, 2
-ERR_TIMEOUT, ERR_WIDE, ERR_FIXED_SCRATCH = 3, 5, 6
+ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_WIDE, ERR_FIXED_SCRATCH = 2, 3, 5, 6
 
 c_i32, c_i64, c_u32, c_u64, c_vp = ctypes.c_int32, ctypes.c_int64, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
 
@@ -31,7 +31,7 @@ class TkdMatmul(ctypes.Structure):
         ("topk_write_y", c_i32), ("topk_base", c_u32), ("topk_n", c_i64), ("workspace", c_vp), ("workspace_bytes", c_u64),
         ("status", c_vp), ("ks", c_i32), ("max_ctas", c_i32),
         ("nranks", c_i32), ("rank", c_i32), ("peer_out", c_vp * 7), ("peer_records", c_vp * 7), ("peer_flags", c_vp * 7),
-        ("flags", c_vp), ("exchange_wait", c_i32), ("weights_fresh", c_i32),
+        ("flags", c_vp), ("exchange_wait", c_i32), ("weights_fresh", c_i32), ("hadamard", c_vp),
     ]
 
 

@@ -75,7 +75,7 @@ MAX_CTAS = None
 
 _TENSIX_OPTS = {"cores_per_bank", "split", "rows", "xs", "kb", "kw", "sbw", "noscale", "glu2", "budget", "mt"}
 _OPTS = _TENSIX_OPTS | {"glu", "glu_act", "residual", "residual_mode", "out32", "blocks", "max_banks", "col_scales", "ks",
-                        "max_ctas", "exchange"}
+                        "max_ctas", "exchange", "hadamard"}
 
 _CALLS = {}      # whole calls by the identity of their arguments (a hit goes straight to the library)
 _CALLS_MAX = 256
@@ -387,7 +387,9 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     Extensions: exchange= (a sharded.Exchange): the output and the records, where they lie inside the exchange's
     buffer, are also written to every other rank's buffer, and the call completes when all ranks' have arrived.
     col_scales=(gate scales, up scales) float32 [N] each with w_up (or one float32 vector in the
-    interleaved weight's column order with glu); a float32 residual with out32 (y = x @ w + residual in float32).
+    interleaved weight's column order with glu); a float32 residual with out32 (y = x @ w + residual in float32);
+    hadamard= (the sign words of ternary_matmul.t2.hadamard_signs; int4-stream weights only): x is rotated by the block
+    Hadamard inside the kernel first.
 
     A block list in place of w, [(w | (gate, up), col0_tiles), ...]: one launch over two to four weights of one K and
     dtype, each written at its col0_tiles (in 32-column tiles); bit for bit one call per block. More than 32 rows run
@@ -432,6 +434,7 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
     residual = opts.pop("residual", None)
     col_scales = opts.pop("col_scales", None)
     exchange = opts.pop("exchange", None)
+    hadamard = opts.pop("hadamard", None)
     out32 = bool(opts.get("out32"))
     assert not (out32 and topk is not None), "dense_reader: out32 without top-k"
     assert not (out32 and out is not None and out.dtype != ttnn.float32), out.dtype
@@ -496,7 +499,7 @@ def matmul(x, w, scale, *, memory_config=None, fidelity="hifi2", full_sync=False
         _block_kw_check(device, x, blocks_all, full_sync, opts, slices)
     for m0, _ in slices:
         launched.append(_launch(x, blocks_all, scale, col_scales, y, m0, min(32, M - m0), topk, act, residual, glu,
-                                out32, opts.get("ks") or KS or 0, opts.get("max_ctas") or MAX_CTAS or 0, exchange))
+                                out32, opts.get("ks") or KS or 0, opts.get("max_ctas") or MAX_CTAS or 0, exchange, hadamard))
     if call_key is not None and out is not None:
         # (only calls that write into a given output: a fresh output per call cannot be replayed)
         if len(_CALLS) >= _CALLS_MAX:
@@ -566,7 +569,8 @@ def _replay(hit):
     return True
 
 
-def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, out32, ks=0, max_ctas=0, exchange=None):
+def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, out32, ks=0, max_ctas=0, exchange=None,
+            hadamard=None):
     """One launch of the stream kernel: rows m0 .. m0 + m of x into the same rows of y. The descriptor is cached by
     everything that shapes it; a hit only rewrites the activation, output and residual addresses.
     (linear.py:828-1070)"""
@@ -602,6 +606,7 @@ def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, o
             ttnn.EPOCH, tuple((g.serial, u.serial if u is not None else 0, c0) for g, u, c0 in entries),
             m, tuple(xt.shape), tuple(yt.shape), epi, act, sc.data_ptr() if sc is not None else 0,
             sc_up.data_ptr() if sc_up is not None else 0, scale_dt, res_dt, tk, ks, max_ctas, device.id, id(exchange),
+            _raw(hadamard).data_ptr() if hadamard is not None else 0,
         )
     hit = _LAUNCHES.get(key) if key is not None else None
     if hit is None:
@@ -609,7 +614,8 @@ def _launch(x, entries, scale, col_scales, y, m0, m, topk, act, residual, glu, o
         a = _describe(xt, m, blocks, epi, act, sc, sc_up, scale_dt, rt, res_dt, yt, topk, ks, max_ctas)
         need = ctypes.c_uint64(0)
         _tkd.check(_tkd.lib().tkd_matmul_workspace(ctypes.byref(a), ctypes.byref(need)), "tkd_matmul_workspace")
-        hit = (a, need.value, (sc, sc_up, exchange))
+        a.hadamard = _raw(hadamard).data_ptr() if hadamard is not None else None
+        hit = (a, need.value, (sc, sc_up, exchange, hadamard))
         if key is not None:
             _LAUNCHES[key] = hit
     a, need, _ = hit

@@ -16,7 +16,8 @@ tensor) therefore run the same stream and give the same bits; the stream is 4.5 
 save HBM space, not time. Many rows run the ordinary stream kernels on the weight's values q * s held as bf16 (exact:
 a trit times a bf16 scale), as the reference's multi-row kernel dequantizes each tile by its scale row. The Hadamard
 is one small kernel (tkd_hadamard: a fast Walsh-Hadamard transform in fp32) for one row or many; with hadamard=
-t2_linear runs it first, so the fused form and the op give the same bits. The Tensix options (cores_per_bank, sbw, kw,
+t2_linear has the stream kernel do the same transform on its own copy of x (the same additions in the same order, so
+the fused form and the op give the same bits). The Tensix options (cores_per_bank, sbw, kw,
 split, budget, fidelity) are accepted and steer nothing. The weight is exactly q * bf16(s); the kernel's error is its
 arithmetic alone.
 """
@@ -198,10 +199,20 @@ def t2_linear(x, w, scale, g=128, *, hadamard=None, memory_config=None, fidelity
     assert x.dtype == ttnn.bfloat16 and x.layout == ttnn.TILE_LAYOUT
     assert x.shape[-1] == w["k"], (x.shape, w["k"])
     pw = packed(w, scale, g)
-    xr = _rotated(x, hadamard, ttnn.L1_MEMORY_CONFIG) if hadamard is not None else x
     spec = None if topk is None else {**topk, "rows": 1}
     if out is None or gap is None:
-        return dense_linear.matmul(xr, pw, None, memory_config=memory_config, fidelity=fidelity, topk=spec, out=out, col0=col0)
+        if hadamard is not None:
+            # the rotation inside the stream kernel's own copy of x (the same arithmetic as the op's, hence the same bits);
+            # a K whose row does not fit in shared memory beside the ring takes the op first
+            try:
+                return dense_linear.matmul(x, pw, None, memory_config=memory_config, fidelity=fidelity, topk=spec, out=out,
+                                           col0=col0, hadamard=hadamard)
+            except _tkd.TkdError as e:
+                if e.code != _tkd.ERR_UNSUPPORTED:
+                    raise
+            x = _rotated(x, hadamard, ttnn.L1_MEMORY_CONFIG)
+        return dense_linear.matmul(x, pw, None, memory_config=memory_config, fidelity=fidelity, topk=spec, out=out, col0=col0)
+    xr = _rotated(x, hadamard, ttnn.L1_MEMORY_CONFIG) if hadamard is not None else x
     # the output's columns in two runs: the plain row, then its two runs copied to their places
     assert topk is None, "t2: gap takes no top-k"
     cut, shift = gap
