@@ -257,20 +257,25 @@ def from_torch(t, dtype=None, layout=ROW_MAJOR_LAYOUT, device=None, memory_confi
     return Tensor(t.to(device.torch, _TORCH[dtype]).contiguous(), dtype, layout, device, memory_config)
 
 
+def held_values(t):
+    """The float32 values a Weight holds, [K, N padded to a panel], on its device (tkd_unpack)."""
+    L = _tkd.lib()
+    with torch.cuda.device(t._device.torch):
+        out = torch.empty(t.k, L.tkd_padded_cols(t.n), dtype=torch.float32, device=t._device.torch)
+        _tkd.check(
+            L.tkd_unpack(t.fmt, t.k, t.n, t.t.data_ptr(), t.emax.data_ptr() if t.emax is not None else None,
+                         out.data_ptr(), _stream_ptr()),
+            "tkd_unpack",
+        )
+    return out
+
+
 def to_torch(t):
     """ttnn.to_torch: the tensor on the host. A Weight comes back as the float32 values it holds, [1, 1, K, padded N]."""
     if isinstance(t, Weight):
-        L = _tkd.lib()
-        npad16 = L.tkd_padded_cols(t.n)
-        with torch.cuda.device(t._device.torch):
-            out = torch.empty(t.k, npad16, dtype=torch.float32, device=t._device.torch)
-            _tkd.check(
-                L.tkd_unpack(t.fmt, t.k, t.n, t.t.data_ptr(), t.emax.data_ptr() if t.emax is not None else None,
-                             out.data_ptr(), _stream_ptr()),
-                "tkd_unpack",
-            )
-        full = torch.zeros(1, 1, t.k, max(t.padded_shape[-1], npad16), dtype=torch.float32)
-        full[0, 0, :, :npad16] = out.cpu()
+        out = held_values(t)
+        full = torch.zeros(1, 1, t.k, max(t.padded_shape[-1], out.shape[1]), dtype=torch.float32)
+        full[0, 0, :, : out.shape[1]] = out.cpu()
         return full
     return t.t.cpu()
 

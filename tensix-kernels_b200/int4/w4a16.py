@@ -119,7 +119,7 @@ def dequantize(wq, scale, out=None, cores_per_bank=3):
     """The int4 weight times its group scales as a bfloat8_b weight [1, 1, K, N] for an ordinary block-float matmul
     over many rows. out: a weight of that shape to refill (returned, rewritten on every call)."""
     device, k, n = wq["_device"], wq["k"], wq["n"]
-    vals = ttnn.to_torch(packed(wq, scale))[0, 0, :, :n]  # q * s, exact in float32
+    vals = ttnn.held_values(packed(wq, scale))[:, :n]  # q * s, exact in float32, on the device
     w = ttnn.pack_weight(device, vals, ttnn.bfloat8_b, 1, memory_config=dev.sharded_memcfg(device, k, n, wq["banks"]))
     if out is None:
         return w

@@ -183,7 +183,7 @@ def _rows_weight(w, scale, g):
     pw = packed(w, scale, g)
     hit = w.get("_rows")
     if hit is None or hit[0] is not pw:
-        vals = ttnn.to_torch(pw)[0, 0, :, : w["n"]]
+        vals = ttnn.held_values(pw)[:, : w["n"]]  # (on the device)
         hit = w["_rows"] = (pw, ttnn.pack_weight(w["_device"], vals, ttnn.bfloat16, 1))
     return hit[1]
 
