@@ -29,6 +29,26 @@ void emul_pack(int fmt, int64_t K, int64_t npad, const uint8_t* exps, const void
         return;
     }
     const uint8_t* codes = (const uint8_t*)codes_v;
+    if (fmt == TKD_INT4) {
+        // exps: the bf16 bits of the group scales [ceil(K / 32)][npad]; a scale is stored times 2^TKD_INT4_SCALE_EXP
+        const uint16_t* sc = (const uint16_t*)exps;
+        for (int64_t kg = 0; kg * 32 < K; ++kg)
+            for (int64_t n = 0; n < npad; ++n) {
+                TkdLoc L = tkd_locate(fmt, K, kg * 32, n);
+                const float v = ldexpf(bf16f(sc[kg * npad + n]), TKD_INT4_SCALE_EXP);
+                uint32_t u; memcpy(&u, &v, 4);
+                const uint16_t b = (uint16_t)(u >> 16);
+                memcpy(stream + L.exp_word + 2 * L.exp_r, &b, 2);
+            }
+        for (int64_t k = 0; k < K; ++k)
+            for (int64_t n = 0; n < npad; ++n) {
+                TkdLoc L = tkd_locate(fmt, K, k, n);
+                uint32_t w; memcpy(&w, stream + L.code_word, 4);
+                w |= tkd_code_bits(fmt, codes[k * npad + n], L.rot, L.half);
+                memcpy(stream + L.code_word, &w, 4);
+            }
+        return;
+    }
     std::vector<uint8_t> nz(K * G, 0);
     for (int64_t g = 0; g < G; ++g) {
         int hi = 0, lo = 255;
@@ -74,6 +94,39 @@ void emul_matmul(int fmt, int64_t K, int64_t npad, const uint8_t* stream, const 
         std::vector<double> acc(16 * M, 0.0);
         for (int64_t sa = 0; sa < nsa; ++sa) {
             const uint8_t* b = stream + tkd_sa_offset(fmt, K, g, sa);
+            if (fmt == TKD_INT4) {
+                // per k32 block: the codes (bf16 subnormals) times x * 2^64 summed from zero, then the block's stored
+                // scale (this lane's word 2 gl + qq: column gl in the low half, gl + 8 in the high) takes the sum over
+                for (int lane = 0; lane < 32; ++lane) {
+                    const int gl = lane >> 2, t = lane & 3;
+                    for (int qq = 0; qq < 2; ++qq) {
+                        std::vector<double> tmp(2 * M, 0.0);
+                        for (int jj = 0; jj < 2; ++jj) {
+                            uint32_t w, a[4];
+                            memcpy(&w, b + 64 + lane * 16 + (2 * qq + jj) * 4, 4);
+                            const uint32_t t8 = tkd_rotr(w, 8);
+                            a[0] = w & TKD_MASK_BFP4, a[1] = (w << 4) & TKD_MASK_BFP4;
+                            a[2] = t8 & TKD_MASK_BFP4, a[3] = (t8 << 4) & TKD_MASK_BFP4;
+                            for (int r = 0; r < 4; ++r) {
+                                const int64_t k = sa * ksa + qq * 32 + 8 * t + 4 * jj + r;
+                                if (k >= K) continue;
+                                for (int hi = 0; hi < 2; ++hi) {
+                                    const double wv = (double)bf16f((uint16_t)(a[hi + 2 * (r >> 1)] >> (16 * (r & 1))));
+                                    for (int m = 0; m < M; ++m)
+                                        tmp[hi * M + m] += wv * ldexp((double)bf16f(x[m * K + k]), 64);
+                                }
+                            }
+                        }
+                        uint32_t sw;
+                        memcpy(&sw, b + gl * 8 + qq * 4, 4);
+                        for (int hi = 0; hi < 2; ++hi) {
+                            const double s = (double)bf16f((uint16_t)(sw >> (16 * hi)));
+                            for (int m = 0; m < M; ++m) acc[(gl + 8 * hi) * M + m] += tmp[hi * M + m] * s;
+                        }
+                    }
+                }
+                continue;
+            }
             for (int lane = 0; lane < 32; ++lane) {
                 const int gl = lane >> 2, t = lane & 3;
                 for (int j = 0; j < ksa / 16; ++j) {  // the mmas of the super-atom
@@ -114,7 +167,7 @@ void emul_matmul(int fmt, int64_t K, int64_t npad, const uint8_t* stream, const 
                 }
             }
         }
-        const int e = fmt == TKD_BF16 ? 0 : tkd_out_exp(fmt, (int)emax[g]);
+        const int e = fmt == TKD_BF16 || fmt == TKD_INT4 ? 0 : tkd_out_exp(fmt, (int)emax[g]);
         for (int i = 0; i < 16; ++i)
             for (int m = 0; m < M; ++m) y[(int64_t)m * npad + g * 16 + i] = ldexp(acc[i * M + m], e);
     }
@@ -135,8 +188,12 @@ void emul_unpack(int fmt, int64_t K, int64_t npad, const uint8_t* stream, const 
                 memcpy(&w, stream + L.code_word, 4);
                 memcpy(&ew, stream + L.exp_word, 4);
                 const uint32_t c = tkd_code_from_word(fmt, w, L.rot, L.half), m = c & ((1u << mb) - 1);
-                const int e = (int)tkd_exp_from_word(fmt, ew, L.exp_r) + (int)emax[n >> 4] - tkd_ebias(fmt);
-                v = m ? ldexpf((float)m, e - tkd_unit_exp(fmt)) : 0.f;
+                if (fmt == TKD_INT4) {
+                    v = (float)m * ldexpf(bf16f((uint16_t)(ew >> (16 * L.exp_r))), -TKD_INT4_SCALE_EXP);
+                } else {
+                    const int e = (int)tkd_exp_from_word(fmt, ew, L.exp_r) + (int)emax[n >> 4] - tkd_ebias(fmt);
+                    v = m ? ldexpf((float)m, e - tkd_unit_exp(fmt)) : 0.f;
+                }
                 if ((c >> mb) & 1u) v = -v;
             }
             out[k * npad + n] = v;

@@ -12,9 +12,9 @@ import torch
 from oracle import oracle as orc
 
 HERE = Path(__file__).resolve().parent
-FMT = {"bfp8": 0, "bfp4": 1, "bf16": 2}
-KSA = {"bfp8": 32, "bfp4": 64, "bf16": 32}
-SAB = {"bfp8": 544, "bfp4": 576, "bf16": 1024}
+FMT = {"bfp8": 0, "bfp4": 1, "bf16": 2, "int4": 3}
+KSA = {"bfp8": 32, "bfp4": 64, "bf16": 32, "int4": 64}
+SAB = {"bfp8": 544, "bfp4": 576, "bf16": 1024, "int4": 576}
 
 
 @pytest.fixture(scope="module")
@@ -65,6 +65,31 @@ def test_stream_round_trip_and_decode(emul, fmt, k, n):
         emul.emul_matmul(FMT[fmt], ctypes.c_int64(k), ctypes.c_int64(n), p(stream), p(emax), p(xb), m, p(y))
         want = x.double().numpy() @ held.astype(np.float64)
         assert np.allclose(y, want, rtol=1e-12, atol=1e-300), np.abs(y - want).max()
+
+
+@pytest.mark.parametrize("k,n", [(64, 128), (96, 128), (288, 256)])
+def test_int4_stream_round_trip_and_decode(emul, k, n):
+    """TKD_INT4: codes in bfloat4_b's words, the group scales (times 2^65) where bfloat4_b keeps its exponents; the
+    kernel's per-block sum-then-scale gives x @ (q * s)."""
+    g = torch.Generator().manual_seed(k * n)
+    q = torch.randint(-7, 8, (k, n), generator=g).numpy()
+    kg = k // 32  # (96 and 288 end inside a super-atom of 64 k)
+    scales = (torch.rand(kg, n, generator=g) * 0.02 + 1e-3).to(torch.bfloat16)
+    codes = np.ascontiguousarray((np.abs(q) | ((q < 0) << 3)).astype(np.uint8))
+    sbits = np.ascontiguousarray(scales.view(torch.int16).numpy().view(np.uint16))
+    held = orc.int4_dequantized(q.T, scales.float().numpy().T).T
+    stream, _, wide = pack(emul, "int4", sbits, codes)
+    assert wide == 0
+    back = np.zeros((k, n), np.float32)
+    emul.emul_unpack(FMT["int4"], ctypes.c_int64(k), ctypes.c_int64(n), p(stream), None, p(back))
+    assert np.array_equal(back.view(np.uint32), np.ascontiguousarray(held).view(np.uint32))
+    for m in (1, 5):
+        x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+        y = np.zeros((m, n), np.float64)
+        xb = np.ascontiguousarray(x.view(torch.int16).numpy().view(np.uint16))
+        emul.emul_matmul(FMT["int4"], ctypes.c_int64(k), ctypes.c_int64(n), p(stream), None, p(xb), m, p(y))
+        want = x.double().numpy() @ held.astype(np.float64)
+        assert np.allclose(y, want, rtol=1e-11, atol=1e-300), np.abs(y - want).max()
 
 
 def test_every_stream_bit_is_owned_once(emul):
