@@ -47,7 +47,7 @@ int tkd_version(void);
 /* The version of the packed streams' bit layout (tkd_pack's output): it changes whenever the layout does, and a cache
  * of packed weights records it (the counterpart of the pack cache's version key, moe/moe8.py:289-346). */
 int tkd_layout_version(void);
-/* sizeof of a structure of this header as the library was built (0 TkdMatmul, 1 TkdPlan, 2 TkdBlock): a binding
+/* sizeof of a structure of this header as the library was built (0 TkdMatmul, 1 TkdPlan, 2 TkdBlock, 3 TkdMoe): a binding
  * compares it with its own mirror before the first call. */
 int tkd_struct_bytes(int which);
 const char* tkd_error_string(int code);
@@ -218,6 +218,50 @@ int tkd_noalloc_scratch_address(void** ptr);
  * bases; out may be x); k a multiple of 1024; signs: k / 2 words, word q with bit 15 set when input 2 q is negated and
  * bit 31 for input 2 q + 1 (the reference's mask, t2.py:185-202). */
 int tkd_hadamard(const void* x, int64_t ldx, const uint32_t* signs, int rows, int k, void* out, int64_t ldo, void* stream);
+
+/* --- the mixture-of-experts layer's two matmuls: stand in for moe8.gate_up / down and gate_up_rows / down_rows
+ * (moe/moe8.py:710-911, 928-1136 of the reference; kernels/moe_gu_*.cpp, moe_dn_*.cpp, moe8_rows.h). Only the chosen
+ * experts' weights are read, and the expert ids are read on the device: nothing goes to the host. ------------------- */
+
+typedef struct {
+    const void* w;           /* every expert's packed stream, TKD_FMT_BFP4, expert e at e * expert_bytes: tkd_pack of
+                                the expert's [k_in, n] weight. gate_up: n = 2 I columns in the GLU's tile order (32 gate
+                                columns, then their 32 up columns: interleave_glu, dense_reader/linear.py:122-130);
+                                down: [I, H] */
+    const uint8_t* emax;     /* tkd_pack's side arrays, expert e at e * (tkd_padded_cols(n) / 16) */
+    int64_t expert_bytes;    /* a multiple of 16 */
+    int32_t experts;
+    int32_t k_in;            /* inputs of one expert's weight: H (gate_up) or I (down); a multiple of 32 */
+    int32_t n;               /* its columns: 2 I (gate_up; a multiple of 64) or H (down) */
+    int32_t rows;            /* activation rows R: 1 (decode), or 1..32 with by_union */
+    const void* x;           /* bf16. gate_up: [rows, ldx], k_in used; down: gate_up's result, slot q's inputs at q * k_in */
+    int64_t ldx;             /* elements a row, a multiple of 8; x 16-byte aligned */
+    const void* ids;         /* [rows, ld_ids] expert ids, uint16 (ids32 0) or uint32; an id at or past `experts` counts
+                                as no expert (its slot gives zeros) */
+    int32_t ids32;
+    int32_t k;               /* experts chosen per row, 1..16 */
+    int64_t ld_ids;
+    const void* route_w;     /* gate_up: [rows, ld_w] bf16 routing weights, one per id */
+    int64_t ld_w;
+    int32_t by_union;        /* 0: one row; slot s is expert ids[s] (gate_up, down). 1: the work goes by the distinct
+                                experts of all rows' ids in increasing order (gate_up_rows, down_rows, moe8_rows.h): slot
+                                q is the q-th of them, a row that did not choose it gets zeros there; experts <= 1024 */
+    int32_t slots;           /* by_union 0: k; 1: the slots of the result, min(experts, rows * k) (u_max, moe8.py:923) */
+    int32_t act;             /* gate_up: 0 silu, 1 gelu_tanh, 2 swiglu_oai (moe8.py:83-85) */
+    const void* bias;        /* gate_up, or NULL: bf16 [experts, tkd_padded_cols(n)] in the weight's column order,
+                                added to x G and x U before the activation (moe8.py:224-230) */
+    void* out;               /* bf16 [rows, ldo]. gate_up: slot q's I values at q * I, each routing weight * act(x G +
+                                b) * (x U + b); down: the n columns of y = sum over the slots of h_q @ D_q */
+    int64_t ldo;
+    void* workspace;         /* down: tkd_moe_workspace bytes, zeroed once by the caller before the first use */
+    uint64_t workspace_bytes;
+} TkdMoe;
+
+int tkd_moe_workspace(const TkdMoe* a, uint64_t* bytes);
+/* Rows whose activations do not fit in shared memory together are taken in passes (the experts' weights are read again
+ * for each, from L2). TKD_ERR_UNSUPPORTED: not even one row of k_in inputs fits. */
+int tkd_moe_gate_up(const TkdMoe* a, void* stream);
+int tkd_moe_down(const TkdMoe* a, void* stream);
 
 /* The best `top` candidates of every row among `nrecords` top-k records (the record layout above: keys[rows][k] then
  * indices[rows][k]), key descending and index ascending among equal keys; out is one record of the same layout with

@@ -337,3 +337,58 @@ def t2_reference(x, trits, scales, g):
     """x (as bf16) @ (q * bf16(s)).T, accumulated in float64 (t2.py:348-350 states it in float32)."""
     xb = torch.as_tensor(x).to(torch.bfloat16).double().numpy()
     return xb @ t2_dequantize(trits, torch.as_tensor(scales).to(torch.bfloat16), g).astype(np.float64).T
+
+
+# ---- the mixture-of-experts layer (moe/moe8.py of the reference). PARITY PINNED for these host forms
+# (tests/golden/moe.npz, made by running the reference's reference / reference_rows / union).
+
+
+def moe_glu(gt, u, act):
+    """act(x G) * (x U) in float64 (moe8.py:607-616): silu; gelu_tanh, 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)));
+    swiglu_oai, min(g, 7) * sigmoid(1.702 min(g, 7)) * (clamp(u, -7, 7) + 1)."""
+    gt, u = np.asarray(gt, np.float64), np.asarray(u, np.float64)
+    if act == "silu":
+        return gt / (1.0 + np.exp(-gt)) * u
+    if act == "gelu_tanh":
+        return 0.5 * gt * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (gt + 0.044715 * gt**3))) * u
+    assert act == "swiglu_oai", act
+    g = np.minimum(gt, 7.0)
+    return g / (1.0 + np.exp(-1.702 * g)) * (np.clip(u, -7.0, 7.0) + 1.0)
+
+
+def moe_reference(x, gate_up, down, ids, w, act="silu", gu_bias=None):
+    """(y [1, H], h [1, k * I]) in float64 for one row (moe8.py:619-636): slot s of expert e = ids[s] gives h_s = w_s *
+    act(x G_e + b) * (x U_e + b), y = sum of h_s @ D_e. gate_up [E, H, 2I] as [up | gate]; gu_bias [E, 2I] likewise,
+    rounded to bf16 first. numpy arrays (x, w already the bf16 values)."""
+    x = np.asarray(x, np.float64).reshape(1, -1)
+    gate_up, down = np.asarray(gate_up, np.float64), np.asarray(down, np.float64)
+    I = gate_up.shape[-1] // 2
+    y = np.zeros((1, gate_up.shape[1]))
+    hs = []
+    for s, e in enumerate(ids):
+        both = x @ gate_up[e]
+        if gu_bias is not None:
+            both = both + torch.as_tensor(np.asarray(gu_bias[e])).to(torch.bfloat16).double().numpy()
+        hs.append(moe_glu(both[:, I:], both[:, :I], act) * float(w[s]))
+        y += hs[-1] @ down[e]
+    return y, np.concatenate(hs, axis=1)
+
+
+def moe_union(ids, E):
+    """The distinct ids below E in increasing order (moe8.py:647-649; kernels/moe8_rows.h builds the same on the device)."""
+    return sorted({int(e) for e in np.asarray(ids).reshape(-1).tolist() if 0 <= int(e) < E})
+
+
+def moe_reference_rows(x, gate_up, down, ids, w, E, act="silu", gu_bias=None):
+    """(y [R, H], h [R, U * I]) in float64 for R rows with their own experts (moe8.py:639-644 and gate_up_rows' layout,
+    :928-934): union index q's I columns of h hold row r's h for expert union[q], 0 where the row did not choose it."""
+    ids = np.asarray(ids)
+    un = moe_union(ids, E)
+    I = np.asarray(gate_up).shape[-1] // 2
+    ys, h = [], np.zeros((len(ids), len(un) * I))
+    for r in range(len(ids)):
+        y, hr = moe_reference(np.asarray(x)[r : r + 1], gate_up, down, ids[r].tolist(), np.asarray(w)[r], act, gu_bias)
+        ys.append(y)
+        for s, e in enumerate(ids[r].tolist()):
+            h[r, un.index(e) * I : (un.index(e) + 1) * I] = hr[0, s * I : (s + 1) * I]
+    return np.concatenate(ys), h

@@ -13,7 +13,7 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent / "csrc"
 SOURCES = ["tkd_api.cu", "tkd_pack.cu", "tkd_stream.cu", "tkd_stream_bfp8.cu", "tkd_stream_bfp4.cu", "tkd_stream_bf16.cu",
-           "tkd_stream_int4.cu", "tkd_hadamard.cu",
+           "tkd_stream_int4.cu", "tkd_hadamard.cu", "tkd_moe.cu",
            "tkd_topk.cu"]
 LIB = CSRC / "libtkd.so"
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC"]

@@ -193,7 +193,7 @@ int tkd_version(void) { return 3; }
 int tkd_layout_version(void) { return TKD_LAYOUT_VERSION; }
 
 int tkd_struct_bytes(int which) {
-    return which == 0 ? (int)sizeof(TkdMatmul) : which == 1 ? (int)sizeof(TkdPlan) : which == 2 ? (int)sizeof(TkdBlock) : 0;
+    return which == 0 ? (int)sizeof(TkdMatmul) : which == 1 ? (int)sizeof(TkdPlan) : which == 2 ? (int)sizeof(TkdBlock) : which == 3 ? (int)sizeof(TkdMoe) : 0;
 }
 
 const char* tkd_error_string(int code) {

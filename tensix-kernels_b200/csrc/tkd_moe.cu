@@ -1,0 +1,379 @@
+// tkd_moe.cu: the mixture-of-experts layer's two matmuls over the chosen experts only, for sm_100a. They take the
+// place of the reference's gate_up / down and gate_up_rows / down_rows (moe/moe8.py:710-911, 928-1136; kernels
+// moe_gu_reader.cpp, moe_gu_compute.cpp, moe_gu_writer.cpp, moe_dn_reader.cpp, moe_dn_compute.cpp, moe_dn_writer.cpp
+// and kernels/moe8_rows.h for the union of the rows' experts).
+//
+// Every expert's weight is a bfloat4_b stream of tkd_layout.h (tkd_pack), all experts back to back, so the kernel
+// finds a chosen expert by its id alone: the ids are read on the device and nothing goes to the host. What a call reads
+// is small (k experts of a few MB) and scattered, so instead of the persistent ring of tkd_stream_kernel.cuh this is
+// a plain grid: a CTA owns (64 columns of one slot's expert, all of its K), its 16 warps are 4 groups of 16 columns x 4
+// runs of super-atoms, and a lane loads its own 16 bytes of codes and 16 bytes of exponents of a super-atom straight
+// from global memory into the mma.sync A fragment's registers (the stream is laid out lane by lane, so a warp's load
+// is one contiguous 512 bytes), four super-atoms ahead. The decode is the stream kernel's (block_mma).
+//   gate_up: 64 weight columns are a (gate, up) pair of 32-column tiles: the CTA finishes 32 outputs,
+//            h = routing weight * act(x G + b) * (x U + b), rounded to bf16 once.
+//   down:    a CTA writes its slot's partial sums of 64 columns of y to the workspace; the CTA that arrives last at
+//            the column block's counter adds the slots up in slot order and writes y (no CTA waits for another).
+// R rows (by_union): every CTA builds the set of distinct experts of the R x k ids (a bitmap), slot q is its q-th
+// member, and the rows are the columns of the mma's B operand (8 a tile).
+#include "tkd_stream_kernel.cuh"
+
+namespace {
+
+constexpr int kMoeGroups = 4;  // groups of 16 columns a CTA covers: one (gate, up) pair of tiles
+constexpr int kMoeSplit = 4;   // warps along K per group
+constexpr int kMoeThreads = kMoeGroups * kMoeSplit * 32;
+constexpr int kMoeBatch = 4;   // super-atoms whose loads are issued before the first is used
+constexpr int kMoeCols = kMoeGroups * 16;
+
+struct MoeParams {
+    const uint8_t* w;
+    const uint8_t* emax;
+    int64_t wbytes;
+    int E, K, N, npad, R;
+    int RB;  // rows a pass: what fits in shared memory (the weights are read again, from L2, for the next rows)
+    const uint16_t* x;
+    int64_t ldx;
+    const void* ids;
+    int ids32, k;
+    int64_t ld_ids;
+    const uint16_t* rw;
+    int64_t ld_w;
+    int slots, act;
+    const uint16_t* bias;
+    uint16_t* out;
+    int64_t ldo;
+    float* part;    // down: [slot][row][npad] partial sums
+    int* counters;  // down: one per block of 64 columns; back to zero when the call ends
+    uint32_t mul16, mul128;
+};
+
+__device__ __forceinline__ uint4 ldg_stream(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t moe_id(const MoeParams& p, int64_t i) {
+    return p.ids32 ? static_cast<const uint32_t*>(p.ids)[i] : static_cast<const uint16_t*>(p.ids)[i];
+}
+// a column sum in the stream's units -> its value (tkd_layout.h: 2^tkd_out_exp, in two factors that are normal floats)
+__device__ __forceinline__ float moe_scale(float v, int ebyte) {
+    const int e = tkd_out_exp(TKD_BFP4, ebyte), e1 = e / 2, e2 = e - e1;
+    return v * __uint_as_float((uint32_t)(e1 + 127) << 23) * __uint_as_float((uint32_t)(e2 + 127) << 23);
+}
+// moe8.py:83-85, 607-616: silu, gelu_tanh, or gpt-oss's clamped SwiGLU min(g, 7) * sigmoid(1.702 min(g, 7)) * (clamp(u, -7, 7) + 1)
+__device__ __forceinline__ float moe_glu(float gt, float u, int act) {
+    if (act == 2) {
+        const float gc = fminf(gt, 7.f);
+        return gc / (1.f + __expf(-1.702f * gc)) * (fminf(fmaxf(u, -7.f), 7.f) + 1.f);
+    }
+    return act_gate(gt, act) * u;
+}
+
+// MT: tiles of 8 rows. ROWS: by_union. DOWN: the down matmul.
+template <int MT, bool ROWS, bool DOWN>
+__global__ void __launch_bounds__(kMoeThreads) tkd_moe_kernel(const MoeParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ uint32_t bm[32];  // ROWS: a bit per expert some row chose
+    __shared__ float wrow[32];   // ROWS: row r's routing weight for this CTA's expert (0: not chosen)
+    __shared__ int s_e, s_count, s_last;
+    constexpr int RP = 8 * MT;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int gi = warp & (kMoeGroups - 1), ksp = warp / kMoeGroups;
+    const int hp = blockIdx.x, q = blockIdx.y;
+    const int R = p.R;
+    const int Kpad = (p.K + 63) & ~63;
+    const int xstride = Kpad * 2 + 16;  // bytes from a row of the activations in shared memory to the next
+    uint8_t* xs = smem;
+    float* red = reinterpret_cast<float*>(smem + (((size_t)p.RB * xstride + 15) & ~(size_t)15));  // [ksp][column][RP]
+
+    // ---- this CTA's expert
+    int e = -1, count = p.slots;
+    if constexpr (!ROWS) {
+        const uint32_t id = moe_id(p, q);
+        if (id < (uint32_t)p.E) e = (int)id;
+    } else {
+        if (tid < 32) bm[tid] = 0;
+        __syncthreads();
+        for (int i = tid; i < R * p.k; i += kMoeThreads) {
+            const int r = i / p.k;
+            const uint32_t id = moe_id(p, r * p.ld_ids + (i - r * p.k));
+            if (id < (uint32_t)p.E) atomicOr(&bm[id >> 5], 1u << (id & 31));
+        }
+        __syncthreads();
+        if (warp == 0) {
+            const uint32_t word = bm[lane];
+            const int c = __popc(word);
+            int incl = c;  // set bits up to and including this lane's word
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                if (lane >= d) incl += v;
+            }
+            const int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+            if (lane == 0) s_count = total, s_e = -1;
+            __syncwarp();
+            if (q >= incl - c && q < incl) {  // the slot's expert is the (q - before)-th set bit of this word
+                uint32_t wv = word;
+                for (int j = incl - c; j < q; ++j) wv &= wv - 1;
+                s_e = lane * 32 + __ffs(wv) - 1;
+            }
+        }
+        __syncthreads();
+        e = s_e, count = s_count;
+        if constexpr (!DOWN) {
+            if (tid < 32) {
+                float wv = 0.f;
+                if (tid < R && e >= 0)
+                    for (int s = 0; s < p.k; ++s)
+                        if (moe_id(p, tid * p.ld_ids + s) == (uint32_t)e) wv = bf16_bits_to_f32(p.rw[tid * p.ld_w + s]);
+                wrow[tid] = wv;
+            }
+        }
+    }
+
+    const uint8_t* em = p.emax + (int64_t)max(e, 0) * (p.npad / 16) + hp * kMoeGroups;
+    float w1 = 0.f;  // one row: the slot's routing weight
+    if constexpr (!ROWS && !DOWN)
+        if (e >= 0) w1 = bf16_bits_to_f32(p.rw[q]);
+    for (int r0 = 0; r0 < R; r0 += p.RB) {
+        const int Rb = min(p.RB, R - r0);
+        // ---- the activations: gate_up: the rows of x; down: the rows' inputs of slot q. Zeros past K up to a super-atom.
+        if (e >= 0) {
+            const uint16_t* xsrc = p.x + (int64_t)r0 * p.ldx + (DOWN ? (int64_t)q * p.K : 0);
+            const int vec = Kpad / 8;
+            for (int i = tid; i < Rb * vec; i += kMoeThreads) {
+                const int r = i / vec, c = i - r * vec;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (c * 8 < p.K) v = __ldg(reinterpret_cast<const uint4*>(xsrc + (int64_t)r * p.ldx) + c);
+                *reinterpret_cast<uint4*>(xs + (size_t)r * xstride + (size_t)c * 16) = v;
+            }
+        }
+        __syncthreads();
+
+        // ---- the group's sums over this warp's run of super-atoms
+        if (e >= 0) {
+            float acc[2][MT][4];
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int m = 0; m < MT; ++m) acc[a][m][0] = acc[a][m][1] = acc[a][m][2] = acc[a][m][3] = 0.f;
+            const int group = hp * kMoeGroups + gi;
+            const uint8_t* wb = p.w + (int64_t)e * p.wbytes;
+            const int nsa = Kpad / 64, per = (nsa + kMoeSplit - 1) / kMoeSplit;
+            const int sa0 = ksp * per, sa1 = min(nsa, sa0 + per);
+            const uint2 sh = make_uint2(p.mul16, p.mul128);
+            uint32_t xa[MT];  // (a lane past the last row reads the last row: its column of the result is never used)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) xa[m] = smem_u32(xs) + (uint32_t)min(8 * m + g, Rb - 1) * xstride + 16 * t;
+            for (int sa = sa0; sa < sa1; sa += kMoeBatch) {
+                uint4 cv[kMoeBatch], ev[kMoeBatch];
+#pragma unroll
+                for (int b = 0; b < kMoeBatch; ++b)
+                    if (sa + b < sa1) {
+                        const uint8_t* s = wb + tkd_sa_offset(TKD_BFP4, p.K, group, sa + b);
+                        ev[b] = ldg_stream(s + t * 16);
+                        cv[b] = ldg_stream(s + 64 + lane * 16);
+                    }
+#pragma unroll
+                for (int b = 0; b < kMoeBatch; ++b)
+                    if (sa + b < sa1) {
+#pragma unroll
+                        for (int qq = 0; qq < 2; ++qq) {
+                            const uint32_t cw[4] = {qq ? cv[b].z : cv[b].x, qq ? cv[b].w : cv[b].y, 0u, 0u};
+                            const uint32_t ew[2] = {qq ? ev[b].z : ev[b].x, qq ? ev[b].w : ev[b].y};
+                            uint4 xv[MT];
+#pragma unroll
+                            for (int m = 0; m < MT; ++m) xv[m] = lds128(xa[m] + (uint32_t)(sa + b) * 128 + 64 * qq);
+                            block_mma<TKD_BFP4, MT, 2>(acc, cw, ew, xv, sh);
+                        }
+                    }
+            }
+            // D fragment: (column g, rows 2t and 2t + 1), (column g + 8, the same rows)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                float* d0 = red + ((size_t)(ksp * kMoeCols + gi * 16 + g) * RP) + 8 * m + 2 * t;
+                d0[0] = acc[0][m][0] + acc[1][m][0], d0[1] = acc[0][m][1] + acc[1][m][1];
+                d0[8 * RP] = acc[0][m][2] + acc[1][m][2], d0[8 * RP + 1] = acc[0][m][3] + acc[1][m][3];
+            }
+        }
+        __syncthreads();
+
+        auto column_sum = [&](int c, int r) {
+            float v = 0.f;
+#pragma unroll
+            for (int s = 0; s < kMoeSplit; ++s) v += red[(size_t)(s * kMoeCols + c) * RP + r];
+            return moe_scale(v, em[c >> 4]);
+        };
+        if constexpr (!DOWN) {
+            const int I = p.N / 2;
+            for (int o = tid; o < 32 * Rb; o += kMoeThreads) {
+                const int c = o & 31, r = o >> 5;
+                float val = 0.f;
+                if (e >= 0) {
+                    float gt = column_sum(c, r), u = column_sum(32 + c, r);
+                    if (p.bias) {
+                        const uint16_t* b = p.bias + (int64_t)e * p.npad + hp * kMoeCols;
+                        gt += bf16_bits_to_f32(b[c]), u += bf16_bits_to_f32(b[32 + c]);
+                    }
+                    val = moe_glu(gt, u, p.act) * (ROWS ? wrow[r0 + r] : w1);
+                }
+                p.out[(int64_t)(r0 + r) * p.ldo + (int64_t)q * I + hp * 32 + c] = f32_to_bf16_bits(val);
+            }
+        } else {
+            if (e >= 0)
+                for (int o = tid; o < kMoeCols * Rb; o += kMoeThreads) {
+                    const int c = o & (kMoeCols - 1), r = o / kMoeCols;
+                    p.part[((int64_t)q * R + r0 + r) * p.npad + hp * kMoeCols + c] = column_sum(c, r);
+                }
+        }
+        __syncthreads();  // (the next rows overwrite the activations and the sums)
+    }
+    if constexpr (DOWN) {
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) s_last = atomicAdd(&p.counters[hp], 1) == p.slots - 1;
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            for (int o = tid; o < kMoeCols * R; o += kMoeThreads) {
+                const int c = o & (kMoeCols - 1), r = o / kMoeCols, col = hp * kMoeCols + c;
+                if (col >= p.N) continue;
+                float v = 0.f;
+                for (int s = 0; s < count; ++s) {
+                    if constexpr (!ROWS)
+                        if (moe_id(p, s) >= (uint32_t)p.E) continue;
+                    v += __ldcg(&p.part[((int64_t)s * R + r) * p.npad + col]);
+                }
+                p.out[(int64_t)r * p.ldo + col] = f32_to_bf16_bits(v);
+            }
+            if (tid == 0) p.counters[hp] = 0;
+        }
+    }
+}
+
+size_t moe_smem(int R, int K, int MT) {
+    const int Kpad = (K + 63) & ~63;
+    return (((size_t)R * (Kpad * 2 + 16) + 15) & ~(size_t)15) + (size_t)kMoeSplit * kMoeCols * 8 * MT * sizeof(float);
+}
+
+template <int MT, bool ROWS, bool DOWN>
+int moe_launch(const MoeParams& p, dim3 grid, size_t smem, cudaStream_t st) {
+    auto kern = tkd_moe_kernel<MT, ROWS, DOWN>;
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    kern<<<grid, kMoeThreads, smem, st>>>(p);
+    return (int)cudaGetLastError();
+}
+
+template <bool DOWN>
+int moe_dispatch(const MoeParams& p, bool rows, dim3 grid, size_t smem, int mt, cudaStream_t st) {
+    if (!rows) return moe_launch<1, false, DOWN>(p, grid, smem, st);
+    switch (mt) {
+        case 1: return moe_launch<1, true, DOWN>(p, grid, smem, st);
+        case 2: return moe_launch<2, true, DOWN>(p, grid, smem, st);
+        case 3: return moe_launch<3, true, DOWN>(p, grid, smem, st);
+        default: return moe_launch<4, true, DOWN>(p, grid, smem, st);
+    }
+}
+
+bool moe_args_ok(const TkdMoe* a, bool down) {
+    if (!a || !a->w || !a->emax || !a->x || !a->ids || !a->out) return false;
+    if (a->experts < 1 || a->k_in < 32 || a->k_in % 32 || a->n < 32 || a->n % 32 || a->k < 1 || a->k > 16) return false;
+    if (a->rows < 1 || a->rows > 32 || (!a->by_union && a->rows != 1)) return false;
+    if (a->by_union && (a->experts > 1024 || a->slots < 1 || a->ld_ids < a->k)) return false;
+    if (!a->by_union && a->slots != a->k) return false;
+    if (a->expert_bytes < tkd_packed_bytes(TKD_FMT_BFP4, a->k_in, a->n) || a->expert_bytes % 16) return false;
+    if (a->ldx % 8 || (reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->w)) & 15) return false;
+    if (down) {
+        if (a->ldx < (int64_t)a->slots * a->k_in || a->ldo < a->n) return false;
+    } else {
+        if (a->n % 64 || !a->route_w || a->ldx < a->k_in || a->ldo < (int64_t)a->slots * (a->n / 2)) return false;
+        if (a->act < 0 || a->act > 2 || (a->by_union && a->ld_w < a->k)) return false;
+    }
+    return true;
+}
+
+MoeParams moe_params(const TkdMoe* a) {
+    MoeParams p = {};
+    p.w = static_cast<const uint8_t*>(a->w), p.emax = a->emax, p.wbytes = a->expert_bytes;
+    p.E = a->experts, p.K = a->k_in, p.N = a->n, p.npad = (int)tkd_padded_cols(a->n), p.R = a->rows;
+    p.x = static_cast<const uint16_t*>(a->x), p.ldx = a->ldx;
+    p.ids = a->ids, p.ids32 = a->ids32, p.k = a->k, p.ld_ids = a->ld_ids;
+    p.rw = static_cast<const uint16_t*>(a->route_w), p.ld_w = a->ld_w;
+    p.slots = a->slots, p.act = a->act, p.bias = static_cast<const uint16_t*>(a->bias);
+    p.out = static_cast<uint16_t*>(a->out), p.ldo = a->ldo;
+    p.mul16 = 16, p.mul128 = 128;
+    return p;
+}
+
+int moe_smem_limit() {
+    static int cached = 0;
+    if (!cached) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
+        cached = v;
+    }
+    return cached;
+}
+
+// How many rows a pass of the kernel takes: all of them if their activations fit in shared memory beside the sums,
+// else as many tiles of 8 as fit (then fewer than 8). false: not even one row fits.
+bool moe_rows_a_pass(const TkdMoe* a, int* rb, int* mt, size_t* smem) {
+    const int64_t limit = (int64_t)moe_smem_limit() - 2048;
+    for (int rows = a->rows; rows >= 1; rows = rows > 8 ? ((rows - 1) & ~7) : rows - 1) {
+        const int tiles = a->by_union ? (rows + 7) / 8 : 1;
+        const size_t need = moe_smem(rows, a->k_in, tiles);
+        if ((int64_t)need <= limit) {
+            *rb = rows, *mt = tiles, *smem = need;
+            return true;
+        }
+    }
+    return false;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tkd_moe_workspace(const TkdMoe* a, uint64_t* bytes) {
+    if (!a || !bytes || a->slots < 1 || a->rows < 1 || a->n < 1) return TKD_ERR_BAD_ARG;
+    const int64_t npad = tkd_padded_cols(a->n);
+    // the column blocks' counters (a cache line's worth at least), then the slots' partial sums
+    *bytes = (uint64_t)(((npad / kMoeCols) * 4 + 255) & ~(int64_t)255) + (uint64_t)a->slots * a->rows * npad * sizeof(float);
+    return TKD_OK;
+}
+
+int tkd_moe_gate_up(const TkdMoe* a, void* stream) {
+    if (!moe_args_ok(a, false)) return TKD_ERR_BAD_ARG;
+    MoeParams p = moe_params(a);
+    int mt = 1;
+    size_t smem = 0;
+    if (!moe_rows_a_pass(a, &p.RB, &mt, &smem)) return TKD_ERR_UNSUPPORTED;
+    const dim3 grid((unsigned)(a->n / kMoeCols), (unsigned)a->slots);
+    const int e = moe_dispatch<false>(p, a->by_union != 0, grid, smem, mt, static_cast<cudaStream_t>(stream));
+    return e == 0 ? TKD_OK : TKD_ERR_CUDA + e;
+}
+
+int tkd_moe_down(const TkdMoe* a, void* stream) {
+    if (!moe_args_ok(a, true)) return TKD_ERR_BAD_ARG;
+    uint64_t need = 0;
+    tkd_moe_workspace(a, &need);
+    if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 15)) return TKD_ERR_WORKSPACE;
+    MoeParams p = moe_params(a);
+    const int64_t npad = tkd_padded_cols(a->n);
+    p.counters = static_cast<int*>(a->workspace);
+    p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + (((npad / kMoeCols) * 4 + 255) & ~(int64_t)255));
+    int mt = 1;
+    size_t smem = 0;
+    if (!moe_rows_a_pass(a, &p.RB, &mt, &smem)) return TKD_ERR_UNSUPPORTED;
+    const dim3 grid((unsigned)(npad / kMoeCols), (unsigned)a->slots);
+    const int e = moe_dispatch<true>(p, a->by_union != 0, grid, smem, mt, static_cast<cudaStream_t>(stream));
+    return e == 0 ? TKD_OK : TKD_ERR_CUDA + e;
+}
+}

@@ -38,6 +38,15 @@ class TkdMatmul(ctypes.Structure):
 MAX_RANKS, FLAG_SEQ, FLAG_WORDS = 8, 8, 16
 
 
+class TkdMoe(ctypes.Structure):
+    _fields_ = [
+        ("w", c_vp), ("emax", c_vp), ("expert_bytes", c_i64), ("experts", c_i32), ("k_in", c_i32), ("n", c_i32),
+        ("rows", c_i32), ("x", c_vp), ("ldx", c_i64), ("ids", c_vp), ("ids32", c_i32), ("k", c_i32), ("ld_ids", c_i64),
+        ("route_w", c_vp), ("ld_w", c_i64), ("by_union", c_i32), ("slots", c_i32), ("act", c_i32), ("bias", c_vp),
+        ("out", c_vp), ("ldo", c_i64), ("workspace", c_vp), ("workspace_bytes", c_u64),
+    ]
+
+
 class TkdPlan(ctypes.Structure):
     _fields_ = [
         ("ks", c_i32), ("nslices", c_i32), ("panels", c_i32), ("grid", c_i32), ("stages", c_i32), ("stream_warps", c_i32),
@@ -64,6 +73,9 @@ SYMBOLS = {
     "tkd_matmul_noalloc_reset": (c_i32, [c_vp]),
     "tkd_noalloc_scratch_address": (c_i32, [ctypes.POINTER(c_vp)]),
     "tkd_hadamard": (c_i32, [c_vp, c_i64, c_vp, c_i32, c_i32, c_vp, c_i64, c_vp]),
+    "tkd_moe_workspace": (c_i32, [ctypes.POINTER(TkdMoe), ctypes.POINTER(c_u64)]),
+    "tkd_moe_gate_up": (c_i32, [ctypes.POINTER(TkdMoe), c_vp]),
+    "tkd_moe_down": (c_i32, [ctypes.POINTER(TkdMoe), c_vp]),
     "tkd_topk_merge": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp]),
     "tkd_head_pick": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_u32, c_vp, c_i64, c_i32, c_vp, c_i64, c_i32, c_vp, c_vp, c_vp]),
     "tkd_head_pick_records": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_u32, c_vp, c_vp, c_vp, c_vp]),
@@ -91,7 +103,7 @@ def lib():
         for name, (res, args) in SYMBOLS.items():
             fn = getattr(L, name)
             fn.restype, fn.argtypes = res, args
-        for which, mirror in enumerate((TkdMatmul, TkdPlan, TkdBlock)):
+        for which, mirror in enumerate((TkdMatmul, TkdPlan, TkdBlock, TkdMoe)):
             if L.tkd_struct_bytes(which) != ctypes.sizeof(mirror):
                 raise RuntimeError(f"dense_reader: {LIB_PATH} was built from another include/tkd.h ({mirror.__name__}"
                                    f" is {L.tkd_struct_bytes(which)} bytes there, {ctypes.sizeof(mirror)} here): rebuild")

@@ -1,0 +1,308 @@
+"""moe8.py: a mixture-of-experts layer that reads only the chosen experts' weights, on a B200.
+
+Mirrors the reference's moe/moe8.py entry points for the layer's two matmuls: bfp4_tiles :117-154, bfp4_values :157-169,
+pack :507-527, reference :619-636, reference_rows :639-644, union :647-649, u_max :923-925, gate_up :710-817,
+down :820-910, gate_up_rows :928-1037, down_rows :1040-1136. The expert ids are read on the device, as there: every op
+is one kernel launch on the current stream and nothing goes to the host, so the ops can be captured in a CUDA graph.
+
+- gate_up(x, P, ids, w, k) -> h [1, 1, 1, k * I]: per chosen expert e (slot s) h_s = w_s * act(x G_e) * (x U_e), act
+  "silu", "gelu_tanh" or "swiglu_oai", an optional per-expert gate/up bias added before the activation;
+- down(h, P, ids, k) -> y [1, 1, 1, H]: the sum over the slots of h_s @ D_e;
+- gate_up_rows / down_rows: R <= 32 rows, each with its own k experts; the work goes by the distinct experts of all
+  R x k ids in increasing order (the union), each read once for all rows; h [1, 1, 32, u_max * I] holds union index q's
+  I columns at q * I, 0 where a row did not choose the expert.
+
+The packed weights (pack): every expert's gate|up matrix [H, 2I], its 32-column tiles in the GLU's order (gate j, up
+j), and its down matrix [I, H], each as one bfloat4_b stream of libtkd (csrc/tkd_layout.h), the experts back to back in
+one buffer, so an id finds its expert by a multiplication. The values are rounded to the bfloat4_b grid exactly as
+bfp4_tiles rounds them (values already on the grid stay as they are). Not built here: the K-block layout (kblock=True:
+shared exponents along K) is refused with NotImplementedError, the pack cache (cache=, prepack, pack_cached,
+repack_down) and the router (route, route_reference, sigmoid_table). The Tensix options (cores_per_bank, banks, kw,
+fidelity, cpb, loaders) are accepted and steer nothing.
+"""
+
+import ctypes
+
+import numpy as np
+import torch
+
+from common import ttnn_like as ttnn
+from dense_reader import _tkd
+
+TILE = 32
+TB = 576  # a bfloat4_b tile: 64 exponent bytes, then 1024 codes of a sign and 3 magnitude bits
+ACTS = {"silu": 0, "gelu_tanh": 1, "swiglu_oai": 2}
+OAI_ALPHA, OAI_LIMIT = 1.702, 7.0
+
+
+# --- the bfloat4_b grid on the host -----------------------------------------------------------------------------------
+
+
+def _faces(a):
+    """[KT, NT, 32, 32] tile values -> [KT, NT, 64, 16]: the 64 face rows of a tile in storage order (faces (rows 0-15,
+    columns 0-15), (0-15, 16-31), (16-31, 0-15), (16-31, 16-31), each row by row)."""
+    kt, nt = a.shape[:2]
+    return np.ascontiguousarray(a.reshape(kt, nt, 2, 16, 2, 16).transpose(0, 1, 2, 4, 3, 5)).reshape(kt, nt, 64, 16)
+
+
+def bfp4_tiles(w, kblock=False):
+    """float [K, N] (multiples of 32) -> uint8 [K / 32, N / 32, 576], each 32 x 32 tile as bfloat4_b (moe8.py:117-154 of
+    the reference, which states it byte-identical to tt-metal's host conversion): the 16 values of a face row share the
+    largest of their float32 exponent fields; a value's 24-bit significand is shifted down by its exponent's distance
+    from that (dropping the bits shifted out; gone beyond 31), its top 3 bits kept and rounded to nearest, ties to even,
+    on the 21 bits below, at most 7; a value whose own exponent field is 0 gives 0; the sign is kept for a non-zero
+    result only. 64 exponent bytes, then two codes a byte, the earlier in the low nibble. kblock: the tile holds its
+    block transposed (a face row is 16 consecutive K at one N)."""
+    w = np.ascontiguousarray(w.detach().float().cpu().numpy() if isinstance(w, torch.Tensor) else w, dtype=np.float32)
+    k, n = w.shape
+    assert k % TILE == 0 and n % TILE == 0, w.shape
+    tiles = w.reshape(k // TILE, TILE, n // TILE, TILE).transpose(0, 2, 1, 3)
+    if kblock:
+        tiles = tiles.swapaxes(-1, -2)
+    u = _faces(tiles).view(np.uint32).astype(np.int64)
+    field = (u >> 23) & 0xFF
+    top = field.max(axis=-1, keepdims=True)
+    gap = top - field
+    sig = ((u & 0x7FFFFF) | 0x800000) >> np.minimum(gap, 31)
+    sig[gap > 31] = 0
+    keep, rest = sig >> 21, sig & 0x1FFFFF
+    keep = keep + ((rest > 0x100000) | ((rest == 0x100000) & ((keep & 1) == 1)))
+    mag = np.minimum(keep, 7)
+    mag[field == 0] = 0
+    code = (((u >> 31) & (mag != 0)) << 3 | mag).astype(np.uint8).reshape(k // TILE, n // TILE, 1024)
+    out = np.empty((k // TILE, n // TILE, TB), np.uint8)
+    out[..., :64] = top[..., 0]
+    out[..., 64:] = code[..., 0::2] | (code[..., 1::2] << 4)
+    return out
+
+
+def bfp4_values(tiles, kblock=False):
+    """uint8 [..., 576] bfloat4_b tiles -> float32 [..., 32, 32], the tiles' values row-major: (-1)^s * m * 2^(shared -
+    129) (moe8.py:157-169). kblock: tiles of bfp4_tiles(kblock=True), turned back to [K, N] order."""
+    tiles = np.asarray(tiles)
+    lead = tiles.shape[:-1]
+    shared = tiles[..., :64].astype(np.int32)
+    body = tiles[..., 64:]
+    code = np.stack((body & 0xF, body >> 4), axis=-1).reshape(*lead, 64, 16).astype(np.int32)
+    val = np.where(code & 8, -1.0, 1.0) * (code & 7) * np.exp2((shared - 129).astype(np.float64))[..., None]
+    val = val.astype(np.float32).reshape(*lead, 2, 2, 16, 16).swapaxes(-3, -2).reshape(*lead, TILE, TILE)
+    return val.swapaxes(-1, -2) if kblock else val
+
+
+# --- the packed layer -------------------------------------------------------------------------------------------------
+
+
+def _glu_order(m, I):
+    """[..., 2I] as [up | gate] -> the same columns in the GLU's tile order: gate tile j, then up tile j."""
+    up, gate = m[..., :I], m[..., I:]
+    lead = m.shape[:-1]
+    pairs = torch.stack((gate.reshape(*lead, I // TILE, TILE), up.reshape(*lead, I // TILE, TILE)), dim=-2)
+    return pairs.reshape(*lead, 2 * I)
+
+
+def _pack_experts(device, mats, what):
+    """[E, K, N] float -> (streams uint8 [E, bytes], emax uint8 [E, N_pad / 16]) on the device: tkd_quantise and tkd_pack
+    of each expert into its slice."""
+    L = _tkd.lib()
+    E, k, n = mats.shape
+    npad = L.tkd_padded_cols(n)
+    nbytes = L.tkd_packed_bytes(_tkd.FMT_BFP4, k, n)
+    assert nbytes % 16 == 0
+    st = torch.cuda.current_stream().cuda_stream
+    with torch.cuda.device(device.torch):
+        streams = torch.empty(E, nbytes, dtype=torch.uint8, device=device.torch)
+        emax = torch.empty(E, npad // 16, dtype=torch.uint8, device=device.torch)
+        exps = torch.empty(k * (npad // 16), dtype=torch.uint8, device=device.torch)
+        codes = torch.empty(k * npad, dtype=torch.uint8, device=device.torch)
+        info = torch.zeros(1, dtype=torch.int32, device=device.torch)
+        for e in range(E):
+            src = mats[e].to(device.torch, torch.float32).contiguous()
+            _tkd.check(L.tkd_quantise(_tkd.FMT_BFP4, src.data_ptr(), 1, k, n, None, exps.data_ptr(), codes.data_ptr(), st),
+                       "tkd_quantise")
+            _tkd.check(L.tkd_pack(_tkd.FMT_BFP4, k, n, exps.data_ptr(), codes.data_ptr(), streams[e].data_ptr(),
+                                  emax[e].data_ptr(), info.data_ptr(), st), "tkd_pack")
+        torch.cuda.current_stream().synchronize()  # (the ops read the weights ahead of nothing, but src is a temporary)
+        if int(info.item()) & 1:
+            raise ValueError(f"moe8: an expert's {what} weight has exponents inside a group of 16 columns more than 48"
+                             " binades apart: the packed stream does not hold it")
+    return streams, emax
+
+
+def pack(device, gate_up, down, cores_per_bank=3, banks=None, cache=None, gu_bias=None, rebuild=False, kblock=False):
+    """One MoE layer's experts as the packed weights the ops take (moe8.py:507-527). gate_up: [E, H, 2I] float with up
+    in columns 0..I-1 and gate in I..2I-1 ([up | gate]); down: [E, I, H]; gu_bias: [E, 2I] as [up | gate], held in bf16.
+    Returns the dict the ops take ("E", "H", "I", "gu", "dn", "gu_bias", "bytes", ...). cores_per_bank and banks are
+    recorded only."""
+    if kblock:
+        raise NotImplementedError("moe8: the K-block layout (shared exponents along K) has no stream format here")
+    if cache is not None:
+        raise NotImplementedError("moe8: the pack cache is not built here; pass cache=None")
+    gate_up, down = torch.as_tensor(gate_up), torch.as_tensor(down)
+    E, H, I2 = gate_up.shape
+    I = I2 // 2
+    assert H % TILE == 0 and I % TILE == 0 and tuple(down.shape) == (E, I, H), (gate_up.shape, down.shape)
+    gu, gu_emax = _pack_experts(device, _glu_order(gate_up.float(), I), "gate|up")
+    dn, dn_emax = _pack_experts(device, down.float(), "down")
+    bias = None
+    if gu_bias is not None:
+        b = _glu_order(torch.as_tensor(gu_bias).to(torch.bfloat16), I)
+        bias = torch.zeros(E, _tkd.lib().tkd_padded_cols(2 * I), dtype=torch.bfloat16, device=device.torch)
+        bias[:, : 2 * I] = b.to(device.torch)
+    u8 = lambda t: ttnn.Tensor(t, ttnn.uint8, ttnn.ROW_MAJOR_LAYOUT, device, ttnn.DRAM_MEMORY_CONFIG)  # noqa: E731
+    return {
+        "E": E, "H": H, "I": I,
+        "banks": banks or device.dram_grid_size().x, "cpb": cores_per_bank,
+        "gu": u8(gu), "gu_emax": gu_emax, "dn": u8(dn), "dn_emax": dn_emax,
+        "gu_bias": bias is not None, "gu_bias_t": bias, "kblock": False,
+        "bytes": gu.numel() + dn.numel() + gu_emax.numel() + dn_emax.numel(),
+        "_device": device, "_ws": {},
+    }
+
+
+# --- references -------------------------------------------------------------------------------------------------------
+
+
+def _glu(gt, u, act):
+    """act(x G) * (x U) for the references (moe8.py:607-616)."""
+    assert act in ACTS, f"moe8: act {act!r}"
+    if act == "silu":
+        return torch.nn.functional.silu(gt) * u
+    if act == "gelu_tanh":
+        return torch.nn.functional.gelu(gt, approximate="tanh") * u
+    g = gt.clamp(max=OAI_LIMIT)
+    return g * torch.sigmoid(OAI_ALPHA * g) * (u.clamp(-OAI_LIMIT, OAI_LIMIT) + 1)
+
+
+def reference(x, gate_up, down, ids, w, act="silu", gu_bias=None):
+    """(y [1, H], h [1, k * I]) in float64 for one row (moe8.py:619-636): h_s = w_s * act(x G_e + b) * (x U_e + b) for
+    e = ids[s], y the sum of h_s @ D_e; gate_up [E, H, 2I] as [up | gate], gu_bias [E, 2I] likewise, rounded to bf16."""
+    x = x.double().reshape(1, -1)
+    I = gate_up.shape[-1] // 2
+    hs = []
+    y = torch.zeros(1, gate_up.shape[1], dtype=torch.float64)
+    for s, e in enumerate(ids):
+        both = x @ gate_up[e].double()
+        if gu_bias is not None:
+            both = both + torch.as_tensor(gu_bias[e]).to(torch.bfloat16).double()
+        hs.append(_glu(both[:, I:], both[:, :I], act) * float(w[s]))
+        y += hs[-1] @ down[e].double()
+    return y, torch.cat(hs, dim=1)
+
+
+def reference_rows(x, gate_up, down, ids, w, act="silu", gu_bias=None):
+    """y [R, H] in float64, each row with its own experts (moe8.py:639-644)."""
+    return torch.cat([reference(x[r : r + 1], gate_up, down, ids[r], w[r], act, gu_bias)[0] for r in range(len(ids))])
+
+
+def union(ids, E):
+    """The distinct ids below E, increasing: the order the rows ops work in (moe8.py:647-649)."""
+    return sorted({int(e) for e in torch.as_tensor(ids).reshape(-1).tolist() if 0 <= int(e) < E})
+
+
+def u_max(P, rows, k):
+    """The most distinct experts rows x k ids can name: h's width is u_max * I (moe8.py:923-925)."""
+    return min(P["E"], rows * k)
+
+
+# --- the ops ----------------------------------------------------------------------------------------------------------
+
+
+def _ids_args(ids, w, rows, k, ids32):
+    want = ttnn.uint32 if ids32 else ttnn.uint16
+    assert ids.dtype == want, f"moe8: ids are {ids.dtype}, ids32={ids32} wants {want}"
+    assert ids.shape[-1] >= k and ids.shape[-2] >= rows, (ids.shape, rows, k)
+    if w is not None:
+        assert w.dtype == ttnn.bfloat16 and w.shape[-1] >= k and w.shape[-2] >= rows, (w.dtype, w.shape)
+
+
+def _fill(a, P, what, x, ids, w, rows, k, ids32, by_union, slots, out):
+    H, I = P["H"], P["I"]
+    gu = what == "gu"
+    a.w, a.emax = (P["gu"].t.data_ptr(), P["gu_emax"].data_ptr()) if gu else (P["dn"].t.data_ptr(), P["dn_emax"].data_ptr())
+    a.expert_bytes = (P["gu"] if gu else P["dn"]).t.shape[1]
+    a.experts, a.k_in, a.n = P["E"], (H if gu else I), (2 * I if gu else H)
+    a.rows, a.x, a.ldx = rows, x.t.data_ptr(), x.t.stride(-2)
+    a.ids, a.ids32, a.k, a.ld_ids = ids.t.data_ptr(), int(ids32), k, ids.t.stride(-2)
+    if w is not None:
+        a.route_w, a.ld_w = w.t.data_ptr(), w.t.stride(-2)
+    a.by_union, a.slots = int(by_union), slots
+    a.out, a.ldo = out.data_ptr(), out.stride(-2)
+
+
+def _gate_up(x, P, ids, w, k, rows, ids32, by_union, act, memory_config):
+    assert act in ACTS, f"moe8: act {act!r}"
+    assert 1 <= k <= 16, k
+    device = x.device()
+    H, I = P["H"], P["I"]
+    assert x.dtype == ttnn.bfloat16 and x.shape[-1] == H and x.shape[-2] >= rows, (x.dtype, x.shape)
+    _ids_args(ids, w, rows, k, ids32)
+    slots = u_max(P, rows, k) if by_union else k
+    with torch.cuda.device(device.torch):
+        if by_union:
+            out = torch.zeros(1, 1, TILE, slots * I, dtype=torch.bfloat16, device=device.torch)
+        else:
+            out = torch.empty(1, 1, 1, slots * I, dtype=torch.bfloat16, device=device.torch)
+        a = _tkd.TkdMoe()
+        _fill(a, P, "gu", x, ids, w, rows, k, ids32, by_union, slots, out)
+        a.act = ACTS[act]
+        a.bias = P["gu_bias_t"].data_ptr() if P["gu_bias"] else None
+        _tkd.check(_tkd.lib().tkd_moe_gate_up(ctypes.byref(a), torch.cuda.current_stream().cuda_stream), "tkd_moe_gate_up")
+    return ttnn.Tensor(out, ttnn.bfloat16, ttnn.TILE_LAYOUT, device, memory_config or ttnn.DRAM_MEMORY_CONFIG)
+
+
+def _down(h, P, ids, k, rows, ids32, by_union, memory_config):
+    assert 1 <= k <= 16, k
+    device = h.device()
+    H, I = P["H"], P["I"]
+    slots = u_max(P, rows, k) if by_union else k
+    assert h.dtype == ttnn.bfloat16 and h.shape[-1] >= slots * I and h.shape[-2] >= rows, (h.dtype, h.shape)
+    _ids_args(ids, None, rows, k, ids32)
+    L = _tkd.lib()
+    with torch.cuda.device(device.torch):
+        if by_union:
+            out = torch.zeros(1, 1, TILE, H, dtype=torch.bfloat16, device=device.torch)
+        else:
+            out = torch.empty(1, 1, 1, H, dtype=torch.bfloat16, device=device.torch)
+        a = _tkd.TkdMoe()
+        _fill(a, P, "dn", h, ids, None, rows, k, ids32, by_union, slots, out)
+        need = ctypes.c_uint64(0)
+        _tkd.check(L.tkd_moe_workspace(ctypes.byref(a), ctypes.byref(need)), "tkd_moe_workspace")
+        ws = P["_ws"].get("dn")
+        if ws is None or ws.numel() < need.value:
+            # (zeroed once: the kernel returns its counters to zero; calls on one layer run in stream order)
+            ws = P["_ws"]["dn"] = torch.zeros(need.value, dtype=torch.uint8, device=device.torch)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        _tkd.check(L.tkd_moe_down(ctypes.byref(a), torch.cuda.current_stream().cuda_stream), "tkd_moe_down")
+    return ttnn.Tensor(out, ttnn.bfloat16, ttnn.TILE_LAYOUT, device, memory_config or ttnn.DRAM_MEMORY_CONFIG)
+
+
+def gate_up(x, P, ids, w, k, *, ids32=False, kw=8, fidelity="hifi2", memory_config=None, cpb=None, loaders=None, act="silu"):
+    """h [1, 1, 1, k * I] bf16: per slot s the routing weight w[s] times act(x G) * (x U) of expert ids[s] (moe8.py:710-817).
+    x [1, 1, 1, H] bf16; ids [1, 1, 1, k] uint16 (uint32 with ids32) and w [1, 1, 1, k] bf16, read on the device. A
+    pack with a bias adds it before the activation. act: "silu", "gelu_tanh" or "swiglu_oai"."""
+    return _gate_up(x, P, ids, w, k, 1, ids32, False, act, memory_config)
+
+
+def down(h, P, ids, k, *, ids32=False, kw=8, fidelity="hifi2", memory_config=None, loaders=None):
+    """y [1, 1, 1, H] bf16 = h @ the chosen experts' down rows, slot s's I rows expert ids[s]'s (moe8.py:820-910). h is
+    gate_up's. The slots' sums are added in slot order, each an fp32 sum over its expert's I rows."""
+    return _down(h, P, ids, k, 1, ids32, False, memory_config)
+
+
+def gate_up_rows(x, P, ids, w, k, rows, *, ids32=False, kw=8, fidelity="hifi2", memory_config=None, cpb=None, act="silu",
+                 loaders=None):
+    """h [1, 1, 32, u_max * I] bf16 for x's first `rows` rows (moe8.py:928-1037): union index q's I columns hold row r's
+    routing weight for expert union(ids)[q] times act(x_r G) * (x_r U), 0 where row r did not choose it, 0 past the
+    union and in rows past `rows`. ids [1, 1, rows, k], w [1, 1, rows, k]; a row's ids are distinct."""
+    assert 1 <= rows <= TILE, rows
+    assert P["E"] <= 1024, "moe8 rows: at most 1024 experts"
+    return _gate_up(x, P, ids, w, k, rows, ids32, True, act, memory_config)
+
+
+def down_rows(h, P, ids, k, rows, *, ids32=False, kw=8, fidelity="hifi2", memory_config=None, loaders=None):
+    """y [1, 1, 32, H] bf16: row r = the sum over the union of the R x k ids of h's row r (union index q's I columns)
+    times expert union(ids)[q]'s down rows (moe8.py:1040-1136); rows past `rows` are 0. h is gate_up_rows' for the same
+    ids, rows and k."""
+    assert 1 <= rows <= TILE, rows
+    assert P["E"] <= 1024, "moe8 rows: at most 1024 experts"
+    return _down(h, P, ids, k, rows, ids32, True, memory_config)

@@ -145,3 +145,40 @@ np.savez_compressed(
     ref=tern.reference(xt, tr, sc, 128).numpy(), sylvester8=tern.sylvester(8).numpy(),
 )
 print("wrote", out / "ternary.npz")
+
+
+# 8. the mixture-of-experts layer (moe/moe8.py): the K-block form of the quantiser, reference / reference_rows / union on
+# a small layer of experts on the bfloat4_b grid (the generators of moe/tests/test_moe.py:35-56 at a smaller shape)
+ME, MH, MI, MK = 6, 64, 32, 3
+
+
+def moe_grid(w):
+    k, n = w.shape
+    v = moe8.bfp4_values(moe8.bfp4_tiles(w))
+    return torch.from_numpy(v.transpose(0, 2, 1, 3).reshape(k, n).copy())
+
+
+gen = torch.Generator().manual_seed(21)
+mgu = torch.stack([moe_grid(torch.randn(MH, 2 * MI, generator=gen) * 0.1) for _ in range(ME)])
+mdn = torch.stack([moe_grid(torch.randn(MI, MH, generator=gen) * 0.05) for _ in range(ME)])
+mgb = torch.randn(ME, 2 * MI, generator=gen) * 0.5
+mx = torch.randn(4, MH, generator=gen).to(torch.bfloat16)
+mids = torch.stack([torch.randperm(ME, generator=gen)[:MK] for _ in range(4)])
+mw = torch.softmax(torch.randn(4, MK, generator=gen), -1).to(torch.bfloat16)
+moe_out = {}
+for act in ("silu", "gelu_tanh", "swiglu_oai"):
+    y, h = moe8.reference(mx[:1].float(), mgu, mdn, mids[0].tolist(), mw[0].float(), act)
+    yb, hb = moe8.reference(mx[:1].float(), mgu, mdn, mids[0].tolist(), mw[0].float(), act, mgb)
+    moe_out.update({f"y_{act}": y.numpy(), f"h_{act}": h.numpy(), f"yb_{act}": yb.numpy(), f"hb_{act}": hb.numpy()})
+moe_out["rows_silu"] = moe8.reference_rows(mx.float(), mgu, mdn, mids.tolist(), mw.float(), "silu").numpy()
+moe_out["rows_oai_bias"] = moe8.reference_rows(mx.float(), mgu, mdn, mids.tolist(), mw.float(), "swiglu_oai", mgb).numpy()
+np.savez_compressed(
+    out / "moe.npz",
+    gu=mgu.numpy(), dn=mdn.numpy(), gb=mgb.numpy(), x_bits=mx.view(torch.int16).numpy(), ids=mids.numpy(),
+    w_bits=mw.view(torch.int16).numpy(), union=np.array(moe8.union(mids, ME), np.int64),
+    union_clip=np.array(moe8.union(torch.tensor([[5, 9, 2], [2, 7, 0]]), 6), np.int64),
+    t1_kblock_sha=sha(moe8.bfp4_tiles(w1, kblock=True)), t4_kblock=moe8.bfp4_tiles(w4, kblock=True),
+    v4_kblock=retile(moe8.bfp4_values(moe8.bfp4_tiles(w4, kblock=True), kblock=True)),
+    **moe_out,
+)
+print("wrote", out / "moe.npz")

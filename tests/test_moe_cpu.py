@@ -1,0 +1,100 @@
+"""The mixture-of-experts sibling without a GPU: the package's host functions (moe/moe8.py: bfp4_tiles, bfp4_values,
+reference, reference_rows, union) and the oracle's restatement against the golden vectors made by running the
+reference (tests/golden/gen_golden.py, section 8, and the quantiser's vectors of section 1-3), and the refusals of what
+is not built."""
+
+import hashlib
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from moe import moe8
+from oracle import oracle as orc
+
+G = Path(__file__).resolve().parent / "golden"
+sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()  # noqa: E731
+BF = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def m():
+    return np.load(G / "moe.npz")
+
+
+@pytest.fixture(scope="module")
+def q():
+    return np.load(G / "quantiser_bfp4.npz")
+
+
+def retile(v):
+    kt, nt = v.shape[:2]
+    return np.ascontiguousarray(v.transpose(0, 2, 1, 3).reshape(kt * 32, nt * 32))
+
+
+def test_bfp4_tiles_and_values_match_the_reference(q, m):
+    g = torch.Generator().manual_seed(0)
+    w1 = torch.randn(256, 512, generator=g) * 0.02
+    w1[3, 5], w1[7, 9] = 0.0, -1e-30
+    t1 = moe8.bfp4_tiles(w1)
+    assert np.array_equal(t1, q["t1"])
+    assert sha(retile(moe8.bfp4_values(t1))) == str(q["v1_sha"])
+    assert sha(moe8.bfp4_tiles(w1, kblock=True)) == str(m["t1_kblock_sha"])
+    # wide exponent spreads, denormals, zeros, huge values; the same tiles with the exponents along K
+    assert np.array_equal(moe8.bfp4_tiles(q["w4"]), q["t4"])
+    assert np.array_equal(retile(moe8.bfp4_values(q["t4"])), q["v4"])
+    assert np.array_equal(moe8.bfp4_tiles(q["w4"], kblock=True), m["t4_kblock"])
+    assert np.array_equal(retile(moe8.bfp4_values(m["t4_kblock"], kblock=True)), m["v4_kblock"])
+    # the rounding cases of one face row, and the oracle's quantiser on the same inputs
+    assert np.array_equal(retile(moe8.bfp4_values(moe8.bfp4_tiles(q["w3"]))), q["v3"])
+    e, c = orc.quantise_c(q["w4"], "bfp4")
+    assert np.array_equal(orc.tiles(e, c, "bfp4"), moe8.bfp4_tiles(q["w4"]))
+
+
+def inputs(m):
+    x = torch.from_numpy(m["x_bits"]).view(BF)
+    w = torch.from_numpy(m["w_bits"]).view(BF)
+    return x, w, torch.from_numpy(m["gu"]), torch.from_numpy(m["dn"]), torch.from_numpy(m["gb"]), torch.from_numpy(m["ids"])
+
+
+def test_references_match_the_reference(m):
+    x, w, gu, dn, gb, ids = inputs(m)
+    for act in ("silu", "gelu_tanh", "swiglu_oai"):
+        for bias, tag in ((None, ""), (gb, "b")):
+            y, h = moe8.reference(x[:1].float(), gu, dn, ids[0].tolist(), w[0].float(), act, bias)
+            assert np.allclose(y.numpy(), m[f"y{tag}_{act}"], rtol=1e-12, atol=1e-15)
+            assert np.allclose(h.numpy(), m[f"h{tag}_{act}"], rtol=1e-12, atol=1e-15)
+            oy, oh = orc.moe_reference(x[:1].float().numpy(), gu.numpy(), dn.numpy(), ids[0].tolist(), w[0].float().numpy(),
+                                       act, None if bias is None else bias.numpy())
+            assert np.allclose(oy, m[f"y{tag}_{act}"], rtol=1e-9, atol=1e-12), act
+            assert np.allclose(oh, m[f"h{tag}_{act}"], rtol=1e-9, atol=1e-12), act
+    rows = moe8.reference_rows(x.float(), gu, dn, ids.tolist(), w.float(), "silu")
+    assert np.allclose(rows.numpy(), m["rows_silu"], rtol=1e-12, atol=1e-15)
+    oy, oh = orc.moe_reference_rows(x.float().numpy(), gu.numpy(), dn.numpy(), ids.numpy(), w.float().numpy(), 6,
+                                    "swiglu_oai", gb.numpy())
+    assert np.allclose(oy, m["rows_oai_bias"], rtol=1e-9, atol=1e-12)
+    un = orc.moe_union(ids.numpy(), 6)
+    assert oh.shape == (4, len(un) * 32)
+    # a row's columns of an expert it did not choose are zero
+    for r in range(4):
+        for qi, e in enumerate(un):
+            assert (e in ids[r].tolist()) == bool(np.any(oh[r, qi * 32 : (qi + 1) * 32] != 0))
+
+
+def test_union(m):
+    ids = torch.from_numpy(m["ids"])
+    assert moe8.union(ids, 6) == m["union"].tolist() == orc.moe_union(ids.numpy(), 6)
+    clip = torch.tensor([[5, 9, 2], [2, 7, 0]])
+    assert moe8.union(clip, 6) == m["union_clip"].tolist() == orc.moe_union(clip.numpy(), 6) == [0, 2, 5]
+    assert moe8.u_max({"E": 16}, 5, 4) == 16 and moe8.u_max({"E": 128}, 5, 4) == 20
+
+
+def test_what_is_not_built_is_refused():
+    gu, dn = torch.zeros(2, 32, 64), torch.zeros(2, 32, 32)
+    with pytest.raises(NotImplementedError):
+        moe8.pack(None, gu, dn, kblock=True)
+    with pytest.raises(NotImplementedError):
+        moe8.pack(None, gu, dn, cache="/nowhere")
+    assert moe8._glu_order(torch.arange(128.0).reshape(1, 128), 64)[0, :64].tolist() == [
+        *range(64, 96), *range(0, 32)]  # gate tile 0 (columns I ..), then up tile 0

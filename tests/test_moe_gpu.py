@@ -1,0 +1,230 @@
+# SPDX-License-Identifier: Apache-2.0
+# Copyright 2026 Xylolabs
+# Ported from XylolabsInc/tensix-kernels, moe/tests/test_moe.py (Apache-2.0): test_decode, test_rows and test_hifi2, their
+# shapes, seeds and bars are that file's; the imports and the device API under them are this package's. test_bias is that
+# file's test_bias_groups_kblock without the K-block layout (not built here); the tests after it are this package's own.
+"""The reference's MoE checks (moe/tests/test_moe.py) against this package's API on a B200: experts on the bfloat4_b
+grid, x with a few outlier channels; gate_up's h and down's y against a float64 reference (relative Frobenius error below
+1 %, PCC above 0.9999) for each activation; the inert options and uint32 ids bit for bit; the rows ops with each row's
+own experts, rows past R zero. Then parity with the CPU oracle and the edge cases: an id past the experts, repeated
+calls on one workspace, a ragged shape."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from common import ttnn_like as ttnn  # noqa: E402
+from common.testing import check, same  # noqa: E402
+from moe import moe8  # noqa: E402
+from oracle import oracle as orc  # noqa: E402
+
+E, H, I, K = 16, 1024, 512, 4
+BF = torch.bfloat16
+REL = 0.01
+REL_HIFI2 = 0.016
+FID = "hifi4"
+
+
+def on_grid(w):
+    k, n = w.shape
+    v = moe8.bfp4_values(moe8.bfp4_tiles(w))
+    return torch.from_numpy(v.transpose(0, 2, 1, 3).reshape(k, n).copy())
+
+
+def experts(seed, gu_scale=0.02, e=E, h=H, i=I):
+    g = torch.Generator().manual_seed(seed)
+    gu = torch.stack([on_grid(torch.randn(h, 2 * i, generator=g) * gu_scale).to(BF) for _ in range(e)])
+    dn = torch.stack([on_grid(torch.randn(i, h, generator=g) * 0.02).to(BF) for _ in range(e)])
+    return gu, dn
+
+
+def make_x(rows, seed, h=H):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, h, generator=g)
+    x[:, torch.randperm(h, generator=g)[:8]] *= 20
+    return x.to(BF)
+
+
+def dev(device, t, dtype, layout=ttnn.TILE_LAYOUT, mc=ttnn.DRAM_MEMORY_CONFIG):
+    return ttnn.from_torch(t, dtype=dtype, layout=layout, device=device, memory_config=mc)
+
+
+def decode_inputs(device, seed, ids32=False):
+    g = torch.Generator().manual_seed(100 + seed)
+    ids = torch.randperm(E, generator=g)[:K]
+    wts = torch.softmax(torch.randn(K, generator=g), 0).to(BF)
+    x = make_x(1, seed)
+    idt, dt = (torch.int32, ttnn.uint32) if ids32 else (torch.int16, ttnn.uint16)
+    tid = dev(device, ids.to(idt).reshape(1, 1, 1, K), dt, ttnn.ROW_MAJOR_LAYOUT)
+    twt = dev(device, wts.reshape(1, 1, 1, K), ttnn.bfloat16)
+    tx = dev(device, x.reshape(1, 1, 1, H), ttnn.bfloat16, mc=ttnn.L1_MEMORY_CONFIG)
+    return ids, wts, x, tid, twt, tx
+
+
+def host(t, cols):
+    return ttnn.to_torch(t).float().reshape(-1, t.shape[-1])[:, :cols]
+
+
+def test_decode(device):
+    decode_case(device, FID, REL)
+
+
+def decode_case(device, fid, rel):
+    for act, scale in (("silu", 0.02), ("gelu_tanh", 0.02), ("swiglu_oai", 0.1)):
+        gu, dn = experts(1, scale)
+        P = moe8.pack(device, gu, dn)
+        ids, wts, x, tid, twt, tx = decode_inputs(device, 2)
+        ry, rh = moe8.reference(x.float(), gu, dn, ids.tolist(), wts.float(), act)
+        outs = {}
+        for loaders in (1, 2):
+            th = moe8.gate_up(tx, P, tid, twt, K, act=act, loaders=loaders, fidelity=fid)
+            ty = moe8.down(th, P, tid, K, loaders=loaders, fidelity=fid)
+            outs[loaders] = (host(th, K * I)[:1], host(ty, H)[:1])
+            check(f"{act} gate_up h, {fid}, loaders {loaders}", outs[loaders][0], rh, rel=rel)
+            check(f"{act} down y, {fid}, loaders {loaders}", outs[loaders][1], ry, rel=rel)
+        same(f"{act} h: two loaders against one", outs[2][0], outs[1][0])
+        same(f"{act} y: two loaders against one", outs[2][1], outs[1][1])
+        if act == "silu" and fid == FID:
+            cpb = 2 if P["cpb"] != 2 else 1
+            th = moe8.gate_up(tx, P, tid, twt, K, act=act, cpb=cpb, fidelity=fid)
+            same(f"h with {cpb} cores a bank against the pack's {P['cpb']}", host(th, K * I)[:1], outs[2][0])
+            _, _, _, tid32, twt32, tx32 = decode_inputs(device, 2, ids32=True)
+            th = moe8.gate_up(tx32, P, tid32, twt32, K, act=act, ids32=True, fidelity=fid)
+            ty = moe8.down(th, P, tid32, K, ids32=True, fidelity=fid)
+            same("h with uint32 ids", host(th, K * I)[:1], outs[2][0])
+            same("y with uint32 ids", host(ty, H)[:1], outs[2][1])
+
+
+def test_bias(device):
+    gu, dn = experts(3, 0.1)
+    g = torch.Generator().manual_seed(4)
+    gb = torch.randn(E, 2 * I, generator=g) * 0.5
+    P = moe8.pack(device, gu, dn, banks=2, gu_bias=gb)
+    for act in ("swiglu_oai", "silu"):
+        ids, wts, x, tid, twt, tx = decode_inputs(device, 5)
+        ry, rh = moe8.reference(x.float(), gu, dn, ids.tolist(), wts.float(), act, gb)
+        th = moe8.gate_up(tx, P, tid, twt, K, act=act, loaders=2, fidelity=FID)
+        ty = moe8.down(th, P, tid, K, loaders=2, fidelity=FID)
+        check(f"{act} with a bias, {FID}: h", host(th, K * I)[:1], rh, rel=REL)
+        check(f"{act} with a bias, {FID}: y", host(ty, H)[:1], ry, rel=REL)
+    rows_case(device, gu, dn, P, 6, act="swiglu_oai", gb=gb, loaders=(1, 2), seed=6)
+
+
+def rows_inputs(device, R, seed, ids32=False):
+    g = torch.Generator().manual_seed(200 + seed)
+    ids = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(R)])
+    wts = torch.softmax(torch.randn(R, K, generator=g), -1).to(BF)
+    x = make_x(R, seed)
+    idt, dt = (torch.int32, ttnn.uint32) if ids32 else (torch.int16, ttnn.uint16)
+    tid = dev(device, ids.to(idt).reshape(1, 1, R, K), dt)
+    twt = dev(device, wts.reshape(1, 1, R, K), ttnn.bfloat16)
+    tx = dev(device, x.reshape(1, 1, R, H), ttnn.bfloat16)
+    return ids, wts, x, tid, twt, tx
+
+
+def rows_case(device, gu, dn, P, R, act="silu", gb=None, loaders=(1,), seed=0, ids32=False, fid=FID):
+    ids, wts, x, tid, twt, tx = rows_inputs(device, R, seed, ids32)
+    ref = moe8.reference_rows(x.float(), gu, dn, ids.tolist(), wts.float(), act, gb)
+    u = moe8.union(ids, E)
+    href = torch.zeros(R, len(u) * I, dtype=torch.float64)
+    for r in range(R):
+        _, hr = moe8.reference(x[r : r + 1].float(), gu, dn, ids[r].tolist(), wts[r].float(), act, gb)
+        for s, e in enumerate(ids[r].tolist()):
+            q = u.index(e)
+            href[r, q * I : (q + 1) * I] = hr[0, s * I : (s + 1) * I]
+    outs = []
+    for ld in loaders:
+        th = moe8.gate_up_rows(tx, P, tid, twt, K, R, act=act, loaders=ld, ids32=ids32, fidelity=fid)
+        ty = moe8.down_rows(th, P, tid, K, R, loaders=ld, ids32=ids32, fidelity=fid)
+        hd = host(th, len(u) * I)[:R]
+        yall = host(ty, H)
+        name = f"rows {R} ({act}{', bias' if gb is not None else ''}{', uint32 ids' if ids32 else ''}), {fid}, loaders {ld}"
+        bar = REL if fid == "hifi4" else REL_HIFI2
+        check(f"{name}: h", hd, href, rel=bar)
+        check(f"{name}: y", yall[:R], ref, rel=bar)
+        same(f"{name}: rows past R zero", yall[R:32], torch.zeros(32 - R, H))
+        outs.append((hd, yall))
+    for (h1, y1), (h2, y2), ld in zip(outs, outs[1:], loaders[1:]):
+        same(f"rows {R}: h with {ld} loaders against {loaders[0]}", h2, h1)
+        same(f"rows {R}: y with {ld} loaders against {loaders[0]}", y2, y1)
+    return outs
+
+
+def test_rows(device):
+    gu, dn = experts(7)
+    P = moe8.pack(device, gu, dn)
+    rows_case(device, gu, dn, P, 1, seed=1)
+    rows_case(device, gu, dn, P, 5, loaders=(1, 2), seed=2)
+    rows_case(device, gu, dn, P, 32, act="gelu_tanh", seed=3)
+    rows_case(device, gu, dn, P, 5, seed=2, ids32=True)
+
+
+def test_hifi2(device):
+    decode_case(device, "hifi2", REL_HIFI2)
+    gu, dn = experts(7)
+    P = moe8.pack(device, gu, dn)
+    rows_case(device, gu, dn, P, 5, loaders=(1, 2), seed=2, fid="hifi2")
+    rows_case(device, gu, dn, P, 32, act="gelu_tanh", seed=3, fid="hifi2")
+
+
+# ---- this package's own checks
+
+
+def bf16_close(got, want, what, tol=1e-2):
+    """got (bf16 values) against the oracle's float64: within a bf16 rounding of the result plus the fp32 sums' error."""
+    want = torch.as_tensor(want).float()
+    err = (got.float() - want).abs().max().item()
+    scale = want.abs().max().item()
+    assert err <= tol * scale, (what, err, scale)
+
+
+def test_decode_against_the_oracle_ragged_and_invalid_ids(device):
+    """A shape whose K ends inside a super-atom of 64 (H 96, I 96) and whose columns end inside a panel of 128; an id at or
+    past the experts gives zeros in its slot and nothing in y; a second call on the same workspace gives the same bits."""
+    e, h, i, k = 5, 96, 96, 3
+    gu, dn = experts(11, 0.1, e, h, i)
+    P = moe8.pack(device, gu, dn)
+    x = make_x(1, 12, h)
+    wts = torch.tensor([0.5, 0.25, 0.25]).to(BF)
+    for ids in ([4, 0, 2], [1, 7, 3]):
+        tid = dev(device, torch.tensor(ids, dtype=torch.int16).reshape(1, 1, 1, k), ttnn.uint16, ttnn.ROW_MAJOR_LAYOUT)
+        twt = dev(device, wts.reshape(1, 1, 1, k), ttnn.bfloat16)
+        tx = dev(device, x.reshape(1, 1, 1, h), ttnn.bfloat16)
+        valid = [(s, v) for s, v in enumerate(ids) if v < e]
+        oy, oh = orc.moe_reference(x.float().numpy(), gu.float().numpy(), dn.float().numpy(), [v for _, v in valid],
+                                   [float(wts[s]) for s, _ in valid], "silu")
+        want_h = torch.zeros(1, k * i, dtype=torch.float64)
+        for j, (s, _) in enumerate(valid):
+            want_h[0, s * i : (s + 1) * i] = torch.from_numpy(oh[0, j * i : (j + 1) * i])
+        th = moe8.gate_up(tx, P, tid, twt, k)
+        ty = moe8.down(th, P, tid, k)
+        bf16_close(host(th, k * i)[:1], want_h, f"h {ids}")
+        # (y against the oracle's y from the device's own bf16 h would be tighter; the float64 chain is within the bar too)
+        bf16_close(host(ty, h)[:1], oy, f"y {ids}", tol=2e-2)
+        if len(valid) < k:
+            s_bad = next(s for s, v in enumerate(ids) if v >= e)
+            assert not host(th, k * i)[0, s_bad * i : (s_bad + 1) * i].any()
+        ty2 = moe8.down(th, P, tid, k)
+        same(f"down twice on one workspace {ids}", host(ty2, h), host(ty, h))
+
+
+def test_rows_many_inputs_in_passes(device):
+    """32 rows of 4096 inputs do not fit in shared memory at once: the kernel takes them in passes of 16 and gives what the
+    reference gives."""
+    e, h, i, k, R = 4, 4096, 64, 2, 32
+    gu, dn = experts(13, 0.02, e, h, i)
+    P = moe8.pack(device, gu, dn)
+    g = torch.Generator().manual_seed(14)
+    ids = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(R)])
+    wts = torch.softmax(torch.randn(R, k, generator=g), -1).to(BF)
+    x = make_x(R, 15, h)
+    tid = dev(device, ids.to(torch.int16).reshape(1, 1, R, k), ttnn.uint16)
+    twt = dev(device, wts.reshape(1, 1, R, k), ttnn.bfloat16)
+    tx = dev(device, x.reshape(1, 1, R, h), ttnn.bfloat16)
+    oy, oh = orc.moe_reference_rows(x.float().numpy(), gu.float().numpy(), dn.float().numpy(), ids.numpy(),
+                                    wts.float().numpy(), e)
+    th = moe8.gate_up_rows(tx, P, tid, twt, k, R)
+    ty = moe8.down_rows(th, P, tid, k, R)
+    check("rows in passes: h", host(th, oh.shape[1])[:R], torch.from_numpy(oh), rel=REL)
+    check("rows in passes: y", host(ty, h)[:R], torch.from_numpy(oy), rel=REL)
