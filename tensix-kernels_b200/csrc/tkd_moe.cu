@@ -74,20 +74,25 @@ __device__ __forceinline__ float moe_glu(float gt, float u, int act) {
 
 // MT: tiles of 8 rows. ROWS: by_union. DOWN: the down matmul.
 template <int MT, bool ROWS, bool DOWN>
-__global__ void __launch_bounds__(kMoeThreads) tkd_moe_kernel(const MoeParams p) {
-    extern __shared__ __align__(16) uint8_t smem[];
+__global__ void __launch_bounds__(kMoeThreads, MT == 1 ? 2 : 1) tkd_moe_kernel(const MoeParams p) {
+    extern __shared__ __align__(16) uint8_t moe_dsm[];
     __shared__ uint32_t bm[32];  // ROWS: a bit per expert some row chose
     __shared__ float wrow[32];   // ROWS: row r's routing weight for this CTA's expert (0: not chosen)
     __shared__ int s_e, s_count, s_last;
     constexpr int RP = 8 * MT;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int gi = warp & (kMoeGroups - 1), ksp = warp / kMoeGroups;
-    const int hp = blockIdx.x, q = blockIdx.y;
+    const int q = blockIdx.y;
     const int R = p.R;
     const int Kpad = (p.K + 63) & ~63;
     const int xstride = Kpad * 2 + 16;  // bytes from a row of the activations in shared memory to the next
-    uint8_t* xs = smem;
-    float* red = reinterpret_cast<float*>(smem + (((size_t)p.RB * xstride + 15) & ~(size_t)15));  // [ksp][column][RP]
+    uint8_t* xs = moe_dsm;
+    float* red = reinterpret_cast<float*>(moe_dsm + (((size_t)p.RB * xstride + 15) & ~(size_t)15));  // [ksp][column][RP]
+
+    // (launched as a programmatic dependent: nothing the kernels before wrote is read above this line, and the kernel
+    // after may bring its CTAs in while this one runs: it waits at the same place)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // ---- this CTA's expert
     int e = -1, count = p.slots;
@@ -134,123 +139,136 @@ __global__ void __launch_bounds__(kMoeThreads) tkd_moe_kernel(const MoeParams p)
         }
     }
 
-    const uint8_t* em = p.emax + (int64_t)max(e, 0) * (p.npad / 16) + hp * kMoeGroups;
     float w1 = 0.f;  // one row: the slot's routing weight
     if constexpr (!ROWS && !DOWN)
         if (e >= 0) w1 = bf16_bits_to_f32(p.rw[q]);
+    const int nhp = (DOWN ? p.npad : p.N) / kMoeCols;  // blocks of 64 columns; this CTA takes every gridDim.x-th
+    const uint8_t* wb = p.w + (int64_t)max(e, 0) * p.wbytes;
+    const int nsa = Kpad / 64, per = (nsa + kMoeSplit - 1) / kMoeSplit;
+    const int sa0 = ksp * per, sa1 = min(nsa, sa0 + per);
+    const uint2 sh = make_uint2(p.mul16, p.mul128);
     for (int r0 = 0; r0 < R; r0 += p.RB) {
         const int Rb = min(p.RB, R - r0);
-        // ---- the activations: gate_up: the rows of x; down: the rows' inputs of slot q. Zeros past K up to a super-atom.
-        if (e >= 0) {
-            const uint16_t* xsrc = p.x + (int64_t)r0 * p.ldx + (DOWN ? (int64_t)q * p.K : 0);
-            const int vec = Kpad / 8;
-            for (int i = tid; i < Rb * vec; i += kMoeThreads) {
-                const int r = i / vec, c = i - r * vec;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (c * 8 < p.K) v = __ldg(reinterpret_cast<const uint4*>(xsrc + (int64_t)r * p.ldx) + c);
-                *reinterpret_cast<uint4*>(xs + (size_t)r * xstride + (size_t)c * 16) = v;
-            }
-        }
-        __syncthreads();
-
-        // ---- the group's sums over this warp's run of super-atoms
-        if (e >= 0) {
-            float acc[2][MT][4];
+        const bool last_rows = r0 + p.RB >= R;
+        bool x_here = false;
+        uint32_t xa[MT];  // (a lane past the last row reads the last row: its column of the result is never used)
 #pragma unroll
-            for (int a = 0; a < 2; ++a)
+        for (int m = 0; m < MT; ++m) xa[m] = smem_u32(xs) + (uint32_t)min(8 * m + g, Rb - 1) * xstride + 16 * t;
+        for (int hp = blockIdx.x; hp < nhp; hp += gridDim.x) {
+            const uint8_t* em = p.emax + (int64_t)max(e, 0) * (p.npad / 16) + hp * kMoeGroups;
+            if (e >= 0) {
+                // ---- the group's sums over this warp's run of super-atoms; the first loads fly while x comes in
+                float acc[2][MT][4];
 #pragma unroll
-                for (int m = 0; m < MT; ++m) acc[a][m][0] = acc[a][m][1] = acc[a][m][2] = acc[a][m][3] = 0.f;
-            const int group = hp * kMoeGroups + gi;
-            const uint8_t* wb = p.w + (int64_t)e * p.wbytes;
-            const int nsa = Kpad / 64, per = (nsa + kMoeSplit - 1) / kMoeSplit;
-            const int sa0 = ksp * per, sa1 = min(nsa, sa0 + per);
-            const uint2 sh = make_uint2(p.mul16, p.mul128);
-            uint32_t xa[MT];  // (a lane past the last row reads the last row: its column of the result is never used)
+                for (int a = 0; a < 2; ++a)
 #pragma unroll
-            for (int m = 0; m < MT; ++m) xa[m] = smem_u32(xs) + (uint32_t)min(8 * m + g, Rb - 1) * xstride + 16 * t;
-            for (int sa = sa0; sa < sa1; sa += kMoeBatch) {
+                    for (int m = 0; m < MT; ++m) acc[a][m][0] = acc[a][m][1] = acc[a][m][2] = acc[a][m][3] = 0.f;
+                const int group = hp * kMoeGroups + gi;
                 uint4 cv[kMoeBatch], ev[kMoeBatch];
+                auto load = [&](int sa) {
 #pragma unroll
-                for (int b = 0; b < kMoeBatch; ++b)
-                    if (sa + b < sa1) {
-                        const uint8_t* s = wb + tkd_sa_offset(TKD_BFP4, p.K, group, sa + b);
-                        ev[b] = ldg_stream(s + t * 16);
-                        cv[b] = ldg_stream(s + 64 + lane * 16);
-                    }
-#pragma unroll
-                for (int b = 0; b < kMoeBatch; ++b)
-                    if (sa + b < sa1) {
-#pragma unroll
-                        for (int qq = 0; qq < 2; ++qq) {
-                            const uint32_t cw[4] = {qq ? cv[b].z : cv[b].x, qq ? cv[b].w : cv[b].y, 0u, 0u};
-                            const uint32_t ew[2] = {qq ? ev[b].z : ev[b].x, qq ? ev[b].w : ev[b].y};
-                            uint4 xv[MT];
-#pragma unroll
-                            for (int m = 0; m < MT; ++m) xv[m] = lds128(xa[m] + (uint32_t)(sa + b) * 128 + 64 * qq);
-                            block_mma<TKD_BFP4, MT, 2>(acc, cw, ew, xv, sh);
+                    for (int b = 0; b < kMoeBatch; ++b)
+                        if (sa + b < sa1) {
+                            const uint8_t* s = wb + tkd_sa_offset(TKD_BFP4, p.K, group, sa + b);
+                            ev[b] = ldg_stream(s + t * 16);
+                            cv[b] = ldg_stream(s + 64 + lane * 16);
                         }
+                };
+                load(sa0);
+                if (!x_here) {
+                    // the activations: gate_up: the rows of x; down: the rows' inputs of slot q. Zeros past K up to a
+                    // super-atom.
+                    const uint16_t* xsrc = p.x + (int64_t)r0 * p.ldx + (DOWN ? (int64_t)q * p.K : 0);
+                    const int vec = Kpad / 8;
+                    for (int i = tid; i < Rb * vec; i += kMoeThreads) {
+                        const int r = i / vec, c = i - r * vec;
+                        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                        if (c * 8 < p.K) v = __ldg(reinterpret_cast<const uint4*>(xsrc + (int64_t)r * p.ldx) + c);
+                        *reinterpret_cast<uint4*>(xs + (size_t)r * xstride + (size_t)c * 16) = v;
                     }
-            }
-            // D fragment: (column g, rows 2t and 2t + 1), (column g + 8, the same rows)
+                    __syncthreads();  // (e is the same for the whole CTA)
+                    x_here = true;
+                }
+                for (int sa = sa0; sa < sa1; sa += kMoeBatch) {
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                float* d0 = red + ((size_t)(ksp * kMoeCols + gi * 16 + g) * RP) + 8 * m + 2 * t;
-                d0[0] = acc[0][m][0] + acc[1][m][0], d0[1] = acc[0][m][1] + acc[1][m][1];
-                d0[8 * RP] = acc[0][m][2] + acc[1][m][2], d0[8 * RP + 1] = acc[0][m][3] + acc[1][m][3];
+                    for (int b = 0; b < kMoeBatch; ++b)
+                        if (sa + b < sa1) {
+#pragma unroll
+                            for (int qq = 0; qq < 2; ++qq) {
+                                const uint32_t cw[4] = {qq ? cv[b].z : cv[b].x, qq ? cv[b].w : cv[b].y, 0u, 0u};
+                                const uint32_t ew[2] = {qq ? ev[b].z : ev[b].x, qq ? ev[b].w : ev[b].y};
+                                uint4 xv[MT];
+#pragma unroll
+                                for (int m = 0; m < MT; ++m) xv[m] = lds128(xa[m] + (uint32_t)(sa + b) * 128 + 64 * qq);
+                                block_mma<TKD_BFP4, MT, 2>(acc, cw, ew, xv, sh);
+                            }
+                        }
+                    if (sa + kMoeBatch < sa1) load(sa + kMoeBatch);
+                }
+                // D fragment: (column g, rows 2t and 2t + 1), (column g + 8, the same rows)
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    float* d0 = red + ((size_t)(ksp * kMoeCols + gi * 16 + g) * RP) + 8 * m + 2 * t;
+                    d0[0] = acc[0][m][0] + acc[1][m][0], d0[1] = acc[0][m][1] + acc[1][m][1];
+                    d0[8 * RP] = acc[0][m][2] + acc[1][m][2], d0[8 * RP + 1] = acc[0][m][3] + acc[1][m][3];
+                }
             }
-        }
-        __syncthreads();
+            __syncthreads();
 
-        auto column_sum = [&](int c, int r) {
-            float v = 0.f;
-#pragma unroll
-            for (int s = 0; s < kMoeSplit; ++s) v += red[(size_t)(s * kMoeCols + c) * RP + r];
-            return moe_scale(v, em[c >> 4]);
-        };
-        if constexpr (!DOWN) {
-            const int I = p.N / 2;
-            for (int o = tid; o < 32 * Rb; o += kMoeThreads) {
-                const int c = o & 31, r = o >> 5;
-                float val = 0.f;
-                if (e >= 0) {
-                    float gt = column_sum(c, r), u = column_sum(32 + c, r);
-                    if (p.bias) {
-                        const uint16_t* b = p.bias + (int64_t)e * p.npad + hp * kMoeCols;
-                        gt += bf16_bits_to_f32(b[c]), u += bf16_bits_to_f32(b[32 + c]);
-                    }
-                    val = moe_glu(gt, u, p.act) * (ROWS ? wrow[r0 + r] : w1);
-                }
-                p.out[(int64_t)(r0 + r) * p.ldo + (int64_t)q * I + hp * 32 + c] = f32_to_bf16_bits(val);
-            }
-        } else {
-            if (e >= 0)
-                for (int o = tid; o < kMoeCols * Rb; o += kMoeThreads) {
-                    const int c = o & (kMoeCols - 1), r = o / kMoeCols;
-                    p.part[((int64_t)q * R + r0 + r) * p.npad + hp * kMoeCols + c] = column_sum(c, r);
-                }
-        }
-        __syncthreads();  // (the next rows overwrite the activations and the sums)
-    }
-    if constexpr (DOWN) {
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) s_last = atomicAdd(&p.counters[hp], 1) == p.slots - 1;
-        __syncthreads();
-        if (s_last) {
-            __threadfence();
-            for (int o = tid; o < kMoeCols * R; o += kMoeThreads) {
-                const int c = o & (kMoeCols - 1), r = o / kMoeCols, col = hp * kMoeCols + c;
-                if (col >= p.N) continue;
+            auto column_sum = [&](int c, int r) {
                 float v = 0.f;
-                for (int s = 0; s < count; ++s) {
-                    if constexpr (!ROWS)
-                        if (moe_id(p, s) >= (uint32_t)p.E) continue;
-                    v += __ldcg(&p.part[((int64_t)s * R + r) * p.npad + col]);
+#pragma unroll
+                for (int s = 0; s < kMoeSplit; ++s) v += red[(size_t)(s * kMoeCols + c) * RP + r];
+                return moe_scale(v, em[c >> 4]);
+            };
+            if constexpr (!DOWN) {
+                const int I = p.N / 2;
+                for (int o = tid; o < 32 * Rb; o += kMoeThreads) {
+                    const int c = o & 31, r = o >> 5;
+                    float val = 0.f;
+                    if (e >= 0) {
+                        float gt = column_sum(c, r), u = column_sum(32 + c, r);
+                        if (p.bias) {
+                            const uint16_t* b = p.bias + (int64_t)e * p.npad + hp * kMoeCols;
+                            gt += bf16_bits_to_f32(b[c]), u += bf16_bits_to_f32(b[32 + c]);
+                        }
+                        val = moe_glu(gt, u, p.act) * (ROWS ? wrow[r0 + r] : w1);
+                    }
+                    p.out[(int64_t)(r0 + r) * p.ldo + (int64_t)q * I + hp * 32 + c] = f32_to_bf16_bits(val);
                 }
-                p.out[(int64_t)r * p.ldo + col] = f32_to_bf16_bits(v);
+                __syncthreads();  // (the next block of columns overwrites the sums)
+            } else {
+                if (e >= 0)
+                    for (int o = tid; o < kMoeCols * Rb; o += kMoeThreads) {
+                        const int c = o & (kMoeCols - 1), r = o / kMoeCols;
+                        p.part[((int64_t)q * R + r0 + r) * p.npad + hp * kMoeCols + c] = column_sum(c, r);
+                    }
+                if (last_rows) {
+                    // this slot's sums of the block of columns are written: the CTA that arrives last adds the slots up
+                    __threadfence();
+                    __syncthreads();
+                    if (tid == 0) s_last = atomicAdd(&p.counters[hp], 1) == p.slots - 1;
+                    __syncthreads();
+                    if (s_last) {
+                        __threadfence();
+                        for (int o = tid; o < kMoeCols * R; o += kMoeThreads) {
+                            const int c = o & (kMoeCols - 1), r = o / kMoeCols, col = hp * kMoeCols + c;
+                            if (col >= p.N) continue;
+                            float v = 0.f;
+                            for (int s = 0; s < count; ++s) {
+                                if constexpr (!ROWS)
+                                    if (moe_id(p, s) >= (uint32_t)p.E) continue;
+                                v += __ldcg(&p.part[((int64_t)s * R + r) * p.npad + col]);
+                            }
+                            p.out[(int64_t)r * p.ldo + col] = f32_to_bf16_bits(v);
+                        }
+                        if (tid == 0) p.counters[hp] = 0;
+                    }
+                }
+                __syncthreads();  // (the next block of columns overwrites the sums, and s_last)
             }
-            if (tid == 0) p.counters[hp] = 0;
         }
+        __syncthreads();  // (the next rows overwrite the activations)
     }
 }
 
@@ -266,8 +284,13 @@ int moe_launch(const MoeParams& p, dim3 grid, size_t smem, cudaStream_t st) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kern<<<grid, kMoeThreads, smem, st>>>(p);
-    return (int)cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = dim3(kMoeThreads), cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 template <bool DOWN>
@@ -322,6 +345,24 @@ int moe_smem_limit() {
     return cached;
 }
 
+int moe_sms() {
+    static int cached = 0;
+    if (!cached) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return 148;
+        cached = v;
+    }
+    return cached;
+}
+// CTAs per slot. One row: a CTA per block of 64 columns. By union: a CTA keeps the rows' activations in shared memory
+// for several blocks of columns, as few CTAs a slot as still give every SM two.
+int moe_grid_x(const TkdMoe* a, int nhp) {
+    if (!a->by_union) return nhp;
+    const int want = (2 * moe_sms() + a->slots - 1) / a->slots;
+    return want < 1 ? 1 : (want > nhp ? nhp : want);
+}
+
 // How many rows a pass of the kernel takes: all of them if their activations fit in shared memory beside the sums,
 // else as many tiles of 8 as fit (then fewer than 8). false: not even one row fits.
 bool moe_rows_a_pass(const TkdMoe* a, int* rb, int* mt, size_t* smem) {
@@ -355,7 +396,7 @@ int tkd_moe_gate_up(const TkdMoe* a, void* stream) {
     int mt = 1;
     size_t smem = 0;
     if (!moe_rows_a_pass(a, &p.RB, &mt, &smem)) return TKD_ERR_UNSUPPORTED;
-    const dim3 grid((unsigned)(a->n / kMoeCols), (unsigned)a->slots);
+    const dim3 grid((unsigned)moe_grid_x(a, a->n / kMoeCols), (unsigned)a->slots);
     const int e = moe_dispatch<false>(p, a->by_union != 0, grid, smem, mt, static_cast<cudaStream_t>(stream));
     return e == 0 ? TKD_OK : TKD_ERR_CUDA + e;
 }
@@ -372,7 +413,7 @@ int tkd_moe_down(const TkdMoe* a, void* stream) {
     int mt = 1;
     size_t smem = 0;
     if (!moe_rows_a_pass(a, &p.RB, &mt, &smem)) return TKD_ERR_UNSUPPORTED;
-    const dim3 grid((unsigned)(npad / kMoeCols), (unsigned)a->slots);
+    const dim3 grid((unsigned)moe_grid_x(a, (int)(npad / kMoeCols)), (unsigned)a->slots);
     const int e = moe_dispatch<true>(p, a->by_union != 0, grid, smem, mt, static_cast<cudaStream_t>(stream));
     return e == 0 ? TKD_OK : TKD_ERR_CUDA + e;
 }
