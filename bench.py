@@ -57,6 +57,10 @@ WORKLOADS = {
     "w4": dict(k=4096, n=28672, fmt="int4", what="int4 codes with bf16 group scales (G = 32): [28672,4096], one token"),
     # ... and ternary_matmul/t2.py: the same shape in trits with G = 128, the block Hadamard in front (inside the kernel)
     "t2": dict(k=4096, n=28672, fmt="int4", what="ternary weight (G = 128) behind the block Hadamard: [28672,4096], one token"),
+    # ... and moe/moe8.py: one token through a layer's chosen experts (the two launches gate_up and down)
+    "moe": dict(k=2048, n=768, fmt="bfp4", experts=128, chosen=8,
+                what="MoE layer, one token: 8 of 128 bfloat4_b experts [2048 -> 2 x 768 -> 2048] (the expert shape of "
+                     "Qwen3-30B-A3B, synthetic weights), gate_up (SwiGLU, routing weights) then down"),
 }
 BYTES_PER_WEIGHT = {"bfp8": 1.0625, "bfp4": 0.5625, "bf16": 2.0, "int4": 0.5625}
 L2_BYTES = 126 * 1024 * 1024
@@ -331,6 +335,9 @@ def main():
     if wl["fmt"] == "int4":
         config["arithmetic"] = "bf16 activations x int4 codes (exact products), fp32 sums per 32 k, times the bf16 group scale in fp32"
 
+    if args.workload == "moe":
+        config.update(K=None, N=None, hidden=wl["k"], intermediate=wl["n"], experts=wl["experts"], chosen=wl["chosen"])
+        return moe_main(args, emit, config, steps, warmup)
     if args.impl == "reference":
         if rank != 0:
             return 0
@@ -510,6 +517,7 @@ def main():
             subs[key] = sub_case("c3", rows, device, max(50, steps // 3))
         subs["int4"] = sub_case("w4", 1, device, max(50, steps // 3))
         subs["ternary"] = sub_case("t2", 1, device, max(50, steps // 3))
+        subs["moe"] = moe_sub_case(device, max(48, steps // 4))
     if args.workload == "c2" and m == 1 and not args.cols and (world == 1 or fused):
         subs["c5_strong"] = lm_head_strong(device, world, rank, max(30, steps // 10))
     linear.check_status(device)
@@ -729,6 +737,192 @@ def end_to_end(name, case, wl, m, device, world, rank, n_total, col_start, copie
             "steps": e_steps, "mode": "pipelined x2 (two calls in flight on two streams)",
             "h2d_bytes_per_step": x_pin.numel() * 2, "d2h_bytes_per_step": lanes[0]["yp"].numel() * lanes[0]["yp"].element_size(),
             "one_call_at_a_time_us": lat_us}
+
+
+
+# ---- the mixture-of-experts sibling (moe/moe8.py of the reference): a workload of its own, two launches a step ----
+
+
+def moe_layer_bytes(wl, experts):
+    """Packed-weight bytes of `experts` experts of the layer: gate|up [H, 2I] and down [I, H] at 0.5625 bytes a weight."""
+    return int(experts * 3 * wl["k"] * wl["n"] * BYTES_PER_WEIGHT["bfp4"])
+
+
+def build_moe_case(device, rows, seed0):
+    """The packed layer (made on the GPU from seeded normal weights), one activation row (or `rows` of them with their own
+    experts), and id sets that together go through all experts, so that a step's experts are never in L2 (all experts:
+    340 MB): step i runs gate_up then down on set i."""
+    from common import ttnn_like as ttnn
+    from moe import moe8
+
+    wl = WORKLOADS["moe"]
+    E, H, I, K = wl["experts"], wl["k"], wl["n"], wl["chosen"]
+    g = torch.Generator(device=device.torch).manual_seed(seed0)
+    gu = torch.randn(E, H, 2 * I, generator=g, device=device.torch) * 0.02
+    dn = torch.randn(E, I, H, generator=g, device=device.torch) * 0.02
+    P = moe8.pack(device, gu, dn)
+    del gu, dn
+    gc = torch.Generator().manual_seed(seed0 + 1)
+    x = torch.randn(rows, H, generator=gc).to(torch.bfloat16)
+    tx = ttnn.from_torch(x.reshape(1, 1, rows, H), dtype=ttnn.bfloat16, layout=ttnn.TILE_LAYOUT, device=device)
+    sets, experts_read = [], []
+    perm = torch.randperm(E, generator=gc)
+    for s in range(E // K if rows == 1 else 8):
+        if rows == 1:
+            ids = perm[s * K:(s + 1) * K].reshape(1, K)
+        else:
+            ids = torch.stack([torch.randperm(E, generator=gc)[:K] for _ in range(rows)])
+        w = torch.softmax(torch.randn(rows, K, generator=gc), -1).to(torch.bfloat16)
+        sets.append((ttnn.from_torch(ids.to(torch.int16).reshape(1, 1, rows, K), dtype=ttnn.uint16, layout=ttnn.TILE_LAYOUT, device=device),
+                     ttnn.from_torch(w.reshape(1, 1, rows, K), dtype=ttnn.bfloat16, layout=ttnn.TILE_LAYOUT, device=device)))
+        experts_read.append(len(moe8.union(ids, E)))
+
+    def step(i, x_t=tx):
+        tid, tw = sets[i % len(sets)]
+        if rows == 1:
+            return moe8.down(moe8.gate_up(x_t, P, tid, tw, K), P, tid, K)
+        return moe8.down_rows(moe8.gate_up_rows(x_t, P, tid, tw, K, rows), P, tid, K, rows)
+
+    nread = sum(experts_read) / len(experts_read)
+    wbytes = moe_layer_bytes(wl, nread)
+    # algorithmic bytes of a step: the chosen experts' weights once, x, ids and routing weights, h written and read, y
+    um = K if rows == 1 else min(E, rows * K)
+    other = rows * H * 2 + rows * K * 4 + 2 * rows * um * I * 2 + rows * H * 2
+    return dict(step=step, P=P, x=tx, x_host=x, sets=sets, wbytes=wbytes, abytes=wbytes + other, experts_read=nread)
+
+
+def moe_cpu_arm(steps, warmup, budget_s, min_s):
+    """The reference's own host statement of the layer (moe8.reference, moe/moe8.py:619-636: float64 matmuls over the
+    chosen experts' dequantised weights) as the oracle restates it, on a layer of 16 experts resident in host memory."""
+    from oracle import oracle as orc
+
+    wl = WORKLOADS["moe"]
+    H, I, K, E = wl["k"], wl["n"], wl["chosen"], 16
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(77)
+    gu = (torch.randn(E, H, 2 * I, generator=g) * 0.02).to(torch.bfloat16).double().numpy()
+    dn = (torch.randn(E, I, H, generator=g) * 0.02).to(torch.bfloat16).double().numpy()
+    x = torch.randn(1, H, generator=g).to(torch.bfloat16).double().numpy()
+    w = torch.softmax(torch.randn(K, generator=g), 0).double().numpy()
+    sets = [torch.randperm(E, generator=g)[:K].tolist() for _ in range(8)]
+    for i in range(max(3, warmup)):
+        orc.moe_reference(x, gu, dn, sets[i % 8], w)
+    t0, done = time.perf_counter(), 0
+    while True:
+        orc.moe_reference(x, gu, dn, sets[done % 8], w)
+        done += 1
+        el = time.perf_counter() - t0
+        if el >= budget_s or (el >= min_s and done >= steps):
+            break
+    dt = el / done
+    info = {"cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"the whole step ({K} experts) on a layer of {E} experts held dequantised in float64, {done} steps",
+            "ms_per_step_sample": dt * 1e3}
+    return moe_layer_bytes(wl, K) / dt / 1e9, info
+
+
+def moe_main(args, emit, config, steps, warmup):
+    """bench.py --workload moe at N = 1 (more ranks: replicas; the layer has no exchange step of its own here)."""
+    from common import ttnn_like as ttnn
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    wl = WORKLOADS["moe"]
+    if args.impl == "reference":
+        if rank == 0:
+            val, info = moe_cpu_arm(steps, warmup, 60.0, 5.0)
+            emit({"impl": "reference", "metric": "weight_stream_gbps", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+                  "steps": steps, "warmup": warmup, "ms_per_step": info["ms_per_step_sample"], "higher_is_better": True,
+                  "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic", "config": config,
+                  "cpu_baseline": {"value": val, "unit": "GB/s", **info},
+                  "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        return 0
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    device = ttnn.open_device(local)
+    case = build_moe_case(device, args.rows, 100 + 1000 * rank)
+    step = case["step"]
+    if args.profile:
+        for i in range(warmup + steps):
+            step(i)
+        torch.cuda.synchronize()
+        finish(world)
+        return 0
+    with Clocks(local) as clk:
+        ms, reps, graphed = timed_graph(step, lambda: None, steps, warmup, world, device)
+    us = ms * 1e3 / steps
+    value = world * case["wbytes"] / (us * 1e-6) / 1e9
+    # end to end, one call at a time: x from pinned host memory, the two launches, y back
+    x_pin = case["x_host"].reshape(1, 1, args.rows, -1).contiguous().pin_memory()
+    y_pin = torch.empty(1, 1, 32 if args.rows > 1 else 1, wl["k"], dtype=torch.bfloat16).pin_memory()
+    e_steps = min(steps, 200)
+
+    def host_call(i):
+        case["x"].t.copy_(x_pin, non_blocking=True)
+        y = step(i)
+        y_pin.copy_(y.t, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(warmup):
+        host_call(i)
+    _barrier(world)
+    t0 = time.perf_counter()
+    for i in range(e_steps):
+        host_call(i)
+    e_us = _max_over_ranks((time.perf_counter() - t0) / e_steps * 1e6, world, device)
+    if rank != 0:
+        finish(world)
+        return 0
+    peak, peak_src = peaks()
+    achieved = case["abytes"] / (us * 1e-6) / 1e9
+    line = {
+        "metric": "weight_stream_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms / steps, "us_per_call": us, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {**config, "experts_read_per_step": case["experts_read"],
+                   "l2": f"the steps' id sets go through all {wl['experts']} experts ({moe_layer_bytes(wl, wl['experts']) / 1e6:.0f} MB > 2 x L2)",
+                   "timing": (f"CUDA graph of {steps} steps (two launches each), {reps} replays, CUDA events" if graphed
+                              else f"{steps} plain steps x {reps}, CUDA events"),
+                   "exchange": "none: every rank runs the whole layer (replicas)"},
+        "pct_of_8000": 100 * value / world / 8000.0, "clocks": clk.summary(), "gpu_launches": steps * reps * 2,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": TRAFFIC.get("moe") if args.rows == 1 else None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": case["abytes"],
+                     "note": "per step of two launches (gate_up and down); traffic likewise"},
+        "e2e": {"value": world * case["wbytes"] / (e_us * 1e-6) / 1e9, "unit": "GB/s", "us_per_call": e_us,
+                "mode": "one call at a time", "h2d_bytes_per_step": x_pin.numel() * 2, "d2h_bytes_per_step": y_pin.numel() * 2},
+    }
+    if world == 1 and not args.no_cpu:
+        val, info = moe_cpu_arm(50, 3, 15.0, 4.0)
+        line["cpu_baseline"] = {"value": val, "unit": "GB/s", **info}
+    emit(line)
+    finish(world)
+    return 0
+
+
+def moe_sub_case(device, steps):
+    """The MoE layer's record for the default line: one token, then 8 and 32 rows with their own experts."""
+    out = {"workload": "moe: " + WORKLOADS["moe"]["what"], "unit": "GB/s"}
+    peak, _ = peaks()
+    for rows in (1, 8, 32):
+        case = build_moe_case(device, rows, 700 + rows)
+        n = steps if rows == 1 else max(10, steps // 8)
+        ms, _, _ = timed_graph(case["step"], lambda: None, n, 5, 1, device, min_s=0.2)
+        us = ms * 1e3 / n
+        rec = {"us_per_call": us, "value": case["wbytes"] / (us * 1e-6) / 1e9, "experts_read": case["experts_read"], "launches": 2,
+               "roofline": {"bound": "hbm", "achieved": case["abytes"] / (us * 1e-6) / 1e9, "peak": peak, "unit": "GB/s",
+                            "frac": case["abytes"] / (us * 1e-6) / 1e9 / peak, "algorithmic_bytes_per_launch": case["abytes"]}}
+        if rows == 1:
+            out.update(rows=1, **rec)
+        else:
+            out[f"rows{rows}"] = rec
+        del case
+        torch.cuda.empty_cache()
+    return out
 
 
 def sub_case(name, rows, device, steps):
