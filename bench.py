@@ -999,7 +999,7 @@ def finish(world):
 
 # DRAM bytes per launch of tkd_stream_kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum), per
 # workload at M = 1 (the summaries under profiles/); None where no capture of the workload is summarised there.
-TRAFFIC = {"c2": 66_769_408, "c3": 62_681_600, "c5": 667_036_928, "w4": 66_386_432}
+TRAFFIC = {"c2": 66_769_408, "c3": 62_681_600, "c5": 667_036_928, "w4": 66_386_432, "moe": 21_298_944}
 
 if __name__ == "__main__":
     sys.exit(main())
