@@ -262,6 +262,22 @@ int tkd_moe_workspace(const TkdMoe* a, uint64_t* bytes);
  * for each, from L2). TKD_ERR_UNSUPPORTED: not even one row of k_in inputs fits. */
 int tkd_moe_gate_up(const TkdMoe* a, void* stream);
 int tkd_moe_down(const TkdMoe* a, void* stream);
+/* The router's top k and their weights, into the ids and weights the ops above read: stands in for moe8.route
+ * (moe/moe8.py:1139-1253; kernels/moe_route.cpp). logits: float32 [rows, ld] (rows <= 32), the experts' columns
+ * 0 .. experts - 1 (a multiple of 32, at most 1024). Per row the k picks in decreasing order of their key, the lower id
+ * among equal keys, computed in float64:
+ *   kind 0 (softmax): key = the logit; weights = the softmax over the k picks' logits;
+ *   kind 1 (sigmoid with a bias): key = sigmoid(logit) + bias[e] (bias: float32 [experts]); weights = the picks'
+ *          sigmoids over their sum (norm 0: each pick's own sigmoid);
+ *   kind 2 (sigmoid without a bias): key = the logit; weights as kind 1's.
+ * Every weight times scale (0 < scale < 4), rounded to bf16. n_group > 1 (kind 1; DeepSeek-V3's group-limited routing): the
+ * experts in n_group groups in order, a group's score the sum of its two largest keys, the topk_group best groups kept (the
+ * lower group among equal scores), the picks among their experts. has_slot: `slot` is written as slot k of every row at
+ * weight 1.0 (ids and w then hold k + 1 slots). ids: uint16 (ids32 0) or uint32 [rows, ld_ids]; w: bf16 [rows, ld_w];
+ * shared (or NULL): bf16 [rows, ld_shared], column 0 gets sigmoid(logits[:, experts]). */
+int tkd_moe_route(const float* logits, int64_t ld, int rows, int experts, int k, int kind, const float* bias, double scale,
+                  int norm, int n_group, int topk_group, int has_slot, uint32_t slot, void* ids, int ids32, int64_t ld_ids,
+                  void* w, int64_t ld_w, void* shared, int64_t ld_shared, void* stream);
 
 /* The best `top` candidates of every row among `nrecords` top-k records (the record layout above: keys[rows][k] then
  * indices[rows][k]), key descending and index ascending among equal keys; out is one record of the same layout with

@@ -392,3 +392,38 @@ def moe_reference_rows(x, gate_up, down, ids, w, E, act="silu", gu_bias=None):
         for s, e in enumerate(ids[r].tolist()):
             h[r, un.index(e) * I : (un.index(e) + 1) * I] = hr[0, s * I : (s + 1) * I]
     return np.concatenate(ys), h
+
+
+def moe_route_reference(logits, k, kind="softmax", bias=None, scale=1.0, norm=True, groups=None, slot=None):
+    """The router's picks and weights in float64 (moe8.py:1256-1286): logits float32 [R, E] numpy -> (ids [R, k] int64, w
+    [R, k] float64). softmax: the top k by logit, the softmax over the k. sigmoid: the top k by sigmoid + bias (without a
+    bias by logit), the picks' sigmoids over their sum (norm False: as they are). The lower id first among equal keys.
+    groups (n_group, topk_group): a group's score the sum of its two largest keys, the topk_group best kept (the lower
+    group first among equal scores), the others out. Weights times scale; slot: an extra column, that id at weight 1."""
+    x = np.asarray(logits, np.float32).astype(np.float64)
+    R, E = x.shape
+    sg = 1.0 / (1.0 + np.exp(-x))
+    key = x.copy() if kind == "softmax" or bias is None else sg + np.asarray(bias, np.float32).astype(np.float64).reshape(1, -1)
+    if kind != "softmax" and groups is not None:
+        ng, tg = groups
+        per = E // ng
+        for r in range(R):
+            score = np.sort(key[r].reshape(ng, per), axis=-1)[:, -2:].sum(-1)
+            best = np.argsort(-score, kind="stable")[:tg]
+            out = np.ones(ng, bool)
+            out[best] = False
+            key[r, np.repeat(out, per)] = -np.inf
+    ids = np.stack([np.argsort(-key[r], kind="stable")[:k] for r in range(R)])
+    if kind == "softmax":
+        v = np.take_along_axis(x, ids, 1)
+        v = np.exp(v - v.max(-1, keepdims=True))
+        w = v / v.sum(-1, keepdims=True)
+    else:
+        w = np.take_along_axis(sg, ids, 1)
+        if norm:
+            w = w / w.sum(-1, keepdims=True)
+    w = w * scale
+    if slot is not None:
+        ids = np.concatenate([ids, np.full((R, 1), int(slot))], 1)
+        w = np.concatenate([w, np.ones((R, 1))], 1)
+    return ids, w

@@ -302,6 +302,126 @@ __global__ void __launch_bounds__(kMoeGroups * (ROWS ? kMoeSplitRows : kMoeSplit
     }
 }
 
+// ---- the router's top k and their weights (moe/moe8.py:1139-1253 route, kernels/moe_route.cpp of the reference). One warp a
+// row: the keys in float64 in shared memory (the reference's core works in fixed point to the same end: picks that equal
+// a float64 host computation's), k rounds of a warp-wide argmax (the larger key, the lower id among equal keys), then the
+// picks' weights in float64, rounded to bf16 once.
+constexpr int kRouteMaxE = 1024;
+
+struct RouteParams {
+    const float* logits;
+    int64_t ld;
+    int E, k, kind, norm, ng, tg, has_slot, ids32;
+    const float* bias;
+    double scale;
+    uint32_t slot;
+    void* ids;
+    int64_t ld_ids;
+    uint16_t* w;
+    int64_t ld_w;
+    uint16_t* shared;
+    int64_t ld_sh;
+};
+
+// (the better of two candidates: key, then the lower index; idx < 0: none)
+__device__ __forceinline__ void route_better(double& key, int& idx, double k2, int i2) {
+    if (i2 >= 0 && (idx < 0 || k2 > key || (k2 == key && i2 < idx))) key = k2, idx = i2;
+}
+__device__ __forceinline__ void route_warp_best(double& key, int& idx) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        const double k2 = __shfl_xor_sync(0xFFFFFFFFu, key, d);
+        const int i2 = __shfl_xor_sync(0xFFFFFFFFu, idx, d);
+        route_better(key, idx, k2, i2);
+    }
+}
+__device__ __forceinline__ uint16_t route_bf16(double v) { return f32_to_bf16_bits((float)v); }
+
+__global__ void __launch_bounds__(32) tkd_moe_route_kernel(const RouteParams p) {
+    __shared__ double skey[kRouteMaxE], ssig[kRouteMaxE];
+    __shared__ uint32_t taken[kRouteMaxE / 32];
+    __shared__ int pick[16];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int row = blockIdx.x, lane = threadIdx.x;
+    const float* lg = p.logits + (int64_t)row * p.ld;
+    const double ninf = -__longlong_as_double(0x7FF0000000000000LL);
+    for (int e = lane; e < p.E; e += 32) {
+        const double x = (double)lg[e];
+        const double sg = 1.0 / (1.0 + exp(-x));
+        ssig[e] = sg;
+        // kind 0: softmax, by logit; 1: sigmoid + bias; 2: sigmoid without a bias, by logit (sigmoid is increasing, and in
+        // float64 it saturates, which would tie logits that differ)
+        skey[e] = p.kind == 1 ? sg + (double)p.bias[e] : x;
+    }
+    if (lane < kRouteMaxE / 32) taken[lane] = 0;
+    __syncwarp();
+    if (p.ng > 1) {
+        // group-limited routing: a group's score is the sum of its two largest keys; the tg best groups stay (the lower
+        // group among equal scores), the others' experts are out
+        const int ge = p.E / p.ng;
+        double score = ninf;
+        if (lane < p.ng) {
+            double a = ninf, b = ninf;
+            for (int i = 0; i < ge; ++i) {
+                const double v = skey[lane * ge + i];
+                if (v > a) b = a, a = v;
+                else if (v > b) b = v;
+            }
+            score = a + b;
+        }
+        uint32_t kept = 0;
+        for (int j = 0; j < p.tg; ++j) {
+            double key = score;
+            int idx = (lane < p.ng && !((kept >> lane) & 1u)) ? lane : -1;
+            route_warp_best(key, idx);
+            if (idx >= 0) kept |= 1u << idx;
+        }
+        for (int wd = lane; wd < p.E / 32; wd += 32) {
+            uint32_t m = 0;
+            for (int b = 0; b < 32; ++b)
+                if (!((kept >> ((wd * 32 + b) / ge)) & 1u)) m |= 1u << b;
+            taken[wd] = m;
+        }
+        __syncwarp();
+    }
+    for (int j = 0; j < p.k; ++j) {
+        double key = 0.0;
+        int idx = -1;
+        for (int e = lane; e < p.E; e += 32)
+            if (!((taken[e >> 5] >> (e & 31)) & 1u)) route_better(key, idx, skey[e], e);
+        route_warp_best(key, idx);
+        if (lane == 0) {
+            pick[j] = idx;
+            if (idx >= 0) taken[idx >> 5] |= 1u << (idx & 31);
+        }
+        __syncwarp();
+    }
+    // the weights: softmax over the picks' logits, or the picks' sigmoids (over their sum unless norm is off), times scale
+    const int id = lane < p.k ? pick[lane] : -1;
+    double v = 0.0;
+    if (p.kind == 0) {
+        const double top = skey[max(pick[0], 0)];
+        if (id >= 0) v = exp(skey[id] - top);
+    } else if (id >= 0) {
+        v = ssig[id];
+    }
+    double sum = v;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+    const double wv = (p.kind == 0 || p.norm ? v / sum : v) * p.scale;
+    const int slots = p.k + p.has_slot;
+    if (lane < slots) {
+        const bool extra = lane == p.k;  // the fixed slot: that id at weight 1
+        const uint32_t out_id = extra ? p.slot : (uint32_t)max(id, 0);
+        if (p.ids32) static_cast<uint32_t*>(p.ids)[(int64_t)row * p.ld_ids + lane] = out_id;
+        else static_cast<uint16_t*>(p.ids)[(int64_t)row * p.ld_ids + lane] = (uint16_t)out_id;
+        p.w[(int64_t)row * p.ld_w + lane] = route_bf16(extra ? 1.0 : (id >= 0 ? wv : 0.0));
+    }
+    if (p.shared && lane == 0) p.shared[(int64_t)row * p.ld_sh] = route_bf16(1.0 / (1.0 + exp(-(double)lg[p.E])));
+}
+
+
 size_t moe_smem(int R, int K, int MT, bool rows) {
     const int Kpad = (K + 63) & ~63, split = rows ? kMoeSplitRows : kMoeSplitOne;
     return (((size_t)R * (Kpad * 2 + (rows ? 64 : 16)) + 15) & ~(size_t)15) +
@@ -448,6 +568,33 @@ int tkd_moe_down(const TkdMoe* a, void* stream) {
     if (!moe_rows_a_pass(a, &p.RB, &mt, &smem)) return TKD_ERR_UNSUPPORTED;
     const dim3 grid((unsigned)moe_grid_x(a, (int)(npad / kMoeCols)), (unsigned)a->slots);
     const int e = moe_dispatch<true>(p, a->by_union != 0, grid, smem, mt, static_cast<cudaStream_t>(stream));
+    return e == 0 ? TKD_OK : TKD_ERR_CUDA + e;
+}
+
+int tkd_moe_route(const float* logits, int64_t ld, int rows, int experts, int k, int kind, const float* bias, double scale,
+                  int norm, int n_group, int topk_group, int has_slot, uint32_t slot, void* ids, int ids32, int64_t ld_ids,
+                  void* w, int64_t ld_w, void* shared, int64_t ld_shared, void* stream) {
+    if (!logits || !ids || !w || rows < 1 || rows > 32 || experts < 32 || experts % 32 || experts > kRouteMaxE) return TKD_ERR_BAD_ARG;
+    if (k < 1 || k > 16 || k > experts || (has_slot && k + 1 > 16) || kind < 0 || kind > 2 || (kind == 1 && !bias)) return TKD_ERR_BAD_ARG;
+    if (!(scale > 0.0 && scale < 4.0) || (!norm && kind == 0)) return TKD_ERR_BAD_ARG;
+    if (ld < experts + (shared ? 1 : 0) || ld_ids < k + (has_slot ? 1 : 0) || ld_w < k + (has_slot ? 1 : 0)) return TKD_ERR_BAD_ARG;
+    if (n_group > 1) {
+        if (kind != 1 || n_group > 32 || experts % n_group || experts / n_group < 2 || topk_group < 1 || topk_group > n_group ||
+            topk_group * (experts / n_group) < k)
+            return TKD_ERR_BAD_ARG;
+    }
+    RouteParams p = {};
+    p.logits = logits, p.ld = ld, p.E = experts, p.k = k, p.kind = kind, p.norm = norm, p.ng = n_group > 1 ? n_group : 1;
+    p.tg = topk_group, p.has_slot = has_slot ? 1 : 0, p.ids32 = ids32, p.bias = bias, p.scale = scale, p.slot = slot;
+    p.ids = ids, p.ld_ids = ld_ids, p.w = static_cast<uint16_t*>(w), p.ld_w = ld_w;
+    p.shared = static_cast<uint16_t*>(shared), p.ld_sh = ld_shared;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)rows), cfg.blockDim = dim3(32), cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    const int e = (int)cudaLaunchKernelEx(&cfg, tkd_moe_route_kernel, p);
     return e == 0 ? TKD_OK : TKD_ERR_CUDA + e;
 }
 }

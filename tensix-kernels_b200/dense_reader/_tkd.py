@@ -76,6 +76,8 @@ SYMBOLS = {
     "tkd_moe_workspace": (c_i32, [ctypes.POINTER(TkdMoe), ctypes.POINTER(c_u64)]),
     "tkd_moe_gate_up": (c_i32, [ctypes.POINTER(TkdMoe), c_vp]),
     "tkd_moe_down": (c_i32, [ctypes.POINTER(TkdMoe), c_vp]),
+    "tkd_moe_route": (c_i32, [c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp, ctypes.c_double, c_i32, c_i32, c_i32, c_i32, c_u32,
+                              c_vp, c_i32, c_i64, c_vp, c_i64, c_vp, c_i64, c_vp]),
     "tkd_topk_merge": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp]),
     "tkd_head_pick": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_i32, c_u32, c_vp, c_i64, c_i32, c_vp, c_i64, c_i32, c_vp, c_vp, c_vp]),
     "tkd_head_pick_records": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_u32, c_vp, c_vp, c_vp, c_vp]),

@@ -16,12 +16,16 @@ The packed weights (pack): every expert's gate|up matrix [H, 2I], its 32-column 
 j), and its down matrix [I, H], each as one bfloat4_b stream of libtkd (csrc/tkd_layout.h), the experts back to back in
 one buffer, so an id finds its expert by a multiplication. The values are rounded to the bfloat4_b grid exactly as
 bfp4_tiles rounds them (values already on the grid stay as they are). Not built here: the K-block layout (kblock=True:
-shared exponents along K) is refused with NotImplementedError, the pack cache (cache=, prepack, pack_cached,
-repack_down) and the router (route, route_reference, sigmoid_table). The Tensix options (cores_per_bank, banks, kw,
-fidelity, cpb, loaders) are accepted and steer nothing.
+shared exponents along K) is refused with NotImplementedError, and so is the pack cache (cache=, prepack, pack_cached,
+repack_down). The Tensix options (cores_per_bank, banks, kw, fidelity, cpb, loaders) are accepted and steer nothing.
+
+- route(logits, ids, w, k): the router's top k and their weights (softmax or sigmoid scoring, a score bias,
+  group-limited routing, a scaling factor, a fixed shared-expert slot) into the ids and weights the other ops read
+  (route :1139-1253, route_reference :1256-1286, sigmoid_table :108-111), one warp a row, keys in float64.
 """
 
 import ctypes
+import math
 
 import numpy as np
 import torch
@@ -306,3 +310,85 @@ def down_rows(h, P, ids, k, rows, *, ids32=False, kw=8, fidelity="hifi2", memory
     assert 1 <= rows <= TILE, rows
     assert P["E"] <= 1024, "moe8 rows: at most 1024 experts"
     return _down(h, P, ids, k, rows, ids32, True, memory_config)
+
+
+# --- the router -------------------------------------------------------------------------------------------------------
+
+
+def sigmoid_table():
+    """sigmoid(i / 16 - 16) for i = 0 .. 512 in Q2.30, rounded: the bounds table of the reference's route kernel
+    (moe8.py:108-111, kernels/moe_sigmoid_q30.h). The kernel here computes in float64 and needs no table; kept for callers
+    that check it."""
+    return [round((1 << 30) / (1.0 + math.exp(16 - i / 16))) for i in range(513)]
+
+
+def route(logits, ids, w, k, *, kind="softmax", bias=None, ids32=False, experts=None, shared=None, scale=1.0, norm=True,
+          groups=None, slot=None):
+    """The router's top k and their weights into ids and w, in place of ttnn.topk and the weights' ops (moe8.py:1139-1253).
+    logits [1, 1, R, W] float32, R <= 32; experts: the first E columns (default all; a multiple of 32); ids [1, 1, R, k]
+    uint16 (uint32 with ids32), w [1, 1, R, k] bf16. Slots in decreasing order of the pick's key, the lower id among equal
+    keys. kind "softmax": the top k by logit, weights the softmax over the k. kind "sigmoid": the top k by sigmoid(logit)
+    + bias (bias [1, 1, 1, E] float32; None: by logit), weights the picks' sigmoids over their sum (norm=False: each its
+    own sigmoid). shared: a [1, 1, R, 1] bf16 that gets sigmoid(logits[:, E]). scale: every weight times it (0 < scale <
+    4). groups=(n_group, topk_group): the sigmoid kind with a bias; a group's score the sum of its two largest keys, the
+    topk_group best groups kept. slot: that id as slot k of every row at weight 1.0 (ids and w hold k + 1). Returns w."""
+    assert kind in ("softmax", "sigmoid"), f"moe8.route: kind {kind!r}"
+    R, W = logits.shape[-2], logits.shape[-1]
+    E = experts or W
+    assert E <= W and (shared is None or E + 1 <= W), (E, W)
+    assert logits.dtype == ttnn.float32, logits.dtype
+    assert R <= 32 and E % TILE == 0 and 1 <= k <= 16, (R, E, k)
+    assert 0 < scale < 4, scale
+    assert norm or kind == "sigmoid", "moe8.route: norm=False is for the sigmoid kind"
+    assert slot is None or (k + 1 <= 16 and 0 <= int(slot) < (1 << 32 if ids32 else 1 << 16)), (k, slot)
+    ng, tg = (1, 1) if groups is None else (int(groups[0]), int(groups[1]))
+    if groups is not None:
+        assert kind == "sigmoid" and bias is not None, "moe8.route: groups need the sigmoid kind with a bias"
+        assert ng <= 32 and E % ng == 0 and E // ng >= 2 and 1 <= tg <= ng and tg * (E // ng) >= k, (E, groups, k)
+    assert ids.dtype == (ttnn.uint32 if ids32 else ttnn.uint16), ids.dtype
+    assert w.dtype == ttnn.bfloat16, w.dtype
+    kk = k + (slot is not None)
+    assert ids.shape[-1] >= kk and w.shape[-1] >= kk and ids.shape[-2] >= R and w.shape[-2] >= R, (ids.shape, w.shape)
+    sig = kind == "sigmoid" and bias is not None
+    if sig:
+        assert bias.dtype == ttnn.float32 and bias.shape[-1] == E, (bias.dtype, bias.shape)
+    if shared is not None:
+        assert shared.dtype == ttnn.bfloat16 and shared.shape[-2] >= R, (shared.dtype, shared.shape)
+    kcode = 0 if kind == "softmax" else (1 if sig else 2)
+    device = logits.device()
+    with torch.cuda.device(device.torch):
+        _tkd.check(
+            _tkd.lib().tkd_moe_route(
+                logits.t.data_ptr(), logits.t.stride(-2), R, E, k, kcode, bias.t.data_ptr() if sig else None, float(scale),
+                int(bool(norm)), ng, tg, int(slot is not None), int(slot or 0), ids.t.data_ptr(), int(ids32), ids.t.stride(-2),
+                w.t.data_ptr(), w.t.stride(-2), shared.t.data_ptr() if shared is not None else None,
+                shared.t.stride(-2) if shared is not None else 0, torch.cuda.current_stream().cuda_stream),
+            "tkd_moe_route")
+    return w
+
+
+def route_reference(logits, k, kind="softmax", bias=None, scale=1.0, norm=True, groups=None, slot=None):
+    """route's result on the host in float64 (moe8.py:1256-1286): (ids [R, k] long, w [R, k] float64) for float32 logits
+    [R, E]. The lower id first among equal keys; groups as route's; slot: an extra column of that id at weight 1."""
+    x = logits.float().double()
+    sg = torch.sigmoid(x)
+    key = x if kind == "softmax" or bias is None else sg + bias.float().double().reshape(1, -1)
+    if kind != "softmax" and groups is not None:
+        ng, tg = groups
+        R, E = key.shape
+        score = key.reshape(R, ng, E // ng).topk(2, dim=-1).values.sum(-1)
+        best = torch.argsort(-score, dim=-1, stable=True)[:, :tg]
+        keep = torch.zeros(R, ng, dtype=torch.bool).scatter_(1, best, True).repeat_interleave(E // ng, dim=1)
+        key = key.masked_fill(~keep, float("-inf"))
+    picks = torch.argsort(-key, dim=-1, stable=True)[:, :k]
+    if kind == "softmax":
+        wt = torch.softmax(x.gather(1, picks), dim=-1)
+    else:
+        wt = sg.gather(1, picks)
+        if norm:
+            wt = wt / wt.sum(-1, keepdim=True)
+    wt = wt * scale
+    if slot is not None:
+        picks = torch.cat([picks, torch.full_like(picks[:, :1], int(slot))], dim=1)
+        wt = torch.cat([wt, torch.ones_like(wt[:, :1])], dim=1)
+    return picks, wt

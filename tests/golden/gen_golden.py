@@ -172,8 +172,26 @@ for act in ("silu", "gelu_tanh", "swiglu_oai"):
     moe_out.update({f"y_{act}": y.numpy(), f"h_{act}": h.numpy(), f"yb_{act}": yb.numpy(), f"hb_{act}": hb.numpy()})
 moe_out["rows_silu"] = moe8.reference_rows(mx.float(), mgu, mdn, mids.tolist(), mw.float(), "silu").numpy()
 moe_out["rows_oai_bias"] = moe8.reference_rows(mx.float(), mgu, mdn, mids.tolist(), mw.float(), "swiglu_oai", mgb).numpy()
+# the router: random rows with ties (every other row rounded to bf16), rows of equal logits, of large and of tiny ones
+gen = torch.Generator().manual_seed(31)
+rl = torch.randn(12, 64, generator=gen) * 3
+rl[::2] = rl[::2].to(torch.bfloat16).float()
+rl[8] = 1.5
+rl[9] = torch.randn(64, generator=gen) * 40
+rl[10] = torch.randn(64, generator=gen) * 1e-6
+rl[11, :10] = 2.5
+rb = torch.randn(64, generator=gen) * 0.1
+route_cases = {
+    "softmax": dict(kind="softmax"), "sigmoid": dict(kind="sigmoid"), "sigmoid_raw": dict(kind="sigmoid", norm=False),
+    "sigmoid_bias": dict(kind="sigmoid", bias=rb),
+    "groups": dict(kind="sigmoid", bias=rb, groups=(8, 3), scale=2.5, slot=64),
+}
+for name, kw in route_cases.items():
+    ri, rw = moe8.route_reference(rl, 6, **kw)
+    moe_out[f"route_ids_{name}"], moe_out[f"route_w_{name}"] = ri.numpy(), rw.numpy()
 np.savez_compressed(
     out / "moe.npz",
+    route_logits=rl.numpy(), route_bias=rb.numpy(), sigmoid_table=np.array(moe8.sigmoid_table(), np.int64),
     gu=mgu.numpy(), dn=mdn.numpy(), gb=mgb.numpy(), x_bits=mx.view(torch.int16).numpy(), ids=mids.numpy(),
     w_bits=mw.view(torch.int16).numpy(), union=np.array(moe8.union(mids, ME), np.int64),
     union_clip=np.array(moe8.union(torch.tensor([[5, 9, 2], [2, 7, 0]]), 6), np.int64),

@@ -1,6 +1,6 @@
 # SPDX-License-Identifier: Apache-2.0
 # Copyright 2026 Xylolabs
-# Ported from XylolabsInc/tensix-kernels, moe/tests/test_moe.py (Apache-2.0): test_decode, test_rows and test_hifi2, their
+# Ported from XylolabsInc/tensix-kernels, moe/tests/test_moe.py (Apache-2.0): test_decode, test_rows, test_hifi2 and test_route, their
 # shapes, seeds and bars are that file's; the imports and the device API under them are this package's. test_bias is that
 # file's test_bias_groups_kblock without the K-block layout (not built here); the tests after it are this package's own.
 """The reference's MoE checks (moe/tests/test_moe.py) against this package's API on a B200: experts on the bfloat4_b
@@ -168,6 +168,80 @@ def test_hifi2(device):
     rows_case(device, gu, dn, P, 32, act="gelu_tanh", seed=3, fid="hifi2")
 
 
+def ulps(a, b):
+    """|a - b| in bf16 ulps of b (bf16 tensors)."""
+    return (a.view(torch.int16).to(torch.int32) - b.view(torch.int16).to(torch.int32)).abs()
+
+
+def edge_rows(e, k, g):
+    """32 rows of logits [32, e] that a range or sign error shows in: all equal, near 0, tiny, large, huge, ties at the
+    k-th place, two values, signs mixed, the rest random."""
+    rows = [
+        torch.zeros(e),
+        torch.full((e,), 1.5),
+        torch.full((e,), -2.0),
+        torch.randn(e, generator=g) * 1e-3,
+        torch.randn(e, generator=g) * 1e-6,
+        torch.randn(e, generator=g) * 40,
+        torch.randn(e, generator=g) * 1e3,
+    ]
+    t = torch.randn(e, generator=g)
+    t[: 2 * k] = 2.5  # 2k equal at the top: the pick is the lowest k ids of them
+    rows.append(t)
+    t = torch.randn(e, generator=g)
+    t[torch.randperm(e, generator=g)[: k + 3]] = 1.25  # ties across the k-th place
+    rows.append(t)
+    rows.append(torch.where(torch.rand(e, generator=g) < 0.5, torch.tensor(-1.0), torch.tensor(1.0)))
+    rows.append(torch.randn(e, generator=g).abs())
+    rows.append(-torch.randn(e, generator=g).abs())
+    while len(rows) < 32:
+        rows.append(torch.randn(e, generator=g) * float(2 ** (len(rows) % 7 - 3)))
+    return torch.stack(rows)
+
+
+def route_case(device, g, name, kind, R, k, ids32=False, bias=False, edge=False, **opts):
+    e = 128
+    lg = edge_rows(e, k, g) if edge else torch.randn(R, e, generator=g) * 3
+    if not edge:
+        lg[::2] = lg[::2].to(BF).float()  # ties in the even rows
+    R = lg.shape[0]
+    tl = dev(device, lg.reshape(1, 1, R, e), ttnn.float32)
+    kk = k + (opts.get("slot") is not None)
+    idt, tdt = (torch.int32, ttnn.uint32) if ids32 else (torch.int16, ttnn.uint16)
+    junk = torch.full((1, 1, R, kk), 7)
+    ti = dev(device, junk.to(idt), tdt)
+    tw = dev(device, junk.to(BF), ttnn.bfloat16)
+    b, tb = None, None
+    if bias:
+        b = torch.randn(e, generator=g) * 0.1
+        tb = dev(device, b.reshape(1, 1, 1, e), ttnn.float32)
+    moe8.route(tl, ti, tw, k, kind=kind, bias=tb, ids32=ids32, **opts)
+    gi = ttnn.to_torch(ti).reshape(R, kk).long() & (0xFFFFFFFF if ids32 else 0xFFFF)
+    gw = ttnn.to_torch(tw).reshape(R, kk).to(BF)
+    ri, rw = moe8.route_reference(lg, k, kind, b, **opts)
+    same(f"route {name}: picks", gi, ri)
+    tol = 2.0**-29 * max(1.0, opts.get("scale", 1.0))
+    bad = (ulps(gw, rw.to(BF)) > 1) & ((gw.double() - rw).abs() > tol)
+    ok = int(bad.sum()) == 0
+    print(f"{'ok  ' if ok else 'FAIL'} route {name}: weights within 1 bf16 ulp or {tol:.0e}: {int(bad.sum())} off")
+    assert ok, name
+
+
+def test_route(device):
+    g = torch.Generator().manual_seed(3)
+    route_case(device, g, "softmax R 1 k 8", "softmax", 1, 8)
+    route_case(device, g, "softmax R 4 k 6 uint32", "softmax", 4, 6, ids32=True)
+    route_case(device, g, "softmax edge rows k 8", "softmax", 32, 8, edge=True)
+    route_case(device, g, "sigmoid + bias R 4 k 8", "sigmoid", 4, 8, bias=True)
+    route_case(device, g, "sigmoid + bias edge rows k 6 uint32", "sigmoid", 32, 6, ids32=True, bias=True, edge=True)
+    route_case(device, g, "sigmoid, no bias, R 4 k 8", "sigmoid", 4, 8)
+    route_case(device, g, "sigmoid, no bias, not normalized, edge rows", "sigmoid", 32, 8, edge=True, norm=False)
+    route_case(
+        device, g, "sigmoid + bias, groups 8/4, scale 2.5, slot", "sigmoid", 8, 8, bias=True,
+        groups=(8, 4), scale=2.5, slot=128,
+    )
+
+
 # ---- this package's own checks
 
 
@@ -228,3 +302,47 @@ def test_rows_many_inputs_in_passes(device):
     ty = moe8.down_rows(th, P, tid, k, R)
     check("rows in passes: h", host(th, oh.shape[1])[:R], torch.from_numpy(oh), rel=REL)
     check("rows in passes: y", host(ty, h)[:R], torch.from_numpy(oy), rel=REL)
+
+
+def test_route_against_the_oracle_and_into_the_layer(device):
+    """The router's picks and weights against the oracle on the golden logits (ties, equal rows, large and tiny logits), the
+    shared expert's gate, and the routed ids and weights driving gate_up and down with nothing read back in between."""
+    import numpy as np
+    from pathlib import Path
+
+    m = np.load(Path(__file__).resolve().parent / "golden" / "moe.npz")
+    lg, rb = torch.from_numpy(m["route_logits"]), torch.from_numpy(m["route_bias"])
+    R, e, k = lg.shape[0], lg.shape[1], 6
+    wide = torch.cat([lg, torch.linspace(-3, 3, R).reshape(R, 1), torch.zeros(R, 31)], 1)  # column e: a shared expert's gate
+    tl = dev(device, wide.reshape(1, 1, R, e + 32), ttnn.float32)
+    tb = dev(device, rb.reshape(1, 1, 1, e), ttnn.float32)
+    for name, kw in (("softmax", dict(kind="softmax")), ("sigmoid_raw", dict(kind="sigmoid", norm=False)),
+                     ("sigmoid_bias", dict(kind="sigmoid", bias=True)),
+                     ("groups", dict(kind="sigmoid", bias=True, groups=(8, 3), scale=2.5, slot=64))):
+        kk = k + ("slot" in kw)
+        ti = dev(device, torch.zeros(1, 1, R, kk, dtype=torch.int16), ttnn.uint16)
+        tw = dev(device, torch.zeros(1, 1, R, kk).to(BF), ttnn.bfloat16)
+        tsh = dev(device, torch.zeros(1, 1, R, 1).to(BF), ttnn.bfloat16)
+        okw = {**kw, "bias": rb.numpy() if kw.get("bias") else None}
+        moe8.route(tl, ti, tw, k, experts=e, shared=tsh, **{**kw, "bias": tb if kw.get("bias") else None})
+        oi, ow = orc.moe_route_reference(lg.numpy(), k, **okw)
+        assert np.array_equal(ttnn.to_torch(ti).reshape(R, kk).long().numpy() & 0xFFFF, oi), name
+        got = ttnn.to_torch(tw).reshape(R, kk).float().numpy()
+        assert np.allclose(got, ow, rtol=2.0**-8, atol=0), name  # (a bf16 rounding)
+        gate = torch.sigmoid(torch.linspace(-3, 3, R).double()).to(BF)
+        assert int(ulps(ttnn.to_torch(tsh).reshape(R).to(BF), gate).max()) <= 1, name
+    # route -> gate_up -> down on the device, against the oracle given the same picks
+    g = torch.Generator().manual_seed(41)
+    gu, dn = experts(17, 0.05, 32, 128, 64)
+    P = moe8.pack(device, gu, dn)
+    x = make_x(1, 18, 128)
+    logits = torch.randn(1, 32, generator=g)
+    tl = dev(device, logits.reshape(1, 1, 1, 32), ttnn.float32)
+    ti = dev(device, torch.zeros(1, 1, 1, 4, dtype=torch.int16), ttnn.uint16)
+    tw = dev(device, torch.zeros(1, 1, 1, 4).to(BF), ttnn.bfloat16)
+    tx = dev(device, x.reshape(1, 1, 1, 128), ttnn.bfloat16)
+    ty = moe8.down(moe8.gate_up(tx, P, ti, moe8.route(tl, ti, tw, 4), 4), P, ti, 4)
+    oi, ow = orc.moe_route_reference(logits.numpy(), 4)
+    wb = torch.from_numpy(ow[0]).to(BF).float().numpy()
+    oy, _ = orc.moe_reference(x.float().numpy(), gu.float().numpy(), dn.float().numpy(), oi[0].tolist(), wb)
+    bf16_close(host(ty, 128)[:1], oy, "routed layer y", tol=2e-2)
