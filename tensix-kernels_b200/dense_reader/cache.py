@@ -41,14 +41,14 @@ def tensor_sum(t):
     return _sha(t.detach().contiguous().cpu().view(torch.uint8).numpy())
 
 
-def write(path, meta, arrays):
-    """The cache directory, whole or absent. arrays: {name: numpy array or None} over ARRAYS."""
+def write(path, meta, arrays, names=ARRAYS):
+    """The cache directory, whole or absent. arrays: {name: numpy array or None} over `names`."""
     path = Path(path)
     tmp = path.with_name(path.name + ".tmp")
     shutil.rmtree(tmp, ignore_errors=True)
     tmp.mkdir(parents=True)
     sums = {}
-    for name in ARRAYS:
+    for name in names:
         a = arrays.get(name)
         if a is not None:
             np.save(tmp / f"{name}.npy", a)

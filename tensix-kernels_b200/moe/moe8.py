@@ -16,8 +16,14 @@ The packed weights (pack): every expert's gate|up matrix [H, 2I], its 32-column 
 j), and its down matrix [I, H], each as one bfloat4_b stream of libtkd (csrc/tkd_layout.h), the experts back to back in
 one buffer, so an id finds its expert by a multiplication. The values are rounded to the bfloat4_b grid exactly as
 bfp4_tiles rounds them (values already on the grid stay as they are). Not built here: the K-block layout (kblock=True:
-shared exponents along K) is refused with NotImplementedError, and so is the pack cache (cache=, prepack, pack_cached,
-repack_down). The Tensix options (cores_per_bank, banks, kw, fidelity, cpb, loaders) are accepted and steer nothing.
+shared exponents along K) is refused with NotImplementedError. The Tensix options (cores_per_bank, banks, kw,
+fidelity, cpb, loaders) are accepted and steer nothing; banks and cores_per_bank are still part of a pack cache's
+identity, as in the reference.
+
+The pack cache (pack(cache=), prepack, pack_cached, repack_down, PackCacheMismatch; moe8.py:278-465, :530-600): a
+directory with meta.json (what was packed), the arrays gu / gu_emax / dn / dn_emax (/ bias) and sums.json (their
+sha256), written whole or not at all; taken only when its meta equals the call's, refused and left alone otherwise.
+prepack needs the GPU (the packer is the GPU's); repack_down only renames the split, which orders nothing here.
 
 - route(logits, ids, w, k): the router's top k and their weights (softmax or sigmoid scoring, a score bias,
   group-limited routing, a scaling factor, a fixed shared-expert slot) into the ids and weights the other ops read
@@ -25,18 +31,26 @@ repack_down). The Tensix options (cores_per_bank, banks, kw, fidelity, cpb, load
 """
 
 import ctypes
+import hashlib
+import json
 import math
+from pathlib import Path
 
 import numpy as np
 import torch
 
 from common import ttnn_like as ttnn
+from common.device import dram_banks
 from dense_reader import _tkd
+from dense_reader import cache as _cache
 
 TILE = 32
 TB = 576  # a bfloat4_b tile: 64 exponent bytes, then 1024 codes of a sign and 3 magnitude bits
 ACTS = {"silu": 0, "gelu_tanh": 1, "swiglu_oai": 2}
 OAI_ALPHA, OAI_LIMIT = 1.702, 7.0
+PACK_VERSION = 1  # the cache's arrays below; a cache of another version (or of another stream layout) is refused
+PackCacheMismatch = _cache.PackCacheMismatch
+_CACHE_ARRAYS = ("gu", "gu_emax", "dn", "dn_emax", "bias")
 
 
 # --- the bfloat4_b grid on the host -----------------------------------------------------------------------------------
@@ -132,19 +146,33 @@ def _pack_experts(device, mats, what):
     return streams, emax
 
 
-def pack(device, gate_up, down, cores_per_bank=3, banks=None, cache=None, gu_bias=None, rebuild=False, kblock=False):
-    """One MoE layer's experts as the packed weights the ops take (moe8.py:507-527). gate_up: [E, H, 2I] float with up
-    in columns 0..I-1 and gate in I..2I-1 ([up | gate]); down: [E, I, H]; gu_bias: [E, 2I] as [up | gate], held in bf16.
-    Returns the dict the ops take ("E", "H", "I", "gu", "dn", "gu_bias", "bytes", ...). cores_per_bank and banks are
-    recorded only."""
-    if kblock:
-        raise NotImplementedError("moe8: the K-block layout (shared exponents along K) has no stream format here")
-    if cache is not None:
-        raise NotImplementedError("moe8: the pack cache is not built here; pass cache=None")
-    gate_up, down = torch.as_tensor(gate_up), torch.as_tensor(down)
+def _clamp_cpb(device, banks, cores_per_bank):
+    g = device.compute_with_storage_grid_size()
+    return max(1, min(cores_per_bank, (g.x * g.y) // banks))
+
+
+def _fingerprint(t):
+    """A cheap identity of a weight tensor for the pack cache: shape, dtype and the sha256 of a strided sample of its
+    values as float32 (one in 2039), so that a cache made from other weights is not taken."""
+    t = torch.as_tensor(t)
+    sample = t.reshape(-1)[::2039].detach().float().cpu().contiguous().numpy()
+    return f"{list(t.shape)}/{t.dtype}/{hashlib.sha256(sample.tobytes()).hexdigest()[:40]}"
+
+
+def _meta(gate_up, down, banks, cpb, gu_bias):
+    E, H, I2 = gate_up.shape
+    meta = {"version": PACK_VERSION, "layout_version": int(_tkd.lib().tkd_layout_version()), "banks": int(banks),
+            "cpb": int(cpb), "E": int(E), "H": int(H), "I": int(I2 // 2), "gate_up": _fingerprint(gate_up),
+            "down": _fingerprint(down)}
+    if gu_bias is not None:
+        meta["gu_bias"] = _fingerprint(gu_bias)
+    return meta
+
+
+def _pack_arrays(device, gate_up, down, gu_bias):
+    """The layer's device arrays: {gu, gu_emax, dn, dn_emax, bias (or None)}."""
     E, H, I2 = gate_up.shape
     I = I2 // 2
-    assert H % TILE == 0 and I % TILE == 0 and tuple(down.shape) == (E, I, H), (gate_up.shape, down.shape)
     gu, gu_emax = _pack_experts(device, _glu_order(gate_up.float(), I), "gate|up")
     dn, dn_emax = _pack_experts(device, down.float(), "down")
     bias = None
@@ -152,15 +180,138 @@ def pack(device, gate_up, down, cores_per_bank=3, banks=None, cache=None, gu_bia
         b = _glu_order(torch.as_tensor(gu_bias).to(torch.bfloat16), I)
         bias = torch.zeros(E, _tkd.lib().tkd_padded_cols(2 * I), dtype=torch.bfloat16, device=device.torch)
         bias[:, : 2 * I] = b.to(device.torch)
+    return {"gu": gu, "gu_emax": gu_emax, "dn": dn, "dn_emax": dn_emax, "bias": bias}
+
+
+def _to_host(arrays):
+    return {n: (None if a is None else (a.view(torch.int16) if a.dtype == torch.bfloat16 else a).cpu().numpy())
+            for n, a in arrays.items()}
+
+
+def _to_device(device, host):
+    out = {n: torch.from_numpy(np.ascontiguousarray(host[n])).to(device.torch) for n in ("gu", "gu_emax", "dn", "dn_emax")}
+    b = host.get("bias")
+    out["bias"] = None if b is None else torch.from_numpy(np.ascontiguousarray(b)).to(device.torch).view(torch.bfloat16)
+    return out
+
+
+def _layer(device, E, H, I, banks, cpb, arrays):
+    """The dict the ops take."""
+    L = _tkd.lib()
+    want = (E, L.tkd_packed_bytes(_tkd.FMT_BFP4, H, 2 * I)), (E, L.tkd_packed_bytes(_tkd.FMT_BFP4, I, H))
+    if (tuple(arrays["gu"].shape), tuple(arrays["dn"].shape)) != want:
+        raise PackCacheMismatch(f"moe8: the packed arrays are {tuple(arrays['gu'].shape)}, {tuple(arrays['dn'].shape)}; this"
+                                f" library packs {E} experts of [{H}, {2 * I}] and [{I}, {H}] into {want}")
     u8 = lambda t: ttnn.Tensor(t, ttnn.uint8, ttnn.ROW_MAJOR_LAYOUT, device, ttnn.DRAM_MEMORY_CONFIG)  # noqa: E731
     return {
-        "E": E, "H": H, "I": I,
-        "banks": banks or device.dram_grid_size().x, "cpb": cores_per_bank,
-        "gu": u8(gu), "gu_emax": gu_emax, "dn": u8(dn), "dn_emax": dn_emax,
-        "gu_bias": bias is not None, "gu_bias_t": bias, "kblock": False,
-        "bytes": gu.numel() + dn.numel() + gu_emax.numel() + dn_emax.numel(),
+        "E": E, "H": H, "I": I, "banks": banks, "cpb": cpb,
+        "gu": u8(arrays["gu"]), "gu_emax": arrays["gu_emax"], "dn": u8(arrays["dn"]), "dn_emax": arrays["dn_emax"],
+        "gu_bias": arrays["bias"] is not None, "gu_bias_t": arrays["bias"], "kblock": False,
+        "bytes": sum(arrays[n].numel() for n in ("gu", "gu_emax", "dn", "dn_emax")),
         "_device": device, "_ws": {},
     }
+
+
+def _check_shapes(gate_up, down, gu_bias, kblock):
+    if kblock:
+        raise NotImplementedError("moe8: the K-block layout (shared exponents along K) has no stream format here")
+    gate_up, down = torch.as_tensor(gate_up), torch.as_tensor(down)
+    E, H, I2 = gate_up.shape
+    I = I2 // 2
+    assert H % TILE == 0 and I % TILE == 0 and tuple(down.shape) == (E, I, H), (gate_up.shape, down.shape)
+    if gu_bias is not None:
+        assert tuple(gu_bias.shape) == (E, 2 * I), (tuple(gu_bias.shape), (E, 2 * I))
+    return gate_up, down, E, H, I
+
+
+def _cached_arrays(device, gate_up, down, banks, cpb, cache, gu_bias, rebuild):
+    """(the layer's device arrays, whether they were packed now): from the cache when its meta matches; packed and
+    written when there is none (or with rebuild); a cache that differs raises PackCacheMismatch and is left alone."""
+    if cache is None:
+        return _pack_arrays(device, gate_up, down, gu_bias), True
+    meta = _meta(gate_up, down, banks, cpb, gu_bias)
+    host = _cache.read(cache, meta, rebuild=rebuild)
+    if host is not None:
+        return _to_device(device, host), False
+    arrays = _pack_arrays(device, gate_up, down, gu_bias)
+    _cache.write(cache, meta, _to_host(arrays), names=_CACHE_ARRAYS)
+    return arrays, True
+
+
+def pack(device, gate_up, down, cores_per_bank=3, banks=None, cache=None, gu_bias=None, rebuild=False, kblock=False):
+    """One MoE layer's experts as the packed weights the ops take (moe8.py:507-527). gate_up: [E, H, 2I] float with up
+    in columns 0..I-1 and gate in I..2I-1 ([up | gate]); down: [E, I, H]; gu_bias: [E, 2I] as [up | gate], held in bf16.
+    Returns the dict the ops take ("E", "H", "I", "gu", "dn", "gu_bias", "bytes", ...). cores_per_bank and banks are
+    recorded only. cache: a directory for this layer's packed arrays: taken when its meta matches (the versions, the
+    banks and cores, the shapes and a fingerprint of the weights), made when absent or empty; a cache that differs
+    raises PackCacheMismatch and is left as it is, unless rebuild=True, which packs again over it."""
+    gate_up, down, E, H, I = _check_shapes(gate_up, down, gu_bias, kblock)
+    banks = banks or dram_banks(device)
+    cpb = _clamp_cpb(device, banks, cores_per_bank)
+    arrays, _ = _cached_arrays(device, gate_up, down, banks, cpb, cache, gu_bias, rebuild)
+    return _layer(device, E, H, I, banks, cpb, arrays)
+
+
+def prepack(gate_up, down, cache, banks, cores_per_bank=3, gu_bias=None, rebuild=False, kblock=False, device=None):
+    """pack()'s arrays into its cache (moe8.py:423-432): the cache pack(..., cache=) or pack_cached then takes. True when it
+    was made, False when the cache already held these weights; a cache that differs raises PackCacheMismatch unless
+    rebuild=True. Unlike the reference's it needs a GPU (device, default device 0): the packer is the GPU's."""
+    gate_up, down, _, _, _ = _check_shapes(gate_up, down, gu_bias, kblock)
+    device = device or ttnn.open_device(0)
+    return _cached_arrays(device, gate_up, down, banks, cores_per_bank, cache, gu_bias, rebuild)[1]
+
+
+def pack_cached(device, cache, cores_per_bank=3, banks=None, kblock=False, gu_bias=None, verify=True):
+    """pack()'s result from a pack cache alone, without the weights (moe8.py:530-600). The call must match the cache's meta:
+    the versions, the banks and cores per bank (clamped to the device as pack() does), and the bias: gu_bias None (the
+    cache has none), True (it has one) or the [E, 2I] tensor itself (its fingerprint must equal the cache's). verify:
+    every array's sha256 against sums.json. Anything that differs raises PackCacheMismatch, and nothing is changed."""
+    if kblock:
+        raise NotImplementedError("moe8: the K-block layout (shared exponents along K) has no stream format here")
+    path = Path(cache)
+    try:
+        meta = json.loads((path / "meta.json").read_text())
+        sums = json.loads((path / "sums.json").read_text()) if verify else None
+    except (OSError, ValueError) as e:
+        raise PackCacheMismatch(f"moe8 pack cache {path}: no readable meta.json / sums.json ({type(e).__name__})") from e
+    banks = banks or dram_banks(device)
+    cpb = _clamp_cpb(device, banks, cores_per_bank)
+    want = {"version": PACK_VERSION, "layout_version": int(_tkd.lib().tkd_layout_version()), "banks": banks, "cpb": cpb,
+            "a bias": gu_bias is not None}
+    have = {"version": meta.get("version"), "layout_version": meta.get("layout_version"), "banks": meta.get("banks"),
+            "cpb": meta.get("cpb"), "a bias": "gu_bias" in meta}
+    diff = [f"{k}: cache {have[k]}, call {want[k]}" for k in want if want[k] != have[k]]
+    if gu_bias is not None and gu_bias is not True and "gu_bias" in meta and _fingerprint(gu_bias) != meta["gu_bias"]:
+        diff.append("the bias's fingerprint")
+    if diff:
+        raise PackCacheMismatch(f"moe8 pack cache {path} does not match this call ({'; '.join(diff)}). It was not taken.")
+    host = {}
+    for n in _CACHE_ARRAYS:
+        if n == "bias" and "gu_bias" not in meta:
+            continue
+        try:
+            host[n] = np.load(path / f"{n}.npy")
+        except (OSError, ValueError) as e:
+            raise PackCacheMismatch(f"moe8 pack cache {path}: {n}.npy cannot be read ({type(e).__name__})") from e
+        if verify and sums.get(n) != _cache._sha(host[n]):
+            raise PackCacheMismatch(f"moe8 pack cache {path}: {n}.npy differs from sums.json. It was not taken.")
+    return _layer(device, meta["E"], meta["H"], meta["I"], banks, cpb, _to_device(device, host))
+
+
+def repack_down(cache, cores_per_bank=2):
+    """A pack cache moved to another number of cores per bank, without the weights (moe8.py:379-420). There the split
+    orders down's tiles; here the arrays do not depend on it, so only the cache's meta changes, and the result equals a
+    fresh pack at cores_per_bank, its meta too. True when it was converted, False when the cache already has that split."""
+    path = Path(cache) / "meta.json"
+    meta = json.loads(path.read_text())
+    assert meta["version"] == PACK_VERSION, (cache, meta["version"], PACK_VERSION)
+    if meta["cpb"] == cores_per_bank:
+        return False
+    meta["cpb"] = int(cores_per_bank)
+    tmp = path.with_name("meta.json.tmp")
+    tmp.write_text(json.dumps(meta, indent=1, sort_keys=True))
+    tmp.replace(path)
+    return True
 
 
 # --- references -------------------------------------------------------------------------------------------------------

@@ -95,7 +95,7 @@ def test_what_is_not_built_is_refused():
     with pytest.raises(NotImplementedError):
         moe8.pack(None, gu, dn, kblock=True)
     with pytest.raises(NotImplementedError):
-        moe8.pack(None, gu, dn, cache="/nowhere")
+        moe8.pack_cached(None, "/nowhere", kblock=True)
     assert moe8._glu_order(torch.arange(128.0).reshape(1, 128), 64)[0, :64].tolist() == [
         *range(64, 96), *range(0, 32)]  # gate tile 0 (columns I ..), then up tile 0
 
@@ -118,3 +118,68 @@ def test_route_reference_and_sigmoid_table_match_the_reference(m):
         assert np.array_equal(oi, m[f"route_ids_{name}"]), name
         assert np.allclose(ow, m[f"route_w_{name}"], rtol=1e-12, atol=0), name
     assert moe8.sigmoid_table() == m["sigmoid_table"].tolist()
+
+
+class HostDevice:
+    """What the cache functions ask of a device, over host memory (no kernel is launched by pack_cached)."""
+
+    torch = torch.device("cpu")
+
+    def dram_grid_size(self):
+        from common import ttnn_like as ttnn
+        return ttnn.Grid(8, 1)
+
+    def compute_with_storage_grid_size(self):
+        from common import ttnn_like as ttnn
+        return ttnn.Grid(148, 1)
+
+
+def test_pack_cache_identity_and_refusals(tmp_path):
+    """A cache directory written by the package's own writer, read back through pack_cached: taken when the call matches
+    its meta, refused (and left alone) for another split, another layout version, a changed array, a missing bias;
+    repack_down renames the split."""
+    import json
+
+    from dense_reader import _tkd
+    from dense_reader import cache as wcache
+
+    L = _tkd.lib()
+    E, H, I = 3, 64, 32
+    g = torch.Generator().manual_seed(5)
+    gu, dn = torch.randn(E, H, 2 * I, generator=g), torch.randn(E, I, H, generator=g)
+    dev = HostDevice()
+    meta = moe8._meta(gu, dn, 8, 3, None)
+    assert meta["gate_up"] != moe8._meta(gu + 1, dn, 8, 3, None)["gate_up"]
+    arrays = {"gu": np.arange(E * L.tkd_packed_bytes(1, H, 2 * I), dtype=np.int64).astype(np.uint8).reshape(E, -1),
+              "gu_emax": np.full((E, L.tkd_padded_cols(2 * I) // 16), 120, np.uint8),
+              "dn": np.ones((E, L.tkd_packed_bytes(1, I, H)), np.uint8),
+              "dn_emax": np.full((E, L.tkd_padded_cols(H) // 16), 121, np.uint8), "bias": None}
+    cache = tmp_path / "layer0"
+    wcache.write(cache, meta, arrays, names=moe8._CACHE_ARRAYS)
+    P = moe8.pack_cached(dev, cache)
+    assert (P["E"], P["H"], P["I"], P["cpb"], P["banks"], P["gu_bias"]) == (E, H, I, 3, 8, False)
+    assert np.array_equal(P["gu"].t.numpy(), arrays["gu"]) and np.array_equal(P["dn_emax"].numpy(), arrays["dn_emax"])
+    before = sorted(p.name for p in cache.iterdir())
+    with pytest.raises(moe8.PackCacheMismatch, match="cpb"):
+        moe8.pack_cached(dev, cache, cores_per_bank=1)
+    with pytest.raises(moe8.PackCacheMismatch, match="a bias"):
+        moe8.pack_cached(dev, cache, gu_bias=True)
+    assert moe8.repack_down(cache, cores_per_bank=1) is True and moe8.repack_down(cache, cores_per_bank=1) is False
+    assert moe8.pack_cached(dev, cache, cores_per_bank=1)["cpb"] == 1
+    assert json.loads((cache / "meta.json").read_text()) == moe8._meta(gu, dn, 8, 1, None)  # a fresh pack's meta at that split
+    # a changed array is caught by its checksum (and taken unchecked only on request)
+    bad = arrays["dn"].copy()
+    bad[1, 7] ^= 1
+    np.save(cache / "dn.npy", bad)
+    with pytest.raises(moe8.PackCacheMismatch, match="dn.npy"):
+        moe8.pack_cached(dev, cache, cores_per_bank=1)
+    assert moe8.pack_cached(dev, cache, cores_per_bank=1, verify=False)["dn"].t[1, 7] == bad[1, 7]
+    # another stream layout
+    m2 = json.loads((cache / "meta.json").read_text())
+    m2["layout_version"] += 1
+    (cache / "meta.json").write_text(json.dumps(m2))
+    with pytest.raises(moe8.PackCacheMismatch, match="layout_version"):
+        moe8.pack_cached(dev, cache, cores_per_bank=1, verify=False)
+    assert sorted(p.name for p in cache.iterdir()) == before
+    with pytest.raises(moe8.PackCacheMismatch):
+        moe8.pack_cached(dev, tmp_path / "nothing")

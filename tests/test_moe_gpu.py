@@ -1,6 +1,6 @@
 # SPDX-License-Identifier: Apache-2.0
 # Copyright 2026 Xylolabs
-# Ported from XylolabsInc/tensix-kernels, moe/tests/test_moe.py (Apache-2.0): test_decode, test_rows, test_hifi2 and test_route, their
+# Ported from XylolabsInc/tensix-kernels, moe/tests/test_moe.py (Apache-2.0): test_decode, test_rows, test_hifi2, test_route and test_pack_cache, their
 # shapes, seeds and bars are that file's; the imports and the device API under them are this package's. test_bias is that
 # file's test_bias_groups_kblock without the K-block layout (not built here); the tests after it are this package's own.
 """The reference's MoE checks (moe/tests/test_moe.py) against this package's API on a B200: experts on the bfloat4_b
@@ -9,13 +9,17 @@ grid, x with a few outlier channels; gate_up's h and down's y against a float64 
 own experts, rows past R zero. Then parity with the CPU oracle and the edge cases: an id past the experts, repeated
 calls on one workspace, a ragged shape."""
 
+import shutil
+import tempfile
+from pathlib import Path
+
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
 
 from common import ttnn_like as ttnn  # noqa: E402
-from common.testing import check, same  # noqa: E402
+from common.testing import check, raises, same  # noqa: E402
 from moe import moe8  # noqa: E402
 from oracle import oracle as orc  # noqa: E402
 
@@ -240,6 +244,38 @@ def test_route(device):
         device, g, "sigmoid + bias, groups 8/4, scale 2.5, slot", "sigmoid", 8, 8, bias=True,
         groups=(8, 4), scale=2.5, slot=128,
     )
+
+
+def test_pack_cache(device):
+    gu, dn = experts(9)
+    banks = moe8.dram_banks(device)
+    tmp = Path(tempfile.mkdtemp(prefix="moe8-cache-"))
+    try:
+        cache = tmp / "layer0"
+        cpb = moe8._clamp_cpb(device, banks, 3)  # (pack's cores a bank on this grid)
+        assert moe8.prepack(gu, dn, cache, banks, cpb) is True
+        assert moe8.prepack(gu, dn, cache, banks, cpb) is False  # already there
+        ids, wts, x, tid, twt, tx = decode_inputs(device, 8)
+        P0 = moe8.pack(device, gu, dn)
+        P1 = moe8.pack_cached(device, cache)
+        h0, h1 = moe8.gate_up(tx, P0, tid, twt, K), moe8.gate_up(tx, P1, tid, twt, K)
+        same("pack_cached against pack: h", host(h1, K * I), host(h0, K * I))
+        same("pack_cached against pack: y", host(moe8.down(h1, P1, tid, K), H), host(moe8.down(h0, P0, tid, K), H))
+        other = experts(10)
+        raises("a cache of other weights", moe8.PackCacheMismatch, lambda: moe8.prepack(*other, cache, banks, cpb))
+        raises("a cache of another split", moe8.PackCacheMismatch, lambda: moe8.pack_cached(device, cache, cores_per_bank=1))
+        assert moe8.repack_down(cache, cores_per_bank=1) is True
+        P2 = moe8.pack_cached(device, cache, cores_per_bank=1)
+        P3 = moe8.pack(device, gu, dn, cores_per_bank=1)
+        same("repack_down against a fresh pack: y", host(moe8.down(h0, P2, tid, K), H), host(moe8.down(h0, P3, tid, K), H))
+        # (this package's addition) pack(cache=) takes the directory too, and rebuild=True packs over other weights' cache
+        P4 = moe8.pack(device, gu, dn, cores_per_bank=1, cache=cache)
+        same("pack(cache=) against pack: y", host(moe8.down(h0, P4, tid, K), H), host(moe8.down(h0, P3, tid, K), H))
+        moe8.pack(device, *other, cores_per_bank=1, cache=cache, rebuild=True)
+        raises("the cache now holds the other weights", moe8.PackCacheMismatch,
+               lambda: moe8.pack(device, gu, dn, cores_per_bank=1, cache=cache))
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
 
 
 # ---- this package's own checks
