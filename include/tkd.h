@@ -224,7 +224,7 @@ int tkd_hadamard(const void* x, int64_t ldx, const uint32_t* signs, int rows, in
  * experts' weights are read, and the expert ids are read on the device: nothing goes to the host. ------------------- */
 
 typedef struct {
-    const void* w;           /* every expert's packed stream, TKD_FMT_BFP4, expert e at e * expert_bytes: tkd_pack of
+    const void* w;           /* every expert's packed stream (fmt), expert e at e * expert_bytes: tkd_pack of
                                 the expert's [k_in, n] weight. gate_up: n = 2 I columns in the GLU's tile order (32 gate
                                 columns, then their 32 up columns: interleave_glu, dense_reader/linear.py:122-130);
                                 down: [I, H] */
@@ -255,6 +255,9 @@ typedef struct {
     int64_t ldo;
     void* workspace;         /* down: tkd_moe_workspace bytes, zeroed once by the caller before the first use */
     uint64_t workspace_bytes;
+    int32_t fmt;             /* TKD_FMT_BFP4, or TKD_FMT_BF16: experts whose values no bfloat4_b stream holds (the K-block
+                                layout, moe8.py:507-527 kblock: shared exponents along K), kept exactly at 2 bytes a weight;
+                                emax is then unused */
 } TkdMoe;
 
 int tkd_moe_workspace(const TkdMoe* a, uint64_t* bytes);

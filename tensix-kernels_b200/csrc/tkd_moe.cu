@@ -75,11 +75,13 @@ __device__ __forceinline__ float moe_glu(float gt, float u, int act) {
     return act_gate(gt, act) * u;
 }
 
-// MT: tiles of 8 rows. ROWS: by_union. DOWN: the down matmul.
-template <int MT, bool ROWS, bool DOWN>
+// FMT: the experts' stream format (bfloat4_b, or bf16 for a pack held exactly). MT: tiles of 8 rows. ROWS: by_union. DOWN:
+// the down matmul.
+template <int FMT, int MT, bool ROWS, bool DOWN>
 __global__ void __launch_bounds__(kMoeGroups * (ROWS ? kMoeSplitRows : kMoeSplitOne) * 32, ROWS ? 1 : 4)
     tkd_moe_kernel(const MoeParams p) {
     constexpr int kMoeSplit = ROWS ? kMoeSplitRows : kMoeSplitOne, kMoeThreads = kMoeGroups * kMoeSplit * 32;
+    using F = Fmt<FMT>;  // (k and bytes of a super-atom, super-atoms of a group in a chunk)
     extern __shared__ __align__(16) uint8_t moe_dsm[];
     __shared__ uint32_t bm[32];  // ROWS: a bit per expert some row chose
     __shared__ float wrow[32];   // ROWS: row r's routing weight for this CTA's expert (0: not chosen)
@@ -157,8 +159,8 @@ __global__ void __launch_bounds__(kMoeGroups * (ROWS ? kMoeSplitRows : kMoeSplit
     // going through the units in the same order the last stayed last: 908 us against 407 for 32 rows of 8 experts.)
     const int nmine = (nunits - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x, urot = ROWS ? q : 0;
     const uint8_t* wb = p.w + (int64_t)max(e, 0) * p.wbytes;
-    const uint8_t* emx = p.emax + (int64_t)max(e, 0) * (p.npad / 16);
-    const int nsa = Kpad / 64, per = (nsa + kMoeSplit - 1) / kMoeSplit;
+    const uint8_t* emx = FMT == TKD_BFP4 ? p.emax + (int64_t)max(e, 0) * (p.npad / 16) : nullptr;
+    const int nsa = (p.K + F::KSA - 1) / F::KSA, per = (nsa + kMoeSplit - 1) / kMoeSplit;
     const int sa0 = ksp * per, sa1 = min(nsa, sa0 + per);
     const uint2 sh = make_uint2(p.mul16, p.mul128);
     // The first unit's super-atoms of this warp are asked into L2 at once (one instruction per run inside a chunk), so
@@ -166,9 +168,9 @@ __global__ void __launch_bounds__(kMoeGroups * (ROWS ? kMoeSplitRows : kMoeSplit
     if (e >= 0 && lane == 0 && nmine > 0) {
         const int u = blockIdx.x + urot % nmine * gridDim.x, group = DOWN ? u * kMoeGroups + gi : (u >> 1) * 4 + 2 * gi + (u & 1);
         for (int sa = sa0; sa < sa1;) {
-            const int end = min(sa1, (sa | 7) + 1);
-            const uint8_t* s = wb + tkd_sa_offset(TKD_BFP4, p.K, group, sa);
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(s), "r"((end - sa) * Fmt<TKD_BFP4>::SAB) : "memory");
+            const int end = min(sa1, (sa | (F::SUBSA - 1)) + 1);
+            const uint8_t* s = wb + tkd_sa_offset(FMT, p.K, group, sa);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(s), "r"((end - sa) * F::SAB) : "memory");
             sa = end;
         }
     }
@@ -207,22 +209,36 @@ __global__ void __launch_bounds__(kMoeGroups * (ROWS ? kMoeSplitRows : kMoeSplit
 #pragma unroll
                     for (int b = 0; b < kMoeBatch; ++b)
                         if (sa + b < sa1) {
-                            s = (b == 0 && sa == sa0) || ((sa + b) & 7) == 0 ? wb + tkd_sa_offset(TKD_BFP4, p.K, group, sa + b)
-                                                                             : s + Fmt<TKD_BFP4>::SAB;
-                            ev[b] = ldg_stream(s + t * 16);
-                            cv[b] = ldg_stream(s + 64 + lane * 16);
+                            s = (b == 0 && sa == sa0) || ((sa + b) & (F::SUBSA - 1)) == 0 ? wb + tkd_sa_offset(FMT, p.K, group, sa + b)
+                                                                                          : s + F::SAB;
+                            if constexpr (FMT == TKD_BFP4) {
+                                ev[b] = ldg_stream(s + t * 16);
+                                cv[b] = ldg_stream(s + 64 + lane * 16);
+                            } else {  // (bf16: the A fragments of the super-atom's two mmas as they are)
+                                cv[b] = ldg_stream(s + lane * 16);
+                                ev[b] = ldg_stream(s + 512 + lane * 16);
+                            }
                         }
 #pragma unroll
                     for (int b = 0; b < kMoeBatch; ++b)
                         if (sa + b < sa1) {
+                            if constexpr (FMT == TKD_BFP4) {
 #pragma unroll
-                            for (int qq = 0; qq < 2; ++qq) {
-                                const uint32_t cw[4] = {qq ? cv[b].z : cv[b].x, qq ? cv[b].w : cv[b].y, 0u, 0u};
-                                const uint32_t ew[2] = {qq ? ev[b].z : ev[b].x, qq ? ev[b].w : ev[b].y};
-                                uint4 xv[MT];
+                                for (int qq = 0; qq < 2; ++qq) {
+                                    const uint32_t cw[4] = {qq ? cv[b].z : cv[b].x, qq ? cv[b].w : cv[b].y, 0u, 0u};
+                                    const uint32_t ew[2] = {qq ? ev[b].z : ev[b].x, qq ? ev[b].w : ev[b].y};
+                                    uint4 xv[MT];
 #pragma unroll
-                                for (int m = 0; m < MT; ++m) xv[m] = lds128(xa[m] + (uint32_t)(sa + b) * 128 + 64 * qq);
-                                block_mma<TKD_BFP4, MT, 2>(acc, cw, ew, xv, sh);
+                                    for (int m = 0; m < MT; ++m) xv[m] = lds128(xa[m] + (uint32_t)(sa + b) * 128 + 64 * qq);
+                                    block_mma<TKD_BFP4, MT, 2>(acc, cw, ew, xv, sh);
+                                }
+                            } else {
+#pragma unroll
+                                for (int m = 0; m < MT; ++m) {
+                                    const uint4 xv = lds128(xa[m] + (uint32_t)(sa + b) * 64);
+                                    mma_bf16(acc[0][m], cv[b].x, cv[b].y, cv[b].z, cv[b].w, xv.x, xv.y);
+                                    mma_bf16(acc[1][m], ev[b].x, ev[b].y, ev[b].z, ev[b].w, xv.z, xv.w);
+                                }
                             }
                         }
                 }
@@ -241,7 +257,8 @@ __global__ void __launch_bounds__(kMoeGroups * (ROWS ? kMoeSplitRows : kMoeSplit
                 float v = 0.f;
 #pragma unroll
                 for (int sp = 0; sp < kMoeSplit; ++sp) v += red[(size_t)(sp * kMoeCols + c) * RP + r];
-                return moe_scale(v, emx[grp]);
+                if constexpr (FMT == TKD_BFP4) v = moe_scale(v, emx[grp]);
+                return v;
             };
             if constexpr (!DOWN) {
                 const int I = p.N / 2, j = u >> 1, hf = u & 1;
@@ -428,9 +445,9 @@ size_t moe_smem(int R, int K, int MT, bool rows) {
            (size_t)split * kMoeCols * (8 * MT + (rows ? 1 : 0)) * sizeof(float);
 }
 
-template <int MT, bool ROWS, bool DOWN>
+template <int FMT, int MT, bool ROWS, bool DOWN>
 int moe_launch(const MoeParams& p, dim3 grid, size_t smem, cudaStream_t st) {
-    auto kern = tkd_moe_kernel<MT, ROWS, DOWN>;
+    auto kern = tkd_moe_kernel<FMT, MT, ROWS, DOWN>;
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -445,24 +462,31 @@ int moe_launch(const MoeParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     return (int)cudaLaunchKernelEx(&cfg, kern, p);
 }
 
-template <bool DOWN>
-int moe_dispatch(const MoeParams& p, bool rows, dim3 grid, size_t smem, int mt, cudaStream_t st) {
-    if (!rows) return moe_launch<1, false, DOWN>(p, grid, smem, st);
+template <int FMT, bool DOWN>
+int moe_dispatch_fmt(const MoeParams& p, bool rows, dim3 grid, size_t smem, int mt, cudaStream_t st) {
+    if (!rows) return moe_launch<FMT, 1, false, DOWN>(p, grid, smem, st);
     switch (mt) {
-        case 1: return moe_launch<1, true, DOWN>(p, grid, smem, st);
-        case 2: return moe_launch<2, true, DOWN>(p, grid, smem, st);
-        case 3: return moe_launch<3, true, DOWN>(p, grid, smem, st);
-        default: return moe_launch<4, true, DOWN>(p, grid, smem, st);
+        case 1: return moe_launch<FMT, 1, true, DOWN>(p, grid, smem, st);
+        case 2: return moe_launch<FMT, 2, true, DOWN>(p, grid, smem, st);
+        case 3: return moe_launch<FMT, 3, true, DOWN>(p, grid, smem, st);
+        default: return moe_launch<FMT, 4, true, DOWN>(p, grid, smem, st);
     }
+}
+template <bool DOWN>
+int moe_dispatch(const MoeParams& p, int fmt, bool rows, dim3 grid, size_t smem, int mt, cudaStream_t st) {
+    return fmt == TKD_BF16 ? moe_dispatch_fmt<TKD_BF16, DOWN>(p, rows, grid, smem, mt, st)
+                           : moe_dispatch_fmt<TKD_BFP4, DOWN>(p, rows, grid, smem, mt, st);
 }
 
 bool moe_args_ok(const TkdMoe* a, bool down) {
-    if (!a || !a->w || !a->emax || !a->x || !a->ids || !a->out) return false;
+    if (!a || !a->w || !a->x || !a->ids || !a->out) return false;
+    if (a->fmt != TKD_FMT_BFP4 && a->fmt != TKD_FMT_BF16) return false;
+    if (a->fmt == TKD_FMT_BFP4 && !a->emax) return false;
     if (a->experts < 1 || a->k_in < 32 || a->k_in % 32 || a->n < 32 || a->n % 32 || a->k < 1 || a->k > 16) return false;
     if (a->rows < 1 || a->rows > 32 || (!a->by_union && a->rows != 1)) return false;
     if (a->by_union && (a->experts > 1024 || a->slots < 1 || a->ld_ids < a->k)) return false;
     if (!a->by_union && a->slots != a->k) return false;
-    if (a->expert_bytes < tkd_packed_bytes(TKD_FMT_BFP4, a->k_in, a->n) || a->expert_bytes % 16) return false;
+    if (a->expert_bytes < tkd_packed_bytes(a->fmt, a->k_in, a->n) || a->expert_bytes % 16) return false;
     if (a->ldx % 8 || (reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->w)) & 15) return false;
     if (down) {
         if (a->ldx < (int64_t)a->slots * a->k_in || a->ldo < a->n) return false;
@@ -550,7 +574,7 @@ int tkd_moe_gate_up(const TkdMoe* a, void* stream) {
     size_t smem = 0;
     if (!moe_rows_a_pass(a, &p.RB, &mt, &smem)) return TKD_ERR_UNSUPPORTED;
     const dim3 grid((unsigned)moe_grid_x(a, a->n / kMoeCols), (unsigned)a->slots);
-    const int e = moe_dispatch<false>(p, a->by_union != 0, grid, smem, mt, static_cast<cudaStream_t>(stream));
+    const int e = moe_dispatch<false>(p, a->fmt, a->by_union != 0, grid, smem, mt, static_cast<cudaStream_t>(stream));
     return e == 0 ? TKD_OK : TKD_ERR_CUDA + e;
 }
 
@@ -567,7 +591,7 @@ int tkd_moe_down(const TkdMoe* a, void* stream) {
     size_t smem = 0;
     if (!moe_rows_a_pass(a, &p.RB, &mt, &smem)) return TKD_ERR_UNSUPPORTED;
     const dim3 grid((unsigned)moe_grid_x(a, (int)(npad / kMoeCols)), (unsigned)a->slots);
-    const int e = moe_dispatch<true>(p, a->by_union != 0, grid, smem, mt, static_cast<cudaStream_t>(stream));
+    const int e = moe_dispatch<true>(p, a->fmt, a->by_union != 0, grid, smem, mt, static_cast<cudaStream_t>(stream));
     return e == 0 ? TKD_OK : TKD_ERR_CUDA + e;
 }
 

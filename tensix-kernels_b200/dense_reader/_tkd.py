@@ -43,7 +43,7 @@ class TkdMoe(ctypes.Structure):
         ("w", c_vp), ("emax", c_vp), ("expert_bytes", c_i64), ("experts", c_i32), ("k_in", c_i32), ("n", c_i32),
         ("rows", c_i32), ("x", c_vp), ("ldx", c_i64), ("ids", c_vp), ("ids32", c_i32), ("k", c_i32), ("ld_ids", c_i64),
         ("route_w", c_vp), ("ld_w", c_i64), ("by_union", c_i32), ("slots", c_i32), ("act", c_i32), ("bias", c_vp),
-        ("out", c_vp), ("ldo", c_i64), ("workspace", c_vp), ("workspace_bytes", c_u64),
+        ("out", c_vp), ("ldo", c_i64), ("workspace", c_vp), ("workspace_bytes", c_u64), ("fmt", c_i32),
     ]
 
 

@@ -15,10 +15,12 @@ is one kernel launch on the current stream and nothing goes to the host, so the 
 The packed weights (pack): every expert's gate|up matrix [H, 2I], its 32-column tiles in the GLU's order (gate j, up
 j), and its down matrix [I, H], each as one bfloat4_b stream of libtkd (csrc/tkd_layout.h), the experts back to back in
 one buffer, so an id finds its expert by a multiplication. The values are rounded to the bfloat4_b grid exactly as
-bfp4_tiles rounds them (values already on the grid stay as they are). Not built here: the K-block layout (kblock=True:
-shared exponents along K) is refused with NotImplementedError. The Tensix options (cores_per_bank, banks, kw,
-fidelity, cpb, loaders) are accepted and steer nothing; banks and cores_per_bank are still part of a pack cache's
-identity, as in the reference.
+bfp4_tiles rounds them (values already on the grid stay as they are). The K-block layout (kblock=True: each 32 x 32
+block held transposed, so the shared exponents run along K in blocks of 16, a GPTQ-along-K export's layout) is rounded
+exactly as bfp4_tiles(kblock=True) rounds it, and its values are then held exactly as a bf16 stream, 2 bytes a weight
+instead of 0.5625: the bfloat4_b stream shares an exponent among 16 columns of one k, which such values do not fit. The
+Tensix options (cores_per_bank, banks, kw, fidelity, cpb, loaders) are accepted and steer nothing; banks and
+cores_per_bank are still part of a pack cache's identity, as in the reference.
 
 The pack cache (pack(cache=), prepack, pack_cached, repack_down, PackCacheMismatch; moe8.py:278-465, :530-600): a
 directory with meta.json (what was packed), the arrays gu / gu_emax / dn / dn_emax (/ bias) and sums.json (their
@@ -146,6 +148,35 @@ def _pack_experts(device, mats, what):
     return streams, emax
 
 
+def _pack_experts_kblock(device, mats, what):
+    """[E, K, N] float -> streams uint8 [E, bytes] of the K-block layout's values: each expert's TRANSPOSE goes through
+    the ordinary quantiser (the 16 values that share an exponent are then 16 consecutive k of one column, as in
+    bfp4_tiles(kblock=True)), and the resulting numbers, each a bf16 value exactly, are packed as a bf16 stream."""
+    L = _tkd.lib()
+    E, k, n = mats.shape
+    kp, npad = L.tkd_padded_cols(k), L.tkd_padded_cols(n)
+    nbytes = L.tkd_packed_bytes(_tkd.FMT_BF16, k, n)
+    st = torch.cuda.current_stream().cuda_stream
+    with torch.cuda.device(device.torch):
+        streams = torch.empty(E, nbytes, dtype=torch.uint8, device=device.torch)
+        exps = torch.empty(n * (kp // 16), dtype=torch.uint8, device=device.torch)
+        codes = torch.empty(n * kp, dtype=torch.uint8, device=device.torch)
+        vt = torch.empty(n, kp, dtype=torch.int16, device=device.torch)
+        vals = torch.zeros(k, npad, dtype=torch.int16, device=device.torch)
+        info = torch.zeros(1, dtype=torch.int32, device=device.torch)
+        for e in range(E):
+            src = mats[e].to(device.torch, torch.float32).T.contiguous()  # [N, K]: a weight of N inputs and K columns
+            _tkd.check(L.tkd_quantise(_tkd.FMT_BFP4, src.data_ptr(), 1, n, k, None, exps.data_ptr(), codes.data_ptr(), st),
+                       "tkd_quantise")
+            _tkd.check(L.tkd_dequantise_bf16(_tkd.FMT_BFP4, n, k, exps.data_ptr(), codes.data_ptr(), vt.data_ptr(), st),
+                       "tkd_dequantise_bf16")
+            vals[:, :n] = vt[:, :k].T
+            _tkd.check(L.tkd_pack(_tkd.FMT_BF16, k, n, None, vals.data_ptr(), streams[e].data_ptr(), None, info.data_ptr(), st),
+                       "tkd_pack")
+        torch.cuda.current_stream().synchronize()
+    return streams, None
+
+
 def _clamp_cpb(device, banks, cores_per_bank):
     g = device.compute_with_storage_grid_size()
     return max(1, min(cores_per_bank, (g.x * g.y) // banks))
@@ -159,22 +190,26 @@ def _fingerprint(t):
     return f"{list(t.shape)}/{t.dtype}/{hashlib.sha256(sample.tobytes()).hexdigest()[:40]}"
 
 
-def _meta(gate_up, down, banks, cpb, gu_bias):
+def _meta(gate_up, down, banks, cpb, gu_bias, kblock=False):
     E, H, I2 = gate_up.shape
     meta = {"version": PACK_VERSION, "layout_version": int(_tkd.lib().tkd_layout_version()), "banks": int(banks),
             "cpb": int(cpb), "E": int(E), "H": int(H), "I": int(I2 // 2), "gate_up": _fingerprint(gate_up),
             "down": _fingerprint(down)}
     if gu_bias is not None:
         meta["gu_bias"] = _fingerprint(gu_bias)
+    if kblock:
+        meta["kblock"] = True
     return meta
 
 
-def _pack_arrays(device, gate_up, down, gu_bias):
-    """The layer's device arrays: {gu, gu_emax, dn, dn_emax, bias (or None)}."""
+def _pack_arrays(device, gate_up, down, gu_bias, kblock=False):
+    """The layer's device arrays: {gu, gu_emax, dn, dn_emax, bias}; the emax arrays are None for a K-block pack (a bf16
+    stream), the bias None without one."""
     E, H, I2 = gate_up.shape
     I = I2 // 2
-    gu, gu_emax = _pack_experts(device, _glu_order(gate_up.float(), I), "gate|up")
-    dn, dn_emax = _pack_experts(device, down.float(), "down")
+    one = _pack_experts_kblock if kblock else _pack_experts
+    gu, gu_emax = one(device, _glu_order(gate_up.float(), I), "gate|up")
+    dn, dn_emax = one(device, down.float(), "down")
     bias = None
     if gu_bias is not None:
         b = _glu_order(torch.as_tensor(gu_bias).to(torch.bfloat16), I)
@@ -189,16 +224,18 @@ def _to_host(arrays):
 
 
 def _to_device(device, host):
-    out = {n: torch.from_numpy(np.ascontiguousarray(host[n])).to(device.torch) for n in ("gu", "gu_emax", "dn", "dn_emax")}
+    out = {n: (None if host.get(n) is None else torch.from_numpy(np.ascontiguousarray(host[n])).to(device.torch))
+           for n in ("gu", "gu_emax", "dn", "dn_emax")}
     b = host.get("bias")
     out["bias"] = None if b is None else torch.from_numpy(np.ascontiguousarray(b)).to(device.torch).view(torch.bfloat16)
     return out
 
 
-def _layer(device, E, H, I, banks, cpb, arrays):
+def _layer(device, E, H, I, banks, cpb, arrays, kblock=False):
     """The dict the ops take."""
     L = _tkd.lib()
-    want = (E, L.tkd_packed_bytes(_tkd.FMT_BFP4, H, 2 * I)), (E, L.tkd_packed_bytes(_tkd.FMT_BFP4, I, H))
+    fmt = _tkd.FMT_BF16 if kblock else _tkd.FMT_BFP4
+    want = (E, L.tkd_packed_bytes(fmt, H, 2 * I)), (E, L.tkd_packed_bytes(fmt, I, H))
     if (tuple(arrays["gu"].shape), tuple(arrays["dn"].shape)) != want:
         raise PackCacheMismatch(f"moe8: the packed arrays are {tuple(arrays['gu'].shape)}, {tuple(arrays['dn'].shape)}; this"
                                 f" library packs {E} experts of [{H}, {2 * I}] and [{I}, {H}] into {want}")
@@ -206,15 +243,13 @@ def _layer(device, E, H, I, banks, cpb, arrays):
     return {
         "E": E, "H": H, "I": I, "banks": banks, "cpb": cpb,
         "gu": u8(arrays["gu"]), "gu_emax": arrays["gu_emax"], "dn": u8(arrays["dn"]), "dn_emax": arrays["dn_emax"],
-        "gu_bias": arrays["bias"] is not None, "gu_bias_t": arrays["bias"], "kblock": False,
-        "bytes": sum(arrays[n].numel() for n in ("gu", "gu_emax", "dn", "dn_emax")),
+        "gu_bias": arrays["bias"] is not None, "gu_bias_t": arrays["bias"], "kblock": bool(kblock), "fmt": fmt,
+        "bytes": sum(arrays[n].numel() for n in ("gu", "gu_emax", "dn", "dn_emax") if arrays[n] is not None),
         "_device": device, "_ws": {},
     }
 
 
-def _check_shapes(gate_up, down, gu_bias, kblock):
-    if kblock:
-        raise NotImplementedError("moe8: the K-block layout (shared exponents along K) has no stream format here")
+def _check_shapes(gate_up, down, gu_bias):
     gate_up, down = torch.as_tensor(gate_up), torch.as_tensor(down)
     E, H, I2 = gate_up.shape
     I = I2 // 2
@@ -224,16 +259,16 @@ def _check_shapes(gate_up, down, gu_bias, kblock):
     return gate_up, down, E, H, I
 
 
-def _cached_arrays(device, gate_up, down, banks, cpb, cache, gu_bias, rebuild):
+def _cached_arrays(device, gate_up, down, banks, cpb, cache, gu_bias, rebuild, kblock=False):
     """(the layer's device arrays, whether they were packed now): from the cache when its meta matches; packed and
     written when there is none (or with rebuild); a cache that differs raises PackCacheMismatch and is left alone."""
     if cache is None:
-        return _pack_arrays(device, gate_up, down, gu_bias), True
-    meta = _meta(gate_up, down, banks, cpb, gu_bias)
+        return _pack_arrays(device, gate_up, down, gu_bias, kblock), True
+    meta = _meta(gate_up, down, banks, cpb, gu_bias, kblock)
     host = _cache.read(cache, meta, rebuild=rebuild)
     if host is not None:
         return _to_device(device, host), False
-    arrays = _pack_arrays(device, gate_up, down, gu_bias)
+    arrays = _pack_arrays(device, gate_up, down, gu_bias, kblock)
     _cache.write(cache, meta, _to_host(arrays), names=_CACHE_ARRAYS)
     return arrays, True
 
@@ -244,21 +279,23 @@ def pack(device, gate_up, down, cores_per_bank=3, banks=None, cache=None, gu_bia
     Returns the dict the ops take ("E", "H", "I", "gu", "dn", "gu_bias", "bytes", ...). cores_per_bank and banks are
     recorded only. cache: a directory for this layer's packed arrays: taken when its meta matches (the versions, the
     banks and cores, the shapes and a fingerprint of the weights), made when absent or empty; a cache that differs
-    raises PackCacheMismatch and is left as it is, unless rebuild=True, which packs again over it."""
-    gate_up, down, E, H, I = _check_shapes(gate_up, down, gu_bias, kblock)
+    raises PackCacheMismatch and is left as it is, unless rebuild=True, which packs again over it. kblock: each 32 x 32
+    block of the weights is rounded with its shared exponents along K (bfp4_tiles(kblock=True)); the values are held
+    exactly, as a bf16 stream (2 bytes a weight)."""
+    gate_up, down, E, H, I = _check_shapes(gate_up, down, gu_bias)
     banks = banks or dram_banks(device)
     cpb = _clamp_cpb(device, banks, cores_per_bank)
-    arrays, _ = _cached_arrays(device, gate_up, down, banks, cpb, cache, gu_bias, rebuild)
-    return _layer(device, E, H, I, banks, cpb, arrays)
+    arrays, _ = _cached_arrays(device, gate_up, down, banks, cpb, cache, gu_bias, rebuild, kblock)
+    return _layer(device, E, H, I, banks, cpb, arrays, kblock)
 
 
 def prepack(gate_up, down, cache, banks, cores_per_bank=3, gu_bias=None, rebuild=False, kblock=False, device=None):
     """pack()'s arrays into its cache (moe8.py:423-432): the cache pack(..., cache=) or pack_cached then takes. True when it
     was made, False when the cache already held these weights; a cache that differs raises PackCacheMismatch unless
     rebuild=True. Unlike the reference's it needs a GPU (device, default device 0): the packer is the GPU's."""
-    gate_up, down, _, _, _ = _check_shapes(gate_up, down, gu_bias, kblock)
+    gate_up, down, _, _, _ = _check_shapes(gate_up, down, gu_bias)
     device = device or ttnn.open_device(0)
-    return _cached_arrays(device, gate_up, down, banks, cores_per_bank, cache, gu_bias, rebuild)[1]
+    return _cached_arrays(device, gate_up, down, banks, cores_per_bank, cache, gu_bias, rebuild, kblock)[1]
 
 
 def pack_cached(device, cache, cores_per_bank=3, banks=None, kblock=False, gu_bias=None, verify=True):
@@ -266,8 +303,6 @@ def pack_cached(device, cache, cores_per_bank=3, banks=None, kblock=False, gu_bi
     the versions, the banks and cores per bank (clamped to the device as pack() does), and the bias: gu_bias None (the
     cache has none), True (it has one) or the [E, 2I] tensor itself (its fingerprint must equal the cache's). verify:
     every array's sha256 against sums.json. Anything that differs raises PackCacheMismatch, and nothing is changed."""
-    if kblock:
-        raise NotImplementedError("moe8: the K-block layout (shared exponents along K) has no stream format here")
     path = Path(cache)
     try:
         meta = json.loads((path / "meta.json").read_text())
@@ -277,9 +312,9 @@ def pack_cached(device, cache, cores_per_bank=3, banks=None, kblock=False, gu_bi
     banks = banks or dram_banks(device)
     cpb = _clamp_cpb(device, banks, cores_per_bank)
     want = {"version": PACK_VERSION, "layout_version": int(_tkd.lib().tkd_layout_version()), "banks": banks, "cpb": cpb,
-            "a bias": gu_bias is not None}
+            "kblock": bool(kblock), "a bias": gu_bias is not None}
     have = {"version": meta.get("version"), "layout_version": meta.get("layout_version"), "banks": meta.get("banks"),
-            "cpb": meta.get("cpb"), "a bias": "gu_bias" in meta}
+            "cpb": meta.get("cpb"), "kblock": bool(meta.get("kblock", False)), "a bias": "gu_bias" in meta}
     diff = [f"{k}: cache {have[k]}, call {want[k]}" for k in want if want[k] != have[k]]
     if gu_bias is not None and gu_bias is not True and "gu_bias" in meta and _fingerprint(gu_bias) != meta["gu_bias"]:
         diff.append("the bias's fingerprint")
@@ -287,7 +322,7 @@ def pack_cached(device, cache, cores_per_bank=3, banks=None, kblock=False, gu_bi
         raise PackCacheMismatch(f"moe8 pack cache {path} does not match this call ({'; '.join(diff)}). It was not taken.")
     host = {}
     for n in _CACHE_ARRAYS:
-        if n == "bias" and "gu_bias" not in meta:
+        if (n == "bias" and "gu_bias" not in meta) or (n.endswith("_emax") and kblock):
             continue
         try:
             host[n] = np.load(path / f"{n}.npy")
@@ -295,7 +330,7 @@ def pack_cached(device, cache, cores_per_bank=3, banks=None, kblock=False, gu_bi
             raise PackCacheMismatch(f"moe8 pack cache {path}: {n}.npy cannot be read ({type(e).__name__})") from e
         if verify and sums.get(n) != _cache._sha(host[n]):
             raise PackCacheMismatch(f"moe8 pack cache {path}: {n}.npy differs from sums.json. It was not taken.")
-    return _layer(device, meta["E"], meta["H"], meta["I"], banks, cpb, _to_device(device, host))
+    return _layer(device, meta["E"], meta["H"], meta["I"], banks, cpb, _to_device(device, host), kblock)
 
 
 def repack_down(cache, cores_per_bank=2):
@@ -373,7 +408,8 @@ def _ids_args(ids, w, rows, k, ids32):
 def _fill(a, P, what, x, ids, w, rows, k, ids32, by_union, slots, out):
     H, I = P["H"], P["I"]
     gu = what == "gu"
-    a.w, a.emax = (P["gu"].t.data_ptr(), P["gu_emax"].data_ptr()) if gu else (P["dn"].t.data_ptr(), P["dn_emax"].data_ptr())
+    em = P["gu_emax"] if gu else P["dn_emax"]
+    a.w, a.emax, a.fmt = (P["gu"] if gu else P["dn"]).t.data_ptr(), (None if em is None else em.data_ptr()), P["fmt"]
     a.expert_bytes = (P["gu"] if gu else P["dn"]).t.shape[1]
     a.experts, a.k_in, a.n = P["E"], (H if gu else I), (2 * I if gu else H)
     a.rows, a.x, a.ldx = rows, x.t.data_ptr(), x.t.stride(-2)

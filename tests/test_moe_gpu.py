@@ -1,8 +1,8 @@
 # SPDX-License-Identifier: Apache-2.0
 # Copyright 2026 Xylolabs
 # Ported from XylolabsInc/tensix-kernels, moe/tests/test_moe.py (Apache-2.0): test_decode, test_rows, test_hifi2, test_route and test_pack_cache, their
-# shapes, seeds and bars are that file's; the imports and the device API under them are this package's. test_bias is that
-# file's test_bias_groups_kblock without the K-block layout (not built here); the tests after it are this package's own.
+# shapes, seeds and bars are that file's; the imports and the device API under them are this package's (test_bias_groups_kblock
+# without its check of gu_groups, a Tensix work split that has no counterpart here). The tests after them are this package's own.
 """The reference's MoE checks (moe/tests/test_moe.py) against this package's API on a B200: experts on the bfloat4_b
 grid, x with a few outlier channels; gate_up's h and down's y against a float64 reference (relative Frobenius error below
 1 %, PCC above 0.9999) for each activation; the inert options and uint32 ids bit for bit; the rows ops with each row's
@@ -30,16 +30,17 @@ REL_HIFI2 = 0.016
 FID = "hifi4"
 
 
-def on_grid(w):
+def on_grid(w, kblock=False):
+    """w's values rounded to BFP4_b as tt-metal rounds them (moe8.bfp4_tiles), as float32 [K, N]."""
     k, n = w.shape
-    v = moe8.bfp4_values(moe8.bfp4_tiles(w))
+    v = moe8.bfp4_values(moe8.bfp4_tiles(w, kblock=kblock), kblock=kblock)  # [KT, NT, 32, 32]
     return torch.from_numpy(v.transpose(0, 2, 1, 3).reshape(k, n).copy())
 
 
-def experts(seed, gu_scale=0.02, e=E, h=H, i=I):
+def experts(seed, gu_scale=0.02, e=E, h=H, i=I, kblock=False):
     g = torch.Generator().manual_seed(seed)
-    gu = torch.stack([on_grid(torch.randn(h, 2 * i, generator=g) * gu_scale).to(BF) for _ in range(e)])
-    dn = torch.stack([on_grid(torch.randn(i, h, generator=g) * 0.02).to(BF) for _ in range(e)])
+    gu = torch.stack([on_grid(torch.randn(h, 2 * i, generator=g) * gu_scale, kblock).to(BF) for _ in range(e)])
+    dn = torch.stack([on_grid(torch.randn(i, h, generator=g) * 0.02, kblock).to(BF) for _ in range(e)])
     return gu, dn
 
 
@@ -100,19 +101,32 @@ def decode_case(device, fid, rel):
             same("y with uint32 ids", host(ty, H)[:1], outs[2][1])
 
 
-def test_bias(device):
-    gu, dn = experts(3, 0.1)
+def test_bias_groups_kblock(device):
+    gu, dn = experts(3, 0.1, kblock=True)
     g = torch.Generator().manual_seed(4)
     gb = torch.randn(E, 2 * I, generator=g) * 0.5
-    P = moe8.pack(device, gu, dn, banks=2, gu_bias=gb)
+    P = moe8.pack(device, gu, dn, banks=2, gu_bias=gb, kblock=True)
     for act in ("swiglu_oai", "silu"):
         ids, wts, x, tid, twt, tx = decode_inputs(device, 5)
         ry, rh = moe8.reference(x.float(), gu, dn, ids.tolist(), wts.float(), act, gb)
         th = moe8.gate_up(tx, P, tid, twt, K, act=act, loaders=2, fidelity=FID)
         ty = moe8.down(th, P, tid, K, loaders=2, fidelity=FID)
-        check(f"{act} with a bias, {FID}: h", host(th, K * I)[:1], rh, rel=REL)
-        check(f"{act} with a bias, {FID}: y", host(ty, H)[:1], ry, rel=REL)
+        check(f"{act} with a bias, column groups and K blocks, {FID}: h", host(th, K * I)[:1], rh, rel=REL)
+        check(f"{act} with a bias, column groups and K blocks, {FID}: y", host(ty, H)[:1], ry, rel=REL)
     rows_case(device, gu, dn, P, 6, act="swiglu_oai", gb=gb, loaders=(1, 2), seed=6)
+
+
+def test_bias(device):
+    """(this package's) the bias on the ordinary layout."""
+    gu, dn = experts(3, 0.1)
+    g = torch.Generator().manual_seed(4)
+    gb = torch.randn(E, 2 * I, generator=g) * 0.5
+    P = moe8.pack(device, gu, dn, gu_bias=gb)
+    ids, wts, x, tid, twt, tx = decode_inputs(device, 5)
+    ry, rh = moe8.reference(x.float(), gu, dn, ids.tolist(), wts.float(), "silu", gb)
+    th = moe8.gate_up(tx, P, tid, twt, K, fidelity=FID)
+    check(f"silu with a bias, {FID}: h", host(th, K * I)[:1], rh, rel=REL)
+    check(f"silu with a bias, {FID}: y", host(moe8.down(th, P, tid, K, fidelity=FID), H)[:1], ry, rel=REL)
 
 
 def rows_inputs(device, R, seed, ids32=False):
@@ -382,3 +396,33 @@ def test_route_against_the_oracle_and_into_the_layer(device):
     wb = torch.from_numpy(ow[0]).to(BF).float().numpy()
     oy, _ = orc.moe_reference(x.float().numpy(), gu.float().numpy(), dn.float().numpy(), oi[0].tolist(), wb)
     bf16_close(host(ty, 128)[:1], oy, "routed layer y", tol=2e-2)
+
+
+def test_kblock_pack_holds_the_host_quantisers_values(device):
+    """A K-block pack of weights that are NOT on the grid holds exactly what bfp4_tiles(kblock=True) makes of them (pinned
+    by the golden vectors), ragged shapes included; and it goes through the cache."""
+    import numpy as np
+    from dense_reader import _tkd
+
+    L = _tkd.lib()
+    e, h, i = 2, 96, 160
+    g = torch.Generator().manual_seed(23)
+    gu = torch.randn(e, h, 2 * i, generator=g) * torch.exp2(torch.randint(-6, 6, (e, h, 1), generator=g).float())
+    dn = torch.randn(e, i, h, generator=g) * 0.05
+    P = moe8.pack(device, gu, dn, kblock=True)
+    assert P["kblock"] and P["fmt"] == _tkd.FMT_BF16 and P["gu_emax"] is None
+    for name, mats, k, n in (("gu", moe8._glu_order(gu, i), h, 2 * i), ("dn", dn, i, h)):
+        for x in range(e):
+            out = torch.empty(k, L.tkd_padded_cols(n), dtype=torch.float32, device=device.torch)
+            _tkd.check(L.tkd_unpack(_tkd.FMT_BF16, k, n, P[name].t[x].data_ptr(), None, out.data_ptr(),
+                                    torch.cuda.current_stream().cuda_stream), "tkd_unpack")
+            want = on_grid(mats[x], kblock=True)
+            assert np.array_equal(out[:, :n].cpu().numpy().view(np.uint32), want.numpy().view(np.uint32)), (name, x)
+    tmp = Path(tempfile.mkdtemp(prefix="moe8-kblock-"))
+    try:
+        P1 = moe8.pack(device, gu, dn, kblock=True, cache=tmp / "l")
+        P2 = moe8.pack_cached(device, tmp / "l", kblock=True)
+        assert torch.equal(P1["gu"].t, P["gu"].t) and torch.equal(P2["dn"].t, P["dn"].t)
+        raises("a K-block cache taken as an ordinary one", moe8.PackCacheMismatch, lambda: moe8.pack_cached(device, tmp / "l"))
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
