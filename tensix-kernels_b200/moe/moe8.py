@@ -1,7 +1,7 @@
 """moe8.py: a mixture-of-experts layer that reads only the chosen experts' weights, on a B200.
 
 Mirrors the reference's moe/moe8.py entry points for the layer's two matmuls: bfp4_tiles :117-154, bfp4_values :157-169,
-pack :507-527, reference :619-636, reference_rows :639-644, union :647-649, u_max :923-925, gate_up :710-817,
+pack :507-527 (pack_host :435-465, pack_upload :468-499), reference :619-636, reference_rows :639-644, union :647-649, u_max :923-925, gate_up :710-817,
 down :820-910, gate_up_rows :928-1037, down_rows :1040-1136. The expert ids are read on the device, as there: every op
 is one kernel launch on the current stream and nothing goes to the host, so the ops can be captured in a CUDA graph.
 
@@ -50,6 +50,9 @@ TILE = 32
 TB = 576  # a bfloat4_b tile: 64 exponent bytes, then 1024 codes of a sign and 3 magnitude bits
 ACTS = {"silu": 0, "gelu_tanh": 1, "swiglu_oai": 2}
 OAI_ALPHA, OAI_LIMIT = 1.702, 7.0
+# The reference's Tensix settings (moe8.py:66-91): module attributes callers may set; they steer nothing here (one work
+# split, one loader), so every value gives the same bits.
+ROWS_SFPU, GU_CPB, GU_ROWS_CPB, LOADERS, ROWS_LOADERS, SPLIT_SHARE = True, 0, 0, 2, 1, 0.5
 PACK_VERSION = 1  # the cache's arrays below; a cache of another version (or of another stream layout) is refused
 PackCacheMismatch = _cache.PackCacheMismatch
 _CACHE_ARRAYS = ("gu", "gu_emax", "dn", "dn_emax", "bias")
@@ -287,6 +290,23 @@ def pack(device, gate_up, down, cores_per_bank=3, banks=None, cache=None, gu_bia
     cpb = _clamp_cpb(device, banks, cores_per_bank)
     arrays, _ = _cached_arrays(device, gate_up, down, banks, cpb, cache, gu_bias, rebuild, kblock)
     return _layer(device, E, H, I, banks, cpb, arrays, kblock)
+
+
+def pack_host(gate_up, down, banks, cores_per_bank=3, cache=None, gu_bias=None, rebuild=False, kblock=False, device=None):
+    """pack()'s arrays in host memory (moe8.py:435-465): a dict of numpy arrays and numbers that pack_upload puts on a
+    device. Unlike the reference's it needs a GPU to make them (device, default device 0): the packer is the GPU's."""
+    gate_up, down, E, H, I = _check_shapes(gate_up, down, gu_bias)
+    arrays, _ = _cached_arrays(device or ttnn.open_device(0), gate_up, down, banks, cores_per_bank, cache, gu_bias, rebuild,
+                               kblock)
+    return {"version": PACK_VERSION, "E": E, "H": H, "I": I, "banks": banks, "cpb": cores_per_bank, "arrays": _to_host(arrays),
+            "gu_bias": gu_bias is not None, "kblock": bool(kblock)}
+
+
+def pack_upload(device, host):
+    """pack_host's dict on the device: the dict the ops take (moe8.py:468-499)."""
+    assert host["version"] == PACK_VERSION, (host["version"], PACK_VERSION)
+    return _layer(device, host["E"], host["H"], host["I"], host["banks"], host["cpb"], _to_device(device, host["arrays"]),
+                  host["kblock"])
 
 
 def prepack(gate_up, down, cache, banks, cores_per_bank=3, gu_bias=None, rebuild=False, kblock=False, device=None):

@@ -283,6 +283,8 @@ def test_pack_cache(device):
         P3 = moe8.pack(device, gu, dn, cores_per_bank=1)
         same("repack_down against a fresh pack: y", host(moe8.down(h0, P2, tid, K), H), host(moe8.down(h0, P3, tid, K), H))
         # (this package's addition) pack(cache=) takes the directory too, and rebuild=True packs over other weights' cache
+        P5 = moe8.pack_upload(device, moe8.pack_host(gu, dn, banks, 1, device=device))
+        same("pack_upload of pack_host against pack: y", host(moe8.down(h0, P5, tid, K), H), host(moe8.down(h0, P3, tid, K), H))
         P4 = moe8.pack(device, gu, dn, cores_per_bank=1, cache=cache)
         same("pack(cache=) against pack: y", host(moe8.down(h0, P4, tid, K), H), host(moe8.down(h0, P3, tid, K), H))
         moe8.pack(device, *other, cores_per_bank=1, cache=cache, rebuild=True)
