@@ -95,6 +95,26 @@ def test_glu_order():
         *range(64, 96), *range(0, 32)]  # gate tile 0 (columns I ..), then up tile 0
 
 
+ROUTE_CASES = {
+    "softmax": dict(kind="softmax"), "sigmoid": dict(kind="sigmoid"), "sigmoid_raw": dict(kind="sigmoid", norm=False),
+    "sigmoid_bias": dict(kind="sigmoid", bias=True), "groups": dict(kind="sigmoid", bias=True, groups=(8, 3), scale=2.5, slot=64),
+}
+
+
+def test_route_reference_and_sigmoid_table_match_the_reference(m):
+    lg, rb = torch.from_numpy(m["route_logits"]), torch.from_numpy(m["route_bias"])
+    for name, kw in ROUTE_CASES.items():
+        kw = {**kw, "bias": rb if kw.get("bias") else None}
+        ids, w = moe8.route_reference(lg, 6, **kw)
+        assert np.array_equal(ids.numpy(), m[f"route_ids_{name}"]), name
+        assert np.allclose(w.numpy(), m[f"route_w_{name}"], rtol=1e-13, atol=0), name
+        okw = {**kw, "bias": None if kw["bias"] is None else rb.numpy()}
+        oi, ow = orc.moe_route_reference(lg.numpy(), 6, **okw)
+        assert np.array_equal(oi, m[f"route_ids_{name}"]), name
+        assert np.allclose(ow, m[f"route_w_{name}"], rtol=1e-12, atol=0), name
+    assert moe8.sigmoid_table() == m["sigmoid_table"].tolist()
+
+
 class HostDevice:
     """What the cache functions ask of a device, over host memory (no kernel is launched by pack_cached)."""
 
