@@ -78,7 +78,7 @@ __device__ __forceinline__ float moe_glu(float gt, float u, int act) {
 // FMT: the experts' stream format (bfloat4_b, or bf16 for a pack held exactly). MT: tiles of 8 rows. ROWS: by_union. DOWN:
 // the down matmul.
 template <int FMT, int MT, bool ROWS, bool DOWN>
-__global__ void __launch_bounds__(kMoeGroups * (ROWS ? kMoeSplitRows : kMoeSplitOne) * 32, ROWS ? 1 : 4)
+__global__ void __launch_bounds__(kMoeGroups * (ROWS ? kMoeSplitRows : kMoeSplitOne) * 32, ROWS ? (MT == 1 ? 2 : 1) : 4)
     tkd_moe_kernel(const MoeParams p) {
     constexpr int kMoeSplit = ROWS ? kMoeSplitRows : kMoeSplitOne, kMoeThreads = kMoeGroups * kMoeSplit * 32;
     using F = Fmt<FMT>;  // (k and bytes of a super-atom, super-atoms of a group in a chunk)
@@ -532,11 +532,11 @@ int moe_sms() {
     return cached;
 }
 // CTAs per slot. One row: a CTA per unit of 32 columns. By union: a CTA keeps the rows' activations in shared memory
-// for several units, and all CTAs of the call are resident at once (one an SM): with a second wave, down's last
+// for several units, and all CTAs of the call are resident at once (one an SM, two up to 8 rows): with a second wave, down's last
 // arrivals at every unit's counter, and with them all the adding up of slots, fall to that wave's CTAs.
 int moe_grid_x(const TkdMoe* a, int nunits) {
     if (!a->by_union) return nunits;
-    const int want = moe_sms() / a->slots;
+    const int want = (a->rows <= 8 ? 2 : 1) * moe_sms() / a->slots;  // (up to 8 rows: two CTAs fit an SM)
     return want < 1 ? 1 : (want > nunits ? nunits : want);
 }
 
