@@ -309,6 +309,8 @@ def main():
                     help="N > 1: weak: every rank streams a whole workload; strong: the one workload's columns are split")
     ap.add_argument("--exchange", choices=["fused", "nccl", "none"], default="fused",
                     help="N > 1: how every rank gets all ranks' outputs (fused: peer stores from the stream kernel)")
+    ap.add_argument("--lanes", type=int, default=4,
+                    help="calls in flight in the end-to-end leg at N = 1 (streams taking the steps in turn; N > 1: two)")
     ap.add_argument("--profile", action="store_true",
                     help="for a profiler: warm-up, then `steps` plain launches (no graph, no e2e, no CPU leg, no JSON line)")
     args = ap.parse_args()
@@ -507,7 +509,7 @@ def main():
     e2e = None
     if case.get("host_step") is not None and not (world > 1 and (args.workload == "c3" or not fused)):
         e2e = end_to_end(args.workload, case, wl, m, device, world, rank, n_total, col_start, copies, min(steps, 300),
-                         warmup, job_bytes, fused)
+                         warmup, job_bytes, fused, args.lanes if world == 1 else min(args.lanes, 2))
     linear.check_status(device)
 
     # ---- what else the metric names, timed in the same run ----
@@ -671,11 +673,15 @@ def check_exchange(name, case, step, join, device, world, rank, m, n_loc, col_st
             "against": "NCCL all-gather of every rank's own result, bit for bit, on every rank"}
 
 
-def end_to_end(name, case, wl, m, device, world, rank, n_total, col_start, copies, e_steps, warmup, job_bytes, fused):
+def end_to_end(name, case, wl, m, device, world, rank, n_total, col_start, copies, e_steps, warmup, job_bytes, fused, nlanes=2):
     """The same metric with the activations and the result in pinned host memory: every step is one library call
-    (tkd_matmul_host: the copy of x to the device, the launch, the copy of the result back), two lanes (stream, staging
+    (tkd_matmul_host: the copy of x to the device, the launch, the copy of the result back), nlanes lanes (stream, staging
     tensors, pinned buffers, workspace; with N > 1 an exchange of its own) taking the steps in turn so that one step's
-    copies overlap the other's kernel. Beside it the latency of one call at a time (the call, then a synchronise)."""
+    copies overlap another's kernel. The calls are independent of each other, so a call's last CTAs (the work split leaves
+    some SMs idle at the end of a launch) run beside the next call's first: with four lanes a step takes less than a
+    launch does in the device-resident figure, where every launch is ordered behind the one before (measured on config 2:
+    21.2 us with two lanes, 18.2 with three, 17.1 with four, 17.9 with six, 20.1 with eight; the launch alone 18.5). Beside
+    it the latency of one call at a time (the call, then a synchronise)."""
     from common import ttnn_like as ttnn
     from dense_reader import linear, sharded
 
@@ -683,7 +689,7 @@ def end_to_end(name, case, wl, m, device, world, rank, n_total, col_start, copie
     out_shape = [1, 1, m, n_total if world > 1 else case["y"].shape[-1]]
     x_pin = case["x_host"].reshape(1, 1, m, wl["k"]).contiguous().pin_memory()
     lanes = []
-    for ln in range(2):
+    for ln in range(nlanes):
         ex = sharded.Exchange(device, 4 << 20) if world > 1 and fused else None
         y = (ex.tensor(out_shape, case["y"].dtype) if ex is not None
              else ttnn.allocate_tensor_on_device(out_shape, case["y"].dtype, ttnn.TILE_LAYOUT, device))
@@ -712,13 +718,13 @@ def end_to_end(name, case, wl, m, device, world, rank, n_total, col_start, copie
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     fork()
     for i in range(max(warmup, 2 * copies)):
-        call(i, lanes[i % 2])
+        call(i, lanes[i % nlanes])
     join()
     _barrier(world)
     fork()
     e0.record()
     for i in range(e_steps):
-        call(i, lanes[i % 2])
+        call(i, lanes[i % nlanes])
     join()
     e1.record()
     torch.cuda.synchronize()
@@ -734,7 +740,7 @@ def end_to_end(name, case, wl, m, device, world, rank, n_total, col_start, copie
     lat_us = _max_over_ranks((time.perf_counter() - t0) / lat_steps * 1e6, world, device)
     linear.check_status(device)
     return {"value": job_bytes * e_steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "us_per_call": e2e_ms * 1e3 / e_steps,
-            "steps": e_steps, "mode": "pipelined x2 (two calls in flight on two streams)",
+            "steps": e_steps, "mode": f"pipelined x{nlanes} ({nlanes} calls in flight on {nlanes} streams)",
             "h2d_bytes_per_step": x_pin.numel() * 2, "d2h_bytes_per_step": lanes[0]["yp"].numel() * lanes[0]["yp"].element_size(),
             "one_call_at_a_time_us": lat_us}
 
