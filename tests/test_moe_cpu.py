@@ -180,3 +180,47 @@ def test_pack_cache_identity_and_refusals(tmp_path):
         moe8.pack_cached(dev, tmp_path / "nothing")
     with pytest.raises(moe8.PackCacheMismatch, match="kblock"):
         moe8.pack_cached(dev, cache, cores_per_bank=1, kblock=True, verify=False)
+
+
+def test_cabi_refuses_bad_requests_before_any_launch():
+    """The entry points check their arguments on the host first: these calls return TKD_ERR_BAD_ARG (1) without a GPU."""
+    import ctypes
+
+    from dense_reader import _tkd
+
+    L = _tkd.lib()
+    buf = (ctypes.c_uint8 * 4096)()
+    addr = (ctypes.addressof(buf) + 15) & ~15
+
+    def moe(**kw):
+        a = _tkd.TkdMoe()
+        a.w, a.emax, a.x, a.ids, a.out, a.route_w = addr, addr, addr, addr, addr, addr
+        a.fmt, a.experts, a.k_in, a.n, a.rows, a.k, a.slots = _tkd.FMT_BFP4, 4, 64, 64, 1, 2, 2
+        a.expert_bytes = L.tkd_packed_bytes(_tkd.FMT_BFP4, 64, 64)
+        a.ldx, a.ldo, a.ld_ids, a.ld_w = 64, 64, 2, 2
+        for k, v in kw.items():
+            setattr(a, k, v)
+        return a
+
+    need = ctypes.c_uint64(0)
+    assert L.tkd_moe_workspace(ctypes.byref(moe(rows=3, by_union=1, slots=4)), ctypes.byref(need)) == 0
+    assert need.value == 256 + 4 * 3 * 128 * 4  # the units' counters, then slots x rows x padded columns of float32
+    for bad in (dict(k=0), dict(k=17), dict(k_in=48), dict(n=48), dict(rows=2), dict(rows=33, by_union=1), dict(fmt=0),
+                dict(slots=3), dict(expert_bytes=16), dict(ldx=60), dict(act=3), dict(emax=None), dict(ids=None),
+                dict(by_union=1, experts=2048, slots=2), dict(x=addr + 2)):
+        assert L.tkd_moe_gate_up(ctypes.byref(moe(**bad)), None) == 1, bad
+    assert L.tkd_moe_gate_up(ctypes.byref(moe(route_w=None)), None) == 1
+    for bad in (dict(ldx=64), dict(ldo=32), dict(k=0)):  # (down: the row of h holds slots x k_in inputs)
+        assert L.tkd_moe_down(ctypes.byref(moe(**bad)), None) == 1, bad
+
+    def route(**kw):
+        args = dict(logits=addr, ld=64, rows=2, experts=64, k=4, kind=0, bias=None, scale=1.0, norm=1, ng=1, tg=1, has_slot=0,
+                    slot=0, ids=addr, ids32=0, ld_ids=4, w=addr, ld_w=4, shared=None, ld_sh=0)
+        args.update(kw)
+        return L.tkd_moe_route(*args.values(), None)
+
+    for bad in (dict(rows=33), dict(experts=48), dict(experts=2048, ld=2048), dict(k=17), dict(k=16, has_slot=1, ld_ids=17, ld_w=17),
+                dict(kind=1), dict(kind=3), dict(scale=4.0), dict(scale=0.0), dict(norm=0), dict(ld=32), dict(ld_ids=3),
+                dict(kind=2, ng=8, tg=2), dict(kind=1, bias=addr, ng=8, tg=9), dict(kind=1, bias=addr, ng=64, tg=1),
+                dict(shared=addr, ld=64)):
+        assert route(**bad) == 1, bad
