@@ -6,11 +6,11 @@
 // Every expert's weight is a bfloat4_b stream of tkd_layout.h (tkd_pack), all experts back to back, so the kernel
 // finds a chosen expert by its id alone: the ids are read on the device and nothing goes to the host. What a call reads
 // is small (k experts of a few MB) and scattered, so instead of the persistent ring of tkd_stream_kernel.cuh this is
-// a plain grid: a CTA owns (32 columns of one slot's expert, all of its K), its 8 warps are 2 groups of 16 columns x 4
+// a plain grid: a CTA owns (32 columns of one slot's expert, all of its K), its 4 warps are 2 groups of 16 columns x 2
 // runs of super-atoms, and a lane loads its own 16 bytes of codes and 16 bytes of exponents of a super-atom straight
 // from global memory into the mma.sync A fragment's registers (the stream is laid out lane by lane, so a warp's load
 // is one contiguous 512 bytes), four super-atoms at a time. The decode is the stream kernel's (block_mma), and like it
-// the kernel is bound by instruction issue, not by HBM: units this small (384 and 512 CTAs of 256 threads for a layer
+// the kernel is bound by instruction issue, not by HBM: units this small (384 and 512 CTAs of 128 threads for a layer
 // of 8 experts of 2048 x 1536) are what spreads that work evenly over the SMs.
 //   gate_up: a unit is 16 columns of a gate tile and the same 16 of its up tile: the CTA finishes 16 outputs,
 //            h = routing weight * act(x G + b) * (x U + b), rounded to bf16 once.
@@ -24,9 +24,12 @@
 namespace {
 
 constexpr int kMoeGroups = 2;  // groups of 16 columns a CTA covers at a time (gate_up: 16 gate columns and their 16 up columns)
-constexpr int kMoeSplitOne = 4;   // warps along K per group: one row (8 warps a CTA, up to four CTAs an SM) ...
-constexpr int kMoeSplitRows = 8;  // ... and by union, where the rows' activations leave room for one CTA an SM: 16 warps
-constexpr int kMoeBatch = 4;   // super-atoms whose loads are issued before the first is used
+// warps along K per group. One row: 2 (4 warps a CTA, four CTAs an SM; with 4 a warp had too few super-atoms to spread its
+// set-up over: the layer of the benchmark 16.9 us, 16.35 with down at 2, 16.8 with gate_up at 2; down at 1: 17.6). By
+// union, where the rows' activations leave room for one or two CTAs an SM: 8 (16 warps).
+constexpr int kMoeSplitOne = 2, kMoeSplitRows = 8;
+__host__ __device__ constexpr int moe_split(bool rows, bool down) { return rows ? kMoeSplitRows : kMoeSplitOne; }
+constexpr int kMoeBatch = 4;  // super-atoms whose loads are issued before the first is used (8: spills, slower)
 constexpr int kMoeCols = kMoeGroups * 16;
 
 struct MoeParams {
@@ -78,9 +81,9 @@ __device__ __forceinline__ float moe_glu(float gt, float u, int act) {
 // FMT: the experts' stream format (bfloat4_b, or bf16 for a pack held exactly). MT: tiles of 8 rows. ROWS: by_union. DOWN:
 // the down matmul.
 template <int FMT, int MT, bool ROWS, bool DOWN>
-__global__ void __launch_bounds__(kMoeGroups * (ROWS ? kMoeSplitRows : kMoeSplitOne) * 32, ROWS ? (MT == 1 ? 2 : 1) : 4)
+__global__ void __launch_bounds__(kMoeGroups * moe_split(ROWS, DOWN) * 32, ROWS ? (MT == 1 ? 2 : 1) : 4)
     tkd_moe_kernel(const MoeParams p) {
-    constexpr int kMoeSplit = ROWS ? kMoeSplitRows : kMoeSplitOne, kMoeThreads = kMoeGroups * kMoeSplit * 32;
+    constexpr int kMoeSplit = moe_split(ROWS, DOWN), kMoeThreads = kMoeGroups * kMoeSplit * 32;
     using F = Fmt<FMT>;  // (k and bytes of a super-atom, super-atoms of a group in a chunk)
     extern __shared__ __align__(16) uint8_t moe_dsm[];
     __shared__ uint32_t bm[32];  // ROWS: a bit per expert some row chose
@@ -439,8 +442,8 @@ __global__ void __launch_bounds__(32) tkd_moe_route_kernel(const RouteParams p) 
 }
 
 
-size_t moe_smem(int R, int K, int MT, bool rows) {
-    const int Kpad = (K + 63) & ~63, split = rows ? kMoeSplitRows : kMoeSplitOne;
+size_t moe_smem(int R, int K, int MT, bool rows, bool down) {
+    const int Kpad = (K + 63) & ~63, split = moe_split(rows, down);
     return (((size_t)R * (Kpad * 2 + (rows ? 64 : 16)) + 15) & ~(size_t)15) +
            (size_t)split * kMoeCols * (8 * MT + (rows ? 1 : 0)) * sizeof(float);
 }
@@ -453,7 +456,7 @@ int moe_launch(const MoeParams& p, dim3 grid, size_t smem, cudaStream_t st) {
         if (e != cudaSuccess) return (int)e;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid, cfg.blockDim = dim3(kMoeGroups * (ROWS ? kMoeSplitRows : kMoeSplitOne) * 32);
+    cfg.gridDim = grid, cfg.blockDim = dim3(kMoeGroups * moe_split(ROWS, DOWN) * 32);
     cfg.dynamicSmemBytes = smem, cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -542,11 +545,11 @@ int moe_grid_x(const TkdMoe* a, int nunits) {
 
 // How many rows a pass of the kernel takes: all of them if their activations fit in shared memory beside the sums,
 // else as many tiles of 8 as fit (then fewer than 8). false: not even one row fits.
-bool moe_rows_a_pass(const TkdMoe* a, int* rb, int* mt, size_t* smem) {
+bool moe_rows_a_pass(const TkdMoe* a, bool down, int* rb, int* mt, size_t* smem) {
     const int64_t limit = (int64_t)moe_smem_limit() - 2048;
     for (int rows = a->rows; rows >= 1; rows = rows > 8 ? ((rows - 1) & ~7) : rows - 1) {
         const int tiles = a->by_union ? (rows + 7) / 8 : 1;
-        const size_t need = moe_smem(rows, a->k_in, tiles, a->by_union != 0);
+        const size_t need = moe_smem(rows, a->k_in, tiles, a->by_union != 0, down);
         if ((int64_t)need <= limit) {
             *rb = rows, *mt = tiles, *smem = need;
             return true;
@@ -572,7 +575,7 @@ int tkd_moe_gate_up(const TkdMoe* a, void* stream) {
     MoeParams p = moe_params(a);
     int mt = 1;
     size_t smem = 0;
-    if (!moe_rows_a_pass(a, &p.RB, &mt, &smem)) return TKD_ERR_UNSUPPORTED;
+    if (!moe_rows_a_pass(a, false, &p.RB, &mt, &smem)) return TKD_ERR_UNSUPPORTED;
     const dim3 grid((unsigned)moe_grid_x(a, a->n / kMoeCols), (unsigned)a->slots);
     const int e = moe_dispatch<false>(p, a->fmt, a->by_union != 0, grid, smem, mt, static_cast<cudaStream_t>(stream));
     return e == 0 ? TKD_OK : TKD_ERR_CUDA + e;
@@ -589,7 +592,7 @@ int tkd_moe_down(const TkdMoe* a, void* stream) {
     p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + (((npad / kMoeCols) * 4 + 255) & ~(int64_t)255));
     int mt = 1;
     size_t smem = 0;
-    if (!moe_rows_a_pass(a, &p.RB, &mt, &smem)) return TKD_ERR_UNSUPPORTED;
+    if (!moe_rows_a_pass(a, true, &p.RB, &mt, &smem)) return TKD_ERR_UNSUPPORTED;
     const dim3 grid((unsigned)moe_grid_x(a, (int)(npad / kMoeCols)), (unsigned)a->slots);
     const int e = moe_dispatch<true>(p, a->fmt, a->by_union != 0, grid, smem, mt, static_cast<cudaStream_t>(stream));
     return e == 0 ? TKD_OK : TKD_ERR_CUDA + e;
