@@ -253,7 +253,8 @@ typedef struct {
     void* out;               /* bf16 [rows, ldo]. gate_up: slot q's I values at q * I, each routing weight * act(x G +
                                 b) * (x U + b); down: the n columns of y = sum over the slots of h_q @ D_q */
     int64_t ldo;
-    void* workspace;         /* down: tkd_moe_workspace bytes, zeroed once by the caller before the first use */
+    void* workspace;         /* down: tkd_moe_workspace bytes, zeroed once by the caller before the first use (the kernel
+                                returns its counters to zero); calls that share one must be ordered on one stream */
     uint64_t workspace_bytes;
     int32_t fmt;             /* TKD_FMT_BFP4, or TKD_FMT_BF16: experts whose values no bfloat4_b stream holds (the K-block
                                 layout, moe8.py:507-527 kblock: shared exponents along K), kept exactly at 2 bytes a weight;
